@@ -1,0 +1,304 @@
+/*
+ * sgk.h — C ABI of the B200-native KV-cache hot path (libsgk.so).
+ *
+ * This is the drop-in boundary for the reference engine's resident KV cache,
+ * decode attention and warm-prefix cache. Every entry point names the
+ * reference interface (file:line inside the reference crate) it replaces.
+ *
+ * Conventions (mirroring the reference's Result<_, InferError> surface,
+ * src/error.rs:12-75):
+ *   - every fallible call returns an int32 status, 0 = SGK_OK; results come
+ *     back through out-pointers; nothing throws or aborts across the boundary;
+ *   - sgk_last_error() returns the thread-local message of the last failure;
+ *   - `stream` arguments are a cudaStream_t passed as void* (NULL = the
+ *     state's own stream); "enqueue" calls only enqueue work and move the
+ *     host-side length cursor at enqueue time, like the reference's encode_*
+ *     methods (src/decode_resident/attention.rs:950-1038); host-pointer calls
+ *     are synchronous;
+ *   - pointers named d_* are device pointers, everything else is host memory;
+ *   - there is no CPU fallback: without a CUDA device sgk_state_create fails.
+ */
+#ifndef SGK_H_
+#define SGK_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes: the reference's InferError variants (src/error.rs:12-75). */
+enum {
+  SGK_OK = 0,
+  SGK_ERR_DIMENSION = 1,    /* InferError::Dimension: shape mismatch, overflow at capacity, empty KV/window */
+  SGK_ERR_CONFIG = 2,       /* InferError::Config: zero dimension, invalid GQA */
+  SGK_ERR_BACKEND = 3,      /* InferError::Metal: wrong element type, null pointer, CUDA failure */
+  SGK_ERR_MEMORY_GUARD = 4, /* InferError::MemoryGuard: budget exceeded / pool out of pages */
+  SGK_ERR_SHAPE = 5,        /* InferError::Shape: linear-state restore mismatch */
+  SGK_ERR_TIMEOUT = 6       /* a bounded device-side wait expired (status word set by a kernel) */
+};
+
+/* KV storage types: GpuElement::{F32,Bf16} (src/decode_resident/arena.rs:26-41)
+ * plus the u8 group-32 affine format (32 codes + bf16 scale + bf16 bias). */
+enum { SGK_KV_F32 = 0, SGK_KV_BF16 = 1, SGK_KV_U8G32 = 2 };
+
+/* Tokens per page. The page is the unit of allocation, sharing and copy. */
+#define SGK_PAGE_TOKENS 16
+
+typedef struct sgk_state sgk_state;       /* DecodeResidentState (src/decode_resident/arena.rs:247-349) */
+typedef struct sgk_pool sgk_pool;         /* block allocator: pages of all layers of one model shape */
+typedef struct sgk_seq sgk_seq;           /* one sequence: block table shared by its layers */
+typedef struct sgk_kv sgk_kv;             /* FullAttentionMetalState: one layer of one sequence */
+typedef struct sgk_batch sgk_batch;       /* sequences decoded together in one launch (one layer) */
+typedef struct sgk_step sgk_step;         /* all layers of a batch: one decode token = one submission */
+typedef struct sgk_linstate sgk_linstate; /* LinearAttentionMetalState of all recurrent layers */
+typedef struct sgk_prefix sgk_prefix;     /* BlockAwarePrefixCache (src/serve/cache.rs:74-219) */
+typedef struct sgk_budget sgk_budget;     /* MemoryGuard (src/memory_guard.rs:155-185,331-370) */
+
+const char* sgk_last_error(void);
+const char* sgk_version(void);
+
+/* ---- state: DecodeResidentState::new (src/decode_resident/arena.rs:247-349) ---- */
+int32_t sgk_state_create(int32_t device, sgk_state** out);
+void sgk_state_destroy(sgk_state* state);
+void* sgk_state_stream(sgk_state* state);
+int32_t sgk_state_sync(sgk_state* state);
+/* Reads and clears the device status word kernels set when a bounded wait expires. */
+int32_t sgk_state_device_status(sgk_state* state, int32_t* status_out);
+
+/* ---- page pool (new design: the reference KV is contiguous, not paged) ---- */
+int32_t sgk_pool_create(sgk_state* state, int32_t layers, int32_t kv_heads, int32_t head_dim,
+                        int32_t dtype, int32_t page_tokens, int64_t num_pages, int32_t max_seqs,
+                        int64_t max_seq_tokens, sgk_pool** out);
+void sgk_pool_destroy(sgk_pool* pool);
+int64_t sgk_pool_num_pages(const sgk_pool* pool);
+int64_t sgk_pool_free_pages(const sgk_pool* pool);
+int64_t sgk_pool_page_bytes(const sgk_pool* pool); /* one page, all layers, K and V */
+int64_t sgk_pool_used_bytes(const sgk_pool* pool);
+/* Fisher-Yates shuffle of the free list (seeded): later reservations get a
+ * non-contiguous block table. */
+int32_t sgk_pool_shuffle_free_list(sgk_pool* pool, uint64_t seed);
+int32_t sgk_pool_page_refcount(const sgk_pool* pool, int64_t page, int32_t* out);
+/* Zero-fills pages when they return to the free list (eviction scrub kernel). */
+int32_t sgk_pool_set_scrub_on_free(sgk_pool* pool, int32_t enabled);
+
+/* ---- sequence: a block table over the pool, shared by the layers ---- */
+int32_t sgk_seq_create(sgk_pool* pool, int64_t capacity_tokens, sgk_seq** out);
+void sgk_seq_destroy(sgk_seq* seq);
+/* Makes rows [0, tokens) addressable: takes pages from the pool and publishes
+ * the block-table entries to the device (synchronous). */
+int32_t sgk_seq_reserve(sgk_seq* seq, int64_t tokens);
+int32_t sgk_seq_block_table(const sgk_seq* seq, int32_t* pages_out, int64_t cap, int64_t* n_out);
+/* Sliding-window layers: returns pages that lie wholly before `row` to the pool. */
+int32_t sgk_seq_release_before(sgk_seq* seq, int64_t row);
+/* FullAttentionMetalState view of (sequence, layer). Owned by the sequence. */
+int32_t sgk_seq_layer(sgk_seq* seq, int32_t layer, int32_t q_heads, sgk_kv** out);
+
+/* ---- KV state: state.full_attention(capacity,q,kv,hd,sampled)
+ *      (src/decode_resident/attention.rs:26-108). Standalone: owns a private
+ *      one-layer pool of ceil(capacity/16) pages. ---- */
+int32_t sgk_kv_create(sgk_state* state, int64_t capacity, int32_t q_heads, int32_t kv_heads,
+                      int32_t head_dim, int32_t dtype, int32_t page_tokens, sgk_kv** out);
+/* Same, with the pool's free list shuffled first (non-contiguous block table). */
+int32_t sgk_kv_create_shuffled(sgk_state* state, int64_t capacity, int32_t q_heads, int32_t kv_heads,
+                               int32_t head_dim, int32_t dtype, uint64_t seed, sgk_kv** out);
+void sgk_kv_destroy(sgk_kv* kv);
+/* kv.{len,capacity,kv_dim,q_heads,kv_heads,head_dim} (attention.rs:486-548) */
+int64_t sgk_kv_len(const sgk_kv* kv);
+int64_t sgk_kv_capacity(const sgk_kv* kv);
+int32_t sgk_kv_kv_dim(const sgk_kv* kv);
+int32_t sgk_kv_q_heads(const sgk_kv* kv);
+int32_t sgk_kv_kv_heads(const sgk_kv* kv);
+int32_t sgk_kv_head_dim(const sgk_kv* kv);
+int32_t sgk_kv_dtype(const sgk_kv* kv);
+int64_t sgk_kv_byte_len(const sgk_kv* kv); /* capacity * kv_dim * storage bytes, K or V */
+/* kv.truncate(len) (attention.rs:501-510): moves the cursor only. */
+int32_t sgk_kv_truncate(sgk_kv* kv, int64_t len);
+/* kv.seed(keys_rows, values_rows, n_rows) (attention.rs:550-602) */
+int32_t sgk_kv_seed_f32(sgk_kv* kv, const float* k, size_t k_len, const float* v, size_t v_len,
+                        int64_t n_rows);
+/* kv.append_row(key, value) (attention.rs:611-644) */
+int32_t sgk_kv_append_row_f32(sgk_kv* kv, const float* k, size_t k_len, const float* v, size_t v_len);
+/* LayerKvCache::append_batch (src/decoder/attention_cache.rs:38-70): n rows at the cursor. */
+int32_t sgk_kv_append_rows_f32(sgk_kv* kv, const float* k, size_t k_len, const float* v, size_t v_len,
+                               int64_t n_rows);
+/* kv.encode_append_kv_with_offsets(enc,k,koff,v,voff) (attention.rs:950-1001):
+ * device-side append of one f32 row; len += 1 at enqueue time. */
+int32_t sgk_kv_enqueue_append(sgk_kv* kv, void* stream, const float* d_k, const float* d_v);
+/* Device-side append of n rows (the prefill-side producer that replaces
+ * append_batch + seed, src/decoder/generation.rs:3338-3361). */
+int32_t sgk_kv_enqueue_append_rows(sgk_kv* kv, void* stream, const float* d_k, const float* d_v,
+                                   int64_t n_rows);
+/* Fused encode_rms_norm_rope_decode on K (attention.rs:297-385) + append:
+ * d_k_raw is the un-normalised K projection; V is appended as is. The rotation
+ * position is the row being written times position_scale. */
+typedef struct {
+  int32_t rope_dims;     /* rotated leading dims of each head (even, <= head_dim) */
+  int32_t frequency_dim; /* exponent denominator (RopeParams::frequency_dim) */
+  float theta;
+  float position_scale;
+  float eps;
+  int32_t interleaved;   /* 0 = rotate-half pairs (i, i+rope_dims/2), 1 = pairs (2i, 2i+1) */
+} sgk_rope;
+int32_t sgk_kv_enqueue_rope_append(sgk_kv* kv, void* stream, const float* d_k_raw, const float* d_v,
+                                   const float* d_knorm_weight, const sgk_rope* rope);
+/* DecodeResidentState::rms_norm_rope_decode (attention.rs:386-444): host in/out. */
+int32_t sgk_rms_norm_rope_decode(sgk_state* state, const float* x, const float* weight,
+                                 int32_t heads, int32_t head_dim, const sgk_rope* rope,
+                                 int64_t position, float* out);
+/* kv.attention_decode_windowed(q, window_start) (attention.rs:661-720): host q/out.
+ * attn_scalar <= 0 means head_dim (scale = 1/sqrt(attn_scalar),
+ * src/decoder/attention_ops.rs:912). */
+int32_t sgk_kv_attention_decode(sgk_kv* kv, const float* q, size_t q_len, int64_t window_start,
+                                float attn_scalar, float* out);
+/* kv.encode_attention_decode_windowed(enc,q,scores,out,ws) (attention.rs:736-835) */
+int32_t sgk_kv_enqueue_attention(sgk_kv* kv, void* stream, const float* d_q, float* d_out,
+                                 int64_t window_start, float attn_scalar);
+/* encode_append_kv + encode_attention_decode_windowed in ONE launch
+ * (the per-layer pair at src/decode_resident/layers.rs:259-288). */
+int32_t sgk_kv_enqueue_append_attention(sgk_kv* kv, void* stream, const float* d_k, const float* d_v,
+                                        const float* d_q, float* d_out, int64_t sliding_window,
+                                        float attn_scalar);
+/* kv.keys()/values() read-back used by the reference's tests (tests.rs:380-478):
+ * the paged GATHER. Rows [row0,row0+n) as contiguous [n, kv_dim] in the storage
+ * type (f32: float, bf16: uint16 bit patterns). For u8 use the _u8 form. */
+int32_t sgk_kv_gather_rows(sgk_kv* kv, int64_t row0, int64_t n, void* k_out, void* v_out);
+int32_t sgk_kv_gather_rows_u8(sgk_kv* kv, int64_t row0, int64_t n, uint8_t* k_codes, uint16_t* k_scale,
+                              uint16_t* k_bias, uint8_t* v_codes, uint16_t* v_scale, uint16_t* v_bias);
+/* Same rows decoded to f32 (bf16 upcast, u8 q*scale+bias, src/quantization.rs:173-179). */
+int32_t sgk_kv_gather_rows_f32(sgk_kv* kv, int64_t row0, int64_t n, float* k_out, float* v_out);
+int32_t sgk_kv_block_table(const sgk_kv* kv, int32_t* pages_out, int64_t cap, int64_t* n_out);
+/* Forces one attention kernel: 0 = automatic, 1 = generic CUDA-core kernel,
+ * 2 = tensor-core paged kernel (errors if the shape does not qualify). */
+int32_t sgk_kv_set_attention_kernel(sgk_kv* kv, int32_t which);
+
+/* ---- batch: n sequences of ONE layer decoded in one launch. The reference's
+ *      multi-stream mode loops the solo path per stream
+ *      (src/decode_resident/duo.rs:97-199); results are per sequence identical
+ *      to decoding each alone. ---- */
+int32_t sgk_batch_create(sgk_state* state, sgk_kv** kvs, int32_t n, sgk_batch** out);
+void sgk_batch_destroy(sgk_batch* batch);
+/* d_k/d_v: [n, kv_dim] f32; d_q/d_out: [n, q_heads*head_dim] f32.
+ * sliding_window 0 = none, else window_start = len.saturating_sub(window)
+ * (src/decoder/attention_ops.rs:915-918), evaluated after the append. */
+int32_t sgk_batch_enqueue_append(sgk_batch* batch, void* stream, const float* d_k, const float* d_v);
+int32_t sgk_batch_enqueue_attention(sgk_batch* batch, void* stream, const float* d_q, float* d_out,
+                                    int64_t sliding_window, float attn_scalar);
+int32_t sgk_batch_enqueue_step(sgk_batch* batch, void* stream, const float* d_k, const float* d_v,
+                               const float* d_q, float* d_out, int64_t sliding_window,
+                               float attn_scalar);
+/* Tuning hooks read by the benchmark: 0 = automatic. */
+int32_t sgk_batch_set_splits(sgk_batch* batch, int32_t splits);
+int32_t sgk_batch_get_splits(const sgk_batch* batch, int32_t* splits_out);
+int32_t sgk_batch_set_kernel(sgk_batch* batch, int32_t which);
+int32_t sgk_batch_last_kernel(const sgk_batch* batch, int32_t* which_out);
+
+/* ---- step: every layer of a batch; one decode token = one stream submission
+ *      (src/decoder/resident/decode.rs:183-458: one command buffer per token). ---- */
+int32_t sgk_step_create(sgk_state* state, sgk_batch** layers, int32_t n_layers, sgk_step** out);
+void sgk_step_destroy(sgk_step* step);
+/* d_k/d_v: [layers, n, kv_dim]; d_q/d_out: [layers, n, q_dim]; sliding_windows:
+ * one entry per layer (NULL = none). */
+int32_t sgk_step_enqueue(sgk_step* step, void* stream, const float* d_k, const float* d_v,
+                         const float* d_q, float* d_out, const int64_t* sliding_windows,
+                         float attn_scalar);
+/* Captures one sgk_step_enqueue into a CUDA graph; each replay is one submission
+ * and advances every layer's cursor by one on the device and on the host. */
+int32_t sgk_step_capture(sgk_step* step, const float* d_k, const float* d_v, const float* d_q,
+                         float* d_out, const int64_t* sliding_windows, float attn_scalar);
+int32_t sgk_step_replay(sgk_step* step, void* stream);
+/* Same step with HOST buffers: copies inputs in, runs, copies outputs back, waits. */
+int32_t sgk_step_run_host(sgk_step* step, const float* k, const float* v, const float* q, float* out,
+                          const int64_t* sliding_windows, float attn_scalar);
+int64_t sgk_step_launches(const sgk_step* step); /* kernels launched so far by this step */
+
+/* ---- linear-attention recurrent state: LinearAttentionMetalState
+ *      (src/metal_backend/mod.rs:507-531) for all recurrent layers of a sequence;
+ *      snapshot_linear_attn_states / restore_linear_attn_states
+ *      (src/metal_backend/linear_attention.rs:3027-3067,3163-3198). ---- */
+int32_t sgk_linstate_create(sgk_state* state, int32_t layers, int64_t conv_len, int64_t ssm_len,
+                            int32_t ssm_bf16, sgk_linstate** out);
+void sgk_linstate_destroy(sgk_linstate* ls);
+int64_t sgk_linstate_bytes(const sgk_linstate* ls); /* estimated_bytes, mod.rs:521-530 */
+int32_t sgk_linstate_write(sgk_linstate* ls, int32_t layer, const float* conv, const float* ssm);
+int32_t sgk_linstate_read(sgk_linstate* ls, int32_t layer, float* conv, float* ssm);
+int32_t sgk_linstate_snapshot(sgk_linstate* ls, void* stream, sgk_linstate** snapshot_out);
+int32_t sgk_linstate_restore(sgk_linstate* ls, void* stream, const sgk_linstate* snapshot);
+void* sgk_linstate_conv_ptr(sgk_linstate* ls, int32_t layer);
+void* sgk_linstate_ssm_ptr(sgk_linstate* ls, int32_t layer);
+
+/* ---- block hashes: BlockHash::{root,for_session,chain} (src/serve/cache.rs:11-47) ---- */
+void sgk_hash_root(uint8_t out[32]);
+void sgk_hash_for_session(const char* key, size_t key_len, int32_t present, uint8_t out[32]);
+void sgk_hash_chain(const uint8_t prev[32], const uint64_t* tokens, size_t n, uint8_t out[32]);
+
+/* ---- warm-prefix cache: BlockAwarePrefixCache (src/serve/cache.rs:74-219) with
+ *      the budget loop of remember_prefix_block (src/serve/state.rs:613-639).
+ *      Entries sit at block boundaries and pin the pages of their prefix; pages
+ *      are shared between entries by reference count, so an entry costs one
+ *      block. pool may be NULL: pure bookkeeping (no device), used to check
+ *      match / insert / eviction order. ---- */
+int32_t sgk_prefix_create(sgk_pool* pool, int64_t block_tokens, int64_t capacity_blocks,
+                          int64_t blocks_per_session, int64_t budget_bytes, sgk_prefix** out);
+void sgk_prefix_destroy(sgk_prefix* pc);
+int64_t sgk_prefix_block_tokens(const sgk_prefix* pc);
+/* match_prefix (cache.rs:121-151): walks full blocks from the root, moves each hit
+ * to the front, returns the deepest. *entry_out = 0 when nothing matched. */
+int32_t sgk_prefix_match(sgk_prefix* pc, const uint8_t root[32], const uint64_t* tokens, size_t n,
+                         int64_t* tokens_out, uint8_t hash_out[32], uint64_t* entry_out);
+/* remember_prefix_block + insert (state.rs:613-639, cache.rs:154-193): snapshots
+ * the first `tokens` rows of `seq` (and `ls` when not NULL) at a block boundary.
+ * Evicts LRU blocks while the budget would be exceeded; if the cache runs empty
+ * first the insert is skipped (*inserted_out = 0). seq may be NULL only when the
+ * cache was created without a pool. */
+int32_t sgk_prefix_insert(sgk_prefix* pc, const uint8_t session[32], const uint8_t hash[32],
+                          int64_t tokens, sgk_seq* seq, sgk_linstate* ls, void* stream,
+                          int32_t* inserted_out);
+/* copy_prompt_state_metal_snapshot + restore_prompt_state_metal
+ * (src/decoder/generation.rs:2851-2892): makes `seq` hold the entry's rows.
+ * mode 0 = physical copy into pages owned by the sequence (the reference's
+ * never-aliased rule), 1 = share the pages by reference (copy-on-write). */
+int32_t sgk_prefix_restore(sgk_prefix* pc, uint64_t entry, sgk_seq* seq, sgk_linstate* ls,
+                           void* stream, int32_t mode, int64_t* bytes_copied_out);
+/* evict_lru_block (cache.rs:196-198): *evicted_out = 0 when the cache is empty. */
+int32_t sgk_prefix_evict_lru(sgk_prefix* pc, int32_t* evicted_out, int64_t* bytes_out);
+int64_t sgk_prefix_bytes(const sgk_prefix* pc); /* estimated_bytes (cache.rs:200-203) */
+int64_t sgk_prefix_len(const sgk_prefix* pc);
+int64_t sgk_prefix_session_count(const sgk_prefix* pc, const uint8_t session[32]);
+/* Trace hook: which = 0 live entries front-to-rear, 1 = every entry that left, in order. */
+int64_t sgk_prefix_dump(const sgk_prefix* pc, int32_t which, int64_t cap, uint8_t* sessions,
+                        uint8_t* hashes, int64_t* tokens);
+/* Decoder-internal longest-prefix selection (src/decoder/generation.rs:190-204). */
+int64_t sgk_longest_prefix_entry_index(const uint64_t* flat_tokens, const size_t* lens,
+                                       size_t n_entries, const uint64_t* prompt, size_t n);
+
+/* ---- memory budget: MemoryGuard::{check_allocation,projection_over_limit}
+ *      (src/memory_guard.rs:331-370) over device bytes. A cap of 0 is "absent". ---- */
+int32_t sgk_budget_create(uint64_t static_cap, uint64_t total_memory, uint64_t headroom_bytes,
+                          uint64_t device_cap, sgk_budget** out);
+void sgk_budget_destroy(sgk_budget* b);
+void sgk_budget_set_usage(sgk_budget* b, uint64_t current, uint64_t reserved);
+int32_t sgk_budget_limit(const sgk_budget* b, uint64_t* limit_out); /* 1 when a limit exists */
+/* SGK_OK when accepted, SGK_ERR_MEMORY_GUARD when projected > limit. */
+int32_t sgk_budget_check_allocation(const sgk_budget* b, uint64_t requested, uint64_t* projected_out,
+                                    uint64_t* available_out);
+
+/* ---- utilities used by the tests and the benchmark ---- */
+/* Device fill with the counter-based approximate-normal generator (integer only,
+ * bit-identical to the host restatement used for parity inputs). */
+int32_t sgk_util_fill_normal(sgk_state* state, void* stream, float* d_out, int64_t n, uint64_t seed,
+                             uint64_t stream_id, uint64_t index0);
+int32_t sgk_util_malloc(sgk_state* state, size_t bytes, void** d_out);
+int32_t sgk_util_free(sgk_state* state, void* d_ptr);
+int32_t sgk_util_h2d(sgk_state* state, void* d_dst, const void* src, size_t bytes);
+int32_t sgk_util_d2h(sgk_state* state, void* dst, const void* d_src, size_t bytes);
+/* Block copy kernel on raw device ranges (the prefix-restore data mover). */
+int32_t sgk_util_copy_blocks(sgk_state* state, void* stream, void* d_dst, const void* d_src,
+                             const int32_t* dst_pages, const int32_t* src_pages, int32_t n_pages,
+                             int64_t page_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SGK_H_ */

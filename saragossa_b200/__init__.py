@@ -1,0 +1,12 @@
+"""saragossa_b200: the B200-native KV-cache hot path behind the reference's
+resident-cache API (C ABI in include/sgk.h, CUDA kernels in csrc/)."""
+from .resident import (KV_BF16, KV_F32, KV_U8G32, PAGE_TOKENS, Batch, DecodeResidentState, DeviceBuffer,
+                       FullAttentionState, InferError, LinearAttentionState, PagePool, Rope, Sequence, Step,
+                       make_rope)
+from .prefix import BlockAwarePrefixCache, BlockHash, MemoryGuard, PrefixBlockHit, longest_prefix_entry_index
+
+__all__ = [
+    "KV_F32", "KV_BF16", "KV_U8G32", "PAGE_TOKENS", "Batch", "DecodeResidentState", "DeviceBuffer",
+    "FullAttentionState", "InferError", "LinearAttentionState", "PagePool", "Rope", "Sequence", "Step", "make_rope",
+    "BlockAwarePrefixCache", "BlockHash", "MemoryGuard", "PrefixBlockHit", "longest_prefix_entry_index",
+]

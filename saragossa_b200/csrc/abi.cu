@@ -1,0 +1,1232 @@
+// extern "C" surface of libsgk: argument validation in the reference's error
+// vocabulary, then the host objects of host.h. Declared in include/sgk.h.
+#include <algorithm>
+#include <cstring>
+#include <random>
+
+#include "host.h"
+
+using namespace sgk;
+
+struct sgk_state : State {};
+struct sgk_pool : Pool {};
+struct sgk_seq : Seq {};
+struct sgk_kv : Kv {};
+struct sgk_batch : Batch {};
+struct sgk_step : Step {};
+struct sgk_linstate : LinState {};
+struct sgk_prefix : Prefix {};
+struct sgk_budget : Budget {};
+
+namespace sgk {
+int create_batch(State* st, Kv** kvs, int n, Batch** out);
+}
+
+extern "C" {
+
+const char* sgk_last_error(void) { return last_error_cstr(); }
+const char* sgk_version(void) { return "sgk 0.1 (sm_100a)"; }
+
+// ------------------------------------------------------------------ state
+int32_t sgk_state_create(int32_t device, sgk_state** out) {
+  if (!out) return fail(SGK_ERR_BACKEND, "state_create: null out pointer");
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0)
+    return fail(SGK_ERR_BACKEND, "no CUDA device: %s (this library has no CPU path)",
+                e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0");
+  if (device < 0 || device >= count) return fail(SGK_ERR_CONFIG, "device %d out of range [0,%d)", device, count);
+  SGK_CUDA(cudaSetDevice(device));
+  auto st = std::make_unique<sgk_state>();
+  st->device = device;
+  cudaDeviceProp prop;
+  SGK_CUDA(cudaGetDeviceProperties(&prop, device));
+  st->sm_count = prop.multiProcessorCount;
+  if (prop.major < 10)
+    return fail(SGK_ERR_BACKEND, "device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major,
+                prop.minor);
+  SGK_CUDA(cudaStreamCreateWithFlags(&st->stream, cudaStreamNonBlocking));
+  SGK_CUDA(cudaMalloc(&st->d_status, sizeof(int32_t)));
+  SGK_CUDA(cudaMemset(st->d_status, 0, sizeof(int32_t)));
+  SGK_CUDA(attention_mma_configure());
+  *out = st.release();
+  return SGK_OK;
+}
+
+void sgk_state_destroy(sgk_state* st) {
+  if (!st) return;
+  cudaSetDevice(st->device);
+  cudaStreamSynchronize(st->stream);
+  if (st->d_status) cudaFree(st->d_status);
+  if (st->stream) cudaStreamDestroy(st->stream);
+  delete st;
+}
+
+void* sgk_state_stream(sgk_state* st) { return st ? st->stream : nullptr; }
+
+int32_t sgk_state_sync(sgk_state* st) {
+  if (!st) return fail(SGK_ERR_BACKEND, "null state");
+  SGK_CUDA(cudaStreamSynchronize(st->stream));
+  return SGK_OK;
+}
+
+int32_t sgk_state_device_status(sgk_state* st, int32_t* status_out) {
+  if (!st || !status_out) return fail(SGK_ERR_BACKEND, "null argument");
+  SGK_CUDA(cudaStreamSynchronize(st->stream));
+  SGK_CUDA(cudaMemcpy(status_out, st->d_status, sizeof(int32_t), cudaMemcpyDeviceToHost));
+  if (*status_out != 0) SGK_CUDA(cudaMemset(st->d_status, 0, sizeof(int32_t)));
+  return SGK_OK;
+}
+
+static int check_device_status(State* st) {
+  int32_t status = 0;
+  SGK_CUDA(cudaMemcpy(&status, st->d_status, sizeof(int32_t), cudaMemcpyDeviceToHost));
+  if (status == 0) return SGK_OK;
+  cudaMemset(st->d_status, 0, sizeof(int32_t));
+  if (status == DEV_ERR_WAIT_TIMEOUT) return fail(SGK_ERR_TIMEOUT, "a bounded device-side wait expired");
+  return fail(SGK_ERR_BACKEND, "kernel reported status %d (block-table entry out of range)", status);
+}
+
+// ------------------------------------------------------------------ pool
+int32_t sgk_pool_create(sgk_state* st, int32_t layers, int32_t kv_heads, int32_t head_dim, int32_t dtype,
+                        int32_t page_tokens, int64_t num_pages, int32_t max_seqs, int64_t max_seq_tokens,
+                        sgk_pool** out) {
+  if (!out) return fail(SGK_ERR_BACKEND, "pool_create: null out pointer");
+  if (layers <= 0 || kv_heads <= 0 || head_dim <= 0 || num_pages <= 0 || max_seqs <= 0 || max_seq_tokens <= 0)
+    return fail(SGK_ERR_CONFIG, "pool: zero dimension");
+  if (page_tokens != SGK_PAGE_TOKENS) return fail(SGK_ERR_CONFIG, "pool: page_tokens must be %d", SGK_PAGE_TOKENS);
+  if (dtype < SGK_KV_F32 || dtype > SGK_KV_U8G32) return fail(SGK_ERR_BACKEND, "pool: unknown KV element type %d", dtype);
+  if (dtype == SGK_KV_U8G32 && head_dim % QGROUP != 0)
+    return fail(SGK_ERR_CONFIG, "u8 KV needs head_dim to be a multiple of %d", QGROUP);
+  if (head_dim > 512) return fail(SGK_ERR_CONFIG, "head_dim %d > 512 is not supported", head_dim);
+  if (dtype != SGK_KV_U8G32 && (int64_t(head_dim) * (dtype == SGK_KV_F32 ? 4 : 2) * PAGE_TOKENS) % 16 != 0)
+    return fail(SGK_ERR_CONFIG, "head_dim %d gives tiles that are not 16-byte multiples", head_dim);
+  auto p = std::make_unique<sgk_pool>();
+  p->st = st;
+  p->layers = layers;
+  p->kv_heads = kv_heads;
+  p->head_dim = head_dim;
+  p->dtype = dtype;
+  p->num_pages = num_pages;
+  p->max_seqs = max_seqs;
+  p->max_seq_tokens = max_seq_tokens;
+  p->table_stride = static_cast<int>((max_seq_tokens + PAGE_TOKENS - 1) / PAGE_TOKENS);
+  p->tile_b = tile_bytes(dtype, head_dim);
+  p->layer_b = int64_t(kv_heads) * 2 * p->tile_b;
+  p->page_b = int64_t(layers) * p->layer_b;
+  p->refcount.assign(static_cast<size_t>(num_pages), 0);
+  p->free_list.resize(static_cast<size_t>(num_pages));
+  for (int64_t i = 0; i < num_pages; ++i) p->free_list[static_cast<size_t>(i)] = static_cast<int32_t>(num_pages - 1 - i);
+  for (int s = max_seqs - 1; s >= 0; --s) p->free_slots.push_back(s);
+  if (st) {
+    SGK_CUDA(cudaSetDevice(st->device));
+    size_t bytes = static_cast<size_t>(p->page_b) * static_cast<size_t>(num_pages);
+    cudaError_t e = cudaMalloc(&p->d_base, bytes);
+    if (e != cudaSuccess)
+      return fail(SGK_ERR_MEMORY_GUARD, "pool of %zu bytes does not fit the device: %s", bytes, cudaGetErrorString(e));
+    SGK_CUDA(cudaMemset(p->d_base, 0, bytes));
+    size_t tbytes = size_t(max_seqs) * p->table_stride * sizeof(int32_t);
+    SGK_CUDA(cudaMalloc(&p->d_tables, tbytes));
+    SGK_CUDA(cudaMemset(p->d_tables, 0xff, tbytes));
+    SGK_CUDA(cudaMalloc(&p->d_lens, size_t(max_seqs) * layers * sizeof(int32_t)));
+    SGK_CUDA(cudaMemset(p->d_lens, 0, size_t(max_seqs) * layers * sizeof(int32_t)));
+  }
+  *out = p.release();
+  return SGK_OK;
+}
+
+void sgk_pool_destroy(sgk_pool* p) {
+  if (!p) return;
+  if (p->st) {
+    cudaSetDevice(p->st->device);
+    cudaStreamSynchronize(p->st->stream);
+  }
+  if (p->d_base) cudaFree(p->d_base);
+  if (p->d_tables) cudaFree(p->d_tables);
+  if (p->d_lens) cudaFree(p->d_lens);
+  if (p->d_page_list) cudaFree(p->d_page_list);
+  delete p;
+}
+
+int64_t sgk_pool_num_pages(const sgk_pool* p) { return p ? p->num_pages : 0; }
+int64_t sgk_pool_free_pages(const sgk_pool* p) { return p ? static_cast<int64_t>(p->free_list.size()) : 0; }
+int64_t sgk_pool_page_bytes(const sgk_pool* p) { return p ? p->page_b : 0; }
+int64_t sgk_pool_used_bytes(const sgk_pool* p) { return p ? p->used_pages() * p->page_b : 0; }
+
+int32_t sgk_pool_shuffle_free_list(sgk_pool* p, uint64_t seed) {
+  if (!p) return fail(SGK_ERR_BACKEND, "null pool");
+  // Fisher-Yates with splitmix64 draws
+  uint64_t x = seed;
+  auto next = [&]() {
+    x += 0x9E3779B97F4A7C15ull;
+    uint64_t z = x;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+  };
+  for (size_t i = p->free_list.size(); i > 1; --i) std::swap(p->free_list[i - 1], p->free_list[next() % i]);
+  return SGK_OK;
+}
+
+int32_t sgk_pool_page_refcount(const sgk_pool* p, int64_t page, int32_t* out) {
+  if (!p || !out) return fail(SGK_ERR_BACKEND, "null argument");
+  if (page < 0 || page >= p->num_pages) return fail(SGK_ERR_DIMENSION, "page %lld out of range", (long long)page);
+  *out = p->refcount[static_cast<size_t>(page)];
+  return SGK_OK;
+}
+
+int32_t sgk_pool_set_scrub_on_free(sgk_pool* p, int32_t enabled) {
+  if (!p) return fail(SGK_ERR_BACKEND, "null pool");
+  p->scrub_on_free = enabled != 0;
+  return SGK_OK;
+}
+
+// ------------------------------------------------------------------ seq
+int32_t sgk_seq_create(sgk_pool* p, int64_t capacity_tokens, sgk_seq** out) {
+  if (!p || !out) return fail(SGK_ERR_BACKEND, "seq_create: null argument");
+  if (capacity_tokens <= 0) return fail(SGK_ERR_CONFIG, "sequence capacity must be positive");
+  if (capacity_tokens > p->max_seq_tokens)
+    return fail(SGK_ERR_CONFIG, "sequence capacity %lld > pool max_seq_tokens %lld", (long long)capacity_tokens,
+                (long long)p->max_seq_tokens);
+  if (p->free_slots.empty()) return fail(SGK_ERR_MEMORY_GUARD, "pool holds its maximum of %d sequences", p->max_seqs);
+  auto s = std::make_unique<sgk_seq>();
+  s->pool = p;
+  s->slot = p->free_slots.back();
+  p->free_slots.pop_back();
+  s->capacity = capacity_tokens;
+  s->len.assign(static_cast<size_t>(p->layers), 0);
+  if (!p->host_only()) {
+    cudaStream_t stream = p->st->stream;
+    for (int l = 0; l < p->layers; ++l) {
+      int rc = s->set_len(l, 0, stream);
+      if (rc != SGK_OK) return rc;
+    }
+    SGK_CUDA(cudaStreamSynchronize(stream));
+  }
+  p->live_seqs += 1;
+  *out = s.release();
+  return SGK_OK;
+}
+
+void sgk_seq_destroy(sgk_seq* s) {
+  if (!s) return;
+  Pool* p = s->pool;
+  if (!p->host_only()) {
+    cudaSetDevice(p->st->device);
+    cudaStreamSynchronize(p->st->stream);
+  }
+  s->views.clear();
+  s->release_all();
+  if (!p->host_only()) p->flush_scrub(p->st->stream);
+  p->free_slots.push_back(s->slot);
+  p->live_seqs -= 1;
+  delete s;
+}
+
+int32_t sgk_seq_reserve(sgk_seq* s, int64_t tokens) {
+  if (!s) return fail(SGK_ERR_BACKEND, "null sequence");
+  return s->reserve(tokens);
+}
+
+int32_t sgk_seq_block_table(const sgk_seq* s, int32_t* pages_out, int64_t cap, int64_t* n_out) {
+  if (!s || !n_out) return fail(SGK_ERR_BACKEND, "null argument");
+  *n_out = static_cast<int64_t>(s->pages.size());
+  if (pages_out)
+    for (int64_t i = 0; i < std::min<int64_t>(cap, *n_out); ++i) pages_out[i] = s->pages[static_cast<size_t>(i)];
+  return SGK_OK;
+}
+
+int32_t sgk_seq_release_before(sgk_seq* s, int64_t row) {
+  if (!s) return fail(SGK_ERR_BACKEND, "null sequence");
+  if (row < 0) return fail(SGK_ERR_DIMENSION, "negative row");
+  if (!s->pool->host_only()) SGK_CUDA(cudaStreamSynchronize(s->pool->st->stream));
+  return s->release_before(row);
+}
+
+int32_t sgk_seq_layer(sgk_seq* s, int32_t layer, int32_t q_heads, sgk_kv** out) {
+  if (!s || !out) return fail(SGK_ERR_BACKEND, "null argument");
+  if (layer < 0 || layer >= s->pool->layers) return fail(SGK_ERR_DIMENSION, "layer %d out of range", layer);
+  if (q_heads <= 0) return fail(SGK_ERR_CONFIG, "FullAttentionState: zero dimension");
+  if (q_heads % s->pool->kv_heads != 0)
+    return fail(SGK_ERR_CONFIG, "invalid GQA: q_heads=%d is not a multiple of kv_heads=%d", q_heads, s->pool->kv_heads);
+  auto kv = std::make_unique<sgk_kv>();
+  kv->st = s->pool->st;
+  kv->seq = s;
+  kv->layer = layer;
+  kv->q_heads = q_heads;
+  *out = kv.get();
+  s->views.emplace_back(kv.release());
+  return SGK_OK;
+}
+
+// ------------------------------------------------------------------ kv
+static int32_t kv_create_impl(sgk_state* st, int64_t capacity, int32_t q_heads, int32_t kv_heads, int32_t head_dim,
+                              int32_t dtype, int32_t page_tokens, bool shuffle, uint64_t seed, sgk_kv** out) {
+  if (!st || !out) return fail(SGK_ERR_BACKEND, "kv_create: null argument");
+  // src/decode_resident/attention.rs:64-74
+  if (capacity <= 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0)
+    return fail(SGK_ERR_CONFIG, "FullAttentionState: zero dimension");
+  if (q_heads % kv_heads != 0)
+    return fail(SGK_ERR_CONFIG, "invalid GQA: q_heads=%d is not a multiple of kv_heads=%d", q_heads, kv_heads);
+  int64_t pages = (capacity + PAGE_TOKENS - 1) / PAGE_TOKENS;
+  sgk_pool* pool = nullptr;
+  SGK_TRY(sgk_pool_create(st, 1, kv_heads, head_dim, dtype, page_tokens, pages, 1, pages * PAGE_TOKENS, &pool));
+  std::unique_ptr<Pool> pool_owner(pool);
+  if (shuffle) sgk_pool_shuffle_free_list(pool, seed);
+  sgk_seq* seq = nullptr;
+  SGK_TRY(sgk_seq_create(pool, capacity, &seq));
+  std::unique_ptr<Seq> seq_owner(seq);
+  SGK_TRY(seq->reserve(capacity));  // the reference allocates the whole capacity up front
+  auto kv = std::make_unique<sgk_kv>();
+  kv->st = st;
+  kv->seq = seq;
+  kv->layer = 0;
+  kv->q_heads = q_heads;
+  kv->owned_pool = std::move(pool_owner);
+  kv->owned_seq = std::move(seq_owner);
+  *out = kv.release();
+  return SGK_OK;
+}
+
+int32_t sgk_kv_create(sgk_state* st, int64_t capacity, int32_t q_heads, int32_t kv_heads, int32_t head_dim,
+                      int32_t dtype, int32_t page_tokens, sgk_kv** out) {
+  return kv_create_impl(st, capacity, q_heads, kv_heads, head_dim, dtype, page_tokens, false, 0, out);
+}
+
+int32_t sgk_kv_create_shuffled(sgk_state* st, int64_t capacity, int32_t q_heads, int32_t kv_heads, int32_t head_dim,
+                               int32_t dtype, uint64_t seed, sgk_kv** out) {
+  return kv_create_impl(st, capacity, q_heads, kv_heads, head_dim, dtype, SGK_PAGE_TOKENS, true, seed, out);
+}
+
+void sgk_kv_destroy(sgk_kv* kv) {
+  if (!kv) return;
+  if (!kv->owned_seq) return;  // views belong to their sequence
+  cudaSetDevice(kv->st->device);
+  cudaStreamSynchronize(kv->st->stream);
+  kv->self_batch.reset();
+  Pool* pool = kv->owned_pool.release();
+  Seq* seq = kv->owned_seq.release();
+  seq->release_all();
+  delete static_cast<sgk_seq*>(seq);
+  sgk_pool_destroy(static_cast<sgk_pool*>(pool));
+  delete kv;
+}
+
+int64_t sgk_kv_len(const sgk_kv* kv) { return kv ? kv->len() : 0; }
+int64_t sgk_kv_capacity(const sgk_kv* kv) { return kv ? kv->seq->capacity : 0; }
+int32_t sgk_kv_kv_dim(const sgk_kv* kv) { return kv ? kv->kv_dim() : 0; }
+int32_t sgk_kv_q_heads(const sgk_kv* kv) { return kv ? kv->q_heads : 0; }
+int32_t sgk_kv_kv_heads(const sgk_kv* kv) { return kv ? kv->pool()->kv_heads : 0; }
+int32_t sgk_kv_head_dim(const sgk_kv* kv) { return kv ? kv->pool()->head_dim : 0; }
+int32_t sgk_kv_dtype(const sgk_kv* kv) { return kv ? kv->pool()->dtype : 0; }
+int64_t sgk_kv_byte_len(const sgk_kv* kv) {
+  if (!kv) return 0;
+  return kv->seq->capacity * kv->pool()->kv_heads * row_head_bytes(kv->pool()->dtype, kv->pool()->head_dim);
+}
+
+int32_t sgk_kv_truncate(sgk_kv* kv, int64_t len) {
+  if (!kv) return fail(SGK_ERR_BACKEND, "null KV state");
+  // src/decode_resident/attention.rs:501-510: only len > capacity is an error
+  if (len < 0 || len > kv->seq->capacity)
+    return fail(SGK_ERR_DIMENSION, "truncate KV %lld > capacity %lld", (long long)len, (long long)kv->seq->capacity);
+  SGK_TRY(kv->seq->reserve(len));
+  if (kv->pool()->host_only()) {
+    kv->seq->len[kv->layer] = len;
+    return SGK_OK;
+  }
+  SGK_TRY(kv->seq->set_len(kv->layer, len, kv->st->stream));
+  SGK_CUDA(cudaStreamSynchronize(kv->st->stream));
+  return SGK_OK;
+}
+
+static int32_t append_rows_host(sgk_kv* kv, const float* k, size_t k_len, const float* v, size_t v_len, int64_t n_rows,
+                                bool reset) {
+  const size_t kv_dim = static_cast<size_t>(kv->kv_dim());
+  const size_t cells = static_cast<size_t>(n_rows) * kv_dim;
+  if (!k || !v) return fail(SGK_ERR_BACKEND, "null host pointer");
+  if (k_len != cells || v_len != cells)
+    return fail(SGK_ERR_DIMENSION, "KV rows: expected %zu (=%lld x %zu), got keys=%zu values=%zu", cells,
+                (long long)n_rows, kv_dim, k_len, v_len);
+  cudaStream_t stream = kv->st->stream;
+  if (reset) SGK_TRY(kv->seq->set_len(kv->layer, 0, stream));
+  if (n_rows == 0) {
+    SGK_CUDA(cudaStreamSynchronize(stream));
+    return SGK_OK;
+  }
+  SGK_TRY(kv->ensure_self_batch());
+  // stage in pieces so a long prefill needs no matching device buffer
+  const int64_t piece_rows = std::max<int64_t>(1, std::min<int64_t>(n_rows, (64 << 20) / (kv_dim * 4)));
+  SGK_TRY(kv->ensure_io(2 * static_cast<size_t>(piece_rows) * kv_dim * sizeof(float)));
+  float* d_k = kv->d_io;
+  float* d_v = kv->d_io + static_cast<size_t>(piece_rows) * kv_dim;
+  for (int64_t done = 0; done < n_rows; done += piece_rows) {
+    int64_t rows = std::min(piece_rows, n_rows - done);
+    size_t bytes = static_cast<size_t>(rows) * kv_dim * sizeof(float);
+    SGK_CUDA(cudaMemcpyAsync(d_k, k + done * kv_dim, bytes, cudaMemcpyHostToDevice, stream));
+    SGK_CUDA(cudaMemcpyAsync(d_v, v + done * kv_dim, bytes, cudaMemcpyHostToDevice, stream));
+    SGK_TRY(kv->self_batch->enqueue_append(stream, d_k, d_v, static_cast<int>(rows), nullptr, nullptr));
+    SGK_CUDA(cudaStreamSynchronize(stream));
+  }
+  return check_device_status(kv->st);
+}
+
+int32_t sgk_kv_seed_f32(sgk_kv* kv, const float* k, size_t k_len, const float* v, size_t v_len, int64_t n_rows) {
+  if (!kv) return fail(SGK_ERR_BACKEND, "null KV state");
+  // src/decode_resident/attention.rs:555-572
+  if (n_rows < 0 || n_rows > kv->seq->capacity)
+    return fail(SGK_ERR_DIMENSION, "seed KV %lld > capacity %lld", (long long)n_rows, (long long)kv->seq->capacity);
+  const size_t cells = static_cast<size_t>(n_rows) * kv->kv_dim();
+  if (k_len != cells || v_len != cells)
+    return fail(SGK_ERR_DIMENSION, "seed KV: expected %zu (=%lld x %d), got keys=%zu values=%zu", cells,
+                (long long)n_rows, kv->kv_dim(), k_len, v_len);
+  int64_t saved = kv->len();
+  kv->seq->len[kv->layer] = 0;
+  int rc = append_rows_host(kv, k, k_len, v, v_len, n_rows, true);
+  if (rc != SGK_OK && kv->len() == 0) kv->seq->len[kv->layer] = saved;
+  return rc;
+}
+
+int32_t sgk_kv_append_row_f32(sgk_kv* kv, const float* k, size_t k_len, const float* v, size_t v_len) {
+  if (!kv) return fail(SGK_ERR_BACKEND, "null KV state");
+  // src/decode_resident/attention.rs:612-625: wrong length, then overflow
+  if (k_len != static_cast<size_t>(kv->kv_dim()) || v_len != static_cast<size_t>(kv->kv_dim()))
+    return fail(SGK_ERR_DIMENSION, "append KV: expected %d, got key=%zu value=%zu", kv->kv_dim(), k_len, v_len);
+  if (kv->len() >= kv->seq->capacity)
+    return fail(SGK_ERR_DIMENSION, "append KV: capacity %lld reached (overflow)", (long long)kv->seq->capacity);
+  return append_rows_host(kv, k, k_len, v, v_len, 1, false);
+}
+
+int32_t sgk_kv_append_rows_f32(sgk_kv* kv, const float* k, size_t k_len, const float* v, size_t v_len, int64_t n_rows) {
+  if (!kv) return fail(SGK_ERR_BACKEND, "null KV state");
+  // LayerKvCache::append_batch (src/decoder/attention_cache.rs:47-58): seq > 0
+  if (n_rows <= 0) return fail(SGK_ERR_DIMENSION, "append_batch needs at least one row");
+  if (kv->len() + n_rows > kv->seq->capacity)
+    return fail(SGK_ERR_DIMENSION, "append KV: capacity %lld reached (overflow)", (long long)kv->seq->capacity);
+  return append_rows_host(kv, k, k_len, v, v_len, n_rows, false);
+}
+
+int32_t sgk_kv_enqueue_append(sgk_kv* kv, void* stream, const float* d_k, const float* d_v) {
+  if (!kv) return fail(SGK_ERR_BACKEND, "null KV state");
+  SGK_TRY(kv->ensure_self_batch());
+  return kv->self_batch->enqueue_append(kv->st->pick(stream), d_k, d_v, 1, nullptr, nullptr);
+}
+
+int32_t sgk_kv_enqueue_append_rows(sgk_kv* kv, void* stream, const float* d_k, const float* d_v, int64_t n_rows) {
+  if (!kv) return fail(SGK_ERR_BACKEND, "null KV state");
+  if (n_rows <= 0) return fail(SGK_ERR_DIMENSION, "append_batch needs at least one row");
+  SGK_TRY(kv->ensure_self_batch());
+  return kv->self_batch->enqueue_append(kv->st->pick(stream), d_k, d_v, static_cast<int>(n_rows), nullptr, nullptr);
+}
+
+static int32_t check_rope(const sgk_rope* rope, int head_dim, RopeArgs* out) {
+  if (!rope) return fail(SGK_ERR_BACKEND, "null rope parameters");
+  // src/decoder/attention_ops.rs:719-724
+  if (rope->rope_dims <= 0 || rope->rope_dims > head_dim || rope->rope_dims % 2 != 0)
+    return fail(SGK_ERR_DIMENSION, "RMSNorm/RoPE rope_dims %d invalid for head_dim %d", rope->rope_dims, head_dim);
+  if (rope->theta <= 0.0f) return fail(SGK_ERR_DIMENSION, "RoPE base_theta invalid: %f", rope->theta);
+  if (rope->frequency_dim <= 0) return fail(SGK_ERR_DIMENSION, "RoPE frequency_dim invalid");
+  out->rope_dims = rope->rope_dims;
+  out->frequency_dim = rope->frequency_dim;
+  out->theta = rope->theta;
+  out->position_scale = rope->position_scale;
+  out->eps = rope->eps;
+  out->interleaved = rope->interleaved;
+  return SGK_OK;
+}
+
+int32_t sgk_kv_enqueue_rope_append(sgk_kv* kv, void* stream, const float* d_k_raw, const float* d_v,
+                                   const float* d_knorm_weight, const sgk_rope* rope) {
+  if (!kv) return fail(SGK_ERR_BACKEND, "null KV state");
+  if (!d_knorm_weight) return fail(SGK_ERR_BACKEND, "null norm weight");
+  RopeArgs r;
+  SGK_TRY(check_rope(rope, kv->pool()->head_dim, &r));
+  SGK_TRY(kv->ensure_self_batch());
+  return kv->self_batch->enqueue_append(kv->st->pick(stream), d_k_raw, d_v, 1, &r, d_knorm_weight);
+}
+
+int32_t sgk_rms_norm_rope_decode(sgk_state* st, const float* x, const float* weight, int32_t heads, int32_t head_dim,
+                                 const sgk_rope* rope, int64_t position, float* out) {
+  if (!st || !x || !weight || !out) return fail(SGK_ERR_BACKEND, "null argument");
+  if (heads <= 0 || head_dim <= 0 || head_dim > 512)
+    return fail(SGK_ERR_DIMENSION, "RMSNorm/RoPE heads invalid: heads=%d, head_dim=%d", heads, head_dim);
+  RopeArgs r;
+  SGK_TRY(check_rope(rope, head_dim, &r));
+  size_t n = size_t(heads) * head_dim;
+  float* d = nullptr;
+  SGK_CUDA(cudaMalloc(&d, (2 * n + head_dim) * sizeof(float)));
+  float *d_x = d, *d_out = d + n, *d_w = d + 2 * n;
+  cudaStream_t stream = st->stream;
+  AppendArgs a{};
+  a.pool.kv_heads = heads;
+  a.pool.head_dim = head_dim;
+  a.pool.layers = 1;
+  a.k = d_x;
+  a.v = d_x;
+  a.n_rows = 1;
+  a.row0 = position;
+  a.use_device_len = 0;
+  a.bump_len = 0;
+  a.has_rope = 1;
+  a.knorm_w = d_w;
+  a.rope = r;
+  a.out_k = d_out;
+  a.status = st->d_status;
+  int32_t zero_len = 0;
+  (void)zero_len;
+  // lens is dereferenced only when use_device_len is set; give it a valid word anyway
+  a.pool.lens = st->d_status;
+  cudaError_t e = cudaMemcpyAsync(d_x, x, n * sizeof(float), cudaMemcpyHostToDevice, stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(d_w, weight, head_dim * sizeof(float), cudaMemcpyHostToDevice, stream);
+  if (e == cudaSuccess) e = launch_append_rows(a, 1, stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(out, d_out, n * sizeof(float), cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  cudaFree(d);
+  st->launches += 1;
+  if (e != cudaSuccess) return fail(SGK_ERR_BACKEND, "rms_norm_rope_decode failed: %s", cudaGetErrorString(e));
+  return SGK_OK;
+}
+
+int32_t sgk_kv_attention_decode(sgk_kv* kv, const float* q, size_t q_len, int64_t window_start, float attn_scalar,
+                                float* out) {
+  if (!kv) return fail(SGK_ERR_BACKEND, "null KV state");
+  if (!q || !out) return fail(SGK_ERR_BACKEND, "null host pointer");
+  // src/decode_resident/attention.rs:683-698
+  if (kv->len() == 0) return fail(SGK_ERR_DIMENSION, "attention_decode on an empty KV");
+  const size_t q_dim = static_cast<size_t>(kv->q_dim());
+  if (q_len != q_dim) return fail(SGK_ERR_DIMENSION, "attention_decode: q expected [%zu], got %zu", q_dim, q_len);
+  SGK_TRY(kv->ensure_self_batch());
+  SGK_TRY(kv->ensure_io(2 * q_dim * sizeof(float)));
+  cudaStream_t stream = kv->st->stream;
+  float* d_q = kv->d_io;
+  float* d_out = kv->d_io + q_dim;
+  SGK_CUDA(cudaMemcpyAsync(d_q, q, q_dim * sizeof(float), cudaMemcpyHostToDevice, stream));
+  SGK_TRY(kv->self_batch->enqueue_attention(stream, d_q, d_out, window_start, 0, attn_scalar, nullptr, nullptr));
+  SGK_CUDA(cudaMemcpyAsync(out, d_out, q_dim * sizeof(float), cudaMemcpyDeviceToHost, stream));
+  SGK_CUDA(cudaStreamSynchronize(stream));
+  return check_device_status(kv->st);
+}
+
+int32_t sgk_kv_enqueue_attention(sgk_kv* kv, void* stream, const float* d_q, float* d_out, int64_t window_start,
+                                 float attn_scalar) {
+  if (!kv) return fail(SGK_ERR_BACKEND, "null KV state");
+  SGK_TRY(kv->ensure_self_batch());
+  return kv->self_batch->enqueue_attention(kv->st->pick(stream), d_q, d_out, window_start, 0, attn_scalar, nullptr,
+                                           nullptr);
+}
+
+int32_t sgk_kv_enqueue_append_attention(sgk_kv* kv, void* stream, const float* d_k, const float* d_v,
+                                        const float* d_q, float* d_out, int64_t sliding_window, float attn_scalar) {
+  if (!kv) return fail(SGK_ERR_BACKEND, "null KV state");
+  if (!d_k || !d_v) return fail(SGK_ERR_BACKEND, "append: null device pointer");
+  if (sliding_window < 0) return fail(SGK_ERR_DIMENSION, "negative sliding window");
+  SGK_TRY(kv->ensure_self_batch());
+  return kv->self_batch->enqueue_attention(kv->st->pick(stream), d_q, d_out, 0, sliding_window, attn_scalar, d_k, d_v);
+}
+
+static int32_t gather_impl(sgk_kv* kv, int64_t row0, int64_t n, int mode, void* k_out, void* v_out, uint16_t* ks,
+                           uint16_t* kb, uint16_t* vs, uint16_t* vb) {
+  if (!kv) return fail(SGK_ERR_BACKEND, "null KV state");
+  if (!k_out || !v_out) return fail(SGK_ERR_BACKEND, "null host pointer");
+  if (row0 < 0 || n < 0 || row0 + n > kv->len())
+    return fail(SGK_ERR_DIMENSION, "gather rows [%lld,%lld) outside len %lld", (long long)row0, (long long)(row0 + n),
+                (long long)kv->len());
+  if (n == 0) return SGK_OK;
+  if (row0 / PAGE_TOKENS < kv->seq->released_pages)
+    return fail(SGK_ERR_DIMENSION, "gather reaches rows released by the sliding window");
+  Pool* pool = kv->pool();
+  const size_t cells = static_cast<size_t>(n) * kv->kv_dim();
+  size_t esz = mode == 1 ? 4 : (pool->dtype == KV_F32 ? 4 : pool->dtype == KV_BF16 ? 2 : 1);
+  const size_t groups = pool->dtype == KV_U8G32 && mode == 2 ? cells / QGROUP : 0;
+  size_t bytes = 2 * cells * esz + 4 * groups * sizeof(uint16_t);
+  uint8_t* d = nullptr;
+  SGK_CUDA(cudaMalloc(&d, bytes));
+  GatherArgs a{};
+  a.pool = pool->view();
+  a.layer = kv->layer;
+  a.slot = kv->seq->slot;
+  a.row0 = row0;
+  a.n = n;
+  a.mode = mode;
+  a.k_out = d;
+  a.v_out = d + cells * esz;
+  uint16_t* meta = reinterpret_cast<uint16_t*>(d + 2 * cells * esz);
+  a.k_scale = meta;
+  a.k_bias = meta + groups;
+  a.v_scale = meta + 2 * groups;
+  a.v_bias = meta + 3 * groups;
+  a.num_pages = pool->num_pages;
+  a.status = kv->st->d_status;
+  cudaStream_t stream = kv->st->stream;
+  cudaError_t e = launch_gather(a, stream);
+  kv->st->launches += 1;
+  if (e == cudaSuccess) e = cudaMemcpyAsync(k_out, a.k_out, cells * esz, cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(v_out, a.v_out, cells * esz, cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess && groups) {
+    e = cudaMemcpyAsync(ks, a.k_scale, groups * 2, cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(kb, a.k_bias, groups * 2, cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(vs, a.v_scale, groups * 2, cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(vb, a.v_bias, groups * 2, cudaMemcpyDeviceToHost, stream);
+  }
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  cudaFree(d);
+  if (e != cudaSuccess) return fail(SGK_ERR_BACKEND, "gather failed: %s", cudaGetErrorString(e));
+  return check_device_status(kv->st);
+}
+
+int32_t sgk_kv_gather_rows(sgk_kv* kv, int64_t row0, int64_t n, void* k_out, void* v_out) {
+  if (kv && kv->pool()->dtype == KV_U8G32)
+    return fail(SGK_ERR_BACKEND, "gather_rows on a u8 KV: use gather_rows_u8 or gather_rows_f32");
+  return gather_impl(kv, row0, n, 0, k_out, v_out, nullptr, nullptr, nullptr, nullptr);
+}
+
+int32_t sgk_kv_gather_rows_u8(sgk_kv* kv, int64_t row0, int64_t n, uint8_t* k_codes, uint16_t* k_scale,
+                              uint16_t* k_bias, uint8_t* v_codes, uint16_t* v_scale, uint16_t* v_bias) {
+  if (kv && kv->pool()->dtype != KV_U8G32) return fail(SGK_ERR_BACKEND, "gather_rows_u8 on a KV that is not u8");
+  if (!k_scale || !k_bias || !v_scale || !v_bias) return fail(SGK_ERR_BACKEND, "null host pointer");
+  return gather_impl(kv, row0, n, 2, k_codes, v_codes, k_scale, k_bias, v_scale, v_bias);
+}
+
+int32_t sgk_kv_gather_rows_f32(sgk_kv* kv, int64_t row0, int64_t n, float* k_out, float* v_out) {
+  return gather_impl(kv, row0, n, 1, k_out, v_out, nullptr, nullptr, nullptr, nullptr);
+}
+
+int32_t sgk_kv_block_table(const sgk_kv* kv, int32_t* pages_out, int64_t cap, int64_t* n_out) {
+  if (!kv) return fail(SGK_ERR_BACKEND, "null KV state");
+  return sgk_seq_block_table(static_cast<const sgk_seq*>(kv->seq), pages_out, cap, n_out);
+}
+
+int32_t sgk_kv_set_attention_kernel(sgk_kv* kv, int32_t which) {
+  if (!kv) return fail(SGK_ERR_BACKEND, "null KV state");
+  if (which < 0 || which > 2) return fail(SGK_ERR_CONFIG, "kernel selector %d", which);
+  SGK_TRY(kv->ensure_self_batch());
+  kv->self_batch->kernel_override = which;
+  if (kv->self_batch->choose_kernel() < 0) {
+    kv->self_batch->kernel_override = 0;
+    return fail(SGK_ERR_BACKEND, "tensor-core attention kernel does not take this shape");
+  }
+  return SGK_OK;
+}
+
+// ------------------------------------------------------------------ batch
+int32_t sgk_batch_create(sgk_state* st, sgk_kv** kvs, int32_t n, sgk_batch** out) {
+  if (!st || !kvs || !out) return fail(SGK_ERR_BACKEND, "batch_create: null argument");
+  std::vector<Kv*> list(kvs, kvs + std::max(n, 0));
+  Batch* b = nullptr;
+  SGK_TRY(create_batch(st, list.data(), n, &b));
+  *out = static_cast<sgk_batch*>(b);
+  return SGK_OK;
+}
+
+void sgk_batch_destroy(sgk_batch* b) {
+  if (!b) return;
+  cudaSetDevice(b->st->device);
+  cudaStreamSynchronize(b->st->stream);
+  delete static_cast<Batch*>(b);
+}
+
+int32_t sgk_batch_enqueue_append(sgk_batch* b, void* stream, const float* d_k, const float* d_v) {
+  if (!b) return fail(SGK_ERR_BACKEND, "null batch");
+  return b->enqueue_append(b->st->pick(stream), d_k, d_v, 1, nullptr, nullptr);
+}
+
+int32_t sgk_batch_enqueue_attention(sgk_batch* b, void* stream, const float* d_q, float* d_out,
+                                    int64_t sliding_window, float attn_scalar) {
+  if (!b) return fail(SGK_ERR_BACKEND, "null batch");
+  if (sliding_window < 0) return fail(SGK_ERR_DIMENSION, "negative sliding window");
+  return b->enqueue_attention(b->st->pick(stream), d_q, d_out, 0, sliding_window, attn_scalar, nullptr, nullptr);
+}
+
+int32_t sgk_batch_enqueue_step(sgk_batch* b, void* stream, const float* d_k, const float* d_v, const float* d_q,
+                               float* d_out, int64_t sliding_window, float attn_scalar) {
+  if (!b) return fail(SGK_ERR_BACKEND, "null batch");
+  if (!d_k || !d_v) return fail(SGK_ERR_BACKEND, "append: null device pointer");
+  if (sliding_window < 0) return fail(SGK_ERR_DIMENSION, "negative sliding window");
+  return b->enqueue_attention(b->st->pick(stream), d_q, d_out, 0, sliding_window, attn_scalar, d_k, d_v);
+}
+
+int32_t sgk_batch_set_splits(sgk_batch* b, int32_t splits) {
+  if (!b) return fail(SGK_ERR_BACKEND, "null batch");
+  if (splits < 0 || splits > b->max_splits)
+    return fail(SGK_ERR_CONFIG, "splits %d outside [0,%d]", splits, b->max_splits);
+  b->splits_override = splits;
+  return SGK_OK;
+}
+
+int32_t sgk_batch_get_splits(const sgk_batch* b, int32_t* splits_out) {
+  if (!b || !splits_out) return fail(SGK_ERR_BACKEND, "null argument");
+  *splits_out = b->last_splits;
+  return SGK_OK;
+}
+
+int32_t sgk_batch_set_kernel(sgk_batch* b, int32_t which) {
+  if (!b) return fail(SGK_ERR_BACKEND, "null batch");
+  if (which < 0 || which > 2) return fail(SGK_ERR_CONFIG, "kernel selector %d", which);
+  int saved = b->kernel_override;
+  b->kernel_override = which;
+  if (b->choose_kernel() < 0) {
+    b->kernel_override = saved;
+    return fail(SGK_ERR_BACKEND, "tensor-core attention kernel does not take this shape");
+  }
+  return SGK_OK;
+}
+
+int32_t sgk_batch_last_kernel(const sgk_batch* b, int32_t* which_out) {
+  if (!b || !which_out) return fail(SGK_ERR_BACKEND, "null argument");
+  *which_out = b->last_kernel;
+  return SGK_OK;
+}
+
+// ------------------------------------------------------------------ step
+int32_t sgk_step_create(sgk_state* st, sgk_batch** layers, int32_t n_layers, sgk_step** out) {
+  if (!st || !layers || !out) return fail(SGK_ERR_BACKEND, "step_create: null argument");
+  if (n_layers <= 0) return fail(SGK_ERR_CONFIG, "step needs at least one layer");
+  auto s = std::make_unique<sgk_step>();
+  s->st = st;
+  for (int i = 0; i < n_layers; ++i) {
+    if (!layers[i]) return fail(SGK_ERR_BACKEND, "null batch in step");
+    if (layers[i]->n() != layers[0]->n() || layers[i]->q_heads != layers[0]->q_heads ||
+        layers[i]->pool->kv_heads != layers[0]->pool->kv_heads || layers[i]->pool->head_dim != layers[0]->pool->head_dim)
+      return fail(SGK_ERR_CONFIG, "the layers of a step must share batch size and head shape");
+    s->layers.push_back(layers[i]);
+  }
+  *out = s.release();
+  return SGK_OK;
+}
+
+void sgk_step_destroy(sgk_step* s) {
+  if (!s) return;
+  cudaSetDevice(s->st->device);
+  cudaStreamSynchronize(s->st->stream);
+  delete static_cast<Step*>(s);
+}
+
+int32_t sgk_step_enqueue(sgk_step* s, void* stream, const float* d_k, const float* d_v, const float* d_q,
+                         float* d_out, const int64_t* sliding_windows, float attn_scalar) {
+  if (!s) return fail(SGK_ERR_BACKEND, "null step");
+  if (!d_k || !d_v || !d_q || !d_out) return fail(SGK_ERR_BACKEND, "step: null device pointer");
+  return s->enqueue(s->st->pick(stream), d_k, d_v, d_q, d_out, sliding_windows, attn_scalar);
+}
+
+int32_t sgk_step_capture(sgk_step* s, const float* d_k, const float* d_v, const float* d_q, float* d_out,
+                         const int64_t* sliding_windows, float attn_scalar) {
+  if (!s) return fail(SGK_ERR_BACKEND, "null step");
+  if (!d_k || !d_v || !d_q || !d_out) return fail(SGK_ERR_BACKEND, "step: null device pointer");
+  if (s->graph_exec) {
+    cudaGraphExecDestroy(s->graph_exec);
+    s->graph_exec = nullptr;
+  }
+  if (s->graph) {
+    cudaGraphDestroy(s->graph);
+    s->graph = nullptr;
+  }
+  // No host-side table update may fall inside the capture: make every row of the
+  // sequences addressable first, and take private copies of shared tail pages.
+  cudaStream_t stream = s->st->stream;
+  for (Batch* b : s->layers)
+    for (Kv* kv : b->kvs) {
+      SGK_TRY(kv->seq->reserve(kv->seq->capacity));
+      if (kv->len() < kv->seq->capacity) SGK_TRY(kv->seq->ensure_writable(kv->len(), stream));
+    }
+  SGK_CUDA(cudaStreamSynchronize(stream));
+  // The capture moves the host cursors once; put them back, the first replay moves them again.
+  std::vector<std::vector<int64_t>> saved;
+  for (Batch* b : s->layers) {
+    saved.emplace_back();
+    for (Kv* kv : b->kvs) saved.back().push_back(kv->len());
+  }
+  int64_t launches_before = s->launches;
+  SGK_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+  int rc = s->enqueue(stream, d_k, d_v, d_q, d_out, sliding_windows, attn_scalar);
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaStreamEndCapture(stream, &graph);
+  for (size_t l = 0; l < s->layers.size(); ++l)
+    for (size_t i = 0; i < s->layers[l]->kvs.size(); ++i)
+      s->layers[l]->kvs[i]->seq->len[s->layers[l]->layer] = saved[l][i];
+  s->launches_per_replay = s->launches - launches_before;
+  s->launches = launches_before;
+  if (rc != SGK_OK) {
+    if (graph) cudaGraphDestroy(graph);
+    return rc;
+  }
+  if (e != cudaSuccess) return fail(SGK_ERR_BACKEND, "graph capture failed: %s", cudaGetErrorString(e));
+  s->graph = graph;
+  SGK_CUDA(cudaGraphInstantiate(&s->graph_exec, graph, 0));
+  return SGK_OK;
+}
+
+int32_t sgk_step_replay(sgk_step* s, void* stream) {
+  if (!s) return fail(SGK_ERR_BACKEND, "null step");
+  if (!s->graph_exec) return fail(SGK_ERR_CONFIG, "step_replay before step_capture");
+  for (Batch* b : s->layers)
+    for (Kv* kv : b->kvs)
+      if (kv->len() >= kv->seq->capacity)
+        return fail(SGK_ERR_DIMENSION, "append KV: capacity %lld reached (overflow)", (long long)kv->seq->capacity);
+  SGK_CUDA(cudaGraphLaunch(s->graph_exec, s->st->pick(stream)));
+  for (Batch* b : s->layers)
+    for (Kv* kv : b->kvs) kv->seq->len[b->layer] += 1;
+  s->launches += s->launches_per_replay;
+  s->st->launches += s->launches_per_replay;
+  return SGK_OK;
+}
+
+int32_t sgk_step_run_host(sgk_step* s, const float* k, const float* v, const float* q, float* out,
+                          const int64_t* sliding_windows, float attn_scalar) {
+  if (!s) return fail(SGK_ERR_BACKEND, "null step");
+  if (!k || !v || !q || !out) return fail(SGK_ERR_BACKEND, "step: null host pointer");
+  size_t n = size_t(s->layers[0]->n());
+  size_t kv_cells = s->layers.size() * n * s->layers[0]->kvs[0]->kv_dim();
+  size_t q_cells = s->layers.size() * n * s->layers[0]->kvs[0]->q_dim();
+  if (!s->d_k) {
+    SGK_CUDA(cudaMalloc(&s->d_k, kv_cells * sizeof(float)));
+    SGK_CUDA(cudaMalloc(&s->d_v, kv_cells * sizeof(float)));
+    SGK_CUDA(cudaMalloc(&s->d_q, q_cells * sizeof(float)));
+    SGK_CUDA(cudaMalloc(&s->d_out, q_cells * sizeof(float)));
+  }
+  cudaStream_t stream = s->st->stream;
+  SGK_CUDA(cudaMemcpyAsync(s->d_k, k, kv_cells * sizeof(float), cudaMemcpyHostToDevice, stream));
+  SGK_CUDA(cudaMemcpyAsync(s->d_v, v, kv_cells * sizeof(float), cudaMemcpyHostToDevice, stream));
+  SGK_CUDA(cudaMemcpyAsync(s->d_q, q, q_cells * sizeof(float), cudaMemcpyHostToDevice, stream));
+  SGK_TRY(s->enqueue(stream, s->d_k, s->d_v, s->d_q, s->d_out, sliding_windows, attn_scalar));
+  SGK_CUDA(cudaMemcpyAsync(out, s->d_out, q_cells * sizeof(float), cudaMemcpyDeviceToHost, stream));
+  SGK_CUDA(cudaStreamSynchronize(stream));
+  return SGK_OK;
+}
+
+int64_t sgk_step_launches(const sgk_step* s) { return s ? s->launches : 0; }
+
+// ------------------------------------------------------------------ linear state
+int32_t sgk_linstate_create(sgk_state* st, int32_t layers, int64_t conv_len, int64_t ssm_len, int32_t ssm_bf16,
+                            sgk_linstate** out) {
+  if (!st || !out) return fail(SGK_ERR_BACKEND, "linstate_create: null argument");
+  if (layers <= 0 || conv_len < 0 || ssm_len <= 0) return fail(SGK_ERR_CONFIG, "linear state: zero dimension");
+  auto ls = std::make_unique<sgk_linstate>();
+  ls->st = st;
+  ls->layers = layers;
+  ls->conv_len = conv_len;
+  ls->ssm_len = ssm_len;
+  ls->ssm_bf16 = ssm_bf16 != 0;
+  auto up = [](int64_t b) { return (b + 255) / 256 * 256; };
+  ls->conv_stride = up(conv_len * 4);
+  ls->layer_stride = ls->conv_stride + up(ssm_len * ls->ssm_elem());
+  ls->total_bytes = ls->layer_stride * layers;
+  SGK_CUDA(cudaSetDevice(st->device));
+  cudaError_t e = cudaMalloc(&ls->d_base, static_cast<size_t>(ls->total_bytes));
+  if (e != cudaSuccess)
+    return fail(SGK_ERR_MEMORY_GUARD, "linear state of %lld bytes does not fit: %s", (long long)ls->total_bytes,
+                cudaGetErrorString(e));
+  SGK_CUDA(cudaMemset(ls->d_base, 0, static_cast<size_t>(ls->total_bytes)));
+  *out = ls.release();
+  return SGK_OK;
+}
+
+void sgk_linstate_destroy(sgk_linstate* ls) {
+  if (!ls) return;
+  cudaSetDevice(ls->st->device);
+  cudaStreamSynchronize(ls->st->stream);
+  delete static_cast<LinState*>(ls);
+}
+
+int64_t sgk_linstate_bytes(const sgk_linstate* ls) { return ls ? ls->estimated_bytes() : 0; }
+
+void* sgk_linstate_conv_ptr(sgk_linstate* ls, int32_t layer) {
+  if (!ls || layer < 0 || layer >= ls->layers) return nullptr;
+  return ls->d_base + ls->layer_stride * layer;
+}
+void* sgk_linstate_ssm_ptr(sgk_linstate* ls, int32_t layer) {
+  if (!ls || layer < 0 || layer >= ls->layers) return nullptr;
+  return ls->d_base + ls->layer_stride * layer + ls->conv_stride;
+}
+
+int32_t sgk_linstate_write(sgk_linstate* ls, int32_t layer, const float* conv, const float* ssm) {
+  if (!ls || !ssm || (ls && ls->conv_len > 0 && !conv)) return fail(SGK_ERR_BACKEND, "null argument");
+  if (layer < 0 || layer >= ls->layers) return fail(SGK_ERR_DIMENSION, "layer %d out of range", layer);
+  if (ls->conv_len > 0)
+    SGK_CUDA(cudaMemcpy(sgk_linstate_conv_ptr(ls, layer), conv, size_t(ls->conv_len) * 4, cudaMemcpyHostToDevice));
+  if (ls->ssm_bf16) {
+    // same rounding as buffer_from_linear_ssm_seed: f32 -> bf16 RNE on the host
+    std::vector<uint16_t> tmp(static_cast<size_t>(ls->ssm_len));
+    for (size_t i = 0; i < tmp.size(); ++i) {
+      uint32_t bits;
+      std::memcpy(&bits, ssm + i, 4);
+      tmp[i] = static_cast<uint16_t>((bits + 0x7fffu + ((bits >> 16) & 1u)) >> 16);
+    }
+    SGK_CUDA(cudaMemcpy(sgk_linstate_ssm_ptr(ls, layer), tmp.data(), tmp.size() * 2, cudaMemcpyHostToDevice));
+  } else {
+    SGK_CUDA(cudaMemcpy(sgk_linstate_ssm_ptr(ls, layer), ssm, size_t(ls->ssm_len) * 4, cudaMemcpyHostToDevice));
+  }
+  return SGK_OK;
+}
+
+int32_t sgk_linstate_read(sgk_linstate* ls, int32_t layer, float* conv, float* ssm) {
+  if (!ls || !ssm || (ls && ls->conv_len > 0 && !conv)) return fail(SGK_ERR_BACKEND, "null argument");
+  if (layer < 0 || layer >= ls->layers) return fail(SGK_ERR_DIMENSION, "layer %d out of range", layer);
+  SGK_CUDA(cudaStreamSynchronize(ls->st->stream));
+  if (ls->conv_len > 0)
+    SGK_CUDA(cudaMemcpy(conv, sgk_linstate_conv_ptr(ls, layer), size_t(ls->conv_len) * 4, cudaMemcpyDeviceToHost));
+  if (ls->ssm_bf16) {
+    std::vector<uint16_t> tmp(static_cast<size_t>(ls->ssm_len));
+    SGK_CUDA(cudaMemcpy(tmp.data(), sgk_linstate_ssm_ptr(ls, layer), tmp.size() * 2, cudaMemcpyDeviceToHost));
+    for (size_t i = 0; i < tmp.size(); ++i) {
+      uint32_t bits = static_cast<uint32_t>(tmp[i]) << 16;
+      std::memcpy(ssm + i, &bits, 4);
+    }
+  } else {
+    SGK_CUDA(cudaMemcpy(ssm, sgk_linstate_ssm_ptr(ls, layer), size_t(ls->ssm_len) * 4, cudaMemcpyDeviceToHost));
+  }
+  return SGK_OK;
+}
+
+int32_t sgk_linstate_snapshot(sgk_linstate* ls, void* stream, sgk_linstate** snapshot_out) {
+  if (!ls || !snapshot_out) return fail(SGK_ERR_BACKEND, "null argument");
+  sgk_linstate* snap = nullptr;
+  SGK_TRY(sgk_linstate_create(static_cast<sgk_state*>(ls->st), ls->layers, ls->conv_len, ls->ssm_len, ls->ssm_bf16, &snap));
+  // all layers in one launch (the reference: one blit encoder, one submission)
+  cudaError_t e = launch_copy_bytes(snap->d_base, ls->d_base, ls->total_bytes, ls->st->pick(stream));
+  ls->st->launches += 1;
+  if (e != cudaSuccess) {
+    sgk_linstate_destroy(snap);
+    return fail(SGK_ERR_BACKEND, "linear-state snapshot failed: %s", cudaGetErrorString(e));
+  }
+  *snapshot_out = snap;
+  return SGK_OK;
+}
+
+int32_t sgk_linstate_restore(sgk_linstate* ls, void* stream, const sgk_linstate* snap) {
+  if (!ls || !snap) return fail(SGK_ERR_BACKEND, "null argument");
+  // src/metal_backend/linear_attention.rs:3133-3149,3172-3187
+  if (ls->conv_len != snap->conv_len || ls->ssm_len != snap->ssm_len || ls->ssm_bf16 != snap->ssm_bf16 ||
+      ls->layers != snap->layers)
+    return fail(SGK_ERR_SHAPE, "restore linear-attn: snapshot conv=%lld/ssm=%lld/bf16=%d != state conv=%lld/ssm=%lld/bf16=%d",
+                (long long)snap->conv_len, (long long)snap->ssm_len, int(snap->ssm_bf16), (long long)ls->conv_len,
+                (long long)ls->ssm_len, int(ls->ssm_bf16));
+  SGK_CUDA(launch_copy_bytes(ls->d_base, snap->d_base, ls->total_bytes, ls->st->pick(stream)));
+  ls->st->launches += 1;
+  return SGK_OK;
+}
+
+// ------------------------------------------------------------------ hashes
+void sgk_hash_root(uint8_t out[32]) { std::memset(out, 0, 32); }
+
+void sgk_hash_for_session(const char* key, size_t key_len, int32_t present, uint8_t out[32]) {
+  // src/serve/cache.rs:22-33: None or "" keeps the global root
+  if (!present || !key || key_len == 0) {
+    std::memset(out, 0, 32);
+    return;
+  }
+  sha256(reinterpret_cast<const uint8_t*>(key), key_len, out);
+}
+
+void sgk_hash_chain(const uint8_t prev[32], const uint64_t* tokens, size_t n, uint8_t out[32]) {
+  Hash32 p;
+  std::memcpy(p.data(), prev, 32);
+  Hash32 h = hash_chain(p, tokens, n);
+  std::memcpy(out, h.data(), 32);
+}
+
+// ------------------------------------------------------------------ prefix cache
+int32_t sgk_prefix_create(sgk_pool* pool, int64_t block_tokens, int64_t capacity_blocks, int64_t blocks_per_session,
+                          int64_t budget_bytes, sgk_prefix** out) {
+  if (!out) return fail(SGK_ERR_BACKEND, "prefix_create: null out pointer");
+  if (capacity_blocks < 0 || blocks_per_session < 0 || budget_bytes < 0)
+    return fail(SGK_ERR_CONFIG, "prefix cache: negative size");
+  auto pc = std::make_unique<sgk_prefix>();
+  pc->pool = pool;
+  pc->block_tokens = std::max<int64_t>(block_tokens, 1);  // src/serve/cache.rs:111
+  if (pool && pc->block_tokens % PAGE_TOKENS != 0)
+    return fail(SGK_ERR_CONFIG, "block_tokens %lld must be a multiple of the %d-token page", (long long)pc->block_tokens,
+                PAGE_TOKENS);
+  pc->capacity = capacity_blocks;
+  pc->blocks_per_session = blocks_per_session;
+  pc->budget = budget_bytes;
+  *out = pc.release();
+  return SGK_OK;
+}
+
+void sgk_prefix_destroy(sgk_prefix* pc) {
+  if (!pc) return;
+  Pool* pool = pc->pool;
+  if (pool && !pool->host_only()) {
+    cudaSetDevice(pool->st->device);
+    cudaStreamSynchronize(pool->st->stream);
+  }
+  delete static_cast<Prefix*>(pc);
+  if (pool && !pool->host_only()) pool->flush_scrub(pool->st->stream);
+}
+
+int64_t sgk_prefix_block_tokens(const sgk_prefix* pc) { return pc ? pc->block_tokens : 0; }
+
+int32_t sgk_prefix_match(sgk_prefix* pc, const uint8_t root[32], const uint64_t* tokens, size_t n,
+                         int64_t* tokens_out, uint8_t hash_out[32], uint64_t* entry_out) {
+  if (!pc || !root || !tokens_out || !hash_out || !entry_out) return fail(SGK_ERR_BACKEND, "null argument");
+  *entry_out = 0;
+  *tokens_out = 0;
+  if (pc->capacity == 0 || (n > 0 && !tokens)) return SGK_OK;
+  Hash32 session;
+  std::memcpy(session.data(), root, 32);
+  Hash32 previous = session;
+  const size_t bt = static_cast<size_t>(pc->block_tokens);
+  for (size_t index = 0; index < n / bt; ++index) {
+    Hash32 hash = hash_chain(previous, tokens + index * bt, bt);
+    int64_t expected = static_cast<int64_t>((index + 1) * bt);
+    auto it = std::find_if(pc->entries.begin(), pc->entries.end(), [&](const PrefixEntry& e) {
+      return e.session == session && e.hash == hash && e.tokens == expected;
+    });
+    if (it == pc->entries.end()) break;  // stop at the first miss (cache.rs:134-138)
+    // every touched block moves to the front (cache.rs:139-146)
+    std::rotate(pc->entries.begin(), it, it + 1);
+    *tokens_out = pc->entries.front().tokens;
+    std::memcpy(hash_out, pc->entries.front().hash.data(), 32);
+    *entry_out = pc->entries.front().id;
+    previous = hash;
+  }
+  return SGK_OK;
+}
+
+int32_t sgk_prefix_insert(sgk_prefix* pc, const uint8_t session[32], const uint8_t hash[32], int64_t tokens,
+                          sgk_seq* seq, sgk_linstate* ls, void* stream, int32_t* inserted_out) {
+  if (!pc || !session || !hash) return fail(SGK_ERR_BACKEND, "null argument");
+  if (inserted_out) *inserted_out = 0;
+  if (pc->capacity == 0) return SGK_OK;  // cache.rs:162-164
+  if (tokens <= 0) return fail(SGK_ERR_DIMENSION, "prefix block boundary must be positive");
+  if (pc->pool && !seq) return fail(SGK_ERR_BACKEND, "prefix insert needs the sequence to snapshot");
+  std::vector<int32_t> pages;
+  if (seq) {
+    if (seq->pool != pc->pool) return fail(SGK_ERR_CONFIG, "sequence belongs to another pool");
+    if (tokens % PAGE_TOKENS != 0)
+      return fail(SGK_ERR_DIMENSION, "snapshot boundary %lld is not on a page boundary", (long long)tokens);
+    for (int64_t l : seq->len)
+      if (l < tokens)
+        return fail(SGK_ERR_DIMENSION, "snapshot of %lld rows from a sequence holding %lld", (long long)tokens, (long long)l);
+    if (seq->released_pages > 0) return fail(SGK_ERR_DIMENSION, "snapshot of a sequence whose head was released");
+    pages.assign(seq->pages.begin(), seq->pages.begin() + tokens / PAGE_TOKENS);
+  }
+  PrefixEntry e;
+  std::memcpy(e.session.data(), session, 32);
+  std::memcpy(e.hash.data(), hash, 32);
+  e.tokens = tokens;
+  // a refresh replaces the older duplicate without counting as an eviction (cache.rs:165-169)
+  auto dup = std::find_if(pc->entries.begin(), pc->entries.end(), [&](const PrefixEntry& o) {
+    return o.session == e.session && o.hash == e.hash && o.tokens == e.tokens;
+  });
+  if (dup != pc->entries.end()) pc->drop(static_cast<size_t>(dup - pc->entries.begin()), false);
+  // budget loop of remember_prefix_block (src/serve/state.rs:627-635)
+  auto additional = [&]() {
+    int64_t fresh = 0;
+    for (int32_t p : pages) fresh += pc->pins.count(p) ? 0 : 1;
+    return fresh * (pc->pool ? pc->pool->page_b : 0) + (ls ? ls->estimated_bytes() : 0);
+  };
+  if (pc->budget > 0) {
+    while (pc->pinned_bytes() + additional() > pc->budget) {
+      if (!pc->evict_lru(nullptr)) {
+        if (pc->pool && !pc->pool->host_only()) SGK_TRY(pc->pool->flush_scrub(pc->pool->st->stream));
+        return SGK_OK;  // cache empty and still over budget: skip the insert
+      }
+    }
+  }
+  e.bytes = additional();
+  if (ls) {
+    sgk_linstate* snap = nullptr;
+    SGK_TRY(sgk_linstate_snapshot(ls, stream, &snap));
+    e.ls.reset(snap);
+    pc->state_bytes += snap->estimated_bytes();
+  }
+  for (int32_t p : pages) {
+    pc->pool->retain(p);
+    pc->pins[p] += 1;
+  }
+  e.pages = std::move(pages);
+  e.id = pc->next_id++;
+  pc->entries.insert(pc->entries.begin(), std::move(e));  // cache.rs:173-183
+  // per-session cap: that session's rear-most entries leave first (cache.rs:184-188)
+  Hash32 sess = pc->entries.front().session;
+  while (pc->session_count(sess) > pc->blocks_per_session) {
+    long idx = -1;
+    for (long i = static_cast<long>(pc->entries.size()) - 1; i >= 0; --i)
+      if (pc->entries[static_cast<size_t>(i)].session == sess) {
+        idx = i;
+        break;
+      }
+    if (idx < 0) break;
+    pc->drop(static_cast<size_t>(idx), true);
+  }
+  while (static_cast<int64_t>(pc->entries.size()) > pc->capacity) pc->drop(pc->entries.size() - 1, true);  // :189-191
+  if (pc->pool && !pc->pool->host_only()) SGK_TRY(pc->pool->flush_scrub(pc->pool->st->stream));
+  if (inserted_out) *inserted_out = 1;
+  return SGK_OK;
+}
+
+int32_t sgk_prefix_restore(sgk_prefix* pc, uint64_t entry, sgk_seq* seq, sgk_linstate* ls, void* stream, int32_t mode,
+                           int64_t* bytes_copied_out) {
+  if (!pc || !seq) return fail(SGK_ERR_BACKEND, "null argument");
+  if (bytes_copied_out) *bytes_copied_out = 0;
+  if (mode != 0 && mode != 1) return fail(SGK_ERR_CONFIG, "restore mode %d", mode);
+  auto it = std::find_if(pc->entries.begin(), pc->entries.end(), [&](const PrefixEntry& e) { return e.id == entry; });
+  if (it == pc->entries.end()) return fail(SGK_ERR_DIMENSION, "prefix entry %llu is no longer cached", (unsigned long long)entry);
+  if (seq->pool != pc->pool) return fail(SGK_ERR_CONFIG, "sequence belongs to another pool");
+  if (it->tokens > seq->capacity)
+    return fail(SGK_ERR_DIMENSION, "restore of %lld rows > capacity %lld", (long long)it->tokens, (long long)seq->capacity);
+  Pool* pool = pc->pool;
+  cudaStream_t cs = pool->host_only() ? nullptr : pool->st->pick(stream);
+  if (!pool->host_only()) SGK_CUDA(cudaStreamSynchronize(cs));  // the table of a live sequence is about to change
+  seq->release_all();
+  const std::vector<int32_t>& src = it->pages;
+  if (mode == 1) {
+    for (int32_t p : src) pool->retain(p);
+    seq->pages = src;
+  } else {
+    if (src.size() > pool->free_list.size())
+      return fail(SGK_ERR_MEMORY_GUARD, "page pool exhausted: need %zu pages, %zu free", src.size(), pool->free_list.size());
+    std::vector<int32_t> dst;
+    for (size_t i = 0; i < src.size(); ++i) {
+      int32_t p;
+      SGK_TRY(pool->alloc_page(&p));
+      dst.push_back(p);
+    }
+    SGK_TRY(pool->copy_pages(dst, src, cs));
+    seq->pages = dst;
+    if (bytes_copied_out) *bytes_copied_out = static_cast<int64_t>(src.size()) * pool->page_b;
+  }
+  SGK_TRY(seq->publish(0, static_cast<int64_t>(seq->pages.size())));
+  SGK_TRY(seq->set_len_all(it->tokens, cs));
+  if (it->ls) {
+    if (!ls) return fail(SGK_ERR_SHAPE, "entry holds a linear-attention state but none was given to restore into");
+    SGK_TRY(sgk_linstate_restore(ls, stream, static_cast<sgk_linstate*>(it->ls.get())));
+    if (bytes_copied_out) *bytes_copied_out += it->ls->total_bytes;
+  }
+  return SGK_OK;
+}
+
+int32_t sgk_prefix_evict_lru(sgk_prefix* pc, int32_t* evicted_out, int64_t* bytes_out) {
+  if (!pc || !evicted_out) return fail(SGK_ERR_BACKEND, "null argument");
+  int64_t bytes = 0;
+  *evicted_out = pc->evict_lru(&bytes) ? 1 : 0;
+  if (bytes_out) *bytes_out = bytes;
+  if (pc->pool && !pc->pool->host_only()) SGK_TRY(pc->pool->flush_scrub(pc->pool->st->stream));
+  return SGK_OK;
+}
+
+int64_t sgk_prefix_bytes(const sgk_prefix* pc) {
+  int64_t total = 0;
+  if (pc)
+    for (const auto& e : pc->entries) total += e.bytes;
+  return total;
+}
+int64_t sgk_prefix_len(const sgk_prefix* pc) { return pc ? static_cast<int64_t>(pc->entries.size()) : 0; }
+int64_t sgk_prefix_session_count(const sgk_prefix* pc, const uint8_t session[32]) {
+  if (!pc || !session) return 0;
+  Hash32 s;
+  std::memcpy(s.data(), session, 32);
+  return pc->session_count(s);
+}
+
+int64_t sgk_prefix_dump(const sgk_prefix* pc, int32_t which, int64_t cap, uint8_t* sessions, uint8_t* hashes,
+                        int64_t* tokens) {
+  if (!pc) return 0;
+  int64_t total = which == 0 ? static_cast<int64_t>(pc->entries.size()) : static_cast<int64_t>(pc->evicted_log.size());
+  for (int64_t i = 0; i < std::min(cap, total); ++i) {
+    const Hash32& s = which == 0 ? pc->entries[i].session : pc->evicted_log[i].session;
+    const Hash32& h = which == 0 ? pc->entries[i].hash : pc->evicted_log[i].hash;
+    if (sessions) std::memcpy(sessions + 32 * i, s.data(), 32);
+    if (hashes) std::memcpy(hashes + 32 * i, h.data(), 32);
+    if (tokens) tokens[i] = which == 0 ? pc->entries[i].tokens : pc->evicted_log[i].tokens;
+  }
+  return total;
+}
+
+int64_t sgk_longest_prefix_entry_index(const uint64_t* flat, const size_t* lens, size_t n_entries,
+                                       const uint64_t* prompt, size_t n) {
+  // src/decoder/generation.rs:190-204: strictly longer wins, first among equals
+  int64_t best = -1;
+  size_t best_len = 0, off = 0;
+  for (size_t i = 0; i < n_entries; ++i) {
+    size_t len = lens[i];
+    if (len > best_len && len <= n && std::equal(flat + off, flat + off + len, prompt)) {
+      best = static_cast<int64_t>(i);
+      best_len = len;
+    }
+    off += len;
+  }
+  return best;
+}
+
+// ------------------------------------------------------------------ budget
+int32_t sgk_budget_create(uint64_t static_cap, uint64_t total_memory, uint64_t headroom_bytes, uint64_t device_cap,
+                          sgk_budget** out) {
+  if (!out) return fail(SGK_ERR_BACKEND, "budget_create: null out pointer");
+  auto b = std::make_unique<sgk_budget>();
+  b->static_cap = static_cap;
+  b->total_memory = total_memory;
+  b->headroom = headroom_bytes;
+  b->device_cap = device_cap;
+  *out = b.release();
+  return SGK_OK;
+}
+void sgk_budget_destroy(sgk_budget* b) { delete b; }
+void sgk_budget_set_usage(sgk_budget* b, uint64_t current, uint64_t reserved) {
+  if (!b) return;
+  b->current = current;
+  b->reserved = reserved;
+}
+int32_t sgk_budget_limit(const sgk_budget* b, uint64_t* limit_out) {
+  if (!b || !limit_out) return 0;
+  return b->limit(limit_out) ? 1 : 0;
+}
+int32_t sgk_budget_check_allocation(const sgk_budget* b, uint64_t requested, uint64_t* projected_out,
+                                    uint64_t* available_out) {
+  if (!b) return fail(SGK_ERR_BACKEND, "null budget");
+  uint64_t limit = 0;
+  if (!b->limit(&limit)) return SGK_OK;  // no limit: everything is accepted
+  auto sat = [](uint64_t x, uint64_t y) { return x + y < x ? UINT64_MAX : x + y; };
+  uint64_t before = sat(b->current, b->reserved);
+  uint64_t projected = sat(before, requested);
+  if (projected_out) *projected_out = projected;
+  if (available_out) *available_out = limit > before ? limit - before : 0;
+  if (projected > limit)
+    return fail(SGK_ERR_MEMORY_GUARD, "memory budget: projected %llu > limit %llu", (unsigned long long)projected,
+                (unsigned long long)limit);
+  return SGK_OK;
+}
+
+// ------------------------------------------------------------------ utilities
+int32_t sgk_util_fill_normal(sgk_state* st, void* stream, float* d_out, int64_t n, uint64_t seed, uint64_t stream_id,
+                             uint64_t index0) {
+  if (!st || !d_out) return fail(SGK_ERR_BACKEND, "null argument");
+  SGK_CUDA(launch_fill_normal(d_out, n, seed, stream_id, index0, st->pick(stream)));
+  st->launches += 1;
+  return SGK_OK;
+}
+int32_t sgk_util_malloc(sgk_state* st, size_t bytes, void** d_out) {
+  if (!st || !d_out) return fail(SGK_ERR_BACKEND, "null argument");
+  SGK_CUDA(cudaSetDevice(st->device));
+  SGK_CUDA(cudaMalloc(d_out, bytes));
+  return SGK_OK;
+}
+int32_t sgk_util_free(sgk_state* st, void* d_ptr) {
+  if (!st) return fail(SGK_ERR_BACKEND, "null argument");
+  SGK_CUDA(cudaStreamSynchronize(st->stream));
+  SGK_CUDA(cudaFree(d_ptr));
+  return SGK_OK;
+}
+int32_t sgk_util_h2d(sgk_state* st, void* d_dst, const void* src, size_t bytes) {
+  if (!st || !d_dst || !src) return fail(SGK_ERR_BACKEND, "null argument");
+  SGK_CUDA(cudaMemcpyAsync(d_dst, src, bytes, cudaMemcpyHostToDevice, st->stream));
+  SGK_CUDA(cudaStreamSynchronize(st->stream));
+  return SGK_OK;
+}
+int32_t sgk_util_d2h(sgk_state* st, void* dst, const void* d_src, size_t bytes) {
+  if (!st || !dst || !d_src) return fail(SGK_ERR_BACKEND, "null argument");
+  SGK_CUDA(cudaMemcpyAsync(dst, d_src, bytes, cudaMemcpyDeviceToHost, st->stream));
+  SGK_CUDA(cudaStreamSynchronize(st->stream));
+  return SGK_OK;
+}
+int32_t sgk_util_copy_blocks(sgk_state* st, void* stream, void* d_dst, const void* d_src, const int32_t* dst_pages,
+                             const int32_t* src_pages, int32_t n_pages, int64_t page_bytes) {
+  if (!st || !d_dst || !d_src) return fail(SGK_ERR_BACKEND, "null argument");
+  if (page_bytes <= 0 || page_bytes % 16 != 0) return fail(SGK_ERR_DIMENSION, "page_bytes must be a positive multiple of 16");
+  SGK_CUDA(launch_copy_pages(static_cast<uint8_t*>(d_dst), static_cast<const uint8_t*>(d_src), dst_pages, src_pages,
+                             n_pages, page_bytes, st->pick(stream)));
+  st->launches += 1;
+  return SGK_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,214 @@
+// Host-side objects behind the C ABI: the resident state, the page pool with its
+// free list and reference counts, sequences (block tables), per-layer KV views,
+// batches, steps, the linear-attention state container, the prefix cache and the
+// memory budget.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <array>
+#include <cstdarg>
+#include <cstdint>
+#include <memory>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/sgk.h"
+#include "kernels.h"
+
+namespace sgk {
+
+int fail(int code, const char* fmt, ...);
+const char* last_error_cstr();
+
+#define SGK_CUDA(expr)                                                                   \
+  do {                                                                                   \
+    cudaError_t e_ = (expr);                                                             \
+    if (e_ != cudaSuccess)                                                               \
+      return ::sgk::fail(SGK_ERR_BACKEND, "%s failed: %s", #expr, cudaGetErrorString(e_)); \
+  } while (0)
+#define SGK_TRY(expr)              \
+  do {                             \
+    int rc_ = (expr);              \
+    if (rc_ != SGK_OK) return rc_; \
+  } while (0)
+
+struct Batch;
+struct Seq;
+struct Pool;
+
+struct State {
+  int device = 0;
+  int sm_count = 148;
+  cudaStream_t stream = nullptr;
+  int32_t* d_status = nullptr;
+  int64_t launches = 0;  // kernels launched through this state
+  cudaStream_t pick(void* s) const { return s ? static_cast<cudaStream_t>(s) : stream; }
+};
+
+struct Pool {
+  State* st = nullptr;  // NULL: bookkeeping only, no device memory
+  int layers = 0, kv_heads = 0, head_dim = 0, dtype = 0;
+  int64_t num_pages = 0;
+  int max_seqs = 0;
+  int64_t max_seq_tokens = 0;
+  int table_stride = 0;
+  int64_t tile_b = 0, layer_b = 0, page_b = 0;
+  uint8_t* d_base = nullptr;
+  int32_t* d_tables = nullptr;
+  int32_t* d_lens = nullptr;
+  int32_t* d_page_list = nullptr;  // staging for copy / scrub page lists
+  int page_list_cap = 0;
+  std::vector<int32_t> free_list;  // taken from the back
+  std::vector<int32_t> refcount;
+  std::vector<int> free_slots;
+  std::vector<int32_t> pending_scrub;
+  bool scrub_on_free = false;
+  int live_seqs = 0;
+
+  PoolView view() const;
+  bool host_only() const { return st == nullptr; }
+  int alloc_page(int32_t* out);
+  void retain(int32_t page) { refcount[page] += 1; }
+  void release(int32_t page);
+  int flush_scrub(cudaStream_t stream);
+  int64_t used_pages() const { return num_pages - static_cast<int64_t>(free_list.size()); }
+  // Copies pages src[i] -> dst[i] inside the pool (page lists are host arrays).
+  int copy_pages(const std::vector<int32_t>& dst, const std::vector<int32_t>& src, cudaStream_t stream);
+};
+
+struct Kv;
+
+struct Seq {
+  Pool* pool = nullptr;
+  int slot = -1;
+  int64_t capacity = 0;
+  std::vector<int32_t> pages;  // page id per page index, -1 once released
+  int64_t released_pages = 0;  // leading page indices already returned to the pool
+  std::vector<int64_t> len;    // per layer, host mirror of the device cursor
+  std::vector<std::unique_ptr<Kv>> views;
+
+  int reserve(int64_t tokens);
+  int release_before(int64_t row);
+  int release_all();
+  // Makes the page holding `row` exclusively owned (copy-on-write of a shared page).
+  int ensure_writable(int64_t row, cudaStream_t stream);
+  int set_len(int layer, int64_t value, cudaStream_t stream);
+  int set_len_all(int64_t value, cudaStream_t stream);
+  int publish(int64_t first_page, int64_t n);
+};
+
+struct Kv {
+  State* st = nullptr;
+  Seq* seq = nullptr;
+  int layer = 0;
+  int q_heads = 0;
+  int kernel_choice = 0;
+  // standalone KV owns its pool and sequence
+  std::unique_ptr<Pool> owned_pool;
+  std::unique_ptr<Seq> owned_seq;
+  std::unique_ptr<Batch> self_batch;
+  float* d_io = nullptr;  // staging for the host-pointer calls
+  size_t d_io_bytes = 0;
+
+  Pool* pool() const { return seq->pool; }
+  int64_t len() const { return seq->len[layer]; }
+  int kv_dim() const { return pool()->kv_heads * pool()->head_dim; }
+  int q_dim() const { return q_heads * pool()->head_dim; }
+  int ensure_io(size_t bytes);
+  int ensure_self_batch();
+  ~Kv();
+};
+
+struct Batch {
+  State* st = nullptr;
+  Pool* pool = nullptr;
+  std::vector<Kv*> kvs;
+  int layer = 0, q_heads = 0;
+  int32_t* d_slots = nullptr;
+  int32_t* d_counters = nullptr;  // [n*max(q_heads,kv_heads)] head, [n] seq, [n] append-done
+  float* d_part_o = nullptr;
+  float* d_part_ml = nullptr;
+  int max_splits = 1;
+  int splits_override = 0;
+  int kernel_override = 0;
+  int last_kernel = 0;
+  int last_splits = 0;
+
+  int n() const { return static_cast<int>(kvs.size()); }
+  int choose_kernel() const;
+  int choose_splits(int kernel, int64_t max_rows) const;
+  int enqueue_append(cudaStream_t stream, const float* d_k, const float* d_v, int n_rows, const RopeArgs* rope,
+                     const float* knorm_w);
+  int enqueue_attention(cudaStream_t stream, const float* d_q, float* d_out, int64_t window_start,
+                        int64_t sliding_window, float attn_scalar, const float* d_k_new, const float* d_v_new);
+  ~Batch();
+};
+
+struct Step {
+  State* st = nullptr;
+  std::vector<Batch*> layers;
+  cudaGraphExec_t graph_exec = nullptr;
+  cudaGraph_t graph = nullptr;
+  int64_t launches = 0;
+  int64_t launches_per_replay = 0;
+  // staging of run_host
+  float *d_k = nullptr, *d_v = nullptr, *d_q = nullptr, *d_out = nullptr;
+  int enqueue(cudaStream_t stream, const float* d_k, const float* d_v, const float* d_q, float* d_out,
+              const int64_t* sliding_windows, float attn_scalar);
+  ~Step();
+};
+
+struct LinState {
+  State* st = nullptr;
+  int layers = 0;
+  int64_t conv_len = 0, ssm_len = 0;
+  bool ssm_bf16 = false;
+  int64_t conv_stride = 0, layer_stride = 0, total_bytes = 0;
+  uint8_t* d_base = nullptr;
+  int64_t ssm_elem() const { return ssm_bf16 ? 2 : 4; }
+  int64_t estimated_bytes() const { return layers * (conv_len * 4 + ssm_len * ssm_elem()); }
+  ~LinState();
+};
+
+using Hash32 = std::array<uint8_t, 32>;
+void sha256(const uint8_t* data, size_t n, uint8_t out[32]);
+Hash32 hash_chain(const Hash32& prev, const uint64_t* tokens, size_t n);
+
+struct PrefixEntry {
+  Hash32 session, hash;
+  int64_t tokens = 0;
+  uint64_t id = 0;
+  std::vector<int32_t> pages;
+  std::unique_ptr<LinState> ls;
+  int64_t bytes = 0;
+};
+
+struct PrefixKey {
+  Hash32 session, hash;
+  int64_t tokens;
+};
+
+struct Prefix {
+  Pool* pool = nullptr;
+  int64_t block_tokens = 1, capacity = 0, blocks_per_session = 0, budget = 0;
+  std::vector<PrefixEntry> entries;  // front = most recently used
+  std::vector<PrefixKey> evicted_log;
+  std::unordered_map<int32_t, int32_t> pins;  // page -> entries holding it
+  int64_t state_bytes = 0;                    // linear-state snapshots held
+  uint64_t next_id = 1;
+
+  int64_t pinned_bytes() const;
+  void drop(size_t index, bool log);
+  bool evict_lru(int64_t* bytes_out);
+  int64_t session_count(const Hash32& s) const;
+  ~Prefix();
+};
+
+struct Budget {
+  uint64_t static_cap = 0, total_memory = 0, headroom = 0, device_cap = 0;
+  uint64_t current = 0, reserved = 0;
+  bool limit(uint64_t* out) const;
+};
+
+}  // namespace sgk

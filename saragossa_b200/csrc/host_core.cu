@@ -1,0 +1,439 @@
+// Host side of the resident KV path: page pool, block tables, per-layer cursors,
+// kernel selection and split sizing. The residency rule of the reference's
+// scratch pool (two live tensors never share memory; a slot is reused only after
+// release, src/decode_resident/arena.rs:130-234) becomes: every batch owns its
+// split-K workspace, sized once at creation, and reuse is ordered by the stream.
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+
+#include "host.h"
+
+namespace sgk {
+
+static thread_local std::string g_last_error;
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return code;
+}
+const char* last_error_cstr() { return g_last_error.c_str(); }
+
+// ---------------------------------------------------------------- Pool
+PoolView Pool::view() const {
+  PoolView v;
+  v.base = d_base;
+  v.page_bytes = page_b;
+  v.layer_bytes = layer_b;
+  v.tile_bytes = tile_b;
+  v.tables = d_tables;
+  v.lens = d_lens;
+  v.table_stride = table_stride;
+  v.layers = layers;
+  v.kv_heads = kv_heads;
+  v.head_dim = head_dim;
+  v.dtype = dtype;
+  return v;
+}
+
+int Pool::alloc_page(int32_t* out) {
+  if (free_list.empty())
+    return fail(SGK_ERR_MEMORY_GUARD, "page pool exhausted: %lld pages all in use", (long long)num_pages);
+  int32_t p = free_list.back();
+  free_list.pop_back();
+  refcount[p] = 1;
+  *out = p;
+  return SGK_OK;
+}
+
+void Pool::release(int32_t page) {
+  if (page < 0 || page >= num_pages || refcount[page] <= 0) return;
+  refcount[page] -= 1;
+  if (refcount[page] == 0) {
+    free_list.push_back(page);
+    if (scrub_on_free && !host_only()) pending_scrub.push_back(page);
+  }
+}
+
+static int upload_page_list(Pool* pool, const std::vector<int32_t>& a, const std::vector<int32_t>& b) {
+  int need = static_cast<int>(a.size() + b.size());
+  if (need > pool->page_list_cap) {
+    if (pool->d_page_list) cudaFree(pool->d_page_list);
+    pool->d_page_list = nullptr;
+    int cap = std::max(need, 4096);
+    SGK_CUDA(cudaMalloc(&pool->d_page_list, size_t(cap) * sizeof(int32_t)));
+    pool->page_list_cap = cap;
+  }
+  // The staging list is reused by later copies: wait for earlier users first.
+  SGK_CUDA(cudaStreamSynchronize(pool->st->stream));
+  if (!a.empty())
+    SGK_CUDA(cudaMemcpy(pool->d_page_list, a.data(), a.size() * sizeof(int32_t), cudaMemcpyHostToDevice));
+  if (!b.empty())
+    SGK_CUDA(cudaMemcpy(pool->d_page_list + a.size(), b.data(), b.size() * sizeof(int32_t),
+                        cudaMemcpyHostToDevice));
+  return SGK_OK;
+}
+
+int Pool::flush_scrub(cudaStream_t stream) {
+  if (pending_scrub.empty() || host_only()) {
+    pending_scrub.clear();
+    return SGK_OK;
+  }
+  // A page freed and taken again before the flush must not be wiped.
+  std::vector<int32_t> list;
+  for (int32_t p : pending_scrub)
+    if (refcount[p] == 0) list.push_back(p);
+  pending_scrub.clear();
+  if (list.empty()) return SGK_OK;
+  SGK_TRY(upload_page_list(this, list, {}));
+  SGK_CUDA(launch_scrub_pages(d_base, d_page_list, static_cast<int>(list.size()), page_b, stream));
+  st->launches += 1;
+  SGK_CUDA(cudaStreamSynchronize(stream));
+  return SGK_OK;
+}
+
+int Pool::copy_pages(const std::vector<int32_t>& dst, const std::vector<int32_t>& src, cudaStream_t stream) {
+  if (dst.size() != src.size()) return fail(SGK_ERR_DIMENSION, "copy_pages: list sizes differ");
+  if (dst.empty() || host_only()) return SGK_OK;
+  SGK_TRY(upload_page_list(this, dst, src));
+  SGK_CUDA(launch_copy_pages(d_base, d_base, d_page_list, d_page_list + dst.size(), static_cast<int>(dst.size()),
+                             page_b, stream));
+  st->launches += 1;
+  return SGK_OK;
+}
+
+// ---------------------------------------------------------------- Seq
+int Seq::publish(int64_t first_page, int64_t n) {
+  if (pool->host_only() || n <= 0) return SGK_OK;
+  SGK_CUDA(cudaMemcpy(pool->d_tables + int64_t(slot) * pool->table_stride + first_page, pages.data() + first_page,
+                      size_t(n) * sizeof(int32_t), cudaMemcpyHostToDevice));
+  return SGK_OK;
+}
+
+int Seq::reserve(int64_t tokens) {
+  if (tokens > capacity)
+    return fail(SGK_ERR_DIMENSION, "reserve %lld > capacity %lld", (long long)tokens, (long long)capacity);
+  int64_t need = (tokens + PAGE_TOKENS - 1) / PAGE_TOKENS;
+  int64_t have = static_cast<int64_t>(pages.size());
+  if (need <= have) return SGK_OK;
+  if (need - have > static_cast<int64_t>(pool->free_list.size()))
+    return fail(SGK_ERR_MEMORY_GUARD, "page pool exhausted: need %lld pages, %lld free", (long long)(need - have),
+                (long long)pool->free_list.size());
+  for (int64_t i = have; i < need; ++i) {
+    int32_t p;
+    SGK_TRY(pool->alloc_page(&p));
+    pages.push_back(p);
+  }
+  return publish(have, need - have);
+}
+
+int Seq::release_before(int64_t row) {
+  int64_t upto = std::min<int64_t>(row / PAGE_TOKENS, static_cast<int64_t>(pages.size()));
+  for (int64_t i = released_pages; i < upto; ++i) {
+    if (pages[i] >= 0) pool->release(pages[i]);
+    pages[i] = -1;
+  }
+  if (upto > released_pages) {
+    int64_t first = released_pages;
+    released_pages = upto;
+    SGK_TRY(publish(first, upto - first));
+  }
+  if (!pool->host_only()) SGK_TRY(pool->flush_scrub(pool->st->stream));
+  return SGK_OK;
+}
+
+int Seq::release_all() {
+  for (auto& p : pages)
+    if (p >= 0) pool->release(p);
+  pages.clear();
+  released_pages = 0;
+  return SGK_OK;
+}
+
+int Seq::ensure_writable(int64_t row, cudaStream_t stream) {
+  int64_t idx = row / PAGE_TOKENS;
+  if (idx >= static_cast<int64_t>(pages.size())) return SGK_OK;
+  int32_t page = pages[idx];
+  if (page < 0)
+    return fail(SGK_ERR_DIMENSION, "row %lld lies in a page released by the sliding window", (long long)row);
+  if (pool->refcount[page] <= 1) return SGK_OK;
+  int32_t fresh;
+  SGK_TRY(pool->alloc_page(&fresh));
+  SGK_TRY(pool->copy_pages({fresh}, {page}, stream));
+  pool->release(page);
+  pages[idx] = fresh;
+  if (!pool->host_only()) {
+    // in-stream table update: earlier kernels still see the shared page
+    SGK_CUDA(launch_set_len(pool->d_tables + int64_t(slot) * pool->table_stride + idx, fresh, stream));
+    pool->st->launches += 1;
+  }
+  return SGK_OK;
+}
+
+int Seq::set_len(int layer, int64_t value, cudaStream_t stream) {
+  len[layer] = value;
+  if (pool->host_only()) return SGK_OK;
+  SGK_CUDA(launch_set_len(pool->d_lens + int64_t(slot) * pool->layers + layer, static_cast<int32_t>(value), stream));
+  pool->st->launches += 1;
+  return SGK_OK;
+}
+
+int Seq::set_len_all(int64_t value, cudaStream_t stream) {
+  for (int l = 0; l < pool->layers; ++l) SGK_TRY(set_len(l, value, stream));
+  return SGK_OK;
+}
+
+// ---------------------------------------------------------------- Kv
+Kv::~Kv() {
+  self_batch.reset();
+  if (d_io) cudaFree(d_io);
+}
+
+int Kv::ensure_io(size_t bytes) {
+  if (bytes <= d_io_bytes) return SGK_OK;
+  if (d_io) cudaFree(d_io);
+  d_io = nullptr;
+  d_io_bytes = 0;
+  SGK_CUDA(cudaMalloc(&d_io, bytes));
+  d_io_bytes = bytes;
+  return SGK_OK;
+}
+
+int create_batch(State* st, Kv** kvs, int n, Batch** out);
+
+int Kv::ensure_self_batch() {
+  if (self_batch) return SGK_OK;
+  Batch* b = nullptr;
+  Kv* self = this;
+  SGK_TRY(create_batch(st, &self, 1, &b));
+  self_batch.reset(b);
+  return SGK_OK;
+}
+
+// ---------------------------------------------------------------- Batch
+Batch::~Batch() {
+  if (d_slots) cudaFree(d_slots);
+  if (d_counters) cudaFree(d_counters);
+  if (d_part_o) cudaFree(d_part_o);
+  if (d_part_ml) cudaFree(d_part_ml);
+}
+
+int create_batch(State* st, Kv** kvs, int n, Batch** out) {
+  if (n <= 0 || kvs == nullptr) return fail(SGK_ERR_CONFIG, "batch needs at least one KV state");
+  auto b = std::make_unique<Batch>();
+  b->st = st;
+  b->pool = kvs[0]->pool();
+  b->layer = kvs[0]->layer;
+  b->q_heads = kvs[0]->q_heads;
+  if (b->pool->host_only()) return fail(SGK_ERR_BACKEND, "batch over a bookkeeping-only pool");
+  std::vector<int32_t> slots;
+  for (int i = 0; i < n; ++i) {
+    if (kvs[i]->pool() != b->pool || kvs[i]->layer != b->layer || kvs[i]->q_heads != b->q_heads)
+      return fail(SGK_ERR_CONFIG, "batch members must share pool, layer and q_heads");
+    b->kvs.push_back(kvs[i]);
+    slots.push_back(kvs[i]->seq->slot);
+  }
+  const int heads = std::max(b->q_heads, b->pool->kv_heads);
+  // Splits never need to exceed about two blocks per SM for the whole launch.
+  int by_sm = (2 * st->sm_count) / (n * b->pool->kv_heads);
+  b->max_splits = std::min(256, std::max(1, by_sm));
+  SGK_CUDA(cudaMalloc(&b->d_slots, size_t(n) * sizeof(int32_t)));
+  SGK_CUDA(cudaMemcpy(b->d_slots, slots.data(), size_t(n) * sizeof(int32_t), cudaMemcpyHostToDevice));
+  size_t counters = size_t(n) * heads + 2 * size_t(n);
+  SGK_CUDA(cudaMalloc(&b->d_counters, counters * sizeof(int32_t)));
+  SGK_CUDA(cudaMemset(b->d_counters, 0, counters * sizeof(int32_t)));
+  size_t rows = size_t(n) * b->q_heads * b->max_splits;
+  SGK_CUDA(cudaMalloc(&b->d_part_o, rows * b->pool->head_dim * sizeof(float)));
+  SGK_CUDA(cudaMalloc(&b->d_part_ml, rows * 2 * sizeof(float)));
+  *out = b.release();
+  return SGK_OK;
+}
+
+int Batch::choose_kernel() const {
+  int gqa = q_heads / pool->kv_heads;
+  bool can_mma = attention_mma_supported(pool->dtype, pool->head_dim, gqa);
+  if (kernel_override == 2 && !can_mma) return -1;
+  if (kernel_override == 1) return 1;
+  return can_mma ? 2 : 1;
+}
+
+int Batch::choose_splits(int kernel, int64_t max_rows) const {
+  int s = splits_override;
+  if (s <= 0) {
+    // Blocks per launch = heads * n * s over `slots` resident blocks (two per SM
+    // for the tensor-core kernel, eight for the generic one). Take the split count
+    // with the best whole-wave fill (first one above 98.5%), while every split
+    // keeps a few pages of work.
+    const int heads = kernel == 2 ? pool->kv_heads : q_heads;
+    const int64_t slots = int64_t(st->sm_count) * (kernel == 2 ? 2 : 8);
+    const int64_t units = int64_t(heads) * n();
+    const int64_t pages = (max_rows + PAGE_TOKENS - 1) / PAGE_TOKENS;
+    const int min_pages = kernel == 2 ? 8 : 2;
+    int64_t cap = std::max<int64_t>(1, pages / min_pages);
+    cap = std::min<int64_t>(cap, max_splits);
+    int best = 1;
+    double best_eff = 0.0;
+    for (int c = 1; c <= cap; ++c) {
+      int64_t blocks = units * c;
+      int64_t waves = (blocks + slots - 1) / slots;
+      double eff = double(blocks) / double(waves * slots);
+      if (eff > best_eff + 1e-9) {
+        best_eff = eff;
+        best = c;
+      }
+      if (eff >= 0.985) break;
+    }
+    s = best;
+  }
+  return std::max(1, std::min(s, max_splits));
+}
+
+int Batch::enqueue_append(cudaStream_t stream, const float* d_k, const float* d_v, int n_rows, const RopeArgs* rope,
+                          const float* knorm_w) {
+  if (d_k == nullptr || d_v == nullptr) return fail(SGK_ERR_BACKEND, "append: null device pointer");
+  for (Kv* kv : kvs) {
+    // overflow is an error and nothing is written (src/decode_resident/attention.rs:967-972)
+    if (kv->len() + n_rows > kv->seq->capacity)
+      return fail(SGK_ERR_DIMENSION, "append KV: capacity %lld reached (overflow)", (long long)kv->seq->capacity);
+  }
+  for (Kv* kv : kvs) {
+    SGK_TRY(kv->seq->reserve(std::min(kv->seq->capacity, kv->len() + n_rows)));
+    for (int64_t r = kv->len(); r < kv->len() + n_rows; r += PAGE_TOKENS) SGK_TRY(kv->seq->ensure_writable(r, stream));
+    SGK_TRY(kv->seq->ensure_writable(kv->len() + n_rows - 1, stream));
+  }
+  AppendArgs a{};
+  a.pool = pool->view();
+  a.layer = layer;
+  a.slots = n() == 1 ? nullptr : d_slots;
+  a.slot0 = kvs[0]->seq->slot;
+  a.k = d_k;
+  a.v = d_v;
+  a.row0 = 0;
+  a.use_device_len = 1;
+  a.bump_len = 1;
+  a.done_counters = d_counters + size_t(n()) * std::max(q_heads, pool->kv_heads) + n();
+  a.status = st->d_status;
+  a.num_pages = pool->num_pages;
+  a.has_rope = rope != nullptr;
+  if (rope) {
+    a.rope = *rope;
+    a.knorm_w = knorm_w;
+  }
+  a.out_k = nullptr;
+  // gridDim.y is limited: feed long appends in pieces
+  int done = 0;
+  while (done < n_rows) {
+    int piece = std::min(n_rows - done, 32768);
+    if (n() > 1 && piece != n_rows) return fail(SGK_ERR_DIMENSION, "batched append of more than 32768 rows");
+    a.n_rows = piece;
+    a.k = d_k + size_t(done) * kvs[0]->kv_dim();
+    a.v = d_v + size_t(done) * kvs[0]->kv_dim();
+    SGK_CUDA(launch_append_rows(a, n(), stream));
+    st->launches += 1;
+    done += piece;
+  }
+  for (Kv* kv : kvs) kv->seq->len[layer] += n_rows;
+  return SGK_OK;
+}
+
+int Batch::enqueue_attention(cudaStream_t stream, const float* d_q, float* d_out, int64_t window_start,
+                             int64_t sliding_window, float attn_scalar, const float* d_k_new,
+                             const float* d_v_new) {
+  if (d_q == nullptr || d_out == nullptr) return fail(SGK_ERR_BACKEND, "attention: null device pointer");
+  const bool fused = d_k_new != nullptr;
+  int kernel = choose_kernel();
+  if (kernel < 0) return fail(SGK_ERR_BACKEND, "tensor-core attention kernel does not take this shape");
+  int64_t max_rows = 0;
+  for (Kv* kv : kvs) {
+    int64_t len_after = kv->len() + (fused ? 1 : 0);
+    if (fused && kv->len() >= kv->seq->capacity)
+      return fail(SGK_ERR_DIMENSION, "append KV: capacity %lld reached (overflow)", (long long)kv->seq->capacity);
+    if (len_after == 0) return fail(SGK_ERR_DIMENSION, "attention_decode on an empty KV");
+    int64_t ws = sliding_window > 0 ? std::max<int64_t>(len_after - sliding_window, 0) : window_start;
+    if (ws < 0 || ws >= len_after)
+      return fail(SGK_ERR_DIMENSION, "attention_decode empty window: start=%lld, len=%lld", (long long)ws,
+                  (long long)len_after);
+    if (ws / PAGE_TOKENS < kv->seq->released_pages)
+      return fail(SGK_ERR_DIMENSION, "attention window reaches rows released by the sliding window");
+    max_rows = std::max(max_rows, len_after - ws);
+  }
+  if (fused && kernel != 2) {
+    SGK_TRY(enqueue_append(stream, d_k_new, d_v_new, 1, nullptr, nullptr));
+  } else if (fused) {
+    for (Kv* kv : kvs) {
+      SGK_TRY(kv->seq->reserve(kv->len() + 1));
+      SGK_TRY(kv->seq->ensure_writable(kv->len(), stream));
+    }
+  }
+  AttnArgs a{};
+  a.pool = pool->view();
+  a.layer = layer;
+  a.slots = n() == 1 ? nullptr : d_slots;
+  a.slot0 = kvs[0]->seq->slot;
+  a.q_heads = q_heads;
+  a.q = d_q;
+  a.out = d_out;
+  a.window_start = window_start;
+  a.sliding_window = sliding_window;
+  float scalar = attn_scalar > 0.0f ? attn_scalar : static_cast<float>(pool->head_dim);
+  a.scale_log2e = 1.4426950408889634f / std::sqrt(scalar);
+  a.splits = choose_splits(kernel, max_rows);
+  a.part.o = d_part_o;
+  a.part.ml = d_part_ml;
+  a.head_counters = d_counters;
+  a.seq_counters = d_counters + size_t(n()) * std::max(q_heads, pool->kv_heads);
+  a.status = st->d_status;
+  a.num_pages = pool->num_pages;
+  if (kernel == 2) {
+    a.k_new = d_k_new;
+    a.v_new = d_v_new;
+    int64_t pages = (max_rows + PAGE_TOKENS - 1) / PAGE_TOKENS + 1;
+    int64_t per_split = (pages + a.splits - 1) / a.splits;
+    a.n_stages = static_cast<int>(std::max<int64_t>(2, std::min<int64_t>(attention_mma_max_stages(pool->head_dim), per_split)));
+    SGK_CUDA(launch_attention_mma(a, n(), stream));
+    if (fused)
+      for (Kv* kv : kvs) kv->seq->len[layer] += 1;
+  } else {
+    SGK_CUDA(launch_attention_generic(a, n(), stream));
+  }
+  st->launches += 1;
+  last_kernel = kernel;
+  last_splits = a.splits;
+  return SGK_OK;
+}
+
+// ---------------------------------------------------------------- Step
+Step::~Step() {
+  if (graph_exec) cudaGraphExecDestroy(graph_exec);
+  if (graph) cudaGraphDestroy(graph);
+  for (float* p : {d_k, d_v, d_q, d_out})
+    if (p) cudaFree(p);
+}
+
+int Step::enqueue(cudaStream_t stream, const float* k, const float* v, const float* q, float* out,
+                  const int64_t* sliding_windows, float attn_scalar) {
+  for (size_t l = 0; l < layers.size(); ++l) {
+    Batch* b = layers[l];
+    size_t kv_stride = size_t(b->n()) * b->kvs[0]->kv_dim();
+    size_t q_stride = size_t(b->n()) * b->kvs[0]->q_dim();
+    int64_t before = st->launches;
+    SGK_TRY(b->enqueue_attention(stream, q + l * q_stride, out + l * q_stride, 0,
+                                 sliding_windows ? sliding_windows[l] : 0, attn_scalar, k + l * kv_stride,
+                                 v + l * kv_stride));
+    launches += st->launches - before;
+  }
+  return SGK_OK;
+}
+
+// ---------------------------------------------------------------- LinState
+LinState::~LinState() {
+  if (d_base) cudaFree(d_base);
+}
+
+}  // namespace sgk

@@ -1,0 +1,105 @@
+// Kernel argument blocks and launchers (device side of libsgk).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "device_common.cuh"
+#include "layout.h"
+
+namespace sgk {
+
+struct RopeArgs {
+  int32_t rope_dims;
+  int32_t frequency_dim;
+  float theta;
+  float position_scale;
+  float eps;
+  int32_t interleaved;
+};
+
+struct AppendArgs {
+  PoolView pool;
+  int32_t layer;
+  const int32_t* slots;  // [n_seq] sequence slots; NULL => slot0 for the only sequence
+  int32_t slot0;
+  const float* k;        // [n_seq][n_rows][kv_dim]
+  const float* v;
+  int32_t n_rows;
+  int64_t row0;             // first row when use_device_len == 0
+  int32_t use_device_len;   // first row = the device cursor lens[slot][layer]
+  int32_t bump_len;         // cursor += n_rows once every block has finished
+  int32_t* done_counters;   // [n_seq], zero between launches
+  int32_t* status;          // device status word
+  int64_t num_pages;
+  int32_t has_rope;
+  const float* knorm_w;     // [head_dim]
+  RopeArgs rope;
+  float* out_k;             // not NULL: write normalised+rotated K rows here, touch no page
+};
+
+struct AttnArgs {
+  PoolView pool;
+  int32_t layer;
+  const int32_t* slots;  // [n_seq]; NULL => slot0
+  int32_t slot0;
+  int32_t q_heads;
+  const float* q;        // [n_seq][q_heads*head_dim]
+  float* out;            // [n_seq][q_heads*head_dim]
+  int64_t window_start;     // explicit start row when sliding_window == 0
+  int64_t sliding_window;   // > 0: start = max(len - window, 0)
+  float scale_log2e;        // log2(e) / sqrt(attn_scalar)
+  int32_t splits;
+  Partials part;
+  int32_t* head_counters;   // [n_seq][kv_heads] (tensor-core kernel) or [n_seq][q_heads] (generic)
+  int32_t* seq_counters;    // [n_seq]
+  int32_t* status;
+  int64_t num_pages;
+  // fused append (tensor-core kernel only): one new f32 row per sequence
+  const float* k_new;  // [n_seq][kv_dim] or NULL
+  const float* v_new;
+  int32_t n_stages;
+};
+
+cudaError_t launch_append_rows(const AppendArgs& a, int n_seq, cudaStream_t stream);
+cudaError_t launch_set_len(int32_t* ptr, int32_t value, cudaStream_t stream);
+
+cudaError_t launch_attention_generic(const AttnArgs& a, int n_seq, cudaStream_t stream);
+// Tensor-core paged kernel: bf16 pages, head_dim 128 or 256, q_heads/kv_heads <= 8.
+bool attention_mma_supported(int dtype, int head_dim, int gqa);
+cudaError_t launch_attention_mma(const AttnArgs& a, int n_seq, cudaStream_t stream);
+cudaError_t attention_mma_configure();
+int attention_mma_max_stages(int head_dim);
+
+// Gather rows [row0, row0+n) of one layer into contiguous [n, kv_dim] arrays.
+// mode 0: storage type (f32 / bf16 bits), 1: decoded f32, 2: u8 codes + scale + bias.
+struct GatherArgs {
+  PoolView pool;
+  int32_t layer;
+  int32_t slot;
+  int64_t row0;
+  int64_t n;
+  int32_t mode;
+  void* k_out;
+  void* v_out;
+  uint16_t* k_scale;
+  uint16_t* k_bias;
+  uint16_t* v_scale;
+  uint16_t* v_bias;
+  int64_t num_pages;
+  int32_t* status;
+};
+cudaError_t launch_gather(const GatherArgs& a, cudaStream_t stream);
+
+// Page copy: dst_pages[i] <- src_pages[i], page_bytes each (16-byte vectors).
+cudaError_t launch_copy_pages(uint8_t* dst_base, const uint8_t* src_base, const int32_t* d_dst_pages,
+                              const int32_t* d_src_pages, int n_pages, int64_t page_bytes,
+                              cudaStream_t stream);
+// Contiguous device copy (linear-state snapshot / restore).
+cudaError_t launch_copy_bytes(void* dst, const void* src, int64_t bytes, cudaStream_t stream);
+// Zero-fill of freed pages (eviction scrub).
+cudaError_t launch_scrub_pages(uint8_t* base, const int32_t* d_pages, int n_pages, int64_t page_bytes,
+                               cudaStream_t stream);
+cudaError_t launch_fill_normal(float* out, int64_t n, uint64_t seed, uint64_t stream_id,
+                               uint64_t index0, cudaStream_t stream);
+
+}  // namespace sgk

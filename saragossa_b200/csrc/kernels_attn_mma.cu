@@ -1,0 +1,475 @@
+// Paged split-K flash-decoding for bf16 pages (head_dim 128 / 256, GQA group <= 8),
+// with the per-token append fused in.
+//
+// One block per (split, kv head, sequence). A producer warp walks the block table
+// and brings each page's K tile + V tile (one contiguous range of the pool, see
+// layout.h) into a shared-memory ring with one bulk async copy (TMA,
+// cp.async.bulk) per page, completion signalled on an mbarrier. Consumer warps
+// take pages round-robin; per page:
+//     S^T[16 rows x 8 heads] = K_tile . Q^T          (mma.sync m16n8k16, bf16)
+//     online softmax over the rows (warp shuffles, log2 domain)
+//     O^T[dims x 8 heads]   += V_tile^T . P^T        (ldmatrix.trans + mma)
+// so the K/V bytes of a kv head are read from HBM once for its whole GQA group.
+// Q and P are split into bf16 hi + lo parts, which keeps the products at ~f32
+// accuracy while the tensor cores stay far from being the limit (the kernel is
+// HBM-bound: ~8 flop/byte). Warps merge in shared memory, the block writes an
+// un-normalised partial, and the block that arrives last for (sequence, kv head)
+// merges the splits and writes the output: one launch, no second pass.
+//
+// The pages are stored XOR-swizzled (layout.h), so the verbatim copy in shared
+// memory is read by ldmatrix without bank conflicts.
+//
+// Fused append (k_new != NULL): the block whose range ends at the row being
+// written converts that row to bf16 (same integer rounding as the append kernel),
+// stores it into its page and patches it into the shared-memory copy of the page,
+// and the block that arrives last for the sequence moves the device cursor.
+//
+// Counterparts in the reference: attention_decode_2pass_1/_2 and
+// attention_decode_flash (src/decode_resident/kernels.rs:166-917) plus copy_at
+// (kernels.rs:1026-1044); selection logic src/decode_resident/attention.rs:755-769.
+#include <cuda_bf16.h>
+
+#include "kernels.h"
+
+namespace sgk {
+
+constexpr int MMA_CONSUMERS = 4;                       // consumer warps
+constexpr int MMA_THREADS = (MMA_CONSUMERS + 1) * 32;  // + one producer warp
+constexpr int MMA_MAX_STAGES = 32;
+constexpr uint32_t WAIT_SPINS = 1u << 22;        // bound of every mbarrier wait
+constexpr uint32_t WAIT_SPINS_ABORTED = 1u << 10;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait. On expiry: sets the block's abort flag and the device status
+// word and returns false; the caller skips the work of that stage but keeps
+// walking its stages, so copies still in flight are waited for (with the short
+// bound) before the block exits.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int32_t* status) {
+  uint32_t limit = *abort_flag ? WAIT_SPINS_ABORTED : WAIT_SPINS;
+  for (uint32_t i = 0; i < limit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+  }
+  *abort_flag = 1;
+  atomicExch(status, DEV_ERR_WAIT_TIMEOUT);
+  return false;
+}
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                                  uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// x -> bf16 hi (nearest) and bf16 lo = nearest(x - hi), packed for two values.
+__device__ __forceinline__ void split_hi_lo(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+  __nv_bfloat16 h0 = __float2bfloat16_rn(x0), h1 = __float2bfloat16_rn(x1);
+  __nv_bfloat16 l0 = __float2bfloat16_rn(x0 - __bfloat162float(h0));
+  __nv_bfloat16 l1 = __float2bfloat16_rn(x1 - __bfloat162float(h1));
+  hi = static_cast<uint32_t>(__bfloat16_as_ushort(h0)) | (static_cast<uint32_t>(__bfloat16_as_ushort(h1)) << 16);
+  lo = static_cast<uint32_t>(__bfloat16_as_ushort(l0)) | (static_cast<uint32_t>(__bfloat16_as_ushort(l1)) << 16);
+}
+
+template <int HD>
+struct MmaSmem {
+  static constexpr int TILE = PAGE_TOKENS * HD * 2;  // bytes of a K or V tile
+  static constexpr int STAGE = 2 * TILE;             // K tile + V tile
+  static constexpr int OPAD = HD + 4;                // padded row of the merge buffer
+  static constexpr int Q_BYTES = 2 * 8 * HD * 2;     // hi and lo, 8 heads
+  static constexpr int O_BYTES = MMA_CONSUMERS * 8 * OPAD * 4;  // aliases the ring once it has drained
+  static constexpr int ML_BYTES = MMA_CONSUMERS * 8 * 2 * 4;
+  static constexpr int BAR_BYTES = 2 * MMA_MAX_STAGES * 8;
+  static constexpr int FIXED = Q_BYTES + ML_BYTES + BAR_BYTES + 64;
+  __host__ __device__ static size_t ring_bytes(int stages) {
+    size_t r = size_t(stages) * STAGE;
+    return r > size_t(O_BYTES) ? r : size_t(O_BYTES);
+  }
+  static size_t total(int stages) { return ring_bytes(stages) + FIXED + 1024; }
+};
+
+template <int HD>
+__global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs a) {
+  using S = MmaSmem<HD>;
+  constexpr int KSTEPS = HD / 16;
+  constexpr int ROWB = HD * 2;  // bytes of a tile row
+  extern __shared__ uint8_t smem_raw[];
+  // stage ring first, 1024-byte aligned so the swizzle pattern lines up with the banks
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int nst = a.n_stages;
+  uint8_t* fixed = ring + S::ring_bytes(nst);
+  uint16_t* q_hi = reinterpret_cast<uint16_t*>(fixed);          // [8][HD]
+  uint16_t* q_lo = q_hi + 8 * HD;                               // [8][HD]
+  float* o_s = reinterpret_cast<float*>(ring);                  // [warps][8][OPAD], used after the ring drained
+  float* ml_s = reinterpret_cast<float*>(fixed + S::Q_BYTES);   // [warps][8][2]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(fixed + S::Q_BYTES + S::ML_BYTES);
+  int* flags = reinterpret_cast<int*>(bars + 2 * MMA_MAX_STAGES);  // [0]=abort [1]=last-for-head [2]=len
+  volatile int* abort_flag = flags;
+
+  const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int gqa = a.q_heads / a.pool.kv_heads;
+  const int slot = a.slots ? a.slots[seq] : a.slot0;
+  int32_t* len_ptr = a.pool.lens + int64_t(slot) * a.pool.layers + a.layer;
+  const bool do_append = a.k_new != nullptr;
+
+  if (tid == 0) {
+    flags[0] = 0;
+    flags[1] = 0;
+    flags[2] = *len_ptr;
+    for (int s = 0; s < nst; ++s) {
+      mbar_init(smem_u32(bars + s), 1);                   // full: producer's expect_tx arrival
+      mbar_init(smem_u32(bars + MMA_MAX_STAGES + s), 1);  // empty: one consumer lane
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  // Q of the group: scale, split into bf16 hi/lo, rows of absent heads are zero.
+  {
+    const float* q = a.q + (int64_t(seq) * a.q_heads + int64_t(kvh) * gqa) * HD;
+    for (int i = tid; i < 8 * HD / 2; i += MMA_THREADS) {
+      int h = (2 * i) / HD;
+      float x0 = 0.0f, x1 = 0.0f;
+      if (h < gqa) {
+        float2 v = *reinterpret_cast<const float2*>(q + 2 * i);
+        x0 = v.x * a.scale_log2e;
+        x1 = v.y * a.scale_log2e;
+      }
+      uint32_t hi, lo;
+      split_hi_lo(x0, x1, hi, lo);
+      reinterpret_cast<uint32_t*>(q_hi)[i] = hi;
+      reinterpret_cast<uint32_t*>(q_lo)[i] = lo;
+    }
+  }
+  __syncthreads();
+
+  const int64_t len_old = flags[2];
+  const int64_t len = len_old + (do_append ? 1 : 0);
+  int64_t ws = a.sliding_window > 0 ? (len > a.sliding_window ? len - a.sliding_window : 0) : a.window_start;
+  if (ws >= len) ws = len > 0 ? len - 1 : 0;
+  const int64_t p_first = ws / PAGE_TOKENS;
+  const int64_t p_last = (len - 1) / PAGE_TOKENS;
+  const int64_t n_pages = p_last - p_first + 1;
+  const int64_t pb = p_first + (n_pages * split) / a.splits;        // this block's pages [pb, pe)
+  const int64_t pe = p_first + (n_pages * (split + 1)) / a.splits;
+  const int my_pages = static_cast<int>(pe - pb);
+  const int32_t* table = a.pool.tables + int64_t(slot) * a.pool.table_stride;
+  const int64_t head_off = int64_t(a.layer) * a.pool.layer_bytes + int64_t(kvh) * 2 * a.pool.tile_bytes;
+  // Page that receives the appended row, and whether this block owns it.
+  const int64_t append_page_index = len_old / PAGE_TOKENS;
+  const bool owns_append = do_append && append_page_index >= pb && append_page_index < pe;
+
+  if (warp == MMA_CONSUMERS) {
+    // ---------------- producer warp ----------------
+    for (int base = 0; base < my_pages; base += 32) {
+      int idx = base + lane;
+      int32_t entry = idx < my_pages ? table[pb + idx] : -1;
+      int cnt = min(32, my_pages - base);
+      for (int j = 0; j < cnt; ++j) {
+        int i = base + j;
+        int32_t page = __shfl_sync(0xffffffffu, entry, j);
+        int stage = i % nst;
+        uint32_t parity = ((i / nst) & 1) ^ 1;
+        bool ok = true;
+        if (lane == 0) {
+          ok = mbar_wait(smem_u32(bars + MMA_MAX_STAGES + stage), parity, abort_flag, a.status);
+          if (ok && (page < 0 || page >= a.num_pages)) {
+            atomicExch(a.status, DEV_ERR_BAD_PAGE);
+            *abort_flag = 1;
+            ok = false;
+          }
+          if (ok) {
+            uint32_t full = smem_u32(bars + stage);
+            mbar_expect_tx(full, S::STAGE);
+            bulk_copy_g2s(smem_u32(ring + size_t(stage) * S::STAGE),
+                          a.pool.base + int64_t(page) * a.pool.page_bytes + head_off, S::STAGE, full);
+          }
+        }
+      }
+    }
+  } else {
+    // ---------------- consumer warps ----------------
+    const int g = lane >> 2, t = lane & 3;
+    // B fragments of Q^T: b0 = Q[head g][k0+2t, +1], b1 = Q[head g][k0+2t+8, +9]
+    uint32_t qh_f[KSTEPS][2], ql_f[KSTEPS][2];
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+      qh_f[ks][0] = *reinterpret_cast<const uint32_t*>(q_hi + g * HD + ks * 16 + 2 * t);
+      qh_f[ks][1] = *reinterpret_cast<const uint32_t*>(q_hi + g * HD + ks * 16 + 2 * t + 8);
+      ql_f[ks][0] = *reinterpret_cast<const uint32_t*>(q_lo + g * HD + ks * 16 + 2 * t);
+      ql_f[ks][1] = *reinterpret_cast<const uint32_t*>(q_lo + g * HD + ks * 16 + 2 * t + 8);
+    }
+    float o_acc[KSTEPS][4];
+#pragma unroll
+    for (int j = 0; j < KSTEPS; ++j) o_acc[j][0] = o_acc[j][1] = o_acc[j][2] = o_acc[j][3] = 0.0f;
+    float m0 = -1.0e30f, m1 = -1.0e30f, l0 = 0.0f, l1 = 0.0f;  // heads 2t and 2t+1
+
+    // ldmatrix lane roles
+    const int lm = lane >> 3, lr = lane & 7;
+    const int k_row = lr + (lm & 1) * 8, k_csel = lm >> 1;   // K: matrices (r0-7,c0) (r8-15,c0) (r0-7,c1) (r8-15,c1)
+    const int v_row = lr + (lm >> 1) * 8, v_csel = lm & 1;   // V^T: (r0-7,c0) (r0-7,c1) (r8-15,c0) (r8-15,c1)
+
+    for (int i = warp; i < my_pages; i += MMA_CONSUMERS) {
+      const int stage = i % nst;
+      const uint32_t parity = (i / nst) & 1;
+      const bool ok = mbar_wait(smem_u32(bars + stage), parity, abort_flag, a.status);
+      uint8_t* ktile = ring + size_t(stage) * S::STAGE;
+      uint8_t* vtile = ktile + S::TILE;
+      const int64_t page_index = pb + i;
+      const int64_t row_base = page_index * PAGE_TOKENS;
+
+      if (ok && owns_append && page_index == append_page_index) {
+        // Convert the new row once; store it to its page and into the staged copy.
+        const int rin = static_cast<int>(len_old % PAGE_TOKENS);
+        int32_t page = table[page_index];
+        if (page >= 0 && page < a.num_pages) {
+          uint8_t* gk = a.pool.base + int64_t(page) * a.pool.page_bytes + head_off;
+          uint8_t* gv = gk + S::TILE;
+          const float* kn = a.k_new + int64_t(seq) * a.pool.kv_heads * HD + kvh * HD;
+          const float* vn = a.v_new + int64_t(seq) * a.pool.kv_heads * HD + kvh * HD;
+          for (int chunk = lane; chunk < HD / 8; chunk += 32) {
+            uint32_t wk[4], wv[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              wk[e] = uint32_t(f32_to_bf16_bits(kn[chunk * 8 + 2 * e])) |
+                      (uint32_t(f32_to_bf16_bits(kn[chunk * 8 + 2 * e + 1])) << 16);
+              wv[e] = uint32_t(f32_to_bf16_bits(vn[chunk * 8 + 2 * e])) |
+                      (uint32_t(f32_to_bf16_bits(vn[chunk * 8 + 2 * e + 1])) << 16);
+            }
+            int off = bf16_elem_index(rin, chunk * 8, HD) * 2;
+            uint4 pk = make_uint4(wk[0], wk[1], wk[2], wk[3]);
+            uint4 pv = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+            *reinterpret_cast<uint4*>(gk + off) = pk;
+            *reinterpret_cast<uint4*>(gv + off) = pv;
+            *reinterpret_cast<uint4*>(ktile + off) = pk;
+            *reinterpret_cast<uint4*>(vtile + off) = pv;
+          }
+        }
+        __syncwarp();
+      }
+
+      if (ok) {
+        // ---- S^T = K . Q^T (hi and lo parts of Q on two accumulators) ----
+        float sh[4] = {0.f, 0.f, 0.f, 0.f}, sl[4] = {0.f, 0.f, 0.f, 0.f};
+        const uint32_t kbase = smem_u32(ktile) + k_row * ROWB;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+          int chunk = 2 * ks + k_csel;
+          int phys = (chunk & ~7) | ((chunk ^ k_row) & 7);
+          uint32_t a0, a1, a2, a3;
+          ldmatrix_x4(kbase + phys * 16, a0, a1, a2, a3);
+          mma_bf16(sh, a0, a1, a2, a3, qh_f[ks][0], qh_f[ks][1]);
+          mma_bf16(sl, a0, a1, a2, a3, ql_f[ks][0], ql_f[ks][1]);
+        }
+        float s[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[e] = sh[e] + sl[e];
+        // rows g (s0,s1) and g+8 (s2,s3); heads 2t (s0,s2) and 2t+1 (s1,s3)
+        if (row_base < ws || row_base + PAGE_TOKENS > len) {
+          int64_t ra = row_base + g, rb = row_base + g + 8;
+          if (ra < ws || ra >= len) s[0] = s[1] = -1.0e30f;
+          if (rb < ws || rb >= len) s[2] = s[3] = -1.0e30f;
+        }
+        float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+          mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+          mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+        }
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const bool grew = (mn0 > m0) || (mn1 > m1);
+        if (__any_sync(0xffffffffu, grew)) {
+          const float al0 = exp2f(m0 - mn0), al1 = exp2f(m1 - mn1);
+          l0 *= al0;
+          l1 *= al1;
+#pragma unroll
+          for (int j = 0; j < KSTEPS; ++j) {
+            o_acc[j][0] *= al0;
+            o_acc[j][2] *= al0;
+            o_acc[j][1] *= al1;
+            o_acc[j][3] *= al1;
+          }
+          m0 = mn0;
+          m1 = mn1;
+        }
+        float p[4];
+        p[0] = exp2f(s[0] - m0);
+        p[2] = exp2f(s[2] - m0);
+        p[1] = exp2f(s[1] - m1);
+        p[3] = exp2f(s[3] - m1);
+        l0 += p[0] + p[2];
+        l1 += p[1] + p[3];
+        // P^T as the B operand: transpose the two 8x8 halves across the warp.
+        uint32_t ph_a, pl_a, ph_b, pl_b;
+        split_hi_lo(p[0], p[1], ph_a, pl_a);  // rows 0-7
+        split_hi_lo(p[2], p[3], ph_b, pl_b);  // rows 8-15
+        const uint32_t bh0 = movmatrix_trans(ph_a), bh1 = movmatrix_trans(ph_b);
+        const uint32_t bl0 = movmatrix_trans(pl_a), bl1 = movmatrix_trans(pl_b);
+        // ---- O^T += V^T . P^T ----
+        const uint32_t vbase = smem_u32(vtile) + v_row * ROWB;
+#pragma unroll
+        for (int j = 0; j < KSTEPS; ++j) {
+          int chunk = 2 * j + v_csel;
+          int phys = (chunk & ~7) | ((chunk ^ v_row) & 7);
+          uint32_t a0, a1, a2, a3;
+          ldmatrix_x4_trans(vbase + phys * 16, a0, a1, a2, a3);
+          mma_bf16(o_acc[j], a0, a1, a2, a3, bh0, bh1);
+          mma_bf16(o_acc[j], a0, a1, a2, a3, bl0, bl1);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(bars + MMA_MAX_STAGES + stage));
+    }
+
+    // ---- hand this warp's state to the merge buffer (it aliases the ring: wait
+    //      until every warp has consumed its last stage) ----
+    asm volatile("bar.sync 1, %0;" ::"r"(MMA_CONSUMERS * 32) : "memory");
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) {
+      l0 += __shfl_xor_sync(0xffffffffu, l0, off);
+      l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+    }
+    float* ow = o_s + warp * 8 * S::OPAD;
+#pragma unroll
+    for (int j = 0; j < KSTEPS; ++j) {
+      ow[(2 * t) * S::OPAD + 16 * j + g] = o_acc[j][0];
+      ow[(2 * t + 1) * S::OPAD + 16 * j + g] = o_acc[j][1];
+      ow[(2 * t) * S::OPAD + 16 * j + g + 8] = o_acc[j][2];
+      ow[(2 * t + 1) * S::OPAD + 16 * j + g + 8] = o_acc[j][3];
+    }
+    if (g == 0) {
+      ml_s[(warp * 8 + 2 * t) * 2] = m0;
+      ml_s[(warp * 8 + 2 * t) * 2 + 1] = l0;
+      ml_s[(warp * 8 + 2 * t + 1) * 2] = m1;
+      ml_s[(warp * 8 + 2 * t + 1) * 2 + 1] = l1;
+    }
+  }
+  __syncthreads();
+
+  // ---- merge the consumer warps; write the partial or the final output ----
+  const int64_t qh0 = int64_t(seq) * a.q_heads + int64_t(kvh) * gqa;
+  for (int idx = tid; idx < gqa * HD; idx += MMA_THREADS) {
+    int h = idx / HD, d = idx % HD;
+    float mb = -1.0e30f;
+#pragma unroll
+    for (int w = 0; w < MMA_CONSUMERS; ++w) mb = fmaxf(mb, ml_s[(w * 8 + h) * 2]);
+    float o = 0.0f, lb = 0.0f;
+#pragma unroll
+    for (int w = 0; w < MMA_CONSUMERS; ++w) {
+      float wg = exp2f(ml_s[(w * 8 + h) * 2] - mb);
+      o += o_s[(w * 8 + h) * S::OPAD + d] * wg;
+      lb += ml_s[(w * 8 + h) * 2 + 1] * wg;
+    }
+    if (a.splits == 1) {
+      a.out[(qh0 + h) * HD + d] = o / lb;
+    } else {
+      a.part.o[((qh0 + h) * a.splits + split) * HD + d] = o;
+      if (d == 0) {
+        float* pml = a.part.ml + ((qh0 + h) * a.splits + split) * 2;
+        pml[0] = mb;
+        pml[1] = lb;
+      }
+    }
+  }
+  if (a.splits > 1 || do_append) {
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence();
+      if (a.splits > 1) {
+        int old = atomicAdd(a.head_counters + int64_t(seq) * a.pool.kv_heads + kvh, 1);
+        flags[1] = (old == a.splits - 1);
+      }
+      if (do_append) {
+        int total = a.splits * a.pool.kv_heads;
+        int old = atomicAdd(a.seq_counters + seq, 1);
+        if (old == total - 1) {
+          *len_ptr = static_cast<int32_t>(len);
+          a.seq_counters[seq] = 0;
+        }
+      }
+    }
+    __syncthreads();
+    if (a.splits > 1 && flags[1]) {
+      __threadfence();
+      for (int h = 0; h < gqa; ++h)
+        merge_partials(a.part, qh0 + h, a.splits, HD, a.out + (qh0 + h) * HD, tid, MMA_THREADS);
+      if (tid == 0) a.head_counters[int64_t(seq) * a.pool.kv_heads + kvh] = 0;
+    }
+  }
+}
+
+bool attention_mma_supported(int dtype, int head_dim, int gqa) {
+  return dtype == KV_BF16 && (head_dim == 128 || head_dim == 256) && gqa >= 1 && gqa <= 8;
+}
+
+int attention_mma_max_stages(int head_dim) {
+  // Two blocks per SM: each gets half of the 227 KiB an SM offers.
+  size_t budget = 113 * 1024;
+  size_t fixed = head_dim == 128 ? MmaSmem<128>::FIXED : MmaSmem<256>::FIXED;
+  size_t stage = head_dim == 128 ? MmaSmem<128>::STAGE : MmaSmem<256>::STAGE;
+  int n = static_cast<int>((budget - fixed - 1024) / stage);
+  return n > MMA_MAX_STAGES ? MMA_MAX_STAGES : n;
+}
+
+cudaError_t attention_mma_configure() {
+  cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       227 * 1024);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(attention_mma_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+}
+
+cudaError_t launch_attention_mma(const AttnArgs& a, int n_seq, cudaStream_t stream) {
+  dim3 grid(a.splits, a.pool.kv_heads, n_seq);
+  if (a.pool.head_dim == 128) {
+    attention_mma_kernel<128><<<grid, MMA_THREADS, MmaSmem<128>::total(a.n_stages), stream>>>(a);
+  } else {
+    attention_mma_kernel<256><<<grid, MMA_THREADS, MmaSmem<256>::total(a.n_stages), stream>>>(a);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace sgk

@@ -1,0 +1,475 @@
+"""Python face of the C ABI, named after the reference's Rust surface.
+
+`DecodeResidentState.full_attention(...)` returns a `FullAttentionState` with the
+methods of the reference's `FullAttentionMetalState`
+(src/decode_resident/attention.rs:446-1038): seed, append_row, truncate,
+attention_decode[_windowed], encode_append_kv, encode_attention_decode_windowed,
+keys()/values(). Failures raise `InferError` whose `kind` is the reference's
+error variant (src/error.rs:12-75). Everything here only forwards to libsgk.so;
+there is no computation in Python.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _ffi
+
+KV_F32, KV_BF16, KV_U8G32 = 0, 1, 2
+PAGE_TOKENS = 16
+_KINDS = {1: "Dimension", 2: "Config", 3: "Backend", 4: "MemoryGuard", 5: "Shape", 6: "Timeout"}
+
+
+class InferError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"{_KINDS.get(code, code)}: {message}")
+        self.code = code
+        self.kind = _KINDS.get(code, str(code))
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise InferError(rc, _ffi.last_error())
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _ptr(a: np.ndarray) -> int:
+    return a.ctypes.data
+
+
+class Rope(C.Structure):
+    """sgk_rope: RopeParams + rope_dims + eps + pairing style."""
+    _fields_ = [("rope_dims", C.c_int32), ("frequency_dim", C.c_int32), ("theta", C.c_float),
+                ("position_scale", C.c_float), ("eps", C.c_float), ("interleaved", C.c_int32)]
+
+
+def make_rope(rope_dims, theta, eps=1e-6, frequency_dim=None, position_scale=1.0, interleaved=False) -> Rope:
+    return Rope(rope_dims, rope_dims if frequency_dim is None else frequency_dim, theta, position_scale, eps,
+                1 if interleaved else 0)
+
+
+class DeviceBuffer:
+    """A device allocation owned through the ABI (f32 unless stated)."""
+
+    def __init__(self, state: "DecodeResidentState", nbytes: int):
+        self.state = state
+        self.nbytes = int(nbytes)
+        p = C.c_void_p()
+        check(state.L.sgk_util_malloc(state.h, self.nbytes, C.byref(p)))
+        self.ptr = p.value
+
+    def upload(self, array: np.ndarray) -> "DeviceBuffer":
+        a = np.ascontiguousarray(array)
+        assert a.nbytes <= self.nbytes
+        check(self.state.L.sgk_util_h2d(self.state.h, self.ptr, _ptr(a), a.nbytes))
+        return self
+
+    def download(self, dtype=np.float32, count=None) -> np.ndarray:
+        n = self.nbytes // np.dtype(dtype).itemsize if count is None else count
+        out = np.empty(n, dtype=dtype)
+        check(self.state.L.sgk_util_d2h(self.state.h, _ptr(out), self.ptr, out.nbytes))
+        return out
+
+    def free(self):
+        if self.ptr:
+            self.state.L.sgk_util_free(self.state.h, self.ptr)
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class DecodeResidentState:
+    """DecodeResidentState::new (src/decode_resident/arena.rs:247-349)."""
+
+    def __init__(self, device: int = 0):
+        self.L = _ffi.lib()
+        h = C.c_void_p()
+        check(self.L.sgk_state_create(device, C.byref(h)))
+        self.h = h
+        self.device = device
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.L.sgk_state_destroy(self.h)
+            self.h = None
+
+    @property
+    def stream(self) -> int:
+        return self.L.sgk_state_stream(self.h)
+
+    def sync(self):
+        check(self.L.sgk_state_sync(self.h))
+
+    def device_status(self) -> int:
+        s = C.c_int32()
+        check(self.L.sgk_state_device_status(self.h, C.byref(s)))
+        return s.value
+
+    def full_attention(self, capacity, q_heads, kv_heads, head_dim, dtype=KV_F32, shuffled_seed=None):
+        """state.full_attention(capacity, q, kv, hd, sampled) (attention.rs:26-108)."""
+        h = C.c_void_p()
+        if shuffled_seed is None:
+            check(self.L.sgk_kv_create(self.h, capacity, q_heads, kv_heads, head_dim, dtype, PAGE_TOKENS, C.byref(h)))
+        else:
+            check(self.L.sgk_kv_create_shuffled(self.h, capacity, q_heads, kv_heads, head_dim, dtype, shuffled_seed,
+                                                C.byref(h)))
+        return FullAttentionState(self, h, owned=True)
+
+    def pool(self, layers, kv_heads, head_dim, dtype, num_pages, max_seqs, max_seq_tokens):
+        return PagePool(self, layers, kv_heads, head_dim, dtype, num_pages, max_seqs, max_seq_tokens)
+
+    def alloc(self, nbytes) -> DeviceBuffer:
+        return DeviceBuffer(self, nbytes)
+
+    def upload(self, array) -> DeviceBuffer:
+        a = np.ascontiguousarray(array)
+        return DeviceBuffer(self, max(a.nbytes, 16)).upload(a)
+
+    def fill_normal(self, buf: DeviceBuffer, n, seed, stream_id, index0=0, stream=None):
+        check(self.L.sgk_util_fill_normal(self.h, stream, buf.ptr, n, seed, stream_id, index0))
+
+    def rms_norm_rope_decode(self, x, weight, heads, head_dim, rope: Rope, position):
+        """DecodeResidentState::rms_norm_rope_decode (attention.rs:386-444)."""
+        x, w = _f32(x).ravel(), _f32(weight).ravel()
+        out = np.empty(heads * head_dim, np.float32)
+        check(self.L.sgk_rms_norm_rope_decode(self.h, _ptr(x), _ptr(w), heads, head_dim, C.byref(rope), position,
+                                              _ptr(out)))
+        return out
+
+    def copy_blocks(self, dst: DeviceBuffer, src: DeviceBuffer, n_pages, page_bytes, dst_pages=None, src_pages=None,
+                    stream=None):
+        check(self.L.sgk_util_copy_blocks(self.h, stream, dst.ptr, src.ptr,
+                                          None if dst_pages is None else dst_pages.ptr,
+                                          None if src_pages is None else src_pages.ptr, n_pages, page_bytes))
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class PagePool:
+    def __init__(self, state, layers, kv_heads, head_dim, dtype, num_pages, max_seqs, max_seq_tokens):
+        self.state = state
+        self.L = _ffi.lib()
+        h = C.c_void_p()
+        check(self.L.sgk_pool_create(state.h if state is not None else None, layers, kv_heads, head_dim, dtype,
+                                     PAGE_TOKENS, num_pages, max_seqs, max_seq_tokens, C.byref(h)))
+        self.h = h
+        self.layers, self.kv_heads, self.head_dim, self.dtype = layers, kv_heads, head_dim, dtype
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.L.sgk_pool_destroy(self.h)
+            self.h = None
+
+    num_pages = property(lambda s: s.L.sgk_pool_num_pages(s.h))
+    free_pages = property(lambda s: s.L.sgk_pool_free_pages(s.h))
+    page_bytes = property(lambda s: s.L.sgk_pool_page_bytes(s.h))
+    used_bytes = property(lambda s: s.L.sgk_pool_used_bytes(s.h))
+
+    def shuffle_free_list(self, seed):
+        check(self.L.sgk_pool_shuffle_free_list(self.h, seed))
+
+    def refcount(self, page):
+        out = C.c_int32()
+        check(self.L.sgk_pool_page_refcount(self.h, page, C.byref(out)))
+        return out.value
+
+    def set_scrub_on_free(self, enabled=True):
+        check(self.L.sgk_pool_set_scrub_on_free(self.h, int(enabled)))
+
+    def sequence(self, capacity_tokens):
+        return Sequence(self, capacity_tokens)
+
+
+class Sequence:
+    def __init__(self, pool: PagePool, capacity_tokens):
+        self.pool = pool
+        self.L = pool.L
+        h = C.c_void_p()
+        check(self.L.sgk_seq_create(pool.h, capacity_tokens, C.byref(h)))
+        self.h = h
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.L.sgk_seq_destroy(self.h)
+            self.h = None
+
+    def reserve(self, tokens):
+        check(self.L.sgk_seq_reserve(self.h, tokens))
+
+    def block_table(self):
+        n = C.c_int64()
+        check(self.L.sgk_seq_block_table(self.h, None, 0, C.byref(n)))
+        out = np.empty(n.value, np.int32)
+        check(self.L.sgk_seq_block_table(self.h, _ptr(out), n.value, C.byref(n)))
+        return out
+
+    def release_before(self, row):
+        check(self.L.sgk_seq_release_before(self.h, row))
+
+    def layer(self, layer, q_heads):
+        h = C.c_void_p()
+        check(self.L.sgk_seq_layer(self.h, layer, q_heads, C.byref(h)))
+        return FullAttentionState(self.pool.state, h, owned=False)
+
+
+class FullAttentionState:
+    """FullAttentionMetalState (src/decode_resident/attention.rs:446-1038)."""
+
+    def __init__(self, state: DecodeResidentState, handle, owned: bool):
+        self.state = state
+        self.L = _ffi.lib()
+        self.h = handle
+        self.owned = owned
+
+    def close(self):
+        if self.owned and getattr(self, "h", None):
+            self.L.sgk_kv_destroy(self.h)
+        self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def len(self):
+        return self.L.sgk_kv_len(self.h)
+
+    def capacity(self):
+        return self.L.sgk_kv_capacity(self.h)
+
+    def kv_dim(self):
+        return self.L.sgk_kv_kv_dim(self.h)
+
+    def q_heads(self):
+        return self.L.sgk_kv_q_heads(self.h)
+
+    def kv_heads(self):
+        return self.L.sgk_kv_kv_heads(self.h)
+
+    def head_dim(self):
+        return self.L.sgk_kv_head_dim(self.h)
+
+    def dtype(self):
+        return self.L.sgk_kv_dtype(self.h)
+
+    def byte_len(self):
+        return self.L.sgk_kv_byte_len(self.h)
+
+    def truncate(self, n):
+        check(self.L.sgk_kv_truncate(self.h, n))
+
+    def seed(self, keys_rows, values_rows, n_rows):
+        k, v = _f32(keys_rows).ravel(), _f32(values_rows).ravel()
+        check(self.L.sgk_kv_seed_f32(self.h, _ptr(k), k.size, _ptr(v), v.size, n_rows))
+
+    def append_row(self, key, value):
+        k, v = _f32(key).ravel(), _f32(value).ravel()
+        check(self.L.sgk_kv_append_row_f32(self.h, _ptr(k), k.size, _ptr(v), v.size))
+
+    def append_batch(self, keys, values, n_rows=None):
+        k, v = _f32(keys), _f32(values)
+        n = k.shape[0] if n_rows is None else n_rows
+        check(self.L.sgk_kv_append_rows_f32(self.h, _ptr(k), k.size, _ptr(v), v.size, n))
+
+    def encode_append_kv(self, d_k: DeviceBuffer, d_v: DeviceBuffer, stream=None):
+        check(self.L.sgk_kv_enqueue_append(self.h, stream, d_k.ptr if d_k else None, d_v.ptr if d_v else None))
+
+    def encode_append_rows(self, d_k: DeviceBuffer, d_v: DeviceBuffer, n_rows, stream=None):
+        check(self.L.sgk_kv_enqueue_append_rows(self.h, stream, d_k.ptr, d_v.ptr, n_rows))
+
+    def encode_rope_append(self, d_k_raw, d_v, d_weight, rope: Rope, stream=None):
+        check(self.L.sgk_kv_enqueue_rope_append(self.h, stream, d_k_raw.ptr, d_v.ptr, d_weight.ptr, C.byref(rope)))
+
+    def attention_decode(self, q, attn_scalar=0.0):
+        return self.attention_decode_windowed(q, 0, attn_scalar)
+
+    def attention_decode_windowed(self, q, window_start, attn_scalar=0.0):
+        q = _f32(q).ravel()
+        out = np.empty(self.q_heads() * self.head_dim(), np.float32)
+        check(self.L.sgk_kv_attention_decode(self.h, _ptr(q), q.size, window_start, attn_scalar, _ptr(out)))
+        return out
+
+    def encode_attention_decode_windowed(self, d_q, d_out, window_start=0, attn_scalar=0.0, stream=None):
+        check(self.L.sgk_kv_enqueue_attention(self.h, stream, d_q.ptr if d_q else None,
+                                              d_out.ptr if d_out else None, window_start, attn_scalar))
+
+    def encode_append_attention(self, d_k, d_v, d_q, d_out, sliding_window=0, attn_scalar=0.0, stream=None):
+        check(self.L.sgk_kv_enqueue_append_attention(self.h, stream, d_k.ptr, d_v.ptr, d_q.ptr, d_out.ptr,
+                                                     sliding_window, attn_scalar))
+
+    def _gather(self, row0, n):
+        n = self.len() - row0 if n is None else n
+        dt = {KV_F32: np.float32, KV_BF16: np.uint16}[self.dtype()]
+        k = np.empty((n, self.kv_dim()), dt)
+        v = np.empty((n, self.kv_dim()), dt)
+        check(self.L.sgk_kv_gather_rows(self.h, row0, n, _ptr(k), _ptr(v)))
+        return k, v
+
+    def keys(self, row0=0, n=None):
+        """kv.keys() read-back: rows in the storage type (bf16 as bit patterns)."""
+        return self._gather(row0, n)[0]
+
+    def values(self, row0=0, n=None):
+        return self._gather(row0, n)[1]
+
+    def gather_rows(self, row0=0, n=None):
+        return self._gather(row0, n)
+
+    def gather_rows_f32(self, row0=0, n=None):
+        n = self.len() - row0 if n is None else n
+        k = np.empty((n, self.kv_dim()), np.float32)
+        v = np.empty((n, self.kv_dim()), np.float32)
+        check(self.L.sgk_kv_gather_rows_f32(self.h, row0, n, _ptr(k), _ptr(v)))
+        return k, v
+
+    def gather_rows_u8(self, row0=0, n=None):
+        n = self.len() - row0 if n is None else n
+        d, g = self.kv_dim(), self.kv_dim() // 32
+        out = [np.empty((n, d), np.uint8), np.empty((n, g), np.uint16), np.empty((n, g), np.uint16),
+               np.empty((n, d), np.uint8), np.empty((n, g), np.uint16), np.empty((n, g), np.uint16)]
+        check(self.L.sgk_kv_gather_rows_u8(self.h, row0, n, *[_ptr(a) for a in out]))
+        return out
+
+    def block_table(self):
+        n = C.c_int64()
+        check(self.L.sgk_kv_block_table(self.h, None, 0, C.byref(n)))
+        out = np.empty(n.value, np.int32)
+        check(self.L.sgk_kv_block_table(self.h, _ptr(out), n.value, C.byref(n)))
+        return out
+
+    def set_attention_kernel(self, which):
+        check(self.L.sgk_kv_set_attention_kernel(self.h, which))
+
+
+class Batch:
+    """n sequences of one layer decoded in one launch."""
+
+    def __init__(self, state: DecodeResidentState, kvs):
+        self.state, self.L, self.kvs = state, _ffi.lib(), list(kvs)
+        arr = (C.c_void_p * len(self.kvs))(*[kv.h for kv in self.kvs])
+        h = C.c_void_p()
+        check(self.L.sgk_batch_create(state.h, arr, len(self.kvs), C.byref(h)))
+        self.h = h
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.L.sgk_batch_destroy(self.h)
+            self.h = None
+
+    def enqueue_append(self, d_k, d_v, stream=None):
+        check(self.L.sgk_batch_enqueue_append(self.h, stream, d_k.ptr, d_v.ptr))
+
+    def enqueue_attention(self, d_q, d_out, sliding_window=0, attn_scalar=0.0, stream=None):
+        check(self.L.sgk_batch_enqueue_attention(self.h, stream, d_q.ptr, d_out.ptr, sliding_window, attn_scalar))
+
+    def enqueue_step(self, d_k, d_v, d_q, d_out, sliding_window=0, attn_scalar=0.0, stream=None):
+        check(self.L.sgk_batch_enqueue_step(self.h, stream, d_k.ptr, d_v.ptr, d_q.ptr, d_out.ptr, sliding_window,
+                                            attn_scalar))
+
+    def set_splits(self, splits):
+        check(self.L.sgk_batch_set_splits(self.h, splits))
+
+    def last_splits(self):
+        s = C.c_int32()
+        check(self.L.sgk_batch_get_splits(self.h, C.byref(s)))
+        return s.value
+
+    def set_kernel(self, which):
+        check(self.L.sgk_batch_set_kernel(self.h, which))
+
+    def last_kernel(self):
+        s = C.c_int32()
+        check(self.L.sgk_batch_last_kernel(self.h, C.byref(s)))
+        return s.value
+
+
+class Step:
+    """Every layer of a batch: one decode token = one stream submission."""
+
+    def __init__(self, state: DecodeResidentState, batches):
+        self.state, self.L, self.batches = state, _ffi.lib(), list(batches)
+        arr = (C.c_void_p * len(self.batches))(*[b.h for b in self.batches])
+        h = C.c_void_p()
+        check(self.L.sgk_step_create(state.h, arr, len(self.batches), C.byref(h)))
+        self.h = h
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.L.sgk_step_destroy(self.h)
+            self.h = None
+
+    @staticmethod
+    def _windows(w):
+        if w is None:
+            return None, None
+        arr = np.ascontiguousarray(w, dtype=np.int64)
+        return arr, _ptr(arr)
+
+    def enqueue(self, d_k, d_v, d_q, d_out, sliding_windows=None, attn_scalar=0.0, stream=None):
+        keep, p = self._windows(sliding_windows)
+        check(self.L.sgk_step_enqueue(self.h, stream, d_k.ptr, d_v.ptr, d_q.ptr, d_out.ptr, p, attn_scalar))
+
+    def capture(self, d_k, d_v, d_q, d_out, sliding_windows=None, attn_scalar=0.0):
+        keep, p = self._windows(sliding_windows)
+        check(self.L.sgk_step_capture(self.h, d_k.ptr, d_v.ptr, d_q.ptr, d_out.ptr, p, attn_scalar))
+
+    def replay(self, stream=None):
+        check(self.L.sgk_step_replay(self.h, stream))
+
+    def run_host(self, k, v, q, out, sliding_windows=None, attn_scalar=0.0):
+        keep, p = self._windows(sliding_windows)
+        check(self.L.sgk_step_run_host(self.h, _ptr(k), _ptr(v), _ptr(q), _ptr(out), p, attn_scalar))
+
+    def launches(self):
+        return self.L.sgk_step_launches(self.h)
+
+
+class LinearAttentionState:
+    """LinearAttentionMetalState of all recurrent layers (src/metal_backend/mod.rs:507-531)."""
+
+    def __init__(self, state, layers=None, conv_len=None, ssm_len=None, ssm_bf16=False, handle=None):
+        self.state, self.L = state, _ffi.lib()
+        if handle is None:
+            handle = C.c_void_p()
+            check(self.L.sgk_linstate_create(state.h, layers, conv_len, ssm_len, int(ssm_bf16), C.byref(handle)))
+        self.h = handle
+        self.layers, self.conv_len, self.ssm_len, self.ssm_bf16 = layers, conv_len, ssm_len, ssm_bf16
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.L.sgk_linstate_destroy(self.h)
+            self.h = None
+
+    def estimated_bytes(self):
+        return self.L.sgk_linstate_bytes(self.h)
+
+    def write(self, layer, conv, ssm):
+        c, s = _f32(conv).ravel(), _f32(ssm).ravel()
+        assert c.size == self.conv_len and s.size == self.ssm_len
+        check(self.L.sgk_linstate_write(self.h, layer, _ptr(c), _ptr(s)))
+
+    def read(self, layer):
+        c, s = np.empty(self.conv_len, np.float32), np.empty(self.ssm_len, np.float32)
+        check(self.L.sgk_linstate_read(self.h, layer, _ptr(c), _ptr(s)))
+        return c, s
+
+    def snapshot(self, stream=None):
+        h = C.c_void_p()
+        check(self.L.sgk_linstate_snapshot(self.h, stream, C.byref(h)))
+        return LinearAttentionState(self.state, self.layers, self.conv_len, self.ssm_len, self.ssm_bf16, handle=h)
+
+    def restore(self, snapshot, stream=None):
+        check(self.L.sgk_linstate_restore(self.h, stream, snapshot.h))

@@ -1,0 +1,199 @@
+"""CPU-side checks of libsgk.so: every symbol sgk.h declares is exported, the
+host-only logic (hashes, prefix-cache bookkeeping, budget, page accounting)
+agrees with the oracle, and nothing computes without a GPU."""
+import ctypes as C
+import random
+import re
+
+import numpy as np
+import pytest
+
+import saragossa_b200 as sg
+from oracle import sgo
+from saragossa_b200 import _ffi
+
+
+def test_library_exports_every_declared_symbol():
+    protos = _ffi.parse_header()
+    text = open(_ffi.HEADER).read()
+    declared = set(re.findall(r"\b(sgk_[a-z0-9_]+)\s*\(", text))
+    assert declared == set(protos), declared ^ set(protos)
+    handle = C.CDLL(_ffi.LIB_PATH)
+    for name in declared:
+        assert hasattr(handle, name), name
+    assert len(declared) >= 90
+
+
+def test_no_cpu_fallback_without_device():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    with pytest.raises(sg.InferError) as err:
+        sg.DecodeResidentState(0)
+    assert err.value.kind == "Backend" and "no CPU path" in str(err.value)
+
+
+def test_block_hashes_match_oracle():
+    assert sg.BlockHash.root() == sgo.hash_root() == bytes(32)
+    for key in (None, "", "alpha", "agent-b", "é" * 40):
+        assert sg.BlockHash.for_session(key) == sgo.hash_for_session(key)
+    rng = random.Random(3)
+    prev = sg.BlockHash.for_session("s")
+    for n in (0, 1, 2, 3, 7, 16, 256):
+        toks = [rng.randrange(0, 2 ** 63) for _ in range(n)]
+        got = sg.BlockHash.chain(prev, toks)
+        assert got == sgo.hash_chain(prev, toks)
+        prev = got
+
+
+def _trace(seed, n_ops, block_tokens, capacity, per_session):
+    """Random serve-like trace replayed on the oracle and on libsgk."""
+    rng = random.Random(seed)
+    ours = sg.BlockAwarePrefixCache(block_tokens, capacity, per_session)
+    ref = sgo.BlockAwarePrefixCache(block_tokens, capacity, per_session)
+    sessions = [None, "a", "b", "c"]
+    prompts = [[rng.randrange(0, 5) for _ in range(rng.randrange(1, 7) * block_tokens + rng.randrange(0, block_tokens))]
+               for _ in range(6)]
+    for _ in range(n_ops):
+        op = rng.random()
+        root = sg.BlockHash.for_session(rng.choice(sessions))
+        toks = rng.choice(prompts)
+        if op < 0.45:
+            hit, want = ours.match_prefix(root, toks), ref.match_prefix(root, toks)
+            assert (hit is None) == (want is None)
+            if hit is not None:
+                assert (hit.tokens, hit.hash) == (want["tokens"], want["hash"])
+        elif op < 0.9:
+            # what prefill_prompt_state does: remember every full block of the prompt
+            prev = root
+            for i in range(len(toks) // block_tokens):
+                prev = sg.BlockHash.chain(prev, toks[i * block_tokens:(i + 1) * block_tokens])
+                if rng.random() < 0.7:
+                    ours.insert(root, prev, (i + 1) * block_tokens)
+                    ref.insert(root, prev, (i + 1) * block_tokens)
+        else:
+            got, want = ours.evict_lru_block(), ref.evict_lru_block()
+            assert (got is None) == (want is None)
+        assert [(s, h, t) for s, h, t in ours.entries()] == [(s, h, t) for s, h, t, _ in ref.entries()]
+    assert ours.evicted() == [(s, h, t) for s, h, t, _ in ref.evicted()]
+    assert len(ours) == len(ref)
+    return len(ours.evicted())
+
+
+@pytest.mark.parametrize("cfg", [(1, 2, 2), (2, 8, 8), (2, 5, 2), (3, 4, 1), (16, 12, 6)])
+def test_prefix_cache_trace_matches_oracle(cfg):
+    evicted = sum(_trace(seed, 300, *cfg) for seed in range(4))
+    assert evicted > 0
+
+
+def test_reference_prefix_cases_through_the_abi():
+    # the ordering assertions of src/serve/cache.rs:341-466, through libsgk
+    cache = sg.BlockAwarePrefixCache(1, 2, 1)
+    alpha, beta = sg.BlockHash.for_session("agent-a"), sg.BlockHash.for_session("agent-b")
+    beta_first = sg.BlockHash.chain(beta, [9])
+    alpha_first = sg.BlockHash.chain(alpha, [1])
+    alpha_second = sg.BlockHash.chain(alpha_first, [2])
+    cache.insert(beta, beta_first, 1)
+    cache.insert(alpha, alpha_first, 1)
+    cache.insert(alpha, alpha_second, 2)
+    assert [e[1] for e in cache.entries()] == [alpha_second, beta_first]
+    assert cache.match_prefix(beta, [9]).hash == beta_first
+    assert cache.session_block_count(alpha) == 1
+    zero = sg.BlockAwarePrefixCache(1, 0)
+    assert zero.insert(alpha, alpha_first, 1) is False and zero.match_prefix(alpha, [1]) is None
+    assert sg.BlockAwarePrefixCache(0, 4).block_tokens() == 1     # block_tokens.max(1), cache.rs:111
+
+
+def test_longest_prefix_entry_index_matches_oracle():
+    entries = [[1, 2], [1, 2, 3], [1]]
+    for prompt in ([1, 2, 3, 4], [1, 9], [9], [1, 2], []):
+        assert sg.longest_prefix_entry_index(entries, prompt) == sgo.longest_prefix_entry_index(entries, prompt)
+
+
+def test_budget_matches_oracle_guard():
+    # src/memory_guard.rs:734-788
+    g = sg.MemoryGuard(static_cap=900, total_memory=1200, headroom=200, device_cap=700)
+    assert g.limit_bytes() == 700
+    g = sg.MemoryGuard(static_cap=150)
+    g.set_usage(100)
+    assert g.check_allocation(50) == (150, 50)
+    with pytest.raises(sg.InferError) as err:
+        g.check_allocation(51)
+    assert err.value.kind == "MemoryGuard"
+    assert g.projection_over_limit(51) == (151, 50)
+    rng = random.Random(0)
+    for _ in range(200):
+        caps = [rng.choice([None, rng.randrange(1, 1000)]) for _ in range(3)]
+        head = rng.randrange(0, 300)
+        ours = sg.MemoryGuard(static_cap=caps[0], total_memory=caps[1], headroom=head, device_cap=caps[2])
+        ref = sgo.MemoryGuard(static_cap=caps[0], host_memory=caps[1], headroom=head, device_cap=caps[2])
+        assert ours.limit_bytes() == ref.limit()
+        cur, res, req = rng.randrange(0, 600), rng.randrange(0, 200), rng.randrange(0, 400)
+        ours.set_usage(cur, res)
+        ref.set(cur, res)
+        assert (ours.projection_over_limit(req) is None) == ref.check_allocation(req)[0]
+
+
+def test_host_only_pool_accounting_and_budget_eviction():
+    """Page sharing, copy-free restore and the budget loop on a bookkeeping-only pool."""
+    pool = sg.PagePool(None, layers=2, kv_heads=2, head_dim=64, dtype=sg.KV_BF16, num_pages=64, max_seqs=8,
+                       max_seq_tokens=512)
+    page_bytes = pool.page_bytes
+    assert page_bytes == 2 * 2 * 2 * 16 * 64 * 2
+    budget = 8 * page_bytes
+    cache = sg.BlockAwarePrefixCache(16, 100, pool=pool, budget_bytes=budget)
+    ref = sgo.BlockAwarePrefixCache(16, 100)
+    pins, seqs = {}, {}
+    for name in ("a", "b", "c", "a"):
+        root = sg.BlockHash.for_session(name)
+        if name not in seqs:
+            seq = pool.sequence(512)
+            seq.reserve(5 * 16)
+            for layer in range(2):
+                seq.layer(layer, 4).truncate(80)     # the cursors, moved the host-only way
+            seqs[name] = seq
+        seq = seqs[name]
+        toks = [ord(name) * 1000 + i for i in range(80)]
+        prev = root
+        for i in range(5):
+            prev = sg.BlockHash.chain(prev, toks[16 * i:16 * i + 16])
+            # oracle side: the reference's loop with this build's accounting (unique pinned pages)
+            pages = list(seq.block_table()[:i + 1])
+            dup = [e for e in ref.entries() if e[1] == prev]
+            skip = False
+            while True:
+                live = set(p for e in ref.entries() if e[1] != prev for p in pins[e[1]])
+                fresh = len(set(pages) - live)
+                if (len(live) + fresh) * page_bytes <= budget:
+                    break
+                if ref.evict_lru_block() is None:
+                    skip = True      # cache ran empty and the block still does not fit: not remembered
+                    break
+            pins[prev] = pages
+            inserted = cache.insert(root, prev, 16 * (i + 1), seq=seq)
+            assert inserted == (not skip)
+            if not skip:
+                ref.insert(root, prev, 16 * (i + 1))
+            assert [e[1] for e in cache.entries()] == [e[1] for e in ref.entries()]
+    assert cache.evicted() == [(s, h, t) for s, h, t, _ in ref.evicted()]
+    assert len(cache.evicted()) > 0 and len(cache) > 0
+    # an entry pins its whole prefix: the first page of a cached chain is shared by its entries
+    root = sg.BlockHash.for_session("a")
+    toks = [ord("a") * 1000 + i for i in range(80)]
+    hit = cache.match_prefix(root, toks)
+    assert hit is not None and hit.tokens == 80
+    first = int(seqs["a"].block_table()[0])
+    holders = sum(1 for e in cache.entries() if e[0] == root)
+    assert pool.refcount(first) == 1 + holders
+    free_before = pool.free_pages
+    other = pool.sequence(512)
+    cache.restore(hit, other, share=True)
+    assert pool.free_pages == free_before            # sharing takes no page
+    assert list(other.block_table()) == list(seqs["a"].block_table()[:5])
+    assert pool.refcount(first) == 2 + holders
+    other.close()
+    for seq in seqs.values():
+        seq.close()
+    cache.close()
+    assert pool.free_pages == 64
+    pool.close()
