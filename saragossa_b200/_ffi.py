@@ -13,7 +13,7 @@ import re
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 HEADER = os.path.join(os.path.dirname(HERE), "include", "sgk.h")
-LIB_PATH = os.path.join(HERE, "_lib", "libsgk.so")
+LIB_PATH = os.environ.get("SGK_LIB") or os.path.join(HERE, "_lib", "libsgk.so")
 
 _SCALARS = {
     "int32_t": C.c_int32, "int64_t": C.c_int64, "uint64_t": C.c_uint64, "uint32_t": C.c_uint32,

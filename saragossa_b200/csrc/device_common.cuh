@@ -52,13 +52,16 @@ __device__ __forceinline__ void merge_partials(const Partials& part, int64_t qh_
                                                int hd, float* out_row, int tid, int nthreads) {
   const float* ml = part.ml + qh_global * splits * 2;
   float m = -1.0e30f;
+#pragma unroll 8
   for (int s = 0; s < splits; ++s) m = fmaxf(m, __ldcg(ml + 2 * s));
   float denom = 0.0f;
+#pragma unroll 8
   for (int s = 0; s < splits; ++s) denom += __ldcg(ml + 2 * s + 1) * exp2f(__ldcg(ml + 2 * s) - m);
   float inv = 1.0f / denom;
   const float* o = part.o + qh_global * splits * hd;
   for (int d = tid; d < hd; d += nthreads) {
     float acc = 0.0f;
+#pragma unroll 8
     for (int s = 0; s < splits; ++s)
       acc += __ldcg(o + int64_t(s) * hd + d) * exp2f(__ldcg(ml + 2 * s) - m);
     out_row[d] = acc * inv;

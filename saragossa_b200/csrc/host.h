@@ -129,7 +129,11 @@ struct Batch {
   int32_t* d_counters = nullptr;  // [n*max(q_heads,kv_heads)] head, [n] seq, [n] append-done
   float* d_part_o = nullptr;
   float* d_part_ml = nullptr;
+  float* d_part2_o = nullptr;   // second merge level
+  float* d_part2_ml = nullptr;
+  int32_t* d_group_counters = nullptr;
   int max_splits = 1;
+  int max_groups = 1;
   int splits_override = 0;
   int kernel_override = 0;
   int last_kernel = 0;

@@ -6,11 +6,17 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "host.h"
 
 namespace sgk {
+
+#ifdef SGK_TRACE
+unsigned long long* g_trace = nullptr;
+extern "C" void sgk_debug_set_trace(unsigned long long* p) { g_trace = p; }
+#endif
 
 static thread_local std::string g_last_error;
 
@@ -222,6 +228,9 @@ Batch::~Batch() {
   if (d_counters) cudaFree(d_counters);
   if (d_part_o) cudaFree(d_part_o);
   if (d_part_ml) cudaFree(d_part_ml);
+  if (d_part2_o) cudaFree(d_part2_o);
+  if (d_part2_ml) cudaFree(d_part2_ml);
+  if (d_group_counters) cudaFree(d_group_counters);
 }
 
 int create_batch(State* st, Kv** kvs, int n, Batch** out) {
@@ -242,7 +251,7 @@ int create_batch(State* st, Kv** kvs, int n, Batch** out) {
   const int heads = std::max(b->q_heads, b->pool->kv_heads);
   // Splits never need to exceed about two blocks per SM for the whole launch.
   int by_sm = (2 * st->sm_count) / (n * b->pool->kv_heads);
-  b->max_splits = std::min(256, std::max(1, by_sm));
+  b->max_splits = std::min(144, std::max(1, by_sm));  // two merge levels of at most 12 partials each
   SGK_CUDA(cudaMalloc(&b->d_slots, size_t(n) * sizeof(int32_t)));
   SGK_CUDA(cudaMemcpy(b->d_slots, slots.data(), size_t(n) * sizeof(int32_t), cudaMemcpyHostToDevice));
   size_t counters = size_t(n) * heads + 2 * size_t(n);
@@ -251,6 +260,13 @@ int create_batch(State* st, Kv** kvs, int n, Batch** out) {
   size_t rows = size_t(n) * b->q_heads * b->max_splits;
   SGK_CUDA(cudaMalloc(&b->d_part_o, rows * b->pool->head_dim * sizeof(float)));
   SGK_CUDA(cudaMalloc(&b->d_part_ml, rows * 2 * sizeof(float)));
+  b->max_groups = 12;
+  size_t rows2 = size_t(n) * b->q_heads * b->max_groups;
+  SGK_CUDA(cudaMalloc(&b->d_part2_o, rows2 * b->pool->head_dim * sizeof(float)));
+  SGK_CUDA(cudaMalloc(&b->d_part2_ml, rows2 * 2 * sizeof(float)));
+  size_t gc = size_t(n) * b->pool->kv_heads * b->max_groups;
+  SGK_CUDA(cudaMalloc(&b->d_group_counters, gc * sizeof(int32_t)));
+  SGK_CUDA(cudaMemset(b->d_group_counters, 0, gc * sizeof(int32_t)));
   *out = b.release();
   return SGK_OK;
 }
@@ -386,6 +402,17 @@ int Batch::enqueue_attention(cudaStream_t stream, const float* d_q, float* d_out
   a.splits = choose_splits(kernel, max_rows);
   a.part.o = d_part_o;
   a.part.ml = d_part_ml;
+  a.part2.o = d_part2_o;
+  a.part2.ml = d_part2_ml;
+  a.group_counters = d_group_counters;
+  a.max_groups = max_groups;
+  // up to 12 partials are merged in one go; beyond that in groups of about sqrt(splits)
+  a.group_size = a.splits;
+  if (a.splits > 12) {
+    int g = static_cast<int>(std::ceil(std::sqrt(double(a.splits))));
+    a.group_size = std::min(g, 12);
+  }
+  a.n_groups = (a.splits + a.group_size - 1) / a.group_size;
   a.head_counters = d_counters;
   a.seq_counters = d_counters + size_t(n()) * std::max(q_heads, pool->kv_heads);
   a.status = st->d_status;
@@ -395,7 +422,17 @@ int Batch::enqueue_attention(cudaStream_t stream, const float* d_q, float* d_out
     a.v_new = d_v_new;
     int64_t pages = (max_rows + PAGE_TOKENS - 1) / PAGE_TOKENS + 1;
     int64_t per_split = (pages + a.splits - 1) / a.splits;
-    a.n_stages = static_cast<int>(std::max<int64_t>(2, std::min<int64_t>(attention_mma_max_stages(pool->head_dim), per_split)));
+    (void)per_split;
+    a.n_stages = attention_mma_max_stages(pool->head_dim);
+    // tuning flag (stages of the shared-memory ring), in the spirit of the reference's RETI_RUST_* switches
+    static const int env_stages = [] {
+      const char* e = std::getenv("SGK_ATTN_STAGES");
+      return e ? std::atoi(e) : 0;
+    }();
+    if (env_stages >= 4 && env_stages <= a.n_stages) a.n_stages = env_stages / 4 * 4;
+#ifdef SGK_TRACE
+    a.trace = g_trace;
+#endif
     SGK_CUDA(launch_attention_mma(a, n(), stream));
     if (fused)
       for (Kv* kv : kvs) kv->seq->len[layer] += 1;

@@ -50,6 +50,14 @@ struct AttnArgs {
   float scale_log2e;        // log2(e) / sqrt(attn_scalar)
   int32_t splits;
   Partials part;
+  // two-level merge of the tensor-core kernel: splits are merged in groups of
+  // group_size by the block that completes a group, the n_groups group results by
+  // the block that completes the head
+  int32_t group_size;
+  int32_t n_groups;
+  int32_t max_groups;
+  Partials part2;           // [n_seq * q_heads][max_groups][head_dim] and {max, sum}
+  int32_t* group_counters;  // [n_seq][kv_heads][max_groups]
   int32_t* head_counters;   // [n_seq][kv_heads] (tensor-core kernel) or [n_seq][q_heads] (generic)
   int32_t* seq_counters;    // [n_seq]
   int32_t* status;
@@ -58,6 +66,9 @@ struct AttnArgs {
   const float* k_new;  // [n_seq][kv_dim] or NULL
   const float* v_new;
   int32_t n_stages;
+#ifdef SGK_TRACE
+  unsigned long long* trace;  // [blocks][16] timestamps, debugging builds only
+#endif
 };
 
 cudaError_t launch_append_rows(const AppendArgs& a, int n_seq, cudaStream_t stream);

@@ -36,6 +36,7 @@ namespace sgk {
 constexpr int MMA_CONSUMERS = 4;                       // consumer warps
 constexpr int MMA_THREADS = (MMA_CONSUMERS + 1) * 32;  // + one producer warp
 constexpr int MMA_MAX_STAGES = 32;
+constexpr int MERGE_MAX = 12;  // partials merged at once (bound of group size and of group count)
 constexpr uint32_t WAIT_SPINS = 1u << 22;        // bound of every mbarrier wait
 constexpr uint32_t WAIT_SPINS_ABORTED = 1u << 10;
 
@@ -85,22 +86,24 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-               : "r"(addr));
+               : "r"(addr)
+               : "memory");
 }
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
                                                   uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-               : "r"(addr));
+               : "r"(addr)
+               : "memory");
 }
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
   uint32_t d;
-  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  asm("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
   return d;
 }
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -114,6 +117,16 @@ __device__ __forceinline__ void split_hi_lo(float x0, float x1, uint32_t& hi, ui
   hi = static_cast<uint32_t>(__bfloat16_as_ushort(h0)) | (static_cast<uint32_t>(__bfloat16_as_ushort(h1)) << 16);
   lo = static_cast<uint32_t>(__bfloat16_as_ushort(l0)) | (static_cast<uint32_t>(__bfloat16_as_ushort(l1)) << 16);
 }
+
+#ifdef SGK_TRACE
+#define SGK_TP(slot)                                                                               \
+  do {                                                                                             \
+    if (a.trace && (threadIdx.x & 31) == 0)                                                        \
+      a.trace[((size_t(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + (slot)] = clock64(); \
+  } while (0)
+#else
+#define SGK_TP(slot) do {} while (0)
+#endif
 
 template <int HD>
 struct MmaSmem {
@@ -132,6 +145,69 @@ struct MmaSmem {
   static size_t total(int stages) { return ring_bytes(stages) + FIXED + 1024; }
 };
 
+// Block-cooperative merge of `count` (<= MERGE_MAX) partials (rows first..first+count
+// of a [q head][stride][HD] array) for the gqa heads starting at qh0. A thread owns
+// cells of four dims; per pass it handles two cells and issues every load it needs
+// (the {max, sum} pairs of the cell's head and the partial values) before the first
+// use, so a pass costs one L2 round trip and no block barrier. final != 0: writes the
+// normalised output; else writes one un-normalised partial (row dst_row of dst).
+template <int HD>
+__device__ __forceinline__ void merge_block(const Partials& src, int stride, int first, int count, int gqa,
+                                            int64_t qh0, bool final, float* out, const Partials& dst,
+                                            int dst_stride, int dst_row, int tid) {
+  constexpr int CELLS = 2;
+  const int total = gqa * (HD / 4);
+  for (int base = 0; base < total; base += CELLS * MMA_THREADS) {
+    float2 ml[CELLS][MERGE_MAX];
+    float4 v[CELLS][MERGE_MAX];
+    int cell[CELLS];
+#pragma unroll
+    for (int c = 0; c < CELLS; ++c) {
+      cell[c] = base + c * MMA_THREADS + tid;
+      if (cell[c] < total) {
+        const int h = cell[c] / (HD / 4), d = (cell[c] % (HD / 4)) * 4;
+        const float* pm = src.ml + ((qh0 + h) * stride + first) * 2;
+        const float* po = src.o + ((qh0 + h) * stride + first) * HD + d;
+#pragma unroll
+        for (int p = 0; p < MERGE_MAX; ++p)
+          if (p < count) {
+            ml[c][p] = __ldcg(reinterpret_cast<const float2*>(pm + 2 * p));
+            v[c][p] = __ldcg(reinterpret_cast<const float4*>(po + int64_t(p) * HD));
+          }
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < CELLS; ++c) {
+      if (cell[c] >= total) continue;
+      const int h = cell[c] / (HD / 4), d = (cell[c] % (HD / 4)) * 4;
+      float m = -1.0e30f;
+#pragma unroll
+      for (int p = 0; p < MERGE_MAX; ++p)
+        if (p < count) m = fmaxf(m, ml[c][p].x);
+      float l = 0.0f;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int p = 0; p < MERGE_MAX; ++p)
+        if (p < count) {
+          const float w = exp2f(ml[c][p].x - m);
+          l += ml[c][p].y * w;
+          acc.x += v[c][p].x * w;
+          acc.y += v[c][p].y * w;
+          acc.z += v[c][p].z * w;
+          acc.w += v[c][p].w * w;
+        }
+      if (final) {
+        const float inv = 1.0f / l;
+        *reinterpret_cast<float4*>(out + (qh0 + h) * HD + d) =
+            make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+      } else {
+        *reinterpret_cast<float4*>(dst.o + ((qh0 + h) * dst_stride + dst_row) * HD + d) = acc;
+        if (d == 0) *reinterpret_cast<float2*>(dst.ml + ((qh0 + h) * dst_stride + dst_row) * 2) = make_float2(m, l);
+      }
+    }
+  }
+}
+
 template <int HD>
 __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs a) {
   using S = MmaSmem<HD>;
@@ -147,7 +223,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
   float* o_s = reinterpret_cast<float*>(ring);                  // [warps][8][OPAD], used after the ring drained
   float* ml_s = reinterpret_cast<float*>(fixed + S::Q_BYTES);   // [warps][8][2]
   uint64_t* bars = reinterpret_cast<uint64_t*>(fixed + S::Q_BYTES + S::ML_BYTES);
-  int* flags = reinterpret_cast<int*>(bars + 2 * MMA_MAX_STAGES);  // [0]=abort [1]=last-for-head [2]=len
+  int* flags = reinterpret_cast<int*>(bars + 2 * MMA_MAX_STAGES);  // [0]=abort [1]=last arriver
   volatile int* abort_flag = flags;
 
   const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
@@ -156,38 +232,19 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
   const int slot = a.slots ? a.slots[seq] : a.slot0;
   int32_t* len_ptr = a.pool.lens + int64_t(slot) * a.pool.layers + a.layer;
   const bool do_append = a.k_new != nullptr;
-
-  if (tid == 0) {
-    flags[0] = 0;
-    flags[1] = 0;
-    flags[2] = *len_ptr;
-    for (int s = 0; s < nst; ++s) {
-      mbar_init(smem_u32(bars + s), 1);                   // full: producer's expect_tx arrival
-      mbar_init(smem_u32(bars + MMA_MAX_STAGES + s), 1);  // empty: one consumer lane
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#ifdef SGK_TRACE
+  if (a.trace && tid == 0) {
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+    a.trace[((size_t(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + 15] = gt;
   }
-  // Q of the group: scale, split into bf16 hi/lo, rows of absent heads are zero.
-  {
-    const float* q = a.q + (int64_t(seq) * a.q_heads + int64_t(kvh) * gqa) * HD;
-    for (int i = tid; i < 8 * HD / 2; i += MMA_THREADS) {
-      int h = (2 * i) / HD;
-      float x0 = 0.0f, x1 = 0.0f;
-      if (h < gqa) {
-        float2 v = *reinterpret_cast<const float2*>(q + 2 * i);
-        x0 = v.x * a.scale_log2e;
-        x1 = v.y * a.scale_log2e;
-      }
-      uint32_t hi, lo;
-      split_hi_lo(x0, x1, hi, lo);
-      reinterpret_cast<uint32_t*>(q_hi)[i] = hi;
-      reinterpret_cast<uint32_t*>(q_lo)[i] = lo;
-    }
-  }
-  __syncthreads();
+  if (tid == 0) SGK_TP(0);
+#endif
 
-  const int64_t len_old = flags[2];
+  // Every thread reads the cursor itself (one broadcast L2 hit), so nothing below waits
+  // on a shared-memory hand-off. With a fused append the cursor is rewritten only by the
+  // block that arrives last for the sequence, i.e. after every block has read it.
+  const int64_t len_old = *reinterpret_cast<const volatile int32_t*>(len_ptr);
   const int64_t len = len_old + (do_append ? 1 : 0);
   int64_t ws = a.sliding_window > 0 ? (len > a.sliding_window ? len - a.sliding_window : 0) : a.window_start;
   if (ws >= len) ws = len > 0 ? len - 1 : 0;
@@ -203,11 +260,49 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
   const int64_t append_page_index = len_old / PAGE_TOKENS;
   const bool owns_append = do_append && append_page_index >= pb && append_page_index < pe;
 
+  int32_t first_entry = -1;
+  if (warp == MMA_CONSUMERS) {
+    // producer warp: barriers, and the first block-table entries, while the others stage Q
+    if (lane == 0) {
+      flags[0] = 0;
+      flags[1] = 0;
+      for (int s = 0; s < nst; ++s) {
+        mbar_init(smem_u32(bars + s), 1);                   // full: producer's expect_tx arrival
+        mbar_init(smem_u32(bars + MMA_MAX_STAGES + s), 1);  // empty: one consumer lane
+      }
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (lane < my_pages) first_entry = table[pb + lane];
+  } else {
+    // Q of the group: scale, split into bf16 hi/lo; rows of absent heads are zero.
+    // All loads are issued before the first conversion.
+    constexpr int NV = HD / 64;  // float4 per consumer thread
+    const float* q = a.q + (int64_t(seq) * a.q_heads + int64_t(kvh) * gqa) * HD;
+    float4 v[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int f = (tid + k * MMA_CONSUMERS * 32) * 4;
+      v[k] = (f / HD < gqa) ? __ldg(reinterpret_cast<const float4*>(q + f)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int f = (tid + k * MMA_CONSUMERS * 32) * 4;
+      uint32_t hi0, lo0, hi1, lo1;
+      split_hi_lo(v[k].x * a.scale_log2e, v[k].y * a.scale_log2e, hi0, lo0);
+      split_hi_lo(v[k].z * a.scale_log2e, v[k].w * a.scale_log2e, hi1, lo1);
+      *reinterpret_cast<uint2*>(q_hi + f) = make_uint2(hi0, hi1);
+      *reinterpret_cast<uint2*>(q_lo + f) = make_uint2(lo0, lo1);
+    }
+  }
+  __syncthreads();
+  if (tid == 0) SGK_TP(1);
+
   if (warp == MMA_CONSUMERS) {
     // ---------------- producer warp ----------------
     for (int base = 0; base < my_pages; base += 32) {
       int idx = base + lane;
-      int32_t entry = idx < my_pages ? table[pb + idx] : -1;
+      int32_t entry = base == 0 ? first_entry : (idx < my_pages ? table[pb + idx] : -1);
       int cnt = min(32, my_pages - base);
       for (int j = 0; j < cnt; ++j) {
         int i = base + j;
@@ -257,6 +352,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
       const int stage = i % nst;
       const uint32_t parity = (i / nst) & 1;
       const bool ok = mbar_wait(smem_u32(bars + stage), parity, abort_flag, a.status);
+      if (i == 0) SGK_TP(2);
       uint8_t* ktile = ring + size_t(stage) * S::STAGE;
       uint8_t* vtile = ktile + S::TILE;
       const int64_t page_index = pb + i;
@@ -293,21 +389,60 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
       }
 
       if (ok) {
-        // ---- S^T = K . Q^T (hi and lo parts of Q on two accumulators) ----
-        float sh[4] = {0.f, 0.f, 0.f, 0.f}, sl[4] = {0.f, 0.f, 0.f, 0.f};
+        // The tensor-core instructions have a long latency, so the page is processed as
+        // few, wide dependency levels: all K fragments are loaded, then the QK products go
+        // to eight independent accumulators (four for the hi part of Q, four for the lo part);
+        // the V fragments are loaded before the softmax so the stage can be handed back to the
+        // producer early; the PV products issue all hi parts, then all lo parts.
+        constexpr int CH = 8;                 // k-steps (QK) / dim tiles (PV) per chunk
+        constexpr int NCH = KSTEPS / CH;      // 1 for head_dim 128, 2 for 256
+        float acc[8][4];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.0f;
         const uint32_t kbase = smem_u32(ktile) + k_row * ROWB;
 #pragma unroll
-        for (int ks = 0; ks < KSTEPS; ++ks) {
-          int chunk = 2 * ks + k_csel;
-          int phys = (chunk & ~7) | ((chunk ^ k_row) & 7);
-          uint32_t a0, a1, a2, a3;
-          ldmatrix_x4(kbase + phys * 16, a0, a1, a2, a3);
-          mma_bf16(sh, a0, a1, a2, a3, qh_f[ks][0], qh_f[ks][1]);
-          mma_bf16(sl, a0, a1, a2, a3, ql_f[ks][0], ql_f[ks][1]);
+        for (int c = 0; c < NCH; ++c) {
+          uint32_t ka[CH][4];
+#pragma unroll
+          for (int u = 0; u < CH; ++u) {
+            int chunk = 2 * (c * CH + u) + k_csel;
+            int phys = (chunk & ~7) | ((chunk ^ k_row) & 7);
+            ldmatrix_x4(kbase + phys * 16, ka[u][0], ka[u][1], ka[u][2], ka[u][3]);
+          }
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int ks = c * CH + half * 4 + u;
+              mma_bf16(acc[u], ka[half * 4 + u][0], ka[half * 4 + u][1], ka[half * 4 + u][2], ka[half * 4 + u][3],
+                       qh_f[ks][0], qh_f[ks][1]);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int ks = c * CH + half * 4 + u;
+              mma_bf16(acc[4 + u], ka[half * 4 + u][0], ka[half * 4 + u][1], ka[half * 4 + u][2],
+                       ka[half * 4 + u][3], ql_f[ks][0], ql_f[ks][1]);
+            }
+          }
+        }
+        // V fragments of the first chunk (all of V for head_dim 128)
+        const uint32_t vbase = smem_u32(vtile) + v_row * ROWB;
+        uint32_t va[CH][4];
+#pragma unroll
+        for (int u = 0; u < CH; ++u) {
+          int chunk = 2 * u + v_csel;
+          int phys = (chunk & ~7) | ((chunk ^ v_row) & 7);
+          ldmatrix_x4_trans(vbase + phys * 16, va[u][0], va[u][1], va[u][2], va[u][3]);
+        }
+        if (NCH == 1) {
+          // every byte of the stage is in registers: give it back before the math
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(bars + MMA_MAX_STAGES + stage));
         }
         float s[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) s[e] = sh[e] + sl[e];
+        for (int e = 0; e < 4; ++e)
+          s[e] = ((acc[0][e] + acc[1][e]) + (acc[2][e] + acc[3][e])) + ((acc[4][e] + acc[5][e]) + (acc[6][e] + acc[7][e]));
         // rows g (s0,s1) and g+8 (s2,s3); heads 2t (s0,s2) and 2t+1 (s1,s3)
         if (row_base < ws || row_base + PAGE_TOKENS > len) {
           int64_t ra = row_base + g, rb = row_base + g + 8;
@@ -350,21 +485,32 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
         const uint32_t bh0 = movmatrix_trans(ph_a), bh1 = movmatrix_trans(ph_b);
         const uint32_t bl0 = movmatrix_trans(pl_a), bl1 = movmatrix_trans(pl_b);
         // ---- O^T += V^T . P^T ----
-        const uint32_t vbase = smem_u32(vtile) + v_row * ROWB;
 #pragma unroll
-        for (int j = 0; j < KSTEPS; ++j) {
-          int chunk = 2 * j + v_csel;
-          int phys = (chunk & ~7) | ((chunk ^ v_row) & 7);
-          uint32_t a0, a1, a2, a3;
-          ldmatrix_x4_trans(vbase + phys * 16, a0, a1, a2, a3);
-          mma_bf16(o_acc[j], a0, a1, a2, a3, bh0, bh1);
-          mma_bf16(o_acc[j], a0, a1, a2, a3, bl0, bl1);
+        for (int c = 0; c < NCH; ++c) {
+          if (c > 0) {
+#pragma unroll
+            for (int u = 0; u < CH; ++u) {
+              int chunk = 2 * (c * CH + u) + v_csel;
+              int phys = (chunk & ~7) | ((chunk ^ v_row) & 7);
+              ldmatrix_x4_trans(vbase + phys * 16, va[u][0], va[u][1], va[u][2], va[u][3]);
+            }
+            if (c == NCH - 1) {
+              __syncwarp();
+              if (lane == 0) mbar_arrive(smem_u32(bars + MMA_MAX_STAGES + stage));
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < CH; ++u) mma_bf16(o_acc[c * CH + u], va[u][0], va[u][1], va[u][2], va[u][3], bh0, bh1);
+#pragma unroll
+          for (int u = 0; u < CH; ++u) mma_bf16(o_acc[c * CH + u], va[u][0], va[u][1], va[u][2], va[u][3], bl0, bl1);
         }
+      } else {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(bars + MMA_MAX_STAGES + stage));
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(bars + MMA_MAX_STAGES + stage));
     }
 
+    if (warp == 0) SGK_TP(3);
     // ---- hand this warp's state to the merge buffer (it aliases the ring: wait
     //      until every warp has consumed its last stage) ----
     asm volatile("bar.sync 1, %0;" ::"r"(MMA_CONSUMERS * 32) : "memory");
@@ -390,6 +536,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
   }
   __syncthreads();
 
+  if (tid == 0) SGK_TP(4);
   // ---- merge the consumer warps; write the partial or the final output ----
   const int64_t qh0 = int64_t(seq) * a.q_heads + int64_t(kvh) * gqa;
   for (int idx = tid; idx < gqa * HD; idx += MMA_THREADS) {
@@ -416,14 +563,21 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
     }
   }
   if (a.splits > 1 || do_append) {
+    const int group = split / a.group_size;
+    const int group_first = group * a.group_size;
+    const int group_count = min(a.group_size, a.splits - group_first);
+    int32_t* group_counter = a.group_counters + (int64_t(seq) * a.pool.kv_heads + kvh) * a.max_groups + group;
+    int32_t* head_counter = a.head_counters + int64_t(seq) * a.pool.kv_heads + kvh;
     __syncthreads();
     if (tid == 0) {
       __threadfence();
       if (a.splits > 1) {
-        int old = atomicAdd(a.head_counters + int64_t(seq) * a.pool.kv_heads + kvh, 1);
-        flags[1] = (old == a.splits - 1);
+        int old = atomicAdd(group_counter, 1);
+        flags[1] = (old == group_count - 1);
+        if (flags[1]) *group_counter = 0;
       }
       if (do_append) {
+        // the block that arrives last for the sequence moves the cursor
         int total = a.splits * a.pool.kv_heads;
         int old = atomicAdd(a.seq_counters + seq, 1);
         if (old == total - 1) {
@@ -433,11 +587,30 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
       }
     }
     __syncthreads();
+    if (tid == 0) SGK_TP(5);
     if (a.splits > 1 && flags[1]) {
+      // this block completed its group: merge the group (or everything, if one group)
       __threadfence();
-      for (int h = 0; h < gqa; ++h)
-        merge_partials(a.part, qh0 + h, a.splits, HD, a.out + (qh0 + h) * HD, tid, MMA_THREADS);
-      if (tid == 0) a.head_counters[int64_t(seq) * a.pool.kv_heads + kvh] = 0;
+      const bool single = a.n_groups == 1;
+      merge_block<HD>(a.part, a.splits, group_first, group_count, gqa, qh0, single, a.out, a.part2,
+                      a.max_groups, group, tid);
+      if (tid == 0) SGK_TP(6);
+      if (!single) {
+        __syncthreads();
+        if (tid == 0) {
+          __threadfence();
+          int old = atomicAdd(head_counter, 1);
+          flags[1] = (old == a.n_groups - 1);
+          if (flags[1]) *head_counter = 0;
+        }
+        __syncthreads();
+        if (flags[1]) {
+          __threadfence();
+          merge_block<HD>(a.part2, a.max_groups, 0, a.n_groups, gqa, qh0, true, a.out, a.part2,
+                          a.max_groups, 0, tid);
+          if (tid == 0) SGK_TP(7);
+        }
+      }
     }
   }
 }
@@ -452,7 +625,10 @@ int attention_mma_max_stages(int head_dim) {
   size_t fixed = head_dim == 128 ? MmaSmem<128>::FIXED : MmaSmem<256>::FIXED;
   size_t stage = head_dim == 128 ? MmaSmem<128>::STAGE : MmaSmem<256>::STAGE;
   int n = static_cast<int>((budget - fixed - 1024) / stage);
-  return n > MMA_MAX_STAGES ? MMA_MAX_STAGES : n;
+  if (n > MMA_MAX_STAGES) n = MMA_MAX_STAGES;
+  // A stage must always be consumed by the same warp (stage = i % n, warp = i % MMA_CONSUMERS):
+  // otherwise a warp could wait on a phase of a barrier two ahead of the current one.
+  return n / MMA_CONSUMERS * MMA_CONSUMERS;
 }
 
 cudaError_t attention_mma_configure() {
