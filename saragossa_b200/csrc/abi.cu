@@ -197,10 +197,8 @@ int32_t sgk_seq_create(sgk_pool* p, int64_t capacity_tokens, sgk_seq** out) {
   s->len.assign(static_cast<size_t>(p->layers), 0);
   if (!p->host_only()) {
     cudaStream_t stream = p->st->stream;
-    for (int l = 0; l < p->layers; ++l) {
-      int rc = s->set_len(l, 0, stream);
-      if (rc != SGK_OK) return rc;
-    }
+    int rc = s->set_len_all(0, stream);
+    if (rc != SGK_OK) return rc;
     SGK_CUDA(cudaStreamSynchronize(stream));
   }
   p->live_seqs += 1;

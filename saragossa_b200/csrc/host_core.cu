@@ -191,7 +191,11 @@ int Seq::set_len(int layer, int64_t value, cudaStream_t stream) {
 }
 
 int Seq::set_len_all(int64_t value, cudaStream_t stream) {
-  for (int l = 0; l < pool->layers; ++l) SGK_TRY(set_len(l, value, stream));
+  for (int l = 0; l < pool->layers; ++l) len[l] = value;
+  if (pool->host_only()) return SGK_OK;
+  SGK_CUDA(launch_set_len(pool->d_lens + int64_t(slot) * pool->layers, static_cast<int32_t>(value), stream,
+                          pool->layers));
+  pool->st->launches += 1;
   return SGK_OK;
 }
 

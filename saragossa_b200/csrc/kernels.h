@@ -72,7 +72,8 @@ struct AttnArgs {
 };
 
 cudaError_t launch_append_rows(const AppendArgs& a, int n_seq, cudaStream_t stream);
-cudaError_t launch_set_len(int32_t* ptr, int32_t value, cudaStream_t stream);
+// Writes `value` into n consecutive int32 words (cursors, block-table entries), in stream order.
+cudaError_t launch_set_len(int32_t* ptr, int32_t value, cudaStream_t stream, int n = 1);
 
 cudaError_t launch_attention_generic(const AttnArgs& a, int n_seq, cudaStream_t stream);
 // Tensor-core paged kernel: bf16 pages, head_dim 128 or 256, q_heads/kv_heads <= 8.

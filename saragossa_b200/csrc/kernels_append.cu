@@ -155,10 +155,9 @@ __global__ void __launch_bounds__(128) append_rows_kernel(AppendArgs a) {
   }
 }
 
-__global__ void set_len_kernel(int32_t* ptr, int32_t value) { *ptr = value; }
-__global__ void add_len_kernel(int32_t* lens, const int32_t* slots, int n, int layers, int layer, int delta) {
+__global__ void set_len_kernel(int32_t* ptr, int n, int32_t value) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) lens[int64_t(slots[i]) * layers + layer] += delta;
+  if (i < n) ptr[i] = value;
 }
 
 cudaError_t launch_append_rows(const AppendArgs& a, int n_seq, cudaStream_t stream) {
@@ -168,8 +167,8 @@ cudaError_t launch_append_rows(const AppendArgs& a, int n_seq, cudaStream_t stre
   return cudaGetLastError();
 }
 
-cudaError_t launch_set_len(int32_t* ptr, int32_t value, cudaStream_t stream) {
-  set_len_kernel<<<1, 1, 0, stream>>>(ptr, value);
+cudaError_t launch_set_len(int32_t* ptr, int32_t value, cudaStream_t stream, int n) {
+  set_len_kernel<<<(n + 127) / 128, 128, 0, stream>>>(ptr, n, value);
   return cudaGetLastError();
 }
 
