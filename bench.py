@@ -426,6 +426,7 @@ def prefix_restore_gbs(sg, st, torch, stream):
 
 
 def main():
+    global LAYERS, BATCH, CTX
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
@@ -438,7 +439,6 @@ def main():
     ap.add_argument("--skip-extras", action="store_true",
                     help="only the device-resident timing (no e2e, batch-1, prefix-restore or CPU legs)")
     args = ap.parse_args()
-    global LAYERS, BATCH, CTX
     reduced = (args.layers, args.batch, args.ctx) != (LAYERS, BATCH, CTX)
     LAYERS, BATCH, CTX = args.layers, args.batch, args.ctx
     args.reduced = reduced
