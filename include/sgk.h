@@ -155,6 +155,21 @@ int32_t sgk_kv_attention_decode(sgk_kv* kv, const float* q, size_t q_len, int64_
 /* kv.encode_attention_decode_windowed(enc,q,scores,out,ws) (attention.rs:736-835) */
 int32_t sgk_kv_enqueue_attention(sgk_kv* kv, void* stream, const float* d_q, float* d_out,
                                  int64_t window_start, float attn_scalar);
+/* NO COUNTERPART IN THE REFERENCE. Same computation and same errors as
+ * sgk_kv_enqueue_attention, for callers that cannot allocate device memory (a host
+ * that owns the whole device through its own arena, a latency-critical loop that
+ * must not take cudaMalloc's implicit synchronisation, code running under stream
+ * capture). It never calls cudaMalloc/cudaFree: the split-K workspace is one static
+ * device array of SGK_NOALLOC_SCRATCH_BYTES that every GPU loading the library
+ * holds until exit. Limits: q_heads*head_dim <= SGK_NOALLOC_MAX_Q_DIM (larger shapes
+ * get SGK_ERR_CONFIG); the split count is reduced to fit the array. The first call
+ * on a device resolves the array's device address (cudaGetSymbolAddress): make it
+ * before any stream capture. All calls share the array: calls whose kernels may
+ * overlap on the GPU race and must be ordered by the caller. */
+#define SGK_NOALLOC_SCRATCH_BYTES (4u << 20)
+#define SGK_NOALLOC_MAX_Q_DIM 16384
+int32_t sgk_kv_enqueue_attention_noalloc(sgk_kv* kv, void* stream, const float* d_q, float* d_out,
+                                         int64_t window_start, float attn_scalar);
 /* encode_append_kv + encode_attention_decode_windowed in ONE launch
  * (the per-layer pair at src/decode_resident/layers.rs:259-288). */
 int32_t sgk_kv_enqueue_append_attention(sgk_kv* kv, void* stream, const float* d_k, const float* d_v,

@@ -23,6 +23,7 @@ SOURCES = [
     "kernels_attn_generic.cu",
     "kernels_attn_mma.cu",
     "kernels_copy.cu",
+    "noalloc.cu",
 ]
 
 NVCC_FLAGS = [

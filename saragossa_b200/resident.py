@@ -306,6 +306,13 @@ class FullAttentionState:
         check(self.L.sgk_kv_enqueue_attention(self.h, stream, d_q.ptr if d_q else None,
                                               d_out.ptr if d_out else None, window_start, attn_scalar))
 
+    def encode_attention_decode_noalloc(self, d_q, d_out, window_start=0, attn_scalar=0.0, stream=None):
+        """Same result as encode_attention_decode_windowed, for callers that cannot allocate device
+        memory: the split-K workspace is the library's static 4 MiB device array. Make the first call
+        on a device before any stream capture, and do not let two such calls overlap on the GPU."""
+        check(self.L.sgk_kv_enqueue_attention_noalloc(self.h, stream, d_q.ptr if d_q else None,
+                                                      d_out.ptr if d_out else None, window_start, attn_scalar))
+
     def encode_append_attention(self, d_k, d_v, d_q, d_out, sliding_window=0, attn_scalar=0.0, stream=None):
         check(self.L.sgk_kv_enqueue_append_attention(self.h, stream, d_k.ptr, d_v.ptr, d_q.ptr, d_out.ptr,
                                                      sliding_window, attn_scalar))
