@@ -39,7 +39,7 @@ CTX, BATCH = 32768, 8
 KV_DIM, Q_DIM = KV_HEADS * HEAD_DIM, Q_HEADS * HEAD_DIM
 WORKLOAD = ("C2: Qwen3-30B-A3B-shaped KV path, 48 layers, 32Q/4KV heads, head_dim 128, bf16 KV, "
             "16-token pages, shuffled block table, ctx 32768, batch 8 per GPU")
-# ncu, attention_mma_kernel<128> at this shape (profiles/attention_mma_hd128_c2.md):
+# ncu capture of attention_mma_kernel<128> at this shape (summary kept under profiles/):
 # DRAM read+write bytes per launch divided by the algorithmic bytes of the launch.
 NCU_TRAFFIC_RATIO = 1.0076
 
