@@ -315,6 +315,11 @@ def run_ours(args):
     b1_us_layer = ms_b1 * 1e3 / (b1_steps * LAYERS)
     b1_gbs = b1_bytes / (ms_b1 * 1e-3) / 1e9
 
+    # ---- one long sequence sharded by KV-head group (only where kv heads divide over the ranks) ----
+    head_sharded = None
+    if world > 1 and KV_HEADS % world == 0:
+        head_sharded = head_sharded_leg(sg, st, torch, dist, world, rank, stream)
+
     # ---- prefix restore: block copy of a 4096-token prefix on the 4B shape (config 4) ----
     restore = prefix_restore_gbs(sg, st, torch, stream)
 
@@ -338,7 +343,7 @@ def run_ours(args):
             "decode_steps_per_s": BATCH * world * K / (ms * 1e-3),
             "batch1": {"us_per_layer": b1_us_layer, "hbm_gbs": b1_gbs, "steps": b1_steps,
                        "frac_of_peak": b1_gbs / peak},
-            "prefix_restore": restore,
+            "prefix_restore": restore, "head_sharded_batch1": head_sharded,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": alg_per_launch * NCU_TRAFFIC_RATIO,
                          "kernel": "attention_mma_kernel<128> (fused append + paged decode attention)",
@@ -357,6 +362,78 @@ def run_ours(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+class _Ptr:
+    """Lets a torch tensor stand where the ABI face expects a device buffer."""
+
+    def __init__(self, tensor):
+        self.tensor = tensor
+        self.ptr = tensor.data_ptr()
+
+
+def head_sharded_leg(sg, st, torch, dist, world, rank, stream):
+    """One long sequence (batch 1) split by KV-head group over the ranks: every rank appends and
+    attends over its heads' pages, then ONE all-gather of attention outputs per layer (NCCL)."""
+    from saragossa_b200 import sharding
+    sh = sharding.head_shard(Q_HEADS, KV_HEADS, world, rank)
+    steps = 8
+    kv_loc, q_loc = sh.kv_heads * HEAD_DIM, sh.q_heads * HEAD_DIM
+    capacity = ((CTX + steps + 8 + 15) // 16) * 16
+    pool = st.pool(LAYERS, sh.kv_heads, HEAD_DIM, sg.KV_BF16, capacity // 16, 1, capacity)
+    pool.shuffle_free_list(3)
+    seq = pool.sequence(capacity)
+    kvs = [seq.layer(layer, sh.q_heads) for layer in range(LAYERS)]
+    chunk = 8192
+    dk, dv = st.alloc(chunk * kv_loc * 4), st.alloc(chunk * kv_loc * 4)
+    for layer in range(LAYERS):
+        for c in range(0, CTX, chunk):
+            n = min(chunk, CTX - c)
+            st.fill_normal(dk, n * kv_loc, 7, (layer * world + rank) * 2, c * kv_loc)
+            st.fill_normal(dv, n * kv_loc, 7, (layer * world + rank) * 2 + 1, c * kv_loc)
+            kvs[layer].encode_append_rows(dk, dv, n)
+    st.sync()
+    dk.free()
+    dv.free()
+    batches = [sg.Batch(st, [kv]) for kv in kvs]
+    dev = torch.device("cuda", torch.cuda.current_device())
+    k = torch.randn(LAYERS, kv_loc, device=dev)
+    v = torch.randn(LAYERS, kv_loc, device=dev)
+    q = torch.randn(LAYERS, q_loc, device=dev)
+    out_loc = torch.zeros(LAYERS, q_loc, device=dev)
+    out_full = torch.zeros(LAYERS, world * q_loc, device=dev)
+    torch.cuda.synchronize()
+
+    def one_step():
+        for layer in range(LAYERS):
+            batches[layer].enqueue_step(_Ptr(k[layer]), _Ptr(v[layer]), _Ptr(q[layer]), _Ptr(out_loc[layer]),
+                                        stream=stream.cuda_stream)
+            dist.all_gather_into_tensor(out_full[layer], out_loc[layer])
+
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            one_step()
+        stream.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            one_step()
+        e1.record(stream)
+        stream.synchronize()
+    ms = e0.elapsed_time(e1)
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    finite = bool(torch.isfinite(out_full).all().item())
+    for b in batches:
+        b.close()
+    seq.close()
+    pool.close()
+    total_bytes = sum(algorithmic_bytes(CTX + 2 + i + 1) for i in range(steps)) * LAYERS
+    return {"us_per_layer": ms * 1e3 / (steps * LAYERS), "hbm_gbs_aggregate": total_bytes / (ms * 1e-3) / 1e9,
+            "ranks": world, "kv_heads_per_rank": sh.kv_heads, "steps": steps, "outputs_finite": finite,
+            "exchange": f"one NCCL all-gather of {world * q_loc * 4} bytes of attention output per layer"}
 
 
 def prefix_restore_gbs(sg, st, torch, stream):
