@@ -1,0 +1,162 @@
+// Pieces shared by the paged tensor-core attention kernels (bf16 and u8 pages): the
+// mbarrier / bulk-copy (TMA) primitives with bounded waits, the warp-level matrix
+// instructions, and the block-cooperative merge of split-K partials.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "kernels.h"
+
+namespace sgk {
+
+constexpr int MMA_CONSUMERS = 4;                       // consumer warps
+constexpr int MMA_THREADS = (MMA_CONSUMERS + 1) * 32;  // + one producer warp
+constexpr int MMA_MAX_STAGES = 32;
+constexpr int MERGE_MAX = 12;  // partials merged at once (bound of group size and of group count)
+constexpr uint32_t WAIT_SPINS = 1u << 22;        // bound of every mbarrier wait
+constexpr uint32_t WAIT_SPINS_ABORTED = 1u << 10;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait. On expiry: sets the block's abort flag and the device status
+// word and returns false; the caller skips the work of that stage but keeps
+// walking its stages, so copies still in flight are waited for (with the short
+// bound) before the block exits.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int32_t* status) {
+  uint32_t limit = *abort_flag ? WAIT_SPINS_ABORTED : WAIT_SPINS;
+  for (uint32_t i = 0; i < limit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+  }
+  *abort_flag = 1;
+  atomicExch(status, DEV_ERR_WAIT_TIMEOUT);
+  return false;
+}
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr)
+               : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                                  uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr)
+               : "memory");
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+#ifdef SGK_TRACE
+#define SGK_TP(slot)                                                                               \
+  do {                                                                                             \
+    if (a.trace && (threadIdx.x & 31) == 0)                                                        \
+      a.trace[((size_t(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + (slot)] = clock64(); \
+  } while (0)
+#else
+#define SGK_TP(slot) do {} while (0)
+#endif
+
+
+// Block-cooperative merge of `count` (<= MERGE_MAX) partials (rows first..first+count
+// of a [q head][stride][HD] array) for the gqa heads starting at qh0. A thread owns
+// cells of four dims; per pass it handles two cells and issues every load it needs
+// (the {max, sum} pairs of the cell's head and the partial values) before the first
+// use, so a pass costs one L2 round trip and no block barrier. final != 0: writes the
+// normalised output; else writes one un-normalised partial (row dst_row of dst).
+template <int HD>
+__device__ __forceinline__ void merge_block(const Partials& src, int stride, int first, int count, int gqa,
+                                            int64_t qh0, bool final, float* out, const Partials& dst,
+                                            int dst_stride, int dst_row, int tid) {
+  constexpr int CELLS = 2;
+  const int total = gqa * (HD / 4);
+  for (int base = 0; base < total; base += CELLS * MMA_THREADS) {
+    float2 ml[CELLS][MERGE_MAX];
+    float4 v[CELLS][MERGE_MAX];
+    int cell[CELLS];
+#pragma unroll
+    for (int c = 0; c < CELLS; ++c) {
+      cell[c] = base + c * MMA_THREADS + tid;
+      if (cell[c] < total) {
+        const int h = cell[c] / (HD / 4), d = (cell[c] % (HD / 4)) * 4;
+        const float* pm = src.ml + ((qh0 + h) * stride + first) * 2;
+        const float* po = src.o + ((qh0 + h) * stride + first) * HD + d;
+#pragma unroll
+        for (int p = 0; p < MERGE_MAX; ++p)
+          if (p < count) {
+            ml[c][p] = __ldcg(reinterpret_cast<const float2*>(pm + 2 * p));
+            v[c][p] = __ldcg(reinterpret_cast<const float4*>(po + int64_t(p) * HD));
+          }
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < CELLS; ++c) {
+      if (cell[c] >= total) continue;
+      const int h = cell[c] / (HD / 4), d = (cell[c] % (HD / 4)) * 4;
+      float m = -1.0e30f;
+#pragma unroll
+      for (int p = 0; p < MERGE_MAX; ++p)
+        if (p < count) m = fmaxf(m, ml[c][p].x);
+      float l = 0.0f;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int p = 0; p < MERGE_MAX; ++p)
+        if (p < count) {
+          const float w = exp2f(ml[c][p].x - m);
+          l += ml[c][p].y * w;
+          acc.x += v[c][p].x * w;
+          acc.y += v[c][p].y * w;
+          acc.z += v[c][p].z * w;
+          acc.w += v[c][p].w * w;
+        }
+      if (final) {
+        const float inv = 1.0f / l;
+        *reinterpret_cast<float4*>(out + (qh0 + h) * HD + d) =
+            make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+      } else {
+        *reinterpret_cast<float4*>(dst.o + ((qh0 + h) * dst_stride + dst_row) * HD + d) = acc;
+        if (d == 0) *reinterpret_cast<float2*>(dst.ml + ((qh0 + h) * dst_stride + dst_row) * 2) = make_float2(m, l);
+      }
+    }
+  }
+}
+
+}  // namespace sgk
