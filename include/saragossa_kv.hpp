@@ -1,0 +1,274 @@
+// saragossa_kv.hpp — C++ host face of libsgk, named after the reference's Rust surface.
+//
+// The reference's host language is Rust; where no Rust toolchain exists this header is the
+// host layer above the C ABI (sgk.h): same type and method names, same argument meaning,
+// same error behaviour as the crate's resident-cache API, so a test written against it reads
+// like the reference's own tests. Every fallible method returns Result<T>, a value or an
+// InferError whose kind is the reference's variant (src/error.rs:12-75); nothing throws.
+// The types are move-only: a resident KV state belongs to one decode and is never cloned
+// (src/decode_resident.rs:21-27).
+#pragma once
+#include <cctype>
+#include <cstdint>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "sgk.h"
+
+namespace saragossa {
+
+struct InferError {
+  enum Kind { None = 0, Dimension = 1, Config = 2, Metal = 3, MemoryGuard = 4, Shape = 5, Timeout = 6 };
+  Kind kind = None;
+  std::string message;
+};
+
+template <class T>
+struct Result {
+  bool ok = false;
+  T value{};
+  InferError error;
+  static Result Ok(T v) {
+    Result r;
+    r.ok = true;
+    r.value = std::move(v);
+    return r;
+  }
+  static Result Err(int32_t code) {
+    Result r;
+    r.error.kind = static_cast<InferError::Kind>(code);
+    r.error.message = sgk_last_error();
+    return r;
+  }
+  bool is_err() const { return !ok; }
+};
+struct Unit {};
+
+enum class GpuElement : int32_t { F32 = SGK_KV_F32, Bf16 = SGK_KV_BF16, U8G32 = SGK_KV_U8G32 };
+
+// KV dtype policy of the reference (src/decode_resident/utils.rs:202-228): an explicit
+// RETI_RUST_KV_BF16 (1/true/on, 0/false/off) wins; otherwise bf16 when sampling, f32 greedy.
+inline bool kv_bf16_for(bool sampled) {
+  const char* e = std::getenv("RETI_RUST_KV_BF16");
+  if (e != nullptr) {
+    std::string v(e);
+    size_t a = v.find_first_not_of(" \t"), b = v.find_last_not_of(" \t");
+    v = a == std::string::npos ? "" : v.substr(a, b - a + 1);
+    for (auto& c : v) c = static_cast<char>(std::tolower(c));
+    if (v == "1" || v == "true" || v == "on") return true;
+    if (v == "0" || v == "false" || v == "off") return false;
+  }
+  return sampled;
+}
+
+// FullAttentionMetalState (src/decode_resident/attention.rs:446-1038).
+class FullAttentionState {
+ public:
+  FullAttentionState() = default;
+  explicit FullAttentionState(sgk_kv* h) : h_(h) {}
+  FullAttentionState(FullAttentionState&& o) noexcept : h_(o.h_) { o.h_ = nullptr; }
+  FullAttentionState& operator=(FullAttentionState&& o) noexcept {
+    if (this != &o) {
+      reset();
+      h_ = o.h_;
+      o.h_ = nullptr;
+    }
+    return *this;
+  }
+  FullAttentionState(const FullAttentionState&) = delete;
+  FullAttentionState& operator=(const FullAttentionState&) = delete;
+  ~FullAttentionState() { reset(); }
+
+  size_t kv_dim() const { return static_cast<size_t>(sgk_kv_kv_dim(h_)); }
+  size_t len() const { return static_cast<size_t>(sgk_kv_len(h_)); }
+  size_t capacity() const { return static_cast<size_t>(sgk_kv_capacity(h_)); }
+  size_t q_heads() const { return static_cast<size_t>(sgk_kv_q_heads(h_)); }
+  size_t kv_heads() const { return static_cast<size_t>(sgk_kv_kv_heads(h_)); }
+  size_t head_dim() const { return static_cast<size_t>(sgk_kv_head_dim(h_)); }
+  GpuElement element() const { return static_cast<GpuElement>(sgk_kv_dtype(h_)); }
+  size_t byte_len() const { return static_cast<size_t>(sgk_kv_byte_len(h_)); }
+
+  Result<Unit> truncate(size_t len) { return unit(sgk_kv_truncate(h_, static_cast<int64_t>(len))); }
+  Result<Unit> seed(const std::vector<float>& keys_rows, const std::vector<float>& values_rows, size_t n_rows) {
+    return unit(sgk_kv_seed_f32(h_, keys_rows.data(), keys_rows.size(), values_rows.data(), values_rows.size(),
+                                static_cast<int64_t>(n_rows)));
+  }
+  Result<Unit> append_row(const std::vector<float>& key, const std::vector<float>& value) {
+    return unit(sgk_kv_append_row_f32(h_, key.data(), key.size(), value.data(), value.size()));
+  }
+  Result<std::vector<float>> attention_decode(const std::vector<float>& q) { return attention_decode_windowed(q, 0); }
+  Result<std::vector<float>> attention_decode_windowed(const std::vector<float>& q, size_t window_start) {
+    std::vector<float> out(q_heads() * head_dim());
+    int32_t rc = sgk_kv_attention_decode(h_, q.data(), q.size(), static_cast<int64_t>(window_start), 0.0f, out.data());
+    if (rc != SGK_OK) return Result<std::vector<float>>::Err(rc);
+    return Result<std::vector<float>>::Ok(std::move(out));
+  }
+  // encode_* only enqueue (stream = the "encoder"); d_* are device pointers.
+  Result<Unit> encode_append_kv(void* stream, const float* d_k, const float* d_v) {
+    return unit(sgk_kv_enqueue_append(h_, stream, d_k, d_v));
+  }
+  Result<Unit> encode_attention_decode_windowed(void* stream, const float* d_q, float* d_out, size_t window_start) {
+    return unit(sgk_kv_enqueue_attention(h_, stream, d_q, d_out, static_cast<int64_t>(window_start), 0.0f));
+  }
+  // kv.keys() / kv.values() read-back of the valid rows, decoded to f32.
+  Result<std::vector<float>> keys() { return rows(true); }
+  Result<std::vector<float>> values() { return rows(false); }
+  // raw bf16 bit patterns of the valid rows (bf16 states only)
+  Result<std::vector<uint16_t>> keys_bf16_bits() {
+    std::vector<uint16_t> k(len() * kv_dim()), v(len() * kv_dim());
+    int32_t rc = sgk_kv_gather_rows(h_, 0, static_cast<int64_t>(len()), k.data(), v.data());
+    if (rc != SGK_OK) return Result<std::vector<uint16_t>>::Err(rc);
+    return Result<std::vector<uint16_t>>::Ok(std::move(k));
+  }
+  sgk_kv* handle() const { return h_; }
+
+ private:
+  static Result<Unit> unit(int32_t rc) { return rc == SGK_OK ? Result<Unit>::Ok(Unit{}) : Result<Unit>::Err(rc); }
+  Result<std::vector<float>> rows(bool want_keys) {
+    std::vector<float> k(len() * kv_dim()), v(len() * kv_dim());
+    int32_t rc = sgk_kv_gather_rows_f32(h_, 0, static_cast<int64_t>(len()), k.data(), v.data());
+    if (rc != SGK_OK) return Result<std::vector<float>>::Err(rc);
+    return Result<std::vector<float>>::Ok(std::move(want_keys ? k : v));
+  }
+  void reset() {
+    if (h_) sgk_kv_destroy(h_);
+    h_ = nullptr;
+  }
+  sgk_kv* h_ = nullptr;
+};
+
+// DecodeResidentState (src/decode_resident/arena.rs:247-349).
+class DecodeResidentState {
+ public:
+  DecodeResidentState() = default;
+  DecodeResidentState(DecodeResidentState&& o) noexcept : h_(o.h_) { o.h_ = nullptr; }
+  DecodeResidentState& operator=(DecodeResidentState&& o) noexcept {
+    if (this != &o) {
+      if (h_) sgk_state_destroy(h_);
+      h_ = o.h_;
+      o.h_ = nullptr;
+    }
+    return *this;
+  }
+  DecodeResidentState(const DecodeResidentState&) = delete;
+  DecodeResidentState& operator=(const DecodeResidentState&) = delete;
+  ~DecodeResidentState() {
+    if (h_) sgk_state_destroy(h_);
+  }
+  static Result<DecodeResidentState> create(int device = 0) {
+    sgk_state* h = nullptr;
+    int32_t rc = sgk_state_create(device, &h);
+    if (rc != SGK_OK) return Result<DecodeResidentState>::Err(rc);
+    DecodeResidentState s;
+    s.h_ = h;
+    return Result<DecodeResidentState>::Ok(std::move(s));
+  }
+  // state.full_attention(capacity, q_heads, kv_heads, head_dim, sampled)
+  Result<FullAttentionState> full_attention(size_t capacity, size_t q_heads, size_t kv_heads, size_t head_dim,
+                                            bool sampled) {
+    return full_attention_with_element(capacity, q_heads, kv_heads, head_dim,
+                                       kv_bf16_for(sampled) ? GpuElement::Bf16 : GpuElement::F32);
+  }
+  Result<FullAttentionState> full_attention_with_element(size_t capacity, size_t q_heads, size_t kv_heads,
+                                                         size_t head_dim, GpuElement element) {
+    sgk_kv* kv = nullptr;
+    int32_t rc = sgk_kv_create(h_, static_cast<int64_t>(capacity), static_cast<int32_t>(q_heads),
+                               static_cast<int32_t>(kv_heads), static_cast<int32_t>(head_dim),
+                               static_cast<int32_t>(element), SGK_PAGE_TOKENS, &kv);
+    if (rc != SGK_OK) return Result<FullAttentionState>::Err(rc);
+    return Result<FullAttentionState>::Ok(FullAttentionState(kv));
+  }
+  Result<std::vector<float>> rms_norm_rope_decode(const std::vector<float>& x, const std::vector<float>& weight,
+                                                  size_t heads, size_t head_dim, size_t rope_dims, size_t position,
+                                                  float eps, float theta) {
+    sgk_rope rope{static_cast<int32_t>(rope_dims), static_cast<int32_t>(rope_dims), theta, 1.0f, eps, 0};
+    std::vector<float> out(heads * head_dim);
+    int32_t rc = sgk_rms_norm_rope_decode(h_, x.data(), weight.data(), static_cast<int32_t>(heads),
+                                          static_cast<int32_t>(head_dim), &rope, static_cast<int64_t>(position),
+                                          out.data());
+    if (rc != SGK_OK) return Result<std::vector<float>>::Err(rc);
+    return Result<std::vector<float>>::Ok(std::move(out));
+  }
+  sgk_state* handle() const { return h_; }
+
+ private:
+  sgk_state* h_ = nullptr;
+};
+
+// BlockHash (src/serve/cache.rs:11-47).
+struct BlockHash {
+  uint8_t bytes[32];
+  static BlockHash root() {
+    BlockHash h;
+    sgk_hash_root(h.bytes);
+    return h;
+  }
+  static BlockHash for_session(const char* session_key) {  // nullptr = None
+    BlockHash h;
+    sgk_hash_for_session(session_key, session_key ? std::strlen(session_key) : 0, session_key != nullptr, h.bytes);
+    return h;
+  }
+  BlockHash chain(const std::vector<uint64_t>& tokens) const {
+    BlockHash h;
+    sgk_hash_chain(bytes, tokens.data(), tokens.size(), h.bytes);
+    return h;
+  }
+  bool operator==(const BlockHash& o) const { return std::memcmp(bytes, o.bytes, 32) == 0; }
+  bool operator!=(const BlockHash& o) const { return !(*this == o); }
+};
+
+struct PrefixBlockHit {
+  size_t tokens = 0;
+  BlockHash hash{};
+  uint64_t entry = 0;
+};
+
+// BlockAwarePrefixCache (src/serve/cache.rs:74-219), bookkeeping form (no pool).
+class BlockAwarePrefixCache {
+ public:
+  BlockAwarePrefixCache(size_t block_tokens, size_t capacity) : BlockAwarePrefixCache(block_tokens, capacity, capacity) {}
+  BlockAwarePrefixCache(size_t block_tokens, size_t capacity, size_t blocks_per_session) {
+    sgk_prefix_create(nullptr, static_cast<int64_t>(block_tokens), static_cast<int64_t>(capacity),
+                      static_cast<int64_t>(blocks_per_session), 0, &h_);
+  }
+  BlockAwarePrefixCache(const BlockAwarePrefixCache&) = delete;
+  BlockAwarePrefixCache& operator=(const BlockAwarePrefixCache&) = delete;
+  ~BlockAwarePrefixCache() { sgk_prefix_destroy(h_); }
+  size_t block_tokens() const { return static_cast<size_t>(sgk_prefix_block_tokens(h_)); }
+  // Some(hit) / None as {found, hit}
+  std::pair<bool, PrefixBlockHit> match_prefix(const BlockHash& root, const std::vector<uint64_t>& tokens) {
+    PrefixBlockHit hit;
+    int64_t n = 0;
+    sgk_prefix_match(h_, root.bytes, tokens.data(), tokens.size(), &n, hit.hash.bytes, &hit.entry);
+    hit.tokens = static_cast<size_t>(n);
+    return {hit.entry != 0, hit};
+  }
+  bool insert(const BlockHash& session, const BlockHash& hash, size_t tokens) {
+    int32_t inserted = 0;
+    sgk_prefix_insert(h_, session.bytes, hash.bytes, static_cast<int64_t>(tokens), nullptr, nullptr, nullptr, &inserted);
+    return inserted != 0;
+  }
+  bool evict_lru_block() {
+    int32_t ev = 0;
+    sgk_prefix_evict_lru(h_, &ev, nullptr);
+    return ev != 0;
+  }
+  size_t estimated_bytes() const { return static_cast<size_t>(sgk_prefix_bytes(h_)); }
+  size_t session_block_count(const BlockHash& s) const { return static_cast<size_t>(sgk_prefix_session_count(h_, s.bytes)); }
+  std::vector<BlockHash> entry_hashes() const {  // front (most recent) to rear
+    int64_t n = sgk_prefix_len(h_);
+    std::vector<uint8_t> raw(static_cast<size_t>(n) * 32);
+    sgk_prefix_dump(h_, 0, n, nullptr, raw.data(), nullptr);
+    std::vector<BlockHash> out(static_cast<size_t>(n));
+    for (int64_t i = 0; i < n; ++i) std::memcpy(out[static_cast<size_t>(i)].bytes, raw.data() + 32 * i, 32);
+    return out;
+  }
+
+ private:
+  sgk_prefix* h_ = nullptr;
+};
+
+}  // namespace saragossa

@@ -22,6 +22,7 @@ SOURCES = [
     "kernels_append.cu",
     "kernels_attn_generic.cu",
     "kernels_attn_mma.cu",
+    "kernels_attn_u8.cu",
     "kernels_copy.cu",
     "noalloc.cu",
 ]

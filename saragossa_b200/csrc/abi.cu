@@ -49,6 +49,7 @@ int32_t sgk_state_create(int32_t device, sgk_state** out) {
   SGK_CUDA(cudaMalloc(&st->d_status, sizeof(int32_t)));
   SGK_CUDA(cudaMemset(st->d_status, 0, sizeof(int32_t)));
   SGK_CUDA(attention_mma_configure());
+  SGK_CUDA(attention_u8_configure());
   *out = st.release();
   return SGK_OK;
 }
@@ -130,6 +131,10 @@ int32_t sgk_pool_create(sgk_state* st, int32_t layers, int32_t kv_heads, int32_t
     SGK_CUDA(cudaMemset(p->d_tables, 0xff, tbytes));
     SGK_CUDA(cudaMalloc(&p->d_lens, size_t(max_seqs) * layers * sizeof(int32_t)));
     SGK_CUDA(cudaMemset(p->d_lens, 0, size_t(max_seqs) * layers * sizeof(int32_t)));
+    if (dtype == SGK_KV_U8G32) {
+      SGK_CUDA(cudaMalloc(&p->d_scale_max, sizeof(uint32_t)));
+      SGK_CUDA(cudaMemset(p->d_scale_max, 0, sizeof(uint32_t)));
+    }
   }
   *out = p.release();
   return SGK_OK;
@@ -144,6 +149,7 @@ void sgk_pool_destroy(sgk_pool* p) {
   if (p->d_base) cudaFree(p->d_base);
   if (p->d_tables) cudaFree(p->d_tables);
   if (p->d_lens) cudaFree(p->d_lens);
+  if (p->d_scale_max) cudaFree(p->d_scale_max);
   if (p->d_page_list) cudaFree(p->d_page_list);
   delete p;
 }

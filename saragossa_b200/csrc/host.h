@@ -57,6 +57,7 @@ struct Pool {
   uint8_t* d_base = nullptr;
   int32_t* d_tables = nullptr;
   int32_t* d_lens = nullptr;
+  uint32_t* d_scale_max = nullptr;  // u8 pools only
   int32_t* d_page_list = nullptr;  // staging for copy / scrub page lists
   int page_list_cap = 0;
   std::vector<int32_t> free_list;  // taken from the back

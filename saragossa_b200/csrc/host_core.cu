@@ -40,6 +40,7 @@ PoolView Pool::view() const {
   v.tile_bytes = tile_b;
   v.tables = d_tables;
   v.lens = d_lens;
+  v.scale_max = d_scale_max;
   v.table_stride = table_stride;
   v.layers = layers;
   v.kv_heads = kv_heads;
@@ -277,10 +278,13 @@ int create_batch(State* st, Kv** kvs, int n, Batch** out) {
 
 int Batch::choose_kernel() const {
   int gqa = q_heads / pool->kv_heads;
-  bool can_mma = attention_mma_supported(pool->dtype, pool->head_dim, gqa);
-  if (kernel_override == 2 && !can_mma) return -1;
+  // 1 = generic CUDA-core kernel, 2 = tensor-core kernel over bf16 pages, 3 = over u8 pages
+  int tensor = attention_mma_supported(pool->dtype, pool->head_dim, gqa)  ? 2
+               : attention_u8_supported(pool->dtype, pool->head_dim, gqa) ? 3
+                                                                          : 0;
+  if (kernel_override == 2 && tensor == 0) return -1;
   if (kernel_override == 1) return 1;
-  return can_mma ? 2 : 1;
+  return tensor ? tensor : 1;
 }
 
 int Batch::choose_splits(int kernel, int64_t max_rows) const {
@@ -290,11 +294,11 @@ int Batch::choose_splits(int kernel, int64_t max_rows) const {
     // for the tensor-core kernel, eight for the generic one). Take the split count
     // with the best whole-wave fill (first one above 98.5%), while every split
     // keeps a few pages of work.
-    const int heads = kernel == 2 ? pool->kv_heads : q_heads;
-    const int64_t slots = int64_t(st->sm_count) * (kernel == 2 ? 2 : 8);
+    const int heads = kernel >= 2 ? pool->kv_heads : q_heads;
+    const int64_t slots = int64_t(st->sm_count) * (kernel >= 2 ? 2 : 8);
     const int64_t units = int64_t(heads) * n();
     const int64_t pages = (max_rows + PAGE_TOKENS - 1) / PAGE_TOKENS;
-    const int min_pages = kernel == 2 ? 8 : 2;
+    const int min_pages = kernel >= 2 ? 8 : 2;
     int64_t cap = std::max<int64_t>(1, pages / min_pages);
     cap = std::min<int64_t>(cap, max_splits);
     int best = 1;
@@ -383,7 +387,7 @@ int Batch::enqueue_attention(cudaStream_t stream, const float* d_q, float* d_out
       return fail(SGK_ERR_DIMENSION, "attention window reaches rows released by the sliding window");
     max_rows = std::max(max_rows, len_after - ws);
   }
-  if (fused && kernel != 2) {
+  if (fused && kernel < 2) {
     SGK_TRY(enqueue_append(stream, d_k_new, d_v_new, 1, nullptr, nullptr));
   } else if (fused) {
     for (Kv* kv : kvs) {
@@ -421,7 +425,7 @@ int Batch::enqueue_attention(cudaStream_t stream, const float* d_q, float* d_out
   a.seq_counters = d_counters + size_t(n()) * std::max(q_heads, pool->kv_heads);
   a.status = st->d_status;
   a.num_pages = pool->num_pages;
-  if (kernel == 2) {
+  if (kernel >= 2) {
     a.k_new = d_k_new;
     a.v_new = d_v_new;
     int64_t pages = (max_rows + PAGE_TOKENS - 1) / PAGE_TOKENS + 1;
@@ -433,11 +437,16 @@ int Batch::enqueue_attention(cudaStream_t stream, const float* d_q, float* d_out
       const char* e = std::getenv("SGK_ATTN_STAGES");
       return e ? std::atoi(e) : 0;
     }();
+    if (kernel == 3) a.n_stages = attention_u8_max_stages(pool->head_dim);
     if (env_stages >= 4 && env_stages <= a.n_stages) a.n_stages = env_stages / 4 * 4;
 #ifdef SGK_TRACE
     a.trace = g_trace;
 #endif
-    SGK_CUDA(launch_attention_mma(a, n(), stream));
+    if (kernel == 3) {
+      SGK_CUDA(launch_attention_u8(a, n(), stream));
+    } else {
+      SGK_CUDA(launch_attention_mma(a, n(), stream));
+    }
     if (fused)
       for (Kv* kv : kvs) kv->seq->len[layer] += 1;
   } else {

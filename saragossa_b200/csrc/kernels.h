@@ -81,6 +81,11 @@ bool attention_mma_supported(int dtype, int head_dim, int gqa);
 cudaError_t launch_attention_mma(const AttnArgs& a, int n_seq, cudaStream_t stream);
 cudaError_t attention_mma_configure();
 int attention_mma_max_stages(int head_dim);
+// Tensor-core paged kernel for u8 group-32 pages: head_dim 128 or 256, q_heads/kv_heads <= 8.
+bool attention_u8_supported(int dtype, int head_dim, int gqa);
+cudaError_t launch_attention_u8(const AttnArgs& a, int n_seq, cudaStream_t stream);
+cudaError_t attention_u8_configure();
+int attention_u8_max_stages(int head_dim);
 
 // Gather rows [row0, row0+n) of one layer into contiguous [n, kv_dim] arrays.
 // mode 0: storage type (f32 / bf16 bits), 1: decoded f32, 2: u8 codes + scale + bias.

@@ -63,7 +63,8 @@ __device__ __forceinline__ uint32_t quantize_group_warp(float x, uint32_t* meta_
 }
 
 // Writes one head row (hd f32 values in shared memory) into its tile.
-__device__ void store_head_row(uint8_t* tile, int dtype, int hd, int is_v, int row, const float* xs) {
+__device__ void store_head_row(uint8_t* tile, int dtype, int hd, int is_v, int row, const float* xs,
+                               uint32_t* scale_max) {
   int tid = threadIdx.x;
   if (dtype == KV_F32) {
     float* dst = reinterpret_cast<float*>(tile) + row * hd;
@@ -91,7 +92,13 @@ __device__ void store_head_row(uint8_t* tile, int dtype, int hd, int is_v, int r
       uint32_t code = quantize_group_warp(xs[dim], &meta);
       int idx = is_v ? u8_v_code_index(row, dim) : u8_k_code_index(row, dim, hd);
       tile[idx] = static_cast<uint8_t>(code);
-      if (lane == 0) *reinterpret_cast<uint32_t*>(tile + u8_meta_offset(row, g, hd)) = meta;
+      if (lane == 0) {
+        *reinterpret_cast<uint32_t*>(tile + u8_meta_offset(row, g, hd)) = meta;
+        // largest scale of the pool (positive floats order like their bit patterns)
+        const uint32_t scale_f32_bits = (meta & 0xffffu) << 16;
+        if (scale_max != nullptr && scale_f32_bits > *reinterpret_cast<volatile uint32_t*>(scale_max))
+          atomicMax(scale_max, scale_f32_bits);
+      }
     }
   }
 }
@@ -133,8 +140,8 @@ __global__ void __launch_bounds__(128) append_rows_kernel(AppendArgs a) {
     const int rin = static_cast<int>(row % PAGE_TOKENS);
     uint8_t* ktile = a.pool.base + tile_offset(a.pool, page, a.layer, head, 0);
     uint8_t* vtile = a.pool.base + tile_offset(a.pool, page, a.layer, head, 1);
-    store_head_row(ktile, a.pool.dtype, hd, 0, rin, ks);
-    store_head_row(vtile, a.pool.dtype, hd, 1, rin, vs);
+    store_head_row(ktile, a.pool.dtype, hd, 0, rin, ks, a.pool.scale_max);
+    store_head_row(vtile, a.pool.dtype, hd, 1, rin, vs, a.pool.scale_max);
   } else if (tid == 0) {
     atomicExch(a.status, DEV_ERR_BAD_PAGE);
   }

@@ -385,83 +385,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
   }
   __syncthreads();
 
-  if (tid == 0) SGK_TP(4);
-  // ---- merge the consumer warps; write the partial or the final output ----
-  const int64_t qh0 = int64_t(seq) * a.q_heads + int64_t(kvh) * gqa;
-  for (int idx = tid; idx < gqa * HD; idx += MMA_THREADS) {
-    int h = idx / HD, d = idx % HD;
-    float mb = -1.0e30f;
-#pragma unroll
-    for (int w = 0; w < MMA_CONSUMERS; ++w) mb = fmaxf(mb, ml_s[(w * 8 + h) * 2]);
-    float o = 0.0f, lb = 0.0f;
-#pragma unroll
-    for (int w = 0; w < MMA_CONSUMERS; ++w) {
-      float wg = exp2f(ml_s[(w * 8 + h) * 2] - mb);
-      o += o_s[(w * 8 + h) * S::OPAD + d] * wg;
-      lb += ml_s[(w * 8 + h) * 2 + 1] * wg;
-    }
-    if (a.splits == 1) {
-      a.out[(qh0 + h) * HD + d] = o / lb;
-    } else {
-      a.part.o[((qh0 + h) * a.splits + split) * HD + d] = o;
-      if (d == 0) {
-        float* pml = a.part.ml + ((qh0 + h) * a.splits + split) * 2;
-        pml[0] = mb;
-        pml[1] = lb;
-      }
-    }
-  }
-  if (a.splits > 1 || do_append) {
-    const int group = split / a.group_size;
-    const int group_first = group * a.group_size;
-    const int group_count = min(a.group_size, a.splits - group_first);
-    int32_t* group_counter = a.group_counters + (int64_t(seq) * a.pool.kv_heads + kvh) * a.max_groups + group;
-    int32_t* head_counter = a.head_counters + int64_t(seq) * a.pool.kv_heads + kvh;
-    __syncthreads();
-    if (tid == 0) {
-      __threadfence();
-      if (a.splits > 1) {
-        int old = atomicAdd(group_counter, 1);
-        flags[1] = (old == group_count - 1);
-        if (flags[1]) *group_counter = 0;
-      }
-      if (do_append) {
-        // the block that arrives last for the sequence moves the cursor
-        int total = a.splits * a.pool.kv_heads;
-        int old = atomicAdd(a.seq_counters + seq, 1);
-        if (old == total - 1) {
-          *len_ptr = static_cast<int32_t>(len);
-          a.seq_counters[seq] = 0;
-        }
-      }
-    }
-    __syncthreads();
-    if (tid == 0) SGK_TP(5);
-    if (a.splits > 1 && flags[1]) {
-      // this block completed its group: merge the group (or everything, if one group)
-      __threadfence();
-      const bool single = a.n_groups == 1;
-      merge_block<HD>(a.part, a.splits, group_first, group_count, gqa, qh0, single, a.out, a.part2,
-                      a.max_groups, group, tid);
-      if (tid == 0) SGK_TP(6);
-      if (!single) {
-        __syncthreads();
-        if (tid == 0) {
-          __threadfence();
-          int old = atomicAdd(head_counter, 1);
-          flags[1] = (old == a.n_groups - 1);
-          if (flags[1]) *head_counter = 0;
-        }
-        __syncthreads();
-        if (flags[1]) {
-          __threadfence();
-          merge_block<HD>(a.part2, a.max_groups, 0, a.n_groups, gqa, qh0, true, a.out, a.part2,
-                          a.max_groups, 0, tid);
-          if (tid == 0) SGK_TP(7);
-        }
-      }
-    }
-  }
+  finish_block<HD>(a, o_s, ml_s, S::OPAD, flags, seq, kvh, split, gqa, do_append, len_ptr, len, tid);
 }
 
 bool attention_mma_supported(int dtype, int head_dim, int gqa) {

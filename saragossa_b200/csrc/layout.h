@@ -12,7 +12,8 @@
 //   bf16 : [row][dim]; when head_dim % 64 == 0 the 16-byte chunks of a row are
 //          XOR-swizzled inside each 128-byte segment: chunk c -> c ^ (row & 7).
 //   u8   : K codes [row][dim] (one byte each) with 16-byte chunks swizzled by
-//          c ^ ((row & 1) << 2) inside each 128-byte segment; V codes are stored
+//          c ^ (row & 7) inside each 128-byte segment (head_dim % 128 == 0), so the
+//          eight rows a warp reads together fall into different banks; V codes are stored
 //          TRANSPOSED, [dim][16 row slots], row r in slot vslot(r); after the
 //          codes come the per-(row, group-of-32) pairs {scale bf16, bias bf16},
 //          [row][group], 4 bytes each.
@@ -51,6 +52,7 @@ struct PoolView {
   int64_t tile_bytes;
   const int32_t* tables;  // [max_seqs][table_stride] page ids
   int32_t* lens;          // [max_seqs][layers] rows held, per layer
+  uint32_t* scale_max;    // u8 pools: f32 bits of the largest group scale ever stored (else NULL)
   int32_t table_stride;
   int32_t layers;
   int32_t kv_heads;
@@ -75,7 +77,7 @@ SGK_HD int bf16_elem_index(int row, int dim, int hd) {
 // Byte index of K code (row, dim) inside a u8 tile.
 SGK_HD int u8_k_code_index(int row, int dim, int hd) {
   int chunk = dim >> 4;
-  if (hd % 128 == 0) chunk ^= (row & 1) << 2;
+  if (hd % 128 == 0) chunk = (chunk & ~7) | ((chunk ^ row) & 7);
   return row * hd + chunk * 16 + (dim & 15);
 }
 // Slot of row r inside the 16 bytes a V dim holds: threads of a quad read the

@@ -390,28 +390,39 @@ def test_paged_decode_normal_inputs_bf16(state, shape):
         kv.close()
 
 
-def test_u8_paged_decode_matches_oracle(state):
-    q_heads, kv_heads, hd = 16, 2, 256
-    n, kv_dim = 1500, kv_heads * hd
+@pytest.mark.parametrize("kernel", [1, 2])
+@pytest.mark.parametrize("shape,n", [((16, 2, 256), 1500), ((32, 4, 128), 4100), ((8, 4, 256), 777),
+                                     ((16, 2, 256), 20000)])
+def test_u8_paged_decode_matches_oracle(state, shape, n, kernel):
+    """u8 group-32 pages (config 3 shape among them): attention over the dequantised rows
+    q*scale+bias (src/quantization.rs:173-179), generic kernel and tensor-core kernel."""
+    q_heads, kv_heads, hd = shape
+    kv_dim = kv_heads * hd
     k, v = _normal_kv(n, kv_dim, 0, 20), _normal_kv(n, kv_dim, 0, 21)
+    # a few rows with a much larger range: the group scales span three orders of magnitude
+    k[5] *= 40.0
+    v[n // 2] *= 300.0
     q = sgo.fill_normal8(q_heads * hd, 0, 22)
     ref = sgo.ResidentKv(n, q_heads, kv_heads, hd, sg.KV_U8G32)
     ref.seed(k, v, n)
-    _, want = ref.attention(q, threads=8)
     kv = state.full_attention(n, q_heads, kv_heads, hd, sg.KV_U8G32, shuffled_seed=9)
     kv.seed(k, v, n)
-    got = kv.attention_decode(q)
-    assert np.all(np.abs(got - want) <= 2e-2 * np.abs(want) + 1e-3)
+    kv.set_attention_kernel(kernel)
+    for ws in (0, 33):
+        _, want = ref.attention(q, window_start=ws, threads=8)
+        got = kv.attention_decode_windowed(q, ws)
+        assert np.all(np.abs(got - want) <= 2e-2 * np.abs(want) + 1e-3), (kernel, ws, np.abs(got - want).max())
     kv.close()
 
 
-def test_batched_step_is_per_sequence_identical(state):
+@pytest.mark.parametrize("dtype", [sg.KV_BF16, sg.KV_U8G32])
+def test_batched_step_is_per_sequence_identical(state, dtype):
     """A batch must not let one sequence's length, page layout or split count change another's
     result (the reference's multi-stream contract, src/decoder/lightbatch.rs:1-12)."""
     q_heads, kv_heads, hd, layers = 32, 4, 128, 2
     kv_dim, q_dim = kv_heads * hd, q_heads * hd
     lens = [700, 33, 2049, 16]
-    pool = state.pool(layers, kv_heads, hd, sg.KV_BF16, num_pages=400, max_seqs=8, max_seq_tokens=2304)
+    pool = state.pool(layers, kv_heads, hd, dtype, num_pages=400, max_seqs=8, max_seq_tokens=2304)
     pool.shuffle_free_list(5)
     seqs = [pool.sequence(n + 8) for n in lens]
     refs, kvs = [], [[], []]
@@ -421,7 +432,7 @@ def test_batched_step_is_per_sequence_identical(state):
             k, v = _normal_kv(n, kv_dim, 1, 100 * s + 2 * layer), _normal_kv(n, kv_dim, 1, 100 * s + 2 * layer + 1)
             kv.seed(k, v, n)
             kvs[layer].append(kv)
-            r = sgo.ResidentKv(n + 8, q_heads, kv_heads, hd, sg.KV_BF16)
+            r = sgo.ResidentKv(n + 8, q_heads, kv_heads, hd, dtype)
             r.seed(k, v, n)
             refs.append(r)
     batches = [sg.Batch(state, kvs[layer]) for layer in range(layers)]
