@@ -44,9 +44,13 @@ WORKLOAD = ("C2: Qwen3-30B-A3B-shaped KV path, 48 layers, 32Q/4KV heads, head_di
 NCU_TRAFFIC_RATIO = 1.0076
 
 
+KV_DTYPE = "bf16"           # or "u8": 32 codes + bf16 scale + bf16 bias per group = 1.125 B per element
+
+
 def algorithmic_bytes(rows_after_append: int) -> int:
-    """K and V rows of one sequence and layer read once, plus the appended row (bf16)."""
-    return rows_after_append * KV_DIM * 2 * 2 + KV_DIM * 2 * 2
+    """K and V rows of one sequence and layer read once, plus the appended row, in storage bytes."""
+    elem = 2.0 if KV_DTYPE == "bf16" else 1.125
+    return int((rows_after_append * KV_DIM * 2 + KV_DIM * 2) * elem)
 
 
 def measured_peak():
@@ -232,7 +236,8 @@ def run_ours(args):
     extra = W + K + e2e_steps + 2 + 2 * (3 + b1_steps) + 16
     capacity = ((CTX + extra + 15) // 16) * 16
     pages_per_seq = capacity // 16
-    pool = st.pool(LAYERS, KV_HEADS, HEAD_DIM, sg.KV_BF16, pages_per_seq * BATCH, BATCH, capacity)
+    dtype = sg.KV_BF16 if KV_DTYPE == "bf16" else sg.KV_U8G32
+    pool = st.pool(LAYERS, KV_HEADS, HEAD_DIM, dtype, pages_per_seq * BATCH, BATCH, capacity)
     pool.shuffle_free_list(0)
     t_seed = time.perf_counter()
     seqs, kvs = build_sequences(sg, st, pool, BATCH, CTX, capacity)
@@ -270,7 +275,9 @@ def run_ours(args):
             print(json.dumps({"metric": "decode_attn_append_hbm_gbs_32k", "value": value, "unit": "GB/s",
                               "n_gpus": world, "steps": K, "warmup": W, "us_per_layer": us_per_layer,
                               "gpu_launches": int(launches), "device_status": status,
-                              "config": {"workload": f"profiling subset: layers={LAYERS} batch={BATCH} ctx={CTX}"}}),
+                              "config": {"workload": f"other shape / subset: layers={LAYERS} batch={BATCH} ctx={CTX} "
+                                                      f"q{Q_HEADS}/kv{KV_HEADS}/hd{HEAD_DIM} {KV_DTYPE}"},
+                              "us_per_layer_per_seq": us_per_layer / BATCH}),
                   flush=True)
         if world > 1:
             dist.barrier()
@@ -335,7 +342,8 @@ def run_ours(args):
             "metric": "decode_attn_append_hbm_gbs_32k", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD if not args.reduced else f"REDUCED layers={LAYERS} batch={BATCH} ctx={CTX}",
+            "config": {"workload": WORKLOAD if not args.reduced else (f"OTHER layers={LAYERS} batch={BATCH} ctx={CTX} "
+                                                                                f"q{Q_HEADS}/kv{KV_HEADS}/hd{HEAD_DIM} {KV_DTYPE}"),
                        "sharding": "by sequence, no collective",
                        "l2": "inputs larger than L2 (24.6 GB of KV per GPU streamed per step)",
                        "timing": "CUDA events on the launching stream around K graph replays, max over ranks"},
@@ -503,7 +511,7 @@ def prefix_restore_gbs(sg, st, torch, stream):
 
 
 def main():
-    global LAYERS, BATCH, CTX
+    global LAYERS, BATCH, CTX, Q_HEADS, KV_HEADS, HEAD_DIM, KV_DIM, Q_DIM, KV_DTYPE
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
@@ -513,11 +521,18 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--ctx", type=int, default=CTX)
+    ap.add_argument("--q-heads", type=int, default=Q_HEADS)
+    ap.add_argument("--kv-heads", type=int, default=KV_HEADS)
+    ap.add_argument("--head-dim", type=int, default=HEAD_DIM)
+    ap.add_argument("--kv-dtype", default=KV_DTYPE, choices=["bf16", "u8"])
     ap.add_argument("--skip-extras", action="store_true",
                     help="only the device-resident timing (no e2e, batch-1, prefix-restore or CPU legs)")
     args = ap.parse_args()
-    reduced = (args.layers, args.batch, args.ctx) != (LAYERS, BATCH, CTX)
+    reduced = (args.layers, args.batch, args.ctx, args.q_heads, args.kv_heads, args.head_dim, args.kv_dtype) != (
+        LAYERS, BATCH, CTX, Q_HEADS, KV_HEADS, HEAD_DIM, KV_DTYPE)
     LAYERS, BATCH, CTX = args.layers, args.batch, args.ctx
+    Q_HEADS, KV_HEADS, HEAD_DIM, KV_DTYPE = args.q_heads, args.kv_heads, args.head_dim, args.kv_dtype
+    KV_DIM, Q_DIM = KV_HEADS * HEAD_DIM, Q_HEADS * HEAD_DIM
     args.reduced = reduced
     if args.impl == "reference":
         run_reference(args)

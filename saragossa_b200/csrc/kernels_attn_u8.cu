@@ -301,34 +301,52 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
       }
 
       if (ok) {
-        // ---- scores: one accumulator per group of 32 dims, scale applied in f32 ----
+        // ---- scores: one accumulator per group of 32 dims, scale applied in f32. The
+        //      tensor-core instructions have a long latency and issue in order, so products
+        //      that do not depend on each other are issued back to back: all groups for one
+        //      half of their dims and the hi part of Q, then the lo part, then the other half. ----
         float s[4] = {0.f, 0.f, 0.f, 0.f};
         const uint8_t* kmeta = ktile + S::CODES;
+        float acc[G][4];
 #pragma unroll
-        for (int grp = 0; grp < G; ++grp) {
-          float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int grp = 0; grp < G; ++grp) acc[grp][0] = acc[grp][1] = acc[grp][2] = acc[grp][3] = 0.0f;
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
+        for (int half = 0; half < 2; ++half) {
+          uint32_t af[G][4];
+#pragma unroll
+          for (int grp = 0; grp < G; ++grp) {
             const int ks = 2 * grp + half;                 // 16-byte chunk index = k-step
             const int phys = (ks & ~7) | ((ks ^ g) & 7);   // rows g and g+8 share the swizzle
             const uint32_t w0 = *reinterpret_cast<const uint32_t*>(ktile + g * HD + phys * 16 + 4 * t);
             const uint32_t w1 = *reinterpret_cast<const uint32_t*>(ktile + (g + 8) * HD + phys * 16 + 4 * t);
-            const uint2 qh = *reinterpret_cast<const uint2*>(qh_row + 32 * ks);
-            const uint2 ql = *reinterpret_cast<const uint2*>(ql_row + 32 * ks);
-            const uint32_t a0 = codes_lo(w0), a1 = codes_lo(w1), a2 = codes_hi(w0), a3 = codes_hi(w1);
-            mma_f16(acc, a0, a1, a2, a3, qh.x, qh.y);
-            mma_f16(acc, a0, a1, a2, a3, ql.x, ql.y);
+            af[grp][0] = codes_lo(w0);
+            af[grp][1] = codes_lo(w1);
+            af[grp][2] = codes_hi(w0);
+            af[grp][3] = codes_hi(w1);
           }
+#pragma unroll
+          for (int grp = 0; grp < G; ++grp) {
+            const uint2 qh = *reinterpret_cast<const uint2*>(qh_row + 32 * (2 * grp + half));
+            mma_f16(acc[grp], af[grp][0], af[grp][1], af[grp][2], af[grp][3], qh.x, qh.y);
+          }
+#pragma unroll
+          for (int grp = 0; grp < G; ++grp) {
+            const uint2 ql = *reinterpret_cast<const uint2*>(ql_row + 32 * (2 * grp + half));
+            mma_f16(acc[grp], af[grp][0], af[grp][1], af[grp][2], af[grp][3], ql.x, ql.y);
+          }
+        }
+#pragma unroll
+        for (int grp = 0; grp < G; ++grp) {
           const uint32_t mk0 = *reinterpret_cast<const uint32_t*>(kmeta + (g * G + grp) * 4);
           const uint32_t mk1 = *reinterpret_cast<const uint32_t*>(kmeta + ((g + 8) * G + grp) * 4);
           const float sc0 = __uint_as_float(mk0 << 16), bi0 = __uint_as_float(mk0 & 0xffff0000u);
           const float sc1 = __uint_as_float(mk1 << 16), bi1 = __uint_as_float(mk1 & 0xffff0000u);
           const float adj0 = fmaf(-1024.0f, sc0, bi0), adj1 = fmaf(-1024.0f, sc1, bi1);
           const float qs0 = qsum_s[(2 * t) * G + grp], qs1 = qsum_s[(2 * t + 1) * G + grp];
-          s[0] += sc0 * acc[0] + adj0 * qs0;
-          s[1] += sc0 * acc[1] + adj0 * qs1;
-          s[2] += sc1 * acc[2] + adj1 * qs0;
-          s[3] += sc1 * acc[3] + adj1 * qs1;
+          s[0] += sc0 * acc[grp][0] + adj0 * qs0;
+          s[1] += sc0 * acc[grp][1] + adj0 * qs1;
+          s[2] += sc1 * acc[grp][2] + adj1 * qs0;
+          s[3] += sc1 * acc[grp][3] + adj1 * qs1;
         }
         if (row_base < ws || row_base + PAGE_TOKENS > len) {
           int64_t ra = row_base + g, rb = row_base + g + 8;
@@ -371,6 +389,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
         l1 += p[1] + p[3];
         // ---- outputs: per group, fold scale_v into the weights; bias_v term in f32 ----
         const uint8_t* vmeta = vtile + S::CODES;
+        uint32_t pb0[G], pb1[G];
 #pragma unroll
         for (int grp = 0; grp < G; ++grp) {
           const uint32_t mv0 = *reinterpret_cast<const uint32_t*>(vmeta + (g * G + grp) * 4);
@@ -379,16 +398,15 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
           const float sc1 = __uint_as_float(mv1 << 16) * pscale, bi1 = __uint_as_float(mv1 & 0xffff0000u);
           corr[grp][0] += bi0 * p[0] + bi1 * p[2];
           corr[grp][1] += bi0 * p[1] + bi1 * p[3];
-          const uint32_t b0 = movmatrix_trans(pack_f16(p[0] * sc0, p[1] * sc0));   // rows 0-7
-          const uint32_t b1 = movmatrix_trans(pack_f16(p[2] * sc1, p[3] * sc1));   // rows 8-15
+          pb0[grp] = movmatrix_trans(pack_f16(p[0] * sc0, p[1] * sc0));   // rows 0-7
+          pb1[grp] = movmatrix_trans(pack_f16(p[2] * sc1, p[3] * sc1));   // rows 8-15
+        }
 #pragma unroll
-          for (int jj = 0; jj < 2; ++jj) {
-            const int j = 2 * grp + jj;
-            const uint32_t w0 = *reinterpret_cast<const uint32_t*>(vtile + (16 * j + g) * PAGE_TOKENS + 4 * t);
-            const uint32_t w1 = *reinterpret_cast<const uint32_t*>(vtile + (16 * j + g + 8) * PAGE_TOKENS + 4 * t);
-            mma_f16(o_acc[j], sub1024(codes_lo(w0)), sub1024(codes_lo(w1)), sub1024(codes_hi(w0)),
-                    sub1024(codes_hi(w1)), b0, b1);
-          }
+        for (int j = 0; j < KSTEPS; ++j) {
+          const uint32_t w0 = *reinterpret_cast<const uint32_t*>(vtile + (16 * j + g) * PAGE_TOKENS + 4 * t);
+          const uint32_t w1 = *reinterpret_cast<const uint32_t*>(vtile + (16 * j + g + 8) * PAGE_TOKENS + 4 * t);
+          mma_f16(o_acc[j], sub1024(codes_lo(w0)), sub1024(codes_lo(w1)), sub1024(codes_hi(w0)),
+                  sub1024(codes_hi(w1)), pb0[j / 2], pb1[j / 2]);
         }
       }
       __syncwarp();
