@@ -67,6 +67,11 @@ int32_t sgk_state_sync(sgk_state* state);
 /* Reads and clears the device status word kernels set when a bounded wait expires. */
 int32_t sgk_state_device_status(sgk_state* state, int32_t* status_out);
 
+/* Failure-detection self test: launches a kernel whose only wait (on an mbarrier nobody
+ * completes) must expire. Returns SGK_ERR_TIMEOUT when the bounded wait reported through the
+ * status word as designed; the device and the state stay usable. */
+int32_t sgk_state_selftest_wait_timeout(sgk_state* state);
+
 /* ---- page pool (new design: the reference KV is contiguous, not paged) ---- */
 int32_t sgk_pool_create(sgk_state* state, int32_t layers, int32_t kv_heads, int32_t head_dim,
                         int32_t dtype, int32_t page_tokens, int64_t num_pages, int32_t max_seqs,

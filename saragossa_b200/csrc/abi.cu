@@ -88,6 +88,14 @@ static int check_device_status(State* st) {
   return fail(SGK_ERR_BACKEND, "kernel reported status %d (block-table entry out of range)", status);
 }
 
+int32_t sgk_state_selftest_wait_timeout(sgk_state* st) {
+  if (!st) return fail(SGK_ERR_BACKEND, "null state");
+  SGK_CUDA(launch_wait_timeout_selftest(st->d_status, st->stream));
+  st->launches += 1;
+  SGK_CUDA(cudaStreamSynchronize(st->stream));
+  return check_device_status(st);
+}
+
 // ------------------------------------------------------------------ pool
 int32_t sgk_pool_create(sgk_state* st, int32_t layers, int32_t kv_heads, int32_t head_dim, int32_t dtype,
                         int32_t page_tokens, int64_t num_pages, int32_t max_seqs, int64_t max_seq_tokens,
@@ -475,8 +483,6 @@ int32_t sgk_rms_norm_rope_decode(sgk_state* st, const float* x, const float* wei
   a.rope = r;
   a.out_k = d_out;
   a.status = st->d_status;
-  int32_t zero_len = 0;
-  (void)zero_len;
   // lens is dereferenced only when use_device_len is set; give it a valid word anyway
   a.pool.lens = st->d_status;
   cudaError_t e = cudaMemcpyAsync(d_x, x, n * sizeof(float), cudaMemcpyHostToDevice, stream);

@@ -104,7 +104,6 @@ struct Kv {
   Seq* seq = nullptr;
   int layer = 0;
   int q_heads = 0;
-  int kernel_choice = 0;
   // standalone KV owns its pool and sequence
   std::unique_ptr<Pool> owned_pool;
   std::unique_ptr<Seq> owned_seq;

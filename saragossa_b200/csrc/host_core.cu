@@ -428,9 +428,6 @@ int Batch::enqueue_attention(cudaStream_t stream, const float* d_q, float* d_out
   if (kernel >= 2) {
     a.k_new = d_k_new;
     a.v_new = d_v_new;
-    int64_t pages = (max_rows + PAGE_TOKENS - 1) / PAGE_TOKENS + 1;
-    int64_t per_split = (pages + a.splits - 1) / a.splits;
-    (void)per_split;
     a.n_stages = attention_mma_max_stages(pool->head_dim);
     // tuning flag (stages of the shared-memory ring), in the spirit of the reference's RETI_RUST_* switches
     static const int env_stages = [] {

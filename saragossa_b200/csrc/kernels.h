@@ -80,6 +80,8 @@ cudaError_t launch_attention_generic(const AttnArgs& a, int n_seq, cudaStream_t 
 bool attention_mma_supported(int dtype, int head_dim, int gqa);
 cudaError_t launch_attention_mma(const AttnArgs& a, int n_seq, cudaStream_t stream);
 cudaError_t attention_mma_configure();
+// A kernel whose only wait can never complete: it must time out, set the status word and return.
+cudaError_t launch_wait_timeout_selftest(int32_t* status, cudaStream_t stream);
 int attention_mma_max_stages(int head_dim);
 // Tensor-core paged kernel for u8 group-32 pages: head_dim 128 or 256, q_heads/kv_heads <= 8.
 bool attention_u8_supported(int dtype, int head_dim, int gqa);

@@ -47,7 +47,7 @@ struct MmaSmem {
   static constexpr int OPAD = HD + 4;                // padded row of the merge buffer
   static constexpr int Q_BYTES = 2 * 8 * HD * 2;     // hi and lo, 8 heads
   static constexpr int O_BYTES = MMA_CONSUMERS * 8 * OPAD * 4;  // aliases the ring once it has drained
-  static constexpr int ML_BYTES = MMA_CONSUMERS * 8 * 2 * 4;
+  static constexpr int ML_BYTES = 512;  // per-warp {max, sum}, then the merge weights and the block's {max, sum}
   static constexpr int BAR_BYTES = 2 * MMA_MAX_STAGES * 8;
   static constexpr int FIXED = Q_BYTES + ML_BYTES + BAR_BYTES + 64;
   __host__ __device__ static size_t ring_bytes(int stages) {
@@ -386,6 +386,26 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
   __syncthreads();
 
   finish_block<HD>(a, o_s, ml_s, S::OPAD, flags, seq, kvh, split, gqa, do_append, len_ptr, len, tid);
+}
+
+// Exercises the bounded wait on purpose: one warp waits on an mbarrier that nobody completes.
+// The wait gives up after its spin limit, sets the device status word and the kernel returns;
+// the context stays usable. Used by the failure-detection test.
+__global__ void wait_timeout_selftest_kernel(int32_t* status) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 1;  // start with the short spin limit
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_wait(smem_u32(&bar), 0, &abort_flag, status);
+}
+
+cudaError_t launch_wait_timeout_selftest(int32_t* status, cudaStream_t stream) {
+  wait_timeout_selftest_kernel<<<1, 32, 0, stream>>>(status);
+  return cudaGetLastError();
 }
 
 bool attention_mma_supported(int dtype, int head_dim, int gqa) {

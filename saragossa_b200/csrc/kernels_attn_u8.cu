@@ -68,7 +68,7 @@ struct U8Smem {
   static constexpr int Q_BYTES = 2 * 8 * QROW;            // hi and lo
   static constexpr int QSUM_BYTES = 8 * G * 4;
   static constexpr int O_BYTES = MMA_CONSUMERS * 8 * OPAD * 4;
-  static constexpr int ML_BYTES = MMA_CONSUMERS * 8 * 2 * 4;
+  static constexpr int ML_BYTES = 512;  // per-warp {max, sum}, then the merge weights and the block's {max, sum}
   static constexpr int BAR_BYTES = 2 * MMA_MAX_STAGES * 8;
   static constexpr int FIXED = Q_BYTES + QSUM_BYTES + ML_BYTES + BAR_BYTES + 64;
   __host__ __device__ static size_t ring_bytes(int stages) {

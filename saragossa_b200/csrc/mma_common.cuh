@@ -96,6 +96,16 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
 #endif
 
 
+// Arrival on a device-wide counter that publishes the block's earlier global writes and, for
+// the block that arrives last, makes the others' writes visible: one acquire-release atomic
+// instead of a fence, a relaxed atomic and a second fence (the block barrier before it orders
+// the other threads' writes before this thread's release).
+__device__ __forceinline__ int arrive_acq_rel(int32_t* counter) {
+  int old;
+  asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(counter) : "memory");
+  return old;
+}
+
 // Block-cooperative merge of `count` (<= MERGE_MAX) partials (rows first..first+count
 // of a [q head][stride][HD] array) for the gqa heads starting at qh0. A thread owns
 // cells of four dims; per pass it handles two cells and issues every load it needs
@@ -169,28 +179,46 @@ __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s
                                              int32_t* len_ptr, int64_t len, int tid) {
   if (tid == 0) SGK_TP(4);
   // ---- merge the consumer warps; write the partial or the final output ----
+  // ml_s holds [warps][8]{max, sum}; behind it: the per-(head, warp) weights and the block's
+  // {max, sum} per head (the shared-memory layouts reserve 512 bytes for this area).
+  float* wgt_s = const_cast<float*>(ml_s) + MMA_CONSUMERS * 8 * 2;   // [8][warps]
+  float* hml_s = wgt_s + 8 * MMA_CONSUMERS;                           // [8]{max, sum}
   const int64_t qh0 = int64_t(seq) * a.q_heads + int64_t(kvh) * gqa;
-  for (int idx = tid; idx < gqa * HD; idx += MMA_THREADS) {
-    int h = idx / HD, d = idx % HD;
+  if (tid < 8) {
     float mb = -1.0e30f;
 #pragma unroll
-    for (int w = 0; w < MMA_CONSUMERS; ++w) mb = fmaxf(mb, ml_s[(w * 8 + h) * 2]);
-    float o = 0.0f, lb = 0.0f;
+    for (int w = 0; w < MMA_CONSUMERS; ++w) mb = fmaxf(mb, ml_s[(w * 8 + tid) * 2]);
+    float lb = 0.0f;
 #pragma unroll
     for (int w = 0; w < MMA_CONSUMERS; ++w) {
-      float wg = exp2f(ml_s[(w * 8 + h) * 2] - mb);
-      o += o_s[(w * 8 + h) * opad + d] * wg;
-      lb += ml_s[(w * 8 + h) * 2 + 1] * wg;
+      const float wg = exp2f(ml_s[(w * 8 + tid) * 2] - mb);
+      wgt_s[tid * MMA_CONSUMERS + w] = wg;
+      lb += ml_s[(w * 8 + tid) * 2 + 1] * wg;
+    }
+    hml_s[2 * tid] = mb;
+    hml_s[2 * tid + 1] = lb;
+  }
+  __syncthreads();
+  for (int idx = tid; idx < gqa * (HD / 4); idx += MMA_THREADS) {
+    const int h = idx / (HD / 4), d = (idx % (HD / 4)) * 4;
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int w = 0; w < MMA_CONSUMERS; ++w) {
+      const float4 v = *reinterpret_cast<const float4*>(o_s + (w * 8 + h) * opad + d);
+      const float wg = wgt_s[h * MMA_CONSUMERS + w];
+      o.x += v.x * wg;
+      o.y += v.y * wg;
+      o.z += v.z * wg;
+      o.w += v.w * wg;
     }
     if (a.splits == 1) {
-      a.out[(qh0 + h) * HD + d] = o / lb;
+      const float inv = 1.0f / hml_s[2 * h + 1];
+      *reinterpret_cast<float4*>(a.out + (qh0 + h) * HD + d) = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
     } else {
-      a.part.o[((qh0 + h) * a.splits + split) * HD + d] = o;
-      if (d == 0) {
-        float* pml = a.part.ml + ((qh0 + h) * a.splits + split) * 2;
-        pml[0] = mb;
-        pml[1] = lb;
-      }
+      *reinterpret_cast<float4*>(a.part.o + ((qh0 + h) * a.splits + split) * HD + d) = o;
+      if (d == 0)
+        *reinterpret_cast<float2*>(a.part.ml + ((qh0 + h) * a.splits + split) * 2) =
+            make_float2(hml_s[2 * h], hml_s[2 * h + 1]);
     }
   }
   if (a.splits > 1 || do_append) {
@@ -201,16 +229,15 @@ __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s
     int32_t* head_counter = a.head_counters + int64_t(seq) * a.pool.kv_heads + kvh;
     __syncthreads();
     if (tid == 0) {
-      __threadfence();
       if (a.splits > 1) {
-        int old = atomicAdd(group_counter, 1);
+        int old = arrive_acq_rel(group_counter);
         flags[1] = (old == group_count - 1);
         if (flags[1]) *group_counter = 0;
       }
       if (do_append) {
         // the block that arrives last for the sequence moves the cursor
         int total = a.splits * a.pool.kv_heads;
-        int old = atomicAdd(a.seq_counters + seq, 1);
+        int old = arrive_acq_rel(a.seq_counters + seq);
         if (old == total - 1) {
           *len_ptr = static_cast<int32_t>(len);
           a.seq_counters[seq] = 0;
@@ -221,7 +248,6 @@ __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s
     if (tid == 0) SGK_TP(5);
     if (a.splits > 1 && flags[1]) {
       // this block completed its group: merge the group (or everything, if one group)
-      __threadfence();
       const bool single = a.n_groups == 1;
       merge_block<HD>(a.part, a.splits, group_first, group_count, gqa, qh0, single, a.out, a.part2,
                       a.max_groups, group, tid);
@@ -229,14 +255,12 @@ __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s
       if (!single) {
         __syncthreads();
         if (tid == 0) {
-          __threadfence();
-          int old = atomicAdd(head_counter, 1);
+          int old = arrive_acq_rel(head_counter);
           flags[1] = (old == a.n_groups - 1);
           if (flags[1]) *head_counter = 0;
         }
         __syncthreads();
         if (flags[1]) {
-          __threadfence();
           merge_block<HD>(a.part2, a.max_groups, 0, a.n_groups, gqa, qh0, true, a.out, a.part2,
                           a.max_groups, 0, tid);
           if (tid == 0) SGK_TP(7);

@@ -113,6 +113,10 @@ class DecodeResidentState:
         check(self.L.sgk_state_device_status(self.h, C.byref(s)))
         return s.value
 
+    def selftest_wait_timeout(self):
+        """Runs the kernel whose wait must expire; raises InferError(kind='Timeout') when it did."""
+        check(self.L.sgk_state_selftest_wait_timeout(self.h))
+
     def full_attention(self, capacity, q_heads, kv_heads, head_dim, dtype=KV_F32, shuffled_seed=None):
         """state.full_attention(capacity, q, kv, hd, sampled) (attention.rs:26-108)."""
         h = C.c_void_p()

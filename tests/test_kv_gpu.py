@@ -554,3 +554,17 @@ def test_device_fill_matches_host_generator(state):
     state.fill_normal(buf, n, 9, 4, 1234)
     state.sync()
     assert np.array_equal(buf.download(), sgo.fill_normal8(n, 9, 4, 1234))
+
+
+def test_bounded_wait_reports_timeout_and_context_survives(state):
+    """Failure detection without faulting the GPU: a wait that nothing completes gives up after its
+    spin limit, the kernel sets the status word and returns, the host sees SGK_ERR_TIMEOUT, and the
+    same state keeps working."""
+    with pytest.raises(sg.InferError) as e:
+        state.selftest_wait_timeout()
+    assert e.value.kind == "Timeout"
+    assert state.device_status() == 0                      # reading the status cleared it
+    kv = state.full_attention(4, 4, 2, 16)
+    kv.append_row(np.ones(32, np.float32), np.ones(32, np.float32))
+    assert np.allclose(kv.attention_decode(np.ones(64, np.float32)), 1.0)
+    kv.close()
