@@ -329,6 +329,7 @@ def run_ours(args):
 
     # ---- prefix restore: block copy of a 4096-token prefix on the 4B shape (config 4) ----
     restore = prefix_restore_gbs(sg, st, torch, stream)
+    recurrent = gated_delta_leg(sg, st, torch, stream)
 
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -351,7 +352,7 @@ def run_ours(args):
             "decode_steps_per_s": BATCH * world * K / (ms * 1e-3),
             "batch1": {"us_per_layer": b1_us_layer, "hbm_gbs": b1_gbs, "steps": b1_steps,
                        "frac_of_peak": b1_gbs / peak},
-            "prefix_restore": restore, "head_sharded_batch1": head_sharded,
+            "prefix_restore": restore, "head_sharded_batch1": head_sharded, "gated_delta_step": recurrent,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": alg_per_launch * NCU_TRAFFIC_RATIO,
                          "kernel": "attention_mma_kernel<128> (fused append + paged decode attention)",
@@ -442,6 +443,54 @@ def head_sharded_leg(sg, st, torch, dist, world, rank, stream):
     return {"us_per_layer": ms * 1e3 / (steps * LAYERS), "hbm_gbs_aggregate": total_bytes / (ms * 1e-3) / 1e9,
             "ranks": world, "kv_heads_per_rank": sh.kv_heads, "steps": steps, "outputs_finite": finite,
             "exchange": f"one NCCL all-gather of {world * q_loc * 4} bytes of attention output per layer"}
+
+
+def gated_delta_leg(sg, st, torch, stream):
+    """One gated-delta token on the recurrent state of config 3's linear layers: 30 layers,
+    32 value heads x 128 x 128 f32 (2 MiB per layer per sequence), 8 sequences per launch,
+    so each step reads and writes 480 MiB of state once (larger than L2)."""
+    layers, n, shape = 30, 8, (16, 32, 128, 128)
+    hk, hv, dk, dv = shape
+    ssm_len = hv * dv * dk
+    states = [sg.LinearAttentionState(st, layers, 0, ssm_len) for _ in range(n)]
+    bufs = []
+    for j, (count, scale) in enumerate([(hk * dk, 1.0 / dk), (hk * dk, dk ** -0.5), (hv * dv, 1.0)]):
+        b = st.alloc(4 * n * count)
+        st.fill_normal(b, n * count, 77, j, stream=stream.cuda_stream)
+        stream.synchronize()
+        bufs.append(st.upload(b.download(count=n * count) * np.float32(scale)))
+    bufs.append(st.upload(np.full(n * hv, 0.97, np.float32)))
+    bufs.append(st.upload(np.full(n * hv, 0.5, np.float32)))
+    d_out = st.alloc(4 * n * hv * dv)
+
+    def step():
+        for layer in range(layers):
+            sg.encode_gated_delta_step_batch(states, layer, shape, *bufs, d_out, stream=stream.cuda_stream)
+
+    step()
+    stream.synchronize()
+    # the 30 launches of a step replay as one CUDA graph, as the decode loop would issue them
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        step()
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 5
+        stream.synchronize()
+        e0.record(stream)
+        for _ in range(reps):
+            graph.replay()
+        e1.record(stream)
+        stream.synchronize()
+    t = e0.elapsed_time(e1) * 1e-3 / (reps * layers)
+    finite = bool(np.isfinite(d_out.download(count=n * hv * dv)).all())
+    for s in states:
+        s.close()
+    nbytes = 2 * 4 * n * ssm_len
+    return {"us_per_layer": t * 1e6, "hbm_gbs": nbytes / t / 1e9, "sequences": n, "state_bytes_per_layer": nbytes // 2,
+            "outputs_finite": finite, "launches": (2 + 3 + reps) * layers}
 
 
 def prefix_restore_gbs(sg, st, torch, stream):

@@ -246,6 +246,31 @@ int32_t sgk_linstate_read(sgk_linstate* ls, int32_t layer, float* conv, float* s
 int32_t sgk_linstate_snapshot(sgk_linstate* ls, void* stream, sgk_linstate** snapshot_out);
 int32_t sgk_linstate_restore(sgk_linstate* ls, void* stream, const sgk_linstate* snapshot);
 void* sgk_linstate_conv_ptr(sgk_linstate* ls, int32_t layer);
+/* One decode token on a layer's state, in stream order (the "next" step of the path:
+ * the state this library snapshots is also advanced here).
+ * depthwise_causal_conv for one token (src/linear_attention.rs:802-852): d_qkv, d_out
+ * [conv_dim]; d_weight [conv_dim][conv_kernel_dim]; the history [(K-1), conv_dim] slides. */
+int32_t sgk_linstate_enqueue_conv_step(sgk_linstate* ls, void* stream, int32_t layer, const float* d_qkv,
+                                       const float* d_weight, int32_t conv_dim, int32_t conv_kernel_dim,
+                                       float* d_out);
+/* gated_delta for one token (src/linear_attention.rs:896-991): S <- g*S; kv = S.k;
+ * delta = (v - kv)*beta; S <- S + delta*k^T; y = S.q, value head h reading the q/k of key
+ * head h / (H_v / H_k). d_q, d_k [H_k*d_k]; d_v, d_out [H_v*d_v]; d_g, d_beta [H_v]. */
+typedef struct {
+  int32_t num_key_heads, num_value_heads, key_head_dim, value_head_dim;
+} sgk_linear_shape;
+int32_t sgk_linstate_enqueue_gated_delta_step(sgk_linstate* ls, void* stream, int32_t layer,
+                                              const sgk_linear_shape* shape, const float* d_q, const float* d_k,
+                                              const float* d_v, const float* d_g, const float* d_beta,
+                                              float* d_out);
+/* The same step for n_states sequences (at most 64) in one launch, as the reference's batch
+ * decode does for its sequences (src/metal_backend/lightbatch_duo.rs): states[i] is sequence
+ * i's state and every input and the output gain a leading [n_states] dimension. All states
+ * must have the same length and storage type. */
+int32_t sgk_linstate_enqueue_gated_delta_step_batch(sgk_linstate* const* states, int32_t n_states, void* stream,
+                                                    int32_t layer, const sgk_linear_shape* shape,
+                                                    const float* d_q, const float* d_k, const float* d_v,
+                                                    const float* d_g, const float* d_beta, float* d_out);
 void* sgk_linstate_ssm_ptr(sgk_linstate* ls, int32_t layer);
 
 /* ---- block hashes: BlockHash::{root,for_session,chain} (src/serve/cache.rs:11-47) ---- */

@@ -185,6 +185,18 @@ struct LinearState {
 };
 LinearState linear_state_snapshot(const LinearState& s);
 Status linear_state_restore(LinearState* state, const LinearState& snapshot);
+// One decode token of the Gated DeltaNet recurrence on the SSM state [H_v][d_v][d_k]
+// (src/linear_attention.rs:896-991): per value head h (key head h / repeat), per state row:
+//   S *= g; kv = S.k; delta = (v - kv) * beta; S += delta * k; y = S.q     (sequential f32 sums)
+struct LinearShape {
+  size_t num_key_heads, num_value_heads, key_head_dim, value_head_dim, conv_kernel_dim;
+};
+Status gated_delta_step(const float* q, const float* k, const float* v, const float* g, const float* beta,
+                        const LinearShape& shape, std::vector<float>* ssm, float* out);
+// Depthwise causal conv of one token with the sliding history [(K-1), conv_dim]
+// (src/linear_attention.rs:802-852); weight is [conv_dim][K].
+Status depthwise_conv_step(const float* qkv, const float* weight, size_t conv_dim, size_t kernel,
+                           std::vector<float>* history, float* out);
 
 // ---- deterministic input generators ---------------------------------------
 // pseudo(): the closed form of the reference's tests (src/decode_resident/tests.rs:544-547).

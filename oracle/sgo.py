@@ -108,6 +108,8 @@ def _declare(L):
         "sgo_guard_limit": (i32, [vp, pu64]),
         "sgo_guard_check": (i32, [vp, u64, pu64, pu64]),
         "sgo_linear_restore_check": (i32, [sz, sz, i32, sz, sz, i32]),
+        "sgo_gated_delta_step": (i32, [pf, pf, pf, pf, pf, sz, sz, sz, sz, pf, sz, pf]),
+        "sgo_depthwise_conv_step": (i32, [pf, pf, sz, sz, pf, sz, pf]),
         "sgo_pseudo": (f, [u64]),
         "sgo_pseudo_array": (None, [u64, sz, pf]),
         "sgo_splitmix64": (u64, [u64]),
@@ -450,6 +452,25 @@ class MemoryGuard:
 
 def linear_restore_check(conv_a, ssm_a, bf16_a, conv_b, ssm_b, bf16_b):
     return lib().sgo_linear_restore_check(conv_a, ssm_a, int(bf16_a), conv_b, ssm_b, int(bf16_b))
+
+
+def gated_delta_step(q, k, v, g, beta, num_key_heads, num_value_heads, key_head_dim, value_head_dim, ssm):
+    """One token of src/linear_attention.rs:896-991; returns (status, out, new_ssm)."""
+    q, k, v, g, beta = (_f32(x).ravel() for x in (q, k, v, g, beta))
+    state = _f32(ssm).ravel().copy()
+    out = np.empty(num_value_heads * value_head_dim, np.float32)
+    st = lib().sgo_gated_delta_step(_fp(q), _fp(k), _fp(v), _fp(g), _fp(beta), num_key_heads, num_value_heads,
+                                    key_head_dim, value_head_dim, _fp(state), state.size, _fp(out))
+    return st, out, state
+
+
+def depthwise_conv_step(qkv, weight, kernel, history):
+    """One token of src/linear_attention.rs:802-852; returns (status, out, new_history)."""
+    qkv, weight = _f32(qkv).ravel(), _f32(weight).ravel()
+    hist = _f32(history).ravel().copy()
+    out = np.empty(qkv.size, np.float32)
+    st = lib().sgo_depthwise_conv_step(_fp(qkv), _fp(weight), qkv.size, kernel, _fp(hist), hist.size, _fp(out))
+    return st, out, hist
 
 
 # ---- generators ----------------------------------------------------------------------

@@ -230,6 +230,23 @@ int32_t sgo_linear_restore_check(size_t conv_a, size_t ssm_a, int32_t bf16_a, si
   return linear_state_restore(&a, b);
 }
 
+int32_t sgo_gated_delta_step(const float* q, const float* k, const float* v, const float* g, const float* beta,
+                             size_t num_key_heads, size_t num_value_heads, size_t key_head_dim,
+                             size_t value_head_dim, float* ssm, size_t ssm_len, float* out) {
+  LinearShape sh{num_key_heads, num_value_heads, key_head_dim, value_head_dim, 0};
+  std::vector<float> state(ssm, ssm + ssm_len);
+  Status st = gated_delta_step(q, k, v, g, beta, sh, &state, out);
+  if (st == OK) std::memcpy(ssm, state.data(), state.size() * sizeof(float));
+  return st;
+}
+int32_t sgo_depthwise_conv_step(const float* qkv, const float* weight, size_t conv_dim, size_t kernel,
+                                float* history, size_t history_len, float* out) {
+  std::vector<float> h(history, history + history_len);
+  Status st = depthwise_conv_step(qkv, weight, conv_dim, kernel, &h, out);
+  if (st == OK && !h.empty()) std::memcpy(history, h.data(), h.size() * sizeof(float));
+  return st;
+}
+
 // ---- generators ---------------------------------------------------------------------------
 float sgo_pseudo(uint64_t seed) { return pseudo(seed); }
 void sgo_pseudo_array(uint64_t seed0, size_t n, float* out) {

@@ -251,4 +251,62 @@ Status linear_state_restore(LinearState* state, const LinearState& snapshot) {
   return OK;
 }
 
+// ---- Gated DeltaNet step (src/linear_attention.rs:896-991) ---------------------
+Status gated_delta_step(const float* q, const float* k, const float* v, const float* g, const float* beta,
+                        const LinearShape& sh, std::vector<float>* ssm, float* out) {
+  if (sh.num_key_heads == 0 || sh.num_value_heads % sh.num_key_heads != 0) return ERR_DIMENSION;
+  const size_t head_len = sh.value_head_dim * sh.key_head_dim;
+  if (ssm->size() != sh.num_value_heads * head_len) return ERR_DIMENSION;  // ensure_ssm_cache, :994-1024
+  const size_t repeat = sh.num_value_heads / sh.num_key_heads;
+  for (size_t vh = 0; vh < sh.num_value_heads; ++vh) {
+    const size_t kh = vh / repeat;  // GQA: q/k of key head floor(h / repeat)
+    const float* q_head = q + kh * sh.key_head_dim;
+    const float* k_head = k + kh * sh.key_head_dim;
+    const float* v_head = v + vh * sh.value_head_dim;
+    const float decay = g[vh], beta_value = beta[vh];
+    float* state_head = ssm->data() + vh * head_len;
+    for (size_t col = 0; col < sh.value_head_dim; ++col) {
+      float* row = state_head + col * sh.key_head_dim;
+      float kv_mem = 0.0f;
+      for (size_t i = 0; i < sh.key_head_dim; ++i) {  // :964-967 decay in place, read before write
+        row[i] *= decay;
+        kv_mem += row[i] * k_head[i];
+      }
+      const float delta = (v_head[col] - kv_mem) * beta_value;  // :970
+      float y = 0.0f;
+      for (size_t i = 0; i < sh.key_head_dim; ++i) {  // :974-980 outer product and read-out fused
+        row[i] += delta * k_head[i];
+        y += row[i] * q_head[i];
+      }
+      out[vh * sh.value_head_dim + col] = y;
+    }
+  }
+  return OK;
+}
+
+// ---- depthwise causal conv, one token (src/linear_attention.rs:802-852) --------
+Status depthwise_conv_step(const float* qkv, const float* weight, size_t conv_dim, size_t kernel,
+                           std::vector<float>* history, float* out) {
+  if (kernel == 0) return ERR_DIMENSION;
+  const size_t keep = kernel - 1;
+  if (history->size() != keep * conv_dim) return ERR_DIMENSION;  // :816-823
+  for (size_t c = 0; c < conv_dim; ++c) {
+    float acc = 0.0f;
+    for (size_t kk = 0; kk < kernel; ++kk) {
+      const float input = kk < keep ? (*history)[kk * conv_dim + c] : qkv[c];
+      acc += input * weight[c * kernel + kk];  // conv_weight_value: [conv_dim][K]
+    }
+    out[c] = acc;
+  }
+  // the history advances to the last K-1 tokens (:841-848)
+  if (keep > 0) {
+    std::vector<float> next(keep * conv_dim);
+    for (size_t r = 0; r + 1 < keep; ++r)
+      std::memcpy(next.data() + r * conv_dim, history->data() + (r + 1) * conv_dim, conv_dim * sizeof(float));
+    std::memcpy(next.data() + (keep - 1) * conv_dim, qkv, conv_dim * sizeof(float));
+    *history = next;
+  }
+  return OK;
+}
+
 }  // namespace sgo

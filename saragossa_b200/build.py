@@ -24,6 +24,7 @@ SOURCES = [
     "kernels_attn_mma.cu",
     "kernels_attn_u8.cu",
     "kernels_copy.cu",
+    "kernels_linear.cu",
     "noalloc.cu",
 ]
 

@@ -914,6 +914,72 @@ int32_t sgk_linstate_restore(sgk_linstate* ls, void* stream, const sgk_linstate*
   return SGK_OK;
 }
 
+int32_t sgk_linstate_enqueue_conv_step(sgk_linstate* ls, void* stream, int32_t layer, const float* d_qkv,
+                                       const float* d_weight, int32_t conv_dim, int32_t conv_kernel_dim,
+                                       float* d_out) {
+  if (!ls || !d_qkv || !d_weight || !d_out) return fail(SGK_ERR_BACKEND, "null argument");
+  if (layer < 0 || layer >= ls->layers) return fail(SGK_ERR_DIMENSION, "layer %d out of range", layer);
+  if (conv_dim <= 0 || conv_kernel_dim <= 0) return fail(SGK_ERR_DIMENSION, "conv shape must be positive");
+  // ensure_conv_cache (src/linear_attention.rs:856-886): the history is [(K-1), conv_dim]
+  if (ls->conv_len != int64_t(conv_kernel_dim - 1) * conv_dim)
+    return fail(SGK_ERR_DIMENSION, "conv history holds %lld values, expected %lld", (long long)ls->conv_len,
+                (long long)(int64_t(conv_kernel_dim - 1) * conv_dim));
+  SGK_CUDA(launch_conv_step(d_qkv, d_weight, static_cast<float*>(sgk_linstate_conv_ptr(ls, layer)), d_out, conv_dim,
+                            conv_kernel_dim, ls->st->pick(stream)));
+  ls->st->launches += 1;
+  return SGK_OK;
+}
+
+int32_t sgk_linstate_enqueue_gated_delta_step_batch(sgk_linstate* const* states, int32_t n_states, void* stream,
+                                                    int32_t layer, const sgk_linear_shape* shape,
+                                                    const float* d_q, const float* d_k, const float* d_v,
+                                                    const float* d_g, const float* d_beta, float* d_out) {
+  if (!states || !shape || !d_q || !d_k || !d_v || !d_g || !d_beta || !d_out) return fail(SGK_ERR_BACKEND, "null argument");
+  if (n_states <= 0 || n_states > GATED_DELTA_MAX_STATES)
+    return fail(SGK_ERR_CONFIG, "n_states %d outside 1..%d", n_states, GATED_DELTA_MAX_STATES);
+  if (shape->num_key_heads <= 0 || shape->num_value_heads <= 0 || shape->key_head_dim <= 0 ||
+      shape->value_head_dim <= 0 || shape->num_value_heads % shape->num_key_heads != 0)
+    return fail(SGK_ERR_DIMENSION, "gated-delta shape invalid");
+  if (shape->key_head_dim > 256) return fail(SGK_ERR_CONFIG, "key_head_dim %d > 256 is not supported", shape->key_head_dim);
+  // ensure_ssm_cache (src/linear_attention.rs:994-1024): the state is [H_v][d_v][d_k]
+  int64_t expect = int64_t(shape->num_value_heads) * shape->value_head_dim * shape->key_head_dim;
+  GatedDeltaArgs a{};
+  for (int32_t i = 0; i < n_states; ++i) {
+    sgk_linstate* ls = states[i];
+    if (!ls) return fail(SGK_ERR_BACKEND, "null state %d", i);
+    if (layer < 0 || layer >= ls->layers) return fail(SGK_ERR_DIMENSION, "layer %d out of range", layer);
+    if (ls->ssm_len != expect)
+      return fail(SGK_ERR_DIMENSION, "ssm state holds %lld values, shape wants %lld", (long long)ls->ssm_len,
+                  (long long)expect);
+    if (ls->st != states[0]->st || ls->ssm_bf16 != states[0]->ssm_bf16)
+      return fail(SGK_ERR_CONFIG, "states of one batch must share device and storage type");
+    a.ssm[i] = sgk_linstate_ssm_ptr(ls, layer);
+  }
+  a.n_states = n_states;
+  a.ssm_bf16 = states[0]->ssm_bf16 ? 1 : 0;
+  a.num_key_heads = shape->num_key_heads;
+  a.num_value_heads = shape->num_value_heads;
+  a.key_head_dim = shape->key_head_dim;
+  a.value_head_dim = shape->value_head_dim;
+  a.q = d_q;
+  a.k = d_k;
+  a.v = d_v;
+  a.g = d_g;
+  a.beta = d_beta;
+  a.out = d_out;
+  SGK_CUDA(launch_gated_delta_step(a, states[0]->st->pick(stream)));
+  states[0]->st->launches += 1;
+  return SGK_OK;
+}
+
+int32_t sgk_linstate_enqueue_gated_delta_step(sgk_linstate* ls, void* stream, int32_t layer,
+                                              const sgk_linear_shape* shape, const float* d_q, const float* d_k,
+                                              const float* d_v, const float* d_g, const float* d_beta,
+                                              float* d_out) {
+  if (!ls) return fail(SGK_ERR_BACKEND, "null argument");
+  return sgk_linstate_enqueue_gated_delta_step_batch(&ls, 1, stream, layer, shape, d_q, d_k, d_v, d_g, d_beta, d_out);
+}
+
 // ------------------------------------------------------------------ hashes
 void sgk_hash_root(uint8_t out[32]) { std::memset(out, 0, 32); }
 

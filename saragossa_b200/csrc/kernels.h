@@ -118,6 +118,23 @@ cudaError_t launch_copy_bytes(void* dst, const void* src, int64_t bytes, cudaStr
 // Zero-fill of freed pages (eviction scrub).
 cudaError_t launch_scrub_pages(uint8_t* base, const int32_t* d_pages, int n_pages, int64_t page_bytes,
                                cudaStream_t stream);
+// Gated DeltaNet step on one layer's state [H_v][d_v][d_k] (f32 or bf16).
+constexpr int GATED_DELTA_MAX_STATES = 64;
+struct GatedDeltaArgs {
+  void* ssm[GATED_DELTA_MAX_STATES];  // one state per sequence, passed by value: no device table
+  int32_t n_states;
+  int32_t ssm_bf16;
+  int32_t num_key_heads, num_value_heads, key_head_dim, value_head_dim;
+  const float* q;     // [n_states][H_k * d_k]
+  const float* k;     // [n_states][H_k * d_k]
+  const float* v;     // [n_states][H_v * d_v]
+  const float* g;     // [n_states][H_v] decay
+  const float* beta;  // [n_states][H_v] write gate
+  float* out;         // [n_states][H_v * d_v]
+};
+cudaError_t launch_gated_delta_step(const GatedDeltaArgs& a, cudaStream_t stream);
+cudaError_t launch_conv_step(const float* qkv, const float* weight, float* history, float* out, int conv_dim,
+                             int kernel, cudaStream_t stream);
 cudaError_t launch_fill_normal(float* out, int64_t n, uint64_t seed, uint64_t stream_id,
                                uint64_t index0, cudaStream_t stream);
 

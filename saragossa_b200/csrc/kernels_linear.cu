@@ -1,0 +1,228 @@
+// One decode token on the linear-attention recurrent state this path stores:
+// the depthwise causal conv with its sliding history, and the Gated DeltaNet update
+//   S <- g*S;  kv = S.k;  delta = (v - kv)*beta;  S <- S + delta*k^T;  y = S.q
+// on the state [H_v][d_v][d_k] (src/linear_attention.rs:802-852,896-991; Metal twins
+// linear_attn_gated_delta_* in src/metal_backend/mod.rs:155-171). Both are HBM-bound:
+// the state is read once and written once per token (4 MiB per layer at 32 x 128 x 128 f32).
+#include "kernels.h"
+
+namespace sgk {
+
+constexpr int GD_THREADS = 256;
+constexpr int GD_WARPS = GD_THREADS / 32;
+constexpr int GD_MAXJ = 8;  // key_head_dim <= 256
+
+template <bool BF16>
+__device__ __forceinline__ float load_state(const void* base, int64_t i) {
+  if (BF16) return bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(base)[i]);
+  return reinterpret_cast<const float*>(base)[i];
+}
+template <bool BF16>
+__device__ __forceinline__ void store_state(void* base, int64_t i, float v) {
+  if (BF16)
+    reinterpret_cast<uint16_t*>(base)[i] = f32_to_bf16_bits(v);
+  else
+    reinterpret_cast<float*>(base)[i] = v;
+}
+
+// One warp per state row (d_k values), rows strided over the grid. With a bf16 state the
+// read-out uses the f32 values before they are rounded for storage, like
+// linear_attn_gated_delta_dk128_bf16_tg4_f32 (src/kernels.metal:2842-2915).
+// The two dot products of
+// a row are warp reductions; everything else is element-wise on the lane's own values.
+template <bool BF16>
+__global__ void __launch_bounds__(GD_THREADS) gated_delta_step_kernel(GatedDeltaArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int warp = blockIdx.x * GD_WARPS + (threadIdx.x >> 5);
+  const int total_warps = gridDim.x * GD_WARPS;
+  const int rows = a.num_value_heads * a.value_head_dim;
+  const int dk = a.key_head_dim;
+  const int repeat = a.num_value_heads / a.num_key_heads;
+  // blockIdx.y picks the sequence: its own state, and its slice of every input and of the output
+  const int b = blockIdx.y;
+  void* ssm = a.ssm[b];
+  const float* q_b = a.q + int64_t(b) * a.num_key_heads * dk;
+  const float* k_b = a.k + int64_t(b) * a.num_key_heads * dk;
+  const float* v_b = a.v + int64_t(b) * rows;
+  const float* g_b = a.g + int64_t(b) * a.num_value_heads;
+  const float* beta_b = a.beta + int64_t(b) * a.num_value_heads;
+  float* out_b = a.out + int64_t(b) * rows;
+  for (int row = warp; row < rows; row += total_warps) {
+    const int vh = row / a.value_head_dim, col = row % a.value_head_dim;
+    const int kh = vh / repeat;
+    const float decay = g_b[vh], beta = beta_b[vh];
+    const float* kp = k_b + kh * dk;
+    const float* qp = q_b + kh * dk;
+    const int64_t base = int64_t(row) * dk;
+    float s[GD_MAXJ], kk[GD_MAXJ];
+    float kv = 0.0f;
+#pragma unroll
+    for (int j = 0; j < GD_MAXJ; ++j) {
+      const int i = lane + 32 * j;
+      if (i < dk) {
+        kk[j] = kp[i];
+        s[j] = load_state<BF16>(ssm, base + i) * decay;
+        kv += s[j] * kk[j];
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) kv += __shfl_xor_sync(0xffffffffu, kv, off);
+    const float delta = (v_b[row] - kv) * beta;
+    float y = 0.0f;
+#pragma unroll
+    for (int j = 0; j < GD_MAXJ; ++j) {
+      const int i = lane + 32 * j;
+      if (i < dk) {
+        s[j] += delta * kk[j];
+        y += s[j] * qp[i];
+        store_state<BF16>(ssm, base + i, s[j]);
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) y += __shfl_xor_sync(0xffffffffu, y, off);
+    if (lane == 0) out_b[row] = y;
+  }
+}
+
+// key_head_dim 128 (the shape the reference ships its own dk128 kernels for): a lane owns four
+// consecutive state values, so a row is one 16-byte (f32) or 8-byte (bf16) access per lane, and a
+// warp carries R rows of one head at once to keep R independent loads in flight per lane.
+// Spelled with intrinsics so that every instantiation rounds in the same places.
+__device__ __forceinline__ float dot4(const float4& a, const float4& b) {
+  return __fmaf_rn(a.w, b.w, __fmaf_rn(a.z, b.z, __fmaf_rn(a.y, b.y, __fmul_rn(a.x, b.x))));
+}
+
+template <bool BF16, int R>
+__global__ void __launch_bounds__(GD_THREADS) gated_delta_step_dk128_kernel(GatedDeltaArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int rows = a.num_value_heads * a.value_head_dim;
+  const int repeat = a.num_value_heads / a.num_key_heads;
+  const int b = blockIdx.y;
+  const int row0 = (blockIdx.x * GD_WARPS + (threadIdx.x >> 5)) * R;  // value_head_dim % R == 0
+  if (row0 >= rows) return;
+  const int vh = row0 / a.value_head_dim;
+  const int kh = vh / repeat;
+  const int64_t in_k = (int64_t(b) * a.num_key_heads + kh) * 128 + lane * 4;
+  const float4 kk = *reinterpret_cast<const float4*>(a.k + in_k);
+  const float4 qq = *reinterpret_cast<const float4*>(a.q + in_k);
+  const float decay = a.g[int64_t(b) * a.num_value_heads + vh];
+  const float beta = a.beta[int64_t(b) * a.num_value_heads + vh];
+  const int64_t base = int64_t(row0) * 128 + lane * 4;
+  float4 s[R];
+  float vv[R];
+  if (BF16) {
+    const uint16_t* p = reinterpret_cast<const uint16_t*>(a.ssm[b]) + base;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(p + r * 128);
+      s[r] = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                         __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+    }
+  } else {
+    const float* p = reinterpret_cast<const float*>(a.ssm[b]) + base;
+#pragma unroll
+    for (int r = 0; r < R; ++r) s[r] = *reinterpret_cast<const float4*>(p + r * 128);
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r) vv[r] = a.v[int64_t(b) * rows + row0 + r];
+  float kv[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    s[r].x = __fmul_rn(s[r].x, decay), s[r].y = __fmul_rn(s[r].y, decay);
+    s[r].z = __fmul_rn(s[r].z, decay), s[r].w = __fmul_rn(s[r].w, decay);
+    kv[r] = dot4(s[r], kk);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+    for (int r = 0; r < R; ++r) kv[r] += __shfl_xor_sync(0xffffffffu, kv[r], off);
+  float y[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const float delta = __fmul_rn(__fsub_rn(vv[r], kv[r]), beta);
+    s[r].x = __fmaf_rn(delta, kk.x, s[r].x), s[r].y = __fmaf_rn(delta, kk.y, s[r].y);
+    s[r].z = __fmaf_rn(delta, kk.z, s[r].z), s[r].w = __fmaf_rn(delta, kk.w, s[r].w);
+    y[r] = dot4(s[r], qq);
+  }
+  if (BF16) {
+    uint16_t* p = reinterpret_cast<uint16_t*>(a.ssm[b]) + base;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      uint2 raw;
+      raw.x = uint32_t(f32_to_bf16_bits(s[r].x)) | (uint32_t(f32_to_bf16_bits(s[r].y)) << 16);
+      raw.y = uint32_t(f32_to_bf16_bits(s[r].z)) | (uint32_t(f32_to_bf16_bits(s[r].w)) << 16);
+      *reinterpret_cast<uint2*>(p + r * 128) = raw;
+    }
+  } else {
+    float* p = reinterpret_cast<float*>(a.ssm[b]) + base;
+#pragma unroll
+    for (int r = 0; r < R; ++r) *reinterpret_cast<float4*>(p + r * 128) = s[r];
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+    for (int r = 0; r < R; ++r) y[r] += __shfl_xor_sync(0xffffffffu, y[r], off);
+  if (lane == 0) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) a.out[int64_t(b) * rows + row0 + r] = y[r];
+  }
+}
+
+template <bool BF16, int R>
+static void launch_dk128(const GatedDeltaArgs& a, int rows, cudaStream_t stream) {
+  const int warps = rows / R;
+  dim3 grid((warps + GD_WARPS - 1) / GD_WARPS, a.n_states);
+  gated_delta_step_dk128_kernel<BF16, R><<<grid, GD_THREADS, 0, stream>>>(a);
+}
+
+cudaError_t launch_gated_delta_step(const GatedDeltaArgs& a, cudaStream_t stream) {
+  const int rows = a.num_value_heads * a.value_head_dim;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k)) & 15) == 0;
+  if (a.key_head_dim == 128 && aligned) {
+    // four rows per warp once that still leaves every SM several blocks; else one row per warp
+    const bool wide = a.value_head_dim % 4 == 0 && int64_t(rows) * a.n_states >= int64_t(4) * GD_WARPS * 148 * 4;
+    if (a.ssm_bf16) {
+      wide ? launch_dk128<true, 4>(a, rows, stream) : launch_dk128<true, 1>(a, rows, stream);
+    } else {
+      wide ? launch_dk128<false, 4>(a, rows, stream) : launch_dk128<false, 1>(a, rows, stream);
+    }
+    return cudaGetLastError();
+  }
+  int blocks = (rows + GD_WARPS - 1) / GD_WARPS;
+  // 8 resident blocks per SM over the whole grid; one row per warp needs no more than that
+  int cap = (148 * 8 + a.n_states - 1) / a.n_states;
+  if (blocks > cap) blocks = cap;
+  dim3 grid(blocks, a.n_states);
+  if (a.ssm_bf16)
+    gated_delta_step_kernel<true><<<grid, GD_THREADS, 0, stream>>>(a);
+  else
+    gated_delta_step_kernel<false><<<grid, GD_THREADS, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
+// One thread per channel: the products are summed in kernel-tap order with separate
+// roundings, exactly like the CPU loop, then the channel's history slides by one token.
+__global__ void __launch_bounds__(256) conv_step_kernel(const float* __restrict__ qkv,
+                                                       const float* __restrict__ weight, float* history,
+                                                       float* __restrict__ out, int conv_dim, int kernel) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= conv_dim) return;
+  const int keep = kernel - 1;
+  const float x = qkv[c];
+  float acc = 0.0f;
+  for (int kk = 0; kk < kernel; ++kk) {
+    const float input = kk < keep ? history[int64_t(kk) * conv_dim + c] : x;
+    acc = __fadd_rn(acc, __fmul_rn(input, weight[int64_t(c) * kernel + kk]));
+  }
+  out[c] = acc;
+  for (int r = 0; r + 1 < keep; ++r) history[int64_t(r) * conv_dim + c] = history[int64_t(r + 1) * conv_dim + c];
+  if (keep > 0) history[int64_t(keep - 1) * conv_dim + c] = x;
+}
+
+cudaError_t launch_conv_step(const float* qkv, const float* weight, float* history, float* out, int conv_dim,
+                             int kernel, cudaStream_t stream) {
+  conv_step_kernel<<<(conv_dim + 255) / 256, 256, 0, stream>>>(qkv, weight, history, out, conv_dim, kernel);
+  return cudaGetLastError();
+}
+
+}  // namespace sgk

@@ -47,6 +47,20 @@ class Rope(C.Structure):
                 ("position_scale", C.c_float), ("eps", C.c_float), ("interleaved", C.c_int32)]
 
 
+def encode_gated_delta_step_batch(states, layer, shape, d_q, d_k, d_v, d_g, d_beta, d_out, stream=None):
+    """One gated-delta token for several sequences in one launch; inputs are [len(states)][...]."""
+    arr = (C.c_void_p * len(states))(*[s.h for s in states])
+    sh = LinearShape(*shape)
+    check(_ffi.lib().sgk_linstate_enqueue_gated_delta_step_batch(arr, len(states), stream, layer, C.byref(sh), d_q.ptr,
+                                                                 d_k.ptr, d_v.ptr, d_g.ptr, d_beta.ptr, d_out.ptr))
+
+
+class LinearShape(C.Structure):
+    """sgk_linear_shape."""
+    _fields_ = [("num_key_heads", C.c_int32), ("num_value_heads", C.c_int32), ("key_head_dim", C.c_int32),
+                ("value_head_dim", C.c_int32)]
+
+
 def make_rope(rope_dims, theta, eps=1e-6, frequency_dim=None, position_scale=1.0, interleaved=False) -> Rope:
     return Rope(rope_dims, rope_dims if frequency_dim is None else frequency_dim, theta, position_scale, eps,
                 1 if interleaved else 0)
@@ -484,3 +498,14 @@ class LinearAttentionState:
 
     def restore(self, snapshot, stream=None):
         check(self.L.sgk_linstate_restore(self.h, stream, snapshot.h))
+
+    def encode_conv_step(self, layer, d_qkv, d_weight, conv_dim, conv_kernel_dim, d_out, stream=None):
+        """depthwise_causal_conv for one token (src/linear_attention.rs:802-852)."""
+        check(self.L.sgk_linstate_enqueue_conv_step(self.h, stream, layer, d_qkv.ptr, d_weight.ptr, conv_dim,
+                                                    conv_kernel_dim, d_out.ptr))
+
+    def encode_gated_delta_step(self, layer, shape, d_q, d_k, d_v, d_g, d_beta, d_out, stream=None):
+        """gated_delta for one token (src/linear_attention.rs:896-991); shape = (H_k, H_v, d_k, d_v)."""
+        sh = LinearShape(*shape)
+        check(self.L.sgk_linstate_enqueue_gated_delta_step(self.h, stream, layer, C.byref(sh), d_q.ptr, d_k.ptr,
+                                                           d_v.ptr, d_g.ptr, d_beta.ptr, d_out.ptr))

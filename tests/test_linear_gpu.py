@@ -1,0 +1,184 @@
+"""GPU parity of the one-token Gated DeltaNet and depthwise-conv steps on the linear-attention
+state, through the C ABI, against the oracle. Tolerances are the reference's for its own Metal
+kernels against its CPU path: 1e-5 for f32 state and output, 5e-4 / 2e-4 for output / state with a
+bf16 state (or one bf16 rounding step, where the stored value is large enough for a step to exceed 2e-4) (src/metal_backend/tests/linear_attention.rs:200-201,322-330). The conv step keeps the
+CPU's summation order and is bit-exact."""
+import numpy as np
+import pytest
+
+import saragossa_b200 as sg
+from oracle import sgo
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def state():
+    st = sg.DecodeResidentState(0)
+    yield st
+    assert st.device_status() == 0
+    st.close()
+
+
+def _inputs(shape, seed, t):
+    hk, hv, dk, dv = shape
+    q = sgo.fill_normal8(hk * dk, seed, 5 * t) / np.float32(dk)
+    k = sgo.fill_normal8(hk * dk, seed, 5 * t + 1) / np.float32(np.sqrt(dk))
+    v = sgo.fill_normal8(hv * dv, seed, 5 * t + 2)
+    u = sgo.fill_normal8(2 * hv, seed, 5 * t + 3)
+    g = (np.float32(0.95) + np.float32(0.01) * np.clip(u[:hv], -4, 4)).astype(np.float32)
+    beta = (np.float32(0.5) + np.float32(0.1) * np.clip(u[hv:], -3.9, 3.9)).astype(np.float32)
+    return q, k, v, g, beta
+
+
+@pytest.mark.parametrize("shape", [(2, 4, 8, 6), (1, 4, 128, 128), (16, 32, 128, 128), (2, 6, 96, 40), (1, 2, 256, 16)])
+@pytest.mark.parametrize("ssm_bf16", [False, True])
+def test_gated_delta_steps_match_the_oracle(state, shape, ssm_bf16):
+    hk, hv, dk, dv = shape
+    layers, layer, steps = 2, 1, 6
+    ssm_len = hv * dv * dk
+    ls = sg.LinearAttentionState(state, layers, 0, ssm_len, ssm_bf16=ssm_bf16)
+    ref = sgo.fill_normal8(ssm_len, 11, 0) * np.float32(0.1)
+    if ssm_bf16:
+        ref = sgo.bf16_round(ref)
+    other = sgo.fill_normal8(ssm_len, 11, 1)
+    if ssm_bf16:
+        other = sgo.bf16_round(other)
+    ls.write(layer, np.zeros(0, np.float32), ref)
+    ls.write(0, np.zeros(0, np.float32), other)
+    d_out = state.alloc(4 * hv * dv)
+    y_tol, s_tol = (5e-4, 2e-4) if ssm_bf16 else (1e-5, 1e-5)
+    for t in range(steps):
+        q, k, v, g, beta = _inputs(shape, 23, t)
+        bufs = [state.upload(a) for a in (q, k, v, g, beta)]
+        ls.encode_gated_delta_step(layer, shape, *bufs, d_out)
+        st, y_ref, ref = sgo.gated_delta_step(q, k, v, g, beta, hk, hv, dk, dv, ref)
+        assert st == sgo.OK
+        if ssm_bf16:
+            ref = sgo.bf16_round(ref)
+        state.sync()
+        np.testing.assert_allclose(d_out.download(count=hv * dv), y_ref, rtol=0, atol=y_tol)
+        _, got = ls.read(layer)
+        if ssm_bf16:
+            # stored values agree to the reference's tolerance, or sit one bf16 step apart where
+            # the last bit of a sum moved the rounding (a step is 2^-8 relative at most)
+            diff = np.abs(got - ref)
+            bad = np.nonzero(diff > np.maximum(s_tol, np.abs(ref) * 2.0 ** -7))[0]
+            assert bad.size == 0, (t, bad[:8], got[bad[:8]], ref[bad[:8]])
+            assert np.mean(got != ref) < 0.02
+            ref = got  # follow the device so the next step compares one update, not drift
+        else:
+            np.testing.assert_allclose(got, ref, rtol=0, atol=s_tol)
+    _, untouched = ls.read(0)
+    np.testing.assert_array_equal(untouched, other)
+    ls.close()
+
+
+def test_gated_delta_rejects_what_the_reference_rejects(state):
+    ls = sg.LinearAttentionState(state, 1, 0, 4 * 6 * 8)
+    z = state.alloc(4096)
+    with pytest.raises(sg.InferError) as e:  # value heads not a multiple of key heads
+        ls.encode_gated_delta_step(0, (3, 4, 8, 6), z, z, z, z, z, z)
+    assert e.value.kind == "Dimension"
+    with pytest.raises(sg.InferError) as e:  # state length does not match the shape
+        ls.encode_gated_delta_step(0, (2, 4, 8, 7), z, z, z, z, z, z)
+    assert e.value.kind == "Dimension"
+    with pytest.raises(sg.InferError) as e:
+        ls.encode_gated_delta_step(1, (2, 4, 8, 6), z, z, z, z, z, z)
+    assert e.value.kind == "Dimension"
+    with pytest.raises(sg.InferError) as e:
+        ls.encode_conv_step(0, z, z, 16, 4, z)  # no conv history of that size
+    assert e.value.kind == "Dimension"
+    ls.close()
+
+
+@pytest.mark.parametrize("conv_dim,kernel", [(10, 4), (8192, 4), (777, 2), (64, 1)])
+def test_conv_steps_are_bit_exact_and_slide_the_history(state, conv_dim, kernel):
+    layers, layer, steps = 2, 0, 7
+    conv_len = (kernel - 1) * conv_dim
+    ls = sg.LinearAttentionState(state, layers, conv_len, 8)
+    hist = sgo.fill_normal8(conv_len, 5, 0)
+    ls.write(layer, hist, np.zeros(8, np.float32))
+    w = sgo.fill_normal8(conv_dim * kernel, 5, 1)
+    d_w, d_out = state.upload(w), state.alloc(4 * conv_dim)
+    for t in range(steps):
+        x = sgo.fill_normal8(conv_dim, 6, t)
+        ls.encode_conv_step(layer, state.upload(x), d_w, conv_dim, kernel, d_out)
+        st, o_ref, hist = sgo.depthwise_conv_step(x, w, kernel, hist)
+        assert st == sgo.OK
+        state.sync()
+        np.testing.assert_array_equal(d_out.download(count=conv_dim), o_ref)
+        got, _ = ls.read(layer)
+        np.testing.assert_array_equal(got, hist)
+    ls.close()
+
+
+def test_recurrent_state_survives_a_prefix_snapshot_between_steps(state):
+    # the warm-prefix flow on a hybrid model: advance, snapshot, advance, restore, advance again:
+    # the replay from the snapshot reproduces the first continuation bit for bit
+    shape = (2, 4, 128, 64)
+    hk, hv, dk, dv = shape
+    conv_dim, kernel = 2 * hk * dk + hv * dv, 4
+    ls = sg.LinearAttentionState(state, 1, (kernel - 1) * conv_dim, hv * dv * dk)
+    d_out, d_cout = state.alloc(4 * hv * dv), state.alloc(4 * conv_dim)
+    d_w = state.upload(sgo.fill_normal8(conv_dim * kernel, 9, 9))
+
+    def advance(t):
+        q, k, v, g, beta = _inputs(shape, 31, t)
+        ls.encode_conv_step(0, state.upload(sgo.fill_normal8(conv_dim, 32, t)), d_w, conv_dim, kernel, d_cout)
+        ls.encode_gated_delta_step(0, shape, *[state.upload(a) for a in (q, k, v, g, beta)], d_out)
+        state.sync()
+        return d_out.download(count=hv * dv), d_cout.download(count=conv_dim)
+
+    for t in range(3):
+        advance(t)
+    snap = ls.snapshot()
+    first = [advance(t) for t in range(3, 6)]
+    end_conv, end_ssm = ls.read(0)
+    ls.restore(snap)
+    again = [advance(t) for t in range(3, 6)]
+    for (y0, c0), (y1, c1) in zip(first, again):
+        np.testing.assert_array_equal(y0, y1)
+        np.testing.assert_array_equal(c0, c1)
+    conv2, ssm2 = ls.read(0)
+    np.testing.assert_array_equal(conv2, end_conv)
+    np.testing.assert_array_equal(ssm2, end_ssm)
+    snap.close()
+    ls.close()
+
+
+@pytest.mark.parametrize("ssm_bf16", [False, True])
+def test_batched_gated_delta_equals_one_launch_per_sequence(state, ssm_bf16):
+    # the batch launch (four rows per warp at this size) and the single-sequence launch (one row
+    # per warp) do the same arithmetic per row: identical bits per sequence
+    shape, n = (16, 32, 128, 128), 5
+    hk, hv, dk, dv = shape
+    ssm_len = hv * dv * dk
+    solo = [sg.LinearAttentionState(state, 1, 0, ssm_len, ssm_bf16=ssm_bf16) for _ in range(n)]
+    both = [sg.LinearAttentionState(state, 1, 0, ssm_len, ssm_bf16=ssm_bf16) for _ in range(n)]
+    inits = []
+    for i in range(n):
+        init = sgo.fill_normal8(ssm_len, 40, i) * np.float32(0.1)
+        inits.append(sgo.bf16_round(init) if ssm_bf16 else init)
+        solo[i].write(0, np.zeros(0, np.float32), init)
+        both[i].write(0, np.zeros(0, np.float32), init)
+    ins = [_inputs(shape, 41 + i, 0) for i in range(n)]
+    stacked = [state.upload(np.stack([ins[i][j] for i in range(n)])) for j in range(5)]
+    d_out = state.alloc(4 * n * hv * dv)
+    sg.encode_gated_delta_step_batch(both, 0, shape, *stacked, d_out)
+    state.sync()
+    y_batch = d_out.download(count=n * hv * dv).reshape(n, -1)
+    d_one = state.alloc(4 * hv * dv)
+    for i in range(n):
+        solo[i].encode_gated_delta_step(0, shape, *[state.upload(a) for a in ins[i]], d_one)
+        state.sync()
+        np.testing.assert_array_equal(y_batch[i], d_one.download(count=hv * dv))
+        np.testing.assert_array_equal(both[i].read(0)[1], solo[i].read(0)[1])
+        st, y_ref, _ = sgo.gated_delta_step(*ins[i], hk, hv, dk, dv, inits[i])
+        assert st == sgo.OK
+        np.testing.assert_allclose(y_batch[i], y_ref, rtol=0, atol=5e-4 if ssm_bf16 else 1e-5)
+    with pytest.raises(sg.InferError) as e:
+        sg.encode_gated_delta_step_batch(both * 13, 0, shape, *stacked, d_out)  # 65 states
+    assert e.value.kind == "Config"
+    for s in solo + both:
+        s.close()
