@@ -148,6 +148,13 @@ typedef struct {
 } sgk_rope;
 int32_t sgk_kv_enqueue_rope_append(sgk_kv* kv, void* stream, const float* d_k_raw, const float* d_v,
                                    const float* d_knorm_weight, const sgk_rope* rope);
+/* The prefill-side producer: n_rows raw K rows [n_rows][kv_dim] are normalised, rotated at
+ * positions len .. len+n_rows-1, rounded to the storage type and written straight into the pages,
+ * V beside them, in ONE launch. Replaces rms_norm_rope_heads_at over the prompt
+ * (src/decoder/attention_ops.rs:682-777) + append_batch + the read-back and re-upload of seed
+ * (src/decoder/generation.rs:3338-3361, src/decode_resident/attention.rs:550-602). */
+int32_t sgk_kv_enqueue_rope_append_rows(sgk_kv* kv, void* stream, const float* d_k_raw, const float* d_v,
+                                        int64_t n_rows, const float* d_knorm_weight, const sgk_rope* rope);
 /* DecodeResidentState::rms_norm_rope_decode (attention.rs:386-444): host in/out. */
 int32_t sgk_rms_norm_rope_decode(sgk_state* state, const float* x, const float* weight,
                                  int32_t heads, int32_t head_dim, const sgk_rope* rope,

@@ -456,6 +456,18 @@ int32_t sgk_kv_enqueue_rope_append(sgk_kv* kv, void* stream, const float* d_k_ra
   return kv->self_batch->enqueue_append(kv->st->pick(stream), d_k_raw, d_v, 1, &r, d_knorm_weight);
 }
 
+int32_t sgk_kv_enqueue_rope_append_rows(sgk_kv* kv, void* stream, const float* d_k_raw, const float* d_v,
+                                        int64_t n_rows, const float* d_knorm_weight, const sgk_rope* rope) {
+  if (!kv) return fail(SGK_ERR_BACKEND, "null KV state");
+  if (!d_knorm_weight) return fail(SGK_ERR_BACKEND, "null norm weight");
+  if (n_rows < 0 || n_rows > INT32_MAX) return fail(SGK_ERR_DIMENSION, "append rows: n_rows %lld invalid", (long long)n_rows);
+  if (n_rows == 0) return SGK_OK;
+  RopeArgs r;
+  SGK_TRY(check_rope(rope, kv->pool()->head_dim, &r));
+  SGK_TRY(kv->ensure_self_batch());
+  return kv->self_batch->enqueue_append(kv->st->pick(stream), d_k_raw, d_v, int(n_rows), &r, d_knorm_weight);
+}
+
 int32_t sgk_rms_norm_rope_decode(sgk_state* st, const float* x, const float* weight, int32_t heads, int32_t head_dim,
                                  const sgk_rope* rope, int64_t position, float* out) {
   if (!st || !x || !weight || !out) return fail(SGK_ERR_BACKEND, "null argument");

@@ -4,24 +4,26 @@
 // Same pipeline as the bf16 kernel (producer warp, one bulk async copy per page into a
 // shared-memory ring, consumer warps, two-level split merge); what differs is the math
 // of a page. The codes are never expanded element by element: a byte b becomes the fp16
-// number 1024 + b with ONE byte-permute (0x6400 | b), two codes per instruction, and the
-// affine metadata is applied around the tensor-core products:
+// subnormal b * 2^-24 with ONE byte-permute (the byte dropped into the low mantissa bits of a
+// zero half), two codes per instruction and exactly, and the affine metadata is applied
+// around the tensor-core products:
 //
-//   scores   s[row][h] = sum_g scale_k[row][g] * (sum_{d in g} q[h][d] * (1024 + code))
-//                              + (bias_k[row][g] - 1024 * scale_k[row][g]) * qsum[h][g]
+//   scores   s[row][h] = 2^24 * sum_g scale_k[row][g] * (sum_{d in g} q[h][d] * code * 2^-24)
+//                              + sum_g bias_k[row][g] * qsum[h][g]
 //            one m16n8k16 fp16 product per 16 dims, one accumulator per group of 32, the
 //            per-(row, group) scale applied to the accumulator in f32;
 //   outputs  O[d][h]  += sum_row code[row][d] * (scale_v[row][g(d)] * p[row][h])   (tensor core,
-//            the scale folded into the B operand of the group, codes exact after an fp16
-//            subtract of 1024)  +  sum_row bias_v[row][g(d)] * p[row][h]  (f32, per thread,
-//            reduced over the warp once at the end).
+//            the scale folded into the B operand of the group)
+//            +  sum_row bias_v[row][g(d)] * p[row][h]  (f32, per thread, reduced over the warp
+//            once at the end).
 //
 // The weights p * scale_v are multiplied by a power of two chosen from the largest scale
 // the pool has ever stored (kept by the append kernels in PoolView::scale_max, and raised
 // by the row a fused append is about to write), so they sit in the middle of the fp16
 // range whatever the data; the accumulators are divided by it at the end.
-// q is split into fp16 hi + lo parts (22 significant bits). Layouts: see layout.h
-// (K codes row-major with the bank swizzle, V codes transposed [dim][row slot]).
+// q is split into fp16 hi + lo parts (22 significant bits).
+// Layouts: see layout.h (K codes row-major with the bank swizzle, V codes transposed
+// [dim][row slot]).
 //
 // The reference has no u8 KV; this kernel computes cached_attention_one
 // (src/decoder/attention_ops.rs:889-974) over the dequantised rows q*scale+bias
@@ -37,24 +39,21 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1,
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-// two bytes of w -> the fp16 pair (1024 + byte_lo, 1024 + byte_hi)
-__device__ __forceinline__ uint32_t codes_lo(uint32_t w) { return __byte_perm(w, 0x64646464u, 0x5140); }
-__device__ __forceinline__ uint32_t codes_hi(uint32_t w) { return __byte_perm(w, 0x64646464u, 0x5342); }
-__device__ __forceinline__ uint32_t sub1024(uint32_t h2) {
-  __half2 v = *reinterpret_cast<__half2*>(&h2);
-  v = __hsub2(v, __half2half2(__ushort_as_half(0x6400)));
-  return *reinterpret_cast<uint32_t*>(&v);
-}
-__device__ __forceinline__ uint32_t pack_f16(float x0, float x1) {
-  __half2 v = __floats2half2_rn(x0, x1);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
+// two bytes of w -> the fp16 pair (byte_lo, byte_hi) * 2^-24: a byte in the low mantissa bits of
+// an fp16 with a zero exponent field is the subnormal byte * 2^-24, exactly
+__device__ __forceinline__ uint32_t codes_lo(uint32_t w) { return __byte_perm(w, 0u, 0x4140); }
+__device__ __forceinline__ uint32_t codes_hi(uint32_t w) { return __byte_perm(w, 0u, 0x4342); }
+constexpr float CODE_UNIT_INV = 16777216.0f;  // 2^24
 // x -> fp16 hi (nearest) and fp16 lo = nearest(x - hi)
 __device__ __forceinline__ void split_f16(float x, uint16_t& hi, uint16_t& lo) {
   __half h = __float2half_rn(x);
   __half l = __float2half_rn(x - __half2float(h));
   hi = __half_as_ushort(h);
   lo = __half_as_ushort(l);
+}
+__device__ __forceinline__ uint32_t pack_f16(float x0, float x1) {
+  __half2 v = __floats2half2_rn(x0, x1);
+  return *reinterpret_cast<uint32_t*>(&v);
 }
 
 template <int HD>
@@ -174,7 +173,8 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
     }
     if (lane < my_pages) first_entry = table[pb + lane];
   } else {
-    // Q of the group: scaled, fp16 hi/lo, rows of absent heads zero.
+    // Q of the group: scaled, fp16 hi/lo, rows of absent heads zero. One fp16 alone (11 bits)
+    // would put an error of |logit| * 2^-12 on every logit, too much for rows with a large range.
     constexpr int NV = HD / 64;
     const float* q = a.q + (int64_t(seq) * a.q_heads + int64_t(kvh) * gqa) * HD;
     float4 v[NV];
@@ -248,7 +248,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
     int e = static_cast<int>((__float_as_uint(smax) >> 23) & 0xffu) - 127;
     e = max(-60, min(60, e));
     const float pscale = exp2f(static_cast<float>(10 - e));
-    const float inv_pscale = exp2f(static_cast<float>(e - 10));
+    const float inv_pscale = exp2f(static_cast<float>(e - 10)) * CODE_UNIT_INV;
 
     float o_acc[KSTEPS][4];
 #pragma unroll
@@ -305,7 +305,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
         //      tensor-core instructions have a long latency and issue in order, so products
         //      that do not depend on each other are issued back to back: all groups for one
         //      half of their dims and the hi part of Q, then the lo part, then the other half. ----
-        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        float s[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
         const uint8_t* kmeta = ktile + S::CODES;
         float acc[G][4];
 #pragma unroll
@@ -341,13 +341,14 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
           const uint32_t mk1 = *reinterpret_cast<const uint32_t*>(kmeta + ((g + 8) * G + grp) * 4);
           const float sc0 = __uint_as_float(mk0 << 16), bi0 = __uint_as_float(mk0 & 0xffff0000u);
           const float sc1 = __uint_as_float(mk1 << 16), bi1 = __uint_as_float(mk1 & 0xffff0000u);
-          const float adj0 = fmaf(-1024.0f, sc0, bi0), adj1 = fmaf(-1024.0f, sc1, bi1);
           const float qs0 = qsum_s[(2 * t) * G + grp], qs1 = qsum_s[(2 * t + 1) * G + grp];
-          s[0] += sc0 * acc[grp][0] + adj0 * qs0;
-          s[1] += sc0 * acc[grp][1] + adj0 * qs1;
-          s[2] += sc1 * acc[grp][2] + adj1 * qs0;
-          s[3] += sc1 * acc[grp][3] + adj1 * qs1;
+          s[0] = fmaf(sc0, acc[grp][0], s[0]), sb[0] = fmaf(bi0, qs0, sb[0]);
+          s[1] = fmaf(sc0, acc[grp][1], s[1]), sb[1] = fmaf(bi0, qs1, sb[1]);
+          s[2] = fmaf(sc1, acc[grp][2], s[2]), sb[2] = fmaf(bi1, qs0, sb[2]);
+          s[3] = fmaf(sc1, acc[grp][3], s[3]), sb[3] = fmaf(bi1, qs1, sb[3]);
         }
+#pragma unroll
+        for (int r = 0; r < 4; ++r) s[r] = fmaf(s[r], CODE_UNIT_INV, sb[r]);  // the codes were in units of 2^-24
         if (row_base < ws || row_base + PAGE_TOKENS > len) {
           int64_t ra = row_base + g, rb = row_base + g + 8;
           if (ra < ws || ra >= len) s[0] = s[1] = -1.0e30f;
@@ -405,8 +406,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
         for (int j = 0; j < KSTEPS; ++j) {
           const uint32_t w0 = *reinterpret_cast<const uint32_t*>(vtile + (16 * j + g) * PAGE_TOKENS + 4 * t);
           const uint32_t w1 = *reinterpret_cast<const uint32_t*>(vtile + (16 * j + g + 8) * PAGE_TOKENS + 4 * t);
-          mma_f16(o_acc[j], sub1024(codes_lo(w0)), sub1024(codes_lo(w1)), sub1024(codes_hi(w0)),
-                  sub1024(codes_hi(w1)), pb0[j / 2], pb1[j / 2]);
+          mma_f16(o_acc[j], codes_lo(w0), codes_lo(w1), codes_hi(w0), codes_hi(w1), pb0[j / 2], pb1[j / 2]);
         }
       }
       __syncwarp();

@@ -64,6 +64,8 @@ class BlockAwarePrefixCache:
         check(self.L.sgk_prefix_create(pool.h if pool is not None else None, block_tokens, capacity, per,
                                        budget_bytes, C.byref(h)))
         self.h = h
+        if pool is not None and pool.state is not None:
+            pool.state._adopt(self)
 
     def close(self):
         if getattr(self, "h", None):

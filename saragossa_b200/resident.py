@@ -11,6 +11,7 @@ there is no computation in Python.
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 
 import numpy as np
 
@@ -75,6 +76,7 @@ class DeviceBuffer:
         p = C.c_void_p()
         check(state.L.sgk_util_malloc(state.h, self.nbytes, C.byref(p)))
         self.ptr = p.value
+        state._adopt(self)
 
     def upload(self, array: np.ndarray) -> "DeviceBuffer":
         a = np.ascontiguousarray(array)
@@ -109,9 +111,25 @@ class DecodeResidentState:
         check(self.L.sgk_state_create(device, C.byref(h)))
         self.h = h
         self.device = device
+        self._children = []
+
+    def _adopt(self, child):
+        """Objects made from this state are closed with it (newest first): a handle that
+        outlives its state must never reach the library."""
+        self._children.append(weakref.ref(child))
+        if len(self._children) > 4096:
+            self._children = [r for r in self._children if r() is not None]
 
     def close(self):
         if getattr(self, "h", None):
+            for ref in reversed(self._children):
+                child = ref()
+                if child is not None:
+                    try:
+                        (child.free if isinstance(child, DeviceBuffer) else child.close)()
+                    except Exception:
+                        pass
+            self._children = []
             self.L.sgk_state_destroy(self.h)
             self.h = None
 
@@ -184,6 +202,8 @@ class PagePool:
                                      PAGE_TOKENS, num_pages, max_seqs, max_seq_tokens, C.byref(h)))
         self.h = h
         self.layers, self.kv_heads, self.head_dim, self.dtype = layers, kv_heads, head_dim, dtype
+        if state is not None:
+            state._adopt(self)
 
     def close(self):
         if getattr(self, "h", None):
@@ -217,6 +237,8 @@ class Sequence:
         h = C.c_void_p()
         check(self.L.sgk_seq_create(pool.h, capacity_tokens, C.byref(h)))
         self.h = h
+        if pool.state is not None:
+            pool.state._adopt(self)
 
     def close(self):
         if getattr(self, "h", None):
@@ -250,6 +272,8 @@ class FullAttentionState:
         self.L = _ffi.lib()
         self.h = handle
         self.owned = owned
+        if state is not None:
+            state._adopt(self)
 
     def close(self):
         if self.owned and getattr(self, "h", None):
@@ -310,6 +334,11 @@ class FullAttentionState:
 
     def encode_rope_append(self, d_k_raw, d_v, d_weight, rope: Rope, stream=None):
         check(self.L.sgk_kv_enqueue_rope_append(self.h, stream, d_k_raw.ptr, d_v.ptr, d_weight.ptr, C.byref(rope)))
+
+    def encode_rope_append_rows(self, d_k_raw, d_v, n_rows, d_weight, rope: Rope, stream=None):
+        """Prefill producer: n_rows raw K rows normalised, rotated and stored at rows len.. in one launch."""
+        check(self.L.sgk_kv_enqueue_rope_append_rows(self.h, stream, d_k_raw.ptr, d_v.ptr, n_rows, d_weight.ptr,
+                                                     C.byref(rope)))
 
     def attention_decode(self, q, attn_scalar=0.0):
         return self.attention_decode_windowed(q, 0, attn_scalar)
@@ -388,6 +417,7 @@ class Batch:
         h = C.c_void_p()
         check(self.L.sgk_batch_create(state.h, arr, len(self.kvs), C.byref(h)))
         self.h = h
+        state._adopt(self)
 
     def close(self):
         if getattr(self, "h", None):
@@ -430,6 +460,7 @@ class Step:
         h = C.c_void_p()
         check(self.L.sgk_step_create(state.h, arr, len(self.batches), C.byref(h)))
         self.h = h
+        state._adopt(self)
 
     def close(self):
         if getattr(self, "h", None):
@@ -472,6 +503,7 @@ class LinearAttentionState:
             check(self.L.sgk_linstate_create(state.h, layers, conv_len, ssm_len, int(ssm_bf16), C.byref(handle)))
         self.h = handle
         self.layers, self.conv_len, self.ssm_len, self.ssm_bf16 = layers, conv_len, ssm_len, ssm_bf16
+        state._adopt(self)
 
     def close(self):
         if getattr(self, "h", None):

@@ -364,6 +364,47 @@ def test_fused_rope_append_matches_cpu_path(state, dtype):
     kv.close()
 
 
+@pytest.mark.parametrize("dtype", [sg.KV_F32, sg.KV_BF16, sg.KV_U8G32])
+def test_prefill_producer_equals_row_by_row_fused_append(state, dtype):
+    """A prompt's K rows through ONE multi-row launch land in the pages with the same bits as the
+    same rows appended one decode step at a time (the reference's multi-row appends are serial
+    single-row appends, src/decoder/attention_ops.rs:976-1017), across page boundaries and on top
+    of rows that are already there; and both match the CPU order of operations."""
+    kv_heads, hd, rope_dims, theta = 2, 128, 128, 10_000.0
+    kv_dim = kv_heads * hd
+    rope = sg.make_rope(rope_dims, theta, eps=1e-6)
+    w = np.float32(0.9) + np.abs(sgo.pseudo(11, hd))
+    d_w = state.upload(w)
+    first, rest = 21, 300
+    n = first + rest
+    k_raw = sgo.fill_normal8(n * kv_dim, 8, 0).reshape(n, kv_dim)
+    v = sgo.fill_normal8(n * kv_dim, 8, 1).reshape(n, kv_dim)
+    bulk = state.full_attention(n + 3, 4, kv_heads, hd, dtype)
+    bulk.encode_rope_append_rows(state.upload(k_raw[:first]), state.upload(v[:first]), first, d_w, rope)
+    bulk.encode_rope_append_rows(state.upload(k_raw[first:]), state.upload(v[first:]), rest, d_w, rope)
+    serial = state.full_attention(n + 3, 4, kv_heads, hd, dtype)
+    for r in range(n):
+        serial.encode_rope_append(state.upload(k_raw[r]), state.upload(v[r]), d_w, rope)
+    state.sync()
+    assert bulk.len() == serial.len() == n
+    bk, bv = bulk.gather_rows_f32()
+    sk, sv = serial.gather_rows_f32()
+    assert np.array_equal(bk, sk) and np.array_equal(bv, sv)
+    _, k_ref = sgo.rms_norm_rope_heads_at(k_raw, kv_heads, hd, rope_dims, w, 1e-6, theta, rope_dims, 1.0, 0)
+    ref = sgo.ResidentKv(n + 3, 4, kv_heads, hd, dtype)
+    ref.seed(k_ref.ravel(), v.ravel(), n)
+    assert np.array_equal(bv, ref.values())
+    assert np.mean(bk == ref.keys()) > 0.99
+    step = {sg.KV_F32: 1e-5, sg.KV_U8G32: 0.05}.get(dtype)
+    bound = step if step is not None else 2.0 ** -7 * np.maximum(np.abs(ref.keys()), 1e-3)
+    assert np.all(np.abs(bk - ref.keys()) <= bound)
+    with pytest.raises(sg.InferError) as e:                    # overflow at capacity writes nothing
+        bulk.encode_rope_append_rows(state.upload(k_raw[:4]), state.upload(v[:4]), 4, d_w, rope)
+    assert e.value.kind == "Dimension" and bulk.len() == n
+    bulk.close()
+    serial.close()
+
+
 # ---- long context, paged, batched: against the oracle on seeded normal inputs ------------------
 def _normal_kv(n, kv_dim, seed, stream):
     return sgo.fill_normal8(n * kv_dim, seed, stream).reshape(n, kv_dim)
