@@ -32,10 +32,9 @@ __device__ __forceinline__ float load_tile_elem(const uint8_t* tile, int dtype, 
   if (dtype == KV_F32) return reinterpret_cast<const float*>(tile)[row * hd + dim];
   if (dtype == KV_BF16)
     return bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(tile)[bf16_elem_index(row, dim, hd)]);
-  int idx = is_v ? u8_v_code_index(row, dim) : u8_k_code_index(row, dim, hd);
-  uint32_t meta = *reinterpret_cast<const uint32_t*>(tile + u8_meta_offset(row, dim / QGROUP, hd));
-  float scale = bf16_bits_to_f32(static_cast<uint16_t>(meta & 0xffffu));
-  float bias = bf16_bits_to_f32(static_cast<uint16_t>(meta >> 16));
+  int idx = is_v ? u8_v_code_index(row, dim, hd) : u8_k_code_index(row, dim, hd);
+  float scale = bf16_bits_to_f32(*reinterpret_cast<const uint16_t*>(tile + u8_scale_offset(row, dim / QGROUP, hd)));
+  float bias = bf16_bits_to_f32(*reinterpret_cast<const uint16_t*>(tile + u8_bias_offset(is_v, row, dim / QGROUP, hd)));
   return __fadd_rn(__fmul_rn(static_cast<float>(tile[idx]), scale), bias);
 }
 

@@ -90,10 +90,11 @@ __device__ void store_head_row(uint8_t* tile, int dtype, int hd, int is_v, int r
       int dim = g * QGROUP + lane;
       uint32_t meta;
       uint32_t code = quantize_group_warp(xs[dim], &meta);
-      int idx = is_v ? u8_v_code_index(row, dim) : u8_k_code_index(row, dim, hd);
+      int idx = is_v ? u8_v_code_index(row, dim, hd) : u8_k_code_index(row, dim, hd);
       tile[idx] = static_cast<uint8_t>(code);
       if (lane == 0) {
-        *reinterpret_cast<uint32_t*>(tile + u8_meta_offset(row, g, hd)) = meta;
+        *reinterpret_cast<uint16_t*>(tile + u8_scale_offset(row, g, hd)) = static_cast<uint16_t>(meta & 0xffffu);
+        *reinterpret_cast<uint16_t*>(tile + u8_bias_offset(is_v, row, g, hd)) = static_cast<uint16_t>(meta >> 16);
         // largest scale of the pool (positive floats order like their bit patterns)
         const uint32_t scale_f32_bits = (meta & 0xffffu) << 16;
         if (scale_max != nullptr && scale_f32_bits > *reinterpret_cast<volatile uint32_t*>(scale_max))

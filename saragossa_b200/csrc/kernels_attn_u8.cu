@@ -56,20 +56,40 @@ __device__ __forceinline__ uint32_t pack_f16(float x0, float x1) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+__device__ __forceinline__ void mma_bf16_k8(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+  asm("mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(b0));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float x0, float x1) {  // x0 in the low half
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(x1), "f"(x0));
+  return r;
+}
+__device__ __forceinline__ float bf16_lo_f32(uint32_t pair) { return __uint_as_float(pair << 16); }
+__device__ __forceinline__ float bf16_hi_f32(uint32_t pair) { return __uint_as_float(pair & 0xffff0000u); }
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+  __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
 template <int HD>
 struct U8Smem {
   static constexpr int G = HD / QGROUP;
-  static constexpr int CODES = PAGE_TOKENS * HD;          // bytes of K or V codes
-  static constexpr int TILE = CODES + PAGE_TOKENS * G * 4;  // + {scale, bias} pairs
+  static constexpr int CODES = PAGE_TOKENS * HD;            // bytes of K or V codes
+  static constexpr int SCALES = CODES;                      // bf16 [row][group]
+  static constexpr int BIASES = CODES + PAGE_TOKENS * G * 2;  // bf16, K [row][group], V [group][row]
+  static constexpr int TILE = CODES + PAGE_TOKENS * G * 4;
   static constexpr int STAGE = 2 * TILE;
   static constexpr int OPAD = HD + 4;
-  static constexpr int QROW = HD * 2 + 32;                // padded fp16 row of Q (bank spread)
+  static constexpr int QROW = HD * 2 + 64;                // fp16 row of Q, rows 64 bytes apart modulo 128
   static constexpr int Q_BYTES = 2 * 8 * QROW;            // hi and lo
-  static constexpr int QSUM_BYTES = 8 * G * 4;
+  static constexpr int QSUM_BYTES = 8 * 8 * 4;            // [head][8 groups], absent groups zero
   static constexpr int O_BYTES = MMA_CONSUMERS * 8 * OPAD * 4;
   static constexpr int ML_BYTES = 512;  // per-warp {max, sum}, then the merge weights and the block's {max, sum}
   static constexpr int BAR_BYTES = 2 * MMA_MAX_STAGES * 8;
-  static constexpr int FIXED = Q_BYTES + QSUM_BYTES + ML_BYTES + BAR_BYTES + 64;
+  static constexpr int NEW_BYTES = 2 * HD * 4;            // the K and V row of a fused append, f32
+  static constexpr int FIXED = Q_BYTES + QSUM_BYTES + ML_BYTES + BAR_BYTES + 64 + NEW_BYTES;
   __host__ __device__ static size_t ring_bytes(int stages) {
     size_t r = size_t(stages) * STAGE;
     return r > size_t(O_BYTES) ? r : size_t(O_BYTES);
@@ -77,43 +97,48 @@ struct U8Smem {
   static size_t total(int stages) { return ring_bytes(stages) + FIXED + 1024; }
 };
 
-// Largest scale (f32) of the 2*G groups of a row about to be appended; every lane gets it.
-template <int HD>
-__device__ __forceinline__ float new_row_max_scale(const float* kn, const float* vn, int lane) {
-  float best = 0.0f;
+// Quantises N groups of 32 values at once (lane l holds element l of every group), with the
+// arithmetic of the append kernel. The min/max butterflies of all groups run side by side:
+// one after the other they would each wait for their own five shuffle round trips.
+template <int N>
+__device__ __forceinline__ void quantize_groups(const float (&x)[N], uint32_t (&code)[N], uint32_t (&meta)[N]) {
+  float lo[N], hi[N];
 #pragma unroll
-  for (int g = 0; g < 2 * (HD / QGROUP); ++g) {
-    const float* src = g < HD / QGROUP ? kn + g * QGROUP : vn + (g - HD / QGROUP) * QGROUP;
-    float x = src[lane], lo = x, hi = x;
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-      lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, off));
-      hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, off));
-    }
-    float bias = bf16_bits_to_f32(f32_to_bf16_bits(lo));
-    float raw = __fdiv_rn(__fsub_rn(hi, bias), 255.0f);
-    best = fmaxf(best, bf16_bits_to_f32(f32_to_bf16_bits(fmaxf(raw, 0x1p-40f))));
-  }
-  return best;
-}
-
-// Quantises 32 values (one per lane), same arithmetic as the append kernel.
-__device__ __forceinline__ uint32_t quantize_lane(float x, uint32_t* meta_out) {
-  float lo = x, hi = x;
+  for (int i = 0; i < N; ++i) lo[i] = hi[i] = x[i];
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) {
-    lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, off));
-    hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, off));
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      lo[i] = fminf(lo[i], __shfl_xor_sync(0xffffffffu, lo[i], off));
+      hi[i] = fmaxf(hi[i], __shfl_xor_sync(0xffffffffu, hi[i], off));
+    }
   }
-  uint16_t bias_bits = f32_to_bf16_bits(lo);
-  float bias = bf16_bits_to_f32(bias_bits);
-  float raw = __fdiv_rn(__fsub_rn(hi, bias), 255.0f);
-  uint16_t scale_bits = f32_to_bf16_bits(fmaxf(raw, 0x1p-40f));
-  float scale = bf16_bits_to_f32(scale_bits);
-  float t = rintf(__fdiv_rn(__fsub_rn(x, bias), scale));
-  t = fminf(fmaxf(t, 0.0f), 255.0f);
-  *meta_out = static_cast<uint32_t>(scale_bits) | (static_cast<uint32_t>(bias_bits) << 16);
-  return static_cast<uint32_t>(t);
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    const uint16_t bias_bits = f32_to_bf16_bits(lo[i]);
+    const float bias = bf16_bits_to_f32(bias_bits);
+    const float raw = __fdiv_rn(__fsub_rn(hi[i], bias), 255.0f);
+    const uint16_t scale_bits = f32_to_bf16_bits(fmaxf(raw, 0x1p-40f));
+    const float scale = bf16_bits_to_f32(scale_bits);
+    float t = rintf(__fdiv_rn(__fsub_rn(x[i], bias), scale));
+    t = fminf(fmaxf(t, 0.0f), 255.0f);
+    meta[i] = static_cast<uint32_t>(scale_bits) | (static_cast<uint32_t>(bias_bits) << 16);
+    code[i] = static_cast<uint32_t>(t);
+  }
+}
+
+// The G bf16 scales of one row as f32, from one 16-byte (G = 8) or 8-byte (G = 4) load.
+template <int G>
+__device__ __forceinline__ void load_row_scales(const uint8_t* p, float (&sc)[G]) {
+  if (G == 8) {
+    const uint4 w = *reinterpret_cast<const uint4*>(p);
+    sc[0] = bf16_lo_f32(w.x), sc[1] = bf16_hi_f32(w.x), sc[2] = bf16_lo_f32(w.y), sc[3] = bf16_hi_f32(w.y);
+    sc[4 % G] = bf16_lo_f32(w.z), sc[5 % G] = bf16_hi_f32(w.z), sc[6 % G] = bf16_lo_f32(w.w),
+           sc[7 % G] = bf16_hi_f32(w.w);
+  } else {
+    const uint2 w = *reinterpret_cast<const uint2*>(p);
+    sc[0] = bf16_lo_f32(w.x), sc[1] = bf16_hi_f32(w.x), sc[2] = bf16_lo_f32(w.y), sc[3] = bf16_hi_f32(w.y);
+  }
 }
 
 template <int HD>
@@ -127,15 +152,30 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
   uint8_t* fixed = ring + S::ring_bytes(nst);
   uint8_t* q_hi = fixed;                          // [8] rows of QROW bytes (fp16)
   uint8_t* q_lo = fixed + 8 * S::QROW;
-  float* qsum_s = reinterpret_cast<float*>(fixed + S::Q_BYTES);                 // [8][G]
+  float* qsum_s = reinterpret_cast<float*>(fixed + S::Q_BYTES);                 // [8][8]
   float* o_s = reinterpret_cast<float*>(ring);    // aliases the ring once it has drained
   float* ml_s = reinterpret_cast<float*>(fixed + S::Q_BYTES + S::QSUM_BYTES);   // [warps][8][2]
   uint64_t* bars = reinterpret_cast<uint64_t*>(fixed + S::Q_BYTES + S::QSUM_BYTES + S::ML_BYTES);
   int* flags = reinterpret_cast<int*>(bars + 2 * MMA_MAX_STAGES);
+  float* new_s = reinterpret_cast<float*>(flags + 16);   // [K row | V row] of the append, staged once
+  float* new_big = reinterpret_cast<float*>(flags + 8);  // [consumer warp] max |x| of its part of that row
   volatile int* abort_flag = flags;
 
   const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef SGK_TRACE
+  if (tid == 0) {
+    SGK_TP(0);
+    if (a.trace) {
+      unsigned long long gt;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
+      a.trace[((size_t(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + 15] = gt;
+      unsigned smid;
+      asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+      a.trace[((size_t(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + 13] = smid;
+    }
+  }
+#endif
   const int gqa = a.q_heads / a.pool.kv_heads;
   const int slot = a.slots ? a.slots[seq] : a.slot0;
   int32_t* len_ptr = a.pool.lens + int64_t(slot) * a.pool.layers + a.layer;
@@ -155,8 +195,8 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
   const int64_t head_off = int64_t(a.layer) * a.pool.layer_bytes + int64_t(kvh) * 2 * a.pool.tile_bytes;
   const int64_t append_page_index = len_old / PAGE_TOKENS;
   const bool owns_append = do_append && append_page_index >= pb && append_page_index < pe;
-  const float* kn = do_append ? a.k_new + int64_t(seq) * a.pool.kv_heads * HD + kvh * HD : nullptr;
-  const float* vn = do_append ? a.v_new + int64_t(seq) * a.pool.kv_heads * HD + kvh * HD : nullptr;
+  const float* kn = new_s;
+  const float* vn = new_s + HD;
 
   int32_t first_entry = -1;
   float smax = __uint_as_float(*reinterpret_cast<const volatile uint32_t*>(a.pool.scale_max));
@@ -183,6 +223,20 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
       const int f = (tid + k * MMA_CONSUMERS * 32) * 4;
       v[k] = (f / HD < gqa) ? __ldg(reinterpret_cast<const float4*>(q + f)) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
+    // The row of a fused append comes into shared memory with the same round trip as Q: read
+    // where it is quantised, element by element, each read would pay the latency again.
+    if (owns_append && tid * 4 < 2 * HD) {
+      const int64_t row_off = int64_t(seq) * a.pool.kv_heads * HD + kvh * HD;
+      const float* src = tid * 4 < HD ? a.k_new + row_off + tid * 4 : a.v_new + row_off + (tid * 4 - HD);
+      const float4 x = __ldg(reinterpret_cast<const float4*>(src));
+      *reinterpret_cast<float4*>(new_s + tid * 4) = x;
+      // bound of the scales the row will get: (max - min) / 255 <= 2 max|x| / 255
+      float big = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, off));
+      if (lane == 0) new_big[warp] = big;
+    }
+    if (owns_append && tid == 0) flags[2] = table[append_page_index];
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int f = (tid + k * MMA_CONSUMERS * 32) * 4;
@@ -197,34 +251,54 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
       *reinterpret_cast<uint2*>(q_lo + h * S::QROW + d * 2) =
           make_uint2(uint32_t(lo[0]) | (uint32_t(lo[1]) << 16), uint32_t(lo[2]) | (uint32_t(lo[3]) << 16));
     }
-    // The row a fused append is about to write may carry a larger scale than any stored one.
-    if (owns_append) smax = fmaxf(smax, new_row_max_scale<HD>(kn, vn, lane));
   }
   __syncthreads();
+  // The row a fused append is about to write may carry a larger scale than any stored one.
+  if (owns_append) {
+    float big = new_big[0];
+#pragma unroll
+    for (int w = 1; w < MMA_CONSUMERS; ++w)
+      if (w * 32 * 4 < 2 * HD) big = fmaxf(big, new_big[w]);
+    smax = fmaxf(smax, big * (2.02f / 255.0f));   // 1 % above the bound covers the bf16 rounding of a scale
+  }
+  // qsum[h][g] = sum over the group of the fp16 value of q (hi + lo), as the tensor core sees it;
+  // each consumer thread keeps the two it feeds to the bias product, as three bf16 parts.
+  uint32_t qs_hi = 0, qs_mid = 0, qs_lo = 0;
   if (warp < MMA_CONSUMERS) {
-    // qsum[h][g] = sum over the group of the fp16 value of q (hi + lo), as the tensor core sees it
-    if (tid < 8 * G) {
-      const int h = tid / G, grp = tid % G;
-      const __half* ph = reinterpret_cast<const __half*>(q_hi + h * S::QROW) + grp * QGROUP;
-      const __half* pl = reinterpret_cast<const __half*>(q_lo + h * S::QROW) + grp * QGROUP;
+    if (tid < 64) {
+      const int h = tid >> 3, grp = tid & 7;
       float sum = 0.0f;
-      for (int d = 0; d < QGROUP; ++d) sum += __half2float(ph[d]) + __half2float(pl[d]);
-      qsum_s[h * G + grp] = sum;
+      if (grp < G) {
+        const __half2* ph = reinterpret_cast<const __half2*>(q_hi + h * S::QROW) + grp * (QGROUP / 2);
+        const __half2* pl = reinterpret_cast<const __half2*>(q_lo + h * S::QROW) + grp * (QGROUP / 2);
+#pragma unroll
+        for (int d = 0; d < QGROUP / 2; ++d) {
+          const float2 x = __half22float2(ph[d]), y = __half22float2(pl[d]);
+          sum += (x.x + y.x) + (x.y + y.y);
+        }
+      }
+      qsum_s[h * 8 + grp] = sum;
     }
     asm volatile("bar.sync 1, %0;" ::"r"(MMA_CONSUMERS * 32) : "memory");
+    // B fragment of the bias product: (k = groups 2t, 2t+1; n = head g)
+    const float2 qs = *reinterpret_cast<const float2*>(qsum_s + (lane >> 2) * 8 + 2 * (lane & 3));
+    qs_hi = pack_bf16(qs.x, qs.y);
+    const float r0 = qs.x - bf16_lo_f32(qs_hi), r1 = qs.y - bf16_hi_f32(qs_hi);
+    qs_mid = pack_bf16(r0, r1);
+    qs_lo = pack_bf16(r0 - bf16_lo_f32(qs_mid), r1 - bf16_hi_f32(qs_mid));
   }
+  if (tid == 0) SGK_TP(1);
 
   if (warp == MMA_CONSUMERS) {
     // ---------------- producer warp ----------------
+    int stage = 0;
+    uint32_t parity = 1;
     for (int base = 0; base < my_pages; base += 32) {
       int idx = base + lane;
       int32_t entry = base == 0 ? first_entry : (idx < my_pages ? table[pb + idx] : -1);
       int cnt = min(32, my_pages - base);
       for (int j = 0; j < cnt; ++j) {
-        int i = base + j;
         int32_t page = __shfl_sync(0xffffffffu, entry, j);
-        int stage = i % nst;
-        uint32_t parity = ((i / nst) & 1) ^ 1;
         if (lane == 0) {
           bool ok = mbar_wait(smem_u32(bars + MMA_MAX_STAGES + stage), parity, abort_flag, a.status);
           if (ok && (page < 0 || page >= a.num_pages)) {
@@ -238,6 +312,10 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
             bulk_copy_g2s(smem_u32(ring + size_t(stage) * S::STAGE),
                           a.pool.base + int64_t(page) * a.pool.page_bytes + head_off, S::STAGE, full);
           }
+        }
+        if (++stage == nst) {
+          stage = 0;
+          parity ^= 1;
         }
       }
     }
@@ -253,17 +331,29 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
     float o_acc[KSTEPS][4];
 #pragma unroll
     for (int j = 0; j < KSTEPS; ++j) o_acc[j][0] = o_acc[j][1] = o_acc[j][2] = o_acc[j][3] = 0.0f;
-    float corr[G][2];  // sum_row bias_v * p for heads 2t, 2t+1: this thread's rows only
-#pragma unroll
-    for (int grp = 0; grp < G; ++grp) corr[grp][0] = corr[grp][1] = 0.0f;
+    // sum_row bias_v[row][grp] * p[row][head]: (m = group g, n = heads 2t, 2t+1) in [0], [1]
+    float cacc[4] = {0.f, 0.f, 0.f, 0.f};
     float m0 = -1.0e30f, m1 = -1.0e30f, l0 = 0.0f, l1 = 0.0f;
-    const uint8_t* qh_row = q_hi + g * S::QROW + 8 * t;   // + 32*ks: the four fp16 of dims 16ks+4t..+3
-    const uint8_t* ql_row = q_lo + g * S::QROW + 8 * t;
+    // this thread's fixed offsets inside a stage
+    const int k_off = g * HD + 8 * t;                        // + (granule ^ (g & 3)) * 32; row g+8: + 8 * HD
+    const int q_off = g * S::QROW + 16 * t;                  // + 64 * group
+    const int kb_off = S::BIASES + (g * G + 2 * t) * 2;      // K biases of (row g; groups 2t, 2t+1)
+    const int vb_off = S::TILE + S::BIASES + (g * PAGE_TOKENS + 2 * t) * 2;  // V biases of (group g; rows 2t, 2t+1)
+    const bool kb_on = 2 * t < G, vb_on = g < G;
 
+#ifdef SGK_TRACE
+    long long tp_wait = 0, tp_s = 0, tp_soft = 0, tp_pv = 0, tp_prev = clock64();
+#define U8_PHASE(acc) do { long long now_ = clock64(); acc += now_ - tp_prev; tp_prev = now_; } while (0)
+#else
+#define U8_PHASE(acc) do {} while (0)
+#endif
+    int stage = warp;
+    uint32_t parity = 0;
+    bool ready = false;  // the page's barrier was already seen complete during the previous page
     for (int i = warp; i < my_pages; i += MMA_CONSUMERS) {
-      const int stage = i % nst;
-      const uint32_t parity = (i / nst) & 1;
-      const bool ok = mbar_wait(smem_u32(bars + stage), parity, abort_flag, a.status);
+      const bool ok = ready || mbar_wait(smem_u32(bars + stage), parity, abort_flag, a.status);
+      U8_PHASE(tp_wait);
+      if (i == 0) SGK_TP(2);
       uint8_t* ktile = ring + size_t(stage) * S::STAGE;
       uint8_t* vtile = ktile + S::TILE;
       const int64_t page_index = pb + i;
@@ -272,83 +362,120 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
       if (ok && owns_append && page_index == append_page_index) {
         // Quantise the new row; store codes and metadata to its page and to the staged copy.
         const int rin = static_cast<int>(len_old % PAGE_TOKENS);
-        int32_t page = table[page_index];
+        const int32_t page = flags[2];
         if (page >= 0 && page < a.num_pages) {
           uint8_t* gk = a.pool.base + int64_t(page) * a.pool.page_bytes + head_off;
           uint8_t* gv = gk + S::TILE;
+          float x[2 * G];
+          uint32_t code[2 * G], meta[2 * G];
+#pragma unroll
+          for (int grp = 0; grp < G; ++grp) {
+            x[grp] = kn[grp * QGROUP + lane];
+            x[G + grp] = vn[grp * QGROUP + lane];
+          }
+          quantize_groups<2 * G>(x, code, meta);
+          uint32_t biggest = 0;
 #pragma unroll
           for (int grp = 0; grp < G; ++grp) {
             const int dim = grp * QGROUP + lane;
-            uint32_t mk, mv;
-            const uint32_t ck = quantize_lane(kn[dim], &mk);
-            const uint32_t cv = quantize_lane(vn[dim], &mv);
-            const int ik = u8_k_code_index(rin, dim, HD), iv = u8_v_code_index(rin, dim);
-            gk[ik] = static_cast<uint8_t>(ck);
-            ktile[ik] = static_cast<uint8_t>(ck);
-            gv[iv] = static_cast<uint8_t>(cv);
-            vtile[iv] = static_cast<uint8_t>(cv);
-            if (lane == 0) {
-              const int mo = u8_meta_offset(rin, grp, HD);
-              *reinterpret_cast<uint32_t*>(gk + mo) = mk;
-              *reinterpret_cast<uint32_t*>(ktile + mo) = mk;
-              *reinterpret_cast<uint32_t*>(gv + mo) = mv;
-              *reinterpret_cast<uint32_t*>(vtile + mo) = mv;
-              atomicMax(a.pool.scale_max, max((mk & 0xffffu) << 16, (mv & 0xffffu) << 16));
+            const int ik = u8_k_code_index(rin, dim, HD), iv = u8_v_code_index(rin, dim, HD);
+            gk[ik] = static_cast<uint8_t>(code[grp]);
+            ktile[ik] = static_cast<uint8_t>(code[grp]);
+            gv[iv] = static_cast<uint8_t>(code[G + grp]);
+            vtile[iv] = static_cast<uint8_t>(code[G + grp]);
+            biggest = max(biggest, max((meta[grp] & 0xffffu) << 16, (meta[G + grp] & 0xffffu) << 16));
+          }
+          // lane grp writes the metadata of group grp (every lane holds every group's)
+#pragma unroll
+          for (int grp = 0; grp < G; ++grp) {
+            if (lane == grp) {
+              const uint32_t mk = meta[grp], mv = meta[G + grp];
+              const int so = u8_scale_offset(rin, grp, HD);
+              const int kbo = u8_bias_offset(0, rin, grp, HD), vbo = u8_bias_offset(1, rin, grp, HD);
+              const uint16_t ks = static_cast<uint16_t>(mk & 0xffffu), kbias = static_cast<uint16_t>(mk >> 16);
+              const uint16_t vs = static_cast<uint16_t>(mv & 0xffffu), vbias = static_cast<uint16_t>(mv >> 16);
+              *reinterpret_cast<uint16_t*>(gk + so) = ks;
+              *reinterpret_cast<uint16_t*>(ktile + so) = ks;
+              *reinterpret_cast<uint16_t*>(gk + kbo) = kbias;
+              *reinterpret_cast<uint16_t*>(ktile + kbo) = kbias;
+              *reinterpret_cast<uint16_t*>(gv + so) = vs;
+              *reinterpret_cast<uint16_t*>(vtile + so) = vs;
+              *reinterpret_cast<uint16_t*>(gv + vbo) = vbias;
+              *reinterpret_cast<uint16_t*>(vtile + vbo) = vbias;
             }
           }
+          if (lane == 0 && biggest > *reinterpret_cast<volatile uint32_t*>(a.pool.scale_max))
+            atomicMax(a.pool.scale_max, biggest);
         }
         __syncwarp();
       }
 
       if (ok) {
-        // ---- scores: one accumulator per group of 32 dims, scale applied in f32. The
-        //      tensor-core instructions have a long latency and issue in order, so products
-        //      that do not depend on each other are issued back to back: all groups for one
-        //      half of their dims and the hi part of Q, then the lo part, then the other half. ----
-        float s[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
-        const uint8_t* kmeta = ktile + S::CODES;
+        // ---- scores. Bias part on the tensor cores: [16 rows x groups] . [groups x 8 heads]
+        //      in bf16 with the group sums of q in three bf16 parts (24 bits). ----
+        float sb[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+          const uint32_t a0 = kb_on ? *reinterpret_cast<const uint32_t*>(ktile + kb_off) : 0u;
+          const uint32_t a1 = kb_on ? *reinterpret_cast<const uint32_t*>(ktile + kb_off + 8 * G * 2) : 0u;
+          mma_bf16_k8(sb, a0, a1, qs_hi);
+          mma_bf16_k8(sb, a0, a1, qs_mid);
+          mma_bf16_k8(sb, a0, a1, qs_lo);
+        }
+        // Code part: one accumulator per group of 32 dims (two k-steps, q hi and lo), the
+        // per-(row, group) scale applied to it in f32. A lane's 8 bytes of a group are its
+        // dims 8t .. 8t+7: the first word is k-step 0, the second k-step 1.
         float acc[G][4];
 #pragma unroll
         for (int grp = 0; grp < G; ++grp) acc[grp][0] = acc[grp][1] = acc[grp][2] = acc[grp][3] = 0.0f;
+        // Four groups at a time, and for them first every product of the first k-step with q hi,
+        // then with q lo, then the second k-step: the tensor-core instructions of one accumulator
+        // depend on each other, so products of different groups are issued between them.
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t af[G][4];
+        for (int set = 0; set < G / 4; ++set) {
+          uint2 w0[4], w1[4];
+          uint4 qh[4], ql[4];
 #pragma unroll
-          for (int grp = 0; grp < G; ++grp) {
-            const int ks = 2 * grp + half;                 // 16-byte chunk index = k-step
-            const int phys = (ks & ~7) | ((ks ^ g) & 7);   // rows g and g+8 share the swizzle
-            const uint32_t w0 = *reinterpret_cast<const uint32_t*>(ktile + g * HD + phys * 16 + 4 * t);
-            const uint32_t w1 = *reinterpret_cast<const uint32_t*>(ktile + (g + 8) * HD + phys * 16 + 4 * t);
-            af[grp][0] = codes_lo(w0);
-            af[grp][1] = codes_lo(w1);
-            af[grp][2] = codes_hi(w0);
-            af[grp][3] = codes_hi(w1);
+          for (int u = 0; u < 4; ++u) {
+            const int grp = 4 * set + u;
+            const int phys = (grp & ~3) | ((grp ^ g) & 3);
+            w0[u] = *reinterpret_cast<const uint2*>(ktile + k_off + phys * 32);
+            w1[u] = *reinterpret_cast<const uint2*>(ktile + k_off + phys * 32 + 8 * HD);
+            qh[u] = *reinterpret_cast<const uint4*>(q_hi + q_off + 64 * grp);
+            ql[u] = *reinterpret_cast<const uint4*>(q_lo + q_off + 64 * grp);
           }
 #pragma unroll
-          for (int grp = 0; grp < G; ++grp) {
-            const uint2 qh = *reinterpret_cast<const uint2*>(qh_row + 32 * (2 * grp + half));
-            mma_f16(acc[grp], af[grp][0], af[grp][1], af[grp][2], af[grp][3], qh.x, qh.y);
-          }
+          for (int u = 0; u < 4; ++u)
+            mma_f16(acc[4 * set + u], codes_lo(w0[u].x), codes_lo(w1[u].x), codes_hi(w0[u].x), codes_hi(w1[u].x),
+                    qh[u].x, qh[u].y);
 #pragma unroll
-          for (int grp = 0; grp < G; ++grp) {
-            const uint2 ql = *reinterpret_cast<const uint2*>(ql_row + 32 * (2 * grp + half));
-            mma_f16(acc[grp], af[grp][0], af[grp][1], af[grp][2], af[grp][3], ql.x, ql.y);
-          }
+          for (int u = 0; u < 4; ++u)
+            mma_f16(acc[4 * set + u], codes_lo(w0[u].x), codes_lo(w1[u].x), codes_hi(w0[u].x), codes_hi(w1[u].x),
+                    ql[u].x, ql[u].y);
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            mma_f16(acc[4 * set + u], codes_lo(w0[u].y), codes_lo(w1[u].y), codes_hi(w0[u].y), codes_hi(w1[u].y),
+                    qh[u].z, qh[u].w);
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            mma_f16(acc[4 * set + u], codes_lo(w0[u].y), codes_lo(w1[u].y), codes_hi(w0[u].y), codes_hi(w1[u].y),
+                    ql[u].z, ql[u].w);
         }
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+          float sc0[G], sc1[G];
+          load_row_scales<G>(ktile + S::SCALES + g * G * 2, sc0);
+          load_row_scales<G>(ktile + S::SCALES + (g + 8) * G * 2, sc1);
 #pragma unroll
-        for (int grp = 0; grp < G; ++grp) {
-          const uint32_t mk0 = *reinterpret_cast<const uint32_t*>(kmeta + (g * G + grp) * 4);
-          const uint32_t mk1 = *reinterpret_cast<const uint32_t*>(kmeta + ((g + 8) * G + grp) * 4);
-          const float sc0 = __uint_as_float(mk0 << 16), bi0 = __uint_as_float(mk0 & 0xffff0000u);
-          const float sc1 = __uint_as_float(mk1 << 16), bi1 = __uint_as_float(mk1 & 0xffff0000u);
-          const float qs0 = qsum_s[(2 * t) * G + grp], qs1 = qsum_s[(2 * t + 1) * G + grp];
-          s[0] = fmaf(sc0, acc[grp][0], s[0]), sb[0] = fmaf(bi0, qs0, sb[0]);
-          s[1] = fmaf(sc0, acc[grp][1], s[1]), sb[1] = fmaf(bi0, qs1, sb[1]);
-          s[2] = fmaf(sc1, acc[grp][2], s[2]), sb[2] = fmaf(bi1, qs0, sb[2]);
-          s[3] = fmaf(sc1, acc[grp][3], s[3]), sb[3] = fmaf(bi1, qs1, sb[3]);
+          for (int grp = 0; grp < G; ++grp) {
+            s[0] = fmaf(sc0[grp], acc[grp][0], s[0]);
+            s[1] = fmaf(sc0[grp], acc[grp][1], s[1]);
+            s[2] = fmaf(sc1[grp], acc[grp][2], s[2]);
+            s[3] = fmaf(sc1[grp], acc[grp][3], s[3]);
+          }
         }
 #pragma unroll
         for (int r = 0; r < 4; ++r) s[r] = fmaf(s[r], CODE_UNIT_INV, sb[r]);  // the codes were in units of 2^-24
+        U8_PHASE(tp_s);
         if (row_base < ws || row_base + PAGE_TOKENS > len) {
           int64_t ra = row_base + g, rb = row_base + g + 8;
           if (ra < ws || ra >= len) s[0] = s[1] = -1.0e30f;
@@ -373,11 +500,8 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
             o_acc[j][1] *= al1;
             o_acc[j][3] *= al1;
           }
-#pragma unroll
-          for (int grp = 0; grp < G; ++grp) {
-            corr[grp][0] *= al0;
-            corr[grp][1] *= al1;
-          }
+          cacc[0] *= al0;
+          cacc[1] *= al1;
           m0 = mn0;
           m1 = mn1;
         }
@@ -388,30 +512,74 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
         p[3] = exp2f(s[3] - m1);
         l0 += p[0] + p[2];
         l1 += p[1] + p[3];
-        // ---- outputs: per group, fold scale_v into the weights; bias_v term in f32 ----
-        const uint8_t* vmeta = vtile + S::CODES;
+        U8_PHASE(tp_soft);
+        {
+          // look at the next page's barrier now: the answer arrives while the products below run
+          int ns = stage + MMA_CONSUMERS;
+          uint32_t np = parity;
+          if (ns >= nst) {
+            ns -= nst;
+            np ^= 1;
+          }
+          ready = (i + MMA_CONSUMERS < my_pages) && mbar_test_wait(smem_u32(bars + ns), np);
+        }
+        // ---- outputs. Bias part: [groups x 16 rows] . [16 rows x 8 heads] in bf16 with p in two
+        //      bf16 parts; the movmatrix turns (row; heads 2t, 2t+1) into (rows 2t, 2t+1; head). ----
+        {
+          const uint32_t ph0 = pack_bf16(p[0], p[1]), ph1 = pack_bf16(p[2], p[3]);
+          const uint32_t pl0 = pack_bf16(p[0] - bf16_lo_f32(ph0), p[1] - bf16_hi_f32(ph0));
+          const uint32_t pl1 = pack_bf16(p[2] - bf16_lo_f32(ph1), p[3] - bf16_hi_f32(ph1));
+          const uint32_t a0 = vb_on ? *reinterpret_cast<const uint32_t*>(ktile + vb_off) : 0u;
+          const uint32_t a2 = vb_on ? *reinterpret_cast<const uint32_t*>(ktile + vb_off + 16) : 0u;
+          mma_bf16(cacc, a0, 0u, a2, 0u, movmatrix_trans(ph0), movmatrix_trans(ph1));
+          mma_bf16(cacc, a0, 0u, a2, 0u, movmatrix_trans(pl0), movmatrix_trans(pl1));
+        }
+        // Code part: scale_v folded into the weights of each group (fp16, times the pool's
+        // power of two), then V^T codes . weights on the tensor cores.
         uint32_t pb0[G], pb1[G];
+        {
+          float sv0[G], sv1[G];
+          load_row_scales<G>(vtile + S::SCALES + g * G * 2, sv0);
+          load_row_scales<G>(vtile + S::SCALES + (g + 8) * G * 2, sv1);
+          const uint32_t pw0 = pack_f16(p[0], p[1]), pw1 = pack_f16(p[2], p[3]);
 #pragma unroll
-        for (int grp = 0; grp < G; ++grp) {
-          const uint32_t mv0 = *reinterpret_cast<const uint32_t*>(vmeta + (g * G + grp) * 4);
-          const uint32_t mv1 = *reinterpret_cast<const uint32_t*>(vmeta + ((g + 8) * G + grp) * 4);
-          const float sc0 = __uint_as_float(mv0 << 16) * pscale, bi0 = __uint_as_float(mv0 & 0xffff0000u);
-          const float sc1 = __uint_as_float(mv1 << 16) * pscale, bi1 = __uint_as_float(mv1 & 0xffff0000u);
-          corr[grp][0] += bi0 * p[0] + bi1 * p[2];
-          corr[grp][1] += bi0 * p[1] + bi1 * p[3];
-          pb0[grp] = movmatrix_trans(pack_f16(p[0] * sc0, p[1] * sc0));   // rows 0-7
-          pb1[grp] = movmatrix_trans(pack_f16(p[2] * sc1, p[3] * sc1));   // rows 8-15
+          for (int grp = 0; grp < G; ++grp) {
+            const float x0 = sv0[grp] * pscale, x1 = sv1[grp] * pscale;
+            pb0[grp] = movmatrix_trans(hmul2_u32(pw0, pack_f16(x0, x0)));   // rows 0-7
+            pb1[grp] = movmatrix_trans(hmul2_u32(pw1, pack_f16(x1, x1)));   // rows 8-15
+          }
         }
 #pragma unroll
-        for (int j = 0; j < KSTEPS; ++j) {
-          const uint32_t w0 = *reinterpret_cast<const uint32_t*>(vtile + (16 * j + g) * PAGE_TOKENS + 4 * t);
-          const uint32_t w1 = *reinterpret_cast<const uint32_t*>(vtile + (16 * j + g + 8) * PAGE_TOKENS + 4 * t);
-          mma_f16(o_acc[j], codes_lo(w0), codes_lo(w1), codes_hi(w0), codes_hi(w1), pb0[j / 2], pb1[j / 2]);
+        for (int jq = 0; jq < KSTEPS / 4; ++jq) {
+          const uint4 wa = *reinterpret_cast<const uint4*>(vtile + ((jq * 2) * 32 + lane) * 16);
+          const uint4 wb = *reinterpret_cast<const uint4*>(vtile + ((jq * 2 + 1) * 32 + lane) * 16);
+          mma_f16(o_acc[4 * jq], codes_lo(wa.x), codes_lo(wa.y), codes_hi(wa.x), codes_hi(wa.y), pb0[2 * jq],
+                  pb1[2 * jq]);
+          mma_f16(o_acc[4 * jq + 1], codes_lo(wa.z), codes_lo(wa.w), codes_hi(wa.z), codes_hi(wa.w), pb0[2 * jq],
+                  pb1[2 * jq]);
+          mma_f16(o_acc[4 * jq + 2], codes_lo(wb.x), codes_lo(wb.y), codes_hi(wb.x), codes_hi(wb.y), pb0[2 * jq + 1],
+                  pb1[2 * jq + 1]);
+          mma_f16(o_acc[4 * jq + 3], codes_lo(wb.z), codes_lo(wb.w), codes_hi(wb.z), codes_hi(wb.w), pb0[2 * jq + 1],
+                  pb1[2 * jq + 1]);
         }
       }
+      else ready = false;
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(bars + MMA_MAX_STAGES + stage));
+      U8_PHASE(tp_pv);
+      stage += MMA_CONSUMERS;   // the stage count is a multiple of the consumer count
+      if (stage >= nst) {
+        stage -= nst;
+        parity ^= 1;
+      }
     }
+    if (warp == 0) SGK_TP(3);
+#ifdef SGK_TRACE
+    if (a.trace && warp == 0 && lane == 0) {
+      unsigned long long* tr = a.trace + ((size_t(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16;
+      tr[8] = tp_wait, tr[9] = tp_s, tr[10] = tp_soft, tr[11] = tp_pv, tr[12] = (my_pages + MMA_CONSUMERS - 1) / MMA_CONSUMERS;
+    }
+#endif
 
     // ---- hand this warp's state to the merge buffer (it aliases the ring) ----
     asm volatile("bar.sync 1, %0;" ::"r"(MMA_CONSUMERS * 32) : "memory");
@@ -419,16 +587,13 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
     for (int off = 4; off < 32; off <<= 1) {
       l0 += __shfl_xor_sync(0xffffffffu, l0, off);
       l1 += __shfl_xor_sync(0xffffffffu, l1, off);
-#pragma unroll
-      for (int grp = 0; grp < G; ++grp) {
-        corr[grp][0] += __shfl_xor_sync(0xffffffffu, corr[grp][0], off);
-        corr[grp][1] += __shfl_xor_sync(0xffffffffu, corr[grp][1], off);
-      }
     }
     float* ow = o_s + warp * 8 * S::OPAD;
 #pragma unroll
     for (int j = 0; j < KSTEPS; ++j) {
-      const float c0 = corr[j / 2][0], c1 = corr[j / 2][1];
+      // the bias sums of group j/2 sit in the lanes of quad j/2
+      const float c0 = __shfl_sync(0xffffffffu, cacc[0], (j / 2) * 4 + t);
+      const float c1 = __shfl_sync(0xffffffffu, cacc[1], (j / 2) * 4 + t);
       ow[(2 * t) * S::OPAD + 16 * j + g] = o_acc[j][0] * inv_pscale + c0;
       ow[(2 * t + 1) * S::OPAD + 16 * j + g] = o_acc[j][1] * inv_pscale + c1;
       ow[(2 * t) * S::OPAD + 16 * j + g + 8] = o_acc[j][2] * inv_pscale + c0;

@@ -38,16 +38,15 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(GatherArgs a) {
       reinterpret_cast<uint16_t*>(a.v_out)[i] = reinterpret_cast<const uint16_t*>(vt)[e];
     } else {
       reinterpret_cast<uint8_t*>(a.k_out)[i] = kt[u8_k_code_index(rin, dim, hd)];
-      reinterpret_cast<uint8_t*>(a.v_out)[i] = vt[u8_v_code_index(rin, dim)];
+      reinterpret_cast<uint8_t*>(a.v_out)[i] = vt[u8_v_code_index(rin, dim, hd)];
       if (dim % QGROUP == 0) {
         const int groups = kv_dim / QGROUP;
         const int64_t gi = r * groups + col / QGROUP;
-        uint32_t mk = *reinterpret_cast<const uint32_t*>(kt + u8_meta_offset(rin, dim / QGROUP, hd));
-        uint32_t mv = *reinterpret_cast<const uint32_t*>(vt + u8_meta_offset(rin, dim / QGROUP, hd));
-        a.k_scale[gi] = static_cast<uint16_t>(mk & 0xffffu);
-        a.k_bias[gi] = static_cast<uint16_t>(mk >> 16);
-        a.v_scale[gi] = static_cast<uint16_t>(mv & 0xffffu);
-        a.v_bias[gi] = static_cast<uint16_t>(mv >> 16);
+        const int grp = dim / QGROUP;
+        a.k_scale[gi] = *reinterpret_cast<const uint16_t*>(kt + u8_scale_offset(rin, grp, hd));
+        a.k_bias[gi] = *reinterpret_cast<const uint16_t*>(kt + u8_bias_offset(0, rin, grp, hd));
+        a.v_scale[gi] = *reinterpret_cast<const uint16_t*>(vt + u8_scale_offset(rin, grp, hd));
+        a.v_bias[gi] = *reinterpret_cast<const uint16_t*>(vt + u8_bias_offset(1, rin, grp, hd));
       }
     }
   }

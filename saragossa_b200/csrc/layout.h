@@ -11,12 +11,15 @@
 //   f32  : [row][dim] linear.
 //   bf16 : [row][dim]; when head_dim % 64 == 0 the 16-byte chunks of a row are
 //          XOR-swizzled inside each 128-byte segment: chunk c -> c ^ (row & 7).
-//   u8   : K codes [row][dim] (one byte each) with 16-byte chunks swizzled by
-//          c ^ (row & 7) inside each 128-byte segment (head_dim % 128 == 0), so the
-//          eight rows a warp reads together fall into different banks; V codes are stored
-//          TRANSPOSED, [dim][16 row slots], row r in slot vslot(r); after the
-//          codes come the per-(row, group-of-32) pairs {scale bf16, bias bf16},
-//          [row][group], 4 bytes each.
+//   u8   : K codes [row][dim] (one byte each); when head_dim % 128 == 0 the 32-byte
+//          granules (= quantisation groups) of a row are XOR-swizzled inside each 128-byte
+//          segment, granule c -> c ^ (row & 3), so the four rows a half-warp reads
+//          together with 8-byte loads fall into different banks. V codes are stored
+//          TRANSPOSED, row r in byte slot vslot(r) of a 4-byte word per (dim, quad), and
+//          (head_dim % 64 == 0) the words are ordered so that a lane's words of four
+//          consecutive 16-dim steps are two 16-byte loads, see u8_v_code_index. After the
+//          codes: the bf16 scales [row][group], then the bf16 biases, [row][group] for K
+//          and [group][row] for V (the order the tensor-core bias products read them in).
 #pragma once
 #include <stdint.h>
 
@@ -76,19 +79,34 @@ SGK_HD int bf16_elem_index(int row, int dim, int hd) {
 
 // Byte index of K code (row, dim) inside a u8 tile.
 SGK_HD int u8_k_code_index(int row, int dim, int hd) {
-  int chunk = dim >> 4;
-  if (hd % 128 == 0) chunk = (chunk & ~7) | ((chunk ^ row) & 7);
-  return row * hd + chunk * 16 + (dim & 15);
+  int gran = dim >> 5;
+  if (hd % 128 == 0) gran = (gran & ~3) | ((gran ^ row) & 3);
+  return row * hd + gran * 32 + (dim & 31);
 }
 // Slot of row r inside the 16 bytes a V dim holds: threads of a quad read the
 // four bytes {2t, 2t+1, 2t+8, 2t+9} they need for one mma A fragment as one word.
 SGK_HD int u8_v_slot(int row) {
   return row < 8 ? 4 * (row >> 1) + (row & 1) : 4 * ((row - 8) >> 1) + 2 + (row & 1);
 }
-SGK_HD int u8_v_code_index(int row, int dim) { return dim * PAGE_TOKENS + u8_v_slot(row); }
-// Byte offset of the {scale, bias} pair of (row, group) inside a u8 tile.
-SGK_HD int u8_meta_offset(int row, int group, int hd) {
-  return PAGE_TOKENS * hd + (row * (hd / QGROUP) + group) * 4;
+// Byte index of V code (row, dim). With j = dim / 16 the 16-dim step, lane = (dim % 8) * 4 +
+// slot / 4 the lane that owns the word in the mma A fragment and half = (dim / 8) % 2 its
+// upper or lower eight dims, the words of steps 4q .. 4q+3 lie as [q][j / 2 % 2][lane][(j % 2) * 2 + half]:
+// a lane reads them with two 16-byte loads at consecutive-lane addresses.
+SGK_HD int u8_v_code_index(int row, int dim, int hd) {
+  const int slot = u8_v_slot(row);
+  if (hd % 64 != 0) return dim * PAGE_TOKENS + slot;
+  const int j = dim >> 4, half = (dim >> 3) & 1, g = dim & 7;
+  const int word = ((((j >> 2) * 2 + ((j >> 1) & 1)) * 32 + g * 4 + (slot >> 2)) * 4) + (j & 1) * 2 + half;
+  return word * 4 + (slot & 3);
+}
+// Byte offsets of the bf16 scale and bias of (row, group) inside a u8 tile.
+SGK_HD int u8_scale_offset(int row, int group, int hd) {
+  return PAGE_TOKENS * hd + (row * (hd / QGROUP) + group) * 2;
+}
+SGK_HD int u8_bias_offset(int is_v, int row, int group, int hd) {
+  const int groups = hd / QGROUP;
+  return PAGE_TOKENS * hd + PAGE_TOKENS * groups * 2 +
+         (is_v ? group * PAGE_TOKENS + row : row * groups + group) * 2;
 }
 
 }  // namespace sgk
