@@ -123,6 +123,7 @@ int32_t sgk_pool_create(sgk_state* st, int32_t layers, int32_t kv_heads, int32_t
   p->tile_b = tile_bytes(dtype, head_dim);
   p->layer_b = int64_t(kv_heads) * 2 * p->tile_b;
   p->page_b = int64_t(layers) * p->layer_b;
+  p->layer_stride = num_pages * p->layer_b;
   p->refcount.assign(static_cast<size_t>(num_pages), 0);
   p->free_list.resize(static_cast<size_t>(num_pages));
   for (int64_t i = 0; i < num_pages; ++i) p->free_list[static_cast<size_t>(i)] = static_cast<int32_t>(num_pages - 1 - i);
@@ -1312,7 +1313,7 @@ int32_t sgk_util_copy_blocks(sgk_state* st, void* stream, void* d_dst, const voi
   if (!st || !d_dst || !d_src) return fail(SGK_ERR_BACKEND, "null argument");
   if (page_bytes <= 0 || page_bytes % 16 != 0) return fail(SGK_ERR_DIMENSION, "page_bytes must be a positive multiple of 16");
   SGK_CUDA(launch_copy_pages(static_cast<uint8_t*>(d_dst), static_cast<const uint8_t*>(d_src), dst_pages, src_pages,
-                             n_pages, page_bytes, st->pick(stream)));
+                             n_pages, page_bytes, 1, 0, st->pick(stream)));
   st->launches += 1;
   return SGK_OK;
 }

@@ -53,7 +53,9 @@ struct Pool {
   int max_seqs = 0;
   int64_t max_seq_tokens = 0;
   int table_stride = 0;
-  int64_t tile_b = 0, layer_b = 0, page_b = 0;
+  // tile_b: one K or V tile; layer_b: one page of one layer (all heads, K and V); page_b: one page
+  // over all layers (what a page costs); layer_stride: distance between layers in the pool
+  int64_t tile_b = 0, layer_b = 0, page_b = 0, layer_stride = 0;
   uint8_t* d_base = nullptr;
   int32_t* d_tables = nullptr;
   int32_t* d_lens = nullptr;

@@ -35,8 +35,8 @@ const char* last_error_cstr() { return g_last_error.c_str(); }
 PoolView Pool::view() const {
   PoolView v;
   v.base = d_base;
-  v.page_bytes = page_b;
-  v.layer_bytes = layer_b;
+  v.page_bytes = layer_b;
+  v.layer_bytes = layer_stride;
   v.tile_bytes = tile_b;
   v.tables = d_tables;
   v.lens = d_lens;
@@ -99,7 +99,7 @@ int Pool::flush_scrub(cudaStream_t stream) {
   pending_scrub.clear();
   if (list.empty()) return SGK_OK;
   SGK_TRY(upload_page_list(this, list, {}));
-  SGK_CUDA(launch_scrub_pages(d_base, d_page_list, static_cast<int>(list.size()), page_b, stream));
+  SGK_CUDA(launch_scrub_pages(d_base, d_page_list, static_cast<int>(list.size()), layer_b, layers, layer_stride, stream));
   st->launches += 1;
   SGK_CUDA(cudaStreamSynchronize(stream));
   return SGK_OK;
@@ -110,7 +110,7 @@ int Pool::copy_pages(const std::vector<int32_t>& dst, const std::vector<int32_t>
   if (dst.empty() || host_only()) return SGK_OK;
   SGK_TRY(upload_page_list(this, dst, src));
   SGK_CUDA(launch_copy_pages(d_base, d_base, d_page_list, d_page_list + dst.size(), static_cast<int>(dst.size()),
-                             page_b, stream));
+                             layer_b, layers, layer_stride, stream));
   st->launches += 1;
   return SGK_OK;
 }

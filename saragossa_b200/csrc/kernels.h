@@ -109,14 +109,17 @@ struct GatherArgs {
 };
 cudaError_t launch_gather(const GatherArgs& a, cudaStream_t stream);
 
-// Page copy: dst_pages[i] <- src_pages[i], page_bytes each (16-byte vectors).
+// Page copy: dst_pages[i] <- src_pages[i]; a page is n_layers pieces of page_bytes, layer_stride
+// apart (16-byte vectors).
 cudaError_t launch_copy_pages(uint8_t* dst_base, const uint8_t* src_base, const int32_t* d_dst_pages,
-                              const int32_t* d_src_pages, int n_pages, int64_t page_bytes,
+                              const int32_t* d_src_pages, int n_pages, int64_t page_bytes, int n_layers,
+                              int64_t layer_stride,
                               cudaStream_t stream);
 // Contiguous device copy (linear-state snapshot / restore).
 cudaError_t launch_copy_bytes(void* dst, const void* src, int64_t bytes, cudaStream_t stream);
 // Zero-fill of freed pages (eviction scrub).
-cudaError_t launch_scrub_pages(uint8_t* base, const int32_t* d_pages, int n_pages, int64_t page_bytes,
+cudaError_t launch_scrub_pages(uint8_t* base, const int32_t* d_pages, int n_pages, int64_t page_bytes, int n_layers,
+                               int64_t layer_stride,
                                cudaStream_t stream);
 // Gated DeltaNet step on one layer's state [H_v][d_v][d_k] (f32 or bf16).
 constexpr int GATED_DELTA_MAX_STATES = 64;

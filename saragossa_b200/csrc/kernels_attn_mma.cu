@@ -49,7 +49,8 @@ struct MmaSmem {
   static constexpr int O_BYTES = MMA_CONSUMERS * 8 * OPAD * 4;  // aliases the ring once it has drained
   static constexpr int ML_BYTES = 512;  // per-warp {max, sum}, then the merge weights and the block's {max, sum}
   static constexpr int BAR_BYTES = 2 * MMA_MAX_STAGES * 8;
-  static constexpr int FIXED = Q_BYTES + ML_BYTES + BAR_BYTES + 64;
+  static constexpr int NEW_BYTES = 2 * HD * 2;       // the K and V row of a fused append, bf16
+  static constexpr int FIXED = Q_BYTES + ML_BYTES + BAR_BYTES + 64 + NEW_BYTES;
   __host__ __device__ static size_t ring_bytes(int stages) {
     size_t r = size_t(stages) * STAGE;
     return r > size_t(O_BYTES) ? r : size_t(O_BYTES);
@@ -72,7 +73,8 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
   float* o_s = reinterpret_cast<float*>(ring);                  // [warps][8][OPAD], used after the ring drained
   float* ml_s = reinterpret_cast<float*>(fixed + S::Q_BYTES);   // [warps][8][2]
   uint64_t* bars = reinterpret_cast<uint64_t*>(fixed + S::Q_BYTES + S::ML_BYTES);
-  int* flags = reinterpret_cast<int*>(bars + 2 * MMA_MAX_STAGES);  // [0]=abort [1]=last arriver
+  int* flags = reinterpret_cast<int*>(bars + 2 * MMA_MAX_STAGES);  // [0]=abort [1]=last arriver [2]=append page
+  uint32_t* new_s = reinterpret_cast<uint32_t*>(flags + 16);       // bf16 pairs of the appended [K row | V row]
   volatile int* abort_flag = flags;
 
   const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
@@ -134,6 +136,20 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
       const int f = (tid + k * MMA_CONSUMERS * 32) * 4;
       v[k] = (f / HD < gqa) ? __ldg(reinterpret_cast<const float4*>(q + f)) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
+    // The row of a fused append is converted here, with the same round trip as Q, and waits in
+    // shared memory for its page: read where it is stored, it would pay that latency at the very
+    // end of the block that every other block of the sequence waits for.
+    if (owns_append) {
+      if (tid * 4 < 2 * HD) {
+        const int64_t row_off = int64_t(seq) * a.pool.kv_heads * HD + kvh * HD;
+        const float* src = tid * 4 < HD ? a.k_new + row_off + tid * 4 : a.v_new + row_off + (tid * 4 - HD);
+        const float4 x = __ldg(reinterpret_cast<const float4*>(src));
+        *reinterpret_cast<uint2*>(new_s + tid * 2) =
+            make_uint2(uint32_t(f32_to_bf16_bits(x.x)) | (uint32_t(f32_to_bf16_bits(x.y)) << 16),
+                       uint32_t(f32_to_bf16_bits(x.z)) | (uint32_t(f32_to_bf16_bits(x.w)) << 16));
+      }
+      if (tid == 0) flags[2] = table[append_page_index];
+    }
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int f = (tid + k * MMA_CONSUMERS * 32) * 4;
@@ -149,15 +165,14 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
 
   if (warp == MMA_CONSUMERS) {
     // ---------------- producer warp ----------------
+    int stage = 0;          // page i uses stage i % nst, in phase i / nst: kept as running counters
+    uint32_t parity = 1;
     for (int base = 0; base < my_pages; base += 32) {
       int idx = base + lane;
       int32_t entry = base == 0 ? first_entry : (idx < my_pages ? table[pb + idx] : -1);
       int cnt = min(32, my_pages - base);
       for (int j = 0; j < cnt; ++j) {
-        int i = base + j;
         int32_t page = __shfl_sync(0xffffffffu, entry, j);
-        int stage = i % nst;
-        uint32_t parity = ((i / nst) & 1) ^ 1;
         bool ok = true;
         if (lane == 0) {
           ok = mbar_wait(smem_u32(bars + MMA_MAX_STAGES + stage), parity, abort_flag, a.status);
@@ -172,6 +187,10 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
             bulk_copy_g2s(smem_u32(ring + size_t(stage) * S::STAGE),
                           a.pool.base + int64_t(page) * a.pool.page_bytes + head_off, S::STAGE, full);
           }
+        }
+        if (++stage == nst) {
+          stage = 0;
+          parity ^= 1;
         }
       }
     }
@@ -197,9 +216,16 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
     const int k_row = lr + (lm & 1) * 8, k_csel = lm >> 1;   // K: matrices (r0-7,c0) (r8-15,c0) (r0-7,c1) (r8-15,c1)
     const int v_row = lr + (lm >> 1) * 8, v_csel = lm & 1;   // V^T: (r0-7,c0) (r0-7,c1) (r8-15,c0) (r8-15,c1)
 
+    int stage = warp, next_stage = warp;   // the stage count is a multiple of the consumer count
+    uint32_t parity = 0, next_parity = 0;
     for (int i = warp; i < my_pages; i += MMA_CONSUMERS) {
-      const int stage = i % nst;
-      const uint32_t parity = (i / nst) & 1;
+      stage = next_stage;
+      parity = next_parity;
+      next_stage = stage + MMA_CONSUMERS;
+      if (next_stage >= nst) {
+        next_stage -= nst;
+        next_parity ^= 1;
+      }
       const bool ok = mbar_wait(smem_u32(bars + stage), parity, abort_flag, a.status);
       if (i == 0) SGK_TP(2);
       uint8_t* ktile = ring + size_t(stage) * S::STAGE;
@@ -208,26 +234,16 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
       const int64_t row_base = page_index * PAGE_TOKENS;
 
       if (ok && owns_append && page_index == append_page_index) {
-        // Convert the new row once; store it to its page and into the staged copy.
+        // The new row (converted in the prologue) goes to its page and into the staged copy.
         const int rin = static_cast<int>(len_old % PAGE_TOKENS);
-        int32_t page = table[page_index];
+        const int32_t page = flags[2];
         if (page >= 0 && page < a.num_pages) {
           uint8_t* gk = a.pool.base + int64_t(page) * a.pool.page_bytes + head_off;
           uint8_t* gv = gk + S::TILE;
-          const float* kn = a.k_new + int64_t(seq) * a.pool.kv_heads * HD + kvh * HD;
-          const float* vn = a.v_new + int64_t(seq) * a.pool.kv_heads * HD + kvh * HD;
           for (int chunk = lane; chunk < HD / 8; chunk += 32) {
-            uint32_t wk[4], wv[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              wk[e] = uint32_t(f32_to_bf16_bits(kn[chunk * 8 + 2 * e])) |
-                      (uint32_t(f32_to_bf16_bits(kn[chunk * 8 + 2 * e + 1])) << 16);
-              wv[e] = uint32_t(f32_to_bf16_bits(vn[chunk * 8 + 2 * e])) |
-                      (uint32_t(f32_to_bf16_bits(vn[chunk * 8 + 2 * e + 1])) << 16);
-            }
             int off = bf16_elem_index(rin, chunk * 8, HD) * 2;
-            uint4 pk = make_uint4(wk[0], wk[1], wk[2], wk[3]);
-            uint4 pv = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+            const uint4 pk = *reinterpret_cast<const uint4*>(new_s + chunk * 4);
+            const uint4 pv = *reinterpret_cast<const uint4*>(new_s + HD / 2 + chunk * 4);
             *reinterpret_cast<uint4*>(gk + off) = pk;
             *reinterpret_cast<uint4*>(gv + off) = pv;
             *reinterpret_cast<uint4*>(ktile + off) = pk;

@@ -61,8 +61,8 @@ cudaError_t launch_gather(const GatherArgs& a, cudaStream_t stream) {
 }
 
 // ---- page copy (prefix snapshot / restore) ---------------------------------------
-// A page (all layers, K and V) is one contiguous, 256-byte aligned range. The grid
-// is a multiple of the SM count; each block walks (page, 16 KiB piece) work items,
+// A page is one contiguous, 256-byte aligned range per layer (all heads, K and V). The grid
+// is a multiple of the SM count; each block walks (page, layer, 16 KiB piece) work items,
 // every thread moving four 16-byte vectors per item with all loads issued before
 // the stores, so ~4 KiB per warp are in flight.
 constexpr int COPY_THREADS = 256;
@@ -73,15 +73,19 @@ __global__ void __launch_bounds__(COPY_THREADS) copy_pages_kernel(uint8_t* __res
                                                                   const uint8_t* __restrict__ src_base,
                                                                   const int32_t* __restrict__ dst_pages,
                                                                   const int32_t* __restrict__ src_pages,
-                                                                  int n_pages, int64_t page_bytes) {
+                                                                  int n_pages, int64_t page_bytes, int n_layers,
+                                                                  int64_t layer_stride) {
   const int64_t pieces_per_page = (page_bytes + COPY_PIECE - 1) / COPY_PIECE;
-  const int64_t items = pieces_per_page * n_pages;
+  const int64_t per_page = pieces_per_page * n_layers;
+  const int64_t items = per_page * n_pages;
   for (int64_t item = blockIdx.x; item < items; item += gridDim.x) {
-    const int64_t p = item / pieces_per_page, piece = item % pieces_per_page;
+    const int64_t p = item / per_page, rest = item % per_page;
+    const int64_t layer = rest / pieces_per_page, piece = rest % pieces_per_page;
     const int64_t dpage = dst_pages ? dst_pages[p] : p;
     const int64_t spage = src_pages ? src_pages[p] : p;
-    const uint4* s = reinterpret_cast<const uint4*>(src_base + spage * page_bytes + piece * COPY_PIECE);
-    uint4* d = reinterpret_cast<uint4*>(dst_base + dpage * page_bytes + piece * COPY_PIECE);
+    const int64_t within = layer * layer_stride + piece * COPY_PIECE;
+    const uint4* s = reinterpret_cast<const uint4*>(src_base + spage * page_bytes + within);
+    uint4* d = reinterpret_cast<uint4*>(dst_base + dpage * page_bytes + within);
     const int64_t vecs = min(COPY_PIECE, page_bytes - piece * COPY_PIECE) / 16;
     uint4 r[COPY_VEC_PER_THREAD];
 #pragma unroll
@@ -104,12 +108,12 @@ static int copy_grid(int64_t items) {
 }
 
 cudaError_t launch_copy_pages(uint8_t* dst_base, const uint8_t* src_base, const int32_t* d_dst_pages,
-                              const int32_t* d_src_pages, int n_pages, int64_t page_bytes,
-                              cudaStream_t stream) {
+                              const int32_t* d_src_pages, int n_pages, int64_t page_bytes, int n_layers,
+                              int64_t layer_stride, cudaStream_t stream) {
   if (n_pages <= 0) return cudaSuccess;
-  int64_t items = ((page_bytes + COPY_PIECE - 1) / COPY_PIECE) * n_pages;
+  int64_t items = ((page_bytes + COPY_PIECE - 1) / COPY_PIECE) * n_layers * n_pages;
   copy_pages_kernel<<<copy_grid(items), COPY_THREADS, 0, stream>>>(dst_base, src_base, d_dst_pages, d_src_pages,
-                                                                   n_pages, page_bytes);
+                                                                   n_pages, page_bytes, n_layers, layer_stride);
   return cudaGetLastError();
 }
 
@@ -127,7 +131,7 @@ cudaError_t launch_copy_bytes(void* dst, const void* src, int64_t bytes, cudaStr
   if (body > 0) {
     int64_t items = (body + COPY_PIECE - 1) / COPY_PIECE;
     copy_pages_kernel<<<copy_grid(items), COPY_THREADS, 0, stream>>>(
-        static_cast<uint8_t*>(dst), static_cast<const uint8_t*>(src), nullptr, nullptr, 1, body);
+        static_cast<uint8_t*>(dst), static_cast<const uint8_t*>(src), nullptr, nullptr, 1, body, 1, 0);
   }
   int64_t tail = bytes - body;
   if (tail > 0) {
@@ -139,22 +143,25 @@ cudaError_t launch_copy_bytes(void* dst, const void* src, int64_t bytes, cudaStr
 
 // ---- eviction scrub ------------------------------------------------------------------
 __global__ void __launch_bounds__(COPY_THREADS) scrub_pages_kernel(uint8_t* base, const int32_t* pages,
-                                                                   int n_pages, int64_t page_bytes) {
-  const int64_t vecs_per_page = page_bytes / 16;
+                                                                   int n_pages, int64_t page_bytes, int n_layers,
+                                                                   int64_t layer_stride) {
+  const int64_t vecs_per_piece = page_bytes / 16;
+  const int64_t vecs_per_page = vecs_per_piece * n_layers;
   const int64_t total = vecs_per_page * n_pages;
   for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < total;
        i += int64_t(gridDim.x) * blockDim.x) {
-    int64_t p = i / vecs_per_page, v = i % vecs_per_page;
-    reinterpret_cast<uint4*>(base + int64_t(pages[p]) * page_bytes)[v] = make_uint4(0, 0, 0, 0);
+    const int64_t p = i / vecs_per_page, rest = i % vecs_per_page;
+    const int64_t layer = rest / vecs_per_piece, v = rest % vecs_per_piece;
+    reinterpret_cast<uint4*>(base + int64_t(pages[p]) * page_bytes + layer * layer_stride)[v] = make_uint4(0, 0, 0, 0);
   }
 }
 
-cudaError_t launch_scrub_pages(uint8_t* base, const int32_t* d_pages, int n_pages, int64_t page_bytes,
-                               cudaStream_t stream) {
+cudaError_t launch_scrub_pages(uint8_t* base, const int32_t* d_pages, int n_pages, int64_t page_bytes, int n_layers,
+                               int64_t layer_stride, cudaStream_t stream) {
   if (n_pages <= 0) return cudaSuccess;
-  int64_t total = page_bytes / 16 * n_pages;
+  int64_t total = page_bytes / 16 * n_layers * n_pages;
   scrub_pages_kernel<<<copy_grid((total + COPY_THREADS - 1) / COPY_THREADS), COPY_THREADS, 0, stream>>>(
-      base, d_pages, n_pages, page_bytes);
+      base, d_pages, n_pages, page_bytes, n_layers, layer_stride);
   return cudaGetLastError();
 }
 

@@ -1,10 +1,13 @@
 // Page layout of the KV pool in HBM, shared by host and device code.
 //
-// pool  = [page][layer][kv_head][K tile | V tile]
-// tile  = the 16 rows of one (page, layer, kv_head) for K or for V, contiguous,
+// pool  = [layer][page][kv_head][K tile | V tile]
+// tile  = the 16 rows of one (layer, page, kv_head) for K or for V, contiguous,
 //         so a K tile and its V tile are one contiguous range that a single
-//         bulk (TMA) copy brings into shared memory, and one page (all layers)
-//         is one contiguous range for the prefix-cache block copy.
+//         bulk (TMA) copy brings into shared memory. Layer-major: the pages a
+//         decode kernel streams (one layer of every sequence) sit in one dense
+//         region instead of being a whole-page stride apart, which keeps the
+//         number of address translations a launch needs small; the prefix-cache
+//         block copy moves a page as one contiguous piece per layer.
 //
 // In-tile layouts (chosen so that the tile, copied verbatim into shared memory,
 // is read conflict-free by the tensor-core kernels):
@@ -50,8 +53,8 @@ SGK_HD int64_t row_head_bytes(int dtype, int hd) { return tile_bytes(dtype, hd) 
 // What every kernel needs to address the pool. Passed by value.
 struct PoolView {
   uint8_t* base;
-  int64_t page_bytes;   // all layers of one page
-  int64_t layer_bytes;  // kv_heads * 2 * tile
+  int64_t page_bytes;   // stride between pages inside a layer: kv_heads * 2 * tile
+  int64_t layer_bytes;  // stride between layers: num_pages * page_bytes
   int64_t tile_bytes;
   const int32_t* tables;  // [max_seqs][table_stride] page ids
   int32_t* lens;          // [max_seqs][layers] rows held, per layer
