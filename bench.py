@@ -41,7 +41,7 @@ WORKLOAD = ("C2: Qwen3-30B-A3B-shaped KV path, 48 layers, 32Q/4KV heads, head_di
             "16-token pages, shuffled block table, ctx 32768, batch 8 per GPU")
 # ncu capture of attention_mma_kernel<128> at this shape (summary kept under profiles/):
 # DRAM read+write bytes per launch divided by the algorithmic bytes of the launch.
-NCU_TRAFFIC_RATIO = 1.0076
+NCU_TRAFFIC_RATIO = 1.0093
 
 
 KV_DTYPE = "bf16"           # or "u8": 32 codes + bf16 scale + bf16 bias per group = 1.125 B per element
