@@ -124,19 +124,19 @@ __device__ __forceinline__ int arrive_acq_rel(int32_t* counter) {
 // (the {max, sum} pairs of the cell's head and the partial values) before the first
 // use, so a pass costs one L2 round trip and no block barrier. final != 0: writes the
 // normalised output; else writes one un-normalised partial (row dst_row of dst).
-template <int HD>
+template <int HD, int NT = MMA_THREADS>
 __device__ __forceinline__ void merge_block(const Partials& src, int stride, int first, int count, int gqa,
                                             int64_t qh0, bool final, float* out, const Partials& dst,
                                             int dst_stride, int dst_row, int tid) {
-  constexpr int CELLS = 2;
+  constexpr int CELLS = NT >= 256 ? 1 : 2;   // the register budget of a 256-thread block is smaller
   const int total = gqa * (HD / 4);
-  for (int base = 0; base < total; base += CELLS * MMA_THREADS) {
+  for (int base = 0; base < total; base += CELLS * NT) {
     float2 ml[CELLS][MERGE_MAX];
     float4 v[CELLS][MERGE_MAX];
     int cell[CELLS];
 #pragma unroll
     for (int c = 0; c < CELLS; ++c) {
-      cell[c] = base + c * MMA_THREADS + tid;
+      cell[c] = base + c * NT + tid;
       if (cell[c] < total) {
         const int h = cell[c] / (HD / 4), d = (cell[c] % (HD / 4)) * 4;
         const float* pm = src.ml + ((qh0 + h) * stride + first) * 2;
@@ -185,7 +185,7 @@ __device__ __forceinline__ void merge_block(const Partials& src, int stride, int
 // (o_s: [warps][8][opad] un-normalised outputs, ml_s: [warps][8] {max, sum}), writes the
 // block's partial (or the final output when there is one split), moves the device cursor
 // after a fused append, and runs the two-level merge of the splits.
-template <int HD>
+template <int HD, int NT = MMA_THREADS>
 __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s, const float* ml_s, int opad,
                                              int* flags, int seq, int kvh, int split, int gqa, bool do_append,
                                              int32_t* len_ptr, int64_t len, int tid) {
@@ -211,7 +211,7 @@ __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s
     hml_s[2 * tid + 1] = lb;
   }
   __syncthreads();
-  for (int idx = tid; idx < gqa * (HD / 4); idx += MMA_THREADS) {
+  for (int idx = tid; idx < gqa * (HD / 4); idx += NT) {
     const int h = idx / (HD / 4), d = (idx % (HD / 4)) * 4;
     float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -261,7 +261,7 @@ __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s
     if (a.splits > 1 && flags[1]) {
       // this block completed its group: merge the group (or everything, if one group)
       const bool single = a.n_groups == 1;
-      merge_block<HD>(a.part, a.splits, group_first, group_count, gqa, qh0, single, a.out, a.part2,
+      merge_block<HD, NT>(a.part, a.splits, group_first, group_count, gqa, qh0, single, a.out, a.part2,
                       a.max_groups, group, tid);
       if (tid == 0) SGK_TP(6);
       if (!single) {
@@ -273,7 +273,7 @@ __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s
         }
         __syncthreads();
         if (flags[1]) {
-          merge_block<HD>(a.part2, a.max_groups, 0, a.n_groups, gqa, qh0, true, a.out, a.part2,
+          merge_block<HD, NT>(a.part2, a.max_groups, 0, a.n_groups, gqa, qh0, true, a.out, a.part2,
                           a.max_groups, 0, tid);
           if (tid == 0) SGK_TP(7);
         }
