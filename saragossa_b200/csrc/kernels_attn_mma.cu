@@ -160,7 +160,15 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
       *reinterpret_cast<uint2*>(q_lo + f) = make_uint2(lo0, lo1);
     }
   }
-  __syncthreads();
+  // The producer only announces that the barriers exist and starts copying; the consumers wait
+  // here for that and for each other's part of Q. The first pages are then on their way while
+  // Q is still being converted.
+  if (warp == MMA_CONSUMERS) {
+    __syncwarp();
+    asm volatile("bar.arrive 3, %0;" ::"r"(MMA_THREADS) : "memory");
+  } else {
+    asm volatile("bar.sync 3, %0;" ::"r"(MMA_THREADS) : "memory");
+  }
   if (tid == 0) SGK_TP(1);
 
   if (warp == MMA_CONSUMERS) {
