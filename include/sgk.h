@@ -155,6 +155,9 @@ int32_t sgk_kv_enqueue_rope_append(sgk_kv* kv, void* stream, const float* d_k_ra
  * (src/decoder/generation.rs:3338-3361, src/decode_resident/attention.rs:550-602). */
 int32_t sgk_kv_enqueue_rope_append_rows(sgk_kv* kv, void* stream, const float* d_k_raw, const float* d_v,
                                         int64_t n_rows, const float* d_knorm_weight, const sgk_rope* rope);
+/* The single-sequence form of sgk_batch_enqueue_verify_rows (n_seq = 1). */
+int32_t sgk_kv_enqueue_verify_rows(sgk_kv* kv, void* stream, const float* d_k, const float* d_v, const float* d_q,
+                                   float* d_out, int32_t n_rows, int64_t sliding_window, float attn_scalar);
 /* DecodeResidentState::rms_norm_rope_decode (attention.rs:386-444): host in/out. */
 int32_t sgk_rms_norm_rope_decode(sgk_state* state, const float* x, const float* weight,
                                  int32_t heads, int32_t head_dim, const sgk_rope* rope,
@@ -216,6 +219,16 @@ int32_t sgk_batch_enqueue_step(sgk_batch* batch, void* stream, const float* d_k,
                                const float* d_q, float* d_out, int64_t sliding_window,
                                float attn_scalar);
 /* Tuning hooks read by the benchmark: 0 = automatic. */
+/* Speculative-decoding verify (src/decode_resident/layers.rs:1295-1433; CPU twin
+ * cached_attention_prefill_rows, src/decoder/attention_ops.rs:976-1017): n_rows draft rows
+ * go through append + attention one after the other, so the attention of row r sees exactly the
+ * rows 0 .. len+r, like n_rows single decode steps. Inputs are row-major over the rows:
+ * d_k, d_v [n_rows][n_seq][kv_dim], d_q and d_out [n_rows][n_seq][q_dim]. Capacity is checked for
+ * all rows first: an overflow is an error and writes nothing. The rejected tail is dropped with
+ * sgk_kv_truncate (src/decoder/generation.rs:1019-1022). */
+int32_t sgk_batch_enqueue_verify_rows(sgk_batch* batch, void* stream, const float* d_k, const float* d_v,
+                                      const float* d_q, float* d_out, int32_t n_rows, int64_t sliding_window,
+                                      float attn_scalar);
 int32_t sgk_batch_set_splits(sgk_batch* batch, int32_t splits);
 int32_t sgk_batch_get_splits(const sgk_batch* batch, int32_t* splits_out);
 int32_t sgk_batch_set_kernel(sgk_batch* batch, int32_t which);
@@ -252,6 +265,11 @@ int32_t sgk_linstate_write(sgk_linstate* ls, int32_t layer, const float* conv, c
 int32_t sgk_linstate_read(sgk_linstate* ls, int32_t layer, float* conv, float* ssm);
 int32_t sgk_linstate_snapshot(sgk_linstate* ls, void* stream, sgk_linstate** snapshot_out);
 int32_t sgk_linstate_restore(sgk_linstate* ls, void* stream, const sgk_linstate* snapshot);
+/* encode_capture_linear_attn_state (src/metal_backend/linear_attention.rs:93-127): copies the
+ * state into an EXISTING state of the same shape (one made ahead with sgk_linstate_create, like the
+ * reference's leased per-row captures, :44-91): enqueue only, no allocation. Shape error if the
+ * lengths or the SSM storage type differ. sgk_linstate_restore copies a capture back. */
+int32_t sgk_linstate_enqueue_capture(sgk_linstate* ls, void* stream, sgk_linstate* capture);
 void* sgk_linstate_conv_ptr(sgk_linstate* ls, int32_t layer);
 /* One decode token on a layer's state, in stream order (the "next" step of the path:
  * the state this library snapshots is also advanced here).

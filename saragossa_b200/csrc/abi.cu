@@ -546,6 +546,14 @@ int32_t sgk_kv_enqueue_append_attention(sgk_kv* kv, void* stream, const float* d
   return kv->self_batch->enqueue_attention(kv->st->pick(stream), d_q, d_out, 0, sliding_window, attn_scalar, d_k, d_v);
 }
 
+int32_t sgk_kv_enqueue_verify_rows(sgk_kv* kv, void* stream, const float* d_k, const float* d_v, const float* d_q,
+                                   float* d_out, int32_t n_rows, int64_t sliding_window, float attn_scalar) {
+  if (!kv) return fail(SGK_ERR_BACKEND, "null KV state");
+  SGK_TRY(kv->ensure_self_batch());
+  return sgk_batch_enqueue_verify_rows(static_cast<sgk_batch*>(kv->self_batch.get()), stream, d_k, d_v, d_q, d_out, n_rows,
+                                       sliding_window, attn_scalar);
+}
+
 static int32_t gather_impl(sgk_kv* kv, int64_t row0, int64_t n, int mode, void* k_out, void* v_out, uint16_t* ks,
                            uint16_t* kb, uint16_t* vs, uint16_t* vb) {
   if (!kv) return fail(SGK_ERR_BACKEND, "null KV state");
@@ -665,6 +673,25 @@ int32_t sgk_batch_enqueue_step(sgk_batch* b, void* stream, const float* d_k, con
   if (!d_k || !d_v) return fail(SGK_ERR_BACKEND, "append: null device pointer");
   if (sliding_window < 0) return fail(SGK_ERR_DIMENSION, "negative sliding window");
   return b->enqueue_attention(b->st->pick(stream), d_q, d_out, 0, sliding_window, attn_scalar, d_k, d_v);
+}
+
+int32_t sgk_batch_enqueue_verify_rows(sgk_batch* b, void* stream, const float* d_k, const float* d_v,
+                                      const float* d_q, float* d_out, int32_t n_rows, int64_t sliding_window,
+                                      float attn_scalar) {
+  if (!b) return fail(SGK_ERR_BACKEND, "null batch");
+  if (!d_k || !d_v || !d_q || !d_out) return fail(SGK_ERR_BACKEND, "verify rows: null device pointer");
+  if (sliding_window < 0) return fail(SGK_ERR_DIMENSION, "negative sliding window");
+  if (n_rows < 0) return fail(SGK_ERR_DIMENSION, "verify rows: n_rows %d invalid", n_rows);
+  for (Kv* kv : b->kvs)
+    if (kv->len() + n_rows > kv->seq->capacity)
+      return fail(SGK_ERR_DIMENSION, "append KV: capacity %lld reached (overflow)", (long long)kv->seq->capacity);
+  const size_t kv_step = size_t(b->n()) * b->kvs[0]->kv_dim();
+  const size_t q_step = size_t(b->n()) * b->q_heads * b->pool->head_dim;
+  cudaStream_t s = b->st->pick(stream);
+  for (int32_t r = 0; r < n_rows; ++r)
+    SGK_TRY(b->enqueue_attention(s, d_q + r * q_step, d_out + r * q_step, 0, sliding_window, attn_scalar,
+                                 d_k + r * kv_step, d_v + r * kv_step));
+  return SGK_OK;
 }
 
 int32_t sgk_batch_set_splits(sgk_batch* b, int32_t splits) {
@@ -923,6 +950,20 @@ int32_t sgk_linstate_restore(sgk_linstate* ls, void* stream, const sgk_linstate*
                 (long long)snap->conv_len, (long long)snap->ssm_len, int(snap->ssm_bf16), (long long)ls->conv_len,
                 (long long)ls->ssm_len, int(ls->ssm_bf16));
   SGK_CUDA(launch_copy_bytes(ls->d_base, snap->d_base, ls->total_bytes, ls->st->pick(stream)));
+  ls->st->launches += 1;
+  return SGK_OK;
+}
+
+int32_t sgk_linstate_enqueue_capture(sgk_linstate* ls, void* stream, sgk_linstate* capture) {
+  if (!ls || !capture) return fail(SGK_ERR_BACKEND, "null argument");
+  if (ls == capture) return fail(SGK_ERR_SHAPE, "capture linear-attn: the capture is the state itself");
+  // src/metal_backend/linear_attention.rs:105-124
+  if (ls->conv_len != capture->conv_len || ls->ssm_len != capture->ssm_len || ls->ssm_bf16 != capture->ssm_bf16 ||
+      ls->layers != capture->layers)
+    return fail(SGK_ERR_SHAPE, "capture linear-attn: capture conv=%lld/ssm=%lld/bf16=%d != state conv=%lld/ssm=%lld/bf16=%d",
+                (long long)capture->conv_len, (long long)capture->ssm_len, int(capture->ssm_bf16),
+                (long long)ls->conv_len, (long long)ls->ssm_len, int(ls->ssm_bf16));
+  SGK_CUDA(launch_copy_bytes(capture->d_base, ls->d_base, ls->total_bytes, ls->st->pick(stream)));
   ls->st->launches += 1;
   return SGK_OK;
 }

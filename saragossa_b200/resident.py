@@ -335,6 +335,11 @@ class FullAttentionState:
     def encode_rope_append(self, d_k_raw, d_v, d_weight, rope: Rope, stream=None):
         check(self.L.sgk_kv_enqueue_rope_append(self.h, stream, d_k_raw.ptr, d_v.ptr, d_weight.ptr, C.byref(rope)))
 
+    def encode_verify_rows(self, d_k, d_v, d_q, d_out, n_rows, sliding_window=0, attn_scalar=0.0, stream=None):
+        """Speculative verify: n_rows x (append, attention over rows 0..len+r), in stream order."""
+        check(self.L.sgk_kv_enqueue_verify_rows(self.h, stream, d_k.ptr, d_v.ptr, d_q.ptr, d_out.ptr, n_rows,
+                                                sliding_window, attn_scalar))
+
     def encode_rope_append_rows(self, d_k_raw, d_v, n_rows, d_weight, rope: Rope, stream=None):
         """Prefill producer: n_rows raw K rows normalised, rotated and stored at rows len.. in one launch."""
         check(self.L.sgk_kv_enqueue_rope_append_rows(self.h, stream, d_k_raw.ptr, d_v.ptr, n_rows, d_weight.ptr,
@@ -434,6 +439,11 @@ class Batch:
         check(self.L.sgk_batch_enqueue_step(self.h, stream, d_k.ptr, d_v.ptr, d_q.ptr, d_out.ptr, sliding_window,
                                             attn_scalar))
 
+    def enqueue_verify_rows(self, d_k, d_v, d_q, d_out, n_rows, sliding_window=0, attn_scalar=0.0, stream=None):
+        """Speculative verify of n_rows draft rows for every sequence; inputs [n_rows][n_seq][...]."""
+        check(self.L.sgk_batch_enqueue_verify_rows(self.h, stream, d_k.ptr, d_v.ptr, d_q.ptr, d_out.ptr, n_rows,
+                                                   sliding_window, attn_scalar))
+
     def set_splits(self, splits):
         check(self.L.sgk_batch_set_splits(self.h, splits))
 
@@ -530,6 +540,10 @@ class LinearAttentionState:
 
     def restore(self, snapshot, stream=None):
         check(self.L.sgk_linstate_restore(self.h, stream, snapshot.h))
+
+    def encode_capture(self, capture, stream=None):
+        """encode_capture_linear_attn_state: copy into an existing state of the same shape (no allocation)."""
+        check(self.L.sgk_linstate_enqueue_capture(self.h, stream, capture.h))
 
     def encode_conv_step(self, layer, d_qkv, d_weight, conv_dim, conv_kernel_dim, d_out, stream=None):
         """depthwise_causal_conv for one token (src/linear_attention.rs:802-852)."""
