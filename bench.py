@@ -448,15 +448,28 @@ def head_sharded_run(sg, st, torch, dist, world, rank, stream, sh, pool, seq, ba
                                         stream=stream.cuda_stream)
             dist.all_gather_into_tensor(out_full[layer], out_loc[layer])
 
+    # One decode token = 48 x (fused kernel, all-gather) as ONE CUDA graph; the pages the replays
+    # will append into are reserved before the capture (a replay moves only the device cursor).
+    seq.reserve(((CTX + steps + 8 + 15) // 16) * 16)
+    mode = "graph"
     with torch.cuda.stream(stream):
-        for _ in range(2):
-            one_step()
+        one_step()
+        stream.synchronize()
+        dist.barrier()
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                one_step()
+            run = graph.replay
+        except Exception:  # noqa: BLE001 - same code on every rank: they all fall back together
+            mode, run = "stream", one_step
+        run()
         stream.synchronize()
         dist.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for _ in range(steps):
-            one_step()
+            run()
         e1.record(stream)
         stream.synchronize()
     ms = e0.elapsed_time(e1)
@@ -471,7 +484,7 @@ def head_sharded_run(sg, st, torch, dist, world, rank, stream, sh, pool, seq, ba
     total_bytes = sum(algorithmic_bytes(CTX + 2 + i + 1) for i in range(steps)) * LAYERS
     return {"us_per_layer": ms * 1e3 / (steps * LAYERS), "hbm_gbs_aggregate": total_bytes / (ms * 1e-3) / 1e9,
             "ranks": world, "kv_heads_per_rank": sh.kv_heads, "steps": steps, "outputs_finite": finite,
-            "exchange": f"one NCCL all-gather of {world * q_loc * 4} bytes of attention output per layer"}
+            "submission": mode, "exchange": f"one NCCL all-gather of {world * q_loc * 4} bytes of attention output per layer"}
 
 
 def gated_delta_leg(sg, st, torch, stream):
