@@ -331,6 +331,7 @@ def run_ours(args):
     # ---- prefix restore: block copy of a 4096-token prefix on the 4B shape (config 4) ----
     restore = guarded(prefix_restore_gbs, sg, st, torch, stream)
     recurrent = guarded(gated_delta_leg, sg, st, torch, stream)
+    producer = guarded(bulk_append_leg, sg, st, torch, stream)
 
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -353,7 +354,7 @@ def run_ours(args):
             "decode_steps_per_s": BATCH * world * K / (ms * 1e-3),
             "batch1": {"us_per_layer": b1_us_layer, "hbm_gbs": b1_gbs, "steps": b1_steps,
                        "frac_of_peak": b1_gbs / peak},
-            "prefix_restore": restore, "head_sharded_batch1": head_sharded, "gated_delta_step": recurrent,
+            "prefix_restore": restore, "head_sharded_batch1": head_sharded, "gated_delta_step": recurrent, "bulk_append": producer,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": alg_per_launch * NCU_TRAFFIC_RATIO,
                          "kernel": "attention_mma_kernel<128> (fused append + paged decode attention)",
@@ -533,6 +534,46 @@ def gated_delta_leg(sg, st, torch, stream):
     nbytes = 2 * 4 * n * ssm_len
     return {"us_per_layer": t * 1e6, "hbm_gbs": nbytes / t / 1e9, "sequences": n, "state_bytes_per_layer": nbytes // 2,
             "outputs_finite": finite, "launches": (2 + 3 + reps) * layers}
+
+
+def bulk_append_leg(sg, st, torch, stream):
+    """The prefill-side producer on the shape of config 4 (8 KV heads x hd128): 4096 prompt rows
+    of one layer per launch, f32 in (K and V), pages out; plain bf16, with RMSNorm+RoPE on K, and
+    u8 group-32. Bytes = what is read plus what is written."""
+    kvh, hd, rows, reps = 8, 128, 4096, 8
+    kv_dim = kvh * hd
+    d_k, d_v = st.alloc(4 * rows * kv_dim), st.alloc(4 * rows * kv_dim)
+    st.fill_normal(d_k, rows * kv_dim, 91, 0, stream=stream.cuda_stream)
+    st.fill_normal(d_v, rows * kv_dim, 91, 1, stream=stream.cuda_stream)
+    d_w = st.upload(np.ones(hd, np.float32))
+    rope = sg.make_rope(hd, 1_000_000.0, eps=1e-6)
+    out = {}
+    for name, dtype, roped, store in (("bf16", sg.KV_BF16, False, 2.0), ("bf16_rope", sg.KV_BF16, True, 2.0),
+                                      ("u8", sg.KV_U8G32, False, 1.125)):
+        kv = st.full_attention(rows * (reps + 2), 32, kvh, hd, dtype)
+
+        def one():
+            if roped:
+                kv.encode_rope_append_rows(d_k, d_v, rows, d_w, rope, stream=stream.cuda_stream)
+            else:
+                kv.encode_append_rows(d_k, d_v, rows, stream=stream.cuda_stream)
+
+        one()
+        one()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        stream.synchronize()
+        st.sync()
+        e0.record(stream)
+        for _ in range(reps):
+            one()
+        e1.record(stream)
+        stream.synchronize()
+        t = e0.elapsed_time(e1) * 1e-3 / reps
+        nbytes = rows * kv_dim * (4 * 2 + store * 2)
+        out[name] = {"us_per_launch": t * 1e6, "hbm_gbs": nbytes / t / 1e9}
+        kv.close()
+    out["shape"] = f"{rows} rows x {kvh} KV heads x hd{hd} per launch, one layer"
+    return out
 
 
 def prefix_restore_gbs(sg, st, torch, stream):

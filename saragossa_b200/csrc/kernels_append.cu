@@ -163,12 +163,252 @@ __global__ void __launch_bounds__(128) append_rows_kernel(AppendArgs a) {
   }
 }
 
+
+// ---- bulk append: one block per (kv head, page, sequence) -------------------------------------
+// The rows of a multi-row append that fall into one page are one tile: the block reads them with
+// 16-byte loads, does what the single-row kernel does per row (same arithmetic, so the bits are
+// the same whichever kernel wrote a row), and writes the tile region with 16-byte stores. One
+// cursor arrival per block instead of one per row: a seeding launch of 8192 rows made 32768
+// atomic arrivals on one counter and ran at 0.9 TB/s.
+template <int N>
+__device__ __forceinline__ void quantize_groups_warp(const float (&x)[N], uint32_t (&code)[N], uint32_t (&meta)[N]) {
+  float lo[N], hi[N];
+  // warp-wide float min / max in one instruction each (sm_100a), instead of a five-step butterfly
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    asm("redux.sync.min.f32 %0, %1, 0xffffffff;" : "=f"(lo[i]) : "f"(x[i]));
+    asm("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(hi[i]) : "f"(x[i]));
+  }
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    const uint16_t bias_bits = f32_to_bf16_bits(lo[i]);
+    const float bias = bf16_bits_to_f32(bias_bits);
+    const float raw = __fdiv_rn(__fsub_rn(hi[i], bias), 255.0f);
+    const uint16_t scale_bits = f32_to_bf16_bits(fmaxf(raw, 0x1p-40f));
+    const float scale = bf16_bits_to_f32(scale_bits);
+    float t = rintf(__fdiv_rn(__fsub_rn(x[i], bias), scale));
+    t = fminf(fmaxf(t, 0.0f), 255.0f);
+    meta[i] = static_cast<uint32_t>(scale_bits) | (static_cast<uint32_t>(bias_bits) << 16);
+    code[i] = static_cast<uint32_t>(t);
+  }
+}
+
+// One (row, K or V) of a u8 tile: all groups of the head row at once, one warp.
+template <int G>
+__device__ __forceinline__ uint32_t store_u8_row(uint8_t* tile, int hd, int is_v, int rin, const float* xs, int lane) {
+  float x[G];
+  uint32_t code[G], meta[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) x[g] = xs[g * QGROUP + lane];
+  quantize_groups_warp<G>(x, code, meta);
+  uint32_t biggest = 0;
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const int dim = g * QGROUP + lane;
+    tile[is_v ? u8_v_code_index(rin, dim, hd) : u8_k_code_index(rin, dim, hd)] = static_cast<uint8_t>(code[g]);
+    biggest = max(biggest, (meta[g] & 0xffffu) << 16);
+    if (lane == g) {
+      *reinterpret_cast<uint16_t*>(tile + u8_scale_offset(rin, g, hd)) = static_cast<uint16_t>(meta[g] & 0xffffu);
+      *reinterpret_cast<uint16_t*>(tile + u8_bias_offset(is_v, rin, g, hd)) = static_cast<uint16_t>(meta[g] >> 16);
+    }
+  }
+  return biggest;
+}
+
+__global__ void __launch_bounds__(128) append_tiles_kernel(AppendArgs a) {
+  extern __shared__ float smem[];
+  const int hd = a.pool.head_dim;
+  float* ks = smem;                           // [16][hd]
+  float* vs = smem + PAGE_TOKENS * hd;        // [16][hd]
+  float* inv_s = vs + PAGE_TOKENS * hd;       // [16] 1/rms per row
+  __shared__ uint32_t big_s;
+  const int head = blockIdx.x, tile_i = blockIdx.y, seq = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int kv_dim = a.pool.kv_heads * hd;
+  const int slot = a.slots ? a.slots[seq] : a.slot0;
+  int32_t* len_ptr = a.pool.lens + int64_t(slot) * a.pool.layers + a.layer;
+  const int64_t len0 = a.use_device_len ? static_cast<int64_t>(*len_ptr) : a.row0;
+  const int64_t page_index = len0 / PAGE_TOKENS + tile_i;
+  const int64_t row_lo = max(len0, page_index * PAGE_TOKENS);
+  const int64_t row_hi = min(len0 + a.n_rows, (page_index + 1) * PAGE_TOKENS);
+  const int rows = static_cast<int>(row_hi - row_lo);
+  if (tid == 0) big_s = 0;
+
+  const bool direct = !a.has_rope && a.pool.dtype != KV_U8G32;
+  if (rows > 0 && direct) {
+    // nothing to compute across a row: registers only, no staging
+    const int rin0 = static_cast<int>(row_lo % PAGE_TOKENS);
+    const float* kbase = a.k + (int64_t(seq) * a.n_rows + (row_lo - len0)) * kv_dim + head * hd;
+    const float* vbase = a.v + (int64_t(seq) * a.n_rows + (row_lo - len0)) * kv_dim + head * hd;
+    int32_t page = -1;
+    if (page_index < a.pool.table_stride) page = a.pool.tables[int64_t(slot) * a.pool.table_stride + page_index];
+    if (page >= 0 && page < a.num_pages) {
+      uint8_t* ktile = a.pool.base + tile_offset(a.pool, page, a.layer, head, 0);
+      uint8_t* vtile = a.pool.base + tile_offset(a.pool, page, a.layer, head, 1);
+      const int chunks = hd / 8;
+      for (int i = tid; i < 2 * rows * chunks; i += blockDim.x) {
+        const int is_v = i / (rows * chunks), rest = i % (rows * chunks);
+        const int r = rest / chunks, chunk = rest % chunks;
+        const float4* src = reinterpret_cast<const float4*>((is_v ? vbase : kbase) + int64_t(r) * kv_dim + chunk * 8);
+        const float4 x0 = __ldg(src), x1 = __ldg(src + 1);
+        uint8_t* tile = is_v ? vtile : ktile;
+        if (a.pool.dtype == KV_F32) {
+          float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(tile) + (rin0 + r) * hd + chunk * 8);
+          dst[0] = x0;
+          dst[1] = x1;
+        } else {
+          const uint4 w = make_uint4(uint32_t(f32_to_bf16_bits(x0.x)) | (uint32_t(f32_to_bf16_bits(x0.y)) << 16),
+                                     uint32_t(f32_to_bf16_bits(x0.z)) | (uint32_t(f32_to_bf16_bits(x0.w)) << 16),
+                                     uint32_t(f32_to_bf16_bits(x1.x)) | (uint32_t(f32_to_bf16_bits(x1.y)) << 16),
+                                     uint32_t(f32_to_bf16_bits(x1.z)) | (uint32_t(f32_to_bf16_bits(x1.w)) << 16));
+          *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(tile) + bf16_elem_index(rin0 + r, chunk * 8, hd)) = w;
+        }
+      }
+    } else if (tid == 0) {
+      atomicExch(a.status, DEV_ERR_BAD_PAGE);
+    }
+  } else if (rows > 0) {
+    const int rin0 = static_cast<int>(row_lo % PAGE_TOKENS);
+    const int vec_per_row = hd / 4;
+    const float* kbase = a.k + (int64_t(seq) * a.n_rows + (row_lo - len0)) * kv_dim + head * hd;
+    const float* vbase = a.v + (int64_t(seq) * a.n_rows + (row_lo - len0)) * kv_dim + head * hd;
+    for (int i = tid; i < rows * vec_per_row; i += blockDim.x) {
+      const int r = i / vec_per_row, c = i % vec_per_row;
+      reinterpret_cast<float4*>(ks + r * hd)[c] = __ldg(reinterpret_cast<const float4*>(kbase + int64_t(r) * kv_dim) + c);
+      reinterpret_cast<float4*>(vs + r * hd)[c] = __ldg(reinterpret_cast<const float4*>(vbase + int64_t(r) * kv_dim) + c);
+    }
+    __syncthreads();
+    if (a.has_rope) {
+      // same float order as norm_rope_head, one thread per row for the sequential sums
+      if (tid < rows) {
+        const float* xs = ks + tid * hd;
+        float sum = 0.0f;
+        for (int c = 0; c < hd; ++c) sum = __fadd_rn(sum, __fmul_rn(xs[c], xs[c]));
+        const float mean_square = __fdiv_rn(sum, static_cast<float>(hd));
+        inv_s[tid] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean_square, a.rope.eps)));
+      }
+      __syncthreads();
+      for (int i = tid; i < rows * hd; i += blockDim.x) {
+        const int r = i / hd, c = i % hd;
+        ks[i] = __fmul_rn(__fmul_rn(ks[i], inv_s[r]), a.knorm_w[c]);
+      }
+      __syncthreads();
+      const int pairs = a.rope.rope_dims / 2;
+      // theta^(2i/d) depends on the pair only: once per pair, not once per (row, pair)
+      float* denom_s = vs + PAGE_TOKENS * hd + PAGE_TOKENS;   // [pairs], behind inv_s
+      for (int pair = tid; pair < pairs; pair += blockDim.x) {
+        const float exponent = __fdiv_rn(static_cast<float>(2 * pair), static_cast<float>(a.rope.frequency_dim));
+        denom_s[pair] = static_cast<float>(pow(static_cast<double>(a.rope.theta), static_cast<double>(exponent)));
+      }
+      __syncthreads();
+      for (int i = tid; i < rows * pairs; i += blockDim.x) {
+        const int r = i / pairs, pair = i % pairs;
+        float* xs = ks + r * hd;
+        const float scaled_position = __fmul_rn(static_cast<float>(row_lo + r), a.rope.position_scale);
+        const float angle = __fdiv_rn(scaled_position, denom_s[pair]);
+        double sd, cd;
+        sincos(static_cast<double>(angle), &sd, &cd);
+        const float c = static_cast<float>(cd);
+        const float s = static_cast<float>(sd);
+        const int i0 = a.rope.interleaved ? 2 * pair : pair;
+        const int i1 = a.rope.interleaved ? 2 * pair + 1 : pair + pairs;
+        const float first = xs[i0], second = xs[i1];
+        xs[i0] = __fsub_rn(__fmul_rn(first, c), __fmul_rn(second, s));
+        xs[i1] = __fadd_rn(__fmul_rn(first, s), __fmul_rn(second, c));
+      }
+      __syncthreads();
+    }
+
+    int32_t page = -1;
+    if (page_index < a.pool.table_stride) page = a.pool.tables[int64_t(slot) * a.pool.table_stride + page_index];
+    if (page >= 0 && page < a.num_pages) {
+      uint8_t* ktile = a.pool.base + tile_offset(a.pool, page, a.layer, head, 0);
+      uint8_t* vtile = a.pool.base + tile_offset(a.pool, page, a.layer, head, 1);
+      if (a.pool.dtype == KV_F32) {
+        for (int i = tid; i < rows * vec_per_row; i += blockDim.x) {
+          const int r = i / vec_per_row, c = i % vec_per_row;
+          reinterpret_cast<float4*>(reinterpret_cast<float*>(ktile) + (rin0 + r) * hd)[c] = reinterpret_cast<const float4*>(ks + r * hd)[c];
+          reinterpret_cast<float4*>(reinterpret_cast<float*>(vtile) + (rin0 + r) * hd)[c] = reinterpret_cast<const float4*>(vs + r * hd)[c];
+        }
+      } else if (a.pool.dtype == KV_BF16) {
+        const int chunks = hd / 8;
+        for (int i = tid; i < 2 * rows * chunks; i += blockDim.x) {
+          const int is_v = i / (rows * chunks), rest = i % (rows * chunks);
+          const int r = rest / chunks, chunk = rest % chunks;
+          const float* xs = (is_v ? vs : ks) + r * hd + chunk * 8;
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            w[e] = static_cast<uint32_t>(f32_to_bf16_bits(xs[2 * e])) | (static_cast<uint32_t>(f32_to_bf16_bits(xs[2 * e + 1])) << 16);
+          uint16_t* dst = reinterpret_cast<uint16_t*>(is_v ? vtile : ktile);
+          *reinterpret_cast<uint4*>(dst + bf16_elem_index(rin0 + r, chunk * 8, hd)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      } else {
+        uint32_t biggest = 0;
+        // a full tile is put together in shared memory and leaves with 16-byte stores; a
+        // partial one (first or last page of the append) is written in place, byte by byte
+        const int tile_b = static_cast<int>(a.pool.tile_bytes);
+        uint8_t* stage = reinterpret_cast<uint8_t*>(vs + PAGE_TOKENS * hd + PAGE_TOKENS + 128);
+        const bool full = rows == PAGE_TOKENS;
+        for (int task = warp; task < 2 * rows; task += blockDim.x / 32) {
+          const int is_v = task / rows, r = task % rows;
+          const float* xs = (is_v ? vs : ks) + r * hd;
+          uint8_t* tile = full ? stage + is_v * tile_b : (is_v ? vtile : ktile);
+          if (hd == 256) biggest = max(biggest, store_u8_row<8>(tile, hd, is_v, rin0 + r, xs, lane));
+          else if (hd == 128) biggest = max(biggest, store_u8_row<4>(tile, hd, is_v, rin0 + r, xs, lane));
+          else biggest = max(biggest, store_u8_row<2>(tile, hd, is_v, rin0 + r, xs, lane));
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) biggest = max(biggest, __shfl_xor_sync(0xffffffffu, biggest, off));
+        if (lane == 0) atomicMax(&big_s, biggest);
+        __syncthreads();
+        if (full) {
+          // the K tile and the V tile are neighbours in the page: one contiguous range
+          const uint4* src = reinterpret_cast<const uint4*>(stage);
+          uint4* dst = reinterpret_cast<uint4*>(ktile);
+          for (int i = tid; i < 2 * tile_b / 16; i += blockDim.x) dst[i] = src[i];
+        }
+        // largest scale of the pool (positive floats order like their bit patterns)
+        if (tid == 0 && a.pool.scale_max != nullptr && big_s > *reinterpret_cast<volatile uint32_t*>(a.pool.scale_max))
+          atomicMax(a.pool.scale_max, big_s);
+      }
+    } else if (tid == 0) {
+      atomicExch(a.status, DEV_ERR_BAD_PAGE);
+    }
+  }
+
+  if (a.bump_len) {
+    // The block that arrives last moves the cursor: every block has read it by then.
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence();
+      int total = gridDim.x * gridDim.y;
+      int old = atomicAdd(a.done_counters + seq, 1);
+      if (old == total - 1) {
+        *len_ptr = static_cast<int32_t>(len0 + a.n_rows);
+        a.done_counters[seq] = 0;
+        __threadfence();
+      }
+    }
+  }
+}
+
 __global__ void set_len_kernel(int32_t* ptr, int n, int32_t value) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) ptr[i] = value;
 }
 
 cudaError_t launch_append_rows(const AppendArgs& a, int n_seq, cudaStream_t stream) {
+  const int hd = a.pool.head_dim;
+  if (a.n_rows >= 4 && a.out_k == nullptr && (hd == 64 || hd == 128 || hd == 256)) {
+    // bulk: one block per page tile; the first row may sit anywhere in its page, so one tile more
+    dim3 grid(a.pool.kv_heads, (a.n_rows + PAGE_TOKENS - 1) / PAGE_TOKENS + 1, n_seq);
+    // K rows, V rows, 1/rms per row, rope denominators (<= 128 pairs), a u8 tile pair being put together
+    size_t smem = (2 * size_t(PAGE_TOKENS) * hd + PAGE_TOKENS + 128) * sizeof(float);
+    if (a.pool.dtype == KV_U8G32) smem += 2 * size_t(a.pool.tile_bytes);
+    append_tiles_kernel<<<grid, 128, smem, stream>>>(a);
+    return cudaGetLastError();
+  }
   dim3 grid(a.pool.kv_heads, a.n_rows, n_seq);
   size_t smem = (2 * size_t(a.pool.head_dim) + 4) * sizeof(float);
   append_rows_kernel<<<grid, 128, smem, stream>>>(a);
