@@ -246,22 +246,40 @@ __global__ void __launch_bounds__(128) append_tiles_kernel(AppendArgs a) {
       uint8_t* ktile = a.pool.base + tile_offset(a.pool, page, a.layer, head, 0);
       uint8_t* vtile = a.pool.base + tile_offset(a.pool, page, a.layer, head, 1);
       const int chunks = hd / 8;
-      for (int i = tid; i < 2 * rows * chunks; i += blockDim.x) {
-        const int is_v = i / (rows * chunks), rest = i % (rows * chunks);
-        const int r = rest / chunks, chunk = rest % chunks;
-        const float4* src = reinterpret_cast<const float4*>((is_v ? vbase : kbase) + int64_t(r) * kv_dim + chunk * 8);
-        const float4 x0 = __ldg(src), x1 = __ldg(src + 1);
-        uint8_t* tile = is_v ? vtile : ktile;
-        if (a.pool.dtype == KV_F32) {
-          float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(tile) + (rin0 + r) * hd + chunk * 8);
-          dst[0] = x0;
-          dst[1] = x1;
-        } else {
-          const uint4 w = make_uint4(uint32_t(f32_to_bf16_bits(x0.x)) | (uint32_t(f32_to_bf16_bits(x0.y)) << 16),
-                                     uint32_t(f32_to_bf16_bits(x0.z)) | (uint32_t(f32_to_bf16_bits(x0.w)) << 16),
-                                     uint32_t(f32_to_bf16_bits(x1.x)) | (uint32_t(f32_to_bf16_bits(x1.y)) << 16),
-                                     uint32_t(f32_to_bf16_bits(x1.z)) | (uint32_t(f32_to_bf16_bits(x1.w)) << 16));
-          *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(tile) + bf16_elem_index(rin0 + r, chunk * 8, hd)) = w;
+      const int total = 2 * rows * chunks;
+      // four chunks of eight values per thread and pass, every load issued before the first store
+      constexpr int U = 4;
+      for (int base = 0; base < total; base += U * blockDim.x) {
+        float4 x0[U], x1[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int i = base + u * blockDim.x + tid;
+          if (i < total) {
+            const int is_v = i / (rows * chunks), rest = i % (rows * chunks);
+            const int r = rest / chunks, chunk = rest % chunks;
+            const float4* src = reinterpret_cast<const float4*>((is_v ? vbase : kbase) + int64_t(r) * kv_dim + chunk * 8);
+            x0[u] = __ldg(src);
+            x1[u] = __ldg(src + 1);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int i = base + u * blockDim.x + tid;
+          if (i >= total) continue;
+          const int is_v = i / (rows * chunks), rest = i % (rows * chunks);
+          const int r = rest / chunks, chunk = rest % chunks;
+          uint8_t* tile = is_v ? vtile : ktile;
+          if (a.pool.dtype == KV_F32) {
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(tile) + (rin0 + r) * hd + chunk * 8);
+            dst[0] = x0[u];
+            dst[1] = x1[u];
+          } else {
+            const uint4 w = make_uint4(uint32_t(f32_to_bf16_bits(x0[u].x)) | (uint32_t(f32_to_bf16_bits(x0[u].y)) << 16),
+                                       uint32_t(f32_to_bf16_bits(x0[u].z)) | (uint32_t(f32_to_bf16_bits(x0[u].w)) << 16),
+                                       uint32_t(f32_to_bf16_bits(x1[u].x)) | (uint32_t(f32_to_bf16_bits(x1[u].y)) << 16),
+                                       uint32_t(f32_to_bf16_bits(x1[u].z)) | (uint32_t(f32_to_bf16_bits(x1[u].w)) << 16));
+            *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(tile) + bf16_elem_index(rin0 + r, chunk * 8, hd)) = w;
+          }
         }
       }
     } else if (tid == 0) {
