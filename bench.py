@@ -332,6 +332,8 @@ def run_ours(args):
     restore = guarded(prefix_restore_gbs, sg, st, torch, stream)
     recurrent = guarded(gated_delta_leg, sg, st, torch, stream)
     producer = guarded(bulk_append_leg, sg, st, torch, stream)
+    c3 = guarded(c3_token_leg, sg, st, torch, stream)
+    c5 = guarded(c5_serving_leg, sg, st, torch, stream)
 
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -354,7 +356,7 @@ def run_ours(args):
             "decode_steps_per_s": BATCH * world * K / (ms * 1e-3),
             "batch1": {"us_per_layer": b1_us_layer, "hbm_gbs": b1_gbs, "steps": b1_steps,
                        "frac_of_peak": b1_gbs / peak},
-            "prefix_restore": restore, "head_sharded_batch1": head_sharded, "gated_delta_step": recurrent, "bulk_append": producer,
+            "prefix_restore": restore, "head_sharded_batch1": head_sharded, "gated_delta_step": recurrent, "bulk_append": producer, "c3_hybrid_token": c3, "c5_serving": c5,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": alg_per_launch * NCU_TRAFFIC_RATIO,
                          "kernel": "attention_mma_kernel<128> (fused append + paged decode attention)",
@@ -534,6 +536,173 @@ def gated_delta_leg(sg, st, torch, stream):
     nbytes = 2 * 4 * n * ssm_len
     return {"us_per_layer": t * 1e6, "hbm_gbs": nbytes / t / 1e9, "sequences": n, "state_bytes_per_layer": nbytes // 2,
             "outputs_finite": finite, "launches": (2 + 3 + reps) * layers}
+
+
+def c3_token_leg(sg, st, torch, stream):
+    """Config 3 as it is stated: one sequence, 40 layers, every 4th a full-attention layer
+    (16 Q / 2 KV heads, hd256, u8 group-32 pages, context 32768), the other 30 recurrent
+    (32 heads x 128 x 128 f32 state + conv history of 8192 channels, kernel 4). One token of the
+    whole KV path (fused append+attention, conv step, gated-delta step) as ONE CUDA graph."""
+    layers, qh, kvh, hd, ctx = 40, 16, 2, 256, CTX
+    attn_layers = [i for i in range(layers) if (i + 1) % 4 == 0]
+    rec_layers = [i for i in range(layers) if (i + 1) % 4 != 0]
+    kv_dim, q_dim = kvh * hd, qh * hd
+    shape = (16, 32, 128, 128)
+    hk, hv, dk, dv = shape
+    conv_dim, kernel = 2 * hk * dk + hv * dv, 4
+    cap = ((ctx + 64 + 15) // 16) * 16
+    pool = st.pool(len(attn_layers), kvh, hd, sg.KV_U8G32, cap // 16 + 2, 1, cap)
+    pool.shuffle_free_list(5)
+    seq = pool.sequence(cap)
+    kvs = [seq.layer(i, qh) for i in range(len(attn_layers))]
+    chunk = 8192
+    dk_, dv_ = st.alloc(chunk * kv_dim * 4), st.alloc(chunk * kv_dim * 4)
+    for i, kv in enumerate(kvs):
+        for c in range(0, ctx, chunk):
+            n = min(chunk, ctx - c)
+            st.fill_normal(dk_, n * kv_dim, 3, 2 * i, c * kv_dim)
+            st.fill_normal(dv_, n * kv_dim, 3, 2 * i + 1, c * kv_dim)
+            kv.encode_append_rows(dk_, dv_, n)
+    st.sync()
+    seq.reserve(cap)
+    batches = [sg.Batch(st, [kv]) for kv in kvs]
+    ls = sg.LinearAttentionState(st, len(rec_layers), (kernel - 1) * conv_dim, hv * dv * dk)
+    bufs = {}
+    for name, n, scale in (("k", kv_dim, 1.0), ("v", kv_dim, 1.0), ("q", q_dim, 1.0), ("gq", hk * dk, 1.0 / dk),
+                           ("gk", hk * dk, dk ** -0.5), ("gv", hv * dv, 1.0), ("x", conv_dim, 1.0),
+                           ("w", conv_dim * kernel, 0.5)):
+        b = st.alloc(4 * n)
+        st.fill_normal(b, n, 4, len(bufs))
+        st.sync()
+        bufs[name] = st.upload(b.download(count=n) * np.float32(scale))
+    bufs["g"] = st.upload(np.full(hv, 0.97, np.float32))
+    bufs["beta"] = st.upload(np.full(hv, 0.5, np.float32))
+    d_out, d_y, d_c = st.alloc(4 * q_dim), st.alloc(4 * hv * dv), st.alloc(4 * conv_dim)
+
+    def token():
+        a = r = 0
+        for layer in range(layers):
+            if layer in attn_layers:
+                batches[a].enqueue_step(bufs["k"], bufs["v"], bufs["q"], d_out, stream=stream.cuda_stream)
+                a += 1
+            else:
+                ls.encode_conv_step(r, bufs["x"], bufs["w"], conv_dim, kernel, d_c, stream=stream.cuda_stream)
+                ls.encode_gated_delta_step(r, shape, bufs["gq"], bufs["gk"], bufs["gv"], bufs["g"], bufs["beta"], d_y,
+                                           stream=stream.cuda_stream)
+                r += 1
+
+    token()
+    stream.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        token()
+    reps = 20
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        stream.synchronize()
+        e0.record(stream)
+        for _ in range(reps):
+            graph.replay()
+        e1.record(stream)
+        stream.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / reps
+    kv_bytes = len(attn_layers) * ctx * kv_dim * 2 * 1.125
+    state_bytes = len(rec_layers) * 2 * 4 * hv * dv * dk
+    finite = bool(np.isfinite(d_out.download(count=q_dim)).all() and np.isfinite(d_y.download(count=hv * dv)).all())
+    for b in batches:
+        b.close()
+    ls.close()
+    seq.close()
+    pool.close()
+    return {"us_per_token": us, "launches_per_token": len(attn_layers) + 2 * len(rec_layers),
+            "hbm_gbs": (kv_bytes + state_bytes) / (us * 1e-6) / 1e9, "kv_bytes": kv_bytes, "state_bytes": state_bytes,
+            "outputs_finite": finite, "device_status": st.device_status(),
+            "shape": "batch 1, ctx 32768: 10 x (16Q/2KV hd256 u8-g32) + 30 x (32 x 128 x 128 f32 state)"}
+
+
+def c5_serving_leg(sg, st, torch, stream):
+    """Config 5's per-GPU share at 8 GPUs: 32 of the 256 sequences, 34 layers (global iff
+    (i + 1) % 6 == 0, the others sliding over 1024 rows), 8 Q / 4 KV heads, hd256, bf16 pages,
+    context lengths uniform in [1024, 32768] (seed 2). Sliding layers live in their own pool and
+    hold only the pages of the window (older pages are released). One decode token for all
+    sequences = 34 launches in one CUDA graph."""
+    n_seq, layers, qh, kvh, hd, window = 32, 34, 8, 4, 256, 1024
+    kv_dim, q_dim = kvh * hd, qh * hd
+    g_layers = [i for i in range(layers) if (i + 1) % 6 == 0]
+    s_layers = [i for i in range(layers) if (i + 1) % 6 != 0]
+    rng = np.random.default_rng(2)
+    lens = [int(x) for x in rng.integers(1024, 32769, size=256)][:n_seq]
+    steps = 8
+    cap = ((32768 + steps + 32 + 15) // 16) * 16
+    pages_g = sum((n + steps + 32 + 15) // 16 for n in lens) + 8
+    pages_s = n_seq * (window // 16 + 4) + cap // 16 + 8
+    pool_g = st.pool(len(g_layers), kvh, hd, sg.KV_BF16, pages_g, n_seq, cap)
+    pool_s = st.pool(len(s_layers), kvh, hd, sg.KV_BF16, pages_s, n_seq, cap)
+    pool_g.shuffle_free_list(6)
+    pool_s.shuffle_free_list(7)
+    # a capture reserves every page up to a sequence's capacity: the capacity is its own length
+    # plus the rows this leg appends, not the longest context of the config
+    own = [((n + steps + 32 + 15) // 16) * 16 for n in lens]
+    seqs_g = [pool_g.sequence(c) for c in own]
+    seqs_s = [pool_s.sequence(c) for c in own]
+    chunk = 8192
+    dk_, dv_ = st.alloc(chunk * kv_dim * 4), st.alloc(chunk * kv_dim * 4)
+    st.fill_normal(dk_, chunk * kv_dim, 8, 0)
+    st.fill_normal(dv_, chunk * kv_dim, 8, 1)
+    kv_of = {}
+    for b, n in enumerate(lens):
+        for li, layer in enumerate(g_layers):
+            kv = seqs_g[b].layer(li, qh)
+            for c in range(0, n, chunk):
+                kv.encode_append_rows(dk_, dv_, min(chunk, n - c))
+            kv_of[b, layer] = kv
+        for li, layer in enumerate(s_layers):
+            kv = seqs_s[b].layer(li, qh)
+            for c in range(0, n, chunk):
+                kv.encode_append_rows(dk_, dv_, min(chunk, n - c))
+            kv_of[b, layer] = kv
+        st.sync()
+        seqs_s[b].release_before(max(n - window, 0))     # rows before the window are never read again
+    batches = [sg.Batch(st, [kv_of[b, layer] for b in range(n_seq)]) for layer in range(layers)]
+    step = sg.Step(st, batches)
+    d_k, d_v = st.alloc(4 * layers * n_seq * kv_dim), st.alloc(4 * layers * n_seq * kv_dim)
+    d_q, d_out = st.alloc(4 * layers * n_seq * q_dim), st.alloc(4 * layers * n_seq * q_dim)
+    st.fill_normal(d_k, layers * n_seq * kv_dim, 9, 0)
+    st.fill_normal(d_v, layers * n_seq * kv_dim, 9, 1)
+    st.fill_normal(d_q, layers * n_seq * q_dim, 9, 2)
+    st.sync()
+    windows = [0 if layer in g_layers else window for layer in range(layers)]
+    step.capture(d_k, d_v, d_q, d_out, sliding_windows=windows)
+    for _ in range(2):
+        step.replay(stream.cuda_stream)
+    stream.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        step.replay(stream.cuda_stream)
+    e1.record(stream)
+    stream.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    row_bytes = kv_dim * 2 * 2
+    alg = sum(len(g_layers) * (n + 3) * row_bytes + len(s_layers) * min(n + 3, window) * row_bytes for n in lens)
+    held_s = pool_s.num_pages - pool_s.free_pages
+    finite = bool(np.isfinite(d_out.download(count=n_seq * q_dim)).all())
+    status = st.device_status()
+    step.close()
+    for b in batches:
+        b.close()
+    for s_ in seqs_g + seqs_s:
+        s_.close()
+    pool_g.close()
+    pool_s.close()
+    return {"ms_per_token_step": ms, "us_per_layer": ms * 1e3 / layers, "decode_steps_per_s": n_seq / (ms * 1e-3),
+            "hbm_gbs": alg / (ms * 1e-3) / 1e9, "sequences": n_seq, "mean_context": float(np.mean(lens)),
+            "sliding_pool_pages_held": int(held_s), "sliding_pool_pages_if_kept": int(sum((n + 15) // 16 for n in lens)),
+            "outputs_finite": finite, "device_status": status,
+            "shape": "32 of config 5's 256 sequences (its share of one of 8 GPUs): 5 global + 29 sliding-1024 layers, "
+                     "8Q/4KV hd256 bf16, contexts U(1k,32k) seed 2"}
 
 
 def bulk_append_leg(sg, st, torch, stream):

@@ -134,6 +134,7 @@ struct Batch {
   float* d_part2_o = nullptr;   // second merge level
   float* d_part2_ml = nullptr;
   int32_t* d_group_counters = nullptr;
+  int uniform_splits = 1;
   int max_splits = 1;
   int max_groups = 1;
   int splits_override = 0;

@@ -256,7 +256,9 @@ int create_batch(State* st, Kv** kvs, int n, Batch** out) {
   const int heads = std::max(b->q_heads, b->pool->kv_heads);
   // Splits never need to exceed about two blocks per SM for the whole launch.
   int by_sm = (2 * st->sm_count) / (n * b->pool->kv_heads);
-  b->max_splits = std::min(144, std::max(1, by_sm));  // two merge levels of at most 12 partials each
+  b->uniform_splits = std::min(144, std::max(1, by_sm));  // two merge levels of at most 12 partials each
+  // an uneven batch cuts its long sequences finer than that (the workspace is sized for it)
+  b->max_splits = n > 1 ? std::max(b->uniform_splits, 16) : b->uniform_splits;
   SGK_CUDA(cudaMalloc(&b->d_slots, size_t(n) * sizeof(int32_t)));
   SGK_CUDA(cudaMemcpy(b->d_slots, slots.data(), size_t(n) * sizeof(int32_t), cudaMemcpyHostToDevice));
   size_t counters = size_t(n) * heads + 2 * size_t(n);
@@ -300,7 +302,7 @@ int Batch::choose_splits(int kernel, int64_t max_rows) const {
     const int64_t pages = (max_rows + PAGE_TOKENS - 1) / PAGE_TOKENS;
     const int min_pages = kernel >= 2 ? 8 : 2;
     int64_t cap = std::max<int64_t>(1, pages / min_pages);
-    cap = std::min<int64_t>(cap, max_splits);
+    cap = std::min<int64_t>(cap, uniform_splits);
     int best = 1;
     double best_eff = 0.0;
     for (int c = 1; c <= cap; ++c) {
@@ -408,6 +410,28 @@ int Batch::enqueue_attention(cudaStream_t stream, const float* d_q, float* d_out
   float scalar = attn_scalar > 0.0f ? attn_scalar : static_cast<float>(pool->head_dim);
   a.scale_log2e = 1.4426950408889634f / std::sqrt(scalar);
   a.splits = choose_splits(kernel, max_rows);
+  a.pages_per_split = 0;
+  if (kernel >= 2 && splits_override <= 0 && n() > 1) {
+    // Uneven batch (longest sequence more than a quarter above the shortest): equal split counts
+    // would make the launch as long as its longest block. Cut every sequence into pieces of the
+    // same size instead, about three waves of blocks in all, and let the scheduler balance them.
+    int64_t lo = INT64_MAX, hi = 0, total = 0;
+    for (Kv* kv : kvs) {
+      int64_t rows = kv->len() + (fused ? 1 : 0);
+      if (sliding_window > 0) rows = std::min<int64_t>(rows, sliding_window + PAGE_TOKENS);
+      else rows -= std::min<int64_t>(rows, window_start);
+      const int64_t pages = (rows + PAGE_TOKENS - 1) / PAGE_TOKENS;
+      lo = std::min(lo, pages), hi = std::max(hi, pages), total += pages;
+    }
+    if (hi * 4 > lo * 5 && hi >= 32) {
+      const int64_t slots = int64_t(st->sm_count) * 2;
+      int64_t pps = (total * pool->kv_heads + slots * 3 - 1) / (slots * 3);
+      pps = std::max<int64_t>(pps, 8);
+      const int64_t need = (hi + pps - 1) / pps + 1;   // one spare: lengths grow while a graph is replayed
+      a.splits = static_cast<int>(std::min<int64_t>(need, max_splits));
+      a.pages_per_split = static_cast<int32_t>(pps);
+    }
+  }
   a.part.o = d_part_o;
   a.part.ml = d_part_ml;
   a.part2.o = d_part2_o;

@@ -47,6 +47,7 @@ struct AttnArgs {
   float* out;            // [n_seq][q_heads*head_dim]
   int64_t window_start;     // explicit start row when sliding_window == 0
   int64_t sliding_window;   // > 0: start = max(len - window, 0)
+  int32_t pages_per_split;  // > 0: a sequence is cut into ceil(pages / this) splits (<= splits), blocks beyond exit
   float scale_log2e;        // log2(e) / sqrt(attn_scalar)
   int32_t splits;
   Partials part;

@@ -188,8 +188,16 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
   const int64_t p_first = ws / PAGE_TOKENS;
   const int64_t p_last = (len - 1) / PAGE_TOKENS;
   const int64_t n_pages = p_last - p_first + 1;
-  const int64_t pb = p_first + (n_pages * split) / a.splits;
-  const int64_t pe = p_first + (n_pages * (split + 1)) / a.splits;
+  // Sequences of one launch may differ a lot in length: each is cut into its own number of
+  // splits of about pages_per_split pages, and the blocks beyond that number have nothing to do.
+  int splits = a.splits;
+  if (a.pages_per_split > 0) {
+    const int64_t want = (n_pages + a.pages_per_split - 1) / a.pages_per_split;
+    splits = static_cast<int>(want < 1 ? 1 : (want > a.splits ? a.splits : want));
+  }
+  if (split >= splits) return;
+  const int64_t pb = p_first + (n_pages * split) / splits;
+  const int64_t pe = p_first + (n_pages * (split + 1)) / splits;
   const int my_pages = static_cast<int>(pe - pb);
   const int32_t* table = a.pool.tables + int64_t(slot) * a.pool.table_stride;
   const int64_t head_off = int64_t(a.layer) * a.pool.layer_bytes + int64_t(kvh) * 2 * a.pool.tile_bytes;
@@ -607,7 +615,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
     }
   }
   __syncthreads();
-  finish_block<HD>(a, o_s, ml_s, S::OPAD, flags, seq, kvh, split, gqa, do_append, len_ptr, len, tid);
+  finish_block<HD>(a, o_s, ml_s, S::OPAD, flags, seq, kvh, split, gqa, do_append, len_ptr, len, tid, splits);
 }
 
 bool attention_u8_supported(int dtype, int head_dim, int gqa) {

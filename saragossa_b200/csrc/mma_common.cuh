@@ -188,7 +188,9 @@ __device__ __forceinline__ void merge_block(const Partials& src, int stride, int
 template <int HD, int NT = MMA_THREADS>
 __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s, const float* ml_s, int opad,
                                              int* flags, int seq, int kvh, int split, int gqa, bool do_append,
-                                             int32_t* len_ptr, int64_t len, int tid) {
+                                             int32_t* len_ptr, int64_t len, int tid, int splits) {
+  // `splits` is this sequence's own split count (<= a.splits, the stride of the partial arrays)
+  const int n_groups = (splits + a.group_size - 1) / a.group_size;
   if (tid == 0) SGK_TP(4);
   // ---- merge the consumer warps; write the partial or the final output ----
   // ml_s holds [warps][8]{max, sum}; behind it: the per-(head, warp) weights and the block's
@@ -223,7 +225,7 @@ __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s
       o.z += v.z * wg;
       o.w += v.w * wg;
     }
-    if (a.splits == 1) {
+    if (splits == 1) {
       const float inv = 1.0f / hml_s[2 * h + 1];
       *reinterpret_cast<float4*>(a.out + (qh0 + h) * HD + d) = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
     } else {
@@ -233,22 +235,22 @@ __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s
             make_float2(hml_s[2 * h], hml_s[2 * h + 1]);
     }
   }
-  if (a.splits > 1 || do_append) {
+  if (splits > 1 || do_append) {
     const int group = split / a.group_size;
     const int group_first = group * a.group_size;
-    const int group_count = min(a.group_size, a.splits - group_first);
+    const int group_count = min(a.group_size, splits - group_first);
     int32_t* group_counter = a.group_counters + (int64_t(seq) * a.pool.kv_heads + kvh) * a.max_groups + group;
     int32_t* head_counter = a.head_counters + int64_t(seq) * a.pool.kv_heads + kvh;
     __syncthreads();
     if (tid == 0) {
-      if (a.splits > 1) {
+      if (splits > 1) {
         int old = arrive_acq_rel(group_counter);
         flags[1] = (old == group_count - 1);
         if (flags[1]) *group_counter = 0;
       }
       if (do_append) {
         // the block that arrives last for the sequence moves the cursor
-        int total = a.splits * a.pool.kv_heads;
+        int total = splits * a.pool.kv_heads;
         int old = arrive_acq_rel(a.seq_counters + seq);
         if (old == total - 1) {
           *len_ptr = static_cast<int32_t>(len);
@@ -258,9 +260,9 @@ __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s
     }
     __syncthreads();
     if (tid == 0) SGK_TP(5);
-    if (a.splits > 1 && flags[1]) {
+    if (splits > 1 && flags[1]) {
       // this block completed its group: merge the group (or everything, if one group)
-      const bool single = a.n_groups == 1;
+      const bool single = n_groups == 1;
       merge_block<HD, NT>(a.part, a.splits, group_first, group_count, gqa, qh0, single, a.out, a.part2,
                       a.max_groups, group, tid);
       if (tid == 0) SGK_TP(6);
@@ -268,12 +270,12 @@ __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s
         __syncthreads();
         if (tid == 0) {
           int old = arrive_acq_rel(head_counter);
-          flags[1] = (old == a.n_groups - 1);
+          flags[1] = (old == n_groups - 1);
           if (flags[1]) *head_counter = 0;
         }
         __syncthreads();
         if (flags[1]) {
-          merge_block<HD, NT>(a.part2, a.max_groups, 0, a.n_groups, gqa, qh0, true, a.out, a.part2,
+          merge_block<HD, NT>(a.part2, a.max_groups, 0, n_groups, gqa, qh0, true, a.out, a.part2,
                           a.max_groups, 0, tid);
           if (tid == 0) SGK_TP(7);
         }
