@@ -334,6 +334,7 @@ def run_ours(args):
     producer = guarded(bulk_append_leg, sg, st, torch, stream)
     c3 = guarded(c3_token_leg, sg, st, torch, stream)
     c5 = guarded(c5_serving_leg, sg, st, torch, stream)
+    c4 = guarded(c4_prefix_leg, sg, st, torch, stream)
 
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -356,7 +357,7 @@ def run_ours(args):
             "decode_steps_per_s": BATCH * world * K / (ms * 1e-3),
             "batch1": {"us_per_layer": b1_us_layer, "hbm_gbs": b1_gbs, "steps": b1_steps,
                        "frac_of_peak": b1_gbs / peak},
-            "prefix_restore": restore, "head_sharded_batch1": head_sharded, "gated_delta_step": recurrent, "bulk_append": producer, "c3_hybrid_token": c3, "c5_serving": c5,
+            "prefix_restore": restore, "head_sharded_batch1": head_sharded, "gated_delta_step": recurrent, "bulk_append": producer, "c3_hybrid_token": c3, "c5_serving": c5, "c4_prefix_turns": c4,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": alg_per_launch * NCU_TRAFFIC_RATIO,
                          "kernel": "attention_mma_kernel<128> (fused append + paged decode attention)",
@@ -620,6 +621,101 @@ def c3_token_leg(sg, st, torch, stream):
             "hbm_gbs": (kv_bytes + state_bytes) / (us * 1e-6) / 1e9, "kv_bytes": kv_bytes, "state_bytes": state_bytes,
             "outputs_finite": finite, "device_status": st.device_status(),
             "shape": "batch 1, ctx 32768: 10 x (16Q/2KV hd256 u8-g32) + 30 x (32 x 128 x 128 f32 state)"}
+
+
+def c4_prefix_leg(sg, st, torch, stream, turns=300, decode_steps=8):
+    """Config 4, shortened: 64 sessions on the 4B shape (36 layers, 8 KV heads, hd128, bf16,
+    16-token blocks of 2.25 MiB), every prompt = a 4096-token system prefix + the session's own
+    history (512..8192 tokens, seed 1) + 64..512 new tokens; sessions drawn Zipf s=1.1; per turn:
+    match -> restore (physical copy) -> append the unmatched rows -> a few decode steps ->
+    remember every new full block; LRU eviction under an 8 GiB budget. Config 4 runs 2000 turns
+    and 128 decode steps per turn; this leg runs fewer of both (stated in the result)."""
+    layers, qh, kvh, hd, block = 36, 32, 8, 128, 16
+    kv_dim, q_dim = kvh * hd, qh * hd
+    budget = 8 << 30
+    max_tokens = 4096 + 8192 + 40 * 512 + 1024
+    cap = ((max_tokens + 15) // 16) * 16
+    page_b = layers * kvh * 2 * 16 * hd * 2
+    pool = st.pool(layers, kvh, hd, sg.KV_BF16, budget // page_b + 2 * (cap // 16) + 64, 4, cap)
+    pool.shuffle_free_list(8)
+    cache = sg.BlockAwarePrefixCache(block, 1 << 20, pool=pool, budget_bytes=budget)
+    rng = np.random.default_rng(1)
+    n_sessions = 64
+    lengths = [4096 + int(x) for x in rng.integers(512, 8193, size=n_sessions)]
+    weights = 1.0 / np.arange(1, n_sessions + 1) ** 1.1
+    weights /= weights.sum()
+    chunk = 8192
+    d_rows_k, d_rows_v = st.alloc(4 * chunk * kv_dim), st.alloc(4 * chunk * kv_dim)
+    st.fill_normal(d_rows_k, chunk * kv_dim, 12, 0)
+    st.fill_normal(d_rows_v, chunk * kv_dim, 12, 1)
+    d_k, d_v = st.alloc(4 * layers * kv_dim), st.alloc(4 * layers * kv_dim)
+    d_q, d_out = st.alloc(4 * layers * q_dim), st.alloc(4 * layers * q_dim)
+    st.fill_normal(d_k, layers * kv_dim, 13, 0)
+    st.fill_normal(d_v, layers * kv_dim, 13, 1)
+    st.fill_normal(d_q, layers * q_dim, 13, 2)
+    st.sync()
+    sys_prefix = list(range(1, 4097))
+    reused_tokens = prompt_tokens = copied_bytes = evicted_before = 0
+    restore_ms = 0.0
+    t0 = time.perf_counter()
+    for turn in range(turns):
+        s_ = int(rng.choice(n_sessions, p=weights))
+        root = sg.BlockHash.for_session(f"session-{s_}")
+        new_len = min(lengths[s_] + int(rng.integers(64, 513)), cap - decode_steps - 16)
+        toks = sys_prefix + [1_000_000 * (s_ + 1) + i for i in range(new_len - 4096)]
+        hit = cache.match_prefix(root, toks)
+        seq = pool.sequence(cap)
+        reused = 0
+        if hit is not None:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            copied_bytes += cache.restore(hit, seq, stream=stream.cuda_stream)
+            e1.record(stream)
+            stream.synchronize()
+            restore_ms += e0.elapsed_time(e1)
+            reused = hit.tokens
+        reused_tokens += reused
+        prompt_tokens += new_len
+        kvs = [seq.layer(layer, qh) for layer in range(layers)]
+        for kv in kvs:                                            # the unmatched rows are "prefilled"
+            for c in range(reused, new_len, chunk):
+                kv.encode_append_rows(d_rows_k, d_rows_v, min(chunk, new_len - c), stream=stream.cuda_stream)
+        batches = [sg.Batch(st, [kv]) for kv in kvs]
+        for _ in range(decode_steps):
+            for layer, b in enumerate(batches):
+                b.enqueue_step(_Off(d_k, 4 * layer * kv_dim), _Off(d_v, 4 * layer * kv_dim), _Off(d_q, 4 * layer * q_dim),
+                               _Off(d_out, 4 * layer * q_dim), stream=stream.cuda_stream)
+        stream.synchronize()
+        for b in batches:
+            b.close()
+        new_len += decode_steps
+        toks = toks + [2_000_000_000 + turn * 1000 + i for i in range(decode_steps)]
+        prev = root
+        for i in range(new_len // block):                        # remember every new full block
+            prev = sg.BlockHash.chain(prev, toks[i * block:(i + 1) * block])
+            if (i + 1) * block > reused:
+                cache.insert(root, prev, (i + 1) * block, seq=seq, stream=stream.cuda_stream)
+        lengths[s_] = new_len
+        seq.close()
+    stream.synchronize()
+    wall = time.perf_counter() - t0
+    out = {"turns": turns, "decode_steps_per_turn": decode_steps, "turns_per_s": turns / wall,
+           "prompt_tokens": prompt_tokens, "reused_tokens": reused_tokens, "hit_rate": reused_tokens / max(prompt_tokens, 1),
+           "restore_bytes_read_plus_written": 2 * copied_bytes,
+           "restore_gbs": 2 * copied_bytes / max(restore_ms * 1e-3, 1e-9) / 1e9,
+           "evicted_blocks": len(cache.evicted()), "cache_bytes": cache.estimated_bytes(), "budget_bytes": budget,
+           "device_status": st.device_status(),
+           "shape": "64 sessions, 36 layers x 8 KV heads x hd128 bf16, 16-token blocks (2.25 MiB), 8 GiB budget"}
+    cache.close()
+    pool.close()
+    return out
+
+
+class _Off:
+    """A device pointer at a byte offset inside a DeviceBuffer (what the ctypes face reads is .ptr)."""
+
+    def __init__(self, buf, offset):
+        self.ptr = buf.ptr + offset
 
 
 def c5_serving_leg(sg, st, torch, stream):
