@@ -113,6 +113,23 @@ class FullAttentionState {
   Result<Unit> encode_attention_decode_windowed(void* stream, const float* d_q, float* d_out, size_t window_start) {
     return unit(sgk_kv_enqueue_attention(h_, stream, d_q, d_out, static_cast<int64_t>(window_start), 0.0f));
   }
+  // One launch for append + attention (the fused form of the two calls above).
+  Result<Unit> encode_append_attention(void* stream, const float* d_k, const float* d_v, const float* d_q, float* d_out,
+                                       size_t sliding_window = 0) {
+    return unit(sgk_kv_enqueue_append_attention(h_, stream, d_k, d_v, d_q, d_out, static_cast<int64_t>(sliding_window), 0.0f));
+  }
+  // Speculative verify of n_rows draft rows (src/decode_resident/layers.rs:1295-1433); d_* are [n_rows][...].
+  Result<Unit> encode_verify_rows(void* stream, const float* d_k, const float* d_v, const float* d_q, float* d_out,
+                                  size_t n_rows, size_t sliding_window = 0) {
+    return unit(sgk_kv_enqueue_verify_rows(h_, stream, d_k, d_v, d_q, d_out, static_cast<int32_t>(n_rows),
+                                           static_cast<int64_t>(sliding_window), 0.0f));
+  }
+  // Prompt rows: RMSNorm + RoPE on K at positions len.., storage rounding, pages; one launch.
+  Result<Unit> encode_rope_append_rows(void* stream, const float* d_k_raw, const float* d_v, size_t n_rows,
+                                       const float* d_knorm_weight, size_t rope_dims, float theta, float eps) {
+    sgk_rope rope{static_cast<int32_t>(rope_dims), static_cast<int32_t>(rope_dims), theta, 1.0f, eps, 0};
+    return unit(sgk_kv_enqueue_rope_append_rows(h_, stream, d_k_raw, d_v, static_cast<int64_t>(n_rows), d_knorm_weight, &rope));
+  }
   // kv.keys() / kv.values() read-back of the valid rows, decoded to f32.
   Result<std::vector<float>> keys() { return rows(true); }
   Result<std::vector<float>> values() { return rows(false); }
@@ -196,6 +213,74 @@ class DecodeResidentState {
 
  private:
   sgk_state* h_ = nullptr;
+};
+
+// LinearAttentionMetalState of all recurrent layers (src/metal_backend/mod.rs:507-531) with the
+// decode step on it (src/linear_attention.rs:802-852,896-991) and the snapshot / restore /
+// per-row capture copies (src/metal_backend/linear_attention.rs:44-127,3027-3198).
+class LinearAttentionState {
+ public:
+  LinearAttentionState() = default;
+  explicit LinearAttentionState(sgk_linstate* h) : h_(h) {}
+  LinearAttentionState(LinearAttentionState&& o) noexcept : h_(o.h_) { o.h_ = nullptr; }
+  LinearAttentionState& operator=(LinearAttentionState&& o) noexcept {
+    if (this != &o) {
+      if (h_) sgk_linstate_destroy(h_);
+      h_ = o.h_;
+      o.h_ = nullptr;
+    }
+    return *this;
+  }
+  LinearAttentionState(const LinearAttentionState&) = delete;
+  LinearAttentionState& operator=(const LinearAttentionState&) = delete;
+  ~LinearAttentionState() {
+    if (h_) sgk_linstate_destroy(h_);
+  }
+  static Result<LinearAttentionState> create(DecodeResidentState& state, size_t layers, size_t conv_len, size_t ssm_len,
+                                             bool ssm_bf16) {
+    sgk_linstate* h = nullptr;
+    int32_t rc = sgk_linstate_create(state.handle(), static_cast<int32_t>(layers), static_cast<int64_t>(conv_len),
+                                     static_cast<int64_t>(ssm_len), ssm_bf16 ? 1 : 0, &h);
+    if (rc != SGK_OK) return Result<LinearAttentionState>::Err(rc);
+    return Result<LinearAttentionState>::Ok(LinearAttentionState(h));
+  }
+  size_t estimated_bytes() const { return static_cast<size_t>(sgk_linstate_bytes(h_)); }
+  Result<Unit> write(size_t layer, const std::vector<float>& conv, const std::vector<float>& ssm) {
+    return unit(sgk_linstate_write(h_, static_cast<int32_t>(layer), conv.empty() ? nullptr : conv.data(), ssm.data()));
+  }
+  Result<Unit> read(size_t layer, std::vector<float>& conv, std::vector<float>& ssm) {
+    return unit(sgk_linstate_read(h_, static_cast<int32_t>(layer), conv.empty() ? nullptr : conv.data(), ssm.data()));
+  }
+  Result<LinearAttentionState> snapshot(void* stream = nullptr) {
+    sgk_linstate* snap = nullptr;
+    int32_t rc = sgk_linstate_snapshot(h_, stream, &snap);
+    if (rc != SGK_OK) return Result<LinearAttentionState>::Err(rc);
+    return Result<LinearAttentionState>::Ok(LinearAttentionState(snap));
+  }
+  Result<Unit> restore(const LinearAttentionState& snap, void* stream = nullptr) {
+    return unit(sgk_linstate_restore(h_, stream, snap.h_));
+  }
+  Result<Unit> encode_capture(LinearAttentionState& capture, void* stream = nullptr) {
+    return unit(sgk_linstate_enqueue_capture(h_, stream, capture.h_));
+  }
+  Result<Unit> encode_conv_step(void* stream, size_t layer, const float* d_qkv, const float* d_weight, size_t conv_dim,
+                                size_t conv_kernel_dim, float* d_out) {
+    return unit(sgk_linstate_enqueue_conv_step(h_, stream, static_cast<int32_t>(layer), d_qkv, d_weight,
+                                               static_cast<int32_t>(conv_dim), static_cast<int32_t>(conv_kernel_dim), d_out));
+  }
+  Result<Unit> encode_gated_delta_step(void* stream, size_t layer, size_t num_key_heads, size_t num_value_heads,
+                                       size_t key_head_dim, size_t value_head_dim, const float* d_q, const float* d_k,
+                                       const float* d_v, const float* d_g, const float* d_beta, float* d_out) {
+    sgk_linear_shape shape{static_cast<int32_t>(num_key_heads), static_cast<int32_t>(num_value_heads),
+                           static_cast<int32_t>(key_head_dim), static_cast<int32_t>(value_head_dim)};
+    return unit(sgk_linstate_enqueue_gated_delta_step(h_, stream, static_cast<int32_t>(layer), &shape, d_q, d_k, d_v, d_g,
+                                                      d_beta, d_out));
+  }
+  sgk_linstate* handle() const { return h_; }
+
+ private:
+  static Result<Unit> unit(int32_t rc) { return rc == SGK_OK ? Result<Unit>::Ok(Unit{}) : Result<Unit>::Err(rc); }
+  sgk_linstate* h_ = nullptr;
 };
 
 // BlockHash (src/serve/cache.rs:11-47).

@@ -832,14 +832,52 @@ int32_t sgk_step_run_host(sgk_step* s, const float* k, const float* v, const flo
     SGK_CUDA(cudaMalloc(&s->d_q, q_cells * sizeof(float)));
     SGK_CUDA(cudaMalloc(&s->d_out, q_cells * sizeof(float)));
   }
+  // The layers go in a few groups: the inputs of every group are sent on a copy stream as soon
+  // as the call starts, a group's kernels wait only for its own inputs, and its outputs leave on
+  // a second copy stream while the next group computes. What stays exposed is the first group's
+  // inputs and the last group's outputs.
   cudaStream_t stream = s->st->stream;
-  SGK_CUDA(cudaMemcpyAsync(s->d_k, k, kv_cells * sizeof(float), cudaMemcpyHostToDevice, stream));
-  SGK_CUDA(cudaMemcpyAsync(s->d_v, v, kv_cells * sizeof(float), cudaMemcpyHostToDevice, stream));
-  SGK_CUDA(cudaMemcpyAsync(s->d_q, q, q_cells * sizeof(float), cudaMemcpyHostToDevice, stream));
-  SGK_TRY(s->enqueue(stream, s->d_k, s->d_v, s->d_q, s->d_out, sliding_windows, attn_scalar));
-  SGK_CUDA(cudaMemcpyAsync(out, s->d_out, q_cells * sizeof(float), cudaMemcpyDeviceToHost, stream));
+  const size_t L = s->layers.size();
+  const size_t groups = std::min<size_t>(L, 6);
+  if (!s->copy_in) {
+    SGK_CUDA(cudaStreamCreateWithFlags(&s->copy_in, cudaStreamNonBlocking));
+    SGK_CUDA(cudaStreamCreateWithFlags(&s->copy_out, cudaStreamNonBlocking));
+  }
+  while (s->events.size() < 2 * groups + 1) {
+    cudaEvent_t e = nullptr;
+    SGK_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    s->events.push_back(e);
+  }
+  const size_t kv_layer = n * s->layers[0]->kvs[0]->kv_dim(), q_layer = n * s->layers[0]->kvs[0]->q_dim();
+  // the copy streams start after whatever the state's stream was given before this call
+  SGK_CUDA(cudaEventRecord(s->events[2 * groups], stream));
+  SGK_CUDA(cudaStreamWaitEvent(s->copy_in, s->events[2 * groups], 0));
+  SGK_CUDA(cudaStreamWaitEvent(s->copy_out, s->events[2 * groups], 0));
+  for (size_t g = 0; g < groups; ++g) {
+    const size_t l0 = L * g / groups, l1 = L * (g + 1) / groups;
+    SGK_CUDA(cudaMemcpyAsync(s->d_k + l0 * kv_layer, k + l0 * kv_layer, (l1 - l0) * kv_layer * sizeof(float),
+                             cudaMemcpyHostToDevice, s->copy_in));
+    SGK_CUDA(cudaMemcpyAsync(s->d_v + l0 * kv_layer, v + l0 * kv_layer, (l1 - l0) * kv_layer * sizeof(float),
+                             cudaMemcpyHostToDevice, s->copy_in));
+    SGK_CUDA(cudaMemcpyAsync(s->d_q + l0 * q_layer, q + l0 * q_layer, (l1 - l0) * q_layer * sizeof(float),
+                             cudaMemcpyHostToDevice, s->copy_in));
+    SGK_CUDA(cudaEventRecord(s->events[2 * g], s->copy_in));
+  }
+  int rc = SGK_OK;
+  for (size_t g = 0; g < groups && rc == SGK_OK; ++g) {
+    const size_t l0 = L * g / groups, l1 = L * (g + 1) / groups;
+    SGK_CUDA(cudaStreamWaitEvent(stream, s->events[2 * g], 0));
+    rc = s->enqueue_range(stream, l0, l1, s->d_k, s->d_v, s->d_q, s->d_out, sliding_windows, attn_scalar);
+    if (rc != SGK_OK) break;
+    SGK_CUDA(cudaEventRecord(s->events[2 * g + 1], stream));
+    SGK_CUDA(cudaStreamWaitEvent(s->copy_out, s->events[2 * g + 1], 0));
+    SGK_CUDA(cudaMemcpyAsync(out + l0 * q_layer, s->d_out + l0 * q_layer, (l1 - l0) * q_layer * sizeof(float),
+                             cudaMemcpyDeviceToHost, s->copy_out));
+  }
+  SGK_CUDA(cudaStreamSynchronize(s->copy_in));
   SGK_CUDA(cudaStreamSynchronize(stream));
-  return SGK_OK;
+  SGK_CUDA(cudaStreamSynchronize(s->copy_out));
+  return rc;
 }
 
 int64_t sgk_step_launches(const sgk_step* s) { return s ? s->launches : 0; }

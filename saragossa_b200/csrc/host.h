@@ -161,8 +161,13 @@ struct Step {
   int64_t launches_per_replay = 0;
   // staging of run_host
   float *d_k = nullptr, *d_v = nullptr, *d_q = nullptr, *d_out = nullptr;
+  // run_host overlaps the copies of one group of layers with the kernels of another
+  cudaStream_t copy_in = nullptr, copy_out = nullptr;
+  std::vector<cudaEvent_t> events;
   int enqueue(cudaStream_t stream, const float* d_k, const float* d_v, const float* d_q, float* d_out,
               const int64_t* sliding_windows, float attn_scalar);
+  int enqueue_range(cudaStream_t stream, size_t l0, size_t l1, const float* d_k, const float* d_v, const float* d_q,
+                    float* d_out, const int64_t* sliding_windows, float attn_scalar);
   ~Step();
 };
 

@@ -483,13 +483,22 @@ int Batch::enqueue_attention(cudaStream_t stream, const float* d_q, float* d_out
 Step::~Step() {
   if (graph_exec) cudaGraphExecDestroy(graph_exec);
   if (graph) cudaGraphDestroy(graph);
+  if (copy_in) cudaStreamDestroy(copy_in);
+  if (copy_out) cudaStreamDestroy(copy_out);
+  for (cudaEvent_t e : events)
+    if (e) cudaEventDestroy(e);
   for (float* p : {d_k, d_v, d_q, d_out})
     if (p) cudaFree(p);
 }
 
 int Step::enqueue(cudaStream_t stream, const float* k, const float* v, const float* q, float* out,
                   const int64_t* sliding_windows, float attn_scalar) {
-  for (size_t l = 0; l < layers.size(); ++l) {
+  return enqueue_range(stream, 0, layers.size(), k, v, q, out, sliding_windows, attn_scalar);
+}
+
+int Step::enqueue_range(cudaStream_t stream, size_t l0, size_t l1, const float* k, const float* v, const float* q,
+                        float* out, const int64_t* sliding_windows, float attn_scalar) {
+  for (size_t l = l0; l < l1; ++l) {
     Batch* b = layers[l];
     size_t kv_stride = size_t(b->n()) * b->kvs[0]->kv_dim();
     size_t q_stride = size_t(b->n()) * b->kvs[0]->q_dim();

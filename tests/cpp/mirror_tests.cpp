@@ -2,6 +2,7 @@
 // (include/saragossa_kv.hpp) so they read like the originals. `cpu` runs the
 // prefix-cache cases (no device); `gpu` also runs the resident-KV cases and checks
 // attention against the CPU oracle (test infrastructure, linked in directly).
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -179,6 +180,76 @@ static void run_attention_case(DecodeResidentState& state, size_t len, bool bf16
   CHECK(mean_abs <= (bf16 ? 2.0e-4f : 1.0e-5f));
 }
 
+// Device copy of a host vector, freed with the test.
+struct DeviceVec {
+  sgk_state* st;
+  float* d = nullptr;
+  size_t n;
+  DeviceVec(sgk_state* s, const std::vector<float>& h) : st(s), n(h.size()) {
+    void* p = nullptr;
+    CHECK(sgk_util_malloc(st, std::max<size_t>(n, 4) * sizeof(float), &p) == SGK_OK);
+    d = static_cast<float*>(p);
+    if (n) CHECK(sgk_util_h2d(st, d, h.data(), n * sizeof(float)) == SGK_OK);
+  }
+  std::vector<float> read() const {
+    std::vector<float> h(n);
+    CHECK(sgk_util_d2h(st, h.data(), d, n * sizeof(float)) == SGK_OK);
+    return h;
+  }
+  ~DeviceVec() { sgk_util_free(st, d); }
+};
+
+// gated_delta_matches_naive_oracle_across_lengths_and_gqa_heads (src/linear_attention/tests.rs:304-372)
+// on the device: the two shapes of that test, several tokens, state and outputs against the CPU
+// recurrence within the reference's Metal-vs-CPU bound (1e-5), then the per-row capture / restore
+// of the speculative path brings the state back bit for bit.
+static void gated_delta_steps_match_cpu(DecodeResidentState& state) {
+  const size_t shapes[2][4] = {{2, 4, 8, 6}, {1, 4, 128, 128}};
+  for (const auto& sh : shapes) {
+    const size_t hk = sh[0], hv = sh[1], dk = sh[2], dv = sh[3];
+    const size_t ssm_len = hv * dv * dk;
+    auto made = LinearAttentionState::create(state, 1, 0, ssm_len, false);
+    auto cap = LinearAttentionState::create(state, 1, 0, ssm_len, false);
+    CHECK(made.ok && cap.ok);
+    if (!made.ok || !cap.ok) return;
+    LinearAttentionState ls = std::move(made.value), capture = std::move(cap.value);
+    std::vector<float> ssm(ssm_len, 0.0f), none;
+    CHECK(ls.write(0, none, ssm).ok);
+    std::vector<float> after_first;
+    for (int t = 0; t < 5; ++t) {
+      std::vector<float> q(hk * dk), k(hk * dk), v(hv * dv), g(hv), beta(hv);
+      sgo::fill_normal8(q.data(), q.size(), 70 + t, 0, 0);
+      sgo::fill_normal8(k.data(), k.size(), 70 + t, 1, 0);
+      sgo::fill_normal8(v.data(), v.size(), 70 + t, 2, 0);
+      for (auto& x : q) x /= static_cast<float>(dk);
+      for (auto& x : k) x /= std::sqrt(static_cast<float>(dk));
+      for (size_t h = 0; h < hv; ++h) g[h] = 0.9f + 0.02f * h, beta[h] = 0.2f + 0.1f * h;
+      DeviceVec dq(state.handle(), q), dkk(state.handle(), k), dvv(state.handle(), v), dg(state.handle(), g),
+          db(state.handle(), beta), dout(state.handle(), std::vector<float>(hv * dv));
+      CHECK(ls.encode_gated_delta_step(nullptr, 0, hk, hv, dk, dv, dq.d, dkk.d, dvv.d, dg.d, db.d, dout.d).ok);
+      if (t == 0) CHECK(ls.encode_capture(capture).ok);
+      std::vector<float> want(hv * dv);
+      sgo::LinearShape shape{hk, hv, dk, dv, 0};
+      CHECK(sgo::gated_delta_step(q.data(), k.data(), v.data(), g.data(), beta.data(), shape, &ssm, want.data()) == sgo::OK);
+      CHECK(sgk_state_sync(state.handle()) == SGK_OK);
+      std::vector<float> got = dout.read(), got_ssm(ssm_len);
+      CHECK(ls.read(0, none, got_ssm).ok);
+      for (size_t i = 0; i < want.size(); ++i) CHECK(std::fabs(got[i] - want[i]) <= 1e-5f);
+      for (size_t i = 0; i < ssm_len; ++i) CHECK(std::fabs(got_ssm[i] - ssm[i]) <= 1e-5f);
+      if (t == 0) after_first = got_ssm;
+    }
+    CHECK(ls.restore(capture).ok);            // roll back to the state after the first token
+    std::vector<float> back(ssm_len);
+    CHECK(ls.read(0, none, back).ok);
+    CHECK(back == after_first);
+    auto other = LinearAttentionState::create(state, 1, 0, ssm_len, true);
+    if (other.ok) {
+      auto r = ls.encode_capture(other.value);   // storage type differs: a shape error, nothing copied
+      CHECK(r.is_err() && r.error.kind == InferError::Shape);
+    }
+  }
+}
+
 int main(int argc, char** argv) {
   const bool gpu = argc > 1 && std::string(argv[1]) == "gpu";
   prefix_cache_evicts_lru_block();
@@ -196,6 +267,7 @@ int main(int argc, char** argv) {
         run_attention_case(state, len, false);
         run_attention_case(state, len, true);
       }
+      gated_delta_steps_match_cpu(state);
     }
   } else {
     auto made = DecodeResidentState::create(0);
