@@ -242,20 +242,19 @@ __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s
     int32_t* group_counter = a.group_counters + (int64_t(seq) * a.pool.kv_heads + kvh) * a.max_groups + group;
     int32_t* head_counter = a.head_counters + int64_t(seq) * a.pool.kv_heads + kvh;
     __syncthreads();
-    if (tid == 0) {
-      if (splits > 1) {
-        int old = arrive_acq_rel(group_counter);
-        flags[1] = (old == group_count - 1);
-        if (flags[1]) *group_counter = 0;
-      }
-      if (do_append) {
-        // the block that arrives last for the sequence moves the cursor
-        int total = splits * a.pool.kv_heads;
-        int old = arrive_acq_rel(a.seq_counters + seq);
-        if (old == total - 1) {
-          *len_ptr = static_cast<int32_t>(len);
-          a.seq_counters[seq] = 0;
-        }
+    // two arrivals, on two threads of different warps so that their round trips overlap
+    if (tid == 0 && splits > 1) {
+      int old = arrive_acq_rel(group_counter);
+      flags[1] = (old == group_count - 1);
+      if (flags[1]) *group_counter = 0;
+    }
+    if (tid == 32 && do_append) {
+      // the block that arrives last for the sequence moves the cursor
+      int total = splits * a.pool.kv_heads;
+      int old = arrive_acq_rel(a.seq_counters + seq);
+      if (old == total - 1) {
+        *len_ptr = static_cast<int32_t>(len);
+        a.seq_counters[seq] = 0;
       }
     }
     __syncthreads();
