@@ -314,6 +314,47 @@ def test_rms_norm_rope_decode_matches_cpu(state, rope_dims):
     assert e.value.kind == "Dimension"
 
 
+@pytest.mark.parametrize("prefill_len,seed", [(1, 3), (4, 19), (9, 41)])
+def test_partial_rotary_global_attention_matches_per_op_oracle(state, prefill_len, seed):
+    # gemma4_global_attention_decode_resident_matches_per_op_oracle, src/decode_resident/tests.rs:1128-1226:
+    # head_dim 16, a quarter of it rotated, theta 1e6; the new K row goes through RMSNorm+RoPE on the
+    # device (standalone, and fused into the append), then attention over prefill + 1: max 1e-4, mean 1e-5
+    q_heads, kv_heads, hd = 4, 2, 16
+    rope_dims, kv_dim, eps, theta = hd // 4, kv_heads * hd, 1e-6, 1_000_000.0
+    q_norm = np.float32(0.7) + np.abs(np.array([sgo.pseudo(seed + 11 * i) for i in range(hd)], np.float32))
+    k_norm = np.float32(0.8) + np.abs(np.array([sgo.pseudo(seed + 17 * i) for i in range(hd)], np.float32))
+    keys, values = [], []
+    for row in range(prefill_len):
+        k_raw = sgo.pseudo(seed + row * 131, kv_dim)
+        _, kr = sgo.rms_norm_rope_heads_at(k_raw[None], kv_heads, hd, rope_dims, k_norm, eps, theta, rope_dims, 1.0, row)
+        keys.append(kr.ravel())
+        values.append(sgo.pseudo(seed + 10_000 + row * 137, kv_dim))
+    position = prefill_len
+    q_raw, k_raw, v_raw = sgo.pseudo(seed + 20_000, q_heads * hd), sgo.pseudo(seed + 30_000, kv_dim), sgo.pseudo(seed + 40_000, kv_dim)
+    _, q_cpu = sgo.rms_norm_rope_heads_at(q_raw[None], q_heads, hd, rope_dims, q_norm, eps, theta, rope_dims, 1.0, position)
+    _, k_cpu = sgo.rms_norm_rope_heads_at(k_raw[None], kv_heads, hd, rope_dims, k_norm, eps, theta, rope_dims, 1.0, position)
+    rope = sg.make_rope(rope_dims, theta, eps=eps)
+    q_gpu = state.rms_norm_rope_decode(q_raw, q_norm, q_heads, hd, rope, position)
+    k_gpu = state.rms_norm_rope_decode(k_raw, k_norm, kv_heads, hd, rope, position)
+    st_, want = sgo.cached_attention_one(q_cpu.ravel(), np.concatenate(keys + [k_cpu.ravel()]).reshape(-1, kv_dim),
+                                         np.concatenate(values + [v_raw]).reshape(-1, kv_dim), q_heads, kv_heads, hd)
+    assert st_ == sgo.OK
+    outs = []
+    for fused in (False, True):
+        kv = state.full_attention(prefill_len + 1, q_heads, kv_heads, hd, sg.KV_F32)
+        kv.seed(np.concatenate(keys), np.concatenate(values), prefill_len)
+        if fused:
+            kv.encode_rope_append(state.upload(k_raw), state.upload(v_raw), state.upload(k_norm), rope)
+            state.sync()
+        else:
+            kv.append_row(k_gpu, v_raw)
+        outs.append(kv.attention_decode(q_gpu))
+        kv.close()
+    for got in outs:
+        delta = np.abs(got - want)
+        assert delta.max() <= 1e-4 and delta.mean() <= 1e-5, (prefill_len, seed, delta.max())
+
+
 def test_rope_known_answers_and_scaled_positions(state):
     # apply_rope_styles_match_mlx_reference / position_scale, src/decoder/tests.rs:998-1089 (1e-4).
     # With a unit weight the norm divides by rms(x); undo it to compare with the raw-rope vectors.
