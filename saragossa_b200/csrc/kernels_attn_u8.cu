@@ -260,9 +260,16 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
           make_uint2(uint32_t(lo[0]) | (uint32_t(lo[1]) << 16), uint32_t(lo[2]) | (uint32_t(lo[3]) << 16));
     }
   }
-  __syncthreads();
+  // The producer only announces that the barriers exist and starts copying; the consumers wait
+  // here for that and for each other's part of Q and of the appended row.
+  if (warp == MMA_CONSUMERS) {
+    __syncwarp();
+    asm volatile("bar.arrive 3, %0;" ::"r"(MMA_THREADS) : "memory");
+  } else {
+    asm volatile("bar.sync 3, %0;" ::"r"(MMA_THREADS) : "memory");
+  }
   // The row a fused append is about to write may carry a larger scale than any stored one.
-  if (owns_append) {
+  if (owns_append && warp < MMA_CONSUMERS) {
     float big = new_big[0];
 #pragma unroll
     for (int w = 1; w < MMA_CONSUMERS; ++w)
