@@ -288,6 +288,18 @@ int32_t sgk_linstate_enqueue_gated_delta_step(sgk_linstate* ls, void* stream, in
                                               const sgk_linear_shape* shape, const float* d_q, const float* d_k,
                                               const float* d_v, const float* d_g, const float* d_beta,
                                               float* d_out);
+/* The prompt-side forms: n_tokens tokens of ONE sequence run one after the other with the state
+ * (or the conv window) kept in registers and written back once, like the reference's sequence
+ * kernels (linear_attn_gated_delta_seq_dk128_*_tg4_f32, src/kernels.metal:2644-2840). Inputs and
+ * outputs gain a leading [n_tokens] dimension. With bf16 SSM storage the state is rounded once, at
+ * the end (the step form rounds after every token). */
+int32_t sgk_linstate_enqueue_conv_seq(sgk_linstate* ls, void* stream, int32_t layer, const float* d_qkv,
+                                      const float* d_weight, int32_t conv_dim, int32_t conv_kernel_dim,
+                                      int32_t n_tokens, float* d_out);
+int32_t sgk_linstate_enqueue_gated_delta_seq(sgk_linstate* ls, void* stream, int32_t layer,
+                                             const sgk_linear_shape* shape, const float* d_q, const float* d_k,
+                                             const float* d_v, const float* d_g, const float* d_beta,
+                                             int32_t n_tokens, float* d_out);
 /* The same step for n_states sequences (at most 64) in one launch, as the reference's batch
  * decode does for its sequences (src/metal_backend/lightbatch_duo.rs): states[i] is sequence
  * i's state and every input and the output gain a leading [n_states] dimension. All states

@@ -1006,26 +1006,39 @@ int32_t sgk_linstate_enqueue_capture(sgk_linstate* ls, void* stream, sgk_linstat
   return SGK_OK;
 }
 
-int32_t sgk_linstate_enqueue_conv_step(sgk_linstate* ls, void* stream, int32_t layer, const float* d_qkv,
-                                       const float* d_weight, int32_t conv_dim, int32_t conv_kernel_dim,
-                                       float* d_out) {
+static int32_t conv_impl(sgk_linstate* ls, void* stream, int32_t layer, const float* d_qkv, const float* d_weight,
+                         int32_t conv_dim, int32_t conv_kernel_dim, int32_t n_tokens, float* d_out) {
   if (!ls || !d_qkv || !d_weight || !d_out) return fail(SGK_ERR_BACKEND, "null argument");
   if (layer < 0 || layer >= ls->layers) return fail(SGK_ERR_DIMENSION, "layer %d out of range", layer);
   if (conv_dim <= 0 || conv_kernel_dim <= 0) return fail(SGK_ERR_DIMENSION, "conv shape must be positive");
+  if (conv_kernel_dim > 16) return fail(SGK_ERR_CONFIG, "conv kernel %d > 16 is not supported", conv_kernel_dim);
+  if (n_tokens < 0) return fail(SGK_ERR_DIMENSION, "n_tokens %d invalid", n_tokens);
   // ensure_conv_cache (src/linear_attention.rs:856-886): the history is [(K-1), conv_dim]
   if (ls->conv_len != int64_t(conv_kernel_dim - 1) * conv_dim)
     return fail(SGK_ERR_DIMENSION, "conv history holds %lld values, expected %lld", (long long)ls->conv_len,
                 (long long)(int64_t(conv_kernel_dim - 1) * conv_dim));
+  if (n_tokens == 0) return SGK_OK;
   SGK_CUDA(launch_conv_step(d_qkv, d_weight, static_cast<float*>(sgk_linstate_conv_ptr(ls, layer)), d_out, conv_dim,
-                            conv_kernel_dim, ls->st->pick(stream)));
+                            conv_kernel_dim, n_tokens, ls->st->pick(stream)));
   ls->st->launches += 1;
   return SGK_OK;
 }
 
-int32_t sgk_linstate_enqueue_gated_delta_step_batch(sgk_linstate* const* states, int32_t n_states, void* stream,
-                                                    int32_t layer, const sgk_linear_shape* shape,
-                                                    const float* d_q, const float* d_k, const float* d_v,
-                                                    const float* d_g, const float* d_beta, float* d_out) {
+int32_t sgk_linstate_enqueue_conv_step(sgk_linstate* ls, void* stream, int32_t layer, const float* d_qkv,
+                                       const float* d_weight, int32_t conv_dim, int32_t conv_kernel_dim,
+                                       float* d_out) {
+  return conv_impl(ls, stream, layer, d_qkv, d_weight, conv_dim, conv_kernel_dim, 1, d_out);
+}
+
+int32_t sgk_linstate_enqueue_conv_seq(sgk_linstate* ls, void* stream, int32_t layer, const float* d_qkv,
+                                      const float* d_weight, int32_t conv_dim, int32_t conv_kernel_dim,
+                                      int32_t n_tokens, float* d_out) {
+  return conv_impl(ls, stream, layer, d_qkv, d_weight, conv_dim, conv_kernel_dim, n_tokens, d_out);
+}
+
+static int32_t gated_delta_impl(sgk_linstate* const* states, int32_t n_states, void* stream, int32_t layer,
+                                const sgk_linear_shape* shape, const float* d_q, const float* d_k, const float* d_v,
+                                const float* d_g, const float* d_beta, int32_t n_tokens, float* d_out) {
   if (!states || !shape || !d_q || !d_k || !d_v || !d_g || !d_beta || !d_out) return fail(SGK_ERR_BACKEND, "null argument");
   if (n_states <= 0 || n_states > GATED_DELTA_MAX_STATES)
     return fail(SGK_ERR_CONFIG, "n_states %d outside 1..%d", n_states, GATED_DELTA_MAX_STATES);
@@ -1048,6 +1061,7 @@ int32_t sgk_linstate_enqueue_gated_delta_step_batch(sgk_linstate* const* states,
     a.ssm[i] = sgk_linstate_ssm_ptr(ls, layer);
   }
   a.n_states = n_states;
+  a.n_tokens = n_tokens;
   a.ssm_bf16 = states[0]->ssm_bf16 ? 1 : 0;
   a.num_key_heads = shape->num_key_heads;
   a.num_value_heads = shape->num_value_heads;
@@ -1064,12 +1078,29 @@ int32_t sgk_linstate_enqueue_gated_delta_step_batch(sgk_linstate* const* states,
   return SGK_OK;
 }
 
+int32_t sgk_linstate_enqueue_gated_delta_step_batch(sgk_linstate* const* states, int32_t n_states, void* stream,
+                                                    int32_t layer, const sgk_linear_shape* shape,
+                                                    const float* d_q, const float* d_k, const float* d_v,
+                                                    const float* d_g, const float* d_beta, float* d_out) {
+  return gated_delta_impl(states, n_states, stream, layer, shape, d_q, d_k, d_v, d_g, d_beta, 1, d_out);
+}
+
 int32_t sgk_linstate_enqueue_gated_delta_step(sgk_linstate* ls, void* stream, int32_t layer,
                                               const sgk_linear_shape* shape, const float* d_q, const float* d_k,
                                               const float* d_v, const float* d_g, const float* d_beta,
                                               float* d_out) {
   if (!ls) return fail(SGK_ERR_BACKEND, "null argument");
-  return sgk_linstate_enqueue_gated_delta_step_batch(&ls, 1, stream, layer, shape, d_q, d_k, d_v, d_g, d_beta, d_out);
+  return gated_delta_impl(&ls, 1, stream, layer, shape, d_q, d_k, d_v, d_g, d_beta, 1, d_out);
+}
+
+int32_t sgk_linstate_enqueue_gated_delta_seq(sgk_linstate* ls, void* stream, int32_t layer,
+                                             const sgk_linear_shape* shape, const float* d_q, const float* d_k,
+                                             const float* d_v, const float* d_g, const float* d_beta,
+                                             int32_t n_tokens, float* d_out) {
+  if (!ls) return fail(SGK_ERR_BACKEND, "null argument");
+  if (n_tokens < 0) return fail(SGK_ERR_DIMENSION, "n_tokens %d invalid", n_tokens);
+  if (n_tokens == 0) return SGK_OK;
+  return gated_delta_impl(&ls, 1, stream, layer, shape, d_q, d_k, d_v, d_g, d_beta, n_tokens, d_out);
 }
 
 // ------------------------------------------------------------------ hashes

@@ -127,18 +127,19 @@ constexpr int GATED_DELTA_MAX_STATES = 64;
 struct GatedDeltaArgs {
   void* ssm[GATED_DELTA_MAX_STATES];  // one state per sequence, passed by value: no device table
   int32_t n_states;
+  int32_t n_tokens;   // tokens run one after the other on the state kept in registers; inputs gain a [n_tokens] dim
   int32_t ssm_bf16;
   int32_t num_key_heads, num_value_heads, key_head_dim, value_head_dim;
-  const float* q;     // [n_states][H_k * d_k]
-  const float* k;     // [n_states][H_k * d_k]
-  const float* v;     // [n_states][H_v * d_v]
-  const float* g;     // [n_states][H_v] decay
-  const float* beta;  // [n_states][H_v] write gate
-  float* out;         // [n_states][H_v * d_v]
+  const float* q;     // [n_states][n_tokens][H_k * d_k]
+  const float* k;     // [n_states][n_tokens][H_k * d_k]
+  const float* v;     // [n_states][n_tokens][H_v * d_v]
+  const float* g;     // [n_states][n_tokens][H_v] decay
+  const float* beta;  // [n_states][n_tokens][H_v] write gate
+  float* out;         // [n_states][n_tokens][H_v * d_v]
 };
 cudaError_t launch_gated_delta_step(const GatedDeltaArgs& a, cudaStream_t stream);
 cudaError_t launch_conv_step(const float* qkv, const float* weight, float* history, float* out, int conv_dim,
-                             int kernel, cudaStream_t stream);
+                             int kernel, int n_tokens, cudaStream_t stream);
 cudaError_t launch_fill_normal(float* out, int64_t n, uint64_t seed, uint64_t stream_id,
                                uint64_t index0, cudaStream_t stream);
 

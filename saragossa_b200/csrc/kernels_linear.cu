@@ -41,46 +41,59 @@ __global__ void __launch_bounds__(GD_THREADS) gated_delta_step_kernel(GatedDelta
   // blockIdx.y picks the sequence: its own state, and its slice of every input and of the output
   const int b = blockIdx.y;
   void* ssm = a.ssm[b];
-  const float* q_b = a.q + int64_t(b) * a.num_key_heads * dk;
-  const float* k_b = a.k + int64_t(b) * a.num_key_heads * dk;
-  const float* v_b = a.v + int64_t(b) * rows;
-  const float* g_b = a.g + int64_t(b) * a.num_value_heads;
-  const float* beta_b = a.beta + int64_t(b) * a.num_value_heads;
-  float* out_b = a.out + int64_t(b) * rows;
+  const int T = a.n_tokens;
+  const float* q_b = a.q + int64_t(b) * T * a.num_key_heads * dk;
+  const float* k_b = a.k + int64_t(b) * T * a.num_key_heads * dk;
+  const float* v_b = a.v + int64_t(b) * T * rows;
+  const float* g_b = a.g + int64_t(b) * T * a.num_value_heads;
+  const float* beta_b = a.beta + int64_t(b) * T * a.num_value_heads;
+  float* out_b = a.out + int64_t(b) * T * rows;
   for (int row = warp; row < rows; row += total_warps) {
-    const int vh = row / a.value_head_dim, col = row % a.value_head_dim;
+    const int vh = row / a.value_head_dim;
     const int kh = vh / repeat;
-    const float decay = g_b[vh], beta = beta_b[vh];
-    const float* kp = k_b + kh * dk;
-    const float* qp = q_b + kh * dk;
     const int64_t base = int64_t(row) * dk;
     float s[GD_MAXJ], kk[GD_MAXJ];
-    float kv = 0.0f;
 #pragma unroll
     for (int j = 0; j < GD_MAXJ; ++j) {
       const int i = lane + 32 * j;
-      if (i < dk) {
-        kk[j] = kp[i];
-        s[j] = load_state<BF16>(ssm, base + i) * decay;
-        kv += s[j] * kk[j];
-      }
+      if (i < dk) s[j] = load_state<BF16>(ssm, base + i);
     }
+    // the tokens of a sequence run on the row kept in registers; it goes back to memory once
+    for (int t = 0; t < T; ++t) {
+      const float decay = g_b[int64_t(t) * a.num_value_heads + vh], beta = beta_b[int64_t(t) * a.num_value_heads + vh];
+      const float* kp = k_b + (int64_t(t) * a.num_key_heads + kh) * dk;
+      const float* qp = q_b + (int64_t(t) * a.num_key_heads + kh) * dk;
+      float kv = 0.0f;
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) kv += __shfl_xor_sync(0xffffffffu, kv, off);
-    const float delta = (v_b[row] - kv) * beta;
-    float y = 0.0f;
+      for (int j = 0; j < GD_MAXJ; ++j) {
+        const int i = lane + 32 * j;
+        if (i < dk) {
+          kk[j] = kp[i];
+          s[j] *= decay;
+          kv += s[j] * kk[j];
+        }
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) kv += __shfl_xor_sync(0xffffffffu, kv, off);
+      const float delta = (v_b[int64_t(t) * rows + row] - kv) * beta;
+      float y = 0.0f;
+#pragma unroll
+      for (int j = 0; j < GD_MAXJ; ++j) {
+        const int i = lane + 32 * j;
+        if (i < dk) {
+          s[j] += delta * kk[j];
+          y += s[j] * qp[i];
+        }
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) y += __shfl_xor_sync(0xffffffffu, y, off);
+      if (lane == 0) out_b[int64_t(t) * rows + row] = y;
+    }
 #pragma unroll
     for (int j = 0; j < GD_MAXJ; ++j) {
       const int i = lane + 32 * j;
-      if (i < dk) {
-        s[j] += delta * kk[j];
-        y += s[j] * qp[i];
-        store_state<BF16>(ssm, base + i, s[j]);
-      }
+      if (i < dk) store_state<BF16>(ssm, base + i, s[j]);
     }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) y += __shfl_xor_sync(0xffffffffu, y, off);
-    if (lane == 0) out_b[row] = y;
   }
 }
 
@@ -102,11 +115,7 @@ __global__ void __launch_bounds__(GD_THREADS) gated_delta_step_dk128_kernel(Gate
   if (row0 >= rows) return;
   const int vh = row0 / a.value_head_dim;
   const int kh = vh / repeat;
-  const int64_t in_k = (int64_t(b) * a.num_key_heads + kh) * 128 + lane * 4;
-  const float4 kk = *reinterpret_cast<const float4*>(a.k + in_k);
-  const float4 qq = *reinterpret_cast<const float4*>(a.q + in_k);
-  const float decay = a.g[int64_t(b) * a.num_value_heads + vh];
-  const float beta = a.beta[int64_t(b) * a.num_value_heads + vh];
+  const int T = a.n_tokens;
   const int64_t base = int64_t(row0) * 128 + lane * 4;
   float4 s[R];
   float vv[R];
@@ -123,26 +132,43 @@ __global__ void __launch_bounds__(GD_THREADS) gated_delta_step_dk128_kernel(Gate
 #pragma unroll
     for (int r = 0; r < R; ++r) s[r] = *reinterpret_cast<const float4*>(p + r * 128);
   }
+  // the tokens of a sequence run on the rows kept in registers; they go back to memory once
+  for (int t = 0; t < T; ++t) {
+    const int64_t tok = int64_t(b) * T + t;
+    const int64_t in_k = (tok * a.num_key_heads + kh) * 128 + lane * 4;
+    const float4 kk = *reinterpret_cast<const float4*>(a.k + in_k);
+    const float4 qq = *reinterpret_cast<const float4*>(a.q + in_k);
+    const float decay = a.g[tok * a.num_value_heads + vh];
+    const float beta = a.beta[tok * a.num_value_heads + vh];
 #pragma unroll
-  for (int r = 0; r < R; ++r) vv[r] = a.v[int64_t(b) * rows + row0 + r];
-  float kv[R];
+    for (int r = 0; r < R; ++r) vv[r] = a.v[tok * rows + row0 + r];
+    float kv[R];
 #pragma unroll
-  for (int r = 0; r < R; ++r) {
-    s[r].x = __fmul_rn(s[r].x, decay), s[r].y = __fmul_rn(s[r].y, decay);
-    s[r].z = __fmul_rn(s[r].z, decay), s[r].w = __fmul_rn(s[r].w, decay);
-    kv[r] = dot4(s[r], kk);
-  }
+    for (int r = 0; r < R; ++r) {
+      s[r].x = __fmul_rn(s[r].x, decay), s[r].y = __fmul_rn(s[r].y, decay);
+      s[r].z = __fmul_rn(s[r].z, decay), s[r].w = __fmul_rn(s[r].w, decay);
+      kv[r] = dot4(s[r], kk);
+    }
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1)
+    for (int off = 16; off > 0; off >>= 1)
 #pragma unroll
-    for (int r = 0; r < R; ++r) kv[r] += __shfl_xor_sync(0xffffffffu, kv[r], off);
-  float y[R];
+      for (int r = 0; r < R; ++r) kv[r] += __shfl_xor_sync(0xffffffffu, kv[r], off);
+    float y[R];
 #pragma unroll
-  for (int r = 0; r < R; ++r) {
-    const float delta = __fmul_rn(__fsub_rn(vv[r], kv[r]), beta);
-    s[r].x = __fmaf_rn(delta, kk.x, s[r].x), s[r].y = __fmaf_rn(delta, kk.y, s[r].y);
-    s[r].z = __fmaf_rn(delta, kk.z, s[r].z), s[r].w = __fmaf_rn(delta, kk.w, s[r].w);
-    y[r] = dot4(s[r], qq);
+    for (int r = 0; r < R; ++r) {
+      const float delta = __fmul_rn(__fsub_rn(vv[r], kv[r]), beta);
+      s[r].x = __fmaf_rn(delta, kk.x, s[r].x), s[r].y = __fmaf_rn(delta, kk.y, s[r].y);
+      s[r].z = __fmaf_rn(delta, kk.z, s[r].z), s[r].w = __fmaf_rn(delta, kk.w, s[r].w);
+      y[r] = dot4(s[r], qq);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+      for (int r = 0; r < R; ++r) y[r] += __shfl_xor_sync(0xffffffffu, y[r], off);
+    if (lane == 0) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) a.out[tok * rows + row0 + r] = y[r];
+    }
   }
   if (BF16) {
     uint16_t* p = reinterpret_cast<uint16_t*>(a.ssm[b]) + base;
@@ -157,14 +183,6 @@ __global__ void __launch_bounds__(GD_THREADS) gated_delta_step_dk128_kernel(Gate
     float* p = reinterpret_cast<float*>(a.ssm[b]) + base;
 #pragma unroll
     for (int r = 0; r < R; ++r) *reinterpret_cast<float4*>(p + r * 128) = s[r];
-  }
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1)
-#pragma unroll
-    for (int r = 0; r < R; ++r) y[r] += __shfl_xor_sync(0xffffffffu, y[r], off);
-  if (lane == 0) {
-#pragma unroll
-    for (int r = 0; r < R; ++r) a.out[int64_t(b) * rows + row0 + r] = y[r];
   }
 }
 
@@ -202,26 +220,41 @@ cudaError_t launch_gated_delta_step(const GatedDeltaArgs& a, cudaStream_t stream
 
 // One thread per channel: the products are summed in kernel-tap order with separate
 // roundings, exactly like the CPU loop, then the channel's history slides by one token.
+constexpr int CONV_MAX_KERNEL = 16;
+
 __global__ void __launch_bounds__(256) conv_step_kernel(const float* __restrict__ qkv,
                                                        const float* __restrict__ weight, float* history,
-                                                       float* __restrict__ out, int conv_dim, int kernel) {
+                                                       float* __restrict__ out, int conv_dim, int kernel,
+                                                       int n_tokens) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= conv_dim) return;
   const int keep = kernel - 1;
-  const float x = qkv[c];
-  float acc = 0.0f;
-  for (int kk = 0; kk < kernel; ++kk) {
-    const float input = kk < keep ? history[int64_t(kk) * conv_dim + c] : x;
-    acc = __fadd_rn(acc, __fmul_rn(input, weight[int64_t(c) * kernel + kk]));
+  // the channel's taps and its window of past inputs stay in registers over the tokens
+  float w[CONV_MAX_KERNEL], h[CONV_MAX_KERNEL];
+#pragma unroll
+  for (int kk = 0; kk < CONV_MAX_KERNEL; ++kk) {
+    w[kk] = kk < kernel ? weight[int64_t(c) * kernel + kk] : 0.0f;
+    h[kk] = kk < keep ? history[int64_t(kk) * conv_dim + c] : 0.0f;
   }
-  out[c] = acc;
-  for (int r = 0; r + 1 < keep; ++r) history[int64_t(r) * conv_dim + c] = history[int64_t(r + 1) * conv_dim + c];
-  if (keep > 0) history[int64_t(keep - 1) * conv_dim + c] = x;
+  for (int t = 0; t < n_tokens; ++t) {
+    const float x = qkv[int64_t(t) * conv_dim + c];
+    float acc = 0.0f;
+#pragma unroll
+    for (int kk = 0; kk < CONV_MAX_KERNEL; ++kk)
+      if (kk < kernel) acc = __fadd_rn(acc, __fmul_rn(kk < keep ? h[kk] : x, w[kk]));
+    out[int64_t(t) * conv_dim + c] = acc;
+#pragma unroll
+    for (int kk = 0; kk + 1 < CONV_MAX_KERNEL; ++kk)
+      if (kk < keep) h[kk] = kk + 1 < keep ? h[kk + 1] : x;
+  }
+#pragma unroll
+  for (int kk = 0; kk < CONV_MAX_KERNEL; ++kk)
+    if (kk < keep) history[int64_t(kk) * conv_dim + c] = h[kk];
 }
 
 cudaError_t launch_conv_step(const float* qkv, const float* weight, float* history, float* out, int conv_dim,
-                             int kernel, cudaStream_t stream) {
-  conv_step_kernel<<<(conv_dim + 255) / 256, 256, 0, stream>>>(qkv, weight, history, out, conv_dim, kernel);
+                             int kernel, int n_tokens, cudaStream_t stream) {
+  conv_step_kernel<<<(conv_dim + 255) / 256, 256, 0, stream>>>(qkv, weight, history, out, conv_dim, kernel, n_tokens);
   return cudaGetLastError();
 }
 

@@ -541,6 +541,17 @@ class LinearAttentionState:
     def restore(self, snapshot, stream=None):
         check(self.L.sgk_linstate_restore(self.h, stream, snapshot.h))
 
+    def encode_conv_seq(self, layer, d_qkv, d_weight, conv_dim, conv_kernel_dim, n_tokens, d_out, stream=None):
+        """depthwise_causal_conv over n_tokens tokens of the prompt, the window kept in registers."""
+        check(self.L.sgk_linstate_enqueue_conv_seq(self.h, stream, layer, d_qkv.ptr, d_weight.ptr, conv_dim,
+                                                   conv_kernel_dim, n_tokens, d_out.ptr))
+
+    def encode_gated_delta_seq(self, layer, shape, d_q, d_k, d_v, d_g, d_beta, n_tokens, d_out, stream=None):
+        """gated_delta over n_tokens tokens, the state kept in registers and written back once."""
+        sh = LinearShape(*shape)
+        check(self.L.sgk_linstate_enqueue_gated_delta_seq(self.h, stream, layer, C.byref(sh), d_q.ptr, d_k.ptr,
+                                                          d_v.ptr, d_g.ptr, d_beta.ptr, n_tokens, d_out.ptr))
+
     def encode_capture(self, capture, stream=None):
         """encode_capture_linear_attn_state: copy into an existing state of the same shape (no allocation)."""
         check(self.L.sgk_linstate_enqueue_capture(self.h, stream, capture.h))

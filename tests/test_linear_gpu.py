@@ -182,3 +182,83 @@ def test_batched_gated_delta_equals_one_launch_per_sequence(state, ssm_bf16):
     assert e.value.kind == "Config"
     for s in solo + both:
         s.close()
+
+
+@pytest.mark.parametrize("shape", [(2, 4, 8, 6), (1, 4, 128, 128), (2, 6, 96, 40)])
+@pytest.mark.parametrize("ssm_bf16", [False, True])
+def test_gated_delta_sequence_equals_the_step_loop(state, shape, ssm_bf16):
+    # linear_attn_gated_delta_seq_dk128_matches_step_loop (src/metal_backend/tests/linear_attention.rs:206-403):
+    # the prompt form keeps the state in registers over the tokens. f32 state: the same arithmetic
+    # as the step form, identical bits; bf16 state: rounded once at the end instead of per token,
+    # inside the reference's 5e-4 / 2e-4. Both against the oracle's token loop.
+    hk, hv, dk, dv = shape
+    tokens = 17
+    ssm_len = hv * dv * dk
+    init = sgo.fill_normal8(ssm_len, 70, 0) * np.float32(0.1)
+    if ssm_bf16:
+        init = sgo.bf16_round(init)
+    seq_state = sg.LinearAttentionState(state, 1, 0, ssm_len, ssm_bf16=ssm_bf16)
+    loop_state = sg.LinearAttentionState(state, 1, 0, ssm_len, ssm_bf16=ssm_bf16)
+    seq_state.write(0, np.zeros(0, np.float32), init)
+    loop_state.write(0, np.zeros(0, np.float32), init)
+    ins = [_inputs(shape, 71, t) for t in range(tokens)]
+    stacked = [state.upload(np.stack([ins[t][j] for t in range(tokens)])) for j in range(5)]
+    d_seq = state.alloc(4 * tokens * hv * dv)
+    seq_state.encode_gated_delta_seq(0, shape, *stacked, tokens, d_seq)
+    d_one = state.alloc(4 * hv * dv)
+    ref, ys_loop, ys_ref = init.copy(), [], []
+    for t in range(tokens):
+        loop_state.encode_gated_delta_step(0, shape, *[state.upload(a) for a in ins[t]], d_one)
+        state.sync()
+        ys_loop.append(d_one.download(count=hv * dv))
+        st, y, ref = sgo.gated_delta_step(*ins[t], hk, hv, dk, dv, ref)      # f32 over the whole sequence
+        assert st == sgo.OK
+        ys_ref.append(y)
+    state.sync()
+    ys_seq = d_seq.download(count=tokens * hv * dv).reshape(tokens, -1)
+    _, s_seq = seq_state.read(0)
+    _, s_loop = loop_state.read(0)
+    if not ssm_bf16:
+        np.testing.assert_array_equal(ys_seq, np.array(ys_loop))
+        np.testing.assert_array_equal(s_seq, s_loop)
+        np.testing.assert_allclose(ys_seq, np.array(ys_ref), rtol=0, atol=1e-5)
+        np.testing.assert_allclose(s_seq, ref, rtol=0, atol=1e-5)
+    else:
+        np.testing.assert_allclose(ys_seq, np.array(ys_ref), rtol=0, atol=5e-4)
+        assert np.all(np.abs(s_seq - sgo.bf16_round(ref)) <= np.maximum(2e-4, np.abs(ref) * 2.0 ** -7))
+        np.testing.assert_allclose(ys_seq, np.array(ys_loop), rtol=0, atol=5e-3)   # per-token rounding drifts
+    seq_state.close()
+    loop_state.close()
+
+
+@pytest.mark.parametrize("conv_dim,kernel", [(8192, 4), (100, 2), (33, 7)])
+def test_conv_sequence_equals_the_step_loop_bit_for_bit(state, conv_dim, kernel):
+    tokens = 21
+    conv_len = (kernel - 1) * conv_dim
+    a = sg.LinearAttentionState(state, 1, conv_len, 8)
+    b = sg.LinearAttentionState(state, 1, conv_len, 8)
+    hist = sgo.fill_normal8(conv_len, 80, 0)
+    a.write(0, hist, np.zeros(8, np.float32))
+    b.write(0, hist, np.zeros(8, np.float32))
+    w = sgo.fill_normal8(conv_dim * kernel, 80, 1)
+    x = sgo.fill_normal8(tokens * conv_dim, 80, 2).reshape(tokens, conv_dim)
+    d_w = state.upload(w)
+    d_all, d_one = state.alloc(4 * tokens * conv_dim), state.alloc(4 * conv_dim)
+    a.encode_conv_seq(0, state.upload(x), d_w, conv_dim, kernel, tokens, d_all)
+    state.sync()
+    got = d_all.download(count=tokens * conv_dim).reshape(tokens, conv_dim)
+    ref_hist = hist
+    for t in range(tokens):
+        b.encode_conv_step(0, state.upload(x[t]), d_w, conv_dim, kernel, d_one)
+        st, o_ref, ref_hist = sgo.depthwise_conv_step(x[t], w, kernel, ref_hist)
+        assert st == sgo.OK
+        state.sync()
+        np.testing.assert_array_equal(got[t], d_one.download(count=conv_dim))
+        np.testing.assert_array_equal(got[t], o_ref)
+    np.testing.assert_array_equal(a.read(0)[0], b.read(0)[0])
+    np.testing.assert_array_equal(a.read(0)[0], ref_hist)
+    with pytest.raises(sg.InferError) as e:
+        a.encode_conv_seq(0, d_all, d_w, conv_dim, 17, 1, d_one)
+    assert e.value.kind in ("Config", "Dimension")
+    a.close()
+    b.close()
