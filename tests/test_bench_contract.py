@@ -1,0 +1,34 @@
+"""The benchmark's JSON contract, checked where no GPU is needed: the reference arm (the CPU
+restatement of the reference path, timed on the host cores) prints one line with the keys the
+driver reads, and the other ranks of a multi-rank launch print nothing."""
+import json
+import os
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(env_extra):
+    env = dict(os.environ, **env_extra)
+    return subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "2",
+                           "--warmup", "1"], capture_output=True, text=True, env=env, cwd=ROOT, timeout=300)
+
+
+def test_reference_arm_prints_one_contract_line():
+    out = _run({"RANK": "0"})
+    assert out.returncode == 0, out.stderr
+    lines = [ln for ln in out.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["metric"] == "decode_attn_append_hbm_gbs_32k" and d["unit"] == "GB/s"
+    assert d["higher_is_better"] is True and d["steps"] == 2 and d["warmup"] == 1 and d["value"] > 0
+    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1 and d["cpu_baseline"]["sample"]
+    assert d["e2e"] == {"value": d["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert "workload" in d["config"] and "model" not in d["config"]
+
+
+def test_reference_arm_is_silent_on_other_ranks():
+    out = _run({"RANK": "1", "WORLD_SIZE": "2"})
+    assert out.returncode == 0, out.stderr
+    assert not [ln for ln in out.stdout.splitlines() if ln.startswith("{")]
