@@ -135,6 +135,7 @@ struct Batch {
   float* d_part2_ml = nullptr;
   int32_t* d_group_counters = nullptr;
   int uniform_splits = 1;
+  int resident_per_sm = -1, resident_stages = 0;   // blocks of the attention kernel an SM holds at once
   int max_splits = 1;
   int max_groups = 1;
   int splits_override = 0;

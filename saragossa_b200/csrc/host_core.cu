@@ -463,6 +463,21 @@ int Batch::enqueue_attention(cudaStream_t stream, const float* d_q, float* d_out
 #ifdef SGK_TRACE
     a.trace = g_trace;
 #endif
+    // When every block of the launch is resident at once, all blocks of a (sequence, KV head)
+    // can merge a slice each after waiting for one another; otherwise (several waves, uneven
+    // batches) the last arriver of a group merges, which needs nobody to wait. Blocks that wait
+    // for each other make the launch a cooperative one, which costs about 2 us: worth it only
+    // where the other scheme needs two merge levels (more than 12 splits).
+    static const bool shared_merge_off = std::getenv("SGK_NO_SHARED_MERGE") != nullptr;
+    if (!shared_merge_off && a.pages_per_split == 0 && a.splits > 12 && a.splits <= 160) {
+      if (resident_per_sm < 0 || resident_stages != a.n_stages)   // asked once per batch
+        resident_per_sm = kernel == 3 ? attention_u8_resident_blocks(pool->head_dim, a.n_stages)
+                                      : attention_mma_resident_blocks(pool->head_dim, a.n_stages),
+        resident_stages = a.n_stages;
+      const int per_sm = resident_per_sm;
+      const int64_t blocks = int64_t(a.splits) * pool->kv_heads * n();
+      if (per_sm > 0 && blocks <= int64_t(per_sm) * st->sm_count) a.shared_merge = 1;
+    }
     if (kernel == 3) {
       SGK_CUDA(launch_attention_u8(a, n(), stream));
     } else {

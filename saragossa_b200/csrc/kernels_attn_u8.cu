@@ -638,6 +638,16 @@ int attention_u8_max_stages(int head_dim) {
   return n / MMA_CONSUMERS * MMA_CONSUMERS;  // a stage always belongs to the same warp
 }
 
+int attention_u8_resident_blocks(int head_dim, int n_stages) {
+  int blocks = 0;
+  cudaError_t e = head_dim == 128
+                      ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_u8_kernel<128>, MMA_THREADS,
+                                                                      U8Smem<128>::total(n_stages))
+                      : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_u8_kernel<256>, MMA_THREADS,
+                                                                      U8Smem<256>::total(n_stages));
+  return e == cudaSuccess ? blocks : 0;
+}
+
 cudaError_t attention_u8_configure() {
   cudaError_t e = cudaFuncSetAttribute(attention_u8_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        227 * 1024);
@@ -645,12 +655,29 @@ cudaError_t attention_u8_configure() {
   return cudaFuncSetAttribute(attention_u8_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
 }
 
+// A launch whose blocks wait for one another (shared merge) is a cooperative launch: the driver
+// then places all its blocks at once or not at all, also next to launches of other streams.
+static cudaError_t launch_one(void (*kernel)(AttnArgs), dim3 grid, size_t smem, const AttnArgs& a,
+                              cudaStream_t stream) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(MMA_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = a.shared_merge ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, a);
+}
+
 cudaError_t launch_attention_u8(const AttnArgs& a, int n_seq, cudaStream_t stream) {
   dim3 grid(a.splits, a.pool.kv_heads, n_seq);
   if (a.pool.head_dim == 128) {
-    attention_u8_kernel<128><<<grid, MMA_THREADS, U8Smem<128>::total(a.n_stages), stream>>>(a);
+    return launch_one(attention_u8_kernel<128>, grid, U8Smem<128>::total(a.n_stages), a, stream);
   } else {
-    attention_u8_kernel<256><<<grid, MMA_THREADS, U8Smem<256>::total(a.n_stages), stream>>>(a);
+    return launch_one(attention_u8_kernel<256>, grid, U8Smem<256>::total(a.n_stages), a, stream);
   }
   return cudaGetLastError();
 }

@@ -118,6 +118,98 @@ __device__ __forceinline__ int arrive_acq_rel(int32_t* counter) {
   return old;
 }
 
+__device__ __forceinline__ int ld_acquire_gpu(const int32_t* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Merge shared by ALL blocks of a (sequence, KV head), for launches whose blocks are all resident
+// at once (the host checks that the grid fits the device): every block publishes its partial,
+// waits (bounded) until all `splits` partials are there, and then merges a slice of the output:
+// one warp per cell of four dims, a lane per partial (strided), one round of loads, the sums
+// reduced with shuffles. The tail of the launch is then one wait and one L2 round trip instead of
+// two merge levels done by single blocks. Returns false when the wait ran out.
+constexpr int SHARED_MERGE_MAX_SPLITS = 160;   // five partials per lane
+template <int HD, int NT>
+__device__ __forceinline__ bool shared_merge(const AttnArgs& a, int splits, int split, int gqa, int64_t qh0,
+                                             int32_t* arrive_counter, int32_t* depart_counter, int* flags, int tid) {
+  volatile int* abort_flag = flags;
+  if (tid == 0) {
+    arrive_acq_rel(arrive_counter);   // releases this block's partial (the block has synchronised before)
+    uint32_t spins = 0;
+    while (ld_acquire_gpu(arrive_counter) < splits) {
+      if (++spins > WAIT_SPINS) {
+        *abort_flag = 1;
+        atomicExch(a.status, DEV_ERR_WAIT_TIMEOUT);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  const bool ok = *abort_flag == 0;
+  if (ok) {
+    const int lane = tid & 31;
+    const int warps = NT / 32;
+    const int cells = gqa * (HD / 4);
+    for (int cell = split * warps + (tid >> 5); cell < cells; cell += splits * warps) {
+      const int h = cell / (HD / 4), d = (cell % (HD / 4)) * 4;
+      const float* pm = a.part.ml + (qh0 + h) * a.splits * 2;
+      const float* po = a.part.o + (qh0 + h) * a.splits * HD + d;
+      float2 ml[5];
+      float4 v[5];
+#pragma unroll
+      for (int i = 0; i < 5; ++i) {
+        const int p = lane + 32 * i;
+        if (p < splits) {
+          ml[i] = __ldcg(reinterpret_cast<const float2*>(pm + 2 * p));
+          v[i] = __ldcg(reinterpret_cast<const float4*>(po + int64_t(p) * HD));
+        }
+      }
+      float m = -1.0e30f;
+#pragma unroll
+      for (int i = 0; i < 5; ++i)
+        if (lane + 32 * i < splits) m = fmaxf(m, ml[i].x);
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+      float l = 0.0f;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int i = 0; i < 5; ++i)
+        if (lane + 32 * i < splits) {
+          const float w = exp2f(ml[i].x - m);
+          l += ml[i].y * w;
+          acc.x += v[i].x * w;
+          acc.y += v[i].y * w;
+          acc.z += v[i].z * w;
+          acc.w += v[i].w * w;
+        }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        l += __shfl_xor_sync(0xffffffffu, l, off);
+        acc.x += __shfl_xor_sync(0xffffffffu, acc.x, off);
+        acc.y += __shfl_xor_sync(0xffffffffu, acc.y, off);
+        acc.z += __shfl_xor_sync(0xffffffffu, acc.z, off);
+        acc.w += __shfl_xor_sync(0xffffffffu, acc.w, off);
+      }
+      if (lane == 0) {
+        const float inv = 1.0f / l;
+        *reinterpret_cast<float4*>(a.out + (qh0 + h) * HD + d) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+      }
+    }
+  }
+  __syncthreads();
+  // the block that leaves last puts both counters back (every other block is past its wait)
+  if (tid == 0) {
+    int old = atomicAdd(depart_counter, 1);
+    if (old == splits - 1) {
+      *arrive_counter = 0;
+      *depart_counter = 0;
+    }
+  }
+  return ok;
+}
+
 // Block-cooperative merge of `count` (<= MERGE_MAX) partials (rows first..first+count
 // of a [q head][stride][HD] array) for the gqa heads starting at qh0. A thread owns
 // cells of four dims; per pass it handles two cells and issues every load it needs
@@ -242,6 +334,20 @@ __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s
     int32_t* group_counter = a.group_counters + (int64_t(seq) * a.pool.kv_heads + kvh) * a.max_groups + group;
     int32_t* head_counter = a.head_counters + int64_t(seq) * a.pool.kv_heads + kvh;
     __syncthreads();
+    if (a.shared_merge && splits > 1 && splits <= SHARED_MERGE_MAX_SPLITS) {
+      if (tid == 32 && do_append) {
+        // the block that arrives last for the sequence moves the cursor
+        int total = splits * a.pool.kv_heads;
+        int old = arrive_acq_rel(a.seq_counters + seq);
+        if (old == total - 1) {
+          *len_ptr = static_cast<int32_t>(len);
+          a.seq_counters[seq] = 0;
+        }
+      }
+      shared_merge<HD, NT>(a, splits, split, gqa, qh0, head_counter, group_counter - group, flags, tid);
+      if (tid == 0) SGK_TP(7);
+      return;
+    }
     // two arrivals, on two threads of different warps so that their round trips overlap
     if (tid == 0 && splits > 1) {
       int old = arrive_acq_rel(group_counter);
