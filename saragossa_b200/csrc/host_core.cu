@@ -466,8 +466,8 @@ int Batch::enqueue_attention(cudaStream_t stream, const float* d_q, float* d_out
     // When every block of the launch is resident at once, all blocks of a (sequence, KV head)
     // can merge a slice each after waiting for one another; otherwise (several waves, uneven
     // batches) the last arriver of a group merges, which needs nobody to wait. Blocks that wait
-    // for each other make the launch a cooperative one, which costs about 2 us: worth it only
-    // where the other scheme needs two merge levels (more than 12 splits).
+    // for each other make the launch a cooperative one. Used where the other scheme needs two
+    // merge levels (more than 12 splits); below that, measured, the last arriver alone is faster.
     static const bool shared_merge_off = std::getenv("SGK_NO_SHARED_MERGE") != nullptr;
     if (!shared_merge_off && a.pages_per_split == 0 && a.splits > 12 && a.splits <= 160) {
       if (resident_per_sm < 0 || resident_stages != a.n_stages)   // asked once per batch
