@@ -98,20 +98,15 @@ struct U8Smem {
 };
 
 // Quantises N groups of 32 values at once (lane l holds element l of every group), with the
-// arithmetic of the append kernel. The min/max butterflies of all groups run side by side:
-// one after the other they would each wait for their own five shuffle round trips.
+// arithmetic of the append kernel.
 template <int N>
 __device__ __forceinline__ void quantize_groups(const float (&x)[N], uint32_t (&code)[N], uint32_t (&meta)[N]) {
   float lo[N], hi[N];
+  // warp-wide float min / max in one instruction each (sm_100a)
 #pragma unroll
-  for (int i = 0; i < N; ++i) lo[i] = hi[i] = x[i];
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) {
-#pragma unroll
-    for (int i = 0; i < N; ++i) {
-      lo[i] = fminf(lo[i], __shfl_xor_sync(0xffffffffu, lo[i], off));
-      hi[i] = fmaxf(hi[i], __shfl_xor_sync(0xffffffffu, hi[i], off));
-    }
+  for (int i = 0; i < N; ++i) {
+    asm("redux.sync.min.f32 %0, %1, 0xffffffff;" : "=f"(lo[i]) : "f"(x[i]));
+    asm("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(hi[i]) : "f"(x[i]));
   }
 #pragma unroll
   for (int i = 0; i < N; ++i) {
