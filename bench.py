@@ -76,7 +76,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -335,6 +335,7 @@ def run_ours(args):
     c3 = guarded(c3_token_leg, sg, st, torch, stream)
     c5 = guarded(c5_serving_leg, sg, st, torch, stream)
     c4 = guarded(c4_prefix_leg, sg, st, torch, stream)
+    c1 = guarded(c1_decode_leg, sg, st, torch, stream) if rank == 0 else None
 
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -357,7 +358,7 @@ def run_ours(args):
             "decode_steps_per_s": BATCH * world * K / (ms * 1e-3),
             "batch1": {"us_per_layer": b1_us_layer, "hbm_gbs": b1_gbs, "steps": b1_steps,
                        "frac_of_peak": b1_gbs / peak},
-            "prefix_restore": restore, "head_sharded_batch1": head_sharded, "gated_delta_step": recurrent, "bulk_append": producer, "c3_hybrid_token": c3, "c5_serving": c5, "c4_prefix_turns": c4,
+            "prefix_restore": restore, "head_sharded_batch1": head_sharded, "gated_delta_step": recurrent, "bulk_append": producer, "c3_hybrid_token": c3, "c5_serving": c5, "c4_prefix_turns": c4, "c1_decode": c1,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": alg_per_launch * NCU_TRAFFIC_RATIO,
                          "kernel": "attention_mma_kernel<128> (fused append + paged decode attention)",
@@ -537,6 +538,73 @@ def gated_delta_leg(sg, st, torch, stream):
     nbytes = 2 * 4 * n * ssm_len
     return {"us_per_layer": t * 1e6, "hbm_gbs": nbytes / t / 1e9, "sequences": n, "state_bytes_per_layer": nbytes // 2,
             "outputs_finite": finite, "launches": (2 + 3 + reps) * layers}
+
+
+def c1_decode_leg(sg, st, torch, stream):
+    """Config 1 as stated (the reference's own CPU-runnable case): one sequence, 36 layers,
+    32 Q / 8 KV heads, hd128, bf16 pages, context prefilled to 1024 rows, 64 decode steps of
+    append + attention; the device runs each token as one CUDA graph of 36 fused launches. The
+    CPU restatement of the reference path runs the same token (36 layers) a few times beside it."""
+    from oracle import sgo
+    layers, qh, kvh, hd, ctx, steps = 36, 32, 8, 128, 1024, 64
+    kv_dim, q_dim = kvh * hd, qh * hd
+    cap = ctx + steps + 16
+    pool = st.pool(layers, kvh, hd, sg.KV_BF16, cap // 16 + 2, 1, cap)
+    pool.shuffle_free_list(1)
+    seq = pool.sequence(cap)
+    kvs = [seq.layer(layer, qh) for layer in range(layers)]
+    dk_, dv_ = st.alloc(ctx * kv_dim * 4), st.alloc(ctx * kv_dim * 4)
+    for layer, kv in enumerate(kvs):
+        st.fill_normal(dk_, ctx * kv_dim, 0, 2 * layer)
+        st.fill_normal(dv_, ctx * kv_dim, 0, 2 * layer + 1)
+        kv.encode_append_rows(dk_, dv_, ctx)
+    st.sync()
+    batches = [sg.Batch(st, [kv]) for kv in kvs]
+    step = sg.Step(st, batches)
+    d_k, d_v = st.alloc(4 * layers * kv_dim), st.alloc(4 * layers * kv_dim)
+    d_q, d_out = st.alloc(4 * layers * q_dim), st.alloc(4 * layers * q_dim)
+    st.fill_normal(d_k, layers * kv_dim, 1, 0)
+    st.fill_normal(d_v, layers * kv_dim, 1, 1)
+    st.fill_normal(d_q, layers * q_dim, 1, 2)
+    st.sync()
+    step.capture(d_k, d_v, d_q, d_out)
+    for _ in range(3):
+        step.replay(stream.cuda_stream)
+    stream.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps - 3):
+        step.replay(stream.cuda_stream)
+    e1.record(stream)
+    stream.synchronize()
+    us_token = e0.elapsed_time(e1) * 1e3 / (steps - 3)
+    finite = bool(np.isfinite(d_out.download(count=layers * q_dim)).all())
+    step.close()
+    for b in batches:
+        b.close()
+    seq.close()
+    pool.close()
+    # the CPU path on the same token: one layer's cache, walked 36 times per token
+    threads = min(qh, os.cpu_count() or 1)
+    k = sgo.bf16_round(sgo.fill_normal8(ctx * kv_dim, 0, 0)).reshape(ctx, kv_dim)
+    v = sgo.bf16_round(sgo.fill_normal8(ctx * kv_dim, 0, 1)).reshape(ctx, kv_dim)
+    cache = sgo.LayerKvCache()
+    assert cache.append_batch(k, v, kv_dim) == sgo.OK
+    q = sgo.fill_normal8(q_dim, 1, 2)
+    row = sgo.bf16_round(sgo.fill_normal8(kv_dim, 1, 0))
+    t_cpu = []
+    for it in range(3):
+        t0 = time.perf_counter()
+        for _ in range(layers):
+            assert cache.append(row[None], row[None], kv_dim) == sgo.OK
+            rc, _ = sgo.cached_attention_one(q, np.ctypeslib.as_array(sgo.lib().sgo_cache_keys(cache._h), shape=(cache.len() * kv_dim,)),
+                                             np.ctypeslib.as_array(sgo.lib().sgo_cache_values(cache._h), shape=(cache.len() * kv_dim,)),
+                                             qh, kvh, hd, threads=threads)
+            assert rc == sgo.OK
+        t_cpu.append(time.perf_counter() - t0)
+    return {"us_per_token": us_token, "us_per_layer": us_token / layers, "launches_per_token": layers,
+            "cpu_port_us_per_token": min(t_cpu[1:]) * 1e6, "cpu_threads": threads, "outputs_finite": finite,
+            "shape": "batch 1, 36 layers, 32Q/8KV hd128 bf16, ctx 1024 -> 1088"}
 
 
 def c3_token_leg(sg, st, torch, stream):
