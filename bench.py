@@ -336,6 +336,7 @@ def run_ours(args):
     c5 = guarded(c5_serving_leg, sg, st, torch, stream)
     c4 = guarded(c4_prefix_leg, sg, st, torch, stream)
     c1 = guarded(c1_decode_leg, sg, st, torch, stream) if rank == 0 else None
+    lm_head = guarded(lm_head_leg, sg, st, torch, stream)
 
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -358,7 +359,7 @@ def run_ours(args):
             "decode_steps_per_s": BATCH * world * K / (ms * 1e-3),
             "batch1": {"us_per_layer": b1_us_layer, "hbm_gbs": b1_gbs, "steps": b1_steps,
                        "frac_of_peak": b1_gbs / peak},
-            "prefix_restore": restore, "head_sharded_batch1": head_sharded, "gated_delta_step": recurrent, "bulk_append": producer, "c3_hybrid_token": c3, "c5_serving": c5, "c4_prefix_turns": c4, "c1_decode": c1,
+            "prefix_restore": restore, "head_sharded_batch1": head_sharded, "gated_delta_step": recurrent, "bulk_append": producer, "c3_hybrid_token": c3, "c5_serving": c5, "c4_prefix_turns": c4, "c1_decode": c1, "lm_head_argmax": lm_head,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": alg_per_launch * NCU_TRAFFIC_RATIO,
                          "kernel": "attention_mma_kernel<128> (fused append + paged decode attention)",
@@ -538,6 +539,43 @@ def gated_delta_leg(sg, st, torch, stream):
     nbytes = 2 * 4 * n * ssm_len
     return {"us_per_layer": t * 1e6, "hbm_gbs": nbytes / t / 1e9, "sequences": n, "state_bytes_per_layer": nbytes // 2,
             "outputs_finite": finite, "launches": (2 + 3 + reps) * layers}
+
+
+def lm_head_leg(sg, st, torch, stream):
+    """Greedy epilogue of a token: argmax of W . x over a dense bf16 [151936][2560] weight
+    (778 MB, larger than L2, read once per launch), for one row and for the 4 rows of a
+    speculative verify that share the pass."""
+    vocab, hidden = 151936, 2560
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(11)
+    w = (torch.randn(vocab, hidden, device=dev, generator=gen) * 0.02).to(torch.bfloat16)
+    x = torch.randn(4, hidden, device=dev, generator=gen)
+    idx = torch.zeros(8, dtype=torch.int32, device=dev)
+    out = {"vocab": vocab, "hidden": hidden, "weight_bytes": vocab * hidden * 2}
+    launches = 0
+    for rows in (1, 4):
+        def step():
+            st.encode_lm_head_argmax(_Ptr(w), sg.KV_BF16, vocab, hidden, _Ptr(x), _Ptr(idx), n_rows=rows,
+                                     stream=stream.cuda_stream)
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                step()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 10
+            stream.synchronize()
+            e0.record(stream)
+            for _ in range(reps):
+                step()
+            e1.record(stream)
+            stream.synchronize()
+        launches += 3 + reps
+        t = e0.elapsed_time(e1) * 1e-3 / reps
+        want = torch.argmax(x[:rows] @ w.float().T, dim=1).to(torch.int32)
+        out[f"rows{rows}"] = {"us": t * 1e6, "hbm_gbs": vocab * hidden * 2 / t / 1e9,
+                              "matches_torch_argmax": bool((idx[:rows] == want).all().item())}
+    out["launches"] = launches
+    return out
 
 
 def c1_decode_leg(sg, st, torch, stream):

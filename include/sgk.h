@@ -265,6 +265,23 @@ int32_t sgk_linstate_write(sgk_linstate* ls, int32_t layer, const float* conv, c
 int32_t sgk_linstate_read(sgk_linstate* ls, int32_t layer, float* conv, float* ssm);
 int32_t sgk_linstate_snapshot(sgk_linstate* ls, void* stream, sgk_linstate** snapshot_out);
 int32_t sgk_linstate_restore(sgk_linstate* ls, void* stream, const sgk_linstate* snapshot);
+/* Greedy token epilogue, resident on the device: for each of n_rows (1..8) activation rows x
+ * [n_rows][hidden] (f32), the index of the largest of W . x over a dense biasless [vocab][hidden]
+ * weight (weight_dtype SGK_KV_F32 or SGK_KV_BF16), without writing the logits; the rows of a
+ * speculative verify share ONE pass over the weight (argmax_linear_biasless_rows_buffers,
+ * src/metal_backend/lm_head.rs:766-820, re-reads it per row). Replaces encode_lm_head_argmax / argmax_linear_biasless for dense weights
+ * (src/metal_backend/lm_head.rs:150-195,288-337; kernels argmax_blocks_f32 / argmax_finalize_f32,
+ * src/kernels.metal:8362-8440). Ties go to the LOWEST index (src/sampling.rs:49-62). Products are
+ * accumulated in f32; against bf16 weights x enters the tensor cores as the sum of two bf16 values
+ * (16 mantissa bits), and a row's logit is the same bit for bit whichever rows share the call.
+ * d_index_out [n_rows] receives index + index_offset (a vocabulary shard adds its first row);
+ * d_value_out [n_rows] (may be NULL) the winning logits. hidden: a multiple of 8; the rows must fit
+ * 200 KiB of shared memory (4 bytes per value; f32 weights pad the rows to 1, 2, 4 or 8); weight
+ * and x 16-byte aligned. Enqueue only; calls on one state must be stream-ordered (they share a
+ * 16-byte workspace). Quantised weights are not handled here. */
+int32_t sgk_lm_head_enqueue_argmax(sgk_state* state, void* stream, const void* d_weight, int32_t weight_dtype,
+                                   int64_t vocab, int32_t hidden, const float* d_x, int32_t n_rows,
+                                   int32_t index_offset, int32_t* d_index_out, float* d_value_out);
 /* encode_capture_linear_attn_state (src/metal_backend/linear_attention.rs:93-127): copies the
  * state into an EXISTING state of the same shape (one made ahead with sgk_linstate_create, like the
  * reference's leased per-row captures, :44-91): enqueue only, no allocation. Shape error if the

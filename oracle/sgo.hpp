@@ -198,6 +198,12 @@ Status gated_delta_step(const float* q, const float* k, const float* v, const fl
 Status depthwise_conv_step(const float* qkv, const float* weight, size_t conv_dim, size_t kernel,
                            std::vector<float>* history, float* out);
 
+// Greedy epilogue: logits = W . x for a biasless [vocab][hidden] weight (sequential f32 sums), then
+// the FIRST maximum (src/sampling.rs:49-62: a later equal value does not replace the best; the Metal
+// path breaks ties the same way, src/kernels.metal:8362-8440). ERR_DIMENSION when vocab is 0 (the
+// reference returns None).
+Status lm_head_argmax(const float* weight, size_t vocab, size_t hidden, const float* x, size_t* index, float* value);
+
 // ---- deterministic input generators ---------------------------------------
 // pseudo(): the closed form of the reference's tests (src/decode_resident/tests.rs:544-547).
 float pseudo(uint64_t seed);

@@ -110,6 +110,7 @@ def _declare(L):
         "sgo_linear_restore_check": (i32, [sz, sz, i32, sz, sz, i32]),
         "sgo_gated_delta_step": (i32, [pf, pf, pf, pf, pf, sz, sz, sz, sz, pf, sz, pf]),
         "sgo_depthwise_conv_step": (i32, [pf, pf, sz, sz, pf, sz, pf]),
+        "sgo_lm_head_argmax": (i32, [pf, sz, sz, pf, psz, pf]),
         "sgo_pseudo": (f, [u64]),
         "sgo_pseudo_array": (None, [u64, sz, pf]),
         "sgo_splitmix64": (u64, [u64]),
@@ -471,6 +472,15 @@ def depthwise_conv_step(qkv, weight, kernel, history):
     out = np.empty(qkv.size, np.float32)
     st = lib().sgo_depthwise_conv_step(_fp(qkv), _fp(weight), qkv.size, kernel, _fp(hist), hist.size, _fp(out))
     return st, out, hist
+
+
+def lm_head_argmax(weight, x):
+    """First maximum of W . x (src/sampling.rs:49-62); weight [vocab][hidden]; returns (status, index, value)."""
+    weight, x = _f32(weight), _f32(x).ravel()
+    vocab = weight.shape[0] if weight.ndim == 2 else 0
+    idx, val = C.c_size_t(0), C.c_float(0.0)
+    st = lib().sgo_lm_head_argmax(_fp(weight.ravel()), vocab, x.size, _fp(x), C.byref(idx), C.byref(val))
+    return st, int(idx.value), float(val.value)
 
 
 # ---- generators ----------------------------------------------------------------------

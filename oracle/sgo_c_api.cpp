@@ -247,6 +247,11 @@ int32_t sgo_depthwise_conv_step(const float* qkv, const float* weight, size_t co
   return st;
 }
 
+int32_t sgo_lm_head_argmax(const float* weight, size_t vocab, size_t hidden, const float* x, size_t* index,
+                           float* value) {
+  return lm_head_argmax(weight, vocab, hidden, x, index, value);
+}
+
 // ---- generators ---------------------------------------------------------------------------
 float sgo_pseudo(uint64_t seed) { return pseudo(seed); }
 void sgo_pseudo_array(uint64_t seed0, size_t n, float* out) {

@@ -309,4 +309,22 @@ Status depthwise_conv_step(const float* qkv, const float* weight, size_t conv_di
   return OK;
 }
 
+// ---- greedy epilogue (src/sampling.rs:49-62 over a biasless Linear) -------------
+Status lm_head_argmax(const float* weight, size_t vocab, size_t hidden, const float* x, size_t* index, float* value) {
+  if (vocab == 0) return ERR_DIMENSION;
+  size_t best = 0;
+  float best_value = 0.0f;
+  for (size_t r = 0; r < vocab; ++r) {
+    float acc = 0.0f;
+    for (size_t c = 0; c < hidden; ++c) acc += weight[r * hidden + c] * x[c];
+    if (r == 0 || acc > best_value) {  // strictly greater: the first maximum stays
+      best = r;
+      best_value = acc;
+    }
+  }
+  *index = best;
+  *value = best_value;
+  return OK;
+}
+
 }  // namespace sgo

@@ -48,6 +48,8 @@ int32_t sgk_state_create(int32_t device, sgk_state** out) {
   SGK_CUDA(cudaStreamCreateWithFlags(&st->stream, cudaStreamNonBlocking));
   SGK_CUDA(cudaMalloc(&st->d_status, sizeof(int32_t)));
   SGK_CUDA(cudaMemset(st->d_status, 0, sizeof(int32_t)));
+  SGK_CUDA(cudaMalloc(&st->d_lm_ws, 9 * sizeof(unsigned long long)));
+  SGK_CUDA(cudaMemset(st->d_lm_ws, 0, 9 * sizeof(unsigned long long)));
   SGK_CUDA(attention_mma_configure());
   SGK_CUDA(attention_u8_configure());
   *out = st.release();
@@ -59,6 +61,7 @@ void sgk_state_destroy(sgk_state* st) {
   cudaSetDevice(st->device);
   cudaStreamSynchronize(st->stream);
   if (st->d_status) cudaFree(st->d_status);
+  if (st->d_lm_ws) cudaFree(st->d_lm_ws);
   if (st->stream) cudaStreamDestroy(st->stream);
   delete st;
 }
@@ -989,6 +992,39 @@ int32_t sgk_linstate_restore(sgk_linstate* ls, void* stream, const sgk_linstate*
                 (long long)ls->ssm_len, int(ls->ssm_bf16));
   SGK_CUDA(launch_copy_bytes(ls->d_base, snap->d_base, ls->total_bytes, ls->st->pick(stream)));
   ls->st->launches += 1;
+  return SGK_OK;
+}
+
+int32_t sgk_lm_head_enqueue_argmax(sgk_state* st, void* stream, const void* d_weight, int32_t weight_dtype,
+                                   int64_t vocab, int32_t hidden, const float* d_x, int32_t n_rows,
+                                   int32_t index_offset, int32_t* d_index_out, float* d_value_out) {
+  if (!st || !d_weight || !d_x || !d_index_out) return fail(SGK_ERR_BACKEND, "null argument");
+  if (weight_dtype != SGK_KV_F32 && weight_dtype != SGK_KV_BF16)
+    return fail(SGK_ERR_CONFIG, "lm_head weight dtype %d: only dense f32 and bf16 weights are supported", weight_dtype);
+  // argmax of an empty slice is None (src/sampling.rs:49-62); the device form has no None to write
+  if (vocab <= 0 || hidden <= 0) return fail(SGK_ERR_DIMENSION, "lm_head argmax: vocab %lld, hidden %d must be positive",
+                                              (long long)vocab, hidden);
+  if (vocab > 0x7fffffffLL) return fail(SGK_ERR_DIMENSION, "lm_head argmax: vocab %lld exceeds the 32-bit index", (long long)vocab);
+  if (n_rows < 1 || n_rows > 8) return fail(SGK_ERR_DIMENSION, "lm_head argmax: %d rows, 1 to 8 per call", n_rows);
+  if (hidden % 8 != 0) return fail(SGK_ERR_CONFIG, "lm_head argmax: hidden %d must be a multiple of 8", hidden);
+  if (lm_head_smem_bytes(weight_dtype == SGK_KV_BF16, n_rows, hidden) > size_t(200) * 1024)
+    return fail(SGK_ERR_CONFIG, "lm_head argmax: %d rows of %d values do not fit 200 KiB of shared memory", n_rows, hidden);
+  if ((reinterpret_cast<uintptr_t>(d_weight) & 15) || (reinterpret_cast<uintptr_t>(d_x) & 15))
+    return fail(SGK_ERR_CONFIG, "lm_head argmax: weight and x must be 16-byte aligned");
+  LmHeadArgs a{};
+  a.w = d_weight;
+  a.w_bf16 = weight_dtype == SGK_KV_BF16;
+  a.vocab = vocab;
+  a.hidden = hidden;
+  a.n_rows = n_rows;
+  a.x = d_x;
+  a.keys = st->d_lm_ws;
+  a.counter = reinterpret_cast<unsigned int*>(st->d_lm_ws + 8);
+  a.index_offset = index_offset;
+  a.index_out = d_index_out;
+  a.value_out = d_value_out;
+  SGK_CUDA(launch_lm_head_argmax(a, st->sm_count, st->pick(stream)));
+  st->launches += 1;
   return SGK_OK;
 }
 

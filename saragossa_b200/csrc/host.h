@@ -42,6 +42,7 @@ struct State {
   int sm_count = 148;
   cudaStream_t stream = nullptr;
   int32_t* d_status = nullptr;
+  unsigned long long* d_lm_ws = nullptr;  // lm_head argmax: [0..8) best key per row, [8] blocks-done counter; zero between launches
   int64_t launches = 0;  // kernels launched through this state
   cudaStream_t pick(void* s) const { return s ? static_cast<cudaStream_t>(s) : stream; }
 };

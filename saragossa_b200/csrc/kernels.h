@@ -144,6 +144,22 @@ struct GatedDeltaArgs {
 cudaError_t launch_gated_delta_step(const GatedDeltaArgs& a, cudaStream_t stream);
 cudaError_t launch_conv_step(const float* qkv, const float* weight, float* history, float* out, int conv_dim,
                              int kernel, int n_tokens, cudaStream_t stream);
+// Greedy epilogue: argmax over W . x without materialising the logits.
+struct LmHeadArgs {
+  const void* w;   // [vocab][hidden], f32 or bf16
+  int32_t w_bf16;
+  int64_t vocab;
+  int32_t hidden;  // multiple of 8; the activation rows are held in shared memory (lm_head_smem_bytes)
+  int32_t n_rows;  // 1..8 activation rows sharing the pass over the weight
+  const float* x;  // [n_rows][hidden]
+  unsigned long long* keys;  // workspace [8]: packed (value, index) of the best row so far; zero between launches
+  unsigned int* counter;    // workspace: blocks done; zero between launches
+  int32_t index_offset;
+  int32_t* index_out;  // [n_rows]
+  float* value_out;    // [n_rows], may be NULL
+};
+cudaError_t launch_lm_head_argmax(const LmHeadArgs& a, int sm_count, cudaStream_t stream);
+size_t lm_head_smem_bytes(int w_bf16, int n_rows, int hidden);  // shared memory a launch needs
 cudaError_t launch_fill_normal(float* out, int64_t n, uint64_t seed, uint64_t stream_id,
                                uint64_t index0, cudaStream_t stream);
 

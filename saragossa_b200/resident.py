@@ -169,6 +169,36 @@ class DecodeResidentState:
         a = np.ascontiguousarray(array)
         return DeviceBuffer(self, max(a.nbytes, 16)).upload(a)
 
+    def encode_lm_head_argmax(self, d_weight, weight_dtype, vocab, hidden, d_x, d_index_out, n_rows=1,
+                              index_offset=0, d_value_out=None, stream=None):
+        """encode_lm_head_argmax for a dense biasless weight (src/metal_backend/lm_head.rs:288-337):
+        the token index stays on the device. n_rows > 1 is the verify form (lm_head.rs:766-820)."""
+        check(self.L.sgk_lm_head_enqueue_argmax(self.h, stream, d_weight.ptr, weight_dtype, vocab, hidden, d_x.ptr,
+                                                n_rows, index_offset, d_index_out.ptr,
+                                                d_value_out.ptr if d_value_out is not None else None))
+
+    def argmax_linear_biasless(self, x, weight):
+        """argmax_linear_biasless (src/metal_backend/lm_head.rs:150-182): host x [hidden] or [rows][hidden]
+        and host weight [vocab][hidden] (float32, or uint16 holding bf16 bit patterns) -> indices."""
+        x = _f32(x)
+        w = np.ascontiguousarray(weight)
+        if w.dtype not in (np.float32, np.uint16):
+            raise InferError(2, f"argmax: weight dtype {w.dtype}, expected float32 or uint16 (bf16 bits)")
+        if w.ndim != 2 or x.shape[-1] != w.shape[1]:
+            raise InferError(1, f"argmax: x {x.shape} against weight {w.shape}")
+        rows = 1 if x.ndim == 1 else x.shape[0]
+        d_w, d_x = self.upload(w), self.upload(x)
+        d_i = self.alloc(4 * max(rows, 1))
+        try:
+            self.encode_lm_head_argmax(d_w, KV_BF16 if w.dtype == np.uint16 else KV_F32, w.shape[0], w.shape[1], d_x,
+                                       d_i, n_rows=rows)
+            self.sync()
+            out = d_i.download(np.int32, rows)
+        finally:
+            for b in (d_w, d_x, d_i):
+                b.free()
+        return int(out[0]) if x.ndim == 1 else out
+
     def fill_normal(self, buf: DeviceBuffer, n, seed, stream_id, index0=0, stream=None):
         check(self.L.sgk_util_fill_normal(self.h, stream, buf.ptr, n, seed, stream_id, index0))
 
