@@ -119,7 +119,14 @@ __global__ void __launch_bounds__(LM_THREADS) lm_head_argmax_f32_kernel(LmHeadAr
 }
 
 // ---- bf16 weights on the tensor cores ---------------------------------------------------
-constexpr int LM_UNROLL = 4;                 // 32-wide k chunks in flight per lane (8 x 16-byte loads)
+#ifndef SGK_LM_UNROLL
+#define SGK_LM_UNROLL 8
+#endif
+#ifndef SGK_LM_BLOCKS_PER_SM
+#define SGK_LM_BLOCKS_PER_SM 2
+#endif
+constexpr int LM_UNROLL = SGK_LM_UNROLL;     // 32-wide k chunks in flight per lane (2 x 16-byte loads each)
+constexpr int LM_BLOCKS_PER_SM = SGK_LM_BLOCKS_PER_SM;
 constexpr int LM_KPAD = 32 * LM_UNROLL;      // the activation rows are zero-padded to this many values
 
 __host__ __device__ inline int lm_x_stride_bytes(int hidden) {
@@ -127,7 +134,7 @@ __host__ __device__ inline int lm_x_stride_bytes(int hidden) {
   return padded + 64;                                                 // = 64 mod 128: rows g and g+1 hit different banks
 }
 
-__global__ void __launch_bounds__(LM_THREADS, 2) lm_head_argmax_bf16_kernel(LmHeadArgs a) {
+__global__ void __launch_bounds__(LM_THREADS, LM_BLOCKS_PER_SM) lm_head_argmax_bf16_kernel(LmHeadArgs a) {
   extern __shared__ __align__(16) unsigned char lm_smem[];
   __shared__ unsigned long long best_s[LM_WARPS][8];
   __shared__ unsigned int last_s;
@@ -244,7 +251,7 @@ cudaError_t launch_lm_head_argmax(const LmHeadArgs& a, int sm_count, cudaStream_
   const size_t smem = lm_head_smem_bytes(a.w_bf16, a.n_rows, a.hidden);
   int per_sm = static_cast<int>((200 * 1024) / (smem + 1024));
   if (a.w_bf16) {
-    per_sm = per_sm > 2 ? 2 : per_sm < 1 ? 1 : per_sm;
+    per_sm = per_sm > LM_BLOCKS_PER_SM ? LM_BLOCKS_PER_SM : per_sm < 1 ? 1 : per_sm;
     int blocks = sm_count * per_sm;
     const int64_t tiles = (a.vocab + 15) / 16;
     if (int64_t(blocks) * LM_WARPS > tiles) blocks = static_cast<int>((tiles + LM_WARPS - 1) / LM_WARPS);
