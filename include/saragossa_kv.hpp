@@ -209,9 +209,19 @@ class DecodeResidentState {
     if (rc != SGK_OK) return Result<std::vector<float>>::Err(rc);
     return Result<std::vector<float>>::Ok(std::move(out));
   }
+  // encode_lm_head_argmax (src/metal_backend/lm_head.rs:288-337) for a dense biasless weight; n_rows > 1 is
+  // the verify form (:766-820). Enqueue only: the indices land in d_index_out on the device.
+  Result<Unit> encode_lm_head_argmax(void* stream, const void* d_weight, GpuElement weight_element, size_t vocab,
+                                     size_t hidden, const float* d_x, size_t n_rows, int32_t* d_index_out,
+                                     int32_t index_offset = 0, float* d_value_out = nullptr) {
+    return unit(sgk_lm_head_enqueue_argmax(h_, stream, d_weight, static_cast<int32_t>(weight_element),
+                                           static_cast<int64_t>(vocab), static_cast<int32_t>(hidden), d_x,
+                                           static_cast<int32_t>(n_rows), index_offset, d_index_out, d_value_out));
+  }
   sgk_state* handle() const { return h_; }
 
  private:
+  static Result<Unit> unit(int32_t rc) { return rc == SGK_OK ? Result<Unit>::Ok(Unit{}) : Result<Unit>::Err(rc); }
   sgk_state* h_ = nullptr;
 };
 

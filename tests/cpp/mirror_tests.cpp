@@ -250,6 +250,41 @@ static void gated_delta_steps_match_cpu(DecodeResidentState& state) {
   }
 }
 
+// The greedy epilogue on the device against the CPU rule (first maximum, src/sampling.rs:49-62):
+// a planted winner per verify row, an exact tie that must go to the lower index, and the
+// dimension error of an empty vocabulary.
+static void lm_head_argmax_matches_cpu(DecodeResidentState& state) {
+  const size_t vocab = 1201, hidden = 96, rows = 3;
+  std::vector<float> w(vocab * hidden), x(rows * hidden);
+  sgo::fill_normal8(w.data(), w.size(), 91, 0, 0);
+  sgo::fill_normal8(x.data(), x.size(), 91, 1, 0);
+  for (auto& v : w) v *= 0.05f;
+  const size_t winners[rows] = {1200, 17, 640};
+  for (size_t r = 0; r < rows; ++r)
+    for (size_t c = 0; c < hidden; ++c) w[winners[r] * hidden + c] = x[r * hidden + c];  // logit = |x|^2 ~ 96
+  // row 1's winner gets an exact twin at a higher index: the lower one must stay
+  for (size_t c = 0; c < hidden; ++c) w[900 * hidden + c] = w[17 * hidden + c];
+  DeviceVec dw(state.handle(), w), dx(state.handle(), x), didx(state.handle(), std::vector<float>(8)),
+      dval(state.handle(), std::vector<float>(8));
+  CHECK(state.encode_lm_head_argmax(nullptr, dw.d, GpuElement::F32, vocab, hidden, dx.d, rows,
+                                    reinterpret_cast<int32_t*>(didx.d), 0, dval.d).ok);
+  CHECK(sgk_state_sync(state.handle()) == SGK_OK);
+  std::vector<float> raw = didx.read(), val = dval.read();
+  for (size_t r = 0; r < rows; ++r) {
+    size_t want = 0;
+    float want_value = 0.0f;
+    CHECK(sgo::lm_head_argmax(w.data(), vocab, hidden, x.data() + r * hidden, &want, &want_value) == sgo::OK);
+    int32_t got;
+    std::memcpy(&got, &raw[r], sizeof(got));
+    CHECK(want == winners[r]);
+    CHECK(static_cast<size_t>(got) == want);
+    CHECK(std::fabs(val[r] - want_value) <= 1e-4f * std::fabs(want_value));
+  }
+  auto bad = state.encode_lm_head_argmax(nullptr, dw.d, GpuElement::F32, 0, hidden, dx.d, 1,
+                                         reinterpret_cast<int32_t*>(didx.d));
+  CHECK(bad.is_err() && bad.error.kind == InferError::Dimension);
+}
+
 int main(int argc, char** argv) {
   const bool gpu = argc > 1 && std::string(argv[1]) == "gpu";
   prefix_cache_evicts_lru_block();
@@ -268,6 +303,7 @@ int main(int argc, char** argv) {
         run_attention_case(state, len, true);
       }
       gated_delta_steps_match_cpu(state);
+      lm_head_argmax_matches_cpu(state);
     }
   } else {
     auto made = DecodeResidentState::create(0);
