@@ -282,6 +282,41 @@ int32_t sgk_linstate_restore(sgk_linstate* ls, void* stream, const sgk_linstate*
 int32_t sgk_lm_head_enqueue_argmax(sgk_state* state, void* stream, const void* d_weight, int32_t weight_dtype,
                                    int64_t vocab, int32_t hidden, const float* d_x, int32_t n_rows,
                                    int32_t index_offset, int32_t* d_index_out, float* d_value_out);
+/* Token feed: the input row of the next token, looked up by an index that lives on the device
+ * (encode_embedding_from_index_buffers_scaled, src/metal_backend/matmul_encode.rs:424-557; kernel
+ * embed_gather_dense_from_u32_f32, src/kernels.metal:308-325): d_out[hidden] = table[*d_index] *
+ * embedding_scale, then rounded to bf16 and widened again when recast_bf16 is set. Dense table
+ * [vocab][hidden], SGK_KV_F32 or SGK_KV_BF16. Like the reference kernel, an index outside the table
+ * writes nothing. Enqueue only. */
+int32_t sgk_embed_enqueue_from_index(sgk_state* state, void* stream, const void* d_table, int32_t table_dtype,
+                                     int64_t vocab, int32_t hidden, const int32_t* d_index, float embedding_scale,
+                                     int32_t recast_bf16, float* d_out);
+
+/* The submission window of the resident decode loop (src/decoder/resident/decode.rs:114-173;
+ * RESIDENT_PIPELINE_WINDOW = 4, src/decoder/resident/types.rs:23): a ring of `depth` token indices
+ * on the device. Token n's epilogue writes its index into output_slot() (slot n % depth), token
+ * n+1's embedding lookup reads previous_slot(); the host enqueues up to `depth` tokens before it
+ * reads the oldest back.
+ *   output_slot    device word the next token's argmax must write; NULL while the window is full
+ *   submit         call after the token's work has been enqueued on `stream`: copies the slot to
+ *                  pinned host memory behind that work and marks it; Dimension error when full
+ *   previous_slot  device word the last submitted token wrote; NULL before the first submit
+ *   pop            waits for the OLDEST token in flight and returns its index; Dimension error
+ *                  when nothing is in flight
+ *   drain          waits for everything in flight and forgets it (the stop-token exit, :167-169)
+ * All tokens of one window go to one stream. */
+typedef struct sgk_token_window sgk_token_window;
+int32_t sgk_token_window_create(sgk_state* state, int32_t depth, sgk_token_window** out);
+void sgk_token_window_destroy(sgk_token_window* w);
+int32_t* sgk_token_window_output_slot(sgk_token_window* w);
+const int32_t* sgk_token_window_previous_slot(sgk_token_window* w);
+int32_t sgk_token_window_submit(sgk_token_window* w, void* stream);
+int32_t sgk_token_window_pop(sgk_token_window* w, int32_t* token_out);
+int32_t sgk_token_window_inflight(const sgk_token_window* w);
+int64_t sgk_token_window_enqueued(const sgk_token_window* w);
+int32_t sgk_token_window_depth(const sgk_token_window* w);
+int32_t sgk_token_window_drain(sgk_token_window* w);
+
 /* encode_capture_linear_attn_state (src/metal_backend/linear_attention.rs:93-127): copies the
  * state into an EXISTING state of the same shape (one made ahead with sgk_linstate_create, like the
  * reference's leased per-row captures, :44-91): enqueue only, no allocation. Shape error if the

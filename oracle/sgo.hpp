@@ -204,6 +204,11 @@ Status depthwise_conv_step(const float* qkv, const float* weight, size_t conv_di
 // reference returns None).
 Status lm_head_argmax(const float* weight, size_t vocab, size_t hidden, const float* x, size_t* index, float* value);
 
+// Token feed: out = table[token] * scale, rounded to bf16 (RNE) and widened again when recast_bf16
+// (embed_gather_dense_from_u32_f32, src/kernels.metal:308-325). A token outside the table leaves out
+// untouched and returns false.
+bool embed_gather(const float* table, size_t vocab, size_t dim, size_t token, float scale, bool recast_bf16, float* out);
+
 // ---- deterministic input generators ---------------------------------------
 // pseudo(): the closed form of the reference's tests (src/decode_resident/tests.rs:544-547).
 float pseudo(uint64_t seed);

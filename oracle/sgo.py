@@ -111,6 +111,7 @@ def _declare(L):
         "sgo_gated_delta_step": (i32, [pf, pf, pf, pf, pf, sz, sz, sz, sz, pf, sz, pf]),
         "sgo_depthwise_conv_step": (i32, [pf, pf, sz, sz, pf, sz, pf]),
         "sgo_lm_head_argmax": (i32, [pf, sz, sz, pf, psz, pf]),
+        "sgo_embed_gather": (i32, [pf, sz, sz, sz, f, i32, pf]),
         "sgo_pseudo": (f, [u64]),
         "sgo_pseudo_array": (None, [u64, sz, pf]),
         "sgo_splitmix64": (u64, [u64]),
@@ -481,6 +482,15 @@ def lm_head_argmax(weight, x):
     idx, val = C.c_size_t(0), C.c_float(0.0)
     st = lib().sgo_lm_head_argmax(_fp(weight.ravel()), vocab, x.size, _fp(x), C.byref(idx), C.byref(val))
     return st, int(idx.value), float(val.value)
+
+
+def embed_gather(table, token, scale=1.0, recast_bf16=False):
+    """src/kernels.metal:308-325; table [vocab][dim]; returns the row, or None for a token outside the table."""
+    table = _f32(table)
+    out = np.zeros(table.shape[1], np.float32)
+    hit = lib().sgo_embed_gather(_fp(table.ravel()), table.shape[0], table.shape[1], token, scale, int(recast_bf16),
+                                 _fp(out))
+    return out if hit else None
 
 
 # ---- generators ----------------------------------------------------------------------

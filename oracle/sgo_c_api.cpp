@@ -252,6 +252,11 @@ int32_t sgo_lm_head_argmax(const float* weight, size_t vocab, size_t hidden, con
   return lm_head_argmax(weight, vocab, hidden, x, index, value);
 }
 
+int32_t sgo_embed_gather(const float* table, size_t vocab, size_t dim, size_t token, float scale, int32_t recast_bf16,
+                         float* out) {
+  return embed_gather(table, vocab, dim, token, scale, recast_bf16 != 0, out) ? 1 : 0;
+}
+
 // ---- generators ---------------------------------------------------------------------------
 float sgo_pseudo(uint64_t seed) { return pseudo(seed); }
 void sgo_pseudo_array(uint64_t seed0, size_t n, float* out) {

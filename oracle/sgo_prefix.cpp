@@ -327,4 +327,14 @@ Status lm_head_argmax(const float* weight, size_t vocab, size_t hidden, const fl
   return OK;
 }
 
+// ---- token feed (src/kernels.metal:308-325) ------------------------------------
+bool embed_gather(const float* table, size_t vocab, size_t dim, size_t token, float scale, bool recast_bf16, float* out) {
+  if (token >= vocab) return false;
+  for (size_t i = 0; i < dim; ++i) {
+    const float value = table[token * dim + i] * scale;
+    out[i] = recast_bf16 ? bf16_round_f32(value) : value;
+  }
+  return true;
+}
+
 }  // namespace sgo

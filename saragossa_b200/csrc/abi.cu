@@ -15,6 +15,7 @@ struct sgk_kv : Kv {};
 struct sgk_batch : Batch {};
 struct sgk_step : Step {};
 struct sgk_linstate : LinState {};
+struct sgk_token_window : TokenWindow {};
 struct sgk_prefix : Prefix {};
 struct sgk_budget : Budget {};
 
@@ -1025,6 +1026,90 @@ int32_t sgk_lm_head_enqueue_argmax(sgk_state* st, void* stream, const void* d_we
   a.value_out = d_value_out;
   SGK_CUDA(launch_lm_head_argmax(a, st->sm_count, st->pick(stream)));
   st->launches += 1;
+  return SGK_OK;
+}
+
+int32_t sgk_embed_enqueue_from_index(sgk_state* st, void* stream, const void* d_table, int32_t table_dtype,
+                                     int64_t vocab, int32_t hidden, const int32_t* d_index, float embedding_scale,
+                                     int32_t recast_bf16, float* d_out) {
+  if (!st || !d_table || !d_index || !d_out) return fail(SGK_ERR_BACKEND, "null argument");
+  if (table_dtype != SGK_KV_F32 && table_dtype != SGK_KV_BF16)
+    return fail(SGK_ERR_CONFIG, "embedding table dtype %d: only dense f32 and bf16 tables are supported", table_dtype);
+  if (vocab <= 0 || hidden <= 0 || vocab > 0x7fffffffLL)
+    return fail(SGK_ERR_DIMENSION, "embedding: vocab %lld, hidden %d invalid", (long long)vocab, hidden);
+  SGK_CUDA(launch_embed_gather(d_table, table_dtype == SGK_KV_BF16, d_index, vocab, hidden, embedding_scale,
+                               recast_bf16 != 0, d_out, st->pick(stream)));
+  st->launches += 1;
+  return SGK_OK;
+}
+
+// ------------------------------------------------------------------ token window
+int32_t sgk_token_window_create(sgk_state* st, int32_t depth, sgk_token_window** out) {
+  if (!st || !out) return fail(SGK_ERR_BACKEND, "null argument");
+  if (depth < 1 || depth > 64) return fail(SGK_ERR_CONFIG, "token window depth %d: 1 to 64", depth);
+  SGK_CUDA(cudaSetDevice(st->device));
+  auto w = std::make_unique<sgk_token_window>();
+  w->st = st;
+  w->depth = depth;
+  SGK_CUDA(cudaMalloc(&w->d_ring, sizeof(int32_t) * depth));
+  SGK_CUDA(cudaMemset(w->d_ring, 0xff, sizeof(int32_t) * depth));
+  SGK_CUDA(cudaHostAlloc(&w->h_ring, sizeof(int32_t) * depth, cudaHostAllocDefault));
+  for (int i = 0; i < depth; ++i) {
+    w->h_ring[i] = -1;
+    cudaEvent_t e;
+    SGK_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    w->done.push_back(e);
+  }
+  *out = w.release();
+  return SGK_OK;
+}
+
+void sgk_token_window_destroy(sgk_token_window* w) { delete w; }
+
+int32_t* sgk_token_window_output_slot(sgk_token_window* w) {
+  if (!w || w->inflight >= w->depth) return nullptr;
+  return w->d_ring + (w->enqueued % w->depth);
+}
+
+const int32_t* sgk_token_window_previous_slot(sgk_token_window* w) {
+  if (!w || w->enqueued == 0) return nullptr;
+  return w->d_ring + ((w->enqueued - 1) % w->depth);
+}
+
+int32_t sgk_token_window_submit(sgk_token_window* w, void* stream) {
+  if (!w) return fail(SGK_ERR_BACKEND, "null argument");
+  if (w->inflight >= w->depth)
+    return fail(SGK_ERR_DIMENSION, "token window: %d tokens in flight, the window holds %d", w->inflight, w->depth);
+  const int slot = static_cast<int>(w->enqueued % w->depth);
+  cudaStream_t s = w->st->pick(stream);
+  SGK_CUDA(cudaMemcpyAsync(w->h_ring + slot, w->d_ring + slot, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+  SGK_CUDA(cudaEventRecord(w->done[slot], s));
+  w->enqueued += 1;
+  w->inflight += 1;
+  return SGK_OK;
+}
+
+int32_t sgk_token_window_pop(sgk_token_window* w, int32_t* token_out) {
+  if (!w || !token_out) return fail(SGK_ERR_BACKEND, "null argument");
+  if (w->inflight == 0) return fail(SGK_ERR_DIMENSION, "token window: nothing in flight");
+  const int slot = static_cast<int>((w->enqueued - w->inflight) % w->depth);
+  SGK_CUDA(cudaEventSynchronize(w->done[slot]));
+  *token_out = w->h_ring[slot];
+  w->inflight -= 1;
+  return SGK_OK;
+}
+
+int32_t sgk_token_window_inflight(const sgk_token_window* w) { return w ? w->inflight : 0; }
+int64_t sgk_token_window_enqueued(const sgk_token_window* w) { return w ? w->enqueued : 0; }
+int32_t sgk_token_window_depth(const sgk_token_window* w) { return w ? w->depth : 0; }
+
+int32_t sgk_token_window_drain(sgk_token_window* w) {
+  if (!w) return fail(SGK_ERR_BACKEND, "null argument");
+  while (w->inflight > 0) {
+    const int slot = static_cast<int>((w->enqueued - w->inflight) % w->depth);
+    SGK_CUDA(cudaEventSynchronize(w->done[slot]));
+    w->inflight -= 1;
+  }
   return SGK_OK;
 }
 

@@ -185,6 +185,21 @@ struct LinState {
   ~LinState();
 };
 
+// The submission window of the resident decode loop (src/decoder/resident/decode.rs:114-173,
+// RESIDENT_PIPELINE_WINDOW = 4, src/decoder/resident/types.rs:23): a ring of token indices on the
+// device, written by the argmax of token n into slot n % depth and read by the embedding lookup of
+// token n+1, so the host can enqueue up to `depth` tokens before it reads the oldest back.
+struct TokenWindow {
+  State* st = nullptr;
+  int depth = 0;
+  int64_t enqueued = 0;  // tokens submitted so far
+  int inflight = 0;      // submitted and not yet popped
+  int32_t* d_ring = nullptr;
+  int32_t* h_ring = nullptr;  // pinned mirror, one word per slot
+  std::vector<cudaEvent_t> done;
+  ~TokenWindow();
+};
+
 using Hash32 = std::array<uint8_t, 32>;
 void sha256(const uint8_t* data, size_t n, uint8_t out[32]);
 Hash32 hash_chain(const Hash32& prev, const uint64_t* tokens, size_t n);

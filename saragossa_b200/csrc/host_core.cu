@@ -531,4 +531,14 @@ LinState::~LinState() {
   if (d_base) cudaFree(d_base);
 }
 
+TokenWindow::~TokenWindow() {
+  // copies still in flight write into h_ring: wait for them before the memory goes
+  for (cudaEvent_t e : done) {
+    cudaEventSynchronize(e);
+    cudaEventDestroy(e);
+  }
+  if (d_ring) cudaFree(d_ring);
+  if (h_ring) cudaFreeHost(h_ring);
+}
+
 }  // namespace sgk

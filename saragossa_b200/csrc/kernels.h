@@ -160,6 +160,9 @@ struct LmHeadArgs {
 };
 cudaError_t launch_lm_head_argmax(const LmHeadArgs& a, int sm_count, cudaStream_t stream);
 size_t lm_head_smem_bytes(int w_bf16, int n_rows, int hidden);  // shared memory a launch needs
+// out[hidden] = table[*index] * scale (dense f32 or bf16 table); an index outside the table writes nothing.
+cudaError_t launch_embed_gather(const void* table, int table_bf16, const int32_t* index, int64_t vocab, int hidden,
+                                float scale, int recast_bf16, float* out, cudaStream_t stream);
 cudaError_t launch_fill_normal(float* out, int64_t n, uint64_t seed, uint64_t stream_id,
                                uint64_t index0, cudaStream_t stream);
 

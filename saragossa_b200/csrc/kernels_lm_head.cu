@@ -241,6 +241,32 @@ static cudaError_t launch_r(const LmHeadArgs& a, int blocks, size_t smem, cudaSt
   return cudaGetLastError();
 }
 
+// ---- token feed: the next token's input row, looked up by an index that lives on the device --
+// embed_gather_dense_from_u32_f32 (src/kernels.metal:308-325): out = table[token] * scale, optionally
+// rounded to bf16 (RNE) and widened again; a token outside the table writes nothing.
+template <bool BF16>
+__global__ void embed_gather_kernel(const void* table, const int32_t* index, int64_t vocab, int hidden, float scale,
+                                    int recast_bf16, float* out) {
+  const int64_t token = *index;
+  if (token < 0 || token >= vocab) return;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < hidden; i += gridDim.x * blockDim.x) {
+    const float w = BF16 ? __uint_as_float(uint32_t(reinterpret_cast<const uint16_t*>(table)[token * hidden + i]) << 16)
+                         : reinterpret_cast<const float*>(table)[token * hidden + i];
+    const float v = __fmul_rn(w, scale);
+    out[i] = recast_bf16 ? __bfloat162float(__float2bfloat16_rn(v)) : v;
+  }
+}
+
+cudaError_t launch_embed_gather(const void* table, int table_bf16, const int32_t* index, int64_t vocab, int hidden,
+                                float scale, int recast_bf16, float* out, cudaStream_t stream) {
+  const int blocks = (hidden + 255) / 256 < 64 ? (hidden + 255) / 256 : 64;
+  if (table_bf16)
+    embed_gather_kernel<true><<<blocks, 256, 0, stream>>>(table, index, vocab, hidden, scale, recast_bf16, out);
+  else
+    embed_gather_kernel<false><<<blocks, 256, 0, stream>>>(table, index, vocab, hidden, scale, recast_bf16, out);
+  return cudaGetLastError();
+}
+
 size_t lm_head_smem_bytes(int w_bf16, int n_rows, int hidden) {
   if (w_bf16) return size_t(2) * n_rows * lm_x_stride_bytes(hidden);
   const int R = n_rows <= 1 ? 1 : n_rows <= 2 ? 2 : n_rows <= 4 ? 4 : 8;

@@ -102,6 +102,69 @@ class DeviceBuffer:
             pass
 
 
+class _RawPtr:
+    """A bare device address where the wrappers expect an object with `.ptr`."""
+
+    def __init__(self, ptr):
+        self.ptr = ptr
+
+
+class TokenWindow:
+    """The 4-deep submission window of the resident decode loop
+    (src/decoder/resident/decode.rs:114-173): a device ring of token indices."""
+
+    def __init__(self, state: "DecodeResidentState", depth: int = 4):
+        self.state, self.L = state, state.L
+        h = C.c_void_p()
+        check(self.L.sgk_token_window_create(state.h, depth, C.byref(h)))
+        self.h = h
+        state._adopt(self)
+
+    def output_slot(self):
+        """Device word the next token's argmax writes; None while the window is full."""
+        p = self.L.sgk_token_window_output_slot(self.h)
+        return _RawPtr(p) if p else None
+
+    def previous_slot(self):
+        """Device word the last submitted token wrote; None before the first submit."""
+        p = self.L.sgk_token_window_previous_slot(self.h)
+        return _RawPtr(p) if p else None
+
+    def submit(self, stream=None):
+        check(self.L.sgk_token_window_submit(self.h, stream))
+
+    def pop(self) -> int:
+        tok = C.c_int32(0)
+        check(self.L.sgk_token_window_pop(self.h, C.byref(tok)))
+        return int(tok.value)
+
+    def drain(self):
+        check(self.L.sgk_token_window_drain(self.h))
+
+    @property
+    def inflight(self) -> int:
+        return int(self.L.sgk_token_window_inflight(self.h))
+
+    @property
+    def enqueued(self) -> int:
+        return int(self.L.sgk_token_window_enqueued(self.h))
+
+    @property
+    def depth(self) -> int:
+        return int(self.L.sgk_token_window_depth(self.h))
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.L.sgk_token_window_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class DecodeResidentState:
     """DecodeResidentState::new (src/decode_resident/arena.rs:247-349)."""
 
@@ -176,6 +239,17 @@ class DecodeResidentState:
         check(self.L.sgk_lm_head_enqueue_argmax(self.h, stream, d_weight.ptr, weight_dtype, vocab, hidden, d_x.ptr,
                                                 n_rows, index_offset, d_index_out.ptr,
                                                 d_value_out.ptr if d_value_out is not None else None))
+
+    def encode_embedding_from_index(self, d_table, table_dtype, vocab, hidden, d_index, d_out, embedding_scale=1.0,
+                                    recast_bf16=False, stream=None):
+        """encode_embedding_from_index_buffers_scaled (src/metal_backend/matmul_encode.rs:424-444): the next
+        token's input row, looked up by an index on the device. d_index: a DeviceBuffer or a raw device address."""
+        index = d_index.ptr if hasattr(d_index, "ptr") else d_index
+        check(self.L.sgk_embed_enqueue_from_index(self.h, stream, d_table.ptr, table_dtype, vocab, hidden, index,
+                                                  embedding_scale, int(recast_bf16), d_out.ptr))
+
+    def token_window(self, depth=4) -> "TokenWindow":
+        return TokenWindow(self, depth)
 
     def argmax_linear_biasless(self, x, weight):
         """argmax_linear_biasless (src/metal_backend/lm_head.rs:150-182): host x [hidden] or [rows][hidden]

@@ -168,3 +168,135 @@ def test_kernel_rejects_bad_shapes(gpu_state):
                                             n_rows=kw.get("n_rows", 1))
     with pytest.raises(sg.InferError):
         gpu_state.encode_lm_head_argmax(d, sg.KV_U8G32, 4, 8, d, d)
+
+
+# ---- token feed: embedding lookup by a device index, and the submission window -------------------
+def test_oracle_embed_gather_known_answers():
+    # embedding_gather_from_index_applies_gemma_scale (src/metal_backend/tests/buffers_core.rs:64-89)
+    table = np.array([[1.0, -2.0, 3.0, -4.0], [0.5, 1.5, -2.5, 4.5]], np.float32)
+    assert sgo.embed_gather(table, 1, 3.0).tolist() == [1.5, 4.5, -7.5, 13.5]
+    # embedding_gather_recast_is_opt_in_and_bf16_exact (:91-133)
+    row = np.array([[1.001, -2.003, 3.007, -4.015]], np.float32)
+    assert sgo.embed_gather(row, 0).tobytes() == row[0].tobytes()
+    assert sgo.embed_gather(row, 0, 1.0, True).tobytes() == _widen(_bf16_bits(row[0])).tobytes()
+    assert sgo.embed_gather(row, 1) is None   # outside the table: nothing written
+
+
+@pytest.mark.gpu
+def test_embedding_from_device_index_matches_oracle(gpu_state):
+    import saragossa_b200 as sg
+    table = np.array([[1.0, -2.0, 3.0, -4.0], [0.5, 1.5, -2.5, 4.5]], np.float32)
+    d_t, d_i, d_o = gpu_state.upload(table), gpu_state.upload(np.array([1], np.int32)), gpu_state.alloc(16)
+    gpu_state.encode_embedding_from_index(d_t, sg.KV_F32, 2, 4, d_i, d_o, embedding_scale=3.0)
+    gpu_state.sync()
+    assert d_o.download(np.float32, 4).tolist() == [1.5, 4.5, -7.5, 13.5]
+    row = np.array([[1.001, -2.003, 3.007, -4.015]], np.float32)
+    d_r, d_z = gpu_state.upload(row), gpu_state.upload(np.array([0], np.int32))
+    for recast in (False, True):
+        gpu_state.encode_embedding_from_index(d_r, sg.KV_F32, 1, 4, d_z, d_o, recast_bf16=recast)
+        gpu_state.sync()
+        assert d_o.download(np.float32, 4).tobytes() == sgo.embed_gather(row, 0, 1.0, recast).tobytes()
+    # an index outside the table writes nothing (and does not fault)
+    before = d_o.download(np.float32, 4).copy()
+    for bad in (1, -1, 2**31 - 1):
+        d_b = gpu_state.upload(np.array([bad], np.int32))
+        gpu_state.encode_embedding_from_index(d_r, sg.KV_F32, 1, 4, d_b, d_o)
+        gpu_state.sync()
+        assert d_o.download(np.float32, 4).tobytes() == before.tobytes()
+    # bf16 table, larger row
+    rng = np.random.default_rng(3)
+    big = rng.standard_normal((50, 1000)).astype(np.float32)
+    bits = _bf16_bits(big)
+    d_bt, d_bo = gpu_state.upload(bits), gpu_state.alloc(4000)
+    d_bi = gpu_state.upload(np.array([37], np.int32))
+    gpu_state.encode_embedding_from_index(d_bt, sg.KV_BF16, 50, 1000, d_bi, d_bo, embedding_scale=0.25)
+    gpu_state.sync()
+    assert d_bo.download(np.float32, 1000).tobytes() == sgo.embed_gather(_widen(bits), 37, 0.25).tobytes()
+
+
+def _toy_model(seed, vocab=600, hidden=64):
+    """A closed token loop: next = argmax(W . (E[token] * scale)). W's rows are planted so that the chain
+    is a fixed permutation with wide margins."""
+    rng = np.random.default_rng(seed)
+    emb = rng.standard_normal((vocab, hidden)).astype(np.float32)
+    perm = rng.permutation(vocab)
+    w = (rng.standard_normal((vocab, hidden)) * 0.02).astype(np.float32)
+    for tok in range(vocab):
+        w[perm[tok]] += emb[tok] / np.linalg.norm(emb[tok]) * 3.0
+    return emb, w, perm
+
+
+def _oracle_chain(emb, w, first, n, scale):
+    out, tok = [], first
+    for _ in range(n):
+        st, tok, _ = sgo.lm_head_argmax(w, sgo.embed_gather(emb, tok, scale))
+        assert st == 0
+        out.append(tok)
+    return out
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("depth", [1, 4])
+def test_token_window_keeps_the_token_on_the_device(gpu_state, depth):
+    """The decode loop of src/decoder/resident/decode.rs:114-173 on a toy model: up to `depth` tokens are
+    enqueued before the oldest is read back; token n+1 reads token n's index from the device ring."""
+    import saragossa_b200 as sg
+    emb, w, perm = _toy_model(21)
+    vocab, hidden = emb.shape
+    first, n, scale = 5, 23, 1.5
+    want = _oracle_chain(emb, w, first, n, scale)
+    assert len(set(want)) > 10   # the chain really moves
+    d_e, d_w = gpu_state.upload(emb), gpu_state.upload(w)
+    d_x = gpu_state.alloc(4 * hidden)
+    d_first = gpu_state.upload(np.array([first], np.int32))
+    win = gpu_state.token_window(depth)
+    assert win.depth == depth and win.previous_slot() is None
+    got, enq = [], 0
+    while len(got) < n:
+        while enq < n and win.inflight < depth:
+            src = win.previous_slot() or d_first
+            gpu_state.encode_embedding_from_index(d_e, sg.KV_F32, vocab, hidden, src, d_x, embedding_scale=scale)
+            gpu_state.encode_lm_head_argmax(d_w, sg.KV_F32, vocab, hidden, d_x, win.output_slot())
+            win.submit()
+            enq += 1
+        got.append(win.pop())
+    assert got == want
+    assert win.inflight == 0 and win.enqueued == n
+    with pytest.raises(sg.InferError):
+        win.pop()   # nothing in flight
+    win.close()
+
+
+@pytest.mark.gpu
+def test_token_window_full_and_stop_token_drain(gpu_state):
+    import saragossa_b200 as sg
+    emb, w, perm = _toy_model(22)
+    vocab, hidden = emb.shape
+    want = _oracle_chain(emb, w, 9, 12, 1.0)
+    stop = want[5]
+    d_e, d_w, d_x = gpu_state.upload(emb), gpu_state.upload(w), gpu_state.alloc(4 * hidden)
+    d_first = gpu_state.upload(np.array([9], np.int32))
+    win = gpu_state.token_window(4)
+    got, enq, stopped = [], 0, False
+    while not stopped:
+        while enq < 12 and win.inflight < win.depth:
+            src = win.previous_slot() or d_first
+            gpu_state.encode_embedding_from_index(d_e, sg.KV_F32, vocab, hidden, src, d_x)
+            gpu_state.encode_lm_head_argmax(d_w, sg.KV_F32, vocab, hidden, d_x, win.output_slot())
+            win.submit()
+            enq += 1
+        assert win.inflight == 4 and win.output_slot() is None   # full: no slot to write
+        with pytest.raises(sg.InferError) as err:
+            win.submit()
+        assert err.value.kind == "Dimension"
+        tok = win.pop()
+        if tok == stop:
+            stopped = True
+        else:
+            got.append(tok)
+    assert got == want[:5]
+    assert win.inflight == 3   # tokens enqueued past the stop token are still running
+    win.drain()
+    assert win.inflight == 0
+    assert gpu_state.device_status() == 0
+    win.close()
