@@ -48,6 +48,8 @@ struct AttnArgs {
   int64_t window_start;     // explicit start row when sliding_window == 0
   int64_t sliding_window;   // > 0: start = max(len - window, 0)
   int32_t shared_merge;     // 1: every block of a (sequence, KV head) merges a slice once all have arrived
+  int32_t cluster_merge;    // 1: the splits of a (sequence, KV head) are one thread-block cluster and merge through
+                            //    distributed shared memory (2..8 splits)
   int32_t pages_per_split;  // > 0: a sequence is cut into ceil(pages / this) splits (<= splits), blocks beyond exit
   float scale_log2e;        // log2(e) / sqrt(attn_scalar)
   int32_t splits;
@@ -87,12 +89,14 @@ cudaError_t launch_wait_timeout_selftest(int32_t* status, cudaStream_t stream);
 int attention_mma_max_stages(int head_dim);
 // Blocks of the kernel one SM holds at once with `n_stages` stages (0 when the query fails).
 int attention_mma_resident_blocks(int head_dim, int n_stages);
+int attention_mma_max_clusters(int head_dim, int n_stages, int splits);
 // Tensor-core paged kernel for u8 group-32 pages: head_dim 128 or 256, q_heads/kv_heads <= 8.
 bool attention_u8_supported(int dtype, int head_dim, int gqa);
 cudaError_t launch_attention_u8(const AttnArgs& a, int n_seq, cudaStream_t stream);
 cudaError_t attention_u8_configure();
 int attention_u8_max_stages(int head_dim);
 int attention_u8_resident_blocks(int head_dim, int n_stages);
+int attention_u8_max_clusters(int head_dim, int n_stages, int splits);
 
 // Gather rows [row0, row0+n) of one layer into contiguous [n, kv_dim] arrays.
 // mode 0: storage type (f32 / bf16 bits), 1: decoded f32, 2: u8 codes + scale + bias.

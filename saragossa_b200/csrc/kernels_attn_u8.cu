@@ -301,34 +301,8 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
 
   if (warp == MMA_CONSUMERS) {
     // ---------------- producer warp ----------------
-    int stage = 0;
-    uint32_t parity = 1;
-    for (int base = 0; base < my_pages; base += 32) {
-      int idx = base + lane;
-      int32_t entry = base == 0 ? first_entry : (idx < my_pages ? table[pb + idx] : -1);
-      int cnt = min(32, my_pages - base);
-      for (int j = 0; j < cnt; ++j) {
-        int32_t page = __shfl_sync(0xffffffffu, entry, j);
-        if (lane == 0) {
-          bool ok = mbar_wait(smem_u32(bars + MMA_MAX_STAGES + stage), parity, abort_flag, a.status);
-          if (ok && (page < 0 || page >= a.num_pages)) {
-            atomicExch(a.status, DEV_ERR_BAD_PAGE);
-            *abort_flag = 1;
-            ok = false;
-          }
-          if (ok) {
-            uint32_t full = smem_u32(bars + stage);
-            mbar_expect_tx(full, S::STAGE);
-            bulk_copy_g2s(smem_u32(ring + size_t(stage) * S::STAGE),
-                          a.pool.base + int64_t(page) * a.pool.page_bytes + head_off, S::STAGE, full);
-          }
-        }
-        if (++stage == nst) {
-          stage = 0;
-          parity ^= 1;
-        }
-      }
-    }
+    produce_pages<S::STAGE>(a, table, pb, my_pages, first_entry, ring, bars, nst, head_off, abort_flag, lane);
+    SGK_TP(12);
   } else {
     // ---------------- consumer warps ----------------
     const int g = lane >> 2, t = lane & 3;
@@ -617,7 +591,8 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
     }
   }
   __syncthreads();
-  finish_block<HD>(a, o_s, ml_s, S::OPAD, flags, seq, kvh, split, gqa, do_append, len_ptr, len, tid, splits);
+  finish_block<HD>(a, o_s, ml_s, S::OPAD, flags, seq, kvh, split, gqa, do_append, len_ptr, len, tid, splits,
+                   reinterpret_cast<float*>(q_hi));
 }
 
 bool attention_u8_supported(int dtype, int head_dim, int gqa) {
@@ -643,6 +618,29 @@ int attention_u8_resident_blocks(int head_dim, int n_stages) {
   return e == cudaSuccess ? blocks : 0;
 }
 
+// How many clusters of `splits` blocks the device can hold at once (0: such a launch would fail).
+int attention_u8_max_clusters(int head_dim, int n_stages, int splits) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(splits, 1, 1);
+  cfg.blockDim = dim3(MMA_THREADS);
+  cfg.dynamicSmemBytes = head_dim == 128 ? U8Smem<128>::total(n_stages) : U8Smem<256>::total(n_stages);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = splits;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  cudaError_t e = head_dim == 128 ? cudaOccupancyMaxActiveClusters(&n, attention_u8_kernel<128>, &cfg)
+                                  : cudaOccupancyMaxActiveClusters(&n, attention_u8_kernel<256>, &cfg);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
 cudaError_t attention_u8_configure() {
   cudaError_t e = cudaFuncSetAttribute(attention_u8_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        227 * 1024);
@@ -651,7 +649,8 @@ cudaError_t attention_u8_configure() {
 }
 
 // A launch whose blocks wait for one another (shared merge) is a cooperative launch: the driver
-// then places all its blocks at once or not at all, also next to launches of other streams.
+// then places all its blocks at once or not at all, also next to launches of other streams. A
+// launch whose splits merge through distributed shared memory is a cluster launch.
 static cudaError_t launch_one(void (*kernel)(AttnArgs), dim3 grid, size_t smem, const AttnArgs& a,
                               cudaStream_t stream) {
   cudaLaunchConfig_t cfg{};
@@ -660,10 +659,18 @@ static cudaError_t launch_one(void (*kernel)(AttnArgs), dim3 grid, size_t smem, 
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeCooperative;
-  attr[0].val.cooperative = 1;
+  if (a.cluster_merge) {
+    // the splits of a (sequence, KV head) are the x extent of the grid and of the cluster
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = grid.x;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+  } else {
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = a.shared_merge ? 1 : 0;
+  cfg.numAttrs = (a.shared_merge || a.cluster_merge) ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, a);
 }
 

@@ -60,6 +60,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   uint32_t limit = *abort_flag ? WAIT_SPINS_ABORTED : WAIT_SPINS;
   for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+#ifdef SGK_WAIT_SLEEP
+    __nanosleep(SGK_WAIT_SLEEP);
+#endif
   }
   *abort_flag = 1;
   atomicExch(status, DEV_ERR_WAIT_TIMEOUT);
@@ -71,6 +74,61 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
       "l"(src), "r"(bytes), "r"(bar)
       : "memory");
 }
+// The producer warp's walk over the block's pages [pb, pb + my_pages): one bulk copy of
+// STAGE_BYTES per page into stage (page index % nst), completion on the stage's "full" barrier
+// (bars[stage]); a stage is refilled once its "empty" barrier (bars[MMA_MAX_STAGES + stage]) has
+// completed. The first min(my_pages, nst) copies find fresh stages and wait for nothing: lane j
+// starts page j, so one pass of the warp puts them all in flight (issued one after the other by
+// one lane, each costs that lane a round trip to its barrier first). first_entry: lane l holds
+// table[pb + l] for l < my_pages.
+template <int STAGE_BYTES>
+__device__ __forceinline__ void produce_pages(const AttnArgs& a, const int32_t* table, int64_t pb, int my_pages,
+                                              int32_t first_entry, uint8_t* ring, uint64_t* bars, int nst,
+                                              int64_t head_off, volatile int* abort_flag, int lane) {
+  const int first = my_pages < nst ? my_pages : nst;
+  if (lane < first) {
+    if (first_entry < 0 || first_entry >= a.num_pages) {
+      atomicExch(a.status, DEV_ERR_BAD_PAGE);
+      *abort_flag = 1;
+    } else {
+      const uint32_t full = smem_u32(bars + lane);
+      mbar_expect_tx(full, STAGE_BYTES);
+      bulk_copy_g2s(smem_u32(ring + size_t(lane) * STAGE_BYTES),
+                    a.pool.base + int64_t(first_entry) * a.pool.page_bytes + head_off, STAGE_BYTES, full);
+    }
+  }
+  __syncwarp();
+  if (my_pages <= nst) return;
+  int stage = 0;          // page i uses stage i % nst, in phase i / nst: kept as running counters
+  uint32_t parity = 0;    // second use of a stage: wait for the consumers' first release
+  for (int base = 0; base < my_pages; base += 32) {
+    const int idx = base + lane;
+    const int32_t entry = base == 0 ? first_entry : (idx < my_pages ? table[pb + idx] : -1);
+    const int cnt = min(32, my_pages - base);
+    for (int j = base == 0 ? nst : 0; j < cnt; ++j) {
+      const int32_t page = __shfl_sync(0xffffffffu, entry, j);
+      if (lane == 0) {
+        bool ok = mbar_wait(smem_u32(bars + MMA_MAX_STAGES + stage), parity, abort_flag, a.status);
+        if (ok && (page < 0 || page >= a.num_pages)) {
+          atomicExch(a.status, DEV_ERR_BAD_PAGE);
+          *abort_flag = 1;
+          ok = false;
+        }
+        if (ok) {
+          const uint32_t full = smem_u32(bars + stage);
+          mbar_expect_tx(full, STAGE_BYTES);
+          bulk_copy_g2s(smem_u32(ring + size_t(stage) * STAGE_BYTES),
+                        a.pool.base + int64_t(page) * a.pool.page_bytes + head_off, STAGE_BYTES, full);
+        }
+      }
+      if (++stage == nst) {
+        stage = 0;
+        parity ^= 1;
+      }
+    }
+  }
+}
+
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
@@ -210,6 +268,101 @@ __device__ __forceinline__ bool shared_merge(const AttnArgs& a, int splits, int 
   return ok;
 }
 
+// ---- thread-block cluster: the splits of one (sequence, KV head) as one cluster ------------
+constexpr int CLUSTER_MERGE_MAX_SPLITS = 8;  // the portable cluster size
+__device__ __forceinline__ uint32_t cluster_map_shared(const void* p, uint32_t cta_rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(p)), "r"(cta_rank));
+  return remote;
+}
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float2 ld_cluster_f2(uint32_t addr) {
+  float2 v;
+  asm volatile("ld.shared::cluster.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+  return v;
+}
+// Hardware barrier over all threads of the cluster (like bar.sync over a block: no spinning on
+// memory; threads that have exited count as arrived).
+__device__ __forceinline__ void cluster_arrive_release() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait_acquire() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The same barrier without memory ordering: only "everybody got here".
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait_plain() { asm volatile("barrier.cluster.wait.aligned;" ::: "memory"); }
+
+// Merge of the splits of one (sequence, KV head) when they run as one thread-block cluster
+// (grid x = cluster x = splits, so the rank in the cluster is the split): every block leaves its
+// un-normalised output [8][HD] and {max, sum} [8] in its own shared memory, the cluster meets at
+// a barrier, and each block then produces a slice of the final output from all blocks' shared
+// memory (distributed shared memory loads): no partial travels through L2, no device-wide
+// atomic is on the path. Same arithmetic, in the same order, as merge_block. Every thread of
+// the block must call this.
+template <int HD, int NT>
+__device__ __forceinline__ void cluster_merge(const AttnArgs& a, const float* comb_s, const float* hml_s, int splits,
+                                              int split, int gqa, int64_t qh0, int tid, int32_t* seq_counter,
+                                              int seq_blocks, int32_t* len_ptr, int64_t len) {
+  cluster_arrive_release();
+  cluster_wait_acquire();
+  if (tid == 0) SGK_TP(5);
+  // After a fused append the block that arrives last for the sequence moves the cursor. The
+  // arrival's round trip runs beside the merge: issued here by a thread that has little else
+  // to do, its result is looked at after the merge.
+  int arrived = -1;
+  if (seq_counter != nullptr && tid == NT - 1) arrived = arrive_acq_rel(seq_counter);
+  const int total = gqa * (HD / 4);
+  // cell = split + splits * i: block `split` owns every splits-th cell of four dims
+  for (int i = tid; split + splits * i < total; i += NT) {
+    const int cell = split + splits * i;
+    const int h = cell / (HD / 4), d = (cell % (HD / 4)) * 4;
+    float2 ml[CLUSTER_MERGE_MAX_SPLITS];
+    float4 v[CLUSTER_MERGE_MAX_SPLITS];
+#pragma unroll
+    for (int p = 0; p < CLUSTER_MERGE_MAX_SPLITS; ++p)
+      if (p < splits) {
+        ml[p] = ld_cluster_f2(cluster_map_shared(hml_s + 2 * h, p));
+        v[p] = ld_cluster_f4(cluster_map_shared(comb_s + h * HD + d, p));
+      }
+    float m = -1.0e30f;
+#pragma unroll
+    for (int p = 0; p < CLUSTER_MERGE_MAX_SPLITS; ++p)
+      if (p < splits) m = fmaxf(m, ml[p].x);
+    float l = 0.0f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int p = 0; p < CLUSTER_MERGE_MAX_SPLITS; ++p)
+      if (p < splits) {
+        const float w = exp2f(ml[p].x - m);
+        l += ml[p].y * w;
+        acc.x += v[p].x * w;
+        acc.y += v[p].y * w;
+        acc.z += v[p].z * w;
+        acc.w += v[p].w * w;
+      }
+    const float inv = 1.0f / l;
+    *reinterpret_cast<float4*>(a.out + (qh0 + h) * HD + d) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+  }
+  if (arrived == seq_blocks - 1) {
+    *len_ptr = static_cast<int32_t>(len);
+    *seq_counter = 0;
+  }
+  if (tid == 0) SGK_TP(7);
+  // nobody leaves (and frees its shared memory) before every block has read what it needs;
+  // nothing written since the first barrier is read inside the cluster, so no ordering is asked for
+  cluster_arrive_relaxed();
+  cluster_wait_plain();
+}
+
 // Block-cooperative merge of `count` (<= MERGE_MAX) partials (rows first..first+count
 // of a [q head][stride][HD] array) for the gqa heads starting at qh0. A thread owns
 // cells of four dims; per pass it handles two cells and issues every load it needs
@@ -280,7 +433,9 @@ __device__ __forceinline__ void merge_block(const Partials& src, int stride, int
 template <int HD, int NT = MMA_THREADS>
 __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s, const float* ml_s, int opad,
                                              int* flags, int seq, int kvh, int split, int gqa, bool do_append,
-                                             int32_t* len_ptr, int64_t len, int tid, int splits) {
+                                             int32_t* len_ptr, int64_t len, int tid, int splits, float* comb_s) {
+  // comb_s: [8][HD] floats of shared memory that nobody reads any more (the staged Q), for the
+  // block's combined output when the splits merge as a cluster
   // `splits` is this sequence's own split count (<= a.splits, the stride of the partial arrays)
   const int n_groups = (splits + a.group_size - 1) / a.group_size;
   if (tid == 0) SGK_TP(4);
@@ -320,6 +475,8 @@ __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s
     if (splits == 1) {
       const float inv = 1.0f / hml_s[2 * h + 1];
       *reinterpret_cast<float4*>(a.out + (qh0 + h) * HD + d) = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
+    } else if (a.cluster_merge) {
+      *reinterpret_cast<float4*>(comb_s + h * HD + d) = o;
     } else {
       *reinterpret_cast<float4*>(a.part.o + ((qh0 + h) * a.splits + split) * HD + d) = o;
       if (d == 0)
@@ -333,6 +490,12 @@ __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s
     const int group_count = min(a.group_size, splits - group_first);
     int32_t* group_counter = a.group_counters + (int64_t(seq) * a.pool.kv_heads + kvh) * a.max_groups + group;
     int32_t* head_counter = a.head_counters + int64_t(seq) * a.pool.kv_heads + kvh;
+    if (a.cluster_merge && splits > 1) {
+      cluster_merge<HD, NT>(a, comb_s, hml_s, splits, split, gqa, qh0, tid, do_append ? a.seq_counters + seq : nullptr,
+                            splits * a.pool.kv_heads, len_ptr, len);
+      if (tid == 0) SGK_TP(6);
+      return;
+    }
     __syncthreads();
     if (a.shared_merge && splits > 1 && splits <= SHARED_MERGE_MAX_SPLITS) {
       if (tid == 32 && do_append) {
