@@ -50,7 +50,8 @@ struct MmaSmem {
   static constexpr int ML_BYTES = 512;  // per-warp {max, sum}, then the merge weights and the block's {max, sum}
   static constexpr int BAR_BYTES = 2 * MMA_MAX_STAGES * 8;
   static constexpr int NEW_BYTES = 2 * HD * 2;       // the K and V row of a fused append, bf16
-  static constexpr int FIXED = Q_BYTES + ML_BYTES + BAR_BYTES + 64 + NEW_BYTES;
+  static constexpr int RECV_BYTES = ClusterRecv<HD>::BYTES;  // what the other blocks of a cluster send for the merge
+  static constexpr int FIXED = Q_BYTES + ML_BYTES + BAR_BYTES + 64 + NEW_BYTES + RECV_BYTES;
   __host__ __device__ static size_t ring_bytes(int stages) {
     size_t r = size_t(stages) * STAGE;
     return r > size_t(O_BYTES) ? r : size_t(O_BYTES);
@@ -73,8 +74,9 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
   float* o_s = reinterpret_cast<float*>(ring);                  // [warps][8][OPAD], used after the ring drained
   float* ml_s = reinterpret_cast<float*>(fixed + S::Q_BYTES);   // [warps][8][2]
   uint64_t* bars = reinterpret_cast<uint64_t*>(fixed + S::Q_BYTES + S::ML_BYTES);
-  int* flags = reinterpret_cast<int*>(bars + 2 * MMA_MAX_STAGES);  // [0]=abort [1]=last arriver [2]=append page
+  int* flags = reinterpret_cast<int*>(bars + 2 * MMA_MAX_STAGES);  // [0]=abort [1]=last arriver
   uint32_t* new_s = reinterpret_cast<uint32_t*>(flags + 16);       // bf16 pairs of the appended [K row | V row]
+  float* recv_s = reinterpret_cast<float*>(fixed + S::FIXED - S::RECV_BYTES);
   volatile int* abort_flag = flags;
 
   const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
@@ -150,13 +152,24 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
     if (owns_append) {
       if (tid * 4 < 2 * HD) {
         const int64_t row_off = int64_t(seq) * a.pool.kv_heads * HD + kvh * HD;
-        const float* src = tid * 4 < HD ? a.k_new + row_off + tid * 4 : a.v_new + row_off + (tid * 4 - HD);
+        const bool is_k = tid * 4 < HD;
+        const int dim = is_k ? tid * 4 : tid * 4 - HD;
+        const float* src = is_k ? a.k_new + row_off + dim : a.v_new + row_off + dim;
+        const int32_t page = table[append_page_index];   // issued with the row's load: one round trip for both
         const float4 x = __ldg(reinterpret_cast<const float4*>(src));
-        *reinterpret_cast<uint2*>(new_s + tid * 2) =
-            make_uint2(uint32_t(f32_to_bf16_bits(x.x)) | (uint32_t(f32_to_bf16_bits(x.y)) << 16),
-                       uint32_t(f32_to_bf16_bits(x.z)) | (uint32_t(f32_to_bf16_bits(x.w)) << 16));
+        const uint2 packed = make_uint2(uint32_t(f32_to_bf16_bits(x.x)) | (uint32_t(f32_to_bf16_bits(x.y)) << 16),
+                                        uint32_t(f32_to_bf16_bits(x.z)) | (uint32_t(f32_to_bf16_bits(x.w)) << 16));
+        *reinterpret_cast<uint2*>(new_s + tid * 2) = packed;
+        // The row goes to its page in global memory now: whatever the bulk copy of that page sees of
+        // it, the staged copy gets the row again from shared memory; and a store issued here has long
+        // been performed when the block's tail asks for its writes to be visible. A page id outside the
+        // pool is reported by the producer, which meets the same table entry.
+        if (page >= 0 && page < a.num_pages) {
+          const int rin = static_cast<int>(len_old % PAGE_TOKENS);
+          uint8_t* tile = a.pool.base + int64_t(page) * a.pool.page_bytes + head_off + (is_k ? 0 : S::TILE);
+          *reinterpret_cast<uint2*>(tile + bf16_elem_index(rin, dim, HD) * 2) = packed;
+        }
       }
-      if (tid == 0) flags[2] = table[append_page_index];
     }
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
@@ -223,21 +236,12 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
       const int64_t row_base = page_index * PAGE_TOKENS;
 
       if (ok && owns_append && page_index == append_page_index) {
-        // The new row (converted in the prologue) goes to its page and into the staged copy.
+        // The new row (converted in the prologue, already on its way to the page) joins the staged copy.
         const int rin = static_cast<int>(len_old % PAGE_TOKENS);
-        const int32_t page = flags[2];
-        if (page >= 0 && page < a.num_pages) {
-          uint8_t* gk = a.pool.base + int64_t(page) * a.pool.page_bytes + head_off;
-          uint8_t* gv = gk + S::TILE;
-          for (int chunk = lane; chunk < HD / 8; chunk += 32) {
-            int off = bf16_elem_index(rin, chunk * 8, HD) * 2;
-            const uint4 pk = *reinterpret_cast<const uint4*>(new_s + chunk * 4);
-            const uint4 pv = *reinterpret_cast<const uint4*>(new_s + HD / 2 + chunk * 4);
-            *reinterpret_cast<uint4*>(gk + off) = pk;
-            *reinterpret_cast<uint4*>(gv + off) = pv;
-            *reinterpret_cast<uint4*>(ktile + off) = pk;
-            *reinterpret_cast<uint4*>(vtile + off) = pv;
-          }
+        for (int chunk = lane; chunk < HD / 8; chunk += 32) {
+          const int off = bf16_elem_index(rin, chunk * 8, HD) * 2;
+          *reinterpret_cast<uint4*>(ktile + off) = *reinterpret_cast<const uint4*>(new_s + chunk * 4);
+          *reinterpret_cast<uint4*>(vtile + off) = *reinterpret_cast<const uint4*>(new_s + HD / 2 + chunk * 4);
         }
         __syncwarp();
       }
@@ -391,7 +395,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
   __syncthreads();
 
   finish_block<HD>(a, o_s, ml_s, S::OPAD, flags, seq, kvh, split, gqa, do_append, len_ptr, len, tid, splits,
-                   reinterpret_cast<float*>(q_hi));
+                   recv_s);
 }
 
 // Exercises the bounded wait on purpose: one warp waits on an mbarrier that nobody completes.

@@ -89,7 +89,8 @@ struct U8Smem {
   static constexpr int ML_BYTES = 512;  // per-warp {max, sum}, then the merge weights and the block's {max, sum}
   static constexpr int BAR_BYTES = 2 * MMA_MAX_STAGES * 8;
   static constexpr int NEW_BYTES = 2 * HD * 4;            // the K and V row of a fused append, f32
-  static constexpr int FIXED = Q_BYTES + QSUM_BYTES + ML_BYTES + BAR_BYTES + 64 + NEW_BYTES;
+  static constexpr int RECV_BYTES = ClusterRecv<HD>::BYTES;  // what the other blocks of a cluster send for the merge
+  static constexpr int FIXED = Q_BYTES + QSUM_BYTES + ML_BYTES + BAR_BYTES + 64 + NEW_BYTES + RECV_BYTES;
   __host__ __device__ static size_t ring_bytes(int stages) {
     size_t r = size_t(stages) * STAGE;
     return r > size_t(O_BYTES) ? r : size_t(O_BYTES);
@@ -154,6 +155,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
   int* flags = reinterpret_cast<int*>(bars + 2 * MMA_MAX_STAGES);
   float* new_s = reinterpret_cast<float*>(flags + 16);   // [K row | V row] of the append, staged once
   float* new_big = reinterpret_cast<float*>(flags + 8);  // [consumer warp] max |x| of its part of that row
+  float* recv_s = reinterpret_cast<float*>(fixed + S::FIXED - S::RECV_BYTES);
   volatile int* abort_flag = flags;
 
   const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
@@ -592,7 +594,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
   }
   __syncthreads();
   finish_block<HD>(a, o_s, ml_s, S::OPAD, flags, seq, kvh, split, gqa, do_append, len_ptr, len, tid, splits,
-                   reinterpret_cast<float*>(q_hi));
+                   recv_s);
 }
 
 bool attention_u8_supported(int dtype, int head_dim, int gqa) {

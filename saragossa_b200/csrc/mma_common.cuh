@@ -60,9 +60,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   uint32_t limit = *abort_flag ? WAIT_SPINS_ABORTED : WAIT_SPINS;
   for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-#ifdef SGK_WAIT_SLEEP
-    __nanosleep(SGK_WAIT_SLEEP);
-#endif
   }
   *abort_flag = 1;
   atomicExch(status, DEV_ERR_WAIT_TIMEOUT);
@@ -275,18 +272,6 @@ __device__ __forceinline__ uint32_t cluster_map_shared(const void* p, uint32_t c
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(p)), "r"(cta_rank));
   return remote;
 }
-__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
-  float4 v;
-  asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ float2 ld_cluster_f2(uint32_t addr) {
-  float2 v;
-  asm volatile("ld.shared::cluster.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
-  return v;
-}
 // Hardware barrier over all threads of the cluster (like bar.sync over a block: no spinning on
 // memory; threads that have exited count as arrived).
 __device__ __forceinline__ void cluster_arrive_release() {
@@ -295,59 +280,83 @@ __device__ __forceinline__ void cluster_arrive_release() {
 __device__ __forceinline__ void cluster_wait_acquire() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// The same barrier without memory ordering: only "everybody got here".
-__device__ __forceinline__ void cluster_arrive_relaxed() {
-  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void cluster_wait_plain() { asm volatile("barrier.cluster.wait.aligned;" ::: "memory"); }
 
 // Merge of the splits of one (sequence, KV head) when they run as one thread-block cluster
-// (grid x = cluster x = splits, so the rank in the cluster is the split): every block leaves its
-// un-normalised output [8][HD] and {max, sum} [8] in its own shared memory, the cluster meets at
-// a barrier, and each block then produces a slice of the final output from all blocks' shared
-// memory (distributed shared memory loads): no partial travels through L2, no device-wide
-// atomic is on the path. Same arithmetic, in the same order, as merge_block. Every thread of
-// the block must call this.
+// (grid x = cluster x = splits, so the rank in the cluster is the split). Cell c (four dims of
+// one head) of the output belongs to block c % splits. Every block SENDS each cell of its
+// un-normalised output, and its {max, sum} pairs, into the owner's shared memory (distributed
+// shared memory stores into a buffer that nothing else uses, so a block that is still streaming
+// is not disturbed); the cluster meets at one barrier; every block then merges the cells it owns
+// from its own shared memory and writes them out. No partial travels through L2, no device-wide
+// atomic is on the path, and after the barrier nobody touches anybody else's memory, so a block
+// may leave as soon as it is done. Same arithmetic, in the same order, as merge_block.
+//   recv layout: float4 o[splits][cells_per_block] then float2 ml[CLUSTER_MERGE_MAX_SPLITS][8]
+template <int HD>
+struct ClusterRecv {
+  static constexpr int MAX_CELLS = 8 * (HD / 4);                         // gqa <= 8
+  static constexpr int O_FLOATS = (MAX_CELLS + CLUSTER_MERGE_MAX_SPLITS) * 4;   // sum over sources of ceil(cells / splits)
+  static constexpr int BYTES = O_FLOATS * 4 + CLUSTER_MERGE_MAX_SPLITS * 8 * 8;
+};
+__device__ __forceinline__ void st_cluster_f4(uint32_t addr, float4 v) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ void st_cluster_f2(uint32_t addr, float2 v) {
+  asm volatile("st.shared::cluster.v2.f32 [%0], {%1,%2};" ::"r"(addr), "f"(v.x), "f"(v.y) : "memory");
+}
+// Sends cell `cell` of this block's output to its owner.
+template <int HD>
+__device__ __forceinline__ void cluster_send_cell(float* recv, int splits, int split, int gqa, int cell, float4 o) {
+  const int cells_per_block = (gqa * (HD / 4) + splits - 1) / splits;
+  const int owner = cell % splits, slot = cell / splits;
+  st_cluster_f4(cluster_map_shared(recv + (split * cells_per_block + slot) * 4, owner), o);
+}
+// Sends this block's {max, sum} of every head to every block. Threads [0, gqa * splits).
+template <int HD>
+__device__ __forceinline__ void cluster_send_ml(float* recv, const float* hml_s, int splits, int split, int gqa,
+                                                int tid) {
+  if (tid < gqa * splits) {
+    const int owner = tid / gqa, h = tid % gqa;
+    float* dst = recv + ClusterRecv<HD>::O_FLOATS + (split * 8 + h) * 2;
+    st_cluster_f2(cluster_map_shared(dst, owner), make_float2(hml_s[2 * h], hml_s[2 * h + 1]));
+  }
+}
+// Every thread of the block must call this, after its sends.
 template <int HD, int NT>
-__device__ __forceinline__ void cluster_merge(const AttnArgs& a, const float* comb_s, const float* hml_s, int splits,
-                                              int split, int gqa, int64_t qh0, int tid, int32_t* seq_counter,
-                                              int seq_blocks, int32_t* len_ptr, int64_t len) {
+__device__ __forceinline__ void cluster_merge(const AttnArgs& a, const float* recv, int splits, int split, int gqa,
+                                              int64_t qh0, int tid, int32_t* seq_counter, int seq_blocks,
+                                              int32_t* len_ptr, int64_t len) {
   cluster_arrive_release();
-  cluster_wait_acquire();
-  if (tid == 0) SGK_TP(5);
   // After a fused append the block that arrives last for the sequence moves the cursor. The
-  // arrival's round trip runs beside the merge: issued here by a thread that has little else
-  // to do, its result is looked at after the merge.
+  // arrival's round trip runs beside the barrier and the merge: issued here by a thread that
+  // has little else to do, its result is looked at after the merge.
   int arrived = -1;
   if (seq_counter != nullptr && tid == NT - 1) arrived = arrive_acq_rel(seq_counter);
+  cluster_wait_acquire();
+  if (tid == 0) SGK_TP(5);
   const int total = gqa * (HD / 4);
-  // cell = split + splits * i: block `split` owns every splits-th cell of four dims
+  const int cells_per_block = (total + splits - 1) / splits;
+  const float* recv_ml = recv + ClusterRecv<HD>::O_FLOATS;
   for (int i = tid; split + splits * i < total; i += NT) {
     const int cell = split + splits * i;
     const int h = cell / (HD / 4), d = (cell % (HD / 4)) * 4;
-    float2 ml[CLUSTER_MERGE_MAX_SPLITS];
-    float4 v[CLUSTER_MERGE_MAX_SPLITS];
-#pragma unroll
-    for (int p = 0; p < CLUSTER_MERGE_MAX_SPLITS; ++p)
-      if (p < splits) {
-        ml[p] = ld_cluster_f2(cluster_map_shared(hml_s + 2 * h, p));
-        v[p] = ld_cluster_f4(cluster_map_shared(comb_s + h * HD + d, p));
-      }
     float m = -1.0e30f;
 #pragma unroll
     for (int p = 0; p < CLUSTER_MERGE_MAX_SPLITS; ++p)
-      if (p < splits) m = fmaxf(m, ml[p].x);
+      if (p < splits) m = fmaxf(m, recv_ml[(p * 8 + h) * 2]);
     float l = 0.0f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int p = 0; p < CLUSTER_MERGE_MAX_SPLITS; ++p)
       if (p < splits) {
-        const float w = exp2f(ml[p].x - m);
-        l += ml[p].y * w;
-        acc.x += v[p].x * w;
-        acc.y += v[p].y * w;
-        acc.z += v[p].z * w;
-        acc.w += v[p].w * w;
+        const float2 ml = *reinterpret_cast<const float2*>(recv_ml + (p * 8 + h) * 2);
+        const float4 v = *reinterpret_cast<const float4*>(recv + (p * cells_per_block + i) * 4);
+        const float w = exp2f(ml.x - m);
+        l += ml.y * w;
+        acc.x += v.x * w;
+        acc.y += v.y * w;
+        acc.z += v.z * w;
+        acc.w += v.w * w;
       }
     const float inv = 1.0f / l;
     *reinterpret_cast<float4*>(a.out + (qh0 + h) * HD + d) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
@@ -357,10 +366,6 @@ __device__ __forceinline__ void cluster_merge(const AttnArgs& a, const float* co
     *seq_counter = 0;
   }
   if (tid == 0) SGK_TP(7);
-  // nobody leaves (and frees its shared memory) before every block has read what it needs;
-  // nothing written since the first barrier is read inside the cluster, so no ordering is asked for
-  cluster_arrive_relaxed();
-  cluster_wait_plain();
 }
 
 // Block-cooperative merge of `count` (<= MERGE_MAX) partials (rows first..first+count
@@ -433,9 +438,9 @@ __device__ __forceinline__ void merge_block(const Partials& src, int stride, int
 template <int HD, int NT = MMA_THREADS>
 __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s, const float* ml_s, int opad,
                                              int* flags, int seq, int kvh, int split, int gqa, bool do_append,
-                                             int32_t* len_ptr, int64_t len, int tid, int splits, float* comb_s) {
-  // comb_s: [8][HD] floats of shared memory that nobody reads any more (the staged Q), for the
-  // block's combined output when the splits merge as a cluster
+                                             int32_t* len_ptr, int64_t len, int tid, int splits, float* recv) {
+  // recv: ClusterRecv<HD>::BYTES of shared memory used by nothing else, where the blocks of a
+  // cluster leave their outputs for this block to merge
   // `splits` is this sequence's own split count (<= a.splits, the stride of the partial arrays)
   const int n_groups = (splits + a.group_size - 1) / a.group_size;
   if (tid == 0) SGK_TP(4);
@@ -476,7 +481,7 @@ __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s
       const float inv = 1.0f / hml_s[2 * h + 1];
       *reinterpret_cast<float4*>(a.out + (qh0 + h) * HD + d) = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
     } else if (a.cluster_merge) {
-      *reinterpret_cast<float4*>(comb_s + h * HD + d) = o;
+      cluster_send_cell<HD>(recv, splits, split, gqa, idx, o);
     } else {
       *reinterpret_cast<float4*>(a.part.o + ((qh0 + h) * a.splits + split) * HD + d) = o;
       if (d == 0)
@@ -491,7 +496,8 @@ __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s
     int32_t* group_counter = a.group_counters + (int64_t(seq) * a.pool.kv_heads + kvh) * a.max_groups + group;
     int32_t* head_counter = a.head_counters + int64_t(seq) * a.pool.kv_heads + kvh;
     if (a.cluster_merge && splits > 1) {
-      cluster_merge<HD, NT>(a, comb_s, hml_s, splits, split, gqa, qh0, tid, do_append ? a.seq_counters + seq : nullptr,
+      cluster_send_ml<HD>(recv, hml_s, splits, split, gqa, tid);
+      cluster_merge<HD, NT>(a, recv, splits, split, gqa, qh0, tid, do_append ? a.seq_counters + seq : nullptr,
                             splits * a.pool.kv_heads, len_ptr, len);
       if (tid == 0) SGK_TP(6);
       return;
