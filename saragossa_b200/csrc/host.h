@@ -137,7 +137,8 @@ struct Batch {
   int32_t* d_group_counters = nullptr;
   int uniform_splits = 1;
   int resident_per_sm = -1, resident_stages = 0;   // blocks of the attention kernel an SM holds at once
-  int cluster_ok[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};   // per split count: can such a cluster be placed (asked once)
+  int max_clusters[17] = {-1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1};   // per split count: clusters of
+                                                     // that many blocks the device holds at once (asked once)
   int cluster_stages = 0;
   int max_splits = 1;
   int max_groups = 1;

@@ -478,18 +478,20 @@ int Batch::enqueue_attention(cudaStream_t stream, const float* d_q, float* d_out
       const int64_t blocks = int64_t(a.splits) * pool->kv_heads * n();
       if (per_sm > 0 && blocks <= int64_t(per_sm) * st->sm_count) a.shared_merge = 1;
     }
-    // Up to 8 splits run as one thread-block cluster and merge through distributed shared memory:
+    // Up to 16 splits run as one thread-block cluster and merge through distributed shared memory:
     // no partial goes through L2 and no device-wide atomic sits between the last page and the output.
+    // Only when every cluster of the launch is resident at once: a launch that would fit one wave of
+    // blocks must not get a second one from the placement of clusters.
     static const bool cluster_merge_off = std::getenv("SGK_NO_CLUSTER_MERGE") != nullptr;
-    if (!cluster_merge_off && a.pages_per_split == 0 && a.splits >= 2 && a.splits <= 8) {
+    if (!cluster_merge_off && a.pages_per_split == 0 && a.splits >= 2 && a.splits <= 16) {
       if (cluster_stages != a.n_stages) {
-        for (int& c : cluster_ok) c = -1;
+        for (int& c : max_clusters) c = -1;
         cluster_stages = a.n_stages;
       }
-      if (cluster_ok[a.splits] < 0)
-        cluster_ok[a.splits] = (kernel == 3 ? attention_u8_max_clusters(pool->head_dim, a.n_stages, a.splits)
-                                            : attention_mma_max_clusters(pool->head_dim, a.n_stages, a.splits)) > 0;
-      a.cluster_merge = cluster_ok[a.splits];
+      if (max_clusters[a.splits] < 0)
+        max_clusters[a.splits] = kernel == 3 ? attention_u8_max_clusters(pool->head_dim, a.n_stages, a.splits)
+                                             : attention_mma_max_clusters(pool->head_dim, a.n_stages, a.splits);
+      a.cluster_merge = int64_t(pool->kv_heads) * n() <= max_clusters[a.splits];
     }
     if (kernel == 3) {
       SGK_CUDA(launch_attention_u8(a, n(), stream));

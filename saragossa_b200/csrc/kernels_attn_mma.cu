@@ -468,6 +468,11 @@ int attention_mma_max_clusters(int head_dim, int n_stages, int splits) {
 }
 
 cudaError_t attention_mma_configure() {
+  // clusters of more than 8 blocks (up to 16 splits merge as one cluster) are an opt-in
+  cudaError_t c = cudaFuncSetAttribute(attention_mma_kernel<128>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+  if (c != cudaSuccess) return c;
+  c = cudaFuncSetAttribute(attention_mma_kernel<256>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+  if (c != cudaSuccess) return c;
   cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        227 * 1024);
   if (e != cudaSuccess) return e;

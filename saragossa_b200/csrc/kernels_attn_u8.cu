@@ -644,6 +644,11 @@ int attention_u8_max_clusters(int head_dim, int n_stages, int splits) {
 }
 
 cudaError_t attention_u8_configure() {
+  // clusters of more than 8 blocks (up to 16 splits merge as one cluster) are an opt-in
+  cudaError_t c = cudaFuncSetAttribute(attention_u8_kernel<128>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+  if (c != cudaSuccess) return c;
+  c = cudaFuncSetAttribute(attention_u8_kernel<256>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+  if (c != cudaSuccess) return c;
   cudaError_t e = cudaFuncSetAttribute(attention_u8_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        227 * 1024);
   if (e != cudaSuccess) return e;

@@ -266,7 +266,7 @@ __device__ __forceinline__ bool shared_merge(const AttnArgs& a, int splits, int 
 }
 
 // ---- thread-block cluster: the splits of one (sequence, KV head) as one cluster ------------
-constexpr int CLUSTER_MERGE_MAX_SPLITS = 8;  // the portable cluster size
+constexpr int CLUSTER_MERGE_MAX_SPLITS = 16;  // the largest cluster the hardware takes (above 8: opt-in per kernel)
 __device__ __forceinline__ uint32_t cluster_map_shared(const void* p, uint32_t cta_rank) {
   uint32_t remote;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(p)), "r"(cta_rank));
@@ -340,24 +340,24 @@ __device__ __forceinline__ void cluster_merge(const AttnArgs& a, const float* re
   for (int i = tid; split + splits * i < total; i += NT) {
     const int cell = split + splits * i;
     const int h = cell / (HD / 4), d = (cell % (HD / 4)) * 4;
+    // This code runs once per block, so what it costs is mostly the fetch of its instructions:
+    // short loops, not sixteen unrolled copies.
     float m = -1.0e30f;
-#pragma unroll
-    for (int p = 0; p < CLUSTER_MERGE_MAX_SPLITS; ++p)
-      if (p < splits) m = fmaxf(m, recv_ml[(p * 8 + h) * 2]);
+#pragma unroll 4
+    for (int p = 0; p < splits; ++p) m = fmaxf(m, recv_ml[(p * 8 + h) * 2]);
     float l = 0.0f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-    for (int p = 0; p < CLUSTER_MERGE_MAX_SPLITS; ++p)
-      if (p < splits) {
-        const float2 ml = *reinterpret_cast<const float2*>(recv_ml + (p * 8 + h) * 2);
-        const float4 v = *reinterpret_cast<const float4*>(recv + (p * cells_per_block + i) * 4);
-        const float w = exp2f(ml.x - m);
-        l += ml.y * w;
-        acc.x += v.x * w;
-        acc.y += v.y * w;
-        acc.z += v.z * w;
-        acc.w += v.w * w;
-      }
+#pragma unroll 4
+    for (int p = 0; p < splits; ++p) {
+      const float2 ml = *reinterpret_cast<const float2*>(recv_ml + (p * 8 + h) * 2);
+      const float4 v = *reinterpret_cast<const float4*>(recv + (p * cells_per_block + i) * 4);
+      const float w = exp2f(ml.x - m);
+      l += ml.y * w;
+      acc.x += v.x * w;
+      acc.y += v.y * w;
+      acc.z += v.z * w;
+      acc.w += v.w * w;
+    }
     const float inv = 1.0f / l;
     *reinterpret_cast<float4*>(a.out + (qh0 + h) * HD + d) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
   }
