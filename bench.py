@@ -586,7 +586,8 @@ def c1_decode_leg(sg, st, torch, stream):
     from oracle import sgo
     layers, qh, kvh, hd, ctx, steps = 36, 32, 8, 128, 1024, 64
     kv_dim, q_dim = kvh * hd, qh * hd
-    cap = ctx + steps + 16
+    loop_tokens = 32
+    cap = ctx + steps + 2 * loop_tokens + 16
     pool = st.pool(layers, kvh, hd, sg.KV_BF16, cap // 16 + 2, 1, cap)
     pool.shuffle_free_list(1)
     seq = pool.sequence(cap)
@@ -617,6 +618,7 @@ def c1_decode_leg(sg, st, torch, stream):
     stream.synchronize()
     us_token = e0.elapsed_time(e1) * 1e3 / (steps - 3)
     finite = bool(np.isfinite(d_out.download(count=layers * q_dim)).all())
+    token_loop = guarded(_c1_token_loop, sg, st, torch, stream, step, d_out, q_dim, loop_tokens)
     step.close()
     for b in batches:
         b.close()
@@ -642,7 +644,45 @@ def c1_decode_leg(sg, st, torch, stream):
         t_cpu.append(time.perf_counter() - t0)
     return {"us_per_token": us_token, "us_per_layer": us_token / layers, "launches_per_token": layers,
             "cpu_port_us_per_token": min(t_cpu[1:]) * 1e6, "cpu_threads": threads, "outputs_finite": finite,
+            "token_loop": token_loop,
             "shape": "batch 1, 36 layers, 32Q/8KV hd128 bf16, ctx 1024 -> 1088"}
+
+
+def _c1_token_loop(sg, st, torch, stream, step, d_out, hidden, tokens):
+    """The whole token with the index resident on the device: embedding lookup by the previous
+    token's index, the 36-layer graph, lm_head argmax into the window's ring (tied bf16
+    151 936 x 4 096 table, 1.24 GB), the host reading tokens back 4 behind (depth 4) or after
+    every token (depth 1). Wall clock per token, host included. The activations between the
+    pieces are not a model's (no projections or MLP here): shapes and dependencies are."""
+    vocab = 151936
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(5)
+    table = (torch.randn(vocab, hidden, device=dev, generator=gen) * 0.02).to(torch.bfloat16)
+    x = torch.zeros(hidden, device=dev)
+    first = torch.tensor([11], dtype=torch.int32, device=dev)
+    out = {"vocab": vocab, "hidden": hidden, "tokens": tokens}
+    for depth in (4, 1):
+        win = st.token_window(depth)
+        got, enq = [], 0
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        while len(got) < tokens:
+            while enq < tokens and win.inflight < depth:
+                src = win.previous_slot() or _Ptr(first)
+                st.encode_embedding_from_index(_Ptr(table), sg.KV_BF16, vocab, hidden, src, _Ptr(x),
+                                               stream=stream.cuda_stream)
+                step.replay(stream.cuda_stream)
+                st.encode_lm_head_argmax(_Ptr(table), sg.KV_BF16, vocab, hidden, d_out, win.output_slot(),
+                                         stream=stream.cuda_stream)
+                win.submit(stream.cuda_stream)
+                enq += 1
+            got.append(win.pop())
+        dt = time.perf_counter() - t0
+        win.close()
+        out[f"depth{depth}_us_per_token"] = dt / tokens * 1e6
+        out[f"depth{depth}_tokens_in_range"] = bool(all(0 <= t < vocab for t in got))
+    return out
 
 
 def c3_token_leg(sg, st, torch, stream):

@@ -137,7 +137,7 @@ __device__ __forceinline__ void load_row_scales(const uint8_t* p, float (&sc)[G]
   }
 }
 
-template <int HD>
+template <int HD, bool CLUSTER>
 __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a) {
   using S = U8Smem<HD>;
   constexpr int G = S::G;
@@ -593,7 +593,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
     }
   }
   __syncthreads();
-  finish_block<HD>(a, o_s, ml_s, S::OPAD, flags, seq, kvh, split, gqa, do_append, len_ptr, len, tid, splits,
+  finish_block<HD, CLUSTER>(a, o_s, ml_s, S::OPAD, flags, seq, kvh, split, gqa, do_append, len_ptr, len, tid, splits,
                    recv_s);
 }
 
@@ -613,9 +613,9 @@ int attention_u8_max_stages(int head_dim) {
 int attention_u8_resident_blocks(int head_dim, int n_stages) {
   int blocks = 0;
   cudaError_t e = head_dim == 128
-                      ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_u8_kernel<128>, MMA_THREADS,
+                      ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_u8_kernel<128, false>, MMA_THREADS,
                                                                       U8Smem<128>::total(n_stages))
-                      : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_u8_kernel<256>, MMA_THREADS,
+                      : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_u8_kernel<256, false>, MMA_THREADS,
                                                                       U8Smem<256>::total(n_stages));
   return e == cudaSuccess ? blocks : 0;
 }
@@ -634,8 +634,8 @@ int attention_u8_max_clusters(int head_dim, int n_stages, int splits) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   int n = 0;
-  cudaError_t e = head_dim == 128 ? cudaOccupancyMaxActiveClusters(&n, attention_u8_kernel<128>, &cfg)
-                                  : cudaOccupancyMaxActiveClusters(&n, attention_u8_kernel<256>, &cfg);
+  cudaError_t e = head_dim == 128 ? cudaOccupancyMaxActiveClusters(&n, attention_u8_kernel<128, true>, &cfg)
+                                  : cudaOccupancyMaxActiveClusters(&n, attention_u8_kernel<256, true>, &cfg);
   if (e != cudaSuccess) {
     cudaGetLastError();
     return 0;
@@ -644,15 +644,16 @@ int attention_u8_max_clusters(int head_dim, int n_stages, int splits) {
 }
 
 cudaError_t attention_u8_configure() {
-  // clusters of more than 8 blocks (up to 16 splits merge as one cluster) are an opt-in
-  cudaError_t c = cudaFuncSetAttribute(attention_u8_kernel<128>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-  if (c != cudaSuccess) return c;
-  c = cudaFuncSetAttribute(attention_u8_kernel<256>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-  if (c != cudaSuccess) return c;
-  cudaError_t e = cudaFuncSetAttribute(attention_u8_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       227 * 1024);
-  if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(attention_u8_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  const void* kernels[4] = {reinterpret_cast<const void*>(attention_u8_kernel<128, false>), reinterpret_cast<const void*>(attention_u8_kernel<256, false>),
+                            reinterpret_cast<const void*>(attention_u8_kernel<128, true>), reinterpret_cast<const void*>(attention_u8_kernel<256, true>)};
+  for (int i = 0; i < 4; ++i) {
+    cudaError_t e = cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    // clusters of more than 8 blocks (up to 16 splits merge as one cluster) are an opt-in
+    if (i >= 2) e = cudaFuncSetAttribute(kernels[i], cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
 }
 
 // A launch whose blocks wait for one another (shared merge) is a cooperative launch: the driver
@@ -684,9 +685,11 @@ static cudaError_t launch_one(void (*kernel)(AttnArgs), dim3 grid, size_t smem, 
 cudaError_t launch_attention_u8(const AttnArgs& a, int n_seq, cudaStream_t stream) {
   dim3 grid(a.splits, a.pool.kv_heads, n_seq);
   if (a.pool.head_dim == 128) {
-    return launch_one(attention_u8_kernel<128>, grid, U8Smem<128>::total(a.n_stages), a, stream);
+    return a.cluster_merge ? launch_one(attention_u8_kernel<128, true>, grid, U8Smem<128>::total(a.n_stages), a, stream)
+                           : launch_one(attention_u8_kernel<128, false>, grid, U8Smem<128>::total(a.n_stages), a, stream);
   } else {
-    return launch_one(attention_u8_kernel<256>, grid, U8Smem<256>::total(a.n_stages), a, stream);
+    return a.cluster_merge ? launch_one(attention_u8_kernel<256, true>, grid, U8Smem<256>::total(a.n_stages), a, stream)
+                           : launch_one(attention_u8_kernel<256, false>, grid, U8Smem<256>::total(a.n_stages), a, stream);
   }
   return cudaGetLastError();
 }

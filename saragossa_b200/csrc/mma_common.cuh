@@ -435,7 +435,10 @@ __device__ __forceinline__ void merge_block(const Partials& src, int stride, int
 // (o_s: [warps][8][opad] un-normalised outputs, ml_s: [warps][8] {max, sum}), writes the
 // block's partial (or the final output when there is one split), moves the device cursor
 // after a fused append, and runs the two-level merge of the splits.
-template <int HD, int NT = MMA_THREADS>
+// CLUSTER: the kernel instance that is launched as clusters (its splits merge through distributed
+// shared memory). A separate instance, so that the other one is compiled without a trace of that path:
+// with both in one kernel the page loop of the long-stream case lost 1.3 % (register allocation).
+template <int HD, bool CLUSTER, int NT = MMA_THREADS>
 __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s, const float* ml_s, int opad,
                                              int* flags, int seq, int kvh, int split, int gqa, bool do_append,
                                              int32_t* len_ptr, int64_t len, int tid, int splits, float* recv) {
@@ -480,7 +483,7 @@ __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s
     if (splits == 1) {
       const float inv = 1.0f / hml_s[2 * h + 1];
       *reinterpret_cast<float4*>(a.out + (qh0 + h) * HD + d) = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
-    } else if (a.cluster_merge) {
+    } else if (CLUSTER) {
       cluster_send_cell<HD>(recv, splits, split, gqa, idx, o);
     } else {
       *reinterpret_cast<float4*>(a.part.o + ((qh0 + h) * a.splits + split) * HD + d) = o;
@@ -495,7 +498,7 @@ __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s
     const int group_count = min(a.group_size, splits - group_first);
     int32_t* group_counter = a.group_counters + (int64_t(seq) * a.pool.kv_heads + kvh) * a.max_groups + group;
     int32_t* head_counter = a.head_counters + int64_t(seq) * a.pool.kv_heads + kvh;
-    if (a.cluster_merge && splits > 1) {
+    if (CLUSTER && splits > 1) {
       cluster_send_ml<HD>(recv, hml_s, splits, split, gqa, tid);
       cluster_merge<HD, NT>(a, recv, splits, split, gqa, qh0, tid, do_append ? a.seq_counters + seq : nullptr,
                             splits * a.pool.kv_heads, len_ptr, len);
