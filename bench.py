@@ -39,9 +39,9 @@ CTX, BATCH = 32768, 8
 KV_DIM, Q_DIM = KV_HEADS * HEAD_DIM, Q_HEADS * HEAD_DIM
 WORKLOAD = ("C2: Qwen3-30B-A3B-shaped KV path, 48 layers, 32Q/4KV heads, head_dim 128, bf16 KV, "
             "16-token pages, shuffled block table, ctx 32768, batch 8 per GPU")
-# ncu capture of attention_mma_kernel<128> at this shape (summary kept under profiles/):
+# ncu capture of attention_mma_kernel<128, false> at this shape (summary kept under profiles/):
 # DRAM read+write bytes per launch divided by the algorithmic bytes of the launch.
-NCU_TRAFFIC_RATIO = 1.0093
+NCU_TRAFFIC_RATIO = 1.0097
 
 
 KV_DTYPE = "bf16"           # or "u8": 32 codes + bf16 scale + bf16 bias per group = 1.125 B per element
@@ -362,7 +362,7 @@ def run_ours(args):
             "prefix_restore": restore, "head_sharded_batch1": head_sharded, "gated_delta_step": recurrent, "bulk_append": producer, "c3_hybrid_token": c3, "c5_serving": c5, "c4_prefix_turns": c4, "c1_decode": c1, "lm_head_argmax": lm_head,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": alg_per_launch * NCU_TRAFFIC_RATIO,
-                         "kernel": "attention_mma_kernel<128> (fused append + paged decode attention)",
+                         "kernel": "attention_mma_kernel<128, false> (fused append + paged decode attention)",
                          "peak_kind": f"of {peak_kind}", "frac_of_nominal_8tbs": achieved / 8000.0,
                          "algorithmic_bytes_per_launch": alg_per_launch, "launch_us": launch_us},
             "cpu_baseline": {"value": cpu_gbs, "unit": "GB/s", "cores": threads, "kind": "port",
