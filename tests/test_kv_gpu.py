@@ -1,6 +1,8 @@
 """GPU parity tests of the resident KV path, through the C ABI, against the CPU
 oracle. Each case names the reference test it ports (paths inside the reference
 crate); tolerances are the reference's own, written next to each assertion."""
+import os
+
 import numpy as np
 import pytest
 
@@ -650,3 +652,32 @@ def test_bounded_wait_reports_timeout_and_context_survives(state):
     kv.append_row(np.ones(32, np.float32), np.ones(32, np.float32))
     assert np.allclose(kv.attention_decode(np.ones(64, np.float32)), 1.0)
     kv.close()
+
+
+def test_cluster_merge_is_bit_identical_to_the_other_merges(tmp_path):
+    """Splits that merge as a thread-block cluster (distributed shared memory) give the same bits as
+    the same splits merged in one level by the last arriver (up to 12 splits: same order of
+    operations); against the two-level / shared merges of 13 to 16 splits the sums are ordered
+    differently and agree to rounding. The same cases run in two child processes, one with the
+    cluster path switched off."""
+    import subprocess
+    import sys
+    helper = os.path.join(os.path.dirname(os.path.abspath(__file__)), "helpers", "merge_paths_case.py")
+    files = []
+    for name, env_extra in (("cluster", {}), ("plain", {"SGK_NO_CLUSTER_MERGE": "1"})):
+        out = str(tmp_path / f"{name}.npz")
+        env = dict(os.environ)
+        env.pop("SGK_NO_CLUSTER_MERGE", None)
+        env.update(env_extra)
+        done = subprocess.run([sys.executable, helper, out], env=env, capture_output=True, text=True, timeout=600)
+        assert done.returncode == 0, done.stderr[-2000:]
+        files.append(np.load(out))
+    a, b = files
+    assert sorted(a.files) == sorted(b.files) and len(a.files) == 5 * 2 * 6 * 2
+    for key in a.files:
+        assert np.isfinite(a[key]).all(), key
+        splits = int(key.split("_")[2][1:])
+        if splits <= 12:
+            assert a[key].tobytes() == b[key].tobytes(), key
+        else:
+            assert np.abs(a[key] - b[key]).max() <= 2e-6, key   # outputs are O(0.1): a few f32 ulps
