@@ -207,6 +207,58 @@ __device__ __forceinline__ bool shared_merge(const AttnArgs& a, int splits, int 
     const int lane = tid & 31;
     const int warps = NT / 32;
     const int cells = gqa * (HD / 4);
+    if (splits <= 32) {
+      // One partial per lane. With few splits a block owns many cells (29 at 18 splits, head_dim
+      // 256): four cells per pass, all their loads issued before the first reduction, so the
+      // block pays a quarter of the L2 round trips.
+      constexpr int CELLS = 4;
+      const int stride = splits * warps;
+      for (int cell0 = split * warps + (tid >> 5); cell0 < cells; cell0 += CELLS * stride) {
+        float2 ml[CELLS];
+        float4 v[CELLS];
+#pragma unroll
+        for (int c = 0; c < CELLS; ++c) {
+          const int cell = cell0 + c * stride;
+          if (cell < cells && lane < splits) {
+            const int h = cell / (HD / 4), d = (cell % (HD / 4)) * 4;
+            ml[c] = __ldcg(reinterpret_cast<const float2*>(a.part.ml + ((qh0 + h) * a.splits + lane) * 2));
+            v[c] = __ldcg(reinterpret_cast<const float4*>(a.part.o + ((qh0 + h) * a.splits + lane) * HD + d));
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < CELLS; ++c) {
+          const int cell = cell0 + c * stride;
+          if (cell >= cells) break;   // uniform over the warp
+          const int h = cell / (HD / 4), d = (cell % (HD / 4)) * 4;
+          float m = lane < splits ? ml[c].x : -1.0e30f;
+#pragma unroll
+          for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+          float l = 0.0f;
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (lane < splits) {
+            const float w = exp2f(ml[c].x - m);
+            l += ml[c].y * w;
+            acc.x += v[c].x * w;
+            acc.y += v[c].y * w;
+            acc.z += v[c].z * w;
+            acc.w += v[c].w * w;
+          }
+#pragma unroll
+          for (int off = 16; off > 0; off >>= 1) {
+            l += __shfl_xor_sync(0xffffffffu, l, off);
+            acc.x += __shfl_xor_sync(0xffffffffu, acc.x, off);
+            acc.y += __shfl_xor_sync(0xffffffffu, acc.y, off);
+            acc.z += __shfl_xor_sync(0xffffffffu, acc.z, off);
+            acc.w += __shfl_xor_sync(0xffffffffu, acc.w, off);
+          }
+          if (lane == 0) {
+            const float inv = 1.0f / l;
+            *reinterpret_cast<float4*>(a.out + (qh0 + h) * HD + d) =
+                make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+          }
+        }
+      }
+    } else
     for (int cell = split * warps + (tid >> 5); cell < cells; cell += splits * warps) {
       const int h = cell / (HD / 4), d = (cell % (HD / 4)) * 4;
       const float* pm = a.part.ml + (qh0 + h) * a.splits * 2;
