@@ -419,7 +419,7 @@ def head_sharded_setup(sg, st, torch, world, rank):
     sh = sharding.head_shard(Q_HEADS, KV_HEADS, world, rank)
     steps = 8
     kv_loc, q_loc = sh.kv_heads * HEAD_DIM, sh.q_heads * HEAD_DIM
-    capacity = ((CTX + steps + 8 + 15) // 16) * 16
+    capacity = ((CTX + 2 * steps + 16 + 15) // 16) * 16
     pool = st.pool(LAYERS, sh.kv_heads, HEAD_DIM, sg.KV_BF16, capacity // 16, 1, capacity)
     pool.shuffle_free_list(3)
     seq = pool.sequence(capacity)
@@ -448,49 +448,89 @@ def head_sharded_run(sg, st, torch, dist, world, rank, stream, sh, pool, seq, ba
     out_full = torch.zeros(LAYERS, world * q_loc, device=dev)
     torch.cuda.synchronize()
 
-    def one_step():
+    # the rows of the direct exchange: [layer][world * q_loc] in memory the peers map
+    row = world * q_loc
+    rows = st.alloc(4 * LAYERS * row)
+    rows.upload(np.zeros(LAYERS * row, np.float32))
+    ex = st.exchange(rank, world)
+    handles = [None] * world
+    dist.all_gather_object(handles, (st.peer_export(rows), ex.handle))
+    peer_rows = {}
+    for p in range(world):
+        if p != rank:
+            peer_rows[p] = st.peer_open(handles[p][0])
+            ex.connect(p, handles[p][1])
+
+    class _At:
+        def __init__(self, ptr):
+            self.ptr = ptr
+
+    def step_nccl():
         for layer in range(LAYERS):
             batches[layer].enqueue_step(_Ptr(k[layer]), _Ptr(v[layer]), _Ptr(q[layer]), _Ptr(out_loc[layer]),
                                         stream=stream.cuda_stream)
             dist.all_gather_into_tensor(out_full[layer], out_loc[layer])
 
-    # One decode token = 48 x (fused kernel, all-gather) as ONE CUDA graph; the pages the replays
+    def step_direct():
+        for layer in range(LAYERS):
+            base = rows.ptr + 4 * layer * row
+            batches[layer].enqueue_step(_Ptr(k[layer]), _Ptr(v[layer]), _Ptr(q[layer]), _At(base + 4 * rank * q_loc),
+                                        stream=stream.cuda_stream)
+            ex.enqueue(base, [0 if p == rank else peer_rows[p].ptr + 4 * layer * row for p in range(world)],
+                       rank * q_loc, q_loc, stream=stream.cuda_stream)
+
+    # One decode token = 48 x (fused kernel, exchange) as ONE CUDA graph; the pages the replays
     # will append into are reserved before the capture (a replay moves only the device cursor).
-    seq.reserve(((CTX + steps + 8 + 15) // 16) * 16)
-    mode = "graph"
-    with torch.cuda.stream(stream):
-        one_step()
-        stream.synchronize()
-        dist.barrier()
-        try:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                one_step()
-            run = graph.replay
-        except Exception:  # noqa: BLE001 - same code on every rank: they all fall back together
-            mode, run = "stream", one_step
-        run()
-        stream.synchronize()
-        dist.barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(steps):
+    seq.reserve(((CTX + 2 * steps + 16 + 15) // 16) * 16)
+    result = {}
+    for name, one_step in (("nccl", step_nccl), ("direct", step_direct)):
+        mode = "graph"
+        with torch.cuda.stream(stream):
+            one_step()
+            stream.synchronize()
+            dist.barrier()
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    one_step()
+                run = graph.replay
+            except Exception:  # noqa: BLE001 - same code on every rank: they all fall back together
+                mode, run = "stream", one_step
             run()
-        e1.record(stream)
-        stream.synchronize()
-    ms = e0.elapsed_time(e1)
-    t = torch.tensor([ms], device=dev, dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
+            stream.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                run()
+            e1.record(stream)
+            stream.synchronize()
+        ms = e0.elapsed_time(e1)
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        result[name] = (float(t.item()), mode)
     finite = bool(torch.isfinite(out_full).all().item())
+    direct_rows = rows.download(np.float32, LAYERS * row).reshape(LAYERS, world, q_loc)
+    # every slice of the last token arrived: no slice of any layer is still the initial zero row
+    direct_complete = bool(np.isfinite(direct_rows).all() and (np.abs(direct_rows).max(axis=2) > 0).all())
+    status = st.device_status()
+    dist.barrier()
+    for p in peer_rows.values():
+        st.peer_close(p)
+    ex.close()
     for b in batches:
         b.close()
     seq.close()
     pool.close()
     total_bytes = sum(algorithmic_bytes(CTX + 2 + i + 1) for i in range(steps)) * LAYERS
-    return {"us_per_layer": ms * 1e3 / (steps * LAYERS), "hbm_gbs_aggregate": total_bytes / (ms * 1e-3) / 1e9,
+    ms, mode = result["nccl"]
+    ms_d, mode_d = result["direct"]
+    return {"us_per_layer": ms_d * 1e3 / (steps * LAYERS), "hbm_gbs_aggregate": total_bytes / (ms_d * 1e-3) / 1e9,
             "ranks": world, "kv_heads_per_rank": sh.kv_heads, "steps": steps, "outputs_finite": finite,
-            "submission": mode, "exchange": f"one NCCL all-gather of {world * q_loc * 4} bytes of attention output per layer"}
+            "all_slices_arrived": direct_complete, "device_status": status, "submission": mode_d,
+            "exchange": f"one kernel per layer: {q_loc * 4} bytes stored into each peer's row over NVLink, flag, bounded wait",
+            "with_nccl_all_gather": {"us_per_layer": ms * 1e3 / (steps * LAYERS), "submission": mode,
+                                     "exchange": f"one NCCL all-gather of {world * q_loc * 4} bytes per layer"}}
 
 
 def gated_delta_leg(sg, st, torch, stream):

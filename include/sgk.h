@@ -292,6 +292,34 @@ int32_t sgk_embed_enqueue_from_index(sgk_state* state, void* stream, const void*
                                      int64_t vocab, int32_t hidden, const int32_t* d_index, float embedding_scale,
                                      int32_t recast_bf16, float* d_out);
 
+/* Several GPUs sharing ONE long sequence by KV-head group (one process per GPU): every rank computes
+ * the attention output of its own heads and needs the whole row [q_heads * head_dim]. The reference
+ * runs on one device and has no counterpart; on one GPU this is `out` of sgk_kv_enqueue_attention.
+ * Device memory is made visible between the processes with the runtime's IPC handles (64 bytes,
+ * carried by whatever channel the host already has):
+ *   sgk_peer_export   handle of a device allocation of this process (its base address)
+ *   sgk_peer_open     maps a peer's allocation; the pointer is valid in kernels of this process
+ *   sgk_peer_close    unmaps it
+ * sgk_exchange_*: rank r of n (2..8). create returns the handle of this rank's flag array; connect
+ * takes every peer's. enqueue (ONE small kernel, enqueue only): stores this rank's slice
+ * [slice_offset, slice_offset + slice_floats) of d_local_row into the same place of every peer's
+ * row d_peer_rows[p] (entry `rank` ignored), raises this rank's flag at every peer and waits, with
+ * a bound, for every peer's flag: when the kernel has run, d_local_row is complete. A wait that runs
+ * out sets the device status (SGK_ERR_TIMEOUT through sgk_state_check_device) and the kernel
+ * returns. Every rank enqueues the same sequence of exchanges. A peer can be one exchange ahead:
+ * alternate between two rows, or keep a row per layer. Graph capture is allowed (the step number
+ * lives on the device). */
+typedef struct sgk_exchange sgk_exchange;
+int32_t sgk_peer_export(sgk_state* state, void* d_ptr, uint8_t handle_out[64]);
+int32_t sgk_peer_open(sgk_state* state, const uint8_t handle[64], void** d_ptr_out);
+int32_t sgk_peer_close(sgk_state* state, void* d_ptr);
+int32_t sgk_exchange_create(sgk_state* state, int32_t rank, int32_t n_ranks, sgk_exchange** out,
+                            uint8_t flags_handle_out[64]);
+void sgk_exchange_destroy(sgk_exchange* ex);
+int32_t sgk_exchange_connect(sgk_exchange* ex, int32_t peer_rank, const uint8_t peer_flags_handle[64]);
+int32_t sgk_exchange_enqueue(sgk_exchange* ex, void* stream, float* d_local_row, float* const* d_peer_rows,
+                             int64_t slice_offset, int32_t slice_floats);
+
 /* The submission window of the resident decode loop (src/decoder/resident/decode.rs:114-173;
  * RESIDENT_PIPELINE_WINDOW = 4, src/decoder/resident/types.rs:23): a ring of `depth` token indices
  * on the device. Token n's epilogue writes its index into output_slot() (slot n % depth), token

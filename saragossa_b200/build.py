@@ -24,6 +24,7 @@ SOURCES = [
     "kernels_attn_mma.cu",
     "kernels_attn_u8.cu",
     "kernels_copy.cu",
+    "kernels_exchange.cu",
     "kernels_linear.cu",
     "kernels_lm_head.cu",
     "noalloc.cu",

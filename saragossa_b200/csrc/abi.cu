@@ -16,6 +16,7 @@ struct sgk_batch : Batch {};
 struct sgk_step : Step {};
 struct sgk_linstate : LinState {};
 struct sgk_token_window : TokenWindow {};
+struct sgk_exchange : Exchange {};
 struct sgk_prefix : Prefix {};
 struct sgk_budget : Budget {};
 
@@ -1040,6 +1041,100 @@ int32_t sgk_embed_enqueue_from_index(sgk_state* st, void* stream, const void* d_
   SGK_CUDA(launch_embed_gather(d_table, table_dtype == SGK_KV_BF16, d_index, vocab, hidden, embedding_scale,
                                recast_bf16 != 0, d_out, st->pick(stream)));
   st->launches += 1;
+  return SGK_OK;
+}
+
+// ------------------------------------------------------------------ peer memory and the exchange
+int32_t sgk_peer_export(sgk_state* st, void* d_ptr, uint8_t handle_out[64]) {
+  if (!st || !d_ptr || !handle_out) return fail(SGK_ERR_BACKEND, "null argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  SGK_CUDA(cudaSetDevice(st->device));
+  cudaIpcMemHandle_t h;
+  SGK_CUDA(cudaIpcGetMemHandle(&h, d_ptr));
+  std::memcpy(handle_out, &h, 64);
+  return SGK_OK;
+}
+
+int32_t sgk_peer_open(sgk_state* st, const uint8_t handle[64], void** d_ptr_out) {
+  if (!st || !handle || !d_ptr_out) return fail(SGK_ERR_BACKEND, "null argument");
+  SGK_CUDA(cudaSetDevice(st->device));
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, 64);
+  SGK_CUDA(cudaIpcOpenMemHandle(d_ptr_out, h, cudaIpcMemLazyEnablePeerAccess));
+  return SGK_OK;
+}
+
+int32_t sgk_peer_close(sgk_state* st, void* d_ptr) {
+  if (!st || !d_ptr) return fail(SGK_ERR_BACKEND, "null argument");
+  SGK_CUDA(cudaSetDevice(st->device));
+  SGK_CUDA(cudaIpcCloseMemHandle(d_ptr));
+  return SGK_OK;
+}
+
+int32_t sgk_exchange_create(sgk_state* st, int32_t rank, int32_t n_ranks, sgk_exchange** out, uint8_t flags_handle_out[64]) {
+  if (!st || !out || !flags_handle_out) return fail(SGK_ERR_BACKEND, "null argument");
+  if (n_ranks < 2 || n_ranks > EXCHANGE_MAX_RANKS || rank < 0 || rank >= n_ranks)
+    return fail(SGK_ERR_CONFIG, "exchange: rank %d of %d (2 to %d ranks)", rank, n_ranks, EXCHANGE_MAX_RANKS);
+  SGK_CUDA(cudaSetDevice(st->device));
+  auto ex = std::make_unique<sgk_exchange>();
+  ex->st = st;
+  ex->rank = rank;
+  ex->n_ranks = n_ranks;
+  SGK_CUDA(cudaMalloc(&ex->d_flags, sizeof(int32_t) * (n_ranks + 1)));
+  SGK_CUDA(cudaMemset(ex->d_flags, 0, sizeof(int32_t) * (n_ranks + 1)));
+  cudaIpcMemHandle_t h;
+  SGK_CUDA(cudaIpcGetMemHandle(&h, ex->d_flags));
+  std::memcpy(flags_handle_out, &h, 64);
+  *out = ex.release();
+  return SGK_OK;
+}
+
+void sgk_exchange_destroy(sgk_exchange* ex) {
+  if (!ex) return;
+  cudaSetDevice(ex->st->device);
+  delete ex;
+}
+
+int32_t sgk_exchange_connect(sgk_exchange* ex, int32_t peer_rank, const uint8_t peer_flags_handle[64]) {
+  if (!ex || !peer_flags_handle) return fail(SGK_ERR_BACKEND, "null argument");
+  if (peer_rank < 0 || peer_rank >= ex->n_ranks || peer_rank == ex->rank)
+    return fail(SGK_ERR_CONFIG, "exchange: peer %d of %d (own rank %d)", peer_rank, ex->n_ranks, ex->rank);
+  if (ex->peer_flags[peer_rank]) return fail(SGK_ERR_CONFIG, "exchange: peer %d is connected already", peer_rank);
+  SGK_CUDA(cudaSetDevice(ex->st->device));
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, peer_flags_handle, 64);
+  void* p = nullptr;
+  SGK_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  ex->peer_flags[peer_rank] = static_cast<int32_t*>(p);
+  return SGK_OK;
+}
+
+int32_t sgk_exchange_enqueue(sgk_exchange* ex, void* stream, float* d_local_row, float* const* d_peer_rows,
+                             int64_t slice_offset, int32_t slice_floats) {
+  if (!ex || !d_local_row || !d_peer_rows) return fail(SGK_ERR_BACKEND, "null argument");
+  if (slice_offset < 0 || slice_floats <= 0 || slice_offset % 4 != 0 || slice_floats % 4 != 0)
+    return fail(SGK_ERR_DIMENSION, "exchange: slice of %d floats at %lld (multiples of 4)", slice_floats,
+                (long long)slice_offset);
+  ExchangeArgs a{};
+  a.local_row = d_local_row;
+  for (int p = 0; p < ex->n_ranks; ++p) {
+    if (p == ex->rank) continue;
+    if (!ex->peer_flags[p]) return fail(SGK_ERR_CONFIG, "exchange: peer %d is not connected", p);
+    if (!d_peer_rows[p]) return fail(SGK_ERR_BACKEND, "exchange: no row for peer %d", p);
+    if (reinterpret_cast<uintptr_t>(d_peer_rows[p]) & 15) return fail(SGK_ERR_CONFIG, "exchange: rows must be 16-byte aligned");
+    a.peer_row[p] = d_peer_rows[p];
+    a.peer_flags[p] = ex->peer_flags[p];
+  }
+  if (reinterpret_cast<uintptr_t>(d_local_row) & 15) return fail(SGK_ERR_CONFIG, "exchange: rows must be 16-byte aligned");
+  a.local_flags = ex->d_flags;
+  a.step = ex->d_flags + ex->n_ranks;
+  a.slice_offset = slice_offset;
+  a.slice_floats = slice_floats;
+  a.rank = ex->rank;
+  a.n_ranks = ex->n_ranks;
+  a.status = ex->st->d_status;
+  SGK_CUDA(launch_exchange_slices(a, ex->st->pick(stream)));
+  ex->st->launches += 1;
   return SGK_OK;
 }
 

@@ -203,6 +203,16 @@ struct TokenWindow {
   ~TokenWindow();
 };
 
+// One rank's end of the exchange between the GPUs that share a sequence by KV-head group: its
+// flag array and step counter (device memory that the peers map), and the peers' mapped arrays.
+struct Exchange {
+  State* st = nullptr;
+  int rank = 0, n_ranks = 1;
+  int32_t* d_flags = nullptr;   // [n_ranks] flags then [1] step counter
+  int32_t* peer_flags[8] = {};  // mapped from the peers' handles
+  ~Exchange();
+};
+
 using Hash32 = std::array<uint8_t, 32>;
 void sha256(const uint8_t* data, size_t n, uint8_t out[32]);
 Hash32 hash_chain(const Hash32& prev, const uint64_t* tokens, size_t n);

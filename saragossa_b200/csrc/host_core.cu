@@ -546,6 +546,12 @@ LinState::~LinState() {
   if (d_base) cudaFree(d_base);
 }
 
+Exchange::~Exchange() {
+  for (int p = 0; p < n_ranks; ++p)
+    if (p != rank && peer_flags[p]) cudaIpcCloseMemHandle(peer_flags[p]);
+  if (d_flags) cudaFree(d_flags);
+}
+
 TokenWindow::~TokenWindow() {
   // copies still in flight write into h_ring: wait for them before the memory goes
   for (cudaEvent_t e : done) {

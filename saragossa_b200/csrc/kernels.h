@@ -167,6 +167,20 @@ size_t lm_head_smem_bytes(int w_bf16, int n_rows, int hidden);  // shared memory
 // out[hidden] = table[*index] * scale (dense f32 or bf16 table); an index outside the table writes nothing.
 cudaError_t launch_embed_gather(const void* table, int table_bf16, const int32_t* index, int64_t vocab, int hidden,
                                 float scale, int recast_bf16, float* out, cudaStream_t stream);
+// Exchange of output slices between ranks over peer memory (kernels_exchange.cu).
+constexpr int EXCHANGE_MAX_RANKS = 8;
+struct ExchangeArgs {
+  const float* local_row;   // this rank's full row; its own slice has been written
+  float* peer_row[EXCHANGE_MAX_RANKS];      // the same row in every peer's memory (entry `rank` unused)
+  int32_t* peer_flags[EXCHANGE_MAX_RANKS];  // every peer's flag array [n_ranks] (entry `rank` unused)
+  int32_t* local_flags;     // this rank's flag array [n_ranks], written by the peers
+  int32_t* step;            // this rank's step counter
+  int64_t slice_offset;     // floats, multiple of 4
+  int32_t slice_floats;     // multiple of 4
+  int32_t rank, n_ranks;
+  int32_t* status;
+};
+cudaError_t launch_exchange_slices(const ExchangeArgs& a, cudaStream_t stream);
 cudaError_t launch_fill_normal(float* out, int64_t n, uint64_t seed, uint64_t stream_id,
                                uint64_t index0, cudaStream_t stream);
 

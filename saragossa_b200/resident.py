@@ -109,6 +109,39 @@ class _RawPtr:
         self.ptr = ptr
 
 
+class Exchange:
+    """One rank's end of the output exchange between GPUs that share a sequence by KV-head group
+    (sgk_exchange_*): `handle` goes to the peers, `connect` takes theirs, `enqueue` is one kernel."""
+
+    def __init__(self, state: "DecodeResidentState", rank: int, n_ranks: int):
+        self.state, self.L, self.rank, self.n_ranks = state, state.L, rank, n_ranks
+        h, handle = C.c_void_p(), (C.c_uint8 * 64)()
+        check(self.L.sgk_exchange_create(state.h, rank, n_ranks, C.byref(h), handle))
+        self.h, self.handle = h, bytes(handle)
+        state._adopt(self)
+
+    def connect(self, peer_rank: int, peer_handle: bytes):
+        check(self.L.sgk_exchange_connect(self.h, peer_rank, (C.c_uint8 * 64).from_buffer_copy(peer_handle)))
+
+    def enqueue(self, local_row_ptr: int, peer_row_ptrs, slice_offset: int, slice_floats: int, stream=None):
+        """local_row_ptr: device address of this rank's row; peer_row_ptrs[p]: the same row in peer p's
+        memory as mapped here (entry `rank` ignored)."""
+        rows = (C.c_void_p * self.n_ranks)(*[None if p == self.rank else int(peer_row_ptrs[p])
+                                              for p in range(self.n_ranks)])
+        check(self.L.sgk_exchange_enqueue(self.h, stream, local_row_ptr, rows, slice_offset, slice_floats))
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.L.sgk_exchange_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class TokenWindow:
     """The 4-deep submission window of the resident decode loop
     (src/decoder/resident/decode.rs:114-173): a device ring of token indices."""
@@ -247,6 +280,25 @@ class DecodeResidentState:
         index = d_index.ptr if hasattr(d_index, "ptr") else d_index
         check(self.L.sgk_embed_enqueue_from_index(self.h, stream, d_table.ptr, table_dtype, vocab, hidden, index,
                                                   embedding_scale, int(recast_bf16), d_out.ptr))
+
+    def peer_export(self, buf) -> bytes:
+        """IPC handle (64 bytes) of a device allocation of this process, for the other ranks."""
+        h = (C.c_uint8 * 64)()
+        check(self.L.sgk_peer_export(self.h, buf.ptr, h))
+        return bytes(h)
+
+    def peer_open(self, handle: bytes) -> "_RawPtr":
+        """Maps a peer's allocation; the result stands where a device buffer is expected."""
+        h = (C.c_uint8 * 64).from_buffer_copy(handle)
+        p = C.c_void_p()
+        check(self.L.sgk_peer_open(self.h, h, C.byref(p)))
+        return _RawPtr(p.value)
+
+    def peer_close(self, mapped):
+        check(self.L.sgk_peer_close(self.h, mapped.ptr))
+
+    def exchange(self, rank, n_ranks) -> "Exchange":
+        return Exchange(self, rank, n_ranks)
 
     def token_window(self, depth=4) -> "TokenWindow":
         return TokenWindow(self, depth)
