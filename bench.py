@@ -419,7 +419,7 @@ def head_sharded_setup(sg, st, torch, world, rank):
     sh = sharding.head_shard(Q_HEADS, KV_HEADS, world, rank)
     steps = 8
     kv_loc, q_loc = sh.kv_heads * HEAD_DIM, sh.q_heads * HEAD_DIM
-    capacity = ((CTX + 2 * steps + 16 + 15) // 16) * 16
+    capacity = ((CTX + 3 * steps + 24 + 15) // 16) * 16
     pool = st.pool(LAYERS, sh.kv_heads, HEAD_DIM, sg.KV_BF16, capacity // 16, 1, capacity)
     pool.shuffle_free_list(3)
     seq = pool.sequence(capacity)
@@ -479,11 +479,19 @@ def head_sharded_run(sg, st, torch, dist, world, rank, stream, sh, pool, seq, ba
             ex.enqueue(base, [0 if p == rank else peer_rows[p].ptr + 4 * layer * row for p in range(world)],
                        rank * q_loc, q_loc, stream=stream.cuda_stream)
 
+    def step_fused():
+        for layer in range(LAYERS):
+            base = rows.ptr + 4 * layer * row
+            batches[layer].enqueue_step_exchange(
+                _Ptr(k[layer]), _Ptr(v[layer]), _Ptr(q[layer]), ex, base,
+                [0 if p == rank else peer_rows[p].ptr + 4 * layer * row for p in range(world)], rank * q_loc,
+                stream=stream.cuda_stream)
+
     # One decode token = 48 x (fused kernel, exchange) as ONE CUDA graph; the pages the replays
     # will append into are reserved before the capture (a replay moves only the device cursor).
-    seq.reserve(((CTX + 2 * steps + 16 + 15) // 16) * 16)
+    seq.reserve(((CTX + 3 * steps + 24 + 15) // 16) * 16)
     result = {}
-    for name, one_step in (("nccl", step_nccl), ("direct", step_direct)):
+    for name, one_step in (("nccl", step_nccl), ("direct", step_direct), ("fused", step_fused)):
         mode = "graph"
         with torch.cuda.stream(stream):
             one_step()
@@ -525,10 +533,14 @@ def head_sharded_run(sg, st, torch, dist, world, rank, stream, sh, pool, seq, ba
     total_bytes = sum(algorithmic_bytes(CTX + 2 + i + 1) for i in range(steps)) * LAYERS
     ms, mode = result["nccl"]
     ms_d, mode_d = result["direct"]
-    return {"us_per_layer": ms_d * 1e3 / (steps * LAYERS), "hbm_gbs_aggregate": total_bytes / (ms_d * 1e-3) / 1e9,
+    ms_f, mode_f = result["fused"]
+    return {"us_per_layer": ms_f * 1e3 / (steps * LAYERS), "hbm_gbs_aggregate": total_bytes / (ms_f * 1e-3) / 1e9,
             "ranks": world, "kv_heads_per_rank": sh.kv_heads, "steps": steps, "outputs_finite": finite,
-            "all_slices_arrived": direct_complete, "device_status": status, "submission": mode_d,
-            "exchange": f"one kernel per layer: {q_loc * 4} bytes stored into each peer's row over NVLink, flag, bounded wait",
+            "all_slices_arrived": direct_complete, "device_status": status, "submission": mode_f,
+            "exchange": f"inside the attention launch: every output cell ({q_loc * 4} bytes per rank) also stored into each "
+                        "peer's row over NVLink; the last block raises the flags and waits (bounded) for the peers'",
+            "with_exchange_kernel": {"us_per_layer": ms_d * 1e3 / (steps * LAYERS), "submission": mode_d,
+                                     "exchange": "attention launch, then one small kernel per layer: slice stored to the peers, flag, bounded wait"},
             "with_nccl_all_gather": {"us_per_layer": ms * 1e3 / (steps * LAYERS), "submission": mode,
                                      "exchange": f"one NCCL all-gather of {world * q_loc * 4} bytes per layer"}}
 

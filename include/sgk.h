@@ -310,6 +310,16 @@ int32_t sgk_embed_enqueue_from_index(sgk_state* state, void* stream, const void*
  * alternate between two rows, or keep a row per layer. Graph capture is allowed (the step number
  * lives on the device). */
 typedef struct sgk_exchange sgk_exchange;
+/* sgk_batch_enqueue_step_exchange: sgk_batch_enqueue_step whose output goes to d_local_row +
+ * slice_offset AND, from the same launch, to the same place of every peer's row: the fused
+ * append + attention kernel stores every final output cell to the peers as well, and the block
+ * that leaves the launch last raises the flags and waits (bounded) for the peers': compute and
+ * exchange are ONE kernel. Where the launch cannot do it (generic kernel, uneven batch) the call
+ * enqueues the attention launch and then sgk_exchange_enqueue: same result, two launches. */
+int32_t sgk_batch_enqueue_step_exchange(sgk_batch* batch, void* stream, const float* d_k, const float* d_v,
+                                        const float* d_q, sgk_exchange* ex, float* d_local_row,
+                                        float* const* d_peer_rows, int64_t slice_offset, int64_t sliding_window,
+                                        float attn_scalar);
 int32_t sgk_peer_export(sgk_state* state, void* d_ptr, uint8_t handle_out[64]);
 int32_t sgk_peer_open(sgk_state* state, const uint8_t handle[64], void** d_ptr_out);
 int32_t sgk_peer_close(sgk_state* state, void* d_ptr);

@@ -1080,8 +1080,8 @@ int32_t sgk_exchange_create(sgk_state* st, int32_t rank, int32_t n_ranks, sgk_ex
   ex->st = st;
   ex->rank = rank;
   ex->n_ranks = n_ranks;
-  SGK_CUDA(cudaMalloc(&ex->d_flags, sizeof(int32_t) * (n_ranks + 1)));
-  SGK_CUDA(cudaMemset(ex->d_flags, 0, sizeof(int32_t) * (n_ranks + 1)));
+  SGK_CUDA(cudaMalloc(&ex->d_flags, sizeof(int32_t) * (n_ranks + 2)));
+  SGK_CUDA(cudaMemset(ex->d_flags, 0, sizeof(int32_t) * (n_ranks + 2)));
   cudaIpcMemHandle_t h;
   SGK_CUDA(cudaIpcGetMemHandle(&h, ex->d_flags));
   std::memcpy(flags_handle_out, &h, 64);
@@ -1136,6 +1136,35 @@ int32_t sgk_exchange_enqueue(sgk_exchange* ex, void* stream, float* d_local_row,
   SGK_CUDA(launch_exchange_slices(a, ex->st->pick(stream)));
   ex->st->launches += 1;
   return SGK_OK;
+}
+
+int32_t sgk_batch_enqueue_step_exchange(sgk_batch* b, void* stream, const float* d_k, const float* d_v, const float* d_q,
+                                        sgk_exchange* ex, float* d_local_row, float* const* d_peer_rows,
+                                        int64_t slice_offset, int64_t sliding_window, float attn_scalar) {
+  if (!b || !ex || !d_local_row || !d_peer_rows) return fail(SGK_ERR_BACKEND, "null argument");
+  if (!d_k || !d_v || !d_q) return fail(SGK_ERR_BACKEND, "append: null device pointer");
+  if (sliding_window < 0) return fail(SGK_ERR_DIMENSION, "negative sliding window");
+  if (slice_offset < 0 || slice_offset % 4 != 0) return fail(SGK_ERR_DIMENSION, "exchange: slice offset %lld", (long long)slice_offset);
+  const int64_t slice = int64_t(b->n()) * b->q_heads * b->pool->head_dim;
+  PeerTarget target;
+  target.ex = ex;
+  for (int p = 0; p < ex->n_ranks; ++p) {
+    if (p == ex->rank) continue;
+    if (!ex->peer_flags[p]) return fail(SGK_ERR_CONFIG, "exchange: peer %d is not connected", p);
+    if (!d_peer_rows[p]) return fail(SGK_ERR_BACKEND, "exchange: no row for peer %d", p);
+    if (reinterpret_cast<uintptr_t>(d_peer_rows[p]) & 15) return fail(SGK_ERR_CONFIG, "exchange: rows must be 16-byte aligned");
+    target.peer_out[p] = d_peer_rows[p] + slice_offset;
+  }
+  if (reinterpret_cast<uintptr_t>(d_local_row) & 15) return fail(SGK_ERR_CONFIG, "exchange: rows must be 16-byte aligned");
+  b->peer_target = &target;
+  b->peer_target_fused = false;
+  int32_t rc = b->enqueue_attention(b->st->pick(stream), d_q, d_local_row + slice_offset, 0, sliding_window, attn_scalar,
+                                    d_k, d_v);
+  b->peer_target = nullptr;
+  if (rc != SGK_OK) return rc;
+  if (b->peer_target_fused) return SGK_OK;
+  // the launch could not take the peers (generic kernel, uneven batch, cluster merge): the small kernel does it
+  return sgk_exchange_enqueue(ex, stream, d_local_row, d_peer_rows, slice_offset, static_cast<int32_t>(slice));
 }
 
 // ------------------------------------------------------------------ token window

@@ -33,6 +33,14 @@ const char* last_error_cstr();
     if (rc_ != SGK_OK) return rc_; \
   } while (0)
 
+struct Exchange;
+// Where the next attention launch of a batch also sends its outputs (set by the exchange entry point
+// for one enqueue): the peers' counterparts of d_out.
+struct PeerTarget {
+  Exchange* ex = nullptr;
+  float* peer_out[8] = {};   // indexed by rank; the own entry is unused
+};
+
 struct Batch;
 struct Seq;
 struct Pool;
@@ -137,6 +145,8 @@ struct Batch {
   int32_t* d_group_counters = nullptr;
   int uniform_splits = 1;
   int resident_per_sm = -1, resident_stages = 0;   // blocks of the attention kernel an SM holds at once
+  const PeerTarget* peer_target = nullptr;   // not null: the launch being enqueued sends its outputs to the peers too
+  bool peer_target_fused = false;            // set by enqueue_attention when the launch did take the peers
   int max_clusters[17] = {-1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1};   // per split count: clusters of
                                                      // that many blocks the device holds at once (asked once)
   int cluster_stages = 0;
@@ -208,7 +218,7 @@ struct TokenWindow {
 struct Exchange {
   State* st = nullptr;
   int rank = 0, n_ranks = 1;
-  int32_t* d_flags = nullptr;   // [n_ranks] flags then [1] step counter
+  int32_t* d_flags = nullptr;   // [n_ranks] flags, then the step counter, then the exit counter of fused launches
   int32_t* peer_flags[8] = {};  // mapped from the peers' handles
   ~Exchange();
 };

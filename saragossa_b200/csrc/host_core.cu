@@ -493,6 +493,26 @@ int Batch::enqueue_attention(cudaStream_t stream, const float* d_q, float* d_out
                                              : attention_mma_max_clusters(pool->head_dim, a.n_stages, a.splits);
       a.cluster_merge = int64_t(pool->kv_heads) * n() <= max_clusters[a.splits];
     }
+    // Several GPUs share the sequence: the launch sends its outputs to the peers itself and its last
+    // block exchanges flags with them, when every block of the launch reaches its end (even splits)
+    // and the merge is not the cluster one (that instance has no peer stores).
+    if (peer_target != nullptr && a.pages_per_split == 0) {
+      const Exchange* ex = peer_target->ex;
+      a.cluster_merge = 0;
+      a.n_peers = 0;
+      a.rank = ex->rank;
+      for (int p = 0; p < ex->n_ranks; ++p) {
+        if (p == ex->rank) continue;
+        a.peer_out[a.n_peers] = peer_target->peer_out[p];
+        a.peer_flags[a.n_peers] = ex->peer_flags[p];
+        a.peer_rank[a.n_peers] = p;
+        a.n_peers += 1;
+      }
+      a.local_flags = ex->d_flags;
+      a.ex_step = ex->d_flags + ex->n_ranks;
+      a.exit_counter = ex->d_flags + ex->n_ranks + 1;
+      peer_target_fused = true;
+    }
     if (kernel == 3) {
       SGK_CUDA(launch_attention_u8(a, n(), stream));
     } else {

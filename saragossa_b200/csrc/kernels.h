@@ -49,7 +49,17 @@ struct AttnArgs {
   int64_t sliding_window;   // > 0: start = max(len - window, 0)
   int32_t shared_merge;     // 1: every block of a (sequence, KV head) merges a slice once all have arrived
   int32_t cluster_merge;    // 1: the splits of a (sequence, KV head) are one thread-block cluster and merge through
-                            //    distributed shared memory (2..8 splits)
+                            //    distributed shared memory (2..16 splits)
+  // Several GPUs share the sequence by KV-head group (n_peers > 0): final output cells also go to
+  // the same place of every peer's row, and the block that leaves last exchanges flags with the peers.
+  int32_t n_peers;          // peers = the other ranks
+  int32_t rank;             // this rank's index in the flag arrays
+  float* peer_out[7];       // a.out's counterpart in every peer's memory
+  int32_t* peer_flags[7];   // every peer's flag array
+  int32_t peer_rank[7];     // every peer's index in this rank's flag array
+  int32_t* local_flags;     // this rank's flag array, written by the peers
+  int32_t* ex_step;         // this rank's step counter
+  int32_t* exit_counter;    // blocks of the launch that have finished; zero between launches
   int32_t pages_per_split;  // > 0: a sequence is cut into ceil(pages / this) splits (<= splits), blocks beyond exit
   float scale_log2e;        // log2(e) / sqrt(attn_scalar)
   int32_t splits;

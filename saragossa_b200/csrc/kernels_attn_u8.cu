@@ -137,7 +137,7 @@ __device__ __forceinline__ void load_row_scales(const uint8_t* p, float (&sc)[G]
   }
 }
 
-template <int HD, bool CLUSTER>
+template <int HD, bool CLUSTER, bool PEERS>
 __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a) {
   using S = U8Smem<HD>;
   constexpr int G = S::G;
@@ -593,8 +593,9 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
     }
   }
   __syncthreads();
-  finish_block<HD, CLUSTER>(a, o_s, ml_s, S::OPAD, flags, seq, kvh, split, gqa, do_append, len_ptr, len, tid, splits,
-                   recv_s);
+  finish_block<HD, CLUSTER, PEERS>(a, o_s, ml_s, S::OPAD, flags, seq, kvh, split, gqa, do_append, len_ptr, len, tid,
+                                   splits, recv_s);
+  if (PEERS) peers_finish(a, tid, flags);
 }
 
 bool attention_u8_supported(int dtype, int head_dim, int gqa) {
@@ -613,9 +614,9 @@ int attention_u8_max_stages(int head_dim) {
 int attention_u8_resident_blocks(int head_dim, int n_stages) {
   int blocks = 0;
   cudaError_t e = head_dim == 128
-                      ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_u8_kernel<128, false>, MMA_THREADS,
+                      ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_u8_kernel<128, false, false>, MMA_THREADS,
                                                                       U8Smem<128>::total(n_stages))
-                      : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_u8_kernel<256, false>, MMA_THREADS,
+                      : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_u8_kernel<256, false, false>, MMA_THREADS,
                                                                       U8Smem<256>::total(n_stages));
   return e == cudaSuccess ? blocks : 0;
 }
@@ -634,8 +635,8 @@ int attention_u8_max_clusters(int head_dim, int n_stages, int splits) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   int n = 0;
-  cudaError_t e = head_dim == 128 ? cudaOccupancyMaxActiveClusters(&n, attention_u8_kernel<128, true>, &cfg)
-                                  : cudaOccupancyMaxActiveClusters(&n, attention_u8_kernel<256, true>, &cfg);
+  cudaError_t e = head_dim == 128 ? cudaOccupancyMaxActiveClusters(&n, attention_u8_kernel<128, true, false>, &cfg)
+                                  : cudaOccupancyMaxActiveClusters(&n, attention_u8_kernel<256, true, false>, &cfg);
   if (e != cudaSuccess) {
     cudaGetLastError();
     return 0;
@@ -644,13 +645,14 @@ int attention_u8_max_clusters(int head_dim, int n_stages, int splits) {
 }
 
 cudaError_t attention_u8_configure() {
-  const void* kernels[4] = {reinterpret_cast<const void*>(attention_u8_kernel<128, false>), reinterpret_cast<const void*>(attention_u8_kernel<256, false>),
-                            reinterpret_cast<const void*>(attention_u8_kernel<128, true>), reinterpret_cast<const void*>(attention_u8_kernel<256, true>)};
-  for (int i = 0; i < 4; ++i) {
+  const void* kernels[6] = {reinterpret_cast<const void*>(attention_u8_kernel<128, false, false>), reinterpret_cast<const void*>(attention_u8_kernel<256, false, false>),
+                            reinterpret_cast<const void*>(attention_u8_kernel<128, true, false>), reinterpret_cast<const void*>(attention_u8_kernel<256, true, false>),
+                            reinterpret_cast<const void*>(attention_u8_kernel<128, false, true>), reinterpret_cast<const void*>(attention_u8_kernel<256, false, true>)};
+  for (int i = 0; i < 6; ++i) {
     cudaError_t e = cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
     // clusters of more than 8 blocks (up to 16 splits merge as one cluster) are an opt-in
-    if (i >= 2) e = cudaFuncSetAttribute(kernels[i], cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (i == 2 || i == 3) e = cudaFuncSetAttribute(kernels[i], cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) return e;
   }
   return cudaSuccess;
@@ -685,11 +687,13 @@ static cudaError_t launch_one(void (*kernel)(AttnArgs), dim3 grid, size_t smem, 
 cudaError_t launch_attention_u8(const AttnArgs& a, int n_seq, cudaStream_t stream) {
   dim3 grid(a.splits, a.pool.kv_heads, n_seq);
   if (a.pool.head_dim == 128) {
-    return a.cluster_merge ? launch_one(attention_u8_kernel<128, true>, grid, U8Smem<128>::total(a.n_stages), a, stream)
-                           : launch_one(attention_u8_kernel<128, false>, grid, U8Smem<128>::total(a.n_stages), a, stream);
+    if (a.n_peers > 0) return launch_one(attention_u8_kernel<128, false, true>, grid, U8Smem<128>::total(a.n_stages), a, stream);
+    return a.cluster_merge ? launch_one(attention_u8_kernel<128, true, false>, grid, U8Smem<128>::total(a.n_stages), a, stream)
+                           : launch_one(attention_u8_kernel<128, false, false>, grid, U8Smem<128>::total(a.n_stages), a, stream);
   } else {
-    return a.cluster_merge ? launch_one(attention_u8_kernel<256, true>, grid, U8Smem<256>::total(a.n_stages), a, stream)
-                           : launch_one(attention_u8_kernel<256, false>, grid, U8Smem<256>::total(a.n_stages), a, stream);
+    if (a.n_peers > 0) return launch_one(attention_u8_kernel<256, false, true>, grid, U8Smem<256>::total(a.n_stages), a, stream);
+    return a.cluster_merge ? launch_one(attention_u8_kernel<256, true, false>, grid, U8Smem<256>::total(a.n_stages), a, stream)
+                           : launch_one(attention_u8_kernel<256, false, false>, grid, U8Smem<256>::total(a.n_stages), a, stream);
   }
   return cudaGetLastError();
 }

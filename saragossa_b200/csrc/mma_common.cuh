@@ -179,6 +179,61 @@ __device__ __forceinline__ int ld_acquire_gpu(const int32_t* p) {
   return v;
 }
 
+// ---- outputs that go to the peers as well -------------------------------------------------
+// PEERS: the kernel instance used when several GPUs share the sequence by KV-head group: every final
+// output cell is stored into the same place of every peer's row too (plain 16-byte stores to peer
+// memory over NVLink), and the block that leaves the launch last raises this rank's flag at every
+// peer and waits, with a bound, for theirs: when the kernel has run, the local row is complete.
+// The compute and the exchange are one launch.
+template <bool PEERS>
+__device__ __forceinline__ void store_out(const AttnArgs& a, int64_t index, float4 v) {
+  *reinterpret_cast<float4*>(a.out + index) = v;
+  if (PEERS) {
+    for (int p = 0; p < a.n_peers; ++p) *reinterpret_cast<float4*>(a.peer_out[p] + index) = v;
+  }
+}
+__device__ __forceinline__ void st_release_sys_s32(int32_t* p, int32_t v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int32_t ld_acquire_sys_s32(const int32_t* p) {
+  int32_t v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Last statement of every block of a PEERS launch (all blocks must get here).
+__device__ __forceinline__ void peers_finish(const AttnArgs& a, int tid, int* flags) {
+  volatile int* last_s = flags + 4;   // a free word of the block's flag area
+  // Ordering, from a store to a peer by any thread of any block to the peer's read after its wait:
+  // block barrier -> this block's arrival (release, gpu scope) -> the last block's arrival (acquire)
+  // -> block barrier -> the flag's store (release, system scope) -> the peer's acquire load. Every
+  // link synchronises at a scope that holds both ends, so the chain is a causality order and the
+  // peer sees the store; no block needs a system-scope fence of its own.
+  __syncthreads();
+  if (tid == 0) {
+    const int total = gridDim.x * gridDim.y * gridDim.z;
+    *last_s = arrive_acq_rel(a.exit_counter) == total - 1;
+  }
+  __syncthreads();
+  if (!*last_s) return;
+  // one thread per peer: flag up, then wait for the peer's
+  int32_t step = *a.ex_step + 1;
+  if (tid < a.n_peers) {
+    st_release_sys_s32(a.peer_flags[tid] + a.rank, step);
+    uint32_t spins = 0;
+    while (ld_acquire_sys_s32(a.local_flags + a.peer_rank[tid]) - step < 0) {
+      if (++spins > WAIT_SPINS) {
+        atomicExch(a.status, DEV_ERR_WAIT_TIMEOUT);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    *a.ex_step = step;
+    *a.exit_counter = 0;
+  }
+}
+
 // Merge shared by ALL blocks of a (sequence, KV head), for launches whose blocks are all resident
 // at once (the host checks that the grid fits the device): every block publishes its partial,
 // waits (bounded) until all `splits` partials are there, and then merges a slice of the output:
@@ -186,7 +241,7 @@ __device__ __forceinline__ int ld_acquire_gpu(const int32_t* p) {
 // reduced with shuffles. The tail of the launch is then one wait and one L2 round trip instead of
 // two merge levels done by single blocks. Returns false when the wait ran out.
 constexpr int SHARED_MERGE_MAX_SPLITS = 160;   // five partials per lane
-template <int HD, int NT>
+template <int HD, int NT, bool PEERS = false>
 __device__ __forceinline__ bool shared_merge(const AttnArgs& a, int splits, int split, int gqa, int64_t qh0,
                                              int32_t* arrive_counter, int32_t* depart_counter, int* flags, int tid) {
   volatile int* abort_flag = flags;
@@ -253,8 +308,7 @@ __device__ __forceinline__ bool shared_merge(const AttnArgs& a, int splits, int 
           }
           if (lane == 0) {
             const float inv = 1.0f / l;
-            *reinterpret_cast<float4*>(a.out + (qh0 + h) * HD + d) =
-                make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+            store_out<PEERS>(a, (qh0 + h) * HD + d, make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv));
           }
         }
       }
@@ -301,7 +355,7 @@ __device__ __forceinline__ bool shared_merge(const AttnArgs& a, int splits, int 
       }
       if (lane == 0) {
         const float inv = 1.0f / l;
-        *reinterpret_cast<float4*>(a.out + (qh0 + h) * HD + d) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+        store_out<PEERS>(a, (qh0 + h) * HD + d, make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv));
       }
     }
   }
@@ -426,9 +480,9 @@ __device__ __forceinline__ void cluster_merge(const AttnArgs& a, const float* re
 // (the {max, sum} pairs of the cell's head and the partial values) before the first
 // use, so a pass costs one L2 round trip and no block barrier. final != 0: writes the
 // normalised output; else writes one un-normalised partial (row dst_row of dst).
-template <int HD, int NT = MMA_THREADS>
-__device__ __forceinline__ void merge_block(const Partials& src, int stride, int first, int count, int gqa,
-                                            int64_t qh0, bool final, float* out, const Partials& dst,
+template <int HD, int NT = MMA_THREADS, bool PEERS = false>
+__device__ __forceinline__ void merge_block(const AttnArgs& a, const Partials& src, int stride, int first, int count, int gqa,
+                                            int64_t qh0, bool final, const Partials& dst,
                                             int dst_stride, int dst_row, int tid) {
   constexpr int CELLS = NT >= 256 ? 1 : 2;   // the register budget of a 256-thread block is smaller
   const int total = gqa * (HD / 4);
@@ -473,8 +527,7 @@ __device__ __forceinline__ void merge_block(const Partials& src, int stride, int
         }
       if (final) {
         const float inv = 1.0f / l;
-        *reinterpret_cast<float4*>(out + (qh0 + h) * HD + d) =
-            make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+        store_out<PEERS>(a, (qh0 + h) * HD + d, make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv));
       } else {
         *reinterpret_cast<float4*>(dst.o + ((qh0 + h) * dst_stride + dst_row) * HD + d) = acc;
         if (d == 0) *reinterpret_cast<float2*>(dst.ml + ((qh0 + h) * dst_stride + dst_row) * 2) = make_float2(m, l);
@@ -490,7 +543,7 @@ __device__ __forceinline__ void merge_block(const Partials& src, int stride, int
 // CLUSTER: the kernel instance that is launched as clusters (its splits merge through distributed
 // shared memory). A separate instance, so that the other one is compiled without a trace of that path:
 // with both in one kernel the page loop of the long-stream case lost 1.3 % (register allocation).
-template <int HD, bool CLUSTER, int NT = MMA_THREADS>
+template <int HD, bool CLUSTER, bool PEERS = false, int NT = MMA_THREADS>
 __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s, const float* ml_s, int opad,
                                              int* flags, int seq, int kvh, int split, int gqa, bool do_append,
                                              int32_t* len_ptr, int64_t len, int tid, int splits, float* recv) {
@@ -534,7 +587,7 @@ __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s
     }
     if (splits == 1) {
       const float inv = 1.0f / hml_s[2 * h + 1];
-      *reinterpret_cast<float4*>(a.out + (qh0 + h) * HD + d) = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
+      store_out<PEERS>(a, (qh0 + h) * HD + d, make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv));
     } else if (CLUSTER) {
       cluster_send_cell<HD>(recv, splits, split, gqa, idx, o);
     } else {
@@ -568,7 +621,7 @@ __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s
           a.seq_counters[seq] = 0;
         }
       }
-      shared_merge<HD, NT>(a, splits, split, gqa, qh0, head_counter, group_counter - group, flags, tid);
+      shared_merge<HD, NT, PEERS>(a, splits, split, gqa, qh0, head_counter, group_counter - group, flags, tid);
       if (tid == 0) SGK_TP(7);
       return;
     }
@@ -592,7 +645,7 @@ __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s
     if (splits > 1 && flags[1]) {
       // this block completed its group: merge the group (or everything, if one group)
       const bool single = n_groups == 1;
-      merge_block<HD, NT>(a.part, a.splits, group_first, group_count, gqa, qh0, single, a.out, a.part2,
+      merge_block<HD, NT, PEERS>(a, a.part, a.splits, group_first, group_count, gqa, qh0, single, a.part2,
                       a.max_groups, group, tid);
       if (tid == 0) SGK_TP(6);
       if (!single) {
@@ -604,7 +657,7 @@ __device__ __forceinline__ void finish_block(const AttnArgs& a, const float* o_s
         }
         __syncthreads();
         if (flags[1]) {
-          merge_block<HD, NT>(a.part2, a.max_groups, 0, n_groups, gqa, qh0, true, a.out, a.part2,
+          merge_block<HD, NT, PEERS>(a, a.part2, a.max_groups, 0, n_groups, gqa, qh0, true, a.part2,
                           a.max_groups, 0, tid);
           if (tid == 0) SGK_TP(7);
         }

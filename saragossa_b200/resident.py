@@ -595,6 +595,14 @@ class Batch:
         check(self.L.sgk_batch_enqueue_step(self.h, stream, d_k.ptr, d_v.ptr, d_q.ptr, d_out.ptr, sliding_window,
                                             attn_scalar))
 
+    def enqueue_step_exchange(self, d_k, d_v, d_q, ex, local_row_ptr, peer_row_ptrs, slice_offset, sliding_window=0,
+                              attn_scalar=0.0, stream=None):
+        """enqueue_step whose launch also stores its outputs into the peers' rows and exchanges flags with
+        them (sgk_batch_enqueue_step_exchange)."""
+        rows = (C.c_void_p * ex.n_ranks)(*[None if p == ex.rank else int(peer_row_ptrs[p]) for p in range(ex.n_ranks)])
+        check(self.L.sgk_batch_enqueue_step_exchange(self.h, stream, d_k.ptr, d_v.ptr, d_q.ptr, ex.h, local_row_ptr, rows,
+                                                     slice_offset, sliding_window, attn_scalar))
+
     def enqueue_verify_rows(self, d_k, d_v, d_q, d_out, n_rows, sliding_window=0, attn_scalar=0.0, stream=None):
         """Speculative verify of n_rows draft rows for every sequence; inputs [n_rows][n_seq][...]."""
         check(self.L.sgk_batch_enqueue_verify_rows(self.h, stream, d_k.ptr, d_v.ptr, d_q.ptr, d_out.ptr, n_rows,

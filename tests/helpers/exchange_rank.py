@@ -58,6 +58,45 @@ def main(rank, n, d):
             for p in range(n):
                 want = np.arange(sl, dtype=np.float32) + 1000.0 * p + 10.0 * layer + 100000.0 * step
                 assert np.array_equal(got[layer, p], want), (step, layer, p)
+    # ---- the fused form: the attention launch itself stores into the peers' rows ----------------
+    qh, kvh, hd = 8, 2, 128                      # this rank's heads
+    kv_dim, q_dim = kvh * hd, qh * hd
+    assert n * q_dim <= row
+    for ctx in (40, 700, 9000):                  # one split; cluster-sized; shared merge
+        n_steps = 60 if ctx == 9000 else 24    # many exchanges: a store that overtook its flag would show as a stale slice
+        cap = ctx + n_steps + 16
+        pool = st.pool(1, kvh, hd, sg.KV_BF16, num_pages=2 * (cap // 16 + 2), max_seqs=2, max_seq_tokens=cap)
+        seqs = [pool.sequence(cap) for _ in range(2)]          # twin sequences: one decodes through the exchange
+        kvs = [sq.layer(0, qh) for sq in seqs]
+        d_k, d_v = st.alloc(4 * ctx * kv_dim), st.alloc(4 * ctx * kv_dim)
+        st.fill_normal(d_k, ctx * kv_dim, 60 + rank, 0)
+        st.fill_normal(d_v, ctx * kv_dim, 60 + rank, 1)
+        for kv in kvs:
+            kv.encode_append_rows(d_k, d_v, ctx)
+        st.sync()
+        b_ex, b_plain = sg.Batch(st, [kvs[0]]), sg.Batch(st, [kvs[1]])
+        d_kn, d_vn, d_q, d_o = st.alloc(4 * kv_dim), st.alloc(4 * kv_dim), st.alloc(4 * q_dim), st.alloc(4 * q_dim)
+        for step in range(n_steps):
+            st.fill_normal(d_kn, kv_dim, 70 + rank, 3 * step)
+            st.fill_normal(d_vn, kv_dim, 70 + rank, 3 * step + 1)
+            st.fill_normal(d_q, q_dim, 70 + rank, 3 * step + 2)
+            off = (step % 2) * layers * row          # row 0 of either set
+            peer_rows = [0 if p == rank else peers[p].ptr + 4 * off for p in range(n)]
+            b_ex.enqueue_step_exchange(d_kn, d_vn, d_q, ex, rows.ptr + 4 * off, peer_rows, rank * q_dim)
+            b_plain.enqueue_step(d_kn, d_vn, d_q, d_o)
+            st.sync()
+            assert st.device_status() == 0
+            own = d_o.download(np.float32, q_dim)
+            put(os.path.join(d, f"slice_{ctx}_{step}_{rank}"), own.tobytes())
+            got = rows.download(np.float32, 2 * layers * row)[off:off + n * q_dim].reshape(n, q_dim)
+            for p in range(n):
+                want = np.frombuffer(get(os.path.join(d, f"slice_{ctx}_{step}_{p}"), deadline), np.float32)
+                assert np.array_equal(got[p], want), (ctx, step, p)
+        b_ex.close()
+        b_plain.close()
+        for sq in seqs:
+            sq.close()
+        pool.close()
     # everybody done before anybody unmaps
     put(os.path.join(d, f"done{rank}"), b"1")
     for p in range(n):
