@@ -7,9 +7,11 @@ Two ways, both new design (the reference has no multi-GPU mode):
   (hash of the session root); no collective on the data path;
 * by KV-head group for one long sequence — rank g holds the pages of kv heads
   [g*KV/G, (g+1)*KV/G) and computes the Q/G query heads of those groups; the only
-  exchange is one all-gather of the attention outputs per layer.
-
-The collective is torch.distributed (NCCL on GPUs, gloo in the CPU tests).
+  exchange is the attention output row of a layer, which every rank needs whole. On GPUs
+  the attention launch itself stores its slice into the peers' rows and trades flags with
+  them (Batch.enqueue_step_exchange over memory mapped with peer_export / peer_open); an
+  all-gather of torch.distributed (NCCL; gloo in the CPU tests) does the same in a separate
+  call and is what the CPU tests of the split use.
 """
 from __future__ import annotations
 
