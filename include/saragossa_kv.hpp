@@ -14,6 +14,7 @@
 #include <cstring>
 #include <string>
 #include <utility>
+#include <array>
 #include <vector>
 
 #include "sgk.h"
@@ -223,6 +224,51 @@ class DecodeResidentState {
  private:
   static Result<Unit> unit(int32_t rc) { return rc == SGK_OK ? Result<Unit>::Ok(Unit{}) : Result<Unit>::Err(rc); }
   sgk_state* h_ = nullptr;
+};
+
+// One rank's end of the output exchange between GPUs that share one sequence by KV-head group
+// (sgk_exchange_*; the reference runs on one device and has no counterpart). handle() goes to the
+// peers over the host's own channel, connect() takes theirs.
+class OutputExchange {
+ public:
+  OutputExchange() = default;
+  OutputExchange(OutputExchange&& o) noexcept : h_(o.h_), handle_(o.handle_) { o.h_ = nullptr; }
+  OutputExchange& operator=(OutputExchange&& o) noexcept {
+    if (this != &o) {
+      if (h_) sgk_exchange_destroy(h_);
+      h_ = o.h_;
+      handle_ = o.handle_;
+      o.h_ = nullptr;
+    }
+    return *this;
+  }
+  OutputExchange(const OutputExchange&) = delete;
+  OutputExchange& operator=(const OutputExchange&) = delete;
+  ~OutputExchange() {
+    if (h_) sgk_exchange_destroy(h_);
+  }
+  static Result<OutputExchange> create(DecodeResidentState& state, int rank, int n_ranks) {
+    OutputExchange ex;
+    int32_t rc = sgk_exchange_create(state.handle(), rank, n_ranks, &ex.h_, ex.handle_.data());
+    if (rc != SGK_OK) return Result<OutputExchange>::Err(rc);
+    return Result<OutputExchange>::Ok(std::move(ex));
+  }
+  const std::array<uint8_t, 64>& handle() const { return handle_; }
+  Result<Unit> connect(int peer_rank, const std::array<uint8_t, 64>& peer_handle) {
+    return unit(sgk_exchange_connect(h_, peer_rank, peer_handle.data()));
+  }
+  // the exchange as a kernel of its own, after an attention launch that wrote the local slice
+  Result<Unit> encode(void* stream, float* d_local_row, float* const* d_peer_rows, size_t slice_offset,
+                      size_t slice_floats) {
+    return unit(sgk_exchange_enqueue(h_, stream, d_local_row, d_peer_rows, static_cast<int64_t>(slice_offset),
+                                     static_cast<int32_t>(slice_floats)));
+  }
+  sgk_exchange* raw() const { return h_; }
+
+ private:
+  static Result<Unit> unit(int32_t rc) { return rc == SGK_OK ? Result<Unit>::Ok(Unit{}) : Result<Unit>::Err(rc); }
+  sgk_exchange* h_ = nullptr;
+  std::array<uint8_t, 64> handle_{};
 };
 
 // LinearAttentionMetalState of all recurrent layers (src/metal_backend/mod.rs:507-531) with the
