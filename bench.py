@@ -448,18 +448,36 @@ def head_sharded_run(sg, st, torch, dist, world, rank, stream, sh, pool, seq, ba
     out_full = torch.zeros(LAYERS, world * q_loc, device=dev)
     torch.cuda.synchronize()
 
-    # the rows of the direct exchange: [layer][world * q_loc] in memory the peers map
+    # the rows of the direct exchange: [layer][world * q_loc] in memory the peers map. Mapping may fail
+    # on one rank only (no IPC between these processes): the ranks agree after every local stage.
     row = world * q_loc
-    rows = st.alloc(4 * LAYERS * row)
-    rows.upload(np.zeros(LAYERS * row, np.float32))
-    ex = st.exchange(rank, world)
-    handles = [None] * world
-    dist.all_gather_object(handles, (st.peer_export(rows), ex.handle))
-    peer_rows = {}
-    for p in range(world):
-        if p != rank:
-            peer_rows[p] = st.peer_open(handles[p][0])
-            ex.connect(p, handles[p][1])
+
+    def agreed(ok):
+        flag = torch.tensor([1 if ok else 0], device=dev, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        return int(flag.item()) == 1
+
+    rows = ex = None
+    peer_rows, peer_error, mine = {}, None, None
+    try:
+        rows = st.alloc(4 * LAYERS * row)
+        rows.upload(np.zeros(LAYERS * row, np.float32))
+        ex = st.exchange(rank, world)
+        mine = (st.peer_export(rows), ex.handle)
+    except Exception as exc:  # noqa: BLE001
+        peer_error = f"{type(exc).__name__}: {exc}"[:200]
+    peers_ok = agreed(peer_error is None)
+    if peers_ok:
+        handles = [None] * world
+        dist.all_gather_object(handles, mine)
+        try:
+            for p in range(world):
+                if p != rank:
+                    peer_rows[p] = st.peer_open(handles[p][0])
+                    ex.connect(p, handles[p][1])
+        except Exception as exc:  # noqa: BLE001
+            peer_error = f"{type(exc).__name__}: {exc}"[:200]
+        peers_ok = agreed(peer_error is None)
 
     class _At:
         def __init__(self, ptr):
@@ -491,7 +509,8 @@ def head_sharded_run(sg, st, torch, dist, world, rank, stream, sh, pool, seq, ba
     # will append into are reserved before the capture (a replay moves only the device cursor).
     seq.reserve(((CTX + 3 * steps + 24 + 15) // 16) * 16)
     result = {}
-    for name, one_step in (("nccl", step_nccl), ("direct", step_direct), ("fused", step_fused)):
+    modes = [("nccl", step_nccl)] + ([("direct", step_direct), ("fused", step_fused)] if peers_ok else [])
+    for name, one_step in modes:
         mode = "graph"
         with torch.cuda.stream(stream):
             one_step()
@@ -518,20 +537,30 @@ def head_sharded_run(sg, st, torch, dist, world, rank, stream, sh, pool, seq, ba
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         result[name] = (float(t.item()), mode)
     finite = bool(torch.isfinite(out_full).all().item())
-    direct_rows = rows.download(np.float32, LAYERS * row).reshape(LAYERS, world, q_loc)
-    # every slice of the last token arrived: no slice of any layer is still the initial zero row
-    direct_complete = bool(np.isfinite(direct_rows).all() and (np.abs(direct_rows).max(axis=2) > 0).all())
+    direct_complete = None
+    if peers_ok:
+        direct_rows = rows.download(np.float32, LAYERS * row).reshape(LAYERS, world, q_loc)
+        # every slice of the last token arrived: no slice of any layer is still the initial zero row
+        direct_complete = bool(np.isfinite(direct_rows).all() and (np.abs(direct_rows).max(axis=2) > 0).all())
     status = st.device_status()
     dist.barrier()
     for p in peer_rows.values():
         st.peer_close(p)
-    ex.close()
+    if ex is not None:
+        ex.close()
     for b in batches:
         b.close()
     seq.close()
     pool.close()
     total_bytes = sum(algorithmic_bytes(CTX + 2 + i + 1) for i in range(steps)) * LAYERS
     ms, mode = result["nccl"]
+    nccl = {"us_per_layer": ms * 1e3 / (steps * LAYERS), "submission": mode,
+            "exchange": f"one NCCL all-gather of {world * q_loc * 4} bytes per layer"}
+    if not peers_ok:
+        return {"us_per_layer": nccl["us_per_layer"], "hbm_gbs_aggregate": total_bytes / (ms * 1e-3) / 1e9, "ranks": world,
+                "kv_heads_per_rank": sh.kv_heads, "steps": steps, "outputs_finite": finite, "device_status": status,
+                "submission": mode, "exchange": nccl["exchange"],
+                "peer_memory_unavailable": peer_error or "on another rank"}
     ms_d, mode_d = result["direct"]
     ms_f, mode_f = result["fused"]
     return {"us_per_layer": ms_f * 1e3 / (steps * LAYERS), "hbm_gbs_aggregate": total_bytes / (ms_f * 1e-3) / 1e9,
@@ -541,8 +570,7 @@ def head_sharded_run(sg, st, torch, dist, world, rank, stream, sh, pool, seq, ba
                         "peer's row over NVLink; the last block raises the flags and waits (bounded) for the peers'",
             "with_exchange_kernel": {"us_per_layer": ms_d * 1e3 / (steps * LAYERS), "submission": mode_d,
                                      "exchange": "attention launch, then one small kernel per layer: slice stored to the peers, flag, bounded wait"},
-            "with_nccl_all_gather": {"us_per_layer": ms * 1e3 / (steps * LAYERS), "submission": mode,
-                                     "exchange": f"one NCCL all-gather of {world * q_loc * 4} bytes per layer"}}
+            "with_nccl_all_gather": nccl}
 
 
 def gated_delta_leg(sg, st, torch, stream):
