@@ -67,6 +67,16 @@ int32_t sgk_state_sync(sgk_state* state);
 /* Reads and clears the device status word kernels set when a bounded wait expires. */
 int32_t sgk_state_device_status(sgk_state* state, int32_t* status_out);
 
+/* Streams. By default the caller promises what the reference does anyway (one decode thread, one
+ * command queue per device, src/decode_resident/arena.rs:247-349): launches enqueued through one
+ * state never run on two streams at the same time. Launches whose blocks wait for one another (the
+ * shared merge of a long single sequence) then go as ordinary launches, placed in stream order,
+ * and the launches of one decode token may overlap their neighbours (sgk_step_*). A caller that
+ * does run two streams of one state at once says so here (enabled = 1): such launches then become
+ * cooperative launches, which the driver places all at once or not at all, at about 2 us more per
+ * launch. Set before the first enqueue; a captured step keeps the mode it was captured in. */
+int32_t sgk_state_set_concurrent_streams(sgk_state* state, int32_t enabled);
+
 /* Failure-detection self test: launches a kernel whose only wait (on an mbarrier nobody
  * completes) must expire. Returns SGK_ERR_TIMEOUT when the bounded wait reported through the
  * status word as designed; the device and the state stay usable. */

@@ -93,6 +93,12 @@ static int check_device_status(State* st) {
   return fail(SGK_ERR_BACKEND, "kernel reported status %d (block-table entry out of range)", status);
 }
 
+int32_t sgk_state_set_concurrent_streams(sgk_state* st, int32_t enabled) {
+  if (!st) return fail(SGK_ERR_BACKEND, "null state");
+  st->concurrent_streams = enabled != 0;
+  return SGK_OK;
+}
+
 int32_t sgk_state_selftest_wait_timeout(sgk_state* st) {
   if (!st) return fail(SGK_ERR_BACKEND, "null state");
   SGK_CUDA(launch_wait_timeout_selftest(st->d_status, st->stream));

@@ -52,6 +52,10 @@ struct State {
   int32_t* d_status = nullptr;
   unsigned long long* d_lm_ws = nullptr;  // lm_head argmax: [0..8) best key per row, [8] blocks-done counter; zero between launches
   int64_t launches = 0;  // kernels launched through this state
+  // false (default): the caller never has two launches of this state in flight on different
+  // streams at once, so launches whose blocks wait for each other go as ordinary launches;
+  // true: they go as cooperative launches (sgk_state_set_concurrent_streams)
+  bool concurrent_streams = false;
   cudaStream_t pick(void* s) const { return s ? static_cast<cudaStream_t>(s) : stream; }
 };
 
@@ -162,8 +166,19 @@ struct Batch {
   int choose_splits(int kernel, int64_t max_rows) const;
   int enqueue_append(cudaStream_t stream, const float* d_k, const float* d_v, int n_rows, const RopeArgs* rope,
                      const float* knorm_w);
+  // chain: the launches of one decode token, layer after layer. A launch FOLLOWS the chain when the
+  // launch enqueued just before it on the stream is the attention launch of another layer (nothing
+  // that launch writes is read by this one before its q / k_new / v_new): prev_other_layer says so of
+  // the previous enqueue, and the state's launch count must still be what it was right after that
+  // launch (a copy-on-write or a table update in between would have moved it).
+  struct Chain {
+    bool in_chain = false;
+    bool prev_other_layer = false;
+    int64_t launches_after_prev = -1;
+  };
   int enqueue_attention(cudaStream_t stream, const float* d_q, float* d_out, int64_t window_start,
-                        int64_t sliding_window, float attn_scalar, const float* d_k_new, const float* d_v_new);
+                        int64_t sliding_window, float attn_scalar, const float* d_k_new, const float* d_v_new,
+                        const Chain* chain = nullptr);
   ~Batch();
 };
 

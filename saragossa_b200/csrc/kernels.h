@@ -48,6 +48,7 @@ struct AttnArgs {
   int64_t window_start;     // explicit start row when sliding_window == 0
   int64_t sliding_window;   // > 0: start = max(len - window, 0)
   int32_t shared_merge;     // 1: every block of a (sequence, KV head) merges a slice once all have arrived
+                            //    (a cooperative launch); 2: the same as an ordinary launch
   int32_t cluster_merge;    // 1: the splits of a (sequence, KV head) are one thread-block cluster and merge through
                             //    distributed shared memory (2..16 splits)
   // Several GPUs share the sequence by KV-head group (n_peers > 0): final output cells also go to
@@ -80,8 +81,14 @@ struct AttnArgs {
   const float* k_new;  // [n_seq][kv_dim] or NULL
   const float* v_new;
   int32_t n_stages;
+  // Launches of one decode token that follow each other on a stream (layer after layer):
+  int32_t pdl_trigger;      // 1: lets the next launch of the stream start before this one has finished
+  int32_t pdl_wait;         // 1: launched with programmatic stream serialisation: the block reads its cursor and
+                            //    block table and starts its first copies at once, and waits for the previous
+                            //    launch before it touches q, k_new, v_new or writes anything
 #ifdef SGK_TRACE
   unsigned long long* trace;  // [blocks][16] timestamps, debugging builds only
+  int32_t trace_gt;           // 1: the points record the global timer (ns) instead of the SM's cycle counter
 #endif
 };
 

@@ -85,6 +85,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
   const int slot = a.slots ? a.slots[seq] : a.slot0;
   int32_t* len_ptr = a.pool.lens + int64_t(slot) * a.pool.layers + a.layer;
   const bool do_append = a.k_new != nullptr;
+  if (a.pdl_trigger) pdl_launch_dependents();
 #ifdef SGK_TRACE
   if (a.trace && tid == 0) {
     unsigned long long gt;
@@ -140,6 +141,10 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
     // All loads are issued before the first conversion.
     constexpr int NV = HD / 64;  // float4 per consumer thread
     const float* q = a.q + (int64_t(seq) * a.q_heads + int64_t(kvh) * gqa) * HD;
+    // q and the row to append come from the launch before this one; the cursor, the block table and
+    // the pages the producer has started to copy do not
+    if (a.pdl_wait) pdl_wait();
+    if (tid == 0) SGK_TP(8);
     float4 v[NV];
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
@@ -149,26 +154,29 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
     // The row of a fused append is converted here, with the same round trip as Q, and waits in
     // shared memory for its page: read where it is stored, it would pay that latency at the very
     // end of the block that every other block of the sequence waits for.
-    if (owns_append) {
-      if (tid * 4 < 2 * HD) {
-        const int64_t row_off = int64_t(seq) * a.pool.kv_heads * HD + kvh * HD;
-        const bool is_k = tid * 4 < HD;
-        const int dim = is_k ? tid * 4 : tid * 4 - HD;
-        const float* src = is_k ? a.k_new + row_off + dim : a.v_new + row_off + dim;
-        const int32_t page = table[append_page_index];   // issued with the row's load: one round trip for both
-        const float4 x = __ldg(reinterpret_cast<const float4*>(src));
-        const uint2 packed = make_uint2(uint32_t(f32_to_bf16_bits(x.x)) | (uint32_t(f32_to_bf16_bits(x.y)) << 16),
-                                        uint32_t(f32_to_bf16_bits(x.z)) | (uint32_t(f32_to_bf16_bits(x.w)) << 16));
-        *reinterpret_cast<uint2*>(new_s + tid * 2) = packed;
-        // The row goes to its page in global memory now: whatever the bulk copy of that page sees of
-        // it, the staged copy gets the row again from shared memory; and a store issued here has long
-        // been performed when the block's tail asks for its writes to be visible. A page id outside the
-        // pool is reported by the producer, which meets the same table entry.
-        if (page >= 0 && page < a.num_pages) {
-          const int rin = static_cast<int>(len_old % PAGE_TOKENS);
-          uint8_t* tile = a.pool.base + int64_t(page) * a.pool.page_bytes + head_off + (is_k ? 0 : S::TILE);
-          *reinterpret_cast<uint2*>(tile + bf16_elem_index(rin, dim, HD) * 2) = packed;
-        }
+    const bool loads_row = owns_append && tid * 4 < 2 * HD;
+    const bool is_k = tid * 4 < HD;
+    const int dim = is_k ? tid * 4 : tid * 4 - HD;
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    int32_t page = -1;
+    if (loads_row) {
+      const int64_t row_off = int64_t(seq) * a.pool.kv_heads * HD + kvh * HD;
+      const float* src = is_k ? a.k_new + row_off + dim : a.v_new + row_off + dim;
+      page = table[append_page_index];   // issued with the row's load: one round trip for both
+      x = __ldg(reinterpret_cast<const float4*>(src));
+    }
+    if (loads_row) {
+      const uint2 packed = make_uint2(uint32_t(f32_to_bf16_bits(x.x)) | (uint32_t(f32_to_bf16_bits(x.y)) << 16),
+                                      uint32_t(f32_to_bf16_bits(x.z)) | (uint32_t(f32_to_bf16_bits(x.w)) << 16));
+      *reinterpret_cast<uint2*>(new_s + tid * 2) = packed;
+      // The row goes to its page in global memory now: whatever the bulk copy of that page sees of
+      // it, the staged copy gets the row again from shared memory; and a store issued here has long
+      // been performed when the block's tail asks for its writes to be visible. A page id outside the
+      // pool is reported by the producer, which meets the same table entry.
+      if (page >= 0 && page < a.num_pages) {
+        const int rin = static_cast<int>(len_old % PAGE_TOKENS);
+        uint8_t* tile = a.pool.base + int64_t(page) * a.pool.page_bytes + head_off + (is_k ? 0 : S::TILE);
+        *reinterpret_cast<uint2*>(tile + bf16_elem_index(rin, dim, HD) * 2) = packed;
       }
     }
 #pragma unroll
@@ -195,6 +203,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
   if (warp == MMA_CONSUMERS) {
     // ---------------- producer warp ----------------
     produce_pages<S::STAGE>(a, table, pb, my_pages, first_entry, ring, bars, nst, head_off, abort_flag, lane);
+    if (a.pdl_wait) pdl_wait();   // the tail writes to memory the earlier launch may still be using
     SGK_TP(12);
   } else {
     // ---------------- consumer warps ----------------
@@ -396,6 +405,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_mma_kernel(AttnArgs 
 
   finish_block<HD, CLUSTER, PEERS>(a, o_s, ml_s, S::OPAD, flags, seq, kvh, split, gqa, do_append, len_ptr, len, tid,
                                    splits, recv_s);
+  if (tid == 0) SGK_TP(10);
   if (PEERS) peers_finish(a, tid, flags);
 }
 
@@ -492,19 +502,29 @@ static cudaError_t launch_one(void (*kernel)(AttnArgs), dim3 grid, size_t smem, 
   cfg.blockDim = dim3(MMA_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  int n_attr = 0;
   if (a.cluster_merge) {
     // the splits of a (sequence, KV head) are the x extent of the grid and of the cluster
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = grid.x;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-  } else {
-    attr[0].id = cudaLaunchAttributeCooperative;
-    attr[0].val.cooperative = 1;
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = grid.x;
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = 1;
+    n_attr += 1;
+  } else if (a.shared_merge == 1) {
+    attr[n_attr].id = cudaLaunchAttributeCooperative;
+    attr[n_attr].val.cooperative = 1;
+    n_attr += 1;
+  }
+  if (a.pdl_wait) {
+    // may start while the launch before it in the stream still runs; the kernel waits for that
+    // launch itself, after its first copies are on their way
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    n_attr += 1;
   }
   cfg.attrs = attr;
-  cfg.numAttrs = (a.shared_merge || a.cluster_merge) ? 1 : 0;
+  cfg.numAttrs = n_attr;
   return cudaLaunchKernelEx(&cfg, kernel, a);
 }
 

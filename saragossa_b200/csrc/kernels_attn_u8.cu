@@ -177,6 +177,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
   const int slot = a.slots ? a.slots[seq] : a.slot0;
   int32_t* len_ptr = a.pool.lens + int64_t(slot) * a.pool.layers + a.layer;
   const bool do_append = a.k_new != nullptr;
+  if (a.pdl_trigger) pdl_launch_dependents();
 
   const int64_t len_old = *reinterpret_cast<const volatile int32_t*>(len_ptr);
   const int64_t len = len_old + (do_append ? 1 : 0);
@@ -204,11 +205,13 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
   const float* vn = new_s + HD;
 
   int32_t first_entry = -1;
-  float smax = __uint_as_float(*reinterpret_cast<const volatile uint32_t*>(a.pool.scale_max));
+  float smax = 0.0f;
+  uint32_t smax_pool = 0;   // the pool's largest scale (f32 bits) as this launch found it
   if (warp == MMA_CONSUMERS) {
     if (lane == 0) {
       flags[0] = 0;
       flags[1] = 0;
+      flags[5] = 0;   // set once the quantised row of a fused append is parked in shared memory
       for (int s = 0; s < nst; ++s) {
         mbar_init(smem_u32(bars + s), 1);
         mbar_init(smem_u32(bars + MMA_MAX_STAGES + s), 1);
@@ -222,6 +225,12 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
     // would put an error of |logit| * 2^-12 on every logit, too much for rows with a large range.
     constexpr int NV = HD / 64;
     const float* q = a.q + (int64_t(seq) * a.q_heads + int64_t(kvh) * gqa) * HD;
+    // q, the row to append and the pool's largest scale come from the launch before this one; the
+    // cursor, the block table and the pages the producer has started to copy do not
+    if (a.pdl_wait) pdl_wait();
+    if (tid == 0) SGK_TP(8);
+    smax_pool = *reinterpret_cast<const volatile uint32_t*>(a.pool.scale_max);
+    smax = __uint_as_float(smax_pool);
     float4 v[NV];
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
@@ -230,10 +239,16 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
     }
     // The row of a fused append comes into shared memory with the same round trip as Q: read
     // where it is quantised, element by element, each read would pay the latency again.
-    if (owns_append && tid * 4 < 2 * HD) {
+    const bool loads_row = owns_append && tid * 4 < 2 * HD;
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    int32_t append_page = -1;
+    if (loads_row) {
       const int64_t row_off = int64_t(seq) * a.pool.kv_heads * HD + kvh * HD;
       const float* src = tid * 4 < HD ? a.k_new + row_off + tid * 4 : a.v_new + row_off + (tid * 4 - HD);
-      const float4 x = __ldg(reinterpret_cast<const float4*>(src));
+      x = __ldg(reinterpret_cast<const float4*>(src));
+    }
+    if (owns_append && tid == 0) append_page = table[append_page_index];
+    if (loads_row) {
       *reinterpret_cast<float4*>(new_s + tid * 4) = x;
       // bound of the scales the row will get: (max - min) / 255 <= 2 max|x| / 255
       float big = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
@@ -241,7 +256,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
       for (int off = 16; off > 0; off >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, off));
       if (lane == 0) new_big[warp] = big;
     }
-    if (owns_append && tid == 0) flags[2] = table[append_page_index];
+    if (owns_append && tid == 0) flags[2] = append_page;
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int f = (tid + k * MMA_CONSUMERS * 32) * 4;
@@ -301,9 +316,67 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
   }
   if (tid == 0) SGK_TP(1);
 
+  // The row of a fused append is quantised now, by the consumer warp with the fewest pages, while the
+  // first pages are still on their way: codes and metadata go to the row's page in global memory at
+  // once and are parked in shared memory (over the f32 row, which nothing reads any more) for the
+  // warp that will meet the page in the ring. Done where the page is consumed, at the very end of
+  // the block every other block of the sequence waits for, the quantiser's divides and its stores
+  // delayed the whole launch.
+  uint8_t* park = reinterpret_cast<uint8_t*>(new_s);   // [K codes HD | V codes HD | meta 2G x u32]
+  if (owns_append && warp == MMA_CONSUMERS - 1) {
+    const int rin = static_cast<int>(len_old % PAGE_TOKENS);
+    const int32_t page = flags[2];
+    float x[2 * G];
+    uint32_t code[2 * G], meta[2 * G];
+#pragma unroll
+    for (int grp = 0; grp < G; ++grp) {
+      x[grp] = kn[grp * QGROUP + lane];
+      x[G + grp] = vn[grp * QGROUP + lane];
+    }
+    __syncwarp();
+    quantize_groups<2 * G>(x, code, meta);
+    uint32_t biggest = 0;
+    const bool page_ok = page >= 0 && page < a.num_pages;   // a bad entry is reported by the producer, which meets it too
+    uint8_t* gk = a.pool.base + int64_t(page_ok ? page : 0) * a.pool.page_bytes + head_off;
+    uint8_t* gv = gk + S::TILE;
+#pragma unroll
+    for (int grp = 0; grp < G; ++grp) {
+      const int dim = grp * QGROUP + lane;
+      park[dim] = static_cast<uint8_t>(code[grp]);
+      park[HD + dim] = static_cast<uint8_t>(code[G + grp]);
+      if (page_ok) {
+        gk[u8_k_code_index(rin, dim, HD)] = static_cast<uint8_t>(code[grp]);
+        gv[u8_v_code_index(rin, dim, HD)] = static_cast<uint8_t>(code[G + grp]);
+      }
+      biggest = max(biggest, max((meta[grp] & 0xffffu) << 16, (meta[G + grp] & 0xffffu) << 16));
+    }
+    // lane grp writes the metadata of group grp (every lane holds every group's)
+#pragma unroll
+    for (int grp = 0; grp < G; ++grp) {
+      if (lane == grp) {
+        const uint32_t mk = meta[grp], mv = meta[G + grp];
+        reinterpret_cast<uint32_t*>(park + 2 * HD)[grp] = mk;
+        reinterpret_cast<uint32_t*>(park + 2 * HD)[G + grp] = mv;
+        if (page_ok) {
+          *reinterpret_cast<uint16_t*>(gk + u8_scale_offset(rin, grp, HD)) = static_cast<uint16_t>(mk & 0xffffu);
+          *reinterpret_cast<uint16_t*>(gk + u8_bias_offset(0, rin, grp, HD)) = static_cast<uint16_t>(mk >> 16);
+          *reinterpret_cast<uint16_t*>(gv + u8_scale_offset(rin, grp, HD)) = static_cast<uint16_t>(mv & 0xffffu);
+          *reinterpret_cast<uint16_t*>(gv + u8_bias_offset(1, rin, grp, HD)) = static_cast<uint16_t>(mv >> 16);
+        }
+      }
+    }
+    if (lane == 0 && page_ok && biggest > smax_pool) atomicMax(a.pool.scale_max, biggest);
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence_block();
+      *reinterpret_cast<volatile int*>(flags + 5) = 1;
+    }
+  }
+
   if (warp == MMA_CONSUMERS) {
     // ---------------- producer warp ----------------
     produce_pages<S::STAGE>(a, table, pb, my_pages, first_entry, ring, bars, nst, head_off, abort_flag, lane);
+    if (a.pdl_wait) pdl_wait();   // the tail writes to memory the earlier launch may still be using
     SGK_TP(12);
   } else {
     // ---------------- consumer warps ----------------
@@ -346,52 +419,30 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
       const int64_t row_base = page_index * PAGE_TOKENS;
 
       if (ok && owns_append && page_index == append_page_index) {
-        // Quantise the new row; store codes and metadata to its page and to the staged copy.
+        // The new row (quantised in the prologue, already on its way to the page) joins the staged copy.
         const int rin = static_cast<int>(len_old % PAGE_TOKENS);
-        const int32_t page = flags[2];
-        if (page >= 0 && page < a.num_pages) {
-          uint8_t* gk = a.pool.base + int64_t(page) * a.pool.page_bytes + head_off;
-          uint8_t* gv = gk + S::TILE;
-          float x[2 * G];
-          uint32_t code[2 * G], meta[2 * G];
-#pragma unroll
-          for (int grp = 0; grp < G; ++grp) {
-            x[grp] = kn[grp * QGROUP + lane];
-            x[G + grp] = vn[grp * QGROUP + lane];
+        uint32_t spins = 0;
+        while (*reinterpret_cast<volatile int*>(flags + 5) == 0) {
+          if (++spins > WAIT_SPINS) {
+            *abort_flag = 1;
+            atomicExch(a.status, DEV_ERR_WAIT_TIMEOUT);
+            break;
           }
-          quantize_groups<2 * G>(x, code, meta);
-          uint32_t biggest = 0;
+        }
+        __syncwarp();
 #pragma unroll
-          for (int grp = 0; grp < G; ++grp) {
-            const int dim = grp * QGROUP + lane;
-            const int ik = u8_k_code_index(rin, dim, HD), iv = u8_v_code_index(rin, dim, HD);
-            gk[ik] = static_cast<uint8_t>(code[grp]);
-            ktile[ik] = static_cast<uint8_t>(code[grp]);
-            gv[iv] = static_cast<uint8_t>(code[G + grp]);
-            vtile[iv] = static_cast<uint8_t>(code[G + grp]);
-            biggest = max(biggest, max((meta[grp] & 0xffffu) << 16, (meta[G + grp] & 0xffffu) << 16));
-          }
-          // lane grp writes the metadata of group grp (every lane holds every group's)
-#pragma unroll
-          for (int grp = 0; grp < G; ++grp) {
-            if (lane == grp) {
-              const uint32_t mk = meta[grp], mv = meta[G + grp];
-              const int so = u8_scale_offset(rin, grp, HD);
-              const int kbo = u8_bias_offset(0, rin, grp, HD), vbo = u8_bias_offset(1, rin, grp, HD);
-              const uint16_t ks = static_cast<uint16_t>(mk & 0xffffu), kbias = static_cast<uint16_t>(mk >> 16);
-              const uint16_t vs = static_cast<uint16_t>(mv & 0xffffu), vbias = static_cast<uint16_t>(mv >> 16);
-              *reinterpret_cast<uint16_t*>(gk + so) = ks;
-              *reinterpret_cast<uint16_t*>(ktile + so) = ks;
-              *reinterpret_cast<uint16_t*>(gk + kbo) = kbias;
-              *reinterpret_cast<uint16_t*>(ktile + kbo) = kbias;
-              *reinterpret_cast<uint16_t*>(gv + so) = vs;
-              *reinterpret_cast<uint16_t*>(vtile + so) = vs;
-              *reinterpret_cast<uint16_t*>(gv + vbo) = vbias;
-              *reinterpret_cast<uint16_t*>(vtile + vbo) = vbias;
-            }
-          }
-          if (lane == 0 && biggest > *reinterpret_cast<volatile uint32_t*>(a.pool.scale_max))
-            atomicMax(a.pool.scale_max, biggest);
+        for (int grp = 0; grp < G; ++grp) {
+          const int dim = grp * QGROUP + lane;
+          ktile[u8_k_code_index(rin, dim, HD)] = park[dim];
+          vtile[u8_v_code_index(rin, dim, HD)] = park[HD + dim];
+        }
+        if (lane < G) {
+          const uint32_t mk = reinterpret_cast<const uint32_t*>(park + 2 * HD)[lane];
+          const uint32_t mv = reinterpret_cast<const uint32_t*>(park + 2 * HD)[G + lane];
+          *reinterpret_cast<uint16_t*>(ktile + u8_scale_offset(rin, lane, HD)) = static_cast<uint16_t>(mk & 0xffffu);
+          *reinterpret_cast<uint16_t*>(ktile + u8_bias_offset(0, rin, lane, HD)) = static_cast<uint16_t>(mk >> 16);
+          *reinterpret_cast<uint16_t*>(vtile + u8_scale_offset(rin, lane, HD)) = static_cast<uint16_t>(mv & 0xffffu);
+          *reinterpret_cast<uint16_t*>(vtile + u8_bias_offset(1, rin, lane, HD)) = static_cast<uint16_t>(mv >> 16);
         }
         __syncwarp();
       }
@@ -595,6 +646,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 2) attention_u8_kernel(AttnArgs a
   __syncthreads();
   finish_block<HD, CLUSTER, PEERS>(a, o_s, ml_s, S::OPAD, flags, seq, kvh, split, gqa, do_append, len_ptr, len, tid,
                                    splits, recv_s);
+  if (tid == 0) SGK_TP(10);
   if (PEERS) peers_finish(a, tid, flags);
 }
 
@@ -668,19 +720,29 @@ static cudaError_t launch_one(void (*kernel)(AttnArgs), dim3 grid, size_t smem, 
   cfg.blockDim = dim3(MMA_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  int n_attr = 0;
   if (a.cluster_merge) {
     // the splits of a (sequence, KV head) are the x extent of the grid and of the cluster
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = grid.x;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-  } else {
-    attr[0].id = cudaLaunchAttributeCooperative;
-    attr[0].val.cooperative = 1;
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = grid.x;
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = 1;
+    n_attr += 1;
+  } else if (a.shared_merge == 1) {
+    attr[n_attr].id = cudaLaunchAttributeCooperative;
+    attr[n_attr].val.cooperative = 1;
+    n_attr += 1;
+  }
+  if (a.pdl_wait) {
+    // may start while the launch before it in the stream still runs; the kernel waits for that
+    // launch itself, after its first copies are on their way
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    n_attr += 1;
   }
   cfg.attrs = attr;
-  cfg.numAttrs = (a.shared_merge || a.cluster_merge) ? 1 : 0;
+  cfg.numAttrs = n_attr;
   return cudaLaunchKernelEx(&cfg, kernel, a);
 }
 

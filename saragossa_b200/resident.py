@@ -241,6 +241,10 @@ class DecodeResidentState:
         check(self.L.sgk_state_device_status(self.h, C.byref(s)))
         return s.value
 
+    def set_concurrent_streams(self, enabled: bool):
+        """Says that launches of this state may run on two streams at once (default: they do not)."""
+        check(self.L.sgk_state_set_concurrent_streams(self.h, 1 if enabled else 0))
+
     def selftest_wait_timeout(self):
         """Runs the kernel whose wait must expire; raises InferError(kind='Timeout') when it did."""
         check(self.L.sgk_state_selftest_wait_timeout(self.h))

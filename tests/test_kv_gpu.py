@@ -605,6 +605,80 @@ def test_graph_replay_is_one_submission_and_matches_stream_mode(state):
     assert np.array_equal(outs[0][1], outs[1][1])
 
 
+class _Off:
+    """A device buffer seen from a byte offset."""
+
+    def __init__(self, buf, offset):
+        self.ptr = buf.ptr + offset
+
+
+@pytest.mark.parametrize("dtype", [sg.KV_BF16, sg.KV_U8G32])
+@pytest.mark.parametrize("concurrent", [False, True])
+def test_token_chain_of_a_long_sequence_equals_solo_launches(dtype, concurrent):
+    """The launches of one decode token over a long single sequence overlap their neighbours
+    (programmatic dependent launch: a layer's blocks read their cursor and block table and start
+    their page copies while the previous layer still runs) and merge their many splits by waiting
+    for one another. Each layer's output and appended row must be what the same launch gives alone,
+    bit for bit, in stream mode and as graph replays, with ordinary and with cooperative launches."""
+    q_heads, kv_heads, hd, layers, n, tokens = 32, 4, 128, 4, 8200, 3
+    kv_dim, q_dim = kv_heads * hd, q_heads * hd
+    st = sg.DecodeResidentState(0)
+    st.set_concurrent_streams(concurrent)
+    results = {}
+    for mode in ("solo", "stream", "graph"):
+        pool = st.pool(layers, kv_heads, hd, dtype, num_pages=(n + 64) // 16 + 2, max_seqs=1, max_seq_tokens=n + 64)
+        pool.shuffle_free_list(5)
+        seq = pool.sequence(n + 64)
+        kvs = [seq.layer(layer, q_heads) for layer in range(layers)]
+        for layer, kv in enumerate(kvs):
+            kv.seed(_normal_kv(n, kv_dim, 21, 2 * layer), _normal_kv(n, kv_dim, 21, 2 * layer + 1), n)
+        d_k, d_v = st.alloc(layers * kv_dim * 4), st.alloc(layers * kv_dim * 4)
+        d_q, d_out = st.alloc(layers * q_dim * 4), st.alloc(layers * q_dim * 4)
+        batches = [sg.Batch(st, [kv]) for kv in kvs]
+        step = sg.Step(st, batches)
+        if mode == "graph":
+            step.capture(d_k, d_v, d_q, d_out)
+        got = []
+        for t in range(tokens):
+            d_k.upload(sgo.fill_normal8(layers * kv_dim, 22, 3 * t))
+            d_v.upload(sgo.fill_normal8(layers * kv_dim, 22, 3 * t + 1))
+            d_q.upload(sgo.fill_normal8(layers * q_dim, 22, 3 * t + 2))
+            if mode == "graph":
+                step.replay()
+            elif mode == "stream":
+                step.enqueue(d_k, d_v, d_q, d_out)
+            else:
+                for layer, kv in enumerate(kvs):
+                    kv.encode_append_attention(_Off(d_k, layer * kv_dim * 4), _Off(d_v, layer * kv_dim * 4),
+                                               _Off(d_q, layer * q_dim * 4), _Off(d_out, layer * q_dim * 4))
+            st.sync()
+            got.append(d_out.download())
+        assert batches[0].last_splits() > 12 or mode == "solo"     # the merge in which blocks wait for each other
+        assert all(kv.len() == n + tokens for kv in kvs)
+        tail = [kv.gather_rows_f32(n - 2, tokens + 2) for kv in kvs]
+        results[mode] = (np.stack(got), tail)
+        assert st.device_status() == 0
+        step.close()
+        for b in batches:
+            b.close()
+        seq.close()
+        pool.close()
+    for mode in ("stream", "graph"):
+        assert np.array_equal(results["solo"][0], results[mode][0]), mode
+        for a, b in zip(results["solo"][1], results[mode][1]):
+            assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1]), mode
+    # and the first token against the CPU restatement of the reference path (layer 0)
+    ref = sgo.ResidentKv(n + 8, q_heads, kv_heads, hd, sgo.KV_BF16 if dtype == sg.KV_BF16 else sgo.KV_F32)
+    k0, v0 = _normal_kv(n, kv_dim, 21, 0), _normal_kv(n, kv_dim, 21, 1)
+    if dtype == sg.KV_BF16:
+        assert ref.seed(k0, v0, n) == sgo.OK
+        assert ref.append_row(sgo.fill_normal8(layers * kv_dim, 22, 0)[:kv_dim], sgo.fill_normal8(layers * kv_dim, 22, 1)[:kv_dim]) == sgo.OK
+        _, want = ref.attention(sgo.fill_normal8(layers * q_dim, 22, 2)[:q_dim], threads=4)
+        err = np.abs(results["graph"][0][0][:q_dim] - want)
+        assert np.all(err <= 2e-2 * np.abs(want) + 1e-3)
+    st.close()
+
+
 def test_sliding_window_release_keeps_results(state):
     """Pages wholly before the window go back to the pool; the answer is unchanged because
     rows before window_start are never read (src/decoder/attention_ops.rs:915-920)."""
