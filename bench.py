@@ -39,9 +39,24 @@ CTX, BATCH = 32768, 8
 KV_DIM, Q_DIM = KV_HEADS * HEAD_DIM, Q_HEADS * HEAD_DIM
 WORKLOAD = ("C2: Qwen3-30B-A3B-shaped KV path, 48 layers, 32Q/4KV heads, head_dim 128, bf16 KV, "
             "16-token pages, shuffled block table, ctx 32768, batch 8 per GPU")
-# ncu capture of attention_mma_kernel<128, false> at this shape (summary kept under profiles/):
-# DRAM read+write bytes per launch divided by the algorithmic bytes of the launch.
-NCU_TRAFFIC_RATIO = 1.0097
+
+
+def workload_config():
+    """The `config` both arms print (the reference arm times a bounded sample of the same workload)."""
+    return {"workload": WORKLOAD, "sharding": "by sequence, no collective",
+            "l2": "inputs larger than L2 (24.6 GB of KV per GPU streamed per step)",
+            "timing": "ours: CUDA events around K graph replays, max over ranks; reference arm: host clock around "
+                      "each bounded sample (one layer of one sequence per step)"}
+
+
+def ncu_traffic_ratio():
+    """DRAM read+write bytes per launch of the headline kernel divided by the launch's algorithmic
+    bytes, from the ncu capture whose summary sits beside this file's numbers."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "attention_mma_hd128_c2.json")) as f:
+            return float(json.load(f)["dram_bytes_over_algorithmic_bytes"])
+    except Exception:
+        return None
 
 
 KV_DTYPE = "bf16"           # or "u8": 32 codes + bf16 scale + bf16 bias per group = 1.125 B per element
@@ -146,6 +161,36 @@ def cpu_sample(threads: int, iters: int):
     return times
 
 
+def parity_spot(threads, rows, gpu_out, k_new, v_new, q):
+    """Full-size parity point: (layer 0, sequence 0) of the last timed step against the CPU
+    restatement of the reference path on the same bytes. The cache holds the 32768 seeded rows
+    (generator streams 0 and 1 of seed 0) and, behind them, the row every step appended (the
+    step's k / v inputs do not change between replays). Tolerance of the task for bf16 pages:
+    |err| <= 2e-2 * |want| + 1e-3."""
+    from oracle import sgo
+    k = np.empty((rows, KV_DIM), np.float32)
+    v = np.empty((rows, KV_DIM), np.float32)
+    k[:CTX] = sgo.bf16_round(sgo.fill_normal8(CTX * KV_DIM, 0, 0)).reshape(CTX, KV_DIM)
+    v[:CTX] = sgo.bf16_round(sgo.fill_normal8(CTX * KV_DIM, 0, 1)).reshape(CTX, KV_DIM)
+    k[CTX:] = sgo.bf16_round(np.ascontiguousarray(k_new, np.float32))
+    v[CTX:] = sgo.bf16_round(np.ascontiguousarray(v_new, np.float32))
+    cache = sgo.LayerKvCache()
+    assert cache.append_batch(k, v, KV_DIM) == sgo.OK
+    want = np.zeros(Q_DIM, np.float32)
+    qq = np.ascontiguousarray(q, np.float32)
+    rc = sgo.lib().sgo_cached_attention_one(
+        qq.ctypes.data_as(sgo.C.POINTER(sgo.C.c_float)), Q_DIM, sgo.lib().sgo_cache_keys(cache._h),
+        sgo.lib().sgo_cache_values(cache._h), rows, Q_HEADS, KV_HEADS, HEAD_DIM, float(HEAD_DIM), 0, 0, threads,
+        want.ctypes.data_as(sgo.C.POINTER(sgo.C.c_float)))
+    assert rc == sgo.OK
+    err = np.abs(gpu_out.astype(np.float64) - want.astype(np.float64))
+    big = np.abs(want) >= 1e-3
+    return {"rows": int(rows), "max_abs": float(err.max()),
+            "max_rel": float((err[big] / np.abs(want[big])).max()) if big.any() else 0.0,
+            "within_2e-2_rel_plus_1e-3_abs": bool(np.all(err <= 2e-2 * np.abs(want) + 1e-3)),
+            "what": "layer 0, sequence 0 of the last timed step vs the CPU path on the same bytes"}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -164,7 +209,7 @@ def run_reference(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": total_t / len(times) * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "reference_unit": "one layer of one sequence per step"},
+        "config": workload_config(),
         "us_per_layer_per_seq": total_t / len(times) * 1e6,
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -270,6 +315,9 @@ def run_ours(args):
     value = bytes_per_gpu * world / (ms * 1e-3) / 1e9
     us_per_layer = ms * 1e3 / (K * LAYERS)
     status = st.device_status()
+    # (layer 0, sequence 0) of the last timed step, for the full-context check against the CPU path
+    spot_rows = kvs[0][0].len()
+    spot_out = d_out.download(count=Q_DIM).copy()
     if args.skip_extras:
         if rank == 0:
             print(json.dumps({"metric": "decode_attn_append_hbm_gbs_32k", "value": value, "unit": "GB/s",
@@ -328,13 +376,17 @@ def run_ours(args):
     if world > 1 and KV_HEADS % world == 0:
         head_sharded = head_sharded_leg(sg, st, torch, dist, world, rank, stream)
 
+    # The headline's pages (24.6 GB) go back before the other configurations take theirs.
+    for obj in [b1_step, step] + b1_batches + batches + seqs + [pool]:
+        obj.close()
+
     # ---- prefix restore: block copy of a 4096-token prefix on the 4B shape (config 4) ----
     restore = guarded(prefix_restore_gbs, sg, st, torch, stream)
     recurrent = guarded(gated_delta_leg, sg, st, torch, stream)
     producer = guarded(bulk_append_leg, sg, st, torch, stream)
     c3 = guarded(c3_token_leg, sg, st, torch, stream)
-    c5 = guarded(c5_serving_leg, sg, st, torch, stream)
-    c4 = guarded(c4_prefix_leg, sg, st, torch, stream)
+    c5 = guarded(c5_serving_leg, sg, st, torch, stream, dist, rank, world)
+    c4 = guarded(c4_prefix_leg, sg, st, torch, stream, 2000, 128, rank, world)
     c1 = guarded(c1_decode_leg, sg, st, torch, stream) if rank == 0 else None
     lm_head = guarded(lm_head_leg, sg, st, torch, stream)
 
@@ -346,23 +398,23 @@ def run_ours(args):
         threads = min(Q_HEADS, os.cpu_count() or 1)
         cpu_times = cpu_sample(threads, 25)[1:]
         cpu_gbs = sum(b for _, b in cpu_times) / sum(t for t, _ in cpu_times) / 1e9
+        spot = guarded(parity_spot, threads, spot_rows, spot_out, h_k[:KV_DIM], h_v[:KV_DIM], h_q[:Q_DIM])
+        ratio = ncu_traffic_ratio()
+        config = workload_config() if not args.reduced else {
+            "workload": f"OTHER layers={LAYERS} batch={BATCH} ctx={CTX} q{Q_HEADS}/kv{KV_HEADS}/hd{HEAD_DIM} {KV_DTYPE}"}
         line = {
             "metric": "decode_attn_append_hbm_gbs_32k", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD if not args.reduced else (f"OTHER layers={LAYERS} batch={BATCH} ctx={CTX} "
-                                                                                f"q{Q_HEADS}/kv{KV_HEADS}/hd{HEAD_DIM} {KV_DTYPE}"),
-                       "sharding": "by sequence, no collective",
-                       "l2": "inputs larger than L2 (24.6 GB of KV per GPU streamed per step)",
-                       "timing": "CUDA events on the launching stream around K graph replays, max over ranks"},
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
             "us_per_layer": us_per_layer, "us_per_layer_per_seq": us_per_layer / BATCH,
             "decode_steps_per_s": BATCH * world * K / (ms * 1e-3),
-            "batch1": {"us_per_layer": b1_us_layer, "hbm_gbs": b1_gbs, "steps": b1_steps,
-                       "frac_of_peak": b1_gbs / peak},
-            "prefix_restore": restore, "head_sharded_batch1": head_sharded, "gated_delta_step": recurrent, "bulk_append": producer, "c3_hybrid_token": c3, "c5_serving": c5, "c4_prefix_turns": c4, "c1_decode": c1, "lm_head_argmax": lm_head,
+            # the other configurations and kernels, longest first; the short ones the scaling run is
+            # read for come last
+            "c4_prefix_turns": c4, "c1_decode": c1, "c3_hybrid_token": c3, "lm_head_argmax": lm_head,
+            "bulk_append": producer, "gated_delta_step": recurrent, "prefix_restore": restore,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": alg_per_launch * NCU_TRAFFIC_RATIO,
-                         "kernel": "attention_mma_kernel<128, false> (fused append + paged decode attention)",
+                         "frac": achieved / peak, "traffic": alg_per_launch * ratio if ratio else None,
+                         "kernel": "attention_mma_kernel<128> (fused append + paged decode attention)",
                          "peak_kind": f"of {peak_kind}", "frac_of_nominal_8tbs": achieved / 8000.0,
                          "algorithmic_bytes_per_launch": alg_per_launch, "launch_us": launch_us},
             "cpu_baseline": {"value": cpu_gbs, "unit": "GB/s", "cores": threads, "kind": "port",
@@ -373,6 +425,11 @@ def run_ours(args):
                     "call": "sgk_step_run_host (pinned host k,v,q in; out back; synchronous)"},
             "gpu_launches": int(launches), "clocks": clocks, "device_status": status, "outputs_finite": finite,
             "seed_seconds": t_seed,
+            "c5_serving": c5,
+            "batch1": {"us_per_layer": b1_us_layer, "hbm_gbs": b1_gbs, "steps": b1_steps,
+                       "frac_of_peak": b1_gbs / peak, "frac_of_nominal_8tbs": b1_gbs / 8000.0},
+            "head_sharded_batch1": head_sharded,
+            "parity_spot": spot,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -436,10 +493,10 @@ def head_sharded_setup(sg, st, torch, world, rank):
     dk.free()
     dv.free()
     batches = [sg.Batch(st, [kv]) for kv in kvs]
-    return sh, pool, seq, batches, kv_loc, q_loc, steps
+    return sh, pool, seq, batches, kv_loc, q_loc, steps, kvs
 
 
-def head_sharded_run(sg, st, torch, dist, world, rank, stream, sh, pool, seq, batches, kv_loc, q_loc, steps):
+def head_sharded_run(sg, st, torch, dist, world, rank, stream, sh, pool, seq, batches, kv_loc, q_loc, steps, kvs):
     dev = torch.device("cuda", torch.cuda.current_device())
     k = torch.randn(LAYERS, kv_loc, device=dev)
     v = torch.randn(LAYERS, kv_loc, device=dev)
@@ -510,6 +567,32 @@ def head_sharded_run(sg, st, torch, dist, world, rank, stream, sh, pool, seq, ba
     seq.reserve(((CTX + 3 * steps + 24 + 15) // 16) * 16)
     result = {}
     modes = [("nccl", step_nccl)] + ([("direct", step_direct), ("fused", step_fused)] if peers_ok else [])
+    # Parity of the exchanges: the SAME decode step (same rows in the cache, same q / k / v) through
+    # the NCCL all-gather and through each peer-memory form; every rank compares its whole rows, bit
+    # for bit. The cursors go back between the runs (truncate never clears, the appended row is
+    # simply written again).
+    parity = {}
+    if peers_ok:
+        base_len = kvs[0].len()
+        with torch.cuda.stream(stream):
+            step_nccl()
+            stream.synchronize()
+        want = out_full.detach().cpu().numpy().copy()
+        for name, one_step in modes[1:]:
+            for kv in kvs:
+                kv.truncate(base_len)
+            st.sync()
+            with torch.cuda.stream(stream):
+                one_step()
+                stream.synchronize()
+            got = rows.download(np.float32, LAYERS * row).reshape(LAYERS, row)
+            parity[name] = bool(np.array_equal(got, want))
+        for kv in kvs:
+            kv.truncate(base_len)
+        st.sync()
+        flag = torch.tensor([1 if all(parity.values()) else 0], device=dev, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        parity["all_ranks"] = int(flag.item()) == 1
     for name, one_step in modes:
         mode = "graph"
         with torch.cuda.stream(stream):
@@ -554,8 +637,7 @@ def head_sharded_run(sg, st, torch, dist, world, rank, stream, sh, pool, seq, ba
     pool.close()
     total_bytes = sum(algorithmic_bytes(CTX + 2 + i + 1) for i in range(steps)) * LAYERS
     ms, mode = result["nccl"]
-    nccl = {"us_per_layer": ms * 1e3 / (steps * LAYERS), "submission": mode,
-            "exchange": f"one NCCL all-gather of {world * q_loc * 4} bytes per layer"}
+    nccl = {"us_per_layer": ms * 1e3 / (steps * LAYERS), "submission": mode, "exchange": "NCCL all-gather per layer"}
     if not peers_ok:
         return {"us_per_layer": nccl["us_per_layer"], "hbm_gbs_aggregate": total_bytes / (ms * 1e-3) / 1e9, "ranks": world,
                 "kv_heads_per_rank": sh.kv_heads, "steps": steps, "outputs_finite": finite, "device_status": status,
@@ -566,11 +648,10 @@ def head_sharded_run(sg, st, torch, dist, world, rank, stream, sh, pool, seq, ba
     return {"us_per_layer": ms_f * 1e3 / (steps * LAYERS), "hbm_gbs_aggregate": total_bytes / (ms_f * 1e-3) / 1e9,
             "ranks": world, "kv_heads_per_rank": sh.kv_heads, "steps": steps, "outputs_finite": finite,
             "all_slices_arrived": direct_complete, "device_status": status, "submission": mode_f,
-            "exchange": f"inside the attention launch: every output cell ({q_loc * 4} bytes per rank) also stored into each "
-                        "peer's row over NVLink; the last block raises the flags and waits (bounded) for the peers'",
-            "with_exchange_kernel": {"us_per_layer": ms_d * 1e3 / (steps * LAYERS), "submission": mode_d,
-                                     "exchange": "attention launch, then one small kernel per layer: slice stored to the peers, flag, bounded wait"},
-            "with_nccl_all_gather": nccl}
+            "parity_vs_nccl": parity.get("all_ranks"), "parity_fused": parity.get("fused"), "parity_direct": parity.get("direct"),
+            "exchange": "fused into the attention launch (peer stores + flags)",
+            "exchange_kernel_us_per_layer": ms_d * 1e3 / (steps * LAYERS),
+            "nccl_all_gather_us_per_layer": nccl["us_per_layer"]}
 
 
 def gated_delta_leg(sg, st, torch, stream):
@@ -808,6 +889,7 @@ def c3_token_leg(sg, st, torch, stream):
 
     def token():
         a = r = 0
+        st.chain_begin(stream.cuda_stream)   # one decode token: every launch lets the next one start early
         for layer in range(layers):
             if layer in attn_layers:
                 batches[a].enqueue_step(bufs["k"], bufs["v"], bufs["q"], d_out, stream=stream.cuda_stream)
@@ -817,6 +899,7 @@ def c3_token_leg(sg, st, torch, stream):
                 ls.encode_gated_delta_step(r, shape, bufs["gq"], bufs["gk"], bufs["gv"], bufs["g"], bufs["beta"], d_y,
                                            stream=stream.cuda_stream)
                 r += 1
+        st.chain_end()
 
     token()
     stream.synchronize()
@@ -849,18 +932,22 @@ def c3_token_leg(sg, st, torch, stream):
             "shape": "batch 1, ctx 32768: 10 x (16Q/2KV hd256 u8-g32) + 30 x (32 x 128 x 128 f32 state)"}
 
 
-def c4_prefix_leg(sg, st, torch, stream, turns=300, decode_steps=8):
-    """Config 4, shortened: 64 sessions on the 4B shape (36 layers, 8 KV heads, hd128, bf16,
+def c4_prefix_leg(sg, st, torch, stream, turns=2000, decode_steps=128, rank=0, world=1):
+    """Config 4 as it is stated: 64 sessions on the 4B shape (36 layers, 8 KV heads, hd128, bf16,
     16-token blocks of 2.25 MiB), every prompt = a 4096-token system prefix + the session's own
-    history (512..8192 tokens, seed 1) + 64..512 new tokens; sessions drawn Zipf s=1.1; per turn:
-    match -> restore (physical copy) -> append the unmatched rows -> a few decode steps ->
-    remember every new full block; LRU eviction under an 8 GiB budget. Config 4 runs 2000 turns
-    and 128 decode steps per turn; this leg runs fewer of both (stated in the result)."""
+    history (512..8192 tokens, seed 1) + 64..512 new tokens; 2000 turns, sessions drawn Zipf
+    s=1.1; per turn: match -> restore the matched blocks (physical copy, enqueue-only) -> append
+    the unmatched rows -> 128 decode tokens (every token ONE graph replay of the 36 fused
+    append+attention launches) -> remember every new full block (one call); LRU eviction under an
+    8 GiB budget. With several GPUs a session lives on the GPU its root hash names
+    (sharding.rank_of_session) and a rank runs only its sessions' turns. A session's context stops
+    growing at 32k tokens (the window of the other configs)."""
+    from saragossa_b200 import sharding
     layers, qh, kvh, hd, block = 36, 32, 8, 128, 16
     kv_dim, q_dim = kvh * hd, qh * hd
     budget = 8 << 30
-    max_tokens = 4096 + 8192 + 40 * 512 + 1024
-    cap = ((max_tokens + 15) // 16) * 16
+    max_tokens = 32768
+    cap = ((max_tokens + decode_steps + 15) // 16) * 16
     page_b = layers * kvh * 2 * 16 * hd * 2
     pool = st.pool(layers, kvh, hd, sg.KV_BF16, budget // page_b + 2 * (cap // 16) + 64, 4, cap)
     pool.shuffle_free_list(8)
@@ -870,6 +957,9 @@ def c4_prefix_leg(sg, st, torch, stream, turns=300, decode_steps=8):
     lengths = [4096 + int(x) for x in rng.integers(512, 8193, size=n_sessions)]
     weights = 1.0 / np.arange(1, n_sessions + 1) ** 1.1
     weights /= weights.sum()
+    roots = [sg.BlockHash.for_session(f"session-{i}") for i in range(n_sessions)]
+    mine = [sharding.rank_of_session(roots[i], world) == rank for i in range(n_sessions)]
+    history = [[1_000_000 * (i + 1) + j for j in range(lengths[i] - 4096)] for i in range(n_sessions)]
     chunk = 8192
     d_rows_k, d_rows_v = st.alloc(4 * chunk * kv_dim), st.alloc(4 * chunk * kv_dim)
     st.fill_normal(d_rows_k, chunk * kv_dim, 12, 0)
@@ -881,57 +971,88 @@ def c4_prefix_leg(sg, st, torch, stream, turns=300, decode_steps=8):
     st.fill_normal(d_q, layers * q_dim, 13, 2)
     st.sync()
     sys_prefix = list(range(1, 4097))
-    reused_tokens = prompt_tokens = copied_bytes = evicted_before = 0
-    restore_ms = 0.0
+    reused_tokens = prompt_tokens = copied_bytes = my_turns = decode_rows = 0
+    phase = {"match": 0.0, "restore_enqueue": 0.0, "append_enqueue": 0.0, "capture": 0.0, "decode_enqueue": 0.0,
+             "remember": 0.0, "wait": 0.0}
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(2)]
+    restore_ms = decode_ms = 0.0
     t0 = time.perf_counter()
     for turn in range(turns):
         s_ = int(rng.choice(n_sessions, p=weights))
-        root = sg.BlockHash.for_session(f"session-{s_}")
-        new_len = min(lengths[s_] + int(rng.integers(64, 513)), cap - decode_steps - 16)
-        toks = sys_prefix + [1_000_000 * (s_ + 1) + i for i in range(new_len - 4096)]
+        n_new = int(rng.integers(64, 513))
+        if not mine[s_]:
+            continue
+        my_turns += 1
+        root = roots[s_]
+        fresh = [3_000_000_000 + turn * 1000 + i for i in range(n_new)]
+        toks = sys_prefix + history[s_] + fresh
+        if len(toks) > max_tokens:                   # the context window: the oldest history falls out
+            toks = sys_prefix + toks[len(toks) - (max_tokens - 4096):]
+        new_len = len(toks)
+        t = time.perf_counter()
         hit = cache.match_prefix(root, toks)
-        seq = pool.sequence(cap)
+        phase["match"] += time.perf_counter() - t
+        seq = pool.sequence(((new_len + decode_steps + 15) // 16) * 16)
         reused = 0
+        t = time.perf_counter()
         if hit is not None:
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
+            ev[0][0].record(stream)
             copied_bytes += cache.restore(hit, seq, stream=stream.cuda_stream)
-            e1.record(stream)
-            stream.synchronize()
-            restore_ms += e0.elapsed_time(e1)
+            ev[0][1].record(stream)
             reused = hit.tokens
+        phase["restore_enqueue"] += time.perf_counter() - t
         reused_tokens += reused
         prompt_tokens += new_len
+        t = time.perf_counter()
         kvs = [seq.layer(layer, qh) for layer in range(layers)]
         for kv in kvs:                                            # the unmatched rows are "prefilled"
             for c in range(reused, new_len, chunk):
                 kv.encode_append_rows(d_rows_k, d_rows_v, min(chunk, new_len - c), stream=stream.cuda_stream)
+        phase["append_enqueue"] += time.perf_counter() - t
+        t = time.perf_counter()
         batches = [sg.Batch(st, [kv]) for kv in kvs]
+        step = sg.Step(st, batches)
+        stream.synchronize()                                      # the capture wants the appends done
+        step.capture(d_k, d_v, d_q, d_out)
+        phase["capture"] += time.perf_counter() - t
+        t = time.perf_counter()
+        ev[1][0].record(stream)
         for _ in range(decode_steps):
-            for layer, b in enumerate(batches):
-                b.enqueue_step(_Off(d_k, 4 * layer * kv_dim), _Off(d_v, 4 * layer * kv_dim), _Off(d_q, 4 * layer * q_dim),
-                               _Off(d_out, 4 * layer * q_dim), stream=stream.cuda_stream)
+            step.replay(stream.cuda_stream)
+        ev[1][1].record(stream)
+        phase["decode_enqueue"] += time.perf_counter() - t
+        t = time.perf_counter()
         stream.synchronize()
+        phase["wait"] += time.perf_counter() - t
+        if hit is not None:
+            restore_ms += ev[0][0].elapsed_time(ev[0][1])
+        decode_ms += ev[1][0].elapsed_time(ev[1][1])
+        decode_rows += decode_steps * layers * (2 * new_len + decode_steps)
+        step.close()
         for b in batches:
             b.close()
-        new_len += decode_steps
-        toks = toks + [2_000_000_000 + turn * 1000 + i for i in range(decode_steps)]
-        prev = root
-        for i in range(new_len // block):                        # remember every new full block
-            prev = sg.BlockHash.chain(prev, toks[i * block:(i + 1) * block])
-            if (i + 1) * block > reused:
-                cache.insert(root, prev, (i + 1) * block, seq=seq, stream=stream.cuda_stream)
-        lengths[s_] = new_len
+        decoded = [2_000_000_000 + turn * 1000 + i for i in range(decode_steps)]
+        toks = toks + decoded
+        t = time.perf_counter()
+        cache.insert_chain(root, toks, seq, from_tokens=reused, stream=stream.cuda_stream)   # every new full block
+        phase["remember"] += time.perf_counter() - t
+        history[s_] = toks[4096:]
         seq.close()
     stream.synchronize()
     wall = time.perf_counter() - t0
-    out = {"turns": turns, "decode_steps_per_turn": decode_steps, "turns_per_s": turns / wall,
+    out = {"turns": turns, "turns_on_this_gpu": my_turns, "decode_steps_per_turn": decode_steps,
+           "turns_per_s": my_turns / wall, "ms_per_turn": wall / max(my_turns, 1) * 1e3,
+           "decode_tokens_per_s": my_turns * decode_steps / wall,
+           "decode_us_per_layer": decode_ms * 1e3 / max(my_turns * decode_steps * layers, 1),
+           "decode_hbm_gbs": decode_rows / 2 * kv_dim * 2 * 2 / max(decode_ms * 1e-3, 1e-9) / 1e9,
+           "host_ms_per_turn": {k: v / max(my_turns, 1) * 1e3 for k, v in phase.items()},
            "prompt_tokens": prompt_tokens, "reused_tokens": reused_tokens, "hit_rate": reused_tokens / max(prompt_tokens, 1),
            "restore_bytes_read_plus_written": 2 * copied_bytes,
            "restore_gbs": 2 * copied_bytes / max(restore_ms * 1e-3, 1e-9) / 1e9,
-           "evicted_blocks": len(cache.evicted()), "cache_bytes": cache.estimated_bytes(), "budget_bytes": budget,
+           "evicted_blocks": len(cache.evicted()), "cache_entries": len(cache), "cache_bytes": cache.estimated_bytes(),
+           "pinned_bytes": cache.pinned_bytes(), "budget_bytes": budget,
            "device_status": st.device_status(),
-           "shape": "64 sessions, 36 layers x 8 KV heads x hd128 bf16, 16-token blocks (2.25 MiB), 8 GiB budget"}
+           "shape": "64 sessions, 36 layers x 8 KV heads x hd128 bf16, 16-token blocks (2.25 MiB), 8 GiB budget, context capped at 32k"}
     cache.close()
     pool.close()
     return out
@@ -944,29 +1065,62 @@ class _Off:
         self.ptr = buf.ptr + offset
 
 
-def c5_serving_leg(sg, st, torch, stream):
-    """Config 5's per-GPU share at 8 GPUs: 32 of the 256 sequences, 34 layers (global iff
-    (i + 1) % 6 == 0, the others sliding over 1024 rows), 8 Q / 4 KV heads, hd256, bf16 pages,
-    context lengths uniform in [1024, 32768] (seed 2). Sliding layers live in their own pool and
-    hold only the pages of the window (older pages are released). One decode token for all
-    sequences = 34 launches in one CUDA graph."""
-    n_seq, layers, qh, kvh, hd, window = 32, 34, 8, 4, 256, 1024
+def c5_serving_leg(sg, st, torch, stream, dist=None, rank=0, world=1, steps=256):
+    """Config 5 on every rank; a rank that fails says so in the reduction instead of leaving the
+    others waiting in it."""
+    try:
+        out = _c5_local(sg, st, torch, stream, dist, rank, world, steps)
+    except Exception as exc:  # noqa: BLE001
+        out = {"error": f"{type(exc).__name__}: {exc}"[:300], "ms_total": 0.0, "alg": 0.0}
+    if world > 1:
+        ok = 0.0 if "error" in out else 1.0
+        t = torch.tensor([out["ms_total"], out["alg"], ok], device="cuda", dtype=torch.float64)
+        tmax, tmin = t.clone(), t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tmin, op=dist.ReduceOp.MIN)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        if float(tmin[2].item()) < 1.0:
+            return {"error": out.get("error", "another rank failed")}
+        out["ms_total"], out["alg"] = float(tmax[0].item()), float(t[1].item())
+    if "error" in out:
+        return {"error": out["error"]}
+    ms_total, alg = out.pop("ms_total"), out.pop("alg")
+    ms = ms_total / steps
+    out.update({"ms_per_token_step": ms, "us_per_layer": ms * 1e3 / 34,
+                "decode_steps_per_s": 256 / (ms * 1e-3), "hbm_gbs": alg / (ms_total * 1e-3) / 1e9,
+                "hbm_gbs_per_gpu": alg / world / (ms_total * 1e-3) / 1e9})
+    return out
+
+
+def _c5_local(sg, st, torch, stream, dist, rank, world, steps):
+    """Config 5 as it is stated: 256 concurrent sequences, 34 layers (global iff (i + 1) % 6 == 0,
+    the others sliding over 1024 rows), 8 Q / 4 KV heads, hd256, bf16 pages, context lengths
+    uniform in [1024, 32768] (seed 2), sharded by sequence over the GPUs of the run
+    (sharding.sequences_of_rank: 256 / N per GPU, no collective on the data path), 256 decode
+    steps. Sliding layers live in their own pool and hold only the pages of the window (older
+    pages are released), which is what lets one GPU hold all 256 sequences (about 118 GB instead
+    of 600). One decode token for all of a GPU's sequences = 34 launches in one CUDA graph; the
+    time is the max over the ranks, the rate the whole job's."""
+    from saragossa_b200 import sharding
+    total_seq, layers, qh, kvh, hd, window = 256, 34, 8, 4, 256, 1024
     kv_dim, q_dim = kvh * hd, qh * hd
     g_layers = [i for i in range(layers) if (i + 1) % 6 == 0]
     s_layers = [i for i in range(layers) if (i + 1) % 6 != 0]
     rng = np.random.default_rng(2)
-    lens = [int(x) for x in rng.integers(1024, 32769, size=256)][:n_seq]
-    steps = 8
-    cap = ((32768 + steps + 32 + 15) // 16) * 16
-    pages_g = sum((n + steps + 32 + 15) // 16 for n in lens) + 8
-    pages_s = n_seq * (window // 16 + 4) + cap // 16 + 8
+    all_lens = [int(x) for x in rng.integers(1024, 32769, size=total_seq)]
+    lens = [all_lens[i] for i in sharding.sequences_of_rank(total_seq, world, rank)]
+    n_seq = len(lens)
+    grow = steps + 8                       # rows appended by the warm-up and the timed steps
+    cap = ((32768 + grow + 32 + 15) // 16) * 16
+    own = [((n + grow + 32 + 15) // 16) * 16 for n in lens]
+    pages_g = sum(c // 16 for c in own) + 8
+    pages_s = n_seq * ((window + grow) // 16 + 12) + cap // 16 + 8
     pool_g = st.pool(len(g_layers), kvh, hd, sg.KV_BF16, pages_g, n_seq, cap)
     pool_s = st.pool(len(s_layers), kvh, hd, sg.KV_BF16, pages_s, n_seq, cap)
     pool_g.shuffle_free_list(6)
     pool_s.shuffle_free_list(7)
     # a capture reserves every page up to a sequence's capacity: the capacity is its own length
     # plus the rows this leg appends, not the longest context of the config
-    own = [((n + steps + 32 + 15) // 16) * 16 for n in lens]
     seqs_g = [pool_g.sequence(c) for c in own]
     seqs_s = [pool_s.sequence(c) for c in own]
     chunk = 8192
@@ -974,19 +1128,26 @@ def c5_serving_leg(sg, st, torch, stream):
     st.fill_normal(dk_, chunk * kv_dim, 8, 0)
     st.fill_normal(dv_, chunk * kv_dim, 8, 1)
     kv_of = {}
+    t_seed = time.perf_counter()
     for b, n in enumerate(lens):
         for li, layer in enumerate(g_layers):
             kv = seqs_g[b].layer(li, qh)
             for c in range(0, n, chunk):
                 kv.encode_append_rows(dk_, dv_, min(chunk, n - c))
             kv_of[b, layer] = kv
-        for li, layer in enumerate(s_layers):
-            kv = seqs_s[b].layer(li, qh)
-            for c in range(0, n, chunk):
-                kv.encode_append_rows(dk_, dv_, min(chunk, n - c))
-            kv_of[b, layer] = kv
-        st.sync()
-        seqs_s[b].release_before(max(n - window, 0))     # rows before the window are never read again
+        # A sliding layer is filled window by window and gives the pages behind its window back as
+        # it goes, as a server does while the sequence grows: its pool never holds the whole context.
+        first = True
+        for c in range(0, n, window):
+            for li, layer in enumerate(s_layers):
+                kv = seqs_s[b].layer(li, qh) if first else kv_of[b, layer]
+                kv.encode_append_rows(dk_, dv_, min(window, n - c))
+                kv_of[b, layer] = kv
+            first = False
+            st.sync()
+            seqs_s[b].release_before(max(min(c + window, n) - window, 0))
+    st.sync()
+    t_seed = time.perf_counter() - t_seed
     batches = [sg.Batch(st, [kv_of[b, layer] for b in range(n_seq)]) for layer in range(layers)]
     step = sg.Step(st, batches)
     d_k, d_v = st.alloc(4 * layers * n_seq * kv_dim), st.alloc(4 * layers * n_seq * kv_dim)
@@ -997,7 +1158,7 @@ def c5_serving_leg(sg, st, torch, stream):
     st.sync()
     windows = [0 if layer in g_layers else window for layer in range(layers)]
     step.capture(d_k, d_v, d_q, d_out, sliding_windows=windows)
-    for _ in range(2):
+    for _ in range(3):
         step.replay(stream.cuda_stream)
     stream.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -1006,12 +1167,15 @@ def c5_serving_leg(sg, st, torch, stream):
         step.replay(stream.cuda_stream)
     e1.record(stream)
     stream.synchronize()
-    ms = e0.elapsed_time(e1) / steps
+    ms_total = e0.elapsed_time(e1)
     row_bytes = kv_dim * 2 * 2
-    alg = sum(len(g_layers) * (n + 3) * row_bytes + len(s_layers) * min(n + 3, window) * row_bytes for n in lens)
+    alg = sum(len(g_layers) * (n + 3 + i + 1) * row_bytes + len(s_layers) * min(n + 3 + i + 1, window) * row_bytes
+              for n in lens for i in range(steps))
     held_s = pool_s.num_pages - pool_s.free_pages
+    held_g = pool_g.num_pages - pool_g.free_pages
     finite = bool(np.isfinite(d_out.download(count=n_seq * q_dim)).all())
     status = st.device_status()
+    resident_gb = (held_s * pool_s.page_bytes + held_g * pool_g.page_bytes) / 1e9
     step.close()
     for b in batches:
         b.close()
@@ -1019,12 +1183,12 @@ def c5_serving_leg(sg, st, torch, stream):
         s_.close()
     pool_g.close()
     pool_s.close()
-    return {"ms_per_token_step": ms, "us_per_layer": ms * 1e3 / layers, "decode_steps_per_s": n_seq / (ms * 1e-3),
-            "hbm_gbs": alg / (ms * 1e-3) / 1e9, "sequences": n_seq, "mean_context": float(np.mean(lens)),
+    return {"n_gpus": world, "sequences": total_seq, "sequences_per_gpu": n_seq, "decode_steps": steps,
+            "ms_total": ms_total, "alg": float(alg),
+            "mean_context": float(np.mean(all_lens)), "kv_resident_gb_this_gpu": resident_gb,
             "sliding_pool_pages_held": int(held_s), "sliding_pool_pages_if_kept": int(sum((n + 15) // 16 for n in lens)),
-            "outputs_finite": finite, "device_status": status,
-            "shape": "32 of config 5's 256 sequences (its share of one of 8 GPUs): 5 global + 29 sliding-1024 layers, "
-                     "8Q/4KV hd256 bf16, contexts U(1k,32k) seed 2"}
+            "seed_seconds": t_seed, "outputs_finite": finite, "device_status": status,
+            "shape": "5 global + 29 sliding-1024 layers, 8Q/4KV hd256 bf16, contexts U(1k,32k) seed 2, by sequence"}
 
 
 def bulk_append_leg(sg, st, torch, stream):

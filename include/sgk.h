@@ -15,6 +15,11 @@
  *     host-side length cursor at enqueue time, like the reference's encode_*
  *     methods (src/decode_resident/attention.rs:950-1038); host-pointer calls
  *     are synchronous;
+ *   - one stream per pool: the calls that use a pool's sequences (append, attention, restore,
+ *     release, destroy) are ordered by the stream they are enqueued on; a caller that spreads them
+ *     over several streams orders them itself (events) before a call that frees, shares or
+ *     replaces pages of a sequence (sgk_prefix_restore, sgk_seq_release_before, sgk_seq_destroy,
+ *     sgk_kv_truncate followed by appends): the library does not track other streams;
  *   - pointers named d_* are device pointers, everything else is host memory;
  *   - there is no CPU fallback: without a CUDA device sgk_state_create fails.
  */
@@ -76,6 +81,21 @@ int32_t sgk_state_device_status(sgk_state* state, int32_t* status_out);
  * cooperative launches, which the driver places all at once or not at all, at about 2 us more per
  * launch. Set before the first enqueue; a captured step keeps the mode it was captured in. */
 int32_t sgk_state_set_concurrent_streams(sgk_state* state, int32_t enabled);
+
+/* Token chain: the launches of ONE decode token, enqueued one after the other on one stream
+ * (the reference encodes them into one command buffer, src/decoder/resident/decode.rs:243-253).
+ * Between _begin and _end every enqueue of this state on `stream` lets the launch after it start
+ * early, and a launch that directly follows another member (nothing else of this library in
+ * between) starts before its predecessor has finished: it reads the persistent state of its own
+ * layer (cursor, block table, pages, recurrent state, conv history and taps) at once and waits for
+ * the predecessor before it reads its per-token inputs (q, k, v, g, beta, qkv) or writes anything.
+ * The caller's part of the contract: inside a chain, no launch on the stream (the caller's own
+ * kernels between two members included) writes persistent state that the NEXT member reads, i.e.
+ * consecutive members work on different layers, and truncate / restore / reserve calls stay
+ * outside the chain. sgk_step_* open a chain of their own around their layers. A chain may be
+ * captured into a CUDA graph; the dependencies are kept as programmatic edges. */
+int32_t sgk_state_chain_begin(sgk_state* state, void* stream);
+int32_t sgk_state_chain_end(sgk_state* state);
 
 /* Failure-detection self test: launches a kernel whose only wait (on an mbarrier nobody
  * completes) must expire. Returns SGK_ERR_TIMEOUT when the bounded wait reported through the
@@ -437,15 +457,30 @@ int32_t sgk_prefix_match(sgk_prefix* pc, const uint8_t root[32], const uint64_t*
 int32_t sgk_prefix_insert(sgk_prefix* pc, const uint8_t session[32], const uint8_t hash[32],
                           int64_t tokens, sgk_seq* seq, sgk_linstate* ls, void* stream,
                           int32_t* inserted_out);
+/* prefill_prompt_state's loop over the full blocks of a prompt (src/serve/state.rs:596-604) in
+ * one call: for every full block of tokens[0..n) that ends after from_tokens (the matched prefix;
+ * a block boundary, 0 for none) the hash chain is advanced and the block is remembered as
+ * sgk_prefix_insert does, each with its own budget loop; `seq` must hold the prompt's rows.
+ * *inserted_out = blocks inserted; last_hash_out (may be NULL) = hash of the last full block.
+ * A turn of a conversation costs one call instead of one per 16-token block. */
+int32_t sgk_prefix_insert_chain(sgk_prefix* pc, const uint8_t root[32], const uint64_t* tokens, size_t n,
+                                int64_t from_tokens, sgk_seq* seq, void* stream, int32_t* inserted_out,
+                                uint8_t last_hash_out[32]);
 /* copy_prompt_state_metal_snapshot + restore_prompt_state_metal
  * (src/decoder/generation.rs:2851-2892): makes `seq` hold the entry's rows.
  * mode 0 = physical copy into pages owned by the sequence (the reference's
- * never-aliased rule), 1 = share the pages by reference (copy-on-write). */
+ * never-aliased rule), 1 = share the pages by reference (copy-on-write).
+ * Enqueue-only: the page copy, the new block table and the new cursors follow each other on
+ * `stream`; launches enqueued on it before the call still see the old sequence. When the pool
+ * cannot hold the copy (mode 0) the call fails with SGK_ERR_MEMORY_GUARD and the sequence is
+ * left exactly as it was. */
 int32_t sgk_prefix_restore(sgk_prefix* pc, uint64_t entry, sgk_seq* seq, sgk_linstate* ls,
                            void* stream, int32_t mode, int64_t* bytes_copied_out);
 /* evict_lru_block (cache.rs:196-198): *evicted_out = 0 when the cache is empty. */
 int32_t sgk_prefix_evict_lru(sgk_prefix* pc, int32_t* evicted_out, int64_t* bytes_out);
 int64_t sgk_prefix_bytes(const sgk_prefix* pc); /* estimated_bytes (cache.rs:200-203) */
+/* What the budget is compared with: distinct pages pinned by the cache x page bytes + state snapshots. */
+int64_t sgk_prefix_pinned_bytes(const sgk_prefix* pc);
 int64_t sgk_prefix_len(const sgk_prefix* pc);
 int64_t sgk_prefix_session_count(const sgk_prefix* pc, const uint8_t session[32]);
 /* Trace hook: which = 0 live entries front-to-rear, 1 = every entry that left, in order. */

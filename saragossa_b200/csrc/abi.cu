@@ -99,6 +99,22 @@ int32_t sgk_state_set_concurrent_streams(sgk_state* st, int32_t enabled) {
   return SGK_OK;
 }
 
+int32_t sgk_state_chain_begin(sgk_state* st, void* stream) {
+  if (!st) return fail(SGK_ERR_BACKEND, "null state");
+  if (st->chain_active) return fail(SGK_ERR_CONFIG, "a token chain is open already");
+  st->chain_active = true;
+  st->chain_stream = st->pick(stream);
+  st->chain_mark = -1;
+  return SGK_OK;
+}
+
+int32_t sgk_state_chain_end(sgk_state* st) {
+  if (!st) return fail(SGK_ERR_BACKEND, "null state");
+  st->chain_active = false;
+  st->chain_mark = -1;
+  return SGK_OK;
+}
+
 int32_t sgk_state_selftest_wait_timeout(sgk_state* st) {
   if (!st) return fail(SGK_ERR_BACKEND, "null state");
   SGK_CUDA(launch_wait_timeout_selftest(st->d_status, st->stream));
@@ -170,7 +186,7 @@ void sgk_pool_destroy(sgk_pool* p) {
   if (p->d_tables) cudaFree(p->d_tables);
   if (p->d_lens) cudaFree(p->d_lens);
   if (p->d_scale_max) cudaFree(p->d_scale_max);
-  if (p->d_page_list) cudaFree(p->d_page_list);
+  p->stage_free();
   delete p;
 }
 
@@ -1269,9 +1285,13 @@ static int32_t conv_impl(sgk_linstate* ls, void* stream, int32_t layer, const fl
     return fail(SGK_ERR_DIMENSION, "conv history holds %lld values, expected %lld", (long long)ls->conv_len,
                 (long long)(int64_t(conv_kernel_dim - 1) * conv_dim));
   if (n_tokens == 0) return SGK_OK;
+  State* st = ls->st;
+  cudaStream_t s = st->pick(stream);
+  const bool member = st->chain_member(s);
   SGK_CUDA(launch_conv_step(d_qkv, d_weight, static_cast<float*>(sgk_linstate_conv_ptr(ls, layer)), d_out, conv_dim,
-                            conv_kernel_dim, n_tokens, ls->st->pick(stream)));
-  ls->st->launches += 1;
+                            conv_kernel_dim, n_tokens, member ? 1 : 0, st->chain_follows(s) ? 1 : 0, s));
+  st->launches += 1;
+  if (member) st->chain_note();
   return SGK_OK;
 }
 
@@ -1324,8 +1344,14 @@ static int32_t gated_delta_impl(sgk_linstate* const* states, int32_t n_states, v
   a.g = d_g;
   a.beta = d_beta;
   a.out = d_out;
-  SGK_CUDA(launch_gated_delta_step(a, states[0]->st->pick(stream)));
-  states[0]->st->launches += 1;
+  State* st = states[0]->st;
+  cudaStream_t s = st->pick(stream);
+  const bool member = st->chain_member(s);
+  a.pdl_trigger = member ? 1 : 0;
+  a.pdl_wait = st->chain_follows(s) ? 1 : 0;
+  SGK_CUDA(launch_gated_delta_step(a, st->sm_count, s));
+  st->launches += 1;
+  if (member) st->chain_note();
   return SGK_OK;
 }
 
@@ -1410,98 +1436,47 @@ int32_t sgk_prefix_match(sgk_prefix* pc, const uint8_t root[32], const uint64_t*
   if (!pc || !root || !tokens_out || !hash_out || !entry_out) return fail(SGK_ERR_BACKEND, "null argument");
   *entry_out = 0;
   *tokens_out = 0;
-  if (pc->capacity == 0 || (n > 0 && !tokens)) return SGK_OK;
-  Hash32 session;
+  if (n > 0 && !tokens) return SGK_OK;
+  Hash32 session, hash{};
   std::memcpy(session.data(), root, 32);
-  Hash32 previous = session;
-  const size_t bt = static_cast<size_t>(pc->block_tokens);
-  for (size_t index = 0; index < n / bt; ++index) {
-    Hash32 hash = hash_chain(previous, tokens + index * bt, bt);
-    int64_t expected = static_cast<int64_t>((index + 1) * bt);
-    auto it = std::find_if(pc->entries.begin(), pc->entries.end(), [&](const PrefixEntry& e) {
-      return e.session == session && e.hash == hash && e.tokens == expected;
-    });
-    if (it == pc->entries.end()) break;  // stop at the first miss (cache.rs:134-138)
-    // every touched block moves to the front (cache.rs:139-146)
-    std::rotate(pc->entries.begin(), it, it + 1);
-    *tokens_out = pc->entries.front().tokens;
-    std::memcpy(hash_out, pc->entries.front().hash.data(), 32);
-    *entry_out = pc->entries.front().id;
-    previous = hash;
-  }
+  pc->match(session, tokens, n, tokens_out, &hash, entry_out);
+  if (*entry_out) std::memcpy(hash_out, hash.data(), 32);
   return SGK_OK;
 }
 
 int32_t sgk_prefix_insert(sgk_prefix* pc, const uint8_t session[32], const uint8_t hash[32], int64_t tokens,
                           sgk_seq* seq, sgk_linstate* ls, void* stream, int32_t* inserted_out) {
   if (!pc || !session || !hash) return fail(SGK_ERR_BACKEND, "null argument");
+  Hash32 s, h;
+  std::memcpy(s.data(), session, 32);
+  std::memcpy(h.data(), hash, 32);
+  return pc->insert(s, h, tokens, seq, ls, stream, inserted_out);
+}
+
+int32_t sgk_prefix_insert_chain(sgk_prefix* pc, const uint8_t root[32], const uint64_t* tokens, size_t n,
+                                int64_t from_tokens, sgk_seq* seq, void* stream, int32_t* inserted_out,
+                                uint8_t last_hash_out[32]) {
+  if (!pc || !root || (n > 0 && !tokens)) return fail(SGK_ERR_BACKEND, "null argument");
   if (inserted_out) *inserted_out = 0;
-  if (pc->capacity == 0) return SGK_OK;  // cache.rs:162-164
-  if (tokens <= 0) return fail(SGK_ERR_DIMENSION, "prefix block boundary must be positive");
-  if (pc->pool && !seq) return fail(SGK_ERR_BACKEND, "prefix insert needs the sequence to snapshot");
-  std::vector<int32_t> pages;
-  if (seq) {
-    if (seq->pool != pc->pool) return fail(SGK_ERR_CONFIG, "sequence belongs to another pool");
-    if (tokens % PAGE_TOKENS != 0)
-      return fail(SGK_ERR_DIMENSION, "snapshot boundary %lld is not on a page boundary", (long long)tokens);
-    for (int64_t l : seq->len)
-      if (l < tokens)
-        return fail(SGK_ERR_DIMENSION, "snapshot of %lld rows from a sequence holding %lld", (long long)tokens, (long long)l);
-    if (seq->released_pages > 0) return fail(SGK_ERR_DIMENSION, "snapshot of a sequence whose head was released");
-    pages.assign(seq->pages.begin(), seq->pages.begin() + tokens / PAGE_TOKENS);
+  if (from_tokens < 0 || from_tokens % pc->block_tokens != 0)
+    return fail(SGK_ERR_DIMENSION, "from_tokens %lld is not on a block boundary", (long long)from_tokens);
+  Hash32 session;
+  std::memcpy(session.data(), root, 32);
+  Hash32 previous = session;
+  const size_t bt = static_cast<size_t>(pc->block_tokens);
+  // prefill_prompt_state's loop (src/serve/state.rs:596-604): every full block of the prompt is
+  // remembered in order, each with its own budget loop; blocks before from_tokens (the matched
+  // prefix) only advance the hash chain.
+  for (size_t i = 0; i < n / bt; ++i) {
+    const Hash32 hash = hash_chain(previous, tokens + i * bt, bt);
+    previous = hash;
+    const int64_t boundary = static_cast<int64_t>((i + 1) * bt);
+    if (boundary <= from_tokens) continue;
+    int32_t inserted = 0;
+    SGK_TRY(pc->insert(session, hash, boundary, seq, nullptr, stream, &inserted));
+    if (inserted_out) *inserted_out += inserted;
   }
-  PrefixEntry e;
-  std::memcpy(e.session.data(), session, 32);
-  std::memcpy(e.hash.data(), hash, 32);
-  e.tokens = tokens;
-  // a refresh replaces the older duplicate without counting as an eviction (cache.rs:165-169)
-  auto dup = std::find_if(pc->entries.begin(), pc->entries.end(), [&](const PrefixEntry& o) {
-    return o.session == e.session && o.hash == e.hash && o.tokens == e.tokens;
-  });
-  if (dup != pc->entries.end()) pc->drop(static_cast<size_t>(dup - pc->entries.begin()), false);
-  // budget loop of remember_prefix_block (src/serve/state.rs:627-635)
-  auto additional = [&]() {
-    int64_t fresh = 0;
-    for (int32_t p : pages) fresh += pc->pins.count(p) ? 0 : 1;
-    return fresh * (pc->pool ? pc->pool->page_b : 0) + (ls ? ls->estimated_bytes() : 0);
-  };
-  if (pc->budget > 0) {
-    while (pc->pinned_bytes() + additional() > pc->budget) {
-      if (!pc->evict_lru(nullptr)) {
-        if (pc->pool && !pc->pool->host_only()) SGK_TRY(pc->pool->flush_scrub(pc->pool->st->stream));
-        return SGK_OK;  // cache empty and still over budget: skip the insert
-      }
-    }
-  }
-  e.bytes = additional();
-  if (ls) {
-    sgk_linstate* snap = nullptr;
-    SGK_TRY(sgk_linstate_snapshot(ls, stream, &snap));
-    e.ls.reset(snap);
-    pc->state_bytes += snap->estimated_bytes();
-  }
-  for (int32_t p : pages) {
-    pc->pool->retain(p);
-    pc->pins[p] += 1;
-  }
-  e.pages = std::move(pages);
-  e.id = pc->next_id++;
-  pc->entries.insert(pc->entries.begin(), std::move(e));  // cache.rs:173-183
-  // per-session cap: that session's rear-most entries leave first (cache.rs:184-188)
-  Hash32 sess = pc->entries.front().session;
-  while (pc->session_count(sess) > pc->blocks_per_session) {
-    long idx = -1;
-    for (long i = static_cast<long>(pc->entries.size()) - 1; i >= 0; --i)
-      if (pc->entries[static_cast<size_t>(i)].session == sess) {
-        idx = i;
-        break;
-      }
-    if (idx < 0) break;
-    pc->drop(static_cast<size_t>(idx), true);
-  }
-  while (static_cast<int64_t>(pc->entries.size()) > pc->capacity) pc->drop(pc->entries.size() - 1, true);  // :189-191
-  if (pc->pool && !pc->pool->host_only()) SGK_TRY(pc->pool->flush_scrub(pc->pool->st->stream));
-  if (inserted_out) *inserted_out = 1;
+  if (last_hash_out) std::memcpy(last_hash_out, previous.data(), 32);
   return SGK_OK;
 }
 
@@ -1510,38 +1485,51 @@ int32_t sgk_prefix_restore(sgk_prefix* pc, uint64_t entry, sgk_seq* seq, sgk_lin
   if (!pc || !seq) return fail(SGK_ERR_BACKEND, "null argument");
   if (bytes_copied_out) *bytes_copied_out = 0;
   if (mode != 0 && mode != 1) return fail(SGK_ERR_CONFIG, "restore mode %d", mode);
-  auto it = std::find_if(pc->entries.begin(), pc->entries.end(), [&](const PrefixEntry& e) { return e.id == entry; });
-  if (it == pc->entries.end()) return fail(SGK_ERR_DIMENSION, "prefix entry %llu is no longer cached", (unsigned long long)entry);
+  auto found = pc->by_id.find(entry);
+  if (found == pc->by_id.end()) return fail(SGK_ERR_DIMENSION, "prefix entry %llu is no longer cached", (unsigned long long)entry);
+  const PrefixEntry& e = *found->second;
   if (seq->pool != pc->pool) return fail(SGK_ERR_CONFIG, "sequence belongs to another pool");
-  if (it->tokens > seq->capacity)
-    return fail(SGK_ERR_DIMENSION, "restore of %lld rows > capacity %lld", (long long)it->tokens, (long long)seq->capacity);
+  if (e.key.tokens > seq->capacity)
+    return fail(SGK_ERR_DIMENSION, "restore of %lld rows > capacity %lld", (long long)e.key.tokens, (long long)seq->capacity);
+  if (e.ls && !ls) return fail(SGK_ERR_SHAPE, "entry holds a linear-attention state but none was given to restore into");
   Pool* pool = pc->pool;
+  std::vector<int32_t> src;
+  pc->collect_pages(e.run.get(), &src);
+  if (mode == 0) {
+    // Nothing is touched unless the copy can be made: the pages the sequence itself gives back
+    // (those nobody else holds) count as free.
+    size_t own = 0;
+    for (int32_t p : seq->pages)
+      if (p >= 0 && pool->refcount[p] == 1) own += 1;
+    if (src.size() > pool->free_list.size() + own)
+      return fail(SGK_ERR_MEMORY_GUARD, "page pool exhausted: need %zu pages, %zu free", src.size(),
+                  pool->free_list.size() + own);
+  }
   cudaStream_t cs = pool->host_only() ? nullptr : pool->st->pick(stream);
-  if (!pool->host_only()) SGK_CUDA(cudaStreamSynchronize(cs));  // the table of a live sequence is about to change
+  // Everything below is enqueued on `cs` in order: earlier launches on it still read the old
+  // table and pages, later ones the restored ones. (Launches on OTHER streams that use this
+  // sequence must have finished: see the stream rule in sgk.h.)
   seq->release_all();
-  const std::vector<int32_t>& src = it->pages;
   if (mode == 1) {
     for (int32_t p : src) pool->retain(p);
     seq->pages = src;
   } else {
-    if (src.size() > pool->free_list.size())
-      return fail(SGK_ERR_MEMORY_GUARD, "page pool exhausted: need %zu pages, %zu free", src.size(), pool->free_list.size());
     std::vector<int32_t> dst;
+    dst.reserve(src.size());
     for (size_t i = 0; i < src.size(); ++i) {
       int32_t p;
       SGK_TRY(pool->alloc_page(&p));
       dst.push_back(p);
     }
-    SGK_TRY(pool->copy_pages(dst, src, cs));
     seq->pages = dst;
+    SGK_TRY(pool->copy_pages(dst, src, cs));
     if (bytes_copied_out) *bytes_copied_out = static_cast<int64_t>(src.size()) * pool->page_b;
   }
-  SGK_TRY(seq->publish(0, static_cast<int64_t>(seq->pages.size())));
-  SGK_TRY(seq->set_len_all(it->tokens, cs));
-  if (it->ls) {
-    if (!ls) return fail(SGK_ERR_SHAPE, "entry holds a linear-attention state but none was given to restore into");
-    SGK_TRY(sgk_linstate_restore(ls, stream, static_cast<sgk_linstate*>(it->ls.get())));
-    if (bytes_copied_out) *bytes_copied_out += it->ls->total_bytes;
+  SGK_TRY(seq->publish(0, static_cast<int64_t>(seq->pages.size()), cs, true));
+  SGK_TRY(seq->set_len_all(e.key.tokens, cs));
+  if (e.ls) {
+    SGK_TRY(sgk_linstate_restore(ls, stream, static_cast<sgk_linstate*>(e.ls.get())));
+    if (bytes_copied_out) *bytes_copied_out += e.ls->total_bytes;
   }
   return SGK_OK;
 }
@@ -1555,12 +1543,8 @@ int32_t sgk_prefix_evict_lru(sgk_prefix* pc, int32_t* evicted_out, int64_t* byte
   return SGK_OK;
 }
 
-int64_t sgk_prefix_bytes(const sgk_prefix* pc) {
-  int64_t total = 0;
-  if (pc)
-    for (const auto& e : pc->entries) total += e.bytes;
-  return total;
-}
+int64_t sgk_prefix_bytes(const sgk_prefix* pc) { return pc ? pc->entry_bytes : 0; }
+int64_t sgk_prefix_pinned_bytes(const sgk_prefix* pc) { return pc ? pc->pinned_bytes() : 0; }
 int64_t sgk_prefix_len(const sgk_prefix* pc) { return pc ? static_cast<int64_t>(pc->entries.size()) : 0; }
 int64_t sgk_prefix_session_count(const sgk_prefix* pc, const uint8_t session[32]) {
   if (!pc || !session) return 0;
@@ -1573,12 +1557,16 @@ int64_t sgk_prefix_dump(const sgk_prefix* pc, int32_t which, int64_t cap, uint8_
                         int64_t* tokens) {
   if (!pc) return 0;
   int64_t total = which == 0 ? static_cast<int64_t>(pc->entries.size()) : static_cast<int64_t>(pc->evicted_log.size());
-  for (int64_t i = 0; i < std::min(cap, total); ++i) {
-    const Hash32& s = which == 0 ? pc->entries[i].session : pc->evicted_log[i].session;
-    const Hash32& h = which == 0 ? pc->entries[i].hash : pc->evicted_log[i].hash;
-    if (sessions) std::memcpy(sessions + 32 * i, s.data(), 32);
-    if (hashes) std::memcpy(hashes + 32 * i, h.data(), 32);
-    if (tokens) tokens[i] = which == 0 ? pc->entries[i].tokens : pc->evicted_log[i].tokens;
+  auto put = [&](int64_t i, const PrefixKey& k) {
+    if (sessions) std::memcpy(sessions + 32 * i, k.session.data(), 32);
+    if (hashes) std::memcpy(hashes + 32 * i, k.hash.data(), 32);
+    if (tokens) tokens[i] = k.tokens;
+  };
+  if (which == 0) {
+    int64_t i = 0;
+    for (auto it = pc->entries.begin(); it != pc->entries.end() && i < cap; ++it, ++i) put(i, it->key);
+  } else {
+    for (int64_t i = 0; i < std::min(cap, total); ++i) put(i, pc->evicted_log[i]);
   }
   return total;
 }
@@ -1674,9 +1662,18 @@ int32_t sgk_util_copy_blocks(sgk_state* st, void* stream, void* d_dst, const voi
   if (!st || !d_dst || !d_src) return fail(SGK_ERR_BACKEND, "null argument");
   if (page_bytes <= 0 || page_bytes % 16 != 0) return fail(SGK_ERR_DIMENSION, "page_bytes must be a positive multiple of 16");
   SGK_CUDA(launch_copy_pages(static_cast<uint8_t*>(d_dst), static_cast<const uint8_t*>(d_src), dst_pages, src_pages,
-                             n_pages, page_bytes, 1, 0, st->pick(stream)));
+                             n_pages, page_bytes, 1, 0, st->sm_count, st->pick(stream)));
   st->launches += 1;
   return SGK_OK;
 }
 
 }  // extern "C"
+
+namespace sgk {
+int linstate_snapshot(LinState* ls, void* stream, LinState** out) {
+  sgk_linstate* snap = nullptr;
+  int rc = sgk_linstate_snapshot(static_cast<sgk_linstate*>(ls), stream, &snap);
+  *out = snap;
+  return rc;
+}
+}  // namespace sgk

@@ -8,6 +8,9 @@
 #include <array>
 #include <cstdarg>
 #include <cstdint>
+#include <cstdlib>
+#include <cstring>
+#include <list>
 #include <memory>
 #include <string>
 #include <unordered_map>
@@ -56,6 +59,23 @@ struct State {
   // streams at once, so launches whose blocks wait for each other go as ordinary launches;
   // true: they go as cooperative launches (sgk_state_set_concurrent_streams)
   bool concurrent_streams = false;
+  // Token chain (sgk_state_chain_begin / _end, and every step): the launches of one decode token on
+  // one stream. A member launch lets its successor start early; it carries the programmatic
+  // stream-serialisation attribute itself when the launch enqueued just before it through this
+  // state was a member too (chain_mark == launches: nothing of ours in between, e.g. no
+  // copy-on-write). What a member reads before its wait is persistent state of its own layer only.
+  bool chain_active = false;
+  cudaStream_t chain_stream = nullptr;
+  int64_t chain_mark = -1;
+  // kill-switch, in the spirit of the reference's RETI_RUST_* flags
+  static bool chain_disabled() {
+    static const bool off = std::getenv("SGK_NO_CHAIN") != nullptr;
+    return off;
+  }
+  bool chain_member(cudaStream_t s) const { return chain_active && s == chain_stream && !chain_disabled(); }
+  bool chain_follows(cudaStream_t s) const { return chain_member(s) && chain_mark == launches; }
+  void chain_note() { chain_mark = launches; }   // call right after counting a member's launch
+  void chain_break() { chain_mark = -1; }
   cudaStream_t pick(void* s) const { return s ? static_cast<cudaStream_t>(s) : stream; }
 };
 
@@ -73,8 +93,25 @@ struct Pool {
   int32_t* d_tables = nullptr;
   int32_t* d_lens = nullptr;
   uint32_t* d_scale_max = nullptr;  // u8 pools only
-  int32_t* d_page_list = nullptr;  // staging for copy / scrub page lists
-  int page_list_cap = 0;
+  // Staging of small host arrays (page lists of a copy or scrub, block-table entries of a restore)
+  // on their way to the device: a ring of pinned host slots with a device twin each. A slot is
+  // filled, copied and consumed in stream order, and its event says when the host may fill it
+  // again, so none of these calls waits for the device unless it is a whole ring ahead.
+  struct StageSlot {
+    int32_t* h = nullptr;
+    int32_t* d = nullptr;
+    int cap = 0;
+    cudaEvent_t done = nullptr;
+    bool pending = false;
+  };
+  static constexpr int STAGE_SLOTS = 8;
+  StageSlot stage[STAGE_SLOTS];
+  int stage_next = 0;
+  // Puts a ++ b into a slot and enqueues its copy to the slot's device twin on `stream`.
+  int stage_words(const int32_t* a, size_t na, const int32_t* b, size_t nb, cudaStream_t stream, int* slot_out);
+  // To be called once the work that reads the slot (or the copy out of it) is enqueued on `stream`.
+  int stage_done(int slot, cudaStream_t stream);
+  void stage_free();
   std::vector<int32_t> free_list;  // taken from the back
   std::vector<int32_t> refcount;
   std::vector<int> free_slots;
@@ -111,7 +148,9 @@ struct Seq {
   int ensure_writable(int64_t row, cudaStream_t stream);
   int set_len(int layer, int64_t value, cudaStream_t stream);
   int set_len_all(int64_t value, cudaStream_t stream);
-  int publish(int64_t first_page, int64_t n);
+  // Block-table entries [first_page, first_page + n) to the device: at once (stream == NULL: entries no
+  // enqueued launch reads yet) or in stream order (entries of a live sequence being replaced).
+  int publish(int64_t first_page, int64_t n, cudaStream_t stream = nullptr, bool ordered = false);
 };
 
 struct Kv {
@@ -166,19 +205,8 @@ struct Batch {
   int choose_splits(int kernel, int64_t max_rows) const;
   int enqueue_append(cudaStream_t stream, const float* d_k, const float* d_v, int n_rows, const RopeArgs* rope,
                      const float* knorm_w);
-  // chain: the launches of one decode token, layer after layer. A launch FOLLOWS the chain when the
-  // launch enqueued just before it on the stream is the attention launch of another layer (nothing
-  // that launch writes is read by this one before its q / k_new / v_new): prev_other_layer says so of
-  // the previous enqueue, and the state's launch count must still be what it was right after that
-  // launch (a copy-on-write or a table update in between would have moved it).
-  struct Chain {
-    bool in_chain = false;
-    bool prev_other_layer = false;
-    int64_t launches_after_prev = -1;
-  };
   int enqueue_attention(cudaStream_t stream, const float* d_q, float* d_out, int64_t window_start,
-                        int64_t sliding_window, float attn_scalar, const float* d_k_new, const float* d_v_new,
-                        const Chain* chain = nullptr);
+                        int64_t sliding_window, float attn_scalar, const float* d_k_new, const float* d_v_new);
   ~Batch();
 };
 
@@ -238,37 +266,91 @@ struct Exchange {
   ~Exchange();
 };
 
+// A fresh state holding a copy of `ls` (snapshot_linear_attn_states); defined beside the ABI.
+int linstate_snapshot(LinState* ls, void* stream, LinState** out);
+
 using Hash32 = std::array<uint8_t, 32>;
 void sha256(const uint8_t* data, size_t n, uint8_t out[32]);
 Hash32 hash_chain(const Hash32& prev, const uint64_t* tokens, size_t n);
 
-struct PrefixEntry {
-  Hash32 session, hash;
-  int64_t tokens = 0;
-  uint64_t id = 0;
-  std::vector<int32_t> pages;
-  std::unique_ptr<LinState> ls;
-  int64_t bytes = 0;
+// The pages of ONE block of a cached prefix, linked to the run of the block before it. An entry
+// of the cache holds the run of its own block; the run keeps its ancestors alive, so an entry pins
+// its whole prefix (what the reference's entry does by cloning the whole state,
+// src/serve/cache.rs:170-183) while the cache stores every page id once: memory is linear in the
+// number of blocks, not quadratic in the prompt length.
+struct PageRun {
+  std::vector<int32_t> pages;        // this block's pages only
+  std::shared_ptr<PageRun> parent;   // the block before it (NULL for the first block)
+  int64_t first_page = 0;            // index of pages[0] in the sequence's block table
 };
 
 struct PrefixKey {
   Hash32 session, hash;
   int64_t tokens;
+  bool operator==(const PrefixKey& o) const { return tokens == o.tokens && hash == o.hash && session == o.session; }
+};
+struct PrefixKeyHash {
+  size_t operator()(const PrefixKey& k) const {
+    uint64_t a, b;   // the digests are uniformly distributed already
+    std::memcpy(&a, k.hash.data(), 8);
+    std::memcpy(&b, k.session.data() + 8, 8);
+    return static_cast<size_t>(a ^ (b * 0x9e3779b97f4a7c15ull) ^ (static_cast<uint64_t>(k.tokens) << 1));
+  }
+};
+struct Hash32Hash {
+  size_t operator()(const Hash32& h) const {
+    uint64_t a;
+    std::memcpy(&a, h.data(), 8);
+    return static_cast<size_t>(a);
+  }
 };
 
+struct PrefixEntry;
+using PrefixList = std::list<PrefixEntry>;
+struct PrefixEntry {
+  PrefixKey key;
+  uint64_t id = 0;
+  std::shared_ptr<PageRun> run;
+  std::unique_ptr<LinState> ls;
+  int64_t bytes = 0;
+  std::list<PrefixList::iterator>::iterator in_session;   // its place in its session's list
+};
+
+// BlockAwarePrefixCache (src/serve/cache.rs:74-219) over the page pool. Order and every observable
+// effect are the reference's (front = most recently used; a matched chain is touched root to leaf;
+// a refresh replaces its duplicate silently; per-session cap, then global cap); the structure is
+// not: the reference scans a Vec per block, here a block is found through a hash index and moved
+// by relinking a list node, so a match costs O(1) per block whatever the cache holds.
 struct Prefix {
   Pool* pool = nullptr;
   int64_t block_tokens = 1, capacity = 0, blocks_per_session = 0, budget = 0;
-  std::vector<PrefixEntry> entries;  // front = most recently used
+  PrefixList entries;  // front = most recently used
+  std::unordered_map<PrefixKey, PrefixList::iterator, PrefixKeyHash> index;
+  std::unordered_map<uint64_t, PrefixList::iterator> by_id;
+  // per session: its entries in the same relative order as `entries`
+  std::unordered_map<Hash32, std::list<PrefixList::iterator>, Hash32Hash> sessions;
+  std::unordered_map<int32_t, std::weak_ptr<PageRun>> run_by_last_page;   // finds the run a new block continues
   std::vector<PrefixKey> evicted_log;
-  std::unordered_map<int32_t, int32_t> pins;  // page -> entries holding it
-  int64_t state_bytes = 0;                    // linear-state snapshots held
+  int64_t pinned_pages = 0;   // pages of all live runs
+  int64_t state_bytes = 0;    // linear-state snapshots held
+  int64_t entry_bytes = 0;    // sum of the entries' own byte counts
   uint64_t next_id = 1;
 
   int64_t pinned_bytes() const;
-  void drop(size_t index, bool log);
-  bool evict_lru(int64_t* bytes_out);
   int64_t session_count(const Hash32& s) const;
+  void touch(PrefixList::iterator it);
+  void drop(PrefixList::iterator it, bool log);
+  bool evict_lru(int64_t* bytes_out);
+  // The run chain of rows [0, tokens) of `seq`: reuses the live runs that hold the same pages and
+  // makes the missing ones; *fresh_pages = pages of the runs it would have to make.
+  std::shared_ptr<PageRun> chain_for(const Seq* seq, int64_t tokens, bool create, int64_t* fresh_pages);
+  void release_run(std::shared_ptr<PageRun>& run);
+  void collect_pages(const PageRun* run, std::vector<int32_t>* out) const;
+  // match_prefix / insert with the budget loop of remember_prefix_block (src/serve/state.rs:613-639)
+  void match(const Hash32& session, const uint64_t* tokens, size_t n, int64_t* tokens_out, Hash32* hash_out,
+             uint64_t* entry_out);
+  int insert(const Hash32& session, const Hash32& hash, int64_t tokens, Seq* seq, LinState* ls, void* stream,
+             int32_t* inserted_out);
   ~Prefix();
 };
 

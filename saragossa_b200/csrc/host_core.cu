@@ -71,23 +71,47 @@ void Pool::release(int32_t page) {
   }
 }
 
-static int upload_page_list(Pool* pool, const std::vector<int32_t>& a, const std::vector<int32_t>& b) {
-  int need = static_cast<int>(a.size() + b.size());
-  if (need > pool->page_list_cap) {
-    if (pool->d_page_list) cudaFree(pool->d_page_list);
-    pool->d_page_list = nullptr;
-    int cap = std::max(need, 4096);
-    SGK_CUDA(cudaMalloc(&pool->d_page_list, size_t(cap) * sizeof(int32_t)));
-    pool->page_list_cap = cap;
+int Pool::stage_words(const int32_t* a, size_t na, const int32_t* b, size_t nb, cudaStream_t stream, int* slot_out) {
+  const int need = static_cast<int>(na + nb);
+  const int idx = stage_next;
+  stage_next = (stage_next + 1) % STAGE_SLOTS;
+  StageSlot& s = stage[idx];
+  if (s.pending) {
+    // the slot's previous user: by now long finished unless the host is a whole ring ahead
+    SGK_CUDA(cudaEventSynchronize(s.done));
+    s.pending = false;
   }
-  // The staging list is reused by later copies: wait for earlier users first.
-  SGK_CUDA(cudaStreamSynchronize(pool->st->stream));
-  if (!a.empty())
-    SGK_CUDA(cudaMemcpy(pool->d_page_list, a.data(), a.size() * sizeof(int32_t), cudaMemcpyHostToDevice));
-  if (!b.empty())
-    SGK_CUDA(cudaMemcpy(pool->d_page_list + a.size(), b.data(), b.size() * sizeof(int32_t),
-                        cudaMemcpyHostToDevice));
+  if (need > s.cap) {
+    if (s.h) cudaFreeHost(s.h);
+    if (s.d) cudaFree(s.d);
+    s.h = nullptr, s.d = nullptr, s.cap = 0;
+    const int cap = std::max(need, 4096);
+    SGK_CUDA(cudaMallocHost(&s.h, size_t(cap) * sizeof(int32_t)));
+    SGK_CUDA(cudaMalloc(&s.d, size_t(cap) * sizeof(int32_t)));
+    s.cap = cap;
+  }
+  if (!s.done) SGK_CUDA(cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming));
+  if (na) std::memcpy(s.h, a, na * sizeof(int32_t));
+  if (nb) std::memcpy(s.h + na, b, nb * sizeof(int32_t));
+  SGK_CUDA(cudaMemcpyAsync(s.d, s.h, size_t(need) * sizeof(int32_t), cudaMemcpyHostToDevice, stream));
+  *slot_out = idx;
   return SGK_OK;
+}
+
+int Pool::stage_done(int slot, cudaStream_t stream) {
+  SGK_CUDA(cudaEventRecord(stage[slot].done, stream));
+  stage[slot].pending = true;
+  return SGK_OK;
+}
+
+void Pool::stage_free() {
+  for (StageSlot& s : stage) {
+    if (s.pending) cudaEventSynchronize(s.done);
+    if (s.done) cudaEventDestroy(s.done);
+    if (s.h) cudaFreeHost(s.h);
+    if (s.d) cudaFree(s.d);
+    s = StageSlot{};
+  }
 }
 
 int Pool::flush_scrub(cudaStream_t stream) {
@@ -101,9 +125,13 @@ int Pool::flush_scrub(cudaStream_t stream) {
     if (refcount[p] == 0) list.push_back(p);
   pending_scrub.clear();
   if (list.empty()) return SGK_OK;
-  SGK_TRY(upload_page_list(this, list, {}));
-  SGK_CUDA(launch_scrub_pages(d_base, d_page_list, static_cast<int>(list.size()), layer_b, layers, layer_stride, stream));
+  int slot;
+  SGK_TRY(stage_words(list.data(), list.size(), nullptr, 0, stream, &slot));
+  SGK_CUDA(launch_scrub_pages(d_base, stage[slot].d, static_cast<int>(list.size()), layer_b, layers, layer_stride,
+                              st->sm_count, stream));
   st->launches += 1;
+  SGK_TRY(stage_done(slot, stream));
+  // a scrubbed page may be handed out and written through another stream right after this call
   SGK_CUDA(cudaStreamSynchronize(stream));
   return SGK_OK;
 }
@@ -111,19 +139,26 @@ int Pool::flush_scrub(cudaStream_t stream) {
 int Pool::copy_pages(const std::vector<int32_t>& dst, const std::vector<int32_t>& src, cudaStream_t stream) {
   if (dst.size() != src.size()) return fail(SGK_ERR_DIMENSION, "copy_pages: list sizes differ");
   if (dst.empty() || host_only()) return SGK_OK;
-  SGK_TRY(upload_page_list(this, dst, src));
-  SGK_CUDA(launch_copy_pages(d_base, d_base, d_page_list, d_page_list + dst.size(), static_cast<int>(dst.size()),
-                             layer_b, layers, layer_stride, stream));
+  int slot;
+  SGK_TRY(stage_words(dst.data(), dst.size(), src.data(), src.size(), stream, &slot));
+  SGK_CUDA(launch_copy_pages(d_base, d_base, stage[slot].d, stage[slot].d + dst.size(), static_cast<int>(dst.size()),
+                             layer_b, layers, layer_stride, st->sm_count, stream));
   st->launches += 1;
-  return SGK_OK;
+  return stage_done(slot, stream);
 }
 
 // ---------------------------------------------------------------- Seq
-int Seq::publish(int64_t first_page, int64_t n) {
+int Seq::publish(int64_t first_page, int64_t n, cudaStream_t stream, bool ordered) {
   if (pool->host_only() || n <= 0) return SGK_OK;
-  SGK_CUDA(cudaMemcpy(pool->d_tables + int64_t(slot) * pool->table_stride + first_page, pages.data() + first_page,
-                      size_t(n) * sizeof(int32_t), cudaMemcpyHostToDevice));
-  return SGK_OK;
+  int32_t* dst = pool->d_tables + int64_t(slot) * pool->table_stride + first_page;
+  if (!ordered) {
+    SGK_CUDA(cudaMemcpy(dst, pages.data() + first_page, size_t(n) * sizeof(int32_t), cudaMemcpyHostToDevice));
+    return SGK_OK;
+  }
+  int s;
+  SGK_TRY(pool->stage_words(pages.data() + first_page, static_cast<size_t>(n), nullptr, 0, stream, &s));
+  SGK_CUDA(cudaMemcpyAsync(dst, pool->stage[s].d, size_t(n) * sizeof(int32_t), cudaMemcpyDeviceToDevice, stream));
+  return pool->stage_done(s, stream);
 }
 
 int Seq::reserve(int64_t tokens) {
@@ -373,7 +408,7 @@ int Batch::enqueue_append(cudaStream_t stream, const float* d_k, const float* d_
 
 int Batch::enqueue_attention(cudaStream_t stream, const float* d_q, float* d_out, int64_t window_start,
                              int64_t sliding_window, float attn_scalar, const float* d_k_new,
-                             const float* d_v_new, const Chain* chain) {
+                             const float* d_v_new) {
   if (d_q == nullptr || d_out == nullptr) return fail(SGK_ERR_BACKEND, "attention: null device pointer");
   const bool fused = d_k_new != nullptr;
   int kernel = choose_kernel();
@@ -412,9 +447,7 @@ int Batch::enqueue_attention(cudaStream_t stream, const float* d_q, float* d_out
   a.sliding_window = sliding_window;
   float scalar = attn_scalar > 0.0f ? attn_scalar : static_cast<float>(pool->head_dim);
   a.scale_log2e = 1.4426950408889634f / std::sqrt(scalar);
-  // Kill-switch of the token chain, in the spirit of the reference's RETI_RUST_* flags.
-  static const bool chain_off = std::getenv("SGK_NO_CHAIN") != nullptr;
-  const bool chained = !chain_off && chain != nullptr && chain->in_chain && kernel >= 2;
+  const bool chained = st->chain_member(stream) && kernel >= 2;
   a.splits = choose_splits(kernel, max_rows);
   a.pages_per_split = 0;
   if (kernel >= 2 && splits_override <= 0 && n() > 1) {
@@ -498,7 +531,7 @@ int Batch::enqueue_attention(cudaStream_t stream, const float* d_q, float* d_out
     // are read after the wait. C2 at batch 1, 48 layers in one graph: 18.6 -> 15.8 us per layer.
     if (chained) {
       a.pdl_trigger = 1;
-      a.pdl_wait = chain->prev_other_layer && chain->launches_after_prev == st->launches ? 1 : 0;
+      a.pdl_wait = st->chain_follows(stream) ? 1 : 0;
     }
     // Up to 16 splits run as one thread-block cluster and merge through distributed shared memory:
     // no partial goes through L2 and no device-wide atomic sits between the last page and the output.
@@ -546,6 +579,7 @@ int Batch::enqueue_attention(cudaStream_t stream, const float* d_q, float* d_out
     SGK_CUDA(launch_attention_generic(a, n(), stream));
   }
   st->launches += 1;
+  if (chained) st->chain_note();
   last_kernel = kernel;
   last_splits = a.splits;
   return SGK_OK;
@@ -570,27 +604,30 @@ int Step::enqueue(cudaStream_t stream, const float* k, const float* v, const flo
 
 int Step::enqueue_range(cudaStream_t stream, size_t l0, size_t l1, const float* k, const float* v, const float* q,
                         float* out, const int64_t* sliding_windows, float attn_scalar) {
-  int64_t after_previous = -1;   // the state's launch count right after the previous layer's attention launch
-  for (size_t l = l0; l < l1; ++l) {
+  // The layers of a step are a token chain of their own (unless the caller has opened one around
+  // the step): each launch lets the next one start early. Two launches over the SAME layer in a
+  // row (not a decode token) break it: the second reads the cursor the first one moves.
+  const bool own_chain = !st->chain_active && layers.size() > 1;
+  if (own_chain) {
+    st->chain_active = true;
+    st->chain_stream = stream;
+    st->chain_mark = -1;
+  }
+  int rc = SGK_OK;
+  for (size_t l = l0; l < l1 && rc == SGK_OK; ++l) {
     Batch* b = layers[l];
     size_t kv_stride = size_t(b->n()) * b->kvs[0]->kv_dim();
     size_t q_stride = size_t(b->n()) * b->kvs[0]->q_dim();
     int64_t before = st->launches;
-    // A launch follows the chain when the launch just before it on the stream is the previous
-    // layer's attention launch over the same sequences and another layer: one launch per enqueue
-    // and none in between (a copy-on-write or a table update would be one).
-    Batch::Chain chain;
-    chain.in_chain = layers.size() > 1;
     const Batch* prev = l > l0 ? layers[l - 1] : nullptr;
-    chain.prev_other_layer = prev != nullptr && (prev->pool != b->pool || prev->layer != b->layer);
-    chain.launches_after_prev = after_previous;
-    SGK_TRY(b->enqueue_attention(stream, q + l * q_stride, out + l * q_stride, 0,
-                                 sliding_windows ? sliding_windows[l] : 0, attn_scalar, k + l * kv_stride,
-                                 v + l * kv_stride, &chain));
-    after_previous = st->launches;
+    if (prev != nullptr && prev->pool == b->pool && prev->layer == b->layer) st->chain_break();
+    rc = b->enqueue_attention(stream, q + l * q_stride, out + l * q_stride, 0,
+                              sliding_windows ? sliding_windows[l] : 0, attn_scalar, k + l * kv_stride,
+                              v + l * kv_stride);
     launches += st->launches - before;
   }
-  return SGK_OK;
+  if (own_chain) st->chain_active = false;
+  return rc;
 }
 
 // ---------------------------------------------------------------- LinState

@@ -105,36 +105,209 @@ Hash32 hash_chain(const Hash32& prev, const uint64_t* tokens, size_t n) {
 // ---- Prefix ----------------------------------------------------------------------
 int64_t Prefix::pinned_bytes() const {
   int64_t page_bytes = pool ? pool->page_b : 0;
-  return static_cast<int64_t>(pins.size()) * page_bytes + state_bytes;
+  return pinned_pages * page_bytes + state_bytes;
 }
 
 int64_t Prefix::session_count(const Hash32& s) const {
-  int64_t n = 0;
-  for (const auto& e : entries) n += e.session == s ? 1 : 0;
-  return n;
+  auto it = sessions.find(s);
+  return it == sessions.end() ? 0 : static_cast<int64_t>(it->second.size());
 }
 
-void Prefix::drop(size_t index, bool log) {
-  PrefixEntry& e = entries[index];
-  if (log) evicted_log.push_back(PrefixKey{e.session, e.hash, e.tokens});
-  for (int32_t p : e.pages) {
-    auto it = pins.find(p);
-    if (it != pins.end() && --it->second == 0) pins.erase(it);
-    if (pool) pool->release(p);
+// Moves an entry to the front of the cache and of its session's list (cache.rs:139-146).
+void Prefix::touch(PrefixList::iterator it) {
+  entries.splice(entries.begin(), entries, it);
+  auto& list = sessions[it->key.session];
+  list.splice(list.begin(), list, it->in_session);
+}
+
+// Gives up one reference to a run; a run nobody holds any more returns its pages to the pool and
+// lets go of the block before it (a loop, not a recursion: a chain may be thousands of blocks deep).
+void Prefix::release_run(std::shared_ptr<PageRun>& run) {
+  std::shared_ptr<PageRun> cur = std::move(run);
+  run.reset();
+  while (cur && cur.use_count() == 1) {
+    if (!cur->pages.empty()) {
+      auto it = run_by_last_page.find(cur->pages.back());
+      if (it != run_by_last_page.end()) {
+        auto held = it->second.lock();
+        if (!held || held.get() == cur.get()) run_by_last_page.erase(it);
+      }
+    }
+    for (int32_t p : cur->pages)
+      if (pool) pool->release(p);
+    pinned_pages -= static_cast<int64_t>(cur->pages.size());
+    std::shared_ptr<PageRun> parent = std::move(cur->parent);
+    cur = std::move(parent);
   }
-  if (e.ls) state_bytes -= e.ls->estimated_bytes();
-  entries.erase(entries.begin() + static_cast<long>(index));
+}
+
+void Prefix::collect_pages(const PageRun* run, std::vector<int32_t>* out) const {
+  std::vector<const PageRun*> chain;
+  for (const PageRun* r = run; r != nullptr; r = r->parent.get()) chain.push_back(r);
+  for (auto it = chain.rbegin(); it != chain.rend(); ++it) out->insert(out->end(), (*it)->pages.begin(), (*it)->pages.end());
+}
+
+std::shared_ptr<PageRun> Prefix::chain_for(const Seq* seq, int64_t tokens, bool create, int64_t* fresh_pages) {
+  const int64_t per_block = block_tokens / PAGE_TOKENS;
+  const int64_t n_blocks = tokens / block_tokens;
+  const int64_t n_pages = tokens / PAGE_TOKENS;
+  // The deepest live run that holds exactly the sequence's pages [0, its end): found through the
+  // last page of a block, then compared page by page down to the root.
+  std::shared_ptr<PageRun> base;
+  int64_t base_blocks = 0;
+  for (int64_t b = n_blocks; b >= 1 && !base; --b) {
+    auto it = run_by_last_page.find(seq->pages[b * per_block - 1]);
+    if (it == run_by_last_page.end()) continue;
+    std::shared_ptr<PageRun> cand = it->second.lock();
+    if (!cand) continue;
+    bool same = true;
+    int64_t depth = 0;
+    for (const PageRun* r = cand.get(); r != nullptr && same; r = r->parent.get()) {
+      ++depth;
+      const int64_t blk = b - depth;   // block index this run must be
+      if (blk < 0 || r->first_page != blk * per_block || static_cast<int64_t>(r->pages.size()) != per_block) {
+        same = false;
+        break;
+      }
+      for (int64_t i = 0; i < per_block; ++i) same = same && r->pages[i] == seq->pages[r->first_page + i];
+    }
+    if (same && depth == b) {
+      base = cand;
+      base_blocks = b;
+    }
+  }
+  if (fresh_pages) *fresh_pages = n_pages - base_blocks * per_block;
+  if (!create) return base_blocks == n_blocks ? base : nullptr;
+  for (int64_t b = base_blocks; b < n_blocks; ++b) {
+    auto run = std::make_shared<PageRun>();
+    run->first_page = b * per_block;
+    run->pages.assign(seq->pages.begin() + b * per_block, seq->pages.begin() + (b + 1) * per_block);
+    run->parent = base;
+    for (int32_t p : run->pages) pool->retain(p);
+    pinned_pages += per_block;
+    run_by_last_page[run->pages.back()] = run;
+    base = run;
+  }
+  return base;
+}
+
+void Prefix::drop(PrefixList::iterator it, bool log) {
+  if (log) evicted_log.push_back(it->key);
+  index.erase(it->key);
+  by_id.erase(it->id);
+  auto sess = sessions.find(it->key.session);
+  if (sess != sessions.end()) {
+    sess->second.erase(it->in_session);
+    if (sess->second.empty()) sessions.erase(sess);
+  }
+  if (it->ls) state_bytes -= it->ls->estimated_bytes();
+  entry_bytes -= it->bytes;
+  release_run(it->run);
+  entries.erase(it);
 }
 
 bool Prefix::evict_lru(int64_t* bytes_out) {
   if (entries.empty()) return false;
   if (bytes_out) *bytes_out = entries.back().bytes;
-  drop(entries.size() - 1, true);
+  drop(std::prev(entries.end()), true);
   return true;
 }
 
 Prefix::~Prefix() {
-  while (!entries.empty()) drop(entries.size() - 1, false);
+  while (!entries.empty()) drop(std::prev(entries.end()), false);
+}
+
+void Prefix::match(const Hash32& session, const uint64_t* tokens, size_t n, int64_t* tokens_out, Hash32* hash_out,
+                   uint64_t* entry_out) {
+  *entry_out = 0;
+  *tokens_out = 0;
+  if (capacity == 0) return;   // cache.rs:127-129
+  Hash32 previous = session;
+  const size_t bt = static_cast<size_t>(block_tokens);
+  for (size_t i = 0; i < n / bt; ++i) {
+    const Hash32 hash = hash_chain(previous, tokens + i * bt, bt);
+    auto it = index.find(PrefixKey{session, hash, static_cast<int64_t>((i + 1) * bt)});
+    if (it == index.end()) break;   // stop at the first miss (cache.rs:134-138)
+    touch(it->second);              // every touched block moves to the front (cache.rs:139-146)
+    *tokens_out = it->second->key.tokens;
+    *hash_out = hash;
+    *entry_out = it->second->id;
+    previous = hash;
+  }
+}
+
+int Prefix::insert(const Hash32& session, const Hash32& hash, int64_t tokens, Seq* seq, LinState* ls, void* stream,
+                   int32_t* inserted_out) {
+  if (inserted_out) *inserted_out = 0;
+  if (capacity == 0) return SGK_OK;  // cache.rs:162-164
+  if (tokens <= 0) return fail(SGK_ERR_DIMENSION, "prefix block boundary must be positive");
+  if (pool && !seq) return fail(SGK_ERR_BACKEND, "prefix insert needs the sequence to snapshot");
+  if (seq) {
+    if (seq->pool != pool) return fail(SGK_ERR_CONFIG, "sequence belongs to another pool");
+    if (tokens % block_tokens != 0)
+      return fail(SGK_ERR_DIMENSION, "snapshot boundary %lld is not on a block boundary", (long long)tokens);
+    for (int64_t l : seq->len)
+      if (l < tokens)
+        return fail(SGK_ERR_DIMENSION, "snapshot of %lld rows from a sequence holding %lld", (long long)tokens, (long long)l);
+    if (seq->released_pages > 0) return fail(SGK_ERR_DIMENSION, "snapshot of a sequence whose head was released");
+  }
+  const PrefixKey key{session, hash, tokens};
+  const bool scrub = pool && !pool->host_only();
+  // Budget loop of remember_prefix_block (src/serve/state.rs:627-635), run BEFORE the insert and
+  // therefore with an older duplicate of this block still in the cache: what the new entry adds is
+  // the pages no live run holds yet plus its state snapshot.
+  auto additional = [&]() {
+    int64_t fresh = 0;
+    if (seq) chain_for(seq, tokens, false, &fresh);
+    return fresh * (pool ? pool->page_b : 0) + (ls ? ls->estimated_bytes() : 0);
+  };
+  if (budget > 0) {
+    while (pinned_bytes() + additional() > budget) {
+      if (!evict_lru(nullptr)) {
+        if (scrub) SGK_TRY(pool->flush_scrub(pool->st->stream));
+        return SGK_OK;  // cache empty and still over budget: skip the insert
+      }
+    }
+  }
+  PrefixEntry e;
+  e.key = key;
+  e.bytes = additional();
+  auto dup = index.find(key);
+  // a refresh over the same pages takes over what its duplicate accounted for
+  if (dup != index.end() && e.bytes < dup->second->bytes) e.bytes = dup->second->bytes;
+  // The new entry's pages are pinned before the duplicate lets go of the same ones.
+  if (seq) e.run = chain_for(seq, tokens, true, nullptr);
+  // a refresh replaces the older duplicate without counting as an eviction (cache.rs:165-169)
+  if (dup != index.end()) drop(dup->second, false);
+  if (ls) {
+    LinState* snap = nullptr;
+    int rc = linstate_snapshot(ls, stream, &snap);
+    if (rc != SGK_OK) {
+      release_run(e.run);
+      return rc;
+    }
+    e.ls.reset(snap);
+    state_bytes += snap->estimated_bytes();
+  }
+  e.id = next_id++;
+  entry_bytes += e.bytes;
+  entries.push_front(std::move(e));  // cache.rs:173-183
+  auto it = entries.begin();
+  index[key] = it;
+  by_id[it->id] = it;
+  auto& list = sessions[session];
+  list.push_front(it);
+  it->in_session = list.begin();
+  // per-session cap: that session's rear-most entries leave first (cache.rs:184-188)
+  while (session_count(session) > blocks_per_session) {
+    auto sess = sessions.find(session);
+    if (sess == sessions.end() || sess->second.empty()) break;
+    drop(sess->second.back(), true);
+  }
+  while (static_cast<int64_t>(entries.size()) > capacity) drop(std::prev(entries.end()), true);  // :189-191
+  if (scrub) SGK_TRY(pool->flush_scrub(pool->st->stream));
+  if (inserted_out) *inserted_out = 1;
+  return SGK_OK;
 }
 
 // ---- Budget (src/memory_guard.rs:168-185) -------------------------------------------

@@ -139,13 +139,13 @@ cudaError_t launch_gather(const GatherArgs& a, cudaStream_t stream);
 // apart (16-byte vectors).
 cudaError_t launch_copy_pages(uint8_t* dst_base, const uint8_t* src_base, const int32_t* d_dst_pages,
                               const int32_t* d_src_pages, int n_pages, int64_t page_bytes, int n_layers,
-                              int64_t layer_stride,
+                              int64_t layer_stride, int sm_count,
                               cudaStream_t stream);
 // Contiguous device copy (linear-state snapshot / restore).
 cudaError_t launch_copy_bytes(void* dst, const void* src, int64_t bytes, cudaStream_t stream);
 // Zero-fill of freed pages (eviction scrub).
 cudaError_t launch_scrub_pages(uint8_t* base, const int32_t* d_pages, int n_pages, int64_t page_bytes, int n_layers,
-                               int64_t layer_stride,
+                               int64_t layer_stride, int sm_count,
                                cudaStream_t stream);
 // Gated DeltaNet step on one layer's state [H_v][d_v][d_k] (f32 or bf16).
 constexpr int GATED_DELTA_MAX_STATES = 64;
@@ -161,10 +161,28 @@ struct GatedDeltaArgs {
   const float* g;     // [n_states][n_tokens][H_v] decay
   const float* beta;  // [n_states][n_tokens][H_v] write gate
   float* out;         // [n_states][n_tokens][H_v * d_v]
+  // member of a token chain: lets the next launch start early / was itself launched with programmatic
+  // stream serialisation and reads the state before, its inputs after, the wait for the previous launch
+  int32_t pdl_trigger, pdl_wait;
 };
-cudaError_t launch_gated_delta_step(const GatedDeltaArgs& a, cudaStream_t stream);
+cudaError_t launch_gated_delta_step(const GatedDeltaArgs& a, int sm_count, cudaStream_t stream);
 cudaError_t launch_conv_step(const float* qkv, const float* weight, float* history, float* out, int conv_dim,
-                             int kernel, int n_tokens, cudaStream_t stream);
+                             int kernel, int n_tokens, int pdl_trigger, int pdl_wait, cudaStream_t stream);
+// Launch configuration shared by the small kernels of a token chain.
+struct ChainLaunch {
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr[1];
+  ChainLaunch(dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl_wait) {
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_wait ? 1 : 0;
+  }
+};
 // Greedy epilogue: argmax over W . x without materialising the logits.
 struct LmHeadArgs {
   const void* w;   // [vocab][hidden], f32 or bf16

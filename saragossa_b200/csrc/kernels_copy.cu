@@ -6,6 +6,20 @@
 
 namespace sgk {
 
+// SMs of the current device (asked once per device).
+static int current_sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 132;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 132;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+
 // ---- gather -------------------------------------------------------------------
 __global__ void __launch_bounds__(256) gather_rows_kernel(GatherArgs a) {
   const int hd = a.pool.head_dim, kvh = a.pool.kv_heads;
@@ -55,7 +69,7 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(GatherArgs a) {
 cudaError_t launch_gather(const GatherArgs& a, cudaStream_t stream) {
   int64_t total = a.n * a.pool.kv_heads * a.pool.head_dim;
   int blocks = static_cast<int>(total / 256 + 1);
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > current_sm_count() * 8) blocks = current_sm_count() * 8;
   gather_rows_kernel<<<blocks, 256, 0, stream>>>(a);
   return cudaGetLastError();
 }
@@ -101,18 +115,18 @@ __global__ void __launch_bounds__(COPY_THREADS) copy_pages_kernel(uint8_t* __res
   }
 }
 
-static int copy_grid(int64_t items) {
-  int64_t g = 148 * 8;
+static int copy_grid(int64_t items, int sm_count = 0) {
+  int64_t g = int64_t(sm_count > 0 ? sm_count : current_sm_count()) * 8;
   if (items < g) g = items;
   return static_cast<int>(g < 1 ? 1 : g);
 }
 
 cudaError_t launch_copy_pages(uint8_t* dst_base, const uint8_t* src_base, const int32_t* d_dst_pages,
                               const int32_t* d_src_pages, int n_pages, int64_t page_bytes, int n_layers,
-                              int64_t layer_stride, cudaStream_t stream) {
+                              int64_t layer_stride, int sm_count, cudaStream_t stream) {
   if (n_pages <= 0) return cudaSuccess;
   int64_t items = ((page_bytes + COPY_PIECE - 1) / COPY_PIECE) * n_layers * n_pages;
-  copy_pages_kernel<<<copy_grid(items), COPY_THREADS, 0, stream>>>(dst_base, src_base, d_dst_pages, d_src_pages,
+  copy_pages_kernel<<<copy_grid(items, sm_count), COPY_THREADS, 0, stream>>>(dst_base, src_base, d_dst_pages, d_src_pages,
                                                                    n_pages, page_bytes, n_layers, layer_stride);
   return cudaGetLastError();
 }
@@ -157,10 +171,10 @@ __global__ void __launch_bounds__(COPY_THREADS) scrub_pages_kernel(uint8_t* base
 }
 
 cudaError_t launch_scrub_pages(uint8_t* base, const int32_t* d_pages, int n_pages, int64_t page_bytes, int n_layers,
-                               int64_t layer_stride, cudaStream_t stream) {
+                               int64_t layer_stride, int sm_count, cudaStream_t stream) {
   if (n_pages <= 0) return cudaSuccess;
   int64_t total = page_bytes / 16 * n_layers * n_pages;
-  scrub_pages_kernel<<<copy_grid((total + COPY_THREADS - 1) / COPY_THREADS), COPY_THREADS, 0, stream>>>(
+  scrub_pages_kernel<<<copy_grid((total + COPY_THREADS - 1) / COPY_THREADS, sm_count), COPY_THREADS, 0, stream>>>(
       base, d_pages, n_pages, page_bytes, n_layers, layer_stride);
   return cudaGetLastError();
 }
@@ -198,7 +212,7 @@ cudaError_t launch_fill_normal(float* out, int64_t n, uint64_t seed, uint64_t st
   x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
   uint64_t key = x ^ (x >> 31);
   int64_t blocks = (n + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > int64_t(current_sm_count()) * 16) blocks = int64_t(current_sm_count()) * 16;
   fill_normal_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(out, n, key, index0);
   return cudaGetLastError();
 }

@@ -4,9 +4,15 @@
 // on the state [H_v][d_v][d_k] (src/linear_attention.rs:802-852,896-991; Metal twins
 // linear_attn_gated_delta_* in src/metal_backend/mod.rs:155-171). Both are HBM-bound:
 // the state is read once and written once per token (4 MiB per layer at 32 x 128 x 128 f32).
+#include <cstdlib>
+
 #include "kernels.h"
 
 namespace sgk {
+
+// Programmatic dependent launch (see mma_common.cuh): no-ops in a launch without such a neighbour.
+__device__ __forceinline__ void lin_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void lin_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 constexpr int GD_THREADS = 256;
 constexpr int GD_WARPS = GD_THREADS / 32;
@@ -42,6 +48,8 @@ __global__ void __launch_bounds__(GD_THREADS) gated_delta_step_kernel(GatedDelta
   const int b = blockIdx.y;
   void* ssm = a.ssm[b];
   const int T = a.n_tokens;
+  if (a.pdl_trigger) lin_pdl_trigger();
+  if (a.pdl_wait) lin_pdl_wait();
   const float* q_b = a.q + int64_t(b) * T * a.num_key_heads * dk;
   const float* k_b = a.k + int64_t(b) * T * a.num_key_heads * dk;
   const float* v_b = a.v + int64_t(b) * T * rows;
@@ -112,6 +120,7 @@ __global__ void __launch_bounds__(GD_THREADS) gated_delta_step_dk128_kernel(Gate
   const int repeat = a.num_value_heads / a.num_key_heads;
   const int b = blockIdx.y;
   const int row0 = (blockIdx.x * GD_WARPS + (threadIdx.x >> 5)) * R;  // value_head_dim % R == 0
+  if (a.pdl_trigger) lin_pdl_trigger();
   if (row0 >= rows) return;
   const int vh = row0 / a.value_head_dim;
   const int kh = vh / repeat;
@@ -132,6 +141,9 @@ __global__ void __launch_bounds__(GD_THREADS) gated_delta_step_dk128_kernel(Gate
 #pragma unroll
     for (int r = 0; r < R; ++r) s[r] = *reinterpret_cast<const float4*>(p + r * 128);
   }
+  // The state rows are on their way; q, k, v, g and beta are what the previous launch of a token
+  // chain may still be writing.
+  if (a.pdl_wait) lin_pdl_wait();
   // the tokens of a sequence run on the rows kept in registers; they go back to memory once
   for (int t = 0; t < T; ++t) {
     const int64_t tok = int64_t(b) * T + t;
@@ -187,35 +199,33 @@ __global__ void __launch_bounds__(GD_THREADS) gated_delta_step_dk128_kernel(Gate
 }
 
 template <bool BF16, int R>
-static void launch_dk128(const GatedDeltaArgs& a, int rows, cudaStream_t stream) {
+static cudaError_t launch_dk128(const GatedDeltaArgs& a, int rows, cudaStream_t stream) {
   const int warps = rows / R;
-  dim3 grid((warps + GD_WARPS - 1) / GD_WARPS, a.n_states);
-  gated_delta_step_dk128_kernel<BF16, R><<<grid, GD_THREADS, 0, stream>>>(a);
+  ChainLaunch l(dim3((warps + GD_WARPS - 1) / GD_WARPS, a.n_states), dim3(GD_THREADS), 0, stream, a.pdl_wait != 0);
+  return cudaLaunchKernelEx(&l.cfg, gated_delta_step_dk128_kernel<BF16, R>, a);
 }
 
-cudaError_t launch_gated_delta_step(const GatedDeltaArgs& a, cudaStream_t stream) {
+cudaError_t launch_gated_delta_step(const GatedDeltaArgs& a, int sm_count, cudaStream_t stream) {
   const int rows = a.num_value_heads * a.value_head_dim;
   const bool aligned = ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k)) & 15) == 0;
   if (a.key_head_dim == 128 && aligned) {
     // four rows per warp once that still leaves every SM several blocks; else one row per warp
-    const bool wide = a.value_head_dim % 4 == 0 && int64_t(rows) * a.n_states >= int64_t(4) * GD_WARPS * 148 * 4;
-    if (a.ssm_bf16) {
-      wide ? launch_dk128<true, 4>(a, rows, stream) : launch_dk128<true, 1>(a, rows, stream);
-    } else {
-      wide ? launch_dk128<false, 4>(a, rows, stream) : launch_dk128<false, 1>(a, rows, stream);
-    }
-    return cudaGetLastError();
+    static const int wide_rows = [] {
+      const char* e = std::getenv("SGK_GD_WIDE_ROWS");
+      return e ? std::atoi(e) : 0;
+    }();
+    const int64_t need = wide_rows > 0 ? wide_rows : int64_t(4) * GD_WARPS * sm_count * 4;
+    const bool wide = a.value_head_dim % 4 == 0 && int64_t(rows) * a.n_states >= need;
+    if (a.ssm_bf16) return wide ? launch_dk128<true, 4>(a, rows, stream) : launch_dk128<true, 1>(a, rows, stream);
+    return wide ? launch_dk128<false, 4>(a, rows, stream) : launch_dk128<false, 1>(a, rows, stream);
   }
   int blocks = (rows + GD_WARPS - 1) / GD_WARPS;
   // 8 resident blocks per SM over the whole grid; one row per warp needs no more than that
-  int cap = (148 * 8 + a.n_states - 1) / a.n_states;
+  int cap = (sm_count * 8 + a.n_states - 1) / a.n_states;
   if (blocks > cap) blocks = cap;
-  dim3 grid(blocks, a.n_states);
-  if (a.ssm_bf16)
-    gated_delta_step_kernel<true><<<grid, GD_THREADS, 0, stream>>>(a);
-  else
-    gated_delta_step_kernel<false><<<grid, GD_THREADS, 0, stream>>>(a);
-  return cudaGetLastError();
+  ChainLaunch l(dim3(blocks, a.n_states), dim3(GD_THREADS), 0, stream, a.pdl_wait != 0);
+  return a.ssm_bf16 ? cudaLaunchKernelEx(&l.cfg, gated_delta_step_kernel<true>, a)
+                    : cudaLaunchKernelEx(&l.cfg, gated_delta_step_kernel<false>, a);
 }
 
 // One thread per channel: the products are summed in kernel-tap order with separate
@@ -225,8 +235,9 @@ constexpr int CONV_MAX_KERNEL = 16;
 __global__ void __launch_bounds__(256) conv_step_kernel(const float* __restrict__ qkv,
                                                        const float* __restrict__ weight, float* history,
                                                        float* __restrict__ out, int conv_dim, int kernel,
-                                                       int n_tokens) {
+                                                       int n_tokens, int pdl_trigger, int pdl_wait) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (pdl_trigger) lin_pdl_trigger();
   if (c >= conv_dim) return;
   const int keep = kernel - 1;
   // the channel's taps and its window of past inputs stay in registers over the tokens
@@ -236,6 +247,7 @@ __global__ void __launch_bounds__(256) conv_step_kernel(const float* __restrict_
     w[kk] = kk < kernel ? weight[int64_t(c) * kernel + kk] : 0.0f;
     h[kk] = kk < keep ? history[int64_t(kk) * conv_dim + c] : 0.0f;
   }
+  if (pdl_wait) lin_pdl_wait();   // the taps and the history are here; qkv comes from the previous launch
   for (int t = 0; t < n_tokens; ++t) {
     const float x = qkv[int64_t(t) * conv_dim + c];
     float acc = 0.0f;
@@ -253,9 +265,10 @@ __global__ void __launch_bounds__(256) conv_step_kernel(const float* __restrict_
 }
 
 cudaError_t launch_conv_step(const float* qkv, const float* weight, float* history, float* out, int conv_dim,
-                             int kernel, int n_tokens, cudaStream_t stream) {
-  conv_step_kernel<<<(conv_dim + 255) / 256, 256, 0, stream>>>(qkv, weight, history, out, conv_dim, kernel, n_tokens);
-  return cudaGetLastError();
+                             int kernel, int n_tokens, int pdl_trigger, int pdl_wait, cudaStream_t stream) {
+  ChainLaunch l(dim3((conv_dim + 255) / 256), dim3(256), 0, stream, pdl_wait != 0);
+  return cudaLaunchKernelEx(&l.cfg, conv_step_kernel, qkv, weight, history, out, conv_dim, kernel, n_tokens,
+                            pdl_trigger, pdl_wait);
 }
 
 }  // namespace sgk

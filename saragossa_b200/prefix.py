@@ -91,6 +91,19 @@ class BlockAwarePrefixCache:
                                        linear_state.h if linear_state is not None else None, stream, C.byref(ins)))
         return bool(ins.value)
 
+    def insert_chain(self, root: bytes, tokens, seq, from_tokens=0, stream=None):
+        """Remembers every full block of the prompt beyond from_tokens in one call (the loop of
+        prefill_prompt_state, src/serve/state.rs:596-604). Returns (blocks inserted, last hash)."""
+        t = _tokens(tokens)
+        ins, h_out = C.c_int32(), (C.c_uint8 * 32)()
+        check(self.L.sgk_prefix_insert_chain(self.h, _h32(root), t.ctypes.data, t.size, from_tokens,
+                                             seq.h if seq is not None else None, stream, C.byref(ins), h_out))
+        return ins.value, bytes(h_out)
+
+    def pinned_bytes(self):
+        """Distinct pages the cache pins x page bytes + state snapshots: what the budget bounds."""
+        return self.L.sgk_prefix_pinned_bytes(self.h)
+
     def restore(self, hit_or_entry, seq, linear_state=None, share=False, stream=None) -> int:
         entry = hit_or_entry.entry if isinstance(hit_or_entry, PrefixBlockHit) else hit_or_entry
         copied = C.c_int64()

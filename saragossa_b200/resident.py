@@ -245,6 +245,13 @@ class DecodeResidentState:
         """Says that launches of this state may run on two streams at once (default: they do not)."""
         check(self.L.sgk_state_set_concurrent_streams(self.h, 1 if enabled else 0))
 
+    def chain_begin(self, stream=None):
+        """Opens a token chain on `stream`: the enqueues up to chain_end are one decode token."""
+        check(self.L.sgk_state_chain_begin(self.h, stream))
+
+    def chain_end(self):
+        check(self.L.sgk_state_chain_end(self.h))
+
     def selftest_wait_timeout(self):
         """Runs the kernel whose wait must expire; raises InferError(kind='Timeout') when it did."""
         check(self.L.sgk_state_selftest_wait_timeout(self.h))

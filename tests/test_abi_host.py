@@ -144,7 +144,7 @@ def test_host_only_pool_accounting_and_budget_eviction():
     cache = sg.BlockAwarePrefixCache(16, 100, pool=pool, budget_bytes=budget)
     ref = sgo.BlockAwarePrefixCache(16, 100)
     pins, seqs = {}, {}
-    for name in ("a", "b", "c", "a"):
+    for name in ("a", "b", "c", "b", "a", "c", "c", "a"):
         root = sg.BlockHash.for_session(name)
         if name not in seqs:
             seq = pool.sequence(512)
@@ -159,10 +159,11 @@ def test_host_only_pool_accounting_and_budget_eviction():
             prev = sg.BlockHash.chain(prev, toks[16 * i:16 * i + 16])
             # oracle side: the reference's loop with this build's accounting (unique pinned pages)
             pages = list(seq.block_table()[:i + 1])
-            dup = [e for e in ref.entries() if e[1] == prev]
             skip = False
             while True:
-                live = set(p for e in ref.entries() if e[1] != prev for p in pins[e[1]])
+                # the budget loop runs before the insert, with an older duplicate of the block still
+                # cached (src/serve/state.rs:627-635 before cache.rs:165-169)
+                live = set(p for e in ref.entries() for p in pins[e[1]])
                 fresh = len(set(pages) - live)
                 if (len(live) + fresh) * page_bytes <= budget:
                     break
@@ -177,13 +178,15 @@ def test_host_only_pool_accounting_and_budget_eviction():
             assert [e[1] for e in cache.entries()] == [e[1] for e in ref.entries()]
     assert cache.evicted() == [(s, h, t) for s, h, t, _ in ref.evicted()]
     assert len(cache.evicted()) > 0 and len(cache) > 0
-    # an entry pins its whole prefix: the first page of a cached chain is shared by its entries
+    # an entry pins its whole prefix, and the cache holds every page of a chain once however many
+    # entries lie on it: the first page is held by the sequence and by ONE run of the cache
     root = sg.BlockHash.for_session("a")
     toks = [ord("a") * 1000 + i for i in range(80)]
     hit = cache.match_prefix(root, toks)
     assert hit is not None and hit.tokens == 80
     first = int(seqs["a"].block_table()[0])
-    holders = sum(1 for e in cache.entries() if e[0] == root)
+    assert sum(1 for e in cache.entries() if e[0] == root) > 1
+    holders = 1
     assert pool.refcount(first) == 1 + holders
     free_before = pool.free_pages
     other = pool.sequence(512)
@@ -196,4 +199,87 @@ def test_host_only_pool_accounting_and_budget_eviction():
         seq.close()
     cache.close()
     assert pool.free_pages == 64
+    pool.close()
+
+
+def test_large_prefix_cache_trace_matches_oracle():
+    """Thousands of 16-token blocks: the hash index and the relinked list give the same hits, the
+    same entry order and the same evicted keys as the reference's Vec scans, op by op."""
+    rng = random.Random(11)
+    block, capacity, per_session = 16, 3000, 1200
+    ours = sg.BlockAwarePrefixCache(block, capacity, per_session)
+    ref = sgo.BlockAwarePrefixCache(block, capacity, per_session)
+    sessions = [None] + [f"s{i}" for i in range(5)]
+    system = [rng.randrange(0, 50000) for _ in range(40 * block)]
+    prompts = [system[:rng.randrange(8, 41) * block] + [rng.randrange(0, 50000) for _ in range(rng.randrange(1, 60) * block)]
+               for _ in range(24)]
+    ops = 0
+    for step in range(3000):
+        root = sg.BlockHash.for_session(rng.choice(sessions))
+        toks = rng.choice(prompts)
+        op = rng.random()
+        if op < 0.5:
+            hit, want = ours.match_prefix(root, toks), ref.match_prefix(root, toks)
+            assert (hit is None) == (want is None)
+            if hit is not None:
+                assert (hit.tokens, hit.hash) == (want["tokens"], want["hash"])
+                ops += hit.tokens // block        # blocks looked up and moved to the front
+            ops += 1
+        elif op < 0.97:
+            hit = ref.match_prefix(root, toks)
+            ours.match_prefix(root, toks)
+            start = hit["tokens"] if hit is not None else 0
+            inserted, last = ours.insert_chain(root, toks, None, from_tokens=start)
+            prev = root
+            for i in range(len(toks) // block):
+                prev = sg.BlockHash.chain(prev, toks[i * block:(i + 1) * block])
+                if (i + 1) * block > start:
+                    ref.insert(root, prev, (i + 1) * block)
+                    ops += 1
+            assert last == prev and inserted == len(toks) // block - start // block
+        else:
+            for _ in range(rng.randrange(1, 40)):
+                got, want = ours.evict_lru_block(), ref.evict_lru_block()
+                assert (got is None) == (want is None)
+                ops += 1
+        if step % 50 == 0:
+            assert [(s, h, t) for s, h, t in ours.entries()] == [(s, h, t) for s, h, t, _ in ref.entries()]
+    assert [(s, h, t) for s, h, t in ours.entries()] == [(s, h, t) for s, h, t, _ in ref.entries()]
+    assert ours.evicted() == [(s, h, t) for s, h, t, _ in ref.evicted()]
+    assert ops > 50_000 and len(ours) > 2000 and len(ours.evicted()) > 1000, (ops, len(ours), len(ours.evicted()))
+
+
+def test_failed_restore_leaves_the_sequence_as_it_was():
+    """A physical restore that the pool cannot hold fails with MemoryGuard before anything is
+    touched: the sequence keeps its pages, its block table and its cursors."""
+    pool = sg.PagePool(None, layers=1, kv_heads=1, head_dim=64, dtype=sg.KV_BF16, num_pages=12, max_seqs=4,
+                       max_seq_tokens=256)
+    cache = sg.BlockAwarePrefixCache(16, 100, pool=pool)
+    a = pool.sequence(128)
+    a.reserve(6 * 16)
+    a.layer(0, 1).truncate(96)
+    root = sg.BlockHash.for_session("a")
+    toks = list(range(96))
+    assert cache.insert_chain(root, toks, a)[0] == 6
+    hit = cache.match_prefix(root, toks)
+    assert hit.tokens == 96
+    b = pool.sequence(128)
+    b.reserve(2 * 16)
+    b.layer(0, 1).truncate(20)
+    table_before, free_before = list(b.block_table()), pool.free_pages
+    assert free_before == 4                      # 6 + 2 of 12 in use: 6 needed, 4 free + 2 of its own
+    c = pool.sequence(128)
+    c.reserve(16)                                # now 3 free + 2 own = 5 < 6
+    with pytest.raises(sg.InferError) as e:
+        cache.restore(hit, b)
+    assert e.value.kind == "MemoryGuard"
+    assert list(b.block_table()) == table_before and b.layer(0, 1).len() == 20
+    assert pool.free_pages == 3
+    c.close()
+    assert cache.restore(hit, b) == 6 * pool.page_bytes    # 4 free + 2 own: fits, by giving its own pages back first
+    assert b.layer(0, 1).len() == 96 and pool.free_pages == 0
+    for s in (a, b):
+        s.close()
+    cache.close()
+    assert pool.free_pages == 12
     pool.close()

@@ -262,3 +262,79 @@ def test_conv_sequence_equals_the_step_loop_bit_for_bit(state, conv_dim, kernel)
     assert e.value.kind in ("Config", "Dimension")
     a.close()
     b.close()
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_token_chain_of_recurrent_layers_equals_plain_enqueues(state, graph):
+    """Inside a token chain the conv and gated-delta launches of consecutive layers overlap their
+    neighbours (each reads its own layer's state before it waits for the launch before it, its
+    inputs after). Outputs, recurrent states and conv histories must be what the same enqueues
+    give outside a chain, bit for bit, in stream mode and captured into a CUDA graph."""
+    import torch
+    shape = (2, 4, 128, 64)
+    hk, hv, dk, dv = shape
+    layers, kernel, tokens = 3, 4, 3
+    conv_dim = 2 * hk * dk + hv * dv
+    ssm_len = hv * dv * dk
+    w = [sgo.fill_normal8(conv_dim * kernel, 41, layer) * np.float32(0.5) for layer in range(layers)]
+    results = []
+    for chained in (False, True):
+        ls = sg.LinearAttentionState(state, layers, (kernel - 1) * conv_dim, ssm_len)
+        for layer in range(layers):
+            ls.write(layer, sgo.fill_normal8((kernel - 1) * conv_dim, 42, layer),
+                     sgo.fill_normal8(ssm_len, 43, layer) * np.float32(0.1))
+        d_w = [state.upload(x) for x in w]
+        d_x, d_in = state.alloc(4 * conv_dim * layers), [state.alloc(4 * n * layers) for n in (hk * dk, hk * dk, hv * dv, hv, hv)]
+        d_c, d_y = state.alloc(4 * conv_dim * layers), state.alloc(4 * hv * dv * layers)
+        stream = torch.cuda.Stream()
+
+        def token():
+            if chained:
+                state.chain_begin(stream.cuda_stream)
+            for layer in range(layers):
+                ls.encode_conv_step(layer, _Off(d_x, 4 * conv_dim * layer), d_w[layer], conv_dim, kernel,
+                                    _Off(d_c, 4 * conv_dim * layer), stream=stream.cuda_stream)
+                ls.encode_gated_delta_step(layer, shape, *[_Off(b, 4 * n * layer) for b, n in zip(d_in, (hk * dk, hk * dk, hv * dv, hv, hv))],
+                                           _Off(d_y, 4 * hv * dv * layer), stream=stream.cuda_stream)
+            if chained:
+                state.chain_end()
+
+        g = None
+        if graph:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                token()
+            # the capture ran nothing: the states are still the written ones
+        got = []
+        for t in range(tokens):
+            d_x.upload(sgo.fill_normal8(conv_dim * layers, 44, t))
+            for i, (b, n) in enumerate(zip(d_in, (hk * dk, hk * dk, hv * dv, hv, hv))):
+                vals = sgo.fill_normal8(n * layers, 45, 5 * t + i)
+                if i >= 3:
+                    vals = (np.float32(0.9) + np.float32(0.01) * np.clip(vals, -4, 4)).astype(np.float32)
+                elif i < 2:
+                    vals = vals / np.float32(dk if i == 0 else np.sqrt(dk))
+                b.upload(vals)
+            state.sync()
+            if g is not None:
+                with torch.cuda.stream(stream):
+                    g.replay()
+            else:
+                token()
+            stream.synchronize()
+            got.append((d_c.download(count=conv_dim * layers).copy(), d_y.download(count=hv * dv * layers).copy()))
+        states = [ls.read(layer) for layer in range(layers)]
+        results.append((got, states))
+        ls.close()
+    plain, chain = results
+    for (c0, y0), (c1, y1) in zip(plain[0], chain[0]):
+        assert np.array_equal(c0, c1) and np.array_equal(y0, y1)
+    for (h0, s0), (h1, s1) in zip(plain[1], chain[1]):
+        assert np.array_equal(h0, h1) and np.array_equal(s0, s1)
+
+
+class _Off:
+    """A device buffer seen from a byte offset."""
+
+    def __init__(self, buf, offset):
+        self.ptr = buf.ptr + offset
