@@ -976,6 +976,12 @@ def c4_prefix_leg(sg, st, torch, stream, turns=2000, decode_steps=128, rank=0, w
              "remember": 0.0, "wait": 0.0}
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(2)]
     restore_ms = decode_ms = 0.0
+    # The decode lane: ONE sequence with its KV views, batches and step serves turn after turn (a
+    # restore or a reset gives it the turn's prefix), so a turn allocates nothing on the device.
+    lane = pool.sequence(cap)
+    kvs = [lane.layer(layer, qh) for layer in range(layers)]
+    batches = [sg.Batch(st, [kv]) for kv in kvs]
+    step = sg.Step(st, batches)
     t0 = time.perf_counter()
     for turn in range(turns):
         s_ = int(rng.choice(n_sessions, p=weights))
@@ -992,28 +998,26 @@ def c4_prefix_leg(sg, st, torch, stream, turns=2000, decode_steps=128, rank=0, w
         t = time.perf_counter()
         hit = cache.match_prefix(root, toks)
         phase["match"] += time.perf_counter() - t
-        seq = pool.sequence(((new_len + decode_steps + 15) // 16) * 16)
         reused = 0
         t = time.perf_counter()
         if hit is not None:
             ev[0][0].record(stream)
-            copied_bytes += cache.restore(hit, seq, stream=stream.cuda_stream)
+            copied_bytes += cache.restore(hit, lane, stream=stream.cuda_stream)
             ev[0][1].record(stream)
             reused = hit.tokens
+        else:
+            lane.reset(stream=stream.cuda_stream)
         phase["restore_enqueue"] += time.perf_counter() - t
         reused_tokens += reused
         prompt_tokens += new_len
         t = time.perf_counter()
-        kvs = [seq.layer(layer, qh) for layer in range(layers)]
         for kv in kvs:                                            # the unmatched rows are "prefilled"
             for c in range(reused, new_len, chunk):
                 kv.encode_append_rows(d_rows_k, d_rows_v, min(chunk, new_len - c), stream=stream.cuda_stream)
         phase["append_enqueue"] += time.perf_counter() - t
         t = time.perf_counter()
-        batches = [sg.Batch(st, [kv]) for kv in kvs]
-        step = sg.Step(st, batches)
         stream.synchronize()                                      # the capture wants the appends done
-        step.capture(d_k, d_v, d_q, d_out)
+        step.capture(d_k, d_v, d_q, d_out)                        # split counts follow this turn's context
         phase["capture"] += time.perf_counter() - t
         t = time.perf_counter()
         ev[1][0].record(stream)
@@ -1028,16 +1032,16 @@ def c4_prefix_leg(sg, st, torch, stream, turns=2000, decode_steps=128, rank=0, w
             restore_ms += ev[0][0].elapsed_time(ev[0][1])
         decode_ms += ev[1][0].elapsed_time(ev[1][1])
         decode_rows += decode_steps * layers * (2 * new_len + decode_steps)
-        step.close()
-        for b in batches:
-            b.close()
         decoded = [2_000_000_000 + turn * 1000 + i for i in range(decode_steps)]
         toks = toks + decoded
         t = time.perf_counter()
-        cache.insert_chain(root, toks, seq, from_tokens=reused, stream=stream.cuda_stream)   # every new full block
+        cache.insert_chain(root, toks, lane, from_tokens=reused, stream=stream.cuda_stream)   # every new full block
         phase["remember"] += time.perf_counter() - t
         history[s_] = toks[4096:]
-        seq.close()
+    step.close()
+    for b in batches:
+        b.close()
+    lane.close()
     stream.synchronize()
     wall = time.perf_counter() - t0
     out = {"turns": turns, "turns_on_this_gpu": my_turns, "decode_steps_per_turn": decode_steps,
@@ -1049,7 +1053,7 @@ def c4_prefix_leg(sg, st, torch, stream, turns=2000, decode_steps=128, rank=0, w
            "prompt_tokens": prompt_tokens, "reused_tokens": reused_tokens, "hit_rate": reused_tokens / max(prompt_tokens, 1),
            "restore_bytes_read_plus_written": 2 * copied_bytes,
            "restore_gbs": 2 * copied_bytes / max(restore_ms * 1e-3, 1e-9) / 1e9,
-           "evicted_blocks": len(cache.evicted()), "cache_entries": len(cache), "cache_bytes": cache.estimated_bytes(),
+           "evicted_blocks": cache.evicted_count(), "cache_entries": len(cache), "cache_bytes": cache.estimated_bytes(),
            "pinned_bytes": cache.pinned_bytes(), "budget_bytes": budget,
            "device_status": st.device_status(),
            "shape": "64 sessions, 36 layers x 8 KV heads x hd128 bf16, 16-token blocks (2.25 MiB), 8 GiB budget, context capped at 32k"}
@@ -1265,6 +1269,19 @@ def prefix_restore_gbs(sg, st, torch, stream):
         if it >= 2:
             call.append((e0.elapsed_time(e1) * 1e-3, copied))
     t_call, copied = min(call)
+    # the call only enqueues: restores issued back to back keep the device busy while the host
+    # prepares the next one (a server restoring several lanes); two lanes take turns
+    dst2 = pool.sequence(tokens + 64)
+    burst = 8
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    stream.synchronize()
+    e0.record(stream)
+    for it in range(burst):
+        cache.restore(hit, dst if it % 2 == 0 else dst2, stream=stream.cuda_stream)
+    e1.record(stream)
+    stream.synchronize()
+    t_burst = e0.elapsed_time(e1) * 1e-3 / burst
+    dst2.close()
     dst.close()
     src.close()
     cache.close()
@@ -1293,6 +1310,8 @@ def prefix_restore_gbs(sg, st, torch, stream):
     return {"gbs": kernel_gbs, "frac_of_copy_peak": kernel_gbs / peak, "peak_kind": f"of {kind}",
             "kernel": "copy_pages_kernel, 512 blocks of 2.25 MiB, shuffled lists, read+write bytes / time",
             "restore_call_gbs": call_gbs, "restore_call_ms": t_call * 1e3, "restore_call_tokens": tokens,
+            "restore_calls_back_to_back_gbs": 2 * copied / t_burst / 1e9,
+            "restore_calls_back_to_back_frac_of_copy_peak": 2 * copied / t_burst / 1e9 / peak,
             "restore_call_bytes_copied": copied,
             "shape": "36 layers, 8 KV heads, hd128, bf16, 16-token blocks (2.25 MiB per block)"}
 

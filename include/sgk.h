@@ -125,6 +125,10 @@ void sgk_seq_destroy(sgk_seq* seq);
  * the block-table entries to the device (synchronous). */
 int32_t sgk_seq_reserve(sgk_seq* seq, int64_t tokens);
 int32_t sgk_seq_block_table(const sgk_seq* seq, int32_t* pages_out, int64_t cap, int64_t* n_out);
+/* Empties the sequence for its next use (a decode lane that serves one conversation turn after
+ * another keeps its slot, its KV views, its batches and its captured step): every page goes back
+ * to the pool and the cursors of all layers return to 0, in stream order. */
+int32_t sgk_seq_reset(sgk_seq* seq, void* stream);
 /* Sliding-window layers: returns pages that lie wholly before `row` to the pool. */
 int32_t sgk_seq_release_before(sgk_seq* seq, int64_t row);
 /* FullAttentionMetalState view of (sequence, layer). Owned by the sequence. */
@@ -482,6 +486,8 @@ int64_t sgk_prefix_bytes(const sgk_prefix* pc); /* estimated_bytes (cache.rs:200
 /* What the budget is compared with: distinct pages pinned by the cache x page bytes + state snapshots. */
 int64_t sgk_prefix_pinned_bytes(const sgk_prefix* pc);
 int64_t sgk_prefix_len(const sgk_prefix* pc);
+/* Entries that left the cache so far (the dump below keeps the first 2^20 keys of them). */
+int64_t sgk_prefix_evicted_count(const sgk_prefix* pc);
 int64_t sgk_prefix_session_count(const sgk_prefix* pc, const uint8_t session[32]);
 /* Trace hook: which = 0 live entries front-to-rear, 1 = every entry that left, in order. */
 int64_t sgk_prefix_dump(const sgk_prefix* pc, int32_t which, int64_t cap, uint8_t* sessions,

@@ -263,6 +263,15 @@ void sgk_seq_destroy(sgk_seq* s) {
   delete s;
 }
 
+int32_t sgk_seq_reset(sgk_seq* s, void* stream) {
+  if (!s) return fail(SGK_ERR_BACKEND, "null sequence");
+  s->release_all();
+  cudaStream_t cs = s->pool->host_only() ? nullptr : s->pool->st->pick(stream);
+  SGK_TRY(s->set_len_all(0, cs));
+  if (!s->pool->host_only()) SGK_TRY(s->pool->flush_scrub(cs));
+  return SGK_OK;
+}
+
 int32_t sgk_seq_reserve(sgk_seq* s, int64_t tokens) {
   if (!s) return fail(SGK_ERR_BACKEND, "null sequence");
   return s->reserve(tokens);
@@ -1522,11 +1531,24 @@ int32_t sgk_prefix_restore(sgk_prefix* pc, uint64_t entry, sgk_seq* seq, sgk_lin
       dst.push_back(p);
     }
     seq->pages = dst;
-    SGK_TRY(pool->copy_pages(dst, src, cs));
+    if (pool->host_only() || src.empty()) {
+      SGK_TRY(seq->set_len_all(e.key.tokens, cs));
+    } else {
+      // one staging copy and one launch: the copy kernel also installs the block table and the cursors
+      CopyInstall install;
+      install.table = pool->d_tables + int64_t(seq->slot) * pool->table_stride;
+      install.lens = pool->d_lens + int64_t(seq->slot) * pool->layers;
+      install.n_lens = pool->layers;
+      install.len_value = static_cast<int32_t>(e.key.tokens);
+      SGK_TRY(pool->copy_pages(dst, src, cs, &install));
+      for (int l = 0; l < pool->layers; ++l) seq->len[l] = e.key.tokens;
+    }
     if (bytes_copied_out) *bytes_copied_out = static_cast<int64_t>(src.size()) * pool->page_b;
   }
-  SGK_TRY(seq->publish(0, static_cast<int64_t>(seq->pages.size()), cs, true));
-  SGK_TRY(seq->set_len_all(e.key.tokens, cs));
+  if (mode == 1) {
+    SGK_TRY(seq->publish(0, static_cast<int64_t>(seq->pages.size()), cs, true));
+    SGK_TRY(seq->set_len_all(e.key.tokens, cs));
+  }
   if (e.ls) {
     SGK_TRY(sgk_linstate_restore(ls, stream, static_cast<sgk_linstate*>(e.ls.get())));
     if (bytes_copied_out) *bytes_copied_out += e.ls->total_bytes;
@@ -1546,6 +1568,7 @@ int32_t sgk_prefix_evict_lru(sgk_prefix* pc, int32_t* evicted_out, int64_t* byte
 int64_t sgk_prefix_bytes(const sgk_prefix* pc) { return pc ? pc->entry_bytes : 0; }
 int64_t sgk_prefix_pinned_bytes(const sgk_prefix* pc) { return pc ? pc->pinned_bytes() : 0; }
 int64_t sgk_prefix_len(const sgk_prefix* pc) { return pc ? static_cast<int64_t>(pc->entries.size()) : 0; }
+int64_t sgk_prefix_evicted_count(const sgk_prefix* pc) { return pc ? pc->evicted_total : 0; }
 int64_t sgk_prefix_session_count(const sgk_prefix* pc, const uint8_t session[32]) {
   if (!pc || !session) return 0;
   Hash32 s;

@@ -127,7 +127,8 @@ struct Pool {
   int flush_scrub(cudaStream_t stream);
   int64_t used_pages() const { return num_pages - static_cast<int64_t>(free_list.size()); }
   // Copies pages src[i] -> dst[i] inside the pool (page lists are host arrays).
-  int copy_pages(const std::vector<int32_t>& dst, const std::vector<int32_t>& src, cudaStream_t stream);
+  int copy_pages(const std::vector<int32_t>& dst, const std::vector<int32_t>& src, cudaStream_t stream,
+                 const CopyInstall* install = nullptr);
 };
 
 struct Kv;
@@ -140,6 +141,10 @@ struct Seq {
   int64_t released_pages = 0;  // leading page indices already returned to the pool
   std::vector<int64_t> len;    // per layer, host mirror of the device cursor
   std::vector<std::unique_ptr<Kv>> views;
+  // Changes whenever pages of the sequence are released or replaced (never when pages are only
+  // added behind them): what the prefix cache remembers of the sequence is valid for one epoch.
+  uint64_t epoch = 0;
+  void new_epoch();
 
   int reserve(int64_t tokens);
   int release_before(int64_t row);
@@ -330,7 +335,17 @@ struct Prefix {
   // per session: its entries in the same relative order as `entries`
   std::unordered_map<Hash32, std::list<PrefixList::iterator>, Hash32Hash> sessions;
   std::unordered_map<int32_t, std::weak_ptr<PageRun>> run_by_last_page;   // finds the run a new block continues
-  std::vector<PrefixKey> evicted_log;
+  std::vector<PrefixKey> evicted_log;   // trace hook: the first EVICTED_LOG_MAX keys that left
+  static constexpr size_t EVICTED_LOG_MAX = size_t(1) << 20;
+  int64_t evicted_total = 0;
+  // The run chain found or made for a sequence last time: the next block of the same sequence
+  // continues it instead of searching again.
+  struct {
+    const Seq* seq = nullptr;
+    uint64_t epoch = 0;
+    int64_t blocks = 0;
+    std::weak_ptr<PageRun> run;
+  } cursor;
   int64_t pinned_pages = 0;   // pages of all live runs
   int64_t state_bytes = 0;    // linear-state snapshots held
   int64_t entry_bytes = 0;    // sum of the entries' own byte counts

@@ -136,13 +136,14 @@ int Pool::flush_scrub(cudaStream_t stream) {
   return SGK_OK;
 }
 
-int Pool::copy_pages(const std::vector<int32_t>& dst, const std::vector<int32_t>& src, cudaStream_t stream) {
+int Pool::copy_pages(const std::vector<int32_t>& dst, const std::vector<int32_t>& src, cudaStream_t stream,
+                     const CopyInstall* install) {
   if (dst.size() != src.size()) return fail(SGK_ERR_DIMENSION, "copy_pages: list sizes differ");
   if (dst.empty() || host_only()) return SGK_OK;
   int slot;
   SGK_TRY(stage_words(dst.data(), dst.size(), src.data(), src.size(), stream, &slot));
   SGK_CUDA(launch_copy_pages(d_base, d_base, stage[slot].d, stage[slot].d + dst.size(), static_cast<int>(dst.size()),
-                             layer_b, layers, layer_stride, st->sm_count, stream));
+                             layer_b, layers, layer_stride, st->sm_count, stream, install));
   st->launches += 1;
   return stage_done(slot, stream);
 }
@@ -178,6 +179,11 @@ int Seq::reserve(int64_t tokens) {
   return publish(have, need - have);
 }
 
+void Seq::new_epoch() {
+  static uint64_t counter = 0;
+  epoch = ++counter;
+}
+
 int Seq::release_before(int64_t row) {
   int64_t upto = std::min<int64_t>(row / PAGE_TOKENS, static_cast<int64_t>(pages.size()));
   for (int64_t i = released_pages; i < upto; ++i) {
@@ -185,6 +191,7 @@ int Seq::release_before(int64_t row) {
     pages[i] = -1;
   }
   if (upto > released_pages) {
+    new_epoch();
     int64_t first = released_pages;
     released_pages = upto;
     SGK_TRY(publish(first, upto - first));
@@ -194,6 +201,7 @@ int Seq::release_before(int64_t row) {
 }
 
 int Seq::release_all() {
+  new_epoch();
   for (auto& p : pages)
     if (p >= 0) pool->release(p);
   pages.clear();
@@ -213,6 +221,7 @@ int Seq::ensure_writable(int64_t row, cudaStream_t stream) {
   SGK_TRY(pool->copy_pages({fresh}, {page}, stream));
   pool->release(page);
   pages[idx] = fresh;
+  new_epoch();
   if (!pool->host_only()) {
     // in-stream table update: earlier kernels still see the shared page
     SGK_CUDA(launch_set_len(pool->d_tables + int64_t(slot) * pool->table_stride + idx, fresh, stream));

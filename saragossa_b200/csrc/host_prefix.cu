@@ -151,10 +151,21 @@ std::shared_ptr<PageRun> Prefix::chain_for(const Seq* seq, int64_t tokens, bool 
   const int64_t per_block = block_tokens / PAGE_TOKENS;
   const int64_t n_blocks = tokens / block_tokens;
   const int64_t n_pages = tokens / PAGE_TOKENS;
-  // The deepest live run that holds exactly the sequence's pages [0, its end): found through the
-  // last page of a block, then compared page by page down to the root.
+  auto holds_block = [&](const PageRun* r, int64_t blk) {
+    if (r->first_page != blk * per_block || static_cast<int64_t>(r->pages.size()) != per_block) return false;
+    for (int64_t i = 0; i < per_block; ++i)
+      if (r->pages[i] != seq->pages[r->first_page + i]) return false;
+    return true;
+  };
   std::shared_ptr<PageRun> base;
   int64_t base_blocks = 0;
+  // Where the previous call for this sequence left off (the blocks of a prompt come in order) ...
+  if (cursor.seq == seq && cursor.epoch == seq->epoch && cursor.blocks <= n_blocks) {
+    base = cursor.run.lock();
+    if (base) base_blocks = cursor.blocks;
+  }
+  // ... else the deepest live run that holds exactly the sequence's pages [0, its end): found through
+  // the last page of a block, then compared page by page down to the root.
   for (int64_t b = n_blocks; b >= 1 && !base; --b) {
     auto it = run_by_last_page.find(seq->pages[b * per_block - 1]);
     if (it == run_by_last_page.end()) continue;
@@ -164,35 +175,50 @@ std::shared_ptr<PageRun> Prefix::chain_for(const Seq* seq, int64_t tokens, bool 
     int64_t depth = 0;
     for (const PageRun* r = cand.get(); r != nullptr && same; r = r->parent.get()) {
       ++depth;
-      const int64_t blk = b - depth;   // block index this run must be
-      if (blk < 0 || r->first_page != blk * per_block || static_cast<int64_t>(r->pages.size()) != per_block) {
-        same = false;
-        break;
-      }
-      for (int64_t i = 0; i < per_block; ++i) same = same && r->pages[i] == seq->pages[r->first_page + i];
+      same = b - depth >= 0 && holds_block(r, b - depth);
     }
     if (same && depth == b) {
       base = cand;
       base_blocks = b;
     }
   }
-  if (fresh_pages) *fresh_pages = n_pages - base_blocks * per_block;
-  if (!create) return base_blocks == n_blocks ? base : nullptr;
-  for (int64_t b = base_blocks; b < n_blocks; ++b) {
-    auto run = std::make_shared<PageRun>();
-    run->first_page = b * per_block;
-    run->pages.assign(seq->pages.begin() + b * per_block, seq->pages.begin() + (b + 1) * per_block);
-    run->parent = base;
-    for (int32_t p : run->pages) pool->retain(p);
-    pinned_pages += per_block;
-    run_by_last_page[run->pages.back()] = run;
-    base = run;
+  // Live runs that continue the chain block by block (a re-inserted prompt finds its old runs).
+  while (base_blocks < n_blocks) {
+    auto it = run_by_last_page.find(seq->pages[(base_blocks + 1) * per_block - 1]);
+    if (it == run_by_last_page.end()) break;
+    std::shared_ptr<PageRun> cand = it->second.lock();
+    if (!cand || cand->parent.get() != base.get() || !holds_block(cand.get(), base_blocks)) break;
+    base = cand;
+    base_blocks += 1;
   }
-  return base;
+  if (fresh_pages) *fresh_pages = n_pages - base_blocks * per_block;
+  if (create) {
+    for (int64_t b = base_blocks; b < n_blocks; ++b) {
+      auto run = std::make_shared<PageRun>();
+      run->first_page = b * per_block;
+      run->pages.assign(seq->pages.begin() + b * per_block, seq->pages.begin() + (b + 1) * per_block);
+      run->parent = base;
+      for (int32_t p : run->pages) pool->retain(p);
+      pinned_pages += per_block;
+      run_by_last_page[run->pages.back()] = run;
+      base = run;
+    }
+    base_blocks = n_blocks;
+  }
+  if (base) {
+    cursor.seq = seq;
+    cursor.epoch = seq->epoch;
+    cursor.blocks = base_blocks;
+    cursor.run = base;
+  }
+  return base_blocks == n_blocks ? base : nullptr;
 }
 
 void Prefix::drop(PrefixList::iterator it, bool log) {
-  if (log) evicted_log.push_back(it->key);
+  if (log) {
+    evicted_total += 1;
+    if (evicted_log.size() < EVICTED_LOG_MAX) evicted_log.push_back(it->key);
+  }
   index.erase(it->key);
   by_id.erase(it->id);
   auto sess = sessions.find(it->key.session);

@@ -135,12 +135,20 @@ struct GatherArgs {
 };
 cudaError_t launch_gather(const GatherArgs& a, cudaStream_t stream);
 
+// What a restore installs with its copy: table[i] = dst_pages[i] for every copied page, and
+// lens[0 .. n_lens) = len_value (the cursors of the sequence's layers).
+struct CopyInstall {
+  int32_t* table = nullptr;
+  int32_t* lens = nullptr;
+  int32_t n_lens = 0;
+  int32_t len_value = 0;
+};
 // Page copy: dst_pages[i] <- src_pages[i]; a page is n_layers pieces of page_bytes, layer_stride
 // apart (16-byte vectors).
 cudaError_t launch_copy_pages(uint8_t* dst_base, const uint8_t* src_base, const int32_t* d_dst_pages,
                               const int32_t* d_src_pages, int n_pages, int64_t page_bytes, int n_layers,
                               int64_t layer_stride, int sm_count,
-                              cudaStream_t stream);
+                              cudaStream_t stream, const CopyInstall* install = nullptr);
 // Contiguous device copy (linear-state snapshot / restore).
 cudaError_t launch_copy_bytes(void* dst, const void* src, int64_t bytes, cudaStream_t stream);
 // Zero-fill of freed pages (eviction scrub).

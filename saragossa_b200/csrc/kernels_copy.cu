@@ -88,7 +88,13 @@ __global__ void __launch_bounds__(COPY_THREADS) copy_pages_kernel(uint8_t* __res
                                                                   const int32_t* __restrict__ dst_pages,
                                                                   const int32_t* __restrict__ src_pages,
                                                                   int n_pages, int64_t page_bytes, int n_layers,
-                                                                  int64_t layer_stride) {
+                                                                  int64_t layer_stride, CopyInstall install) {
+  // A restore also makes the copied pages the sequence's block table and moves its cursors: done
+  // here by the first block, so that the whole restore is one staging copy and one launch.
+  if (blockIdx.x == 0 && install.table != nullptr) {
+    for (int i = threadIdx.x; i < n_pages; i += COPY_THREADS) install.table[i] = dst_pages[i];
+    for (int i = threadIdx.x; i < install.n_lens; i += COPY_THREADS) install.lens[i] = install.len_value;
+  }
   const int64_t pieces_per_page = (page_bytes + COPY_PIECE - 1) / COPY_PIECE;
   const int64_t per_page = pieces_per_page * n_layers;
   const int64_t items = per_page * n_pages;
@@ -123,11 +129,12 @@ static int copy_grid(int64_t items, int sm_count = 0) {
 
 cudaError_t launch_copy_pages(uint8_t* dst_base, const uint8_t* src_base, const int32_t* d_dst_pages,
                               const int32_t* d_src_pages, int n_pages, int64_t page_bytes, int n_layers,
-                              int64_t layer_stride, int sm_count, cudaStream_t stream) {
+                              int64_t layer_stride, int sm_count, cudaStream_t stream, const CopyInstall* install) {
   if (n_pages <= 0) return cudaSuccess;
   int64_t items = ((page_bytes + COPY_PIECE - 1) / COPY_PIECE) * n_layers * n_pages;
   copy_pages_kernel<<<copy_grid(items, sm_count), COPY_THREADS, 0, stream>>>(dst_base, src_base, d_dst_pages, d_src_pages,
-                                                                   n_pages, page_bytes, n_layers, layer_stride);
+                                                                   n_pages, page_bytes, n_layers, layer_stride,
+                                                                   install ? *install : CopyInstall{});
   return cudaGetLastError();
 }
 
@@ -145,7 +152,7 @@ cudaError_t launch_copy_bytes(void* dst, const void* src, int64_t bytes, cudaStr
   if (body > 0) {
     int64_t items = (body + COPY_PIECE - 1) / COPY_PIECE;
     copy_pages_kernel<<<copy_grid(items), COPY_THREADS, 0, stream>>>(
-        static_cast<uint8_t*>(dst), static_cast<const uint8_t*>(src), nullptr, nullptr, 1, body, 1, 0);
+        static_cast<uint8_t*>(dst), static_cast<const uint8_t*>(src), nullptr, nullptr, 1, body, 1, 0, CopyInstall{});
   }
   int64_t tail = bytes - body;
   if (tail > 0) {

@@ -122,6 +122,9 @@ class BlockAwarePrefixCache:
     def __len__(self):
         return self.L.sgk_prefix_len(self.h)
 
+    def evicted_count(self):
+        return self.L.sgk_prefix_evicted_count(self.h)
+
     def session_block_count(self, session: bytes):
         return self.L.sgk_prefix_session_count(self.h, _h32(session))
 

@@ -415,6 +415,10 @@ class Sequence:
     def reserve(self, tokens):
         check(self.L.sgk_seq_reserve(self.h, tokens))
 
+    def reset(self, stream=None):
+        """Empties the sequence (pages back to the pool, cursors to 0) for its next use."""
+        check(self.L.sgk_seq_reset(self.h, stream))
+
     def block_table(self):
         n = C.c_int64()
         check(self.L.sgk_seq_block_table(self.h, None, 0, C.byref(n)))

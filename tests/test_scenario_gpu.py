@@ -93,8 +93,9 @@ def test_multi_turn_prefix_cache_under_budget(state):
                 continue
             pages = list(seq.block_table()[:i + 1])
             skip = False
-            while True:                                               # oracle side of the budget loop
-                live = set(p for e in ref.entries() if e[1] != prev for p in pins[e[1]])
+            while True:                                               # oracle side of the budget loop, which
+                # runs before the insert: an older duplicate of the block is still cached then
+                live = set(p for e in ref.entries() for p in pins[e[1]])
                 if len(live | set(pages)) * pool.page_bytes <= budget:
                     break
                 if ref.evict_lru_block() is None:
