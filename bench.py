@@ -541,26 +541,32 @@ def head_sharded_run(sg, st, torch, dist, world, rank, stream, sh, pool, seq, ba
             self.ptr = ptr
 
     def step_nccl():
+        st.chain_begin(stream.cuda_stream)       # one decode token: every launch lets the next one start early
         for layer in range(LAYERS):
             batches[layer].enqueue_step(_Ptr(k[layer]), _Ptr(v[layer]), _Ptr(q[layer]), _Ptr(out_loc[layer]),
                                         stream=stream.cuda_stream)
             dist.all_gather_into_tensor(out_full[layer], out_loc[layer])
+        st.chain_end()
 
     def step_direct():
+        st.chain_begin(stream.cuda_stream)
         for layer in range(LAYERS):
             base = rows.ptr + 4 * layer * row
             batches[layer].enqueue_step(_Ptr(k[layer]), _Ptr(v[layer]), _Ptr(q[layer]), _At(base + 4 * rank * q_loc),
                                         stream=stream.cuda_stream)
             ex.enqueue(base, [0 if p == rank else peer_rows[p].ptr + 4 * layer * row for p in range(world)],
                        rank * q_loc, q_loc, stream=stream.cuda_stream)
+        st.chain_end()
 
     def step_fused():
+        st.chain_begin(stream.cuda_stream)
         for layer in range(LAYERS):
             base = rows.ptr + 4 * layer * row
             batches[layer].enqueue_step_exchange(
                 _Ptr(k[layer]), _Ptr(v[layer]), _Ptr(q[layer]), ex, base,
                 [0 if p == rank else peer_rows[p].ptr + 4 * layer * row for p in range(world)], rank * q_loc,
                 stream=stream.cuda_stream)
+        st.chain_end()
 
     # One decode token = 48 x (fused kernel, exchange) as ONE CUDA graph; the pages the replays
     # will append into are reserved before the capture (a replay moves only the device cursor).
@@ -748,7 +754,7 @@ def c1_decode_leg(sg, st, torch, stream):
     layers, qh, kvh, hd, ctx, steps = 36, 32, 8, 128, 1024, 64
     kv_dim, q_dim = kvh * hd, qh * hd
     loop_tokens = 32
-    cap = ctx + steps + 2 * loop_tokens + 16
+    cap = ctx + steps + 2 * loop_tokens + 24
     pool = st.pool(layers, kvh, hd, sg.KV_BF16, cap // 16 + 2, 1, cap)
     pool.shuffle_free_list(1)
     seq = pool.sequence(cap)
@@ -779,7 +785,7 @@ def c1_decode_leg(sg, st, torch, stream):
     stream.synchronize()
     us_token = e0.elapsed_time(e1) * 1e3 / (steps - 3)
     finite = bool(np.isfinite(d_out.download(count=layers * q_dim)).all())
-    token_loop = guarded(_c1_token_loop, sg, st, torch, stream, step, d_out, q_dim, loop_tokens)
+    token_loop = guarded(_c1_token_loop, sg, st, torch, stream, step, (d_k, d_v, d_q, d_out), q_dim, loop_tokens)
     step.close()
     for b in batches:
         b.close()
@@ -809,34 +815,36 @@ def c1_decode_leg(sg, st, torch, stream):
             "shape": "batch 1, 36 layers, 32Q/8KV hd128 bf16, ctx 1024 -> 1088"}
 
 
-def _c1_token_loop(sg, st, torch, stream, step, d_out, hidden, tokens):
-    """The whole token with the index resident on the device: embedding lookup by the previous
-    token's index, the 36-layer graph, lm_head argmax into the window's ring (tied bf16
-    151 936 x 4 096 table, 1.24 GB), the host reading tokens back 4 behind (depth 4) or after
-    every token (depth 1). Wall clock per token, host included. The activations between the
-    pieces are not a model's (no projections or MLP here): shapes and dependencies are."""
+def _c1_token_loop(sg, st, torch, stream, step, bufs, hidden, tokens):
+    """The whole token as ONE submission with the index resident on the device: embedding lookup
+    by the previous token's index, the 36 layers and the lm_head argmax into the window's ring are
+    one CUDA graph per ring slot (sgk_token_capture; tied bf16 151 936 x 4 096 table, 1.24 GB); the
+    host reads tokens back 4 behind (depth 4) or after every token (depth 1). Wall clock per token,
+    host included. The activations between the pieces are not a model's (no projections or MLP
+    here): shapes and dependencies are."""
+    d_k, d_v, d_q, d_out = bufs
     vocab = 151936
     dev = torch.device("cuda", torch.cuda.current_device())
     gen = torch.Generator(device=dev)
     gen.manual_seed(5)
     table = (torch.randn(vocab, hidden, device=dev, generator=gen) * 0.02).to(torch.bfloat16)
     x = torch.zeros(hidden, device=dev)
-    first = torch.tensor([11], dtype=torch.int32, device=dev)
-    out = {"vocab": vocab, "hidden": hidden, "tokens": tokens}
+    out = {"vocab": vocab, "hidden": hidden, "tokens": tokens, "submissions_per_token": 1,
+           "launches_per_token": len(step.batches) + 2}
     for depth in (4, 1):
         win = st.token_window(depth)
+        step.token_capture(win, _Ptr(table), sg.KV_BF16, vocab, hidden, _Ptr(x), _Ptr(table), sg.KV_BF16, d_out,
+                           d_k, d_v, d_q, d_out)
+        step.token_seed(11, stream=stream.cuda_stream)
+        for _ in range(min(depth, 2)):                       # warm-up
+            step.token_submit(stream.cuda_stream)
+        win.drain()
         got, enq = [], 0
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         while len(got) < tokens:
             while enq < tokens and win.inflight < depth:
-                src = win.previous_slot() or _Ptr(first)
-                st.encode_embedding_from_index(_Ptr(table), sg.KV_BF16, vocab, hidden, src, _Ptr(x),
-                                               stream=stream.cuda_stream)
-                step.replay(stream.cuda_stream)
-                st.encode_lm_head_argmax(_Ptr(table), sg.KV_BF16, vocab, hidden, d_out, win.output_slot(),
-                                         stream=stream.cuda_stream)
-                win.submit(stream.cuda_stream)
+                step.token_submit(stream.cuda_stream)
                 enq += 1
             got.append(win.pop())
         dt = time.perf_counter() - t0

@@ -389,6 +389,36 @@ int64_t sgk_token_window_enqueued(const sgk_token_window* w);
 int32_t sgk_token_window_depth(const sgk_token_window* w);
 int32_t sgk_token_window_drain(sgk_token_window* w);
 
+/* The WHOLE token as one submission (one command buffer per token in the reference,
+ * src/decoder/resident/decode.rs:183-458: embedding lookup by the previous token's index ->
+ * every layer's fused append + attention -> greedy epilogue -> `commit_nonblocking`, :417).
+ * sgk_token_capture records, for every slot of the window's ring, ONE CUDA graph:
+ *   sgk_embed_enqueue_from_index (index of the previous slot -> io.d_x)
+ *   the step's layers (as sgk_step_capture: d_k, d_v, d_q in, d_out out, cursors on the device)
+ *   sgk_lm_head_enqueue_argmax (io.d_final -> this slot) and the slot's copy to pinned memory
+ * as one token chain (every launch lets the next one start early). What lies between these
+ * pieces in a model (projections, MLP) is the caller's and belongs in the same capture when it
+ * exists; here the pointers are fixed device buffers. sgk_token_seed puts the first input token
+ * into the ring; sgk_token_submit launches the next token's graph (Dimension error when the
+ * window is full) and sgk_token_window_pop returns the oldest token's index. */
+typedef struct {
+  const void* d_table;      /* embedding table [vocab][hidden] */
+  int32_t table_dtype;      /* SGK_KV_F32, SGK_KV_BF16, or SGK_W_U8G64 / SGK_W_U4G64 with the arrays below */
+  int64_t vocab;
+  int32_t hidden;
+  float embedding_scale;
+  int32_t recast_bf16;
+  float* d_x;               /* the looked-up row */
+  const void* d_lm_weight;  /* lm_head weight [vocab][hidden] (may be the table: tied) */
+  int32_t lm_weight_dtype;
+  const float* d_final;     /* the final hidden row the epilogue reads */
+} sgk_token_io;
+int32_t sgk_token_capture(sgk_step* step, sgk_token_window* window, const sgk_token_io* io, const float* d_k,
+                          const float* d_v, const float* d_q, float* d_out, const int64_t* sliding_windows,
+                          float attn_scalar);
+int32_t sgk_token_seed(sgk_step* step, int32_t first_token, void* stream);
+int32_t sgk_token_submit(sgk_step* step, void* stream);
+
 /* encode_capture_linear_attn_state (src/metal_backend/linear_attention.rs:93-127): copies the
  * state into an EXISTING state of the same shape (one made ahead with sgk_linstate_create, like the
  * reference's leased per-row captures, :44-91): enqueue only, no allocation. Shape error if the

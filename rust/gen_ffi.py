@@ -49,6 +49,10 @@ def parse(path: str = HEADER):
             decl = decl.strip()
             if not decl:
                 continue
+            if "*" in decl:                      # one pointer field per declaration
+                name, ctype, _ = parse_param(decl, len(fields))
+                fields.append((name, ctype))
+                continue
             ctype, names = decl.split(None, 1)
             for name in names.split(","):
                 fields.append((name.strip(), ctype))
@@ -153,7 +157,7 @@ def render(info) -> str:
         w("#[derive(Clone, Copy, Debug)]")
         w(f"pub struct {camel(name)} {{")
         for fname, ctype in fields:
-            w(f"    pub {fname}: {SCALARS[ctype]},")
+            w(f"    pub {fname}: {rust_type(ctype, None, handles, struct_names)},")
         w("}")
     w("")
     w('#[link(name = "sgk")]')

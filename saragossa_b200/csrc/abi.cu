@@ -1056,8 +1056,13 @@ int32_t sgk_lm_head_enqueue_argmax(sgk_state* st, void* stream, const void* d_we
   a.index_offset = index_offset;
   a.index_out = d_index_out;
   a.value_out = d_value_out;
-  SGK_CUDA(launch_lm_head_argmax(a, st->sm_count, st->pick(stream)));
+  cudaStream_t cs = st->pick(stream);
+  const bool member = st->chain_member(cs);
+  a.pdl_trigger = member ? 1 : 0;
+  a.pdl_wait = st->chain_follows(cs) ? 1 : 0;
+  SGK_CUDA(launch_lm_head_argmax(a, st->sm_count, cs));
   st->launches += 1;
+  if (member) st->chain_note();
   return SGK_OK;
 }
 
@@ -1069,9 +1074,12 @@ int32_t sgk_embed_enqueue_from_index(sgk_state* st, void* stream, const void* d_
     return fail(SGK_ERR_CONFIG, "embedding table dtype %d: only dense f32 and bf16 tables are supported", table_dtype);
   if (vocab <= 0 || hidden <= 0 || vocab > 0x7fffffffLL)
     return fail(SGK_ERR_DIMENSION, "embedding: vocab %lld, hidden %d invalid", (long long)vocab, hidden);
+  cudaStream_t cs = st->pick(stream);
+  const bool member = st->chain_member(cs);
   SGK_CUDA(launch_embed_gather(d_table, table_dtype == SGK_KV_BF16, d_index, vocab, hidden, embedding_scale,
-                               recast_bf16 != 0, d_out, st->pick(stream)));
+                               recast_bf16 != 0, d_out, member ? 1 : 0, st->chain_follows(cs) ? 1 : 0, cs));
   st->launches += 1;
+  if (member) st->chain_note();
   return SGK_OK;
 }
 
@@ -1265,6 +1273,114 @@ int32_t sgk_token_window_drain(sgk_token_window* w) {
     SGK_CUDA(cudaEventSynchronize(w->done[slot]));
     w->inflight -= 1;
   }
+  return SGK_OK;
+}
+
+// ------------------------------------------------------------------ the whole token as one graph
+int32_t sgk_token_capture(sgk_step* s, sgk_token_window* w, const sgk_token_io* io, const float* d_k, const float* d_v,
+                          const float* d_q, float* d_out, const int64_t* sliding_windows, float attn_scalar) {
+  if (!s || !w || !io) return fail(SGK_ERR_BACKEND, "token_capture: null argument");
+  if (!d_k || !d_v || !d_q || !d_out) return fail(SGK_ERR_BACKEND, "token_capture: null device pointer");
+  if (!io->d_table || !io->d_x || !io->d_lm_weight || !io->d_final)
+    return fail(SGK_ERR_BACKEND, "token_capture: null pointer in the token's inputs");
+  if (w->st != s->st) return fail(SGK_ERR_CONFIG, "token_capture: window and step belong to different states");
+  if (w->inflight != 0) return fail(SGK_ERR_DIMENSION, "token_capture with %d tokens in flight", w->inflight);
+  State* st = s->st;
+  for (cudaGraphExec_t e : s->token_execs)
+    if (e) cudaGraphExecDestroy(e);
+  s->token_execs.clear();
+  s->token_window = nullptr;
+  cudaStream_t stream = st->stream;
+  // as in sgk_step_capture: no host-side table update may fall inside the capture
+  for (Batch* b : s->layers)
+    for (Kv* kv : b->kvs) {
+      SGK_TRY(kv->seq->reserve(kv->seq->capacity));
+      if (kv->len() < kv->seq->capacity) SGK_TRY(kv->seq->ensure_writable(kv->len(), stream));
+    }
+  SGK_CUDA(cudaStreamSynchronize(stream));
+  std::vector<std::vector<int64_t>> saved;
+  for (Batch* b : s->layers) {
+    saved.emplace_back();
+    for (Kv* kv : b->kvs) saved.back().push_back(kv->len());
+  }
+  const int64_t launches_before = s->launches, state_before = st->launches;
+  int rc = SGK_OK;
+  // One graph per slot of the ring: token n runs graph n % depth, which reads the index token n-1
+  // left in slot (n-1) % depth and leaves its own in slot n % depth (and in the pinned mirror).
+  for (int slot = 0; slot < w->depth && rc == SGK_OK; ++slot) {
+    const int32_t* d_prev = w->d_ring + (slot + w->depth - 1) % w->depth;
+    SGK_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+    st->chain_active = true;   // the token is one chain: embedding, layers, epilogue
+    st->chain_stream = stream;
+    st->chain_mark = -1;
+    rc = sgk_embed_enqueue_from_index(static_cast<sgk_state*>(st), stream, io->d_table, io->table_dtype, io->vocab, io->hidden,
+                                      d_prev, io->embedding_scale, io->recast_bf16, io->d_x);
+    if (rc == SGK_OK) rc = s->enqueue(stream, d_k, d_v, d_q, d_out, sliding_windows, attn_scalar);
+    if (rc == SGK_OK)
+      rc = sgk_lm_head_enqueue_argmax(static_cast<sgk_state*>(st), stream, io->d_lm_weight, io->lm_weight_dtype, io->vocab,
+                                      io->hidden, io->d_final, 1, 0, w->d_ring + slot, nullptr);
+    st->chain_active = false;
+    if (rc == SGK_OK) {
+      cudaError_t ce = cudaMemcpyAsync(w->h_ring + slot, w->d_ring + slot, sizeof(int32_t), cudaMemcpyDeviceToHost, stream);
+      if (ce != cudaSuccess) rc = fail(SGK_ERR_BACKEND, "token_capture: %s", cudaGetErrorString(ce));
+    }
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(stream, &graph);
+    for (size_t l = 0; l < s->layers.size(); ++l)
+      for (size_t i = 0; i < s->layers[l]->kvs.size(); ++i)
+        s->layers[l]->kvs[i]->seq->len[s->layers[l]->layer] = saved[l][i];
+    if (slot == 0) s->launches_per_replay = st->launches - state_before;
+    if (rc == SGK_OK && e != cudaSuccess) rc = fail(SGK_ERR_BACKEND, "graph capture failed: %s", cudaGetErrorString(e));
+    if (rc == SGK_OK) {
+      cudaGraphExec_t exec = nullptr;
+      cudaError_t ie = cudaGraphInstantiate(&exec, graph, 0);
+      if (ie != cudaSuccess) rc = fail(SGK_ERR_BACKEND, "graph instantiation failed: %s", cudaGetErrorString(ie));
+      else s->token_execs.push_back(exec);
+    }
+    if (graph) cudaGraphDestroy(graph);
+  }
+  s->launches = launches_before;
+  st->launches = state_before;
+  if (rc != SGK_OK) {
+    for (cudaGraphExec_t e : s->token_execs)
+      if (e) cudaGraphExecDestroy(e);
+    s->token_execs.clear();
+    return rc;
+  }
+  s->token_window = w;
+  return SGK_OK;
+}
+
+int32_t sgk_token_seed(sgk_step* s, int32_t first_token, void* stream) {
+  if (!s || !s->token_window) return fail(SGK_ERR_CONFIG, "token_seed before token_capture");
+  TokenWindow* w = s->token_window;
+  if (w->inflight != 0) return fail(SGK_ERR_DIMENSION, "token_seed with %d tokens in flight", w->inflight);
+  // the slot the NEXT token's graph reads its input index from
+  const int prev = static_cast<int>((w->enqueued + w->depth - 1) % w->depth);
+  SGK_CUDA(launch_set_len(w->d_ring + prev, first_token, s->st->pick(stream)));
+  s->st->launches += 1;
+  return SGK_OK;
+}
+
+int32_t sgk_token_submit(sgk_step* s, void* stream) {
+  if (!s || !s->token_window || s->token_execs.empty()) return fail(SGK_ERR_CONFIG, "token_submit before token_capture");
+  TokenWindow* w = s->token_window;
+  if (w->inflight >= w->depth)
+    return fail(SGK_ERR_DIMENSION, "token window: %d tokens in flight, the window holds %d", w->inflight, w->depth);
+  for (Batch* b : s->layers)
+    for (Kv* kv : b->kvs)
+      if (kv->len() >= kv->seq->capacity)
+        return fail(SGK_ERR_DIMENSION, "append KV: capacity %lld reached (overflow)", (long long)kv->seq->capacity);
+  const int slot = static_cast<int>(w->enqueued % w->depth);
+  cudaStream_t cs = s->st->pick(stream);
+  SGK_CUDA(cudaGraphLaunch(s->token_execs[slot], cs));   // the token's ONE submission
+  SGK_CUDA(cudaEventRecord(w->done[slot], cs));
+  for (Batch* b : s->layers)
+    for (Kv* kv : b->kvs) kv->seq->len[b->layer] += 1;
+  s->launches += s->launches_per_replay;
+  s->st->launches += s->launches_per_replay;
+  w->enqueued += 1;
+  w->inflight += 1;
   return SGK_OK;
 }
 

@@ -227,6 +227,9 @@ struct Step {
   // run_host overlaps the copies of one group of layers with the kernels of another
   cudaStream_t copy_in = nullptr, copy_out = nullptr;
   std::vector<cudaEvent_t> events;
+  // whole-token graphs (sgk_token_capture): one per slot of the submission window's ring
+  std::vector<cudaGraphExec_t> token_execs;
+  struct TokenWindow* token_window = nullptr;
   int enqueue(cudaStream_t stream, const float* d_k, const float* d_v, const float* d_q, float* d_out,
               const int64_t* sliding_windows, float attn_scalar);
   int enqueue_range(cudaStream_t stream, size_t l0, size_t l1, const float* d_k, const float* d_v, const float* d_q,

@@ -596,6 +596,8 @@ int Batch::enqueue_attention(cudaStream_t stream, const float* d_q, float* d_out
 
 // ---------------------------------------------------------------- Step
 Step::~Step() {
+  for (cudaGraphExec_t e : token_execs)
+    if (e) cudaGraphExecDestroy(e);
   if (graph_exec) cudaGraphExecDestroy(graph_exec);
   if (graph) cudaGraphDestroy(graph);
   if (copy_in) cudaStreamDestroy(copy_in);

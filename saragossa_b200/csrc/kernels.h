@@ -204,12 +204,14 @@ struct LmHeadArgs {
   int32_t index_offset;
   int32_t* index_out;  // [n_rows]
   float* value_out;    // [n_rows], may be NULL
+  int32_t pdl_trigger, pdl_wait;   // member of a token chain (see GatedDeltaArgs)
 };
 cudaError_t launch_lm_head_argmax(const LmHeadArgs& a, int sm_count, cudaStream_t stream);
 size_t lm_head_smem_bytes(int w_bf16, int n_rows, int hidden);  // shared memory a launch needs
 // out[hidden] = table[*index] * scale (dense f32 or bf16 table); an index outside the table writes nothing.
 cudaError_t launch_embed_gather(const void* table, int table_bf16, const int32_t* index, int64_t vocab, int hidden,
-                                float scale, int recast_bf16, float* out, cudaStream_t stream);
+                                float scale, int recast_bf16, float* out, int pdl_trigger, int pdl_wait,
+                                cudaStream_t stream);
 // Exchange of output slices between ranks over peer memory (kernels_exchange.cu).
 constexpr int EXCHANGE_MAX_RANKS = 8;
 struct ExchangeArgs {

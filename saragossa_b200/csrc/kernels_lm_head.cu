@@ -69,11 +69,17 @@ __device__ __forceinline__ unsigned long long pack_key(float v, int64_t row) {
   return (static_cast<unsigned long long>(ordered_bits(v)) << 32) | (0xffffffffu - uint32_t(row));
 }
 
+// Programmatic dependent launch (see mma_common.cuh): no-ops in a launch without such a neighbour.
+__device__ __forceinline__ void lm_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void lm_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 template <int R>
 __global__ void __launch_bounds__(LM_THREADS) lm_head_argmax_f32_kernel(LmHeadArgs a) {
   extern __shared__ __align__(16) float xs[];
   __shared__ unsigned long long best_s[LM_WARPS][R];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (a.pdl_trigger) lm_pdl_trigger();
+  if (a.pdl_wait) lm_pdl_wait();
   for (int i = tid; i < a.n_rows * a.hidden / 4; i += LM_THREADS)
     reinterpret_cast<float4*>(xs)[i] = reinterpret_cast<const float4*>(a.x)[i];
   for (int i = a.n_rows * a.hidden + tid; i < R * a.hidden; i += LM_THREADS) xs[i] = 0.0f;
@@ -139,6 +145,8 @@ __global__ void __launch_bounds__(LM_THREADS, LM_BLOCKS_PER_SM) lm_head_argmax_b
   __shared__ unsigned long long best_s[LM_WARPS][8];
   __shared__ unsigned int last_s;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  if (a.pdl_trigger) lm_pdl_trigger();
+  if (a.pdl_wait) lm_pdl_wait();
   const int stride = lm_x_stride_bytes(a.hidden);
   unsigned char* xhi = lm_smem;
   unsigned char* xlo = lm_smem + size_t(a.n_rows) * stride;
@@ -237,8 +245,8 @@ static cudaError_t launch_r(const LmHeadArgs& a, int blocks, size_t smem, cudaSt
     cudaError_t e = cudaFuncSetAttribute(lm_head_argmax_f32_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return e;
   }
-  lm_head_argmax_f32_kernel<R><<<blocks, LM_THREADS, smem, stream>>>(a);
-  return cudaGetLastError();
+  ChainLaunch l(dim3(blocks), dim3(LM_THREADS), smem, stream, a.pdl_wait != 0);
+  return cudaLaunchKernelEx(&l.cfg, lm_head_argmax_f32_kernel<R>, a);
 }
 
 // ---- token feed: the next token's input row, looked up by an index that lives on the device --
@@ -246,7 +254,9 @@ static cudaError_t launch_r(const LmHeadArgs& a, int blocks, size_t smem, cudaSt
 // rounded to bf16 (RNE) and widened again; a token outside the table writes nothing.
 template <bool BF16>
 __global__ void embed_gather_kernel(const void* table, const int32_t* index, int64_t vocab, int hidden, float scale,
-                                    int recast_bf16, float* out) {
+                                    int recast_bf16, float* out, int pdl_trigger, int pdl_wait) {
+  if (pdl_trigger) lm_pdl_trigger();
+  if (pdl_wait) lm_pdl_wait();   // the index is what the previous token's epilogue wrote
   const int64_t token = *index;
   if (token < 0 || token >= vocab) return;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < hidden; i += gridDim.x * blockDim.x) {
@@ -258,13 +268,14 @@ __global__ void embed_gather_kernel(const void* table, const int32_t* index, int
 }
 
 cudaError_t launch_embed_gather(const void* table, int table_bf16, const int32_t* index, int64_t vocab, int hidden,
-                                float scale, int recast_bf16, float* out, cudaStream_t stream) {
+                                float scale, int recast_bf16, float* out, int pdl_trigger, int pdl_wait,
+                                cudaStream_t stream) {
   const int blocks = (hidden + 255) / 256 < 64 ? (hidden + 255) / 256 : 64;
-  if (table_bf16)
-    embed_gather_kernel<true><<<blocks, 256, 0, stream>>>(table, index, vocab, hidden, scale, recast_bf16, out);
-  else
-    embed_gather_kernel<false><<<blocks, 256, 0, stream>>>(table, index, vocab, hidden, scale, recast_bf16, out);
-  return cudaGetLastError();
+  ChainLaunch l(dim3(blocks), dim3(256), 0, stream, pdl_wait != 0);
+  return table_bf16 ? cudaLaunchKernelEx(&l.cfg, embed_gather_kernel<true>, table, index, vocab, hidden, scale,
+                                         recast_bf16, out, pdl_trigger, pdl_wait)
+                    : cudaLaunchKernelEx(&l.cfg, embed_gather_kernel<false>, table, index, vocab, hidden, scale,
+                                         recast_bf16, out, pdl_trigger, pdl_wait);
 }
 
 size_t lm_head_smem_bytes(int w_bf16, int n_rows, int hidden) {
@@ -285,8 +296,8 @@ cudaError_t launch_lm_head_argmax(const LmHeadArgs& a, int sm_count, cudaStream_
       cudaError_t e = cudaFuncSetAttribute(lm_head_argmax_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
       if (e != cudaSuccess) return e;
     }
-    lm_head_argmax_bf16_kernel<<<blocks, LM_THREADS, smem, stream>>>(a);
-    return cudaGetLastError();
+    ChainLaunch l(dim3(blocks), dim3(LM_THREADS), smem, stream, a.pdl_wait != 0);
+    return cudaLaunchKernelEx(&l.cfg, lm_head_argmax_bf16_kernel, a);
   }
   const int R = a.n_rows <= 1 ? 1 : a.n_rows <= 2 ? 2 : a.n_rows <= 4 ? 4 : 8;
   per_sm = per_sm > 4 ? 4 : per_sm < 1 ? 1 : per_sm;

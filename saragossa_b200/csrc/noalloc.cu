@@ -55,9 +55,7 @@ static int noalloc_scratch(int device, unsigned char** out) {
   if (device < 0 || device >= NOALLOC_MAX_DEVICES) return fail(SGK_ERR_CONFIG, "device %d out of range", device);
   std::lock_guard<std::mutex> lock(g_noalloc_mutex);
   if (g_noalloc_ptr[device] == nullptr) {
-    int current = -1;
-    SGK_CUDA(cudaGetDevice(&current));
-    if (current != device) SGK_CUDA(cudaSetDevice(device));
+    // the caller has made `device` current (DeviceGuard in the entry point)
     void* ptr = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
     if (e != cudaSuccess || ptr == nullptr)
@@ -68,6 +66,23 @@ static int noalloc_scratch(int device, unsigned char** out) {
   *out = g_noalloc_ptr[device];
   return SGK_OK;
 }
+
+// Makes `device` current for the duration of a call and puts the caller's device back.
+struct DeviceGuard {
+  int previous = -1;
+  bool switched = false;
+  cudaError_t enter(int device) {
+    cudaError_t e = cudaGetDevice(&previous);
+    if (e != cudaSuccess) return e;
+    if (previous == device) return cudaSuccess;
+    e = cudaSetDevice(device);
+    switched = e == cudaSuccess;
+    return e;
+  }
+  ~DeviceGuard() {
+    if (switched) cudaSetDevice(previous);
+  }
+};
 
 // Bytes of workspace a launch with `splits` splits needs after the counters.
 static size_t noalloc_need(int q_heads, int hd, int splits) {
@@ -106,10 +121,17 @@ extern "C" int32_t sgk_kv_enqueue_attention_noalloc(sgk_kv* kv, void* stream, co
   if (window_start / PAGE_TOKENS < kv->seq->released_pages)
     return fail(SGK_ERR_DIMENSION, "attention window reaches rows released by the sliding window");
 
+  // The state's device is current for every call (not only for the first one, which resolves the
+  // symbol), and the caller's own current device is put back on return.
+  DeviceGuard guard;
+  SGK_CUDA(guard.enter(st->device));
   unsigned char* scratch = nullptr;
   SGK_TRY(noalloc_scratch(st->device, &scratch));
 
-  const bool mma = attention_mma_supported(pool->dtype, hd, qh / kvh);
+  // the same kernel selection as the allocating entry point: tensor-core kernels over bf16 and over
+  // u8 group-32 pages, the generic kernel for everything else
+  const bool u8 = attention_u8_supported(pool->dtype, hd, qh / kvh);
+  const bool mma = u8 || attention_mma_supported(pool->dtype, hd, qh / kvh);
   // split count: fill the SMs (two blocks each for the tensor-core kernel, eight for the
   // generic one), keep a few pages per split, and stay inside the static workspace
   const int64_t pages = (len - window_start + PAGE_TOKENS - 1) / PAGE_TOKENS;
@@ -162,7 +184,10 @@ extern "C" int32_t sgk_kv_enqueue_attention_noalloc(sgk_kv* kv, void* stream, co
   a.num_pages = pool->num_pages;
   a.k_new = nullptr;
   a.v_new = nullptr;
-  if (mma) {
+  if (u8) {
+    a.n_stages = attention_u8_max_stages(hd);
+    SGK_CUDA(launch_attention_u8(a, 1, cs));
+  } else if (mma) {
     a.n_stages = attention_mma_max_stages(hd);
     SGK_CUDA(launch_attention_mma(a, 1, cs));
   } else {

@@ -56,6 +56,13 @@ def encode_gated_delta_step_batch(states, layer, shape, d_q, d_k, d_v, d_g, d_be
                                                                  d_k.ptr, d_v.ptr, d_g.ptr, d_beta.ptr, d_out.ptr))
 
 
+class TokenIO(C.Structure):
+    """sgk_token_io: what the whole-token graph reads and writes around the layers."""
+    _fields_ = [("d_table", C.c_void_p), ("table_dtype", C.c_int32), ("vocab", C.c_int64), ("hidden", C.c_int32),
+                ("embedding_scale", C.c_float), ("recast_bf16", C.c_int32), ("d_x", C.c_void_p),
+                ("d_lm_weight", C.c_void_p), ("lm_weight_dtype", C.c_int32), ("d_final", C.c_void_p)]
+
+
 class LinearShape(C.Structure):
     """sgk_linear_shape."""
     _fields_ = [("num_key_heads", C.c_int32), ("num_value_heads", C.c_int32), ("key_head_dim", C.c_int32),
@@ -673,6 +680,24 @@ class Step:
 
     def replay(self, stream=None):
         check(self.L.sgk_step_replay(self.h, stream))
+
+    def token_capture(self, window, d_table, table_dtype, vocab, hidden, d_x, d_lm_weight, lm_weight_dtype, d_final,
+                      d_k, d_v, d_q, d_out, sliding_windows=None, attn_scalar=0.0, embedding_scale=1.0,
+                      recast_bf16=False):
+        """The whole token as ONE graph per ring slot: embedding lookup by the previous token's index,
+        every layer, greedy epilogue into the window (sgk_token_capture)."""
+        keep, p = self._windows(sliding_windows)
+        io = TokenIO(d_table.ptr, table_dtype, vocab, hidden, embedding_scale, 1 if recast_bf16 else 0, d_x.ptr,
+                     d_lm_weight.ptr, lm_weight_dtype, d_final.ptr)
+        check(self.L.sgk_token_capture(self.h, window.h, C.byref(io), d_k.ptr, d_v.ptr, d_q.ptr, d_out.ptr, p,
+                                       attn_scalar))
+
+    def token_seed(self, first_token: int, stream=None):
+        check(self.L.sgk_token_seed(self.h, first_token, stream))
+
+    def token_submit(self, stream=None):
+        """One submission = one token."""
+        check(self.L.sgk_token_submit(self.h, stream))
 
     def run_host(self, k, v, q, out, sliding_windows=None, attn_scalar=0.0):
         keep, p = self._windows(sliding_windows)

@@ -300,3 +300,69 @@ def test_token_window_full_and_stop_token_drain(gpu_state):
     assert win.inflight == 0
     assert gpu_state.device_status() == 0
     win.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("depth", [1, 4])
+def test_whole_token_is_one_graph_submission(gpu_state, depth):
+    """sgk_token_capture: embedding lookup by the previous token's index, every layer's fused
+    append + attention and the greedy epilogue into the window's ring are ONE graph per ring slot,
+    and a token is ONE submission (src/decoder/resident/decode.rs:183-458, one command buffer per
+    token). The token chain must be the oracle's, the layers must have appended a row per token,
+    and their outputs must be what the same step gives outside the graph."""
+    import saragossa_b200 as sg
+    emb, w, perm = _toy_model(23)
+    vocab, hidden = emb.shape
+    first, n, scale = 7, 19, 1.25
+    want = _oracle_chain(emb, w, first, n, scale)
+    q_heads, kv_heads, hd, layers, n0 = 4, 2, 128, 3, 70
+    kv_dim, q_dim = kv_heads * hd, q_heads * hd
+    outs = []
+    for mode in ("graph", "plain"):
+        pool = gpu_state.pool(layers, kv_heads, hd, sg.KV_BF16, num_pages=16, max_seqs=1, max_seq_tokens=160)
+        seq = pool.sequence(n0 + n + 8)
+        kvs = [seq.layer(layer, q_heads) for layer in range(layers)]
+        for layer, kv in enumerate(kvs):
+            kv.seed(sgo.fill_normal8(n0 * kv_dim, 51, 2 * layer).reshape(n0, kv_dim),
+                    sgo.fill_normal8(n0 * kv_dim, 51, 2 * layer + 1).reshape(n0, kv_dim), n0)
+        batches = [sg.Batch(gpu_state, [kv]) for kv in kvs]
+        step = sg.Step(gpu_state, batches)
+        d_k = gpu_state.upload(sgo.fill_normal8(layers * kv_dim, 52, 0))
+        d_v = gpu_state.upload(sgo.fill_normal8(layers * kv_dim, 52, 1))
+        d_q = gpu_state.upload(sgo.fill_normal8(layers * q_dim, 52, 2))
+        d_out = gpu_state.alloc(4 * layers * q_dim)
+        if mode == "graph":
+            d_e, d_w, d_x = gpu_state.upload(emb), gpu_state.upload(w), gpu_state.alloc(4 * hidden)
+            win = gpu_state.token_window(depth)
+            launches0 = step.launches()
+            step.token_capture(win, d_e, sg.KV_F32, vocab, hidden, d_x, d_w, sg.KV_F32, d_x, d_k, d_v, d_q, d_out,
+                               embedding_scale=scale)
+            assert all(kv.len() == n0 for kv in kvs)          # a capture runs nothing
+            step.token_seed(first)
+            got, enq = [], 0
+            while len(got) < n:
+                while enq < n and win.inflight < depth:
+                    step.token_submit()
+                    enq += 1
+                if enq < n:
+                    with pytest.raises(sg.InferError):
+                        step.token_submit()                    # the window is full
+                got.append(win.pop())
+            assert got == want
+            assert step.launches() - launches0 == n * (layers + 2)   # embed + layers + epilogue per token
+            win.close()
+        else:
+            for _ in range(n):
+                step.enqueue(d_k, d_v, d_q, d_out)
+        gpu_state.sync()
+        assert all(kv.len() == n0 + n for kv in kvs)
+        outs.append((d_out.download().copy(), [kv.gather_rows_f32(n0 - 1, n + 1) for kv in kvs]))
+        step.close()
+        for b in batches:
+            b.close()
+        seq.close()
+        pool.close()
+    assert np.array_equal(outs[0][0], outs[1][0])
+    for a, b in zip(outs[0][1], outs[1][1]):
+        assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+    assert gpu_state.device_status() == 0

@@ -27,6 +27,7 @@ def _close(a, b):
     (16, 2, 256, sg.KV_BF16, 1500),    # tensor-core kernel, head_dim 256
     (16, 2, 256, sg.KV_F32, 300),      # generic kernel
     (8, 4, 64, sg.KV_U8G32, 700),      # generic kernel, u8 pages
+    (16, 2, 256, sg.KV_U8G32, 2100),   # tensor-core kernel over u8 group-32 pages
 ])
 def test_noalloc_matches_regular_entry_point_twice(shape):
     q_heads, kv_heads, hd, dtype, n = shape
