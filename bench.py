@@ -386,7 +386,7 @@ def run_ours(args):
     producer = guarded(bulk_append_leg, sg, st, torch, stream)
     c3 = guarded(c3_token_leg, sg, st, torch, stream)
     c5 = guarded(c5_serving_leg, sg, st, torch, stream, dist, rank, world)
-    c4 = guarded(c4_prefix_leg, sg, st, torch, stream, 2000, 128, rank, world)
+    c4 = guarded(c4_prefix_leg, sg, st, torch, stream, args.c4_turns, 128, rank, world)
     c1 = guarded(c1_decode_leg, sg, st, torch, stream) if rank == 0 else None
     lm_head = guarded(lm_head_leg, sg, st, torch, stream)
 
@@ -741,6 +741,43 @@ def lm_head_leg(sg, st, torch, stream):
         want = torch.argmax(x[:rows] @ w.float().T, dim=1).to(torch.int32)
         out[f"rows{rows}"] = {"us": t * 1e6, "hbm_gbs": vocab * hidden * 2 / t / 1e9,
                               "matches_torch_argmax": bool((idx[:rows] == want).all().item())}
+    del w
+    # the same over affine-quantised weights (the format the reference's models ship in): u8 and u4
+    # codes, group 64, bf16 scale and bias; bytes = codes + 4 bytes of metadata per group
+    from saragossa_b200.resident import AffineWeight
+    peak, _ = measured_peak()
+    for bits in (8, 4):
+        per_word = 32 // bits
+        packed = torch.randint(0, 2 ** 31 - 1, (vocab, hidden // per_word), device=dev, generator=gen, dtype=torch.int32)
+        scales = (torch.rand(vocab, hidden // 64, device=dev, generator=gen) * (0.02 / (1 << bits)) + 1e-4).to(torch.bfloat16)
+        biases = (torch.randn(vocab, hidden // 64, device=dev, generator=gen) * 0.01).to(torch.bfloat16)
+        wq = AffineWeight(packed.data_ptr(), scales.data_ptr(), biases.data_ptr(), bits, 64)
+
+        def qstep():
+            st.encode_lm_head_argmax_affine(wq, vocab, hidden, _Ptr(x), _Ptr(idx), n_rows=1, stream=stream.cuda_stream)
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                qstep()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 10
+            stream.synchronize()
+            e0.record(stream)
+            for _ in range(reps):
+                qstep()
+            e1.record(stream)
+            stream.synchronize()
+        launches += 3 + reps
+        t = e0.elapsed_time(e1) * 1e-3 / reps
+        nbytes = vocab * hidden * bits // 8 + vocab * (hidden // 64) * 4
+        # reference value: dequantise on the device with torch and take the argmax
+        shifts = torch.arange(per_word, device=dev, dtype=torch.int32) * bits
+        codes = ((packed.unsqueeze(-1) >> shifts) & ((1 << bits) - 1)).reshape(vocab, hidden).float()
+        deq = codes * scales.float().repeat_interleave(64, dim=1) + biases.float().repeat_interleave(64, dim=1)
+        want = torch.argmax(x[:1] @ deq.T, dim=1).to(torch.int32)
+        out[f"affine_u{bits}_g64_rows1"] = {"us": t * 1e6, "weight_bytes": nbytes, "hbm_gbs": nbytes / t / 1e9,
+                                            "frac_of_peak": nbytes / t / 1e9 / peak,
+                                            "matches_torch_argmax": bool((idx[:1] == want).all().item())}
+        del packed, scales, biases, codes, deq
     out["launches"] = launches
     return out
 
@@ -1324,6 +1361,23 @@ def prefix_restore_gbs(sg, st, torch, stream):
             "shape": "36 layers, 8 KV heads, hd128, bf16, 16-token blocks (2.25 MiB per block)"}
 
 
+def run_leg(args):
+    import torch
+    import saragossa_b200 as sg
+    torch.cuda.set_device(0)
+    st = sg.DecodeResidentState(0)
+    stream = torch.cuda.Stream()
+    legs = {"prefix_restore": lambda: prefix_restore_gbs(sg, st, torch, stream),
+            "gated_delta_step": lambda: gated_delta_leg(sg, st, torch, stream),
+            "bulk_append": lambda: bulk_append_leg(sg, st, torch, stream),
+            "c3_hybrid_token": lambda: c3_token_leg(sg, st, torch, stream),
+            "c5_serving": lambda: c5_serving_leg(sg, st, torch, stream),
+            "c4_prefix_turns": lambda: c4_prefix_leg(sg, st, torch, stream, args.c4_turns, 128),
+            "c1_decode": lambda: c1_decode_leg(sg, st, torch, stream),
+            "lm_head_argmax": lambda: lm_head_leg(sg, st, torch, stream)}
+    print(json.dumps({args.leg: legs[args.leg]()}), flush=True)
+
+
 def main():
     global LAYERS, BATCH, CTX, Q_HEADS, KV_HEADS, HEAD_DIM, KV_DIM, Q_DIM, KV_DTYPE
     ap = argparse.ArgumentParser()
@@ -1341,7 +1395,14 @@ def main():
     ap.add_argument("--kv-dtype", default=KV_DTYPE, choices=["bf16", "u8"])
     ap.add_argument("--skip-extras", action="store_true",
                     help="only the device-resident timing (no e2e, batch-1, prefix-restore or CPU legs)")
+    ap.add_argument("--leg", default=None,
+                    choices=["prefix_restore", "gated_delta_step", "bulk_append", "c3_hybrid_token", "c5_serving",
+                             "c4_prefix_turns", "c1_decode", "lm_head_argmax"],
+                    help="profiling aid: run ONE of the side legs on one GPU and print its JSON (not a bench line)")
+    ap.add_argument("--c4-turns", type=int, default=2000, help="turns of the config-4 leg (2000 as stated)")
     args = ap.parse_args()
+    if args.leg:
+        return run_leg(args)
     reduced = (args.layers, args.batch, args.ctx, args.q_heads, args.kv_heads, args.head_dim, args.kv_dtype) != (
         LAYERS, BATCH, CTX, Q_HEADS, KV_HEADS, HEAD_DIM, KV_DTYPE)
     LAYERS, BATCH, CTX = args.layers, args.batch, args.ctx

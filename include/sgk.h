@@ -316,6 +316,29 @@ int32_t sgk_linstate_restore(sgk_linstate* ls, void* stream, const sgk_linstate*
 int32_t sgk_lm_head_enqueue_argmax(sgk_state* state, void* stream, const void* d_weight, int32_t weight_dtype,
                                    int64_t vocab, int32_t hidden, const float* d_x, int32_t n_rows,
                                    int32_t index_offset, int32_t* d_index_out, float* d_value_out);
+/* Affine-quantised weight in the layout the reference loads (src/quantization.rs:173-238; MLX's):
+ * codes of `bits` (4 or 8) packed LSB-first into 32-bit words, row-major [rows][cols * bits / 32];
+ * one bf16 scale and one bf16 bias per (row, group of `group_size` columns), [rows][cols /
+ * group_size] each; value = code * scale + bias. */
+typedef struct {
+  const uint32_t* d_packed;
+  const uint16_t* d_scales;
+  const uint16_t* d_biases;
+  int32_t bits;
+  int32_t group_size;
+} sgk_affine_weight;
+/* sgk_lm_head_enqueue_argmax over an affine-quantised weight (encode_affine_argmax_qmv_fast,
+ * src/metal_backend/lm_head.rs:934-990; kernel affine_argmax_qmv_fast_u4_gs64_f32): bits 4 or 8,
+ * group_size 64 or 128, hidden a multiple of the group size, 1-8 activation rows. The codes go
+ * through the tensor cores as exact fp16 values, scale and bias are applied per group in f32. */
+int32_t sgk_lm_head_enqueue_argmax_affine(sgk_state* state, void* stream, const sgk_affine_weight* weight,
+                                          int64_t vocab, int32_t hidden, const float* d_x, int32_t n_rows,
+                                          int32_t index_offset, int32_t* d_index_out, float* d_value_out);
+/* sgk_embed_enqueue_from_index over an affine-quantised table: the row is dequantised
+ * (code * scale + bias, rounded like the CPU path: one multiply, one add) and scaled. */
+int32_t sgk_embed_enqueue_from_index_affine(sgk_state* state, void* stream, const sgk_affine_weight* table,
+                                            int64_t vocab, int32_t hidden, const int32_t* d_index,
+                                            float embedding_scale, int32_t recast_bf16, float* d_out);
 /* Token feed: the input row of the next token, looked up by an index that lives on the device
  * (encode_embedding_from_index_buffers_scaled, src/metal_backend/matmul_encode.rs:424-557; kernel
  * embed_gather_dense_from_u32_f32, src/kernels.metal:308-325): d_out[hidden] = table[*d_index] *
@@ -402,8 +425,8 @@ int32_t sgk_token_window_drain(sgk_token_window* w);
  * into the ring; sgk_token_submit launches the next token's graph (Dimension error when the
  * window is full) and sgk_token_window_pop returns the oldest token's index. */
 typedef struct {
-  const void* d_table;      /* embedding table [vocab][hidden] */
-  int32_t table_dtype;      /* SGK_KV_F32, SGK_KV_BF16, or SGK_W_U8G64 / SGK_W_U4G64 with the arrays below */
+  const void* d_table;      /* embedding table [vocab][hidden], dense (NULL when table_affine is given) */
+  int32_t table_dtype;      /* SGK_KV_F32 or SGK_KV_BF16 */
   int64_t vocab;
   int32_t hidden;
   float embedding_scale;
@@ -412,6 +435,8 @@ typedef struct {
   const void* d_lm_weight;  /* lm_head weight [vocab][hidden] (may be the table: tied) */
   int32_t lm_weight_dtype;
   const float* d_final;     /* the final hidden row the epilogue reads */
+  const sgk_affine_weight* table_affine;  /* not NULL: the table is affine-quantised (d_table ignored) */
+  const sgk_affine_weight* lm_affine;     /* not NULL: the lm_head weight is (d_lm_weight ignored) */
 } sgk_token_io;
 int32_t sgk_token_capture(sgk_step* step, sgk_token_window* window, const sgk_token_io* io, const float* d_k,
                           const float* d_v, const float* d_q, float* d_out, const int64_t* sliding_windows,
@@ -522,6 +547,27 @@ int64_t sgk_prefix_session_count(const sgk_prefix* pc, const uint8_t session[32]
 /* Trace hook: which = 0 live entries front-to-rear, 1 = every entry that left, in order. */
 int64_t sgk_prefix_dump(const sgk_prefix* pc, int32_t which, int64_t cap, uint8_t* sessions,
                         uint8_t* hashes, int64_t* tokens);
+/* The decoder-internal prefix cache (src/decoder/generation.rs:2998-3139; capacity
+ * RETI_RUST_PREFIX_CACHE_CAP, 4 by default, src/runtime_flags.rs:670-678): whole prompts, most
+ * recent first.
+ *   get  prefix_cache_get (:2998-3024) up to the suffix: the longest entry that is a prefix of the
+ *        prompt moves to the front, its rows become `seq`'s (pages shared by reference, copied
+ *        before anybody writes to them; the recurrent state, if the entry has one, is copied into
+ *        `ls`) and *cached_len_out = its length; 0 on a miss, the sequence untouched. The caller
+ *        appends the rows of prompt[cached_len..] and then puts the whole prompt (:3019-3022).
+ *   put  prefix_cache_put (:3105-3139): an entry with the same tokens is replaced, the new one
+ *        goes to the front, entries beyond the capacity fall off the rear; capacity 0 stores nothing.
+ * pool may be NULL (bookkeeping only; seq and ls NULL then). */
+typedef struct sgk_dprefix sgk_dprefix;
+int32_t sgk_dprefix_create(sgk_pool* pool, int64_t capacity, sgk_dprefix** out);
+void sgk_dprefix_destroy(sgk_dprefix* dp);
+int32_t sgk_dprefix_get(sgk_dprefix* dp, const uint64_t* prompt, size_t n, sgk_seq* seq, sgk_linstate* ls,
+                        void* stream, int64_t* cached_len_out);
+int32_t sgk_dprefix_put(sgk_dprefix* dp, const uint64_t* tokens, size_t n, sgk_seq* seq, sgk_linstate* ls,
+                        void* stream);
+int64_t sgk_dprefix_len(const sgk_dprefix* dp);
+/* Trace hook: the tokens of entry `index` (front = 0); returns their number, -1 past the end. */
+int64_t sgk_dprefix_entry_tokens(const sgk_dprefix* dp, int64_t index, uint64_t* tokens_out, int64_t cap);
 /* Decoder-internal longest-prefix selection (src/decoder/generation.rs:190-204). */
 int64_t sgk_longest_prefix_entry_index(const uint64_t* flat_tokens, const size_t* lens,
                                        size_t n_entries, const uint64_t* prompt, size_t n);

@@ -507,3 +507,61 @@ def fill_normal8(n, seed, stream, index0=0):
     out = np.empty(n, np.float32)
     lib().sgo_fill_normal8(_fp(out), n, seed, stream, index0)
     return out
+
+
+def affine_dequantize(packed, scales_bf16, biases_bf16, bits, group_size, rows, cols):
+    """AffineQuantizedTensor::dequantize (src/quantization.rs:131-179, bitpacked_value :208-228):
+    code of column c sits at bit offset c * bits of its row, LSB first inside 32-bit words; value =
+    code * scale + bias in f32 with the group's scale and bias (stored as bf16 here, as the Metal
+    buffers of src/metal_backend/lm_head.rs:960-963 hold them). numpy restatement for 4 and 8 bits
+    (both divide 32: no code straddles a word)."""
+    assert bits in (4, 8) and cols % group_size == 0
+    packed = np.ascontiguousarray(packed, np.uint32).reshape(rows, cols * bits // 32)
+    per_word = 32 // bits
+    shifts = (np.arange(per_word, dtype=np.uint32) * bits)[None, None, :]
+    codes = ((packed[:, :, None] >> shifts) & np.uint32((1 << bits) - 1)).reshape(rows, cols).astype(np.float32)
+    to_f32 = lambda b: (np.ascontiguousarray(b, np.uint16).astype(np.uint32) << 16).view(np.float32)
+    scale = np.repeat(to_f32(scales_bf16).reshape(rows, cols // group_size), group_size, axis=1)
+    bias = np.repeat(to_f32(biases_bf16).reshape(rows, cols // group_size), group_size, axis=1)
+    return (codes * scale).astype(np.float32) + bias
+
+
+def affine_pack(codes, bits):
+    """Inverse of the unpacking above: codes [rows][cols] -> u32 words, LSB first."""
+    codes = np.ascontiguousarray(codes, np.uint32)
+    rows, cols = codes.shape
+    per_word = 32 // bits
+    c = codes.reshape(rows, cols // per_word, per_word)
+    shifts = (np.arange(per_word, dtype=np.uint32) * bits)[None, None, :]
+    return np.bitwise_or.reduce(c << shifts, axis=2).astype(np.uint32)
+
+
+class DecoderPrefixCache:
+    """The decoder-internal prefix cache, bookkeeping only (src/decoder/generation.rs:2998-3139):
+    get = longest_prefix_entry_index, remove, re-insert at the front (:3003-3013); when the hit is
+    shorter than the prompt the caller extends it and puts the whole prompt (:3019-3022); put =
+    drop the entry with the same tokens, insert at the front, truncate to the capacity (:3118-3137)."""
+
+    def __init__(self, capacity=4):
+        self.capacity = capacity
+        self.entries = []          # token lists, front = most recent
+
+    def get(self, prompt):
+        idx = longest_prefix_entry_index(self.entries, prompt)
+        if idx is None:
+            return 0
+        entry = self.entries.pop(idx)
+        self.entries.insert(0, entry)
+        cached = len(entry)
+        if cached < len(prompt):
+            self.put(prompt)
+        return cached
+
+    def put(self, prompt):
+        if self.capacity == 0:
+            return
+        prompt = list(prompt)
+        if prompt in self.entries:
+            self.entries.remove(prompt)
+        self.entries.insert(0, prompt)
+        del self.entries[self.capacity:]

@@ -19,6 +19,7 @@ struct sgk_token_window : TokenWindow {};
 struct sgk_exchange : Exchange {};
 struct sgk_prefix : Prefix {};
 struct sgk_budget : Budget {};
+struct sgk_dprefix : DecoderPrefix {};
 
 namespace sgk {
 int create_batch(State* st, Kv** kvs, int n, Batch** out);
@@ -64,6 +65,7 @@ void sgk_state_destroy(sgk_state* st) {
   cudaStreamSynchronize(st->stream);
   if (st->d_status) cudaFree(st->d_status);
   if (st->d_lm_ws) cudaFree(st->d_lm_ws);
+  if (st->d_rope_table) cudaFree(st->d_rope_table);
   if (st->stream) cudaStreamDestroy(st->stream);
   delete st;
 }
@@ -1083,6 +1085,63 @@ int32_t sgk_embed_enqueue_from_index(sgk_state* st, void* stream, const void* d_
   return SGK_OK;
 }
 
+static int32_t check_affine(const sgk_affine_weight* w, int32_t hidden, const char* what) {
+  if (!w || !w->d_packed || !w->d_scales || !w->d_biases) return fail(SGK_ERR_BACKEND, "%s: null pointer in the quantised weight", what);
+  if (w->bits != 4 && w->bits != 8) return fail(SGK_ERR_CONFIG, "%s: %d-bit codes (4 and 8 are supported)", what, w->bits);
+  if (w->group_size != 64 && w->group_size != 128)
+    return fail(SGK_ERR_CONFIG, "%s: group size %d (64 and 128 are supported)", what, w->group_size);
+  if (hidden <= 0 || hidden % w->group_size != 0)
+    return fail(SGK_ERR_DIMENSION, "%s: hidden %d is not a multiple of the group size %d", what, hidden, w->group_size);
+  if (reinterpret_cast<uintptr_t>(w->d_packed) & 15) return fail(SGK_ERR_CONFIG, "%s: codes must be 16-byte aligned", what);
+  return SGK_OK;
+}
+
+int32_t sgk_lm_head_enqueue_argmax_affine(sgk_state* st, void* stream, const sgk_affine_weight* weight, int64_t vocab,
+                                          int32_t hidden, const float* d_x, int32_t n_rows, int32_t index_offset,
+                                          int32_t* d_index_out, float* d_value_out) {
+  if (!st || !d_x || !d_index_out) return fail(SGK_ERR_BACKEND, "null argument");
+  SGK_TRY(check_affine(weight, hidden, "lm_head argmax"));
+  if (vocab <= 0 || vocab > 0x7fffffffLL) return fail(SGK_ERR_DIMENSION, "lm_head argmax: vocab %lld invalid", (long long)vocab);
+  if (n_rows < 1 || n_rows > 8) return fail(SGK_ERR_DIMENSION, "lm_head argmax: %d rows, 1 to 8 per call", n_rows);
+  if (lm_head_affine_smem_bytes(n_rows, hidden, weight->group_size) > size_t(200) * 1024)
+    return fail(SGK_ERR_CONFIG, "lm_head argmax: %d rows of %d values do not fit 200 KiB of shared memory", n_rows, hidden);
+  LmHeadAffineArgs a{};
+  a.w = AffineWeight{weight->d_packed, weight->d_scales, weight->d_biases, weight->bits, weight->group_size};
+  a.vocab = vocab;
+  a.hidden = hidden;
+  a.n_rows = n_rows;
+  a.x = d_x;
+  a.keys = st->d_lm_ws;
+  a.counter = reinterpret_cast<unsigned int*>(st->d_lm_ws + 8);
+  a.index_offset = index_offset;
+  a.index_out = d_index_out;
+  a.value_out = d_value_out;
+  cudaStream_t cs = st->pick(stream);
+  const bool member = st->chain_member(cs);
+  a.pdl_trigger = member ? 1 : 0;
+  a.pdl_wait = st->chain_follows(cs) ? 1 : 0;
+  SGK_CUDA(launch_lm_head_argmax_affine(a, st->sm_count, cs));
+  st->launches += 1;
+  if (member) st->chain_note();
+  return SGK_OK;
+}
+
+int32_t sgk_embed_enqueue_from_index_affine(sgk_state* st, void* stream, const sgk_affine_weight* table, int64_t vocab,
+                                            int32_t hidden, const int32_t* d_index, float embedding_scale,
+                                            int32_t recast_bf16, float* d_out) {
+  if (!st || !d_index || !d_out) return fail(SGK_ERR_BACKEND, "null argument");
+  SGK_TRY(check_affine(table, hidden, "embedding"));
+  if (vocab <= 0 || vocab > 0x7fffffffLL) return fail(SGK_ERR_DIMENSION, "embedding: vocab %lld invalid", (long long)vocab);
+  cudaStream_t cs = st->pick(stream);
+  const bool member = st->chain_member(cs);
+  SGK_CUDA(launch_embed_gather_affine(AffineWeight{table->d_packed, table->d_scales, table->d_biases, table->bits, table->group_size},
+                                      d_index, vocab, hidden, embedding_scale, recast_bf16 != 0, d_out, member ? 1 : 0,
+                                      st->chain_follows(cs) ? 1 : 0, cs));
+  st->launches += 1;
+  if (member) st->chain_note();
+  return SGK_OK;
+}
+
 // ------------------------------------------------------------------ peer memory and the exchange
 int32_t sgk_peer_export(sgk_state* st, void* d_ptr, uint8_t handle_out[64]) {
   if (!st || !d_ptr || !handle_out) return fail(SGK_ERR_BACKEND, "null argument");
@@ -1281,7 +1340,7 @@ int32_t sgk_token_capture(sgk_step* s, sgk_token_window* w, const sgk_token_io* 
                           const float* d_q, float* d_out, const int64_t* sliding_windows, float attn_scalar) {
   if (!s || !w || !io) return fail(SGK_ERR_BACKEND, "token_capture: null argument");
   if (!d_k || !d_v || !d_q || !d_out) return fail(SGK_ERR_BACKEND, "token_capture: null device pointer");
-  if (!io->d_table || !io->d_x || !io->d_lm_weight || !io->d_final)
+  if ((!io->d_table && !io->table_affine) || !io->d_x || (!io->d_lm_weight && !io->lm_affine) || !io->d_final)
     return fail(SGK_ERR_BACKEND, "token_capture: null pointer in the token's inputs");
   if (w->st != s->st) return fail(SGK_ERR_CONFIG, "token_capture: window and step belong to different states");
   if (w->inflight != 0) return fail(SGK_ERR_DIMENSION, "token_capture with %d tokens in flight", w->inflight);
@@ -1313,12 +1372,18 @@ int32_t sgk_token_capture(sgk_step* s, sgk_token_window* w, const sgk_token_io* 
     st->chain_active = true;   // the token is one chain: embedding, layers, epilogue
     st->chain_stream = stream;
     st->chain_mark = -1;
-    rc = sgk_embed_enqueue_from_index(static_cast<sgk_state*>(st), stream, io->d_table, io->table_dtype, io->vocab, io->hidden,
-                                      d_prev, io->embedding_scale, io->recast_bf16, io->d_x);
+    rc = io->table_affine
+             ? sgk_embed_enqueue_from_index_affine(static_cast<sgk_state*>(st), stream, io->table_affine, io->vocab, io->hidden,
+                                                   d_prev, io->embedding_scale, io->recast_bf16, io->d_x)
+             : sgk_embed_enqueue_from_index(static_cast<sgk_state*>(st), stream, io->d_table, io->table_dtype, io->vocab,
+                                            io->hidden, d_prev, io->embedding_scale, io->recast_bf16, io->d_x);
     if (rc == SGK_OK) rc = s->enqueue(stream, d_k, d_v, d_q, d_out, sliding_windows, attn_scalar);
     if (rc == SGK_OK)
-      rc = sgk_lm_head_enqueue_argmax(static_cast<sgk_state*>(st), stream, io->d_lm_weight, io->lm_weight_dtype, io->vocab,
-                                      io->hidden, io->d_final, 1, 0, w->d_ring + slot, nullptr);
+      rc = io->lm_affine
+               ? sgk_lm_head_enqueue_argmax_affine(static_cast<sgk_state*>(st), stream, io->lm_affine, io->vocab, io->hidden,
+                                                   io->d_final, 1, 0, w->d_ring + slot, nullptr)
+               : sgk_lm_head_enqueue_argmax(static_cast<sgk_state*>(st), stream, io->d_lm_weight, io->lm_weight_dtype,
+                                            io->vocab, io->hidden, io->d_final, 1, 0, w->d_ring + slot, nullptr);
     st->chain_active = false;
     if (rc == SGK_OK) {
       cudaError_t ce = cudaMemcpyAsync(w->h_ring + slot, w->d_ring + slot, sizeof(int32_t), cudaMemcpyDeviceToHost, stream);
@@ -1724,6 +1789,114 @@ int64_t sgk_longest_prefix_entry_index(const uint64_t* flat, const size_t* lens,
     off += len;
   }
   return best;
+}
+
+// ------------------------------------------------------------------ decoder-internal prefix cache
+int32_t sgk_dprefix_create(sgk_pool* pool, int64_t capacity, sgk_dprefix** out) {
+  if (!out) return fail(SGK_ERR_BACKEND, "dprefix_create: null out pointer");
+  if (capacity < 0) return fail(SGK_ERR_CONFIG, "prefix cache: negative capacity");
+  auto dp = std::make_unique<sgk_dprefix>();
+  dp->pool = pool;
+  dp->capacity = capacity;
+  *out = dp.release();
+  return SGK_OK;
+}
+
+void sgk_dprefix_destroy(sgk_dprefix* dp) {
+  if (!dp) return;
+  Pool* pool = dp->pool;
+  if (pool && !pool->host_only()) {
+    cudaSetDevice(pool->st->device);
+    cudaStreamSynchronize(pool->st->stream);
+  }
+  delete static_cast<DecoderPrefix*>(dp);
+  if (pool && !pool->host_only()) pool->flush_scrub(pool->st->stream);
+}
+
+int64_t sgk_dprefix_len(const sgk_dprefix* dp) { return dp ? static_cast<int64_t>(dp->entries.size()) : 0; }
+
+int64_t sgk_dprefix_entry_tokens(const sgk_dprefix* dp, int64_t index, uint64_t* tokens_out, int64_t cap) {
+  if (!dp || index < 0 || index >= static_cast<int64_t>(dp->entries.size())) return -1;
+  const auto& t = dp->entries[static_cast<size_t>(index)].tokens;
+  if (tokens_out)
+    for (int64_t i = 0; i < std::min<int64_t>(cap, static_cast<int64_t>(t.size())); ++i) tokens_out[i] = t[static_cast<size_t>(i)];
+  return static_cast<int64_t>(t.size());
+}
+
+// prefix_cache_put (src/decoder/generation.rs:3105-3139)
+int32_t sgk_dprefix_put(sgk_dprefix* dp, const uint64_t* tokens, size_t n, sgk_seq* seq, sgk_linstate* ls, void* stream) {
+  if (!dp || (n > 0 && !tokens)) return fail(SGK_ERR_BACKEND, "null argument");
+  if (dp->capacity == 0) return SGK_OK;   // :3110-3113
+  if (dp->pool && !seq) return fail(SGK_ERR_BACKEND, "prefix cache put needs the sequence to snapshot");
+  DecoderPrefixEntry e;
+  e.tokens.assign(tokens, tokens + n);
+  if (seq) {
+    if (seq->pool != dp->pool) return fail(SGK_ERR_CONFIG, "sequence belongs to another pool");
+    for (int64_t l : seq->len)
+      if (l < static_cast<int64_t>(n))
+        return fail(SGK_ERR_DIMENSION, "snapshot of %zu rows from a sequence holding %lld", n, (long long)l);
+    if (seq->released_pages > 0) return fail(SGK_ERR_DIMENSION, "snapshot of a sequence whose head was released");
+    const size_t n_pages = (n + PAGE_TOKENS - 1) / PAGE_TOKENS;
+    e.pages.assign(seq->pages.begin(), seq->pages.begin() + static_cast<long>(n_pages));
+  }
+  if (ls) {
+    LinState* snap = nullptr;
+    SGK_TRY(linstate_snapshot(ls, stream, &snap));
+    e.ls.reset(snap);
+  }
+  for (int32_t p : e.pages) dp->pool->retain(p);
+  // an entry with the same tokens is replaced (:3118-3125), the new one goes to the front, the rear is cut (:3137)
+  for (size_t i = 0; i < dp->entries.size(); ++i)
+    if (dp->entries[i].tokens == e.tokens) {
+      dp->drop(i);
+      break;
+    }
+  dp->entries.insert(dp->entries.begin(), std::move(e));
+  while (static_cast<int64_t>(dp->entries.size()) > dp->capacity) dp->drop(dp->entries.size() - 1);
+  if (dp->pool && !dp->pool->host_only()) SGK_TRY(dp->pool->flush_scrub(dp->pool->st->stream));
+  return SGK_OK;
+}
+
+// prefix_cache_get (:2998-3024) up to the point where the caller extends the suffix: the longest
+// entry that is a prefix of the prompt moves to the front and its rows become the sequence's
+// (shared by reference; the entry is never aliased for writing: a shared page is copied before
+// it is written). *cached_len_out = 0 on a miss (the sequence is left alone). The caller appends
+// the rows of prompt[cached_len..] and, when there were any, calls sgk_dprefix_put with the whole
+// prompt, as the reference does (:3019-3022).
+int32_t sgk_dprefix_get(sgk_dprefix* dp, const uint64_t* prompt, size_t n, sgk_seq* seq, sgk_linstate* ls, void* stream,
+                        int64_t* cached_len_out) {
+  if (!dp || !cached_len_out || (n > 0 && !prompt)) return fail(SGK_ERR_BACKEND, "null argument");
+  *cached_len_out = 0;
+  long best = -1;
+  size_t best_len = 0;
+  for (size_t i = 0; i < dp->entries.size(); ++i) {   // longest_prefix_entry_index (:190-204)
+    const auto& t = dp->entries[i].tokens;
+    if (t.size() > best_len && t.size() <= n && std::equal(t.begin(), t.end(), prompt)) {
+      best = static_cast<long>(i);
+      best_len = t.size();
+    }
+  }
+  if (best < 0) return SGK_OK;
+  std::rotate(dp->entries.begin(), dp->entries.begin() + best, dp->entries.begin() + best + 1);
+  const DecoderPrefixEntry& e = dp->entries.front();
+  if (dp->pool) {
+    if (!seq) return fail(SGK_ERR_BACKEND, "prefix cache get needs a sequence to restore into");
+    if (seq->pool != dp->pool) return fail(SGK_ERR_CONFIG, "sequence belongs to another pool");
+    if (static_cast<int64_t>(best_len) > seq->capacity)
+      return fail(SGK_ERR_DIMENSION, "restore of %zu rows > capacity %lld", best_len, (long long)seq->capacity);
+    if (e.ls && !ls) return fail(SGK_ERR_SHAPE, "entry holds a linear-attention state but none was given to restore into");
+    Pool* pool = dp->pool;
+    cudaStream_t cs = pool->host_only() ? nullptr : pool->st->pick(stream);
+    std::vector<int32_t> pages = e.pages;          // the entry may not be referenced across release_all
+    for (int32_t p : pages) pool->retain(p);
+    seq->release_all();
+    seq->pages = pages;
+    SGK_TRY(seq->publish(0, static_cast<int64_t>(seq->pages.size()), cs, true));
+    SGK_TRY(seq->set_len_all(static_cast<int64_t>(best_len), cs));
+    if (e.ls) SGK_TRY(sgk_linstate_restore(ls, stream, static_cast<sgk_linstate*>(e.ls.get())));
+  }
+  *cached_len_out = static_cast<int64_t>(best_len);
+  return SGK_OK;
 }
 
 // ------------------------------------------------------------------ budget

@@ -53,6 +53,9 @@ struct State {
   int sm_count = 148;
   cudaStream_t stream = nullptr;
   int32_t* d_status = nullptr;
+  // {cos, sin} table of a bulk append with rope (grown on demand; reuse is ordered by the stream)
+  float2* d_rope_table = nullptr;
+  size_t rope_table_cap = 0;
   unsigned long long* d_lm_ws = nullptr;  // lm_head argmax: [0..8) best key per row, [8] blocks-done counter; zero between launches
   int64_t launches = 0;  // kernels launched through this state
   // false (default): the caller never has two launches of this state in flight on different
@@ -370,6 +373,23 @@ struct Prefix {
   int insert(const Hash32& session, const Hash32& hash, int64_t tokens, Seq* seq, LinState* ls, void* stream,
              int32_t* inserted_out);
   ~Prefix();
+};
+
+// The decoder-internal prefix cache (src/decoder/generation.rs:2998-3139): whole prompts, most
+// recent first, capacity RETI_RUST_PREFIX_CACHE_CAP (4 by default). An entry holds the pages of
+// its prompt by reference (a partly filled last page is shared too: whoever appends to it next
+// copies it first) and, when the model has recurrent layers, a snapshot of their state.
+struct DecoderPrefixEntry {
+  std::vector<uint64_t> tokens;
+  std::vector<int32_t> pages;
+  std::unique_ptr<LinState> ls;
+};
+struct DecoderPrefix {
+  Pool* pool = nullptr;
+  int64_t capacity = 4;
+  std::vector<DecoderPrefixEntry> entries;   // front = most recently used
+  void drop(size_t index);
+  ~DecoderPrefix();
 };
 
 struct Budget {

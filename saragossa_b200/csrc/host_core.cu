@@ -407,6 +407,28 @@ int Batch::enqueue_append(cudaStream_t stream, const float* d_k, const float* d_
     a.n_rows = piece;
     a.k = d_k + size_t(done) * kvs[0]->kv_dim();
     a.v = d_v + size_t(done) * kvs[0]->kv_dim();
+    a.rope_table = nullptr;
+    if (rope != nullptr && piece >= 16) {
+      // cos and sin of (row, pair) depend neither on the head nor on the sequence: one small launch
+      // makes them for the rows of this piece, every page tile of every head reads them
+      int64_t lo = INT64_MAX, hi = 0;
+      for (Kv* kv : kvs) lo = std::min(lo, kv->len() + done), hi = std::max(hi, kv->len() + done + piece);
+      const size_t pairs = size_t(rope->rope_dims / 2);
+      const size_t need = size_t(hi - lo) * pairs;
+      if (pairs > 0 && hi - lo <= 65536) {
+        if (need > st->rope_table_cap) {
+          if (st->d_rope_table) cudaFree(st->d_rope_table);
+          st->d_rope_table = nullptr, st->rope_table_cap = 0;
+          const size_t cap = std::max(need, size_t(4096) * 64);
+          SGK_CUDA(cudaMalloc(&st->d_rope_table, cap * sizeof(float2)));
+          st->rope_table_cap = cap;
+        }
+        SGK_CUDA(launch_rope_table(st->d_rope_table, lo, static_cast<int>(hi - lo), *rope, stream));
+        st->launches += 1;
+        a.rope_table = st->d_rope_table;
+        a.rope_row0 = lo;
+      }
+    }
     SGK_CUDA(launch_append_rows(a, n(), stream));
     st->launches += 1;
     done += piece;

@@ -336,6 +336,17 @@ int Prefix::insert(const Hash32& session, const Hash32& hash, int64_t tokens, Se
   return SGK_OK;
 }
 
+// ---- DecoderPrefix ---------------------------------------------------------------
+void DecoderPrefix::drop(size_t index) {
+  for (int32_t p : entries[index].pages)
+    if (pool) pool->release(p);
+  entries.erase(entries.begin() + static_cast<long>(index));
+}
+
+DecoderPrefix::~DecoderPrefix() {
+  while (!entries.empty()) drop(entries.size() - 1);
+}
+
 // ---- Budget (src/memory_guard.rs:168-185) -------------------------------------------
 bool Budget::limit(uint64_t* out) const {
   bool any = false;

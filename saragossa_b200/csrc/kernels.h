@@ -35,7 +35,14 @@ struct AppendArgs {
   const float* knorm_w;     // [head_dim]
   RopeArgs rope;
   float* out_k;             // not NULL: write normalised+rotated K rows here, touch no page
+  // not NULL (bulk appends with rope): {cos, sin} of (row - rope_row0, pair), [n][rope_dims / 2], made by
+  // launch_rope_table for this launch's rows: the angle does not depend on the head or on the sequence
+  const float2* rope_table;
+  int64_t rope_row0;
 };
+// {cos, sin}(position * position_scale / theta^(2 pair / frequency_dim)) for positions row0 .. row0 + n_rows - 1,
+// evaluated in double precision and rounded once to f32, like the CPU path (src/decoder/attention_ops.rs:848-887).
+cudaError_t launch_rope_table(float2* table, int64_t row0, int n_rows, const RopeArgs& rope, cudaStream_t stream);
 
 struct AttnArgs {
   PoolView pool;
@@ -207,6 +214,33 @@ struct LmHeadArgs {
   int32_t pdl_trigger, pdl_wait;   // member of a token chain (see GatedDeltaArgs)
 };
 cudaError_t launch_lm_head_argmax(const LmHeadArgs& a, int sm_count, cudaStream_t stream);
+// The same over an affine-quantised weight (MLX layout, src/quantization.rs:173-238): codes of
+// `bits` (4 or 8) packed LSB-first into u32 words, row-major [vocab][hidden * bits / 32]; one bf16
+// scale and one bf16 bias per (row, group of group_size columns); value = code * scale + bias.
+struct AffineWeight {
+  const uint32_t* packed;
+  const uint16_t* scales;
+  const uint16_t* biases;
+  int32_t bits, group_size;
+};
+struct LmHeadAffineArgs {
+  AffineWeight w;
+  int64_t vocab;
+  int32_t hidden;   // multiple of the group size (64 or 128)
+  int32_t n_rows;   // 1..8
+  const float* x;
+  unsigned long long* keys;
+  unsigned int* counter;
+  int32_t index_offset;
+  int32_t* index_out;
+  float* value_out;
+  int32_t pdl_trigger, pdl_wait;
+};
+cudaError_t launch_lm_head_argmax_affine(const LmHeadAffineArgs& a, int sm_count, cudaStream_t stream);
+size_t lm_head_affine_smem_bytes(int n_rows, int hidden, int group_size);
+cudaError_t launch_embed_gather_affine(const AffineWeight& table, const int32_t* index, int64_t vocab, int hidden,
+                                       float scale, int recast_bf16, float* out, int pdl_trigger, int pdl_wait,
+                                       cudaStream_t stream);
 size_t lm_head_smem_bytes(int w_bf16, int n_rows, int hidden);  // shared memory a launch needs
 // out[hidden] = table[*index] * scale (dense f32 or bf16 table); an index outside the table writes nothing.
 cudaError_t launch_embed_gather(const void* table, int table_bf16, const int32_t* index, int64_t vocab, int hidden,

@@ -322,12 +322,19 @@ __global__ void __launch_bounds__(128) append_tiles_kernel(AppendArgs a) {
       for (int i = tid; i < rows * pairs; i += blockDim.x) {
         const int r = i / pairs, pair = i % pairs;
         float* xs = ks + r * hd;
-        const float scaled_position = __fmul_rn(static_cast<float>(row_lo + r), a.rope.position_scale);
-        const float angle = __fdiv_rn(scaled_position, denom_s[pair]);
-        double sd, cd;
-        sincos(static_cast<double>(angle), &sd, &cd);
-        const float c = static_cast<float>(cd);
-        const float s = static_cast<float>(sd);
+        float c, s;
+        if (a.rope_table != nullptr) {
+          // made once per launch: cos and sin of (row, pair) depend neither on the head nor on the sequence
+          const float2 cs = __ldg(a.rope_table + (row_lo + r - a.rope_row0) * pairs + pair);
+          c = cs.x, s = cs.y;
+        } else {
+          const float scaled_position = __fmul_rn(static_cast<float>(row_lo + r), a.rope.position_scale);
+          const float angle = __fdiv_rn(scaled_position, denom_s[pair]);
+          double sd, cd;
+          sincos(static_cast<double>(angle), &sd, &cd);
+          c = static_cast<float>(cd);
+          s = static_cast<float>(sd);
+        }
         const int i0 = a.rope.interleaved ? 2 * pair : pair;
         const int i1 = a.rope.interleaved ? 2 * pair + 1 : pair + pairs;
         const float first = xs[i0], second = xs[i1];
@@ -414,6 +421,29 @@ __global__ void __launch_bounds__(128) append_tiles_kernel(AppendArgs a) {
 __global__ void set_len_kernel(int32_t* ptr, int n, int32_t value) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) ptr[i] = value;
+}
+
+__global__ void __launch_bounds__(128) rope_table_kernel(float2* table, int64_t row0, int n_rows, RopeArgs rope) {
+  const int pairs = rope.rope_dims / 2;
+  const int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x;
+  if (i >= int64_t(n_rows) * pairs) return;
+  const int64_t r = i / pairs;
+  const int pair = static_cast<int>(i % pairs);
+  // the float order of norm_rope_head
+  const float exponent = __fdiv_rn(static_cast<float>(2 * pair), static_cast<float>(rope.frequency_dim));
+  const float denom = static_cast<float>(pow(static_cast<double>(rope.theta), static_cast<double>(exponent)));
+  const float scaled_position = __fmul_rn(static_cast<float>(row0 + r), rope.position_scale);
+  const float angle = __fdiv_rn(scaled_position, denom);
+  double sd, cd;
+  sincos(static_cast<double>(angle), &sd, &cd);
+  table[i] = make_float2(static_cast<float>(cd), static_cast<float>(sd));
+}
+
+cudaError_t launch_rope_table(float2* table, int64_t row0, int n_rows, const RopeArgs& rope, cudaStream_t stream) {
+  const int64_t n = int64_t(n_rows) * (rope.rope_dims / 2);
+  if (n <= 0) return cudaSuccess;
+  rope_table_kernel<<<static_cast<unsigned>((n + 127) / 128), 128, 0, stream>>>(table, row0, n_rows, rope);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_append_rows(const AppendArgs& a, int n_seq, cudaStream_t stream) {

@@ -278,6 +278,288 @@ cudaError_t launch_embed_gather(const void* table, int table_bf16, const int32_t
                                          recast_bf16, out, pdl_trigger, pdl_wait);
 }
 
+
+// ---- affine-quantised weights (u4 / u8 codes, bf16 scale and bias per group) -----------------
+// encode_affine_argmax_qmv_fast (src/metal_backend/lm_head.rs:934-990, kernel
+// affine_argmax_qmv_fast_u4_gs64_f32) and the dequantisation rule code * scale + bias
+// (src/quantization.rs:173-179). HBM-bound on a quarter (u4) or half (u8) of the dense bytes, so
+// the products must cost next to nothing: a code becomes the fp16 SUBNORMAL code * 2^-24 by
+// dropping it into the low bits of a zero half (one byte permute or one shift-and-mask for two
+// codes, exact, nothing to subtract), a warp multiplies 16 vocabulary rows x 64 columns (one
+// quantisation group, so one scale per row) with the activation rows on the tensor cores
+// (m16n8k16, fp16 x fp16 -> f32, x as hi + lo halves), and the group's scale and bias are applied
+// to the group sums in f32:  logit = sum_g scale_g * (codes_g . x_g) + bias_g * sum(x_g).
+// A lane holds 16 consecutive columns of a group for rows g and g+8; as a dot product does not care
+// about the order of k, the lane's codes serve as its k-slots in the order the unpacking yields
+// them and the activation is laid out in shared memory in that same order.
+__device__ __forceinline__ void mma_f16_lm(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                           uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// 64-column blocks in flight per lane (independent accumulators): 16 bytes of codes per row and block at 8 bits, 8 at 4
+template <int BITS> struct LmqGroups { static constexpr int N = BITS == 8 ? 6 : 8; };
+constexpr float LMQ_UNIT_INV = 16777216.0f;   // 2^24: a code enters as code * 2^-24
+
+// column that sits at position p of a lane's 16 slots (u4: the unpacking yields (c0,c4),(c1,c5),(c2,c6),(c3,c7)
+// per 8-column word; u8: (c0,c1),(c2,c3) per 4-column word = natural order)
+template <int BITS>
+__device__ __forceinline__ int lmq_slot_column(int p) {
+  if (BITS == 8) return p;
+  const int word = p >> 3, q = p & 7;
+  return word * 8 + (q >> 1) + (q & 1) * 4;
+}
+
+__host__ __device__ inline int lmq_x_stride_bytes(int hidden) { return hidden * 2 + 64; }
+
+template <int BITS>
+__global__ void __launch_bounds__(LM_THREADS, 2) lm_head_argmax_affine_kernel(LmHeadAffineArgs a) {
+  extern __shared__ __align__(16) unsigned char lm_smem[];
+  __shared__ unsigned long long best_s[LM_WARPS][8];
+  __shared__ unsigned int last_s;
+  __shared__ float red_s[LM_WARPS];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  if (a.pdl_trigger) lm_pdl_trigger();
+  if (a.pdl_wait) lm_pdl_wait();
+  const int stride = lmq_x_stride_bytes(a.hidden);
+  const int blocks64 = a.hidden / 64;               // 64-column blocks of a row
+  const int groups = a.hidden / a.w.group_size;     // quantisation groups of a row
+  const int per_group = a.w.group_size / 64;        // blocks per group (1 or 2)
+  unsigned char* xhi = lm_smem;
+  unsigned char* xlo = lm_smem + size_t(a.n_rows) * stride;
+  float* xsum = reinterpret_cast<float*>(lm_smem + size_t(2) * a.n_rows * stride);   // [n_rows][blocks64]
+  // The activation is scaled by a power of two that puts its largest value in the middle of the
+  // fp16 range (the same in every block: it depends on x only).
+  float big = 0.0f;
+  for (int i = tid; i < a.n_rows * a.hidden; i += LM_THREADS) big = fmaxf(big, fabsf(a.x[i]));
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, off));
+  if (lane == 0) red_s[warp] = big;
+  __syncthreads();
+  big = red_s[0];
+  for (int w = 1; w < LM_WARPS; ++w) big = fmaxf(big, red_s[w]);
+  int e = static_cast<int>((__float_as_uint(big) >> 23) & 0xffu) - 127;
+  e = max(-100, min(100, e));
+  const float xscale = exp2f(static_cast<float>(8 - e)), inv_xscale = exp2f(static_cast<float>(e - 8)) * LMQ_UNIT_INV;
+  // x -> fp16 hi + lo in the slot order of the lanes; per 64-column block the sum of what the tensor core sees
+  for (int i = tid; i < a.n_rows * a.hidden; i += LM_THREADS) {
+    const int r = i / a.hidden, p = i - r * a.hidden;
+    const int col = (p & ~15) + lmq_slot_column<BITS>(p & 15);
+    const float v = a.x[size_t(r) * a.hidden + col] * xscale;
+    const __half h = __float2half_rn(v);
+    const __half l = __float2half_rn(v - __half2float(h));
+    reinterpret_cast<__half*>(xhi + size_t(r) * stride)[p] = h;
+    reinterpret_cast<__half*>(xlo + size_t(r) * stride)[p] = l;
+  }
+  __syncthreads();
+  for (int i = tid; i < a.n_rows * blocks64; i += LM_THREADS) {
+    const int r = i / blocks64, b = i - r * blocks64;
+    const __half* ph = reinterpret_cast<const __half*>(xhi + size_t(r) * stride) + b * 64;
+    const __half* pl = reinterpret_cast<const __half*>(xlo + size_t(r) * stride) + b * 64;
+    float sum = 0.0f;
+    for (int c = 0; c < 64; ++c) sum += __half2float(ph[c]) + __half2float(pl[c]);
+    xsum[i] = sum * (1.0f / LMQ_UNIT_INV);   // in the unit of the code products (a code enters as code * 2^-24)
+  }
+  __syncthreads();
+  // Up to four activation rows: column 2r of the product is the hi half of row r, column 2r+1 its lo
+  // half, so ONE product per k-step serves both (lane t's two C columns then belong to row t). Five
+  // to eight rows: column g is row g and hi and lo take a product each.
+  const bool paired = a.n_rows <= 4;
+  const int act = paired ? g >> 1 : g;                 // activation row this lane's B column belongs to
+  const bool has_col = act < a.n_rows;
+  const unsigned char* bh = (paired && (g & 1) ? xlo : xhi) + (has_col ? act : 0) * stride + t * 32;
+  const unsigned char* bl = xlo + (has_col ? act : 0) * stride + t * 32;
+  // activation rows of this lane's two C columns
+  const int c_row0 = paired ? t : 2 * t, c_row1 = paired ? t : 2 * t + 1;
+  const float* xs0 = xsum + (c_row0 < a.n_rows ? c_row0 : 0) * blocks64;
+  const float* xs1 = xsum + (c_row1 < a.n_rows ? c_row1 : 0) * blocks64;
+  constexpr int ROW_WORDS_PER_BLOCK = 64 * BITS / 32;   // u32 words of a row per 64-column block
+  constexpr int LANE_WORDS = 16 * BITS / 32;            // words a lane holds per row per block (2 or 4)
+  const int64_t row_words = int64_t(a.hidden) * BITS / 32;
+  constexpr int LMQ_GROUPS = LmqGroups<BITS>::N;
+  unsigned long long best0 = 0, best1 = 0;
+  const int64_t tiles = (a.vocab + 15) / 16;
+  for (int64_t tile = int64_t(blockIdx.x) * LM_WARPS + warp; tile < tiles; tile += int64_t(gridDim.x) * LM_WARPS) {
+    const int64_t r0 = tile * 16 + g, r1 = r0 + 8;
+    const int64_t rr0 = r0 < a.vocab ? r0 : a.vocab - 1, rr1 = r1 < a.vocab ? r1 : a.vocab - 1;
+    const uint32_t* w0 = a.w.packed + rr0 * row_words + t * LANE_WORDS;
+    const uint32_t* w1 = a.w.packed + rr1 * row_words + t * LANE_WORDS;
+    const uint16_t* s0 = a.w.scales + rr0 * groups;
+    const uint16_t* s1 = a.w.scales + rr1 * groups;
+    const uint16_t* z0 = a.w.biases + rr0 * groups;
+    const uint16_t* z1 = a.w.biases + rr1 * groups;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};   // (r0, act 2t), (r0, act 2t+1), (r1, act 2t), (r1, act 2t+1)
+    for (int b0 = 0; b0 < blocks64; b0 += LMQ_GROUPS) {
+      uint32_t A0[LMQ_GROUPS][LANE_WORDS], A1[LMQ_GROUPS][LANE_WORDS];
+#pragma unroll
+      for (int u = 0; u < LMQ_GROUPS; ++u) {
+        const bool valid = b0 + u < blocks64;
+        if (LANE_WORDS == 4) {
+          const uint4 p0 = valid ? __ldcs(reinterpret_cast<const uint4*>(w0 + (b0 + u) * ROW_WORDS_PER_BLOCK)) : make_uint4(0, 0, 0, 0);
+          const uint4 p1 = valid ? __ldcs(reinterpret_cast<const uint4*>(w1 + (b0 + u) * ROW_WORDS_PER_BLOCK)) : make_uint4(0, 0, 0, 0);
+          A0[u][0] = p0.x, A0[u][1] = p0.y, A0[u][2 % LANE_WORDS] = p0.z, A0[u][3 % LANE_WORDS] = p0.w;
+          A1[u][0] = p1.x, A1[u][1] = p1.y, A1[u][2 % LANE_WORDS] = p1.z, A1[u][3 % LANE_WORDS] = p1.w;
+        } else {
+          const uint2 p0 = valid ? __ldcs(reinterpret_cast<const uint2*>(w0 + (b0 + u) * ROW_WORDS_PER_BLOCK)) : make_uint2(0, 0);
+          const uint2 p1 = valid ? __ldcs(reinterpret_cast<const uint2*>(w1 + (b0 + u) * ROW_WORDS_PER_BLOCK)) : make_uint2(0, 0);
+          A0[u][0] = p0.x, A0[u][1] = p0.y;
+          A1[u][0] = p1.x, A1[u][1] = p1.y;
+        }
+      }
+      // the blocks' scales and biases, asked for with the codes (each is read once: a DRAM round trip)
+      uint16_t sr0[LMQ_GROUPS], sr1[LMQ_GROUPS], zr0[LMQ_GROUPS], zr1[LMQ_GROUPS];
+#pragma unroll
+      for (int u = 0; u < LMQ_GROUPS; ++u) {
+        const int grp = min(b0 + u, blocks64 - 1) / per_group;
+        sr0[u] = s0[grp], sr1[u] = s1[grp], zr0[u] = z0[grp], zr1[u] = z1[grp];
+      }
+#pragma unroll
+      for (int u = 0; u < LMQ_GROUPS; ++u) {
+        if (b0 + u >= blocks64) break;   // uniform over the warp
+        const int blk = b0 + u;
+        uint4 xh[2], xl[2];
+        xh[0] = xh[1] = xl[0] = xl[1] = make_uint4(0, 0, 0, 0);
+        if (has_col) {
+          xh[0] = *reinterpret_cast<const uint4*>(bh + blk * 128);
+          xh[1] = *reinterpret_cast<const uint4*>(bh + blk * 128 + 16);
+          if (!paired) {
+            xl[0] = *reinterpret_cast<const uint4*>(bl + blk * 128);
+            xl[1] = *reinterpret_cast<const uint4*>(bl + blk * 128 + 16);
+          }
+        }
+        const uint32_t bhr[8] = {xh[0].x, xh[0].y, xh[0].z, xh[0].w, xh[1].x, xh[1].y, xh[1].z, xh[1].w};
+        const uint32_t blr[8] = {xl[0].x, xl[0].y, xl[0].z, xl[0].w, xl[1].x, xl[1].y, xl[1].z, xl[1].w};
+        float ch[4] = {0.f, 0.f, 0.f, 0.f}, cl[4] = {0.f, 0.f, 0.f, 0.f};
+        // four k-steps: slots [4j, 4j+4) of the lane, i.e. B registers 2j and 2j+1
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t a0, a1, a2, a3;
+          if (BITS == 8) {
+            a0 = __byte_perm(A0[u][j % LANE_WORDS], 0, 0x4140), a2 = __byte_perm(A0[u][j % LANE_WORDS], 0, 0x4342);
+            a1 = __byte_perm(A1[u][j % LANE_WORDS], 0, 0x4140), a3 = __byte_perm(A1[u][j % LANE_WORDS], 0, 0x4342);
+          } else {
+            const uint32_t p0 = A0[u][(j >> 1) % LANE_WORDS] >> ((j & 1) * 8), p1 = A1[u][(j >> 1) % LANE_WORDS] >> ((j & 1) * 8);
+            a0 = p0 & 0x000f000fu, a2 = (p0 >> 4) & 0x000f000fu;
+            a1 = p1 & 0x000f000fu, a3 = (p1 >> 4) & 0x000f000fu;
+          }
+          mma_f16_lm(ch, a0, a1, a2, a3, bhr[2 * j], bhr[2 * j + 1]);
+          if (!paired) mma_f16_lm(cl, a0, a1, a2, a3, blr[2 * j], blr[2 * j + 1]);
+        }
+        const float sc0 = __uint_as_float(uint32_t(sr0[u]) << 16), sc1 = __uint_as_float(uint32_t(sr1[u]) << 16);
+        const float bi0 = __uint_as_float(uint32_t(zr0[u]) << 16), bi1 = __uint_as_float(uint32_t(zr1[u]) << 16);
+        const float x0 = xs0[blk], x1 = xs1[blk];
+        if (paired) {   // the two columns are hi and lo of one activation row
+          v[0] += sc0 * (ch[0] + ch[1]) + bi0 * x0;
+          v[2] += sc1 * (ch[2] + ch[3]) + bi1 * x0;
+        } else {
+          v[0] += sc0 * (ch[0] + cl[0]) + bi0 * x0;
+          v[1] += sc0 * (ch[1] + cl[1]) + bi0 * x1;
+          v[2] += sc1 * (ch[2] + cl[2]) + bi1 * x0;
+          v[3] += sc1 * (ch[3] + cl[3]) + bi1 * x1;
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] *= inv_xscale;   // out of the code unit and the activation's power of two
+    if (r0 < a.vocab) {
+      const unsigned long long k0 = pack_key(v[0], r0), k1 = pack_key(v[1], r0);
+      best0 = k0 > best0 ? k0 : best0;
+      best1 = k1 > best1 ? k1 : best1;
+    }
+    if (r1 < a.vocab) {
+      const unsigned long long k0 = pack_key(v[2], r1), k1 = pack_key(v[3], r1);
+      best0 = k0 > best0 ? k0 : best0;
+      best1 = k1 > best1 ? k1 : best1;
+    }
+  }
+#pragma unroll
+  for (int off = 4; off < 32; off <<= 1) {
+    const unsigned long long o0 = __shfl_xor_sync(0xffffffffu, best0, off), o1 = __shfl_xor_sync(0xffffffffu, best1, off);
+    best0 = o0 > best0 ? o0 : best0;
+    best1 = o1 > best1 ? o1 : best1;
+  }
+  if (lane < 4) {
+    // paired: lane t's best0 is activation row t; else best0 / best1 are rows 2t / 2t+1
+    if (paired) {
+      best_s[warp][lane] = best0;
+    } else {
+      best_s[warp][2 * lane] = best0;
+      best_s[warp][2 * lane + 1] = best1;
+    }
+  }
+  __syncthreads();
+  if (tid < a.n_rows) {
+    unsigned long long b = best_s[0][tid];
+    for (int w = 1; w < LM_WARPS; ++w) b = best_s[w][tid] > b ? best_s[w][tid] : b;
+    atomicMax(a.keys + tid, b);
+    __threadfence();
+  }
+  __syncthreads();
+  if (tid == 0) last_s = atomicAdd(a.counter, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (last_s && tid < a.n_rows) {
+    __threadfence();
+    const unsigned long long win = atomicExch(a.keys + tid, 0ull);
+    a.index_out[tid] = static_cast<int32_t>(0xffffffffu - uint32_t(win & 0xffffffffu)) + a.index_offset;
+    if (a.value_out) a.value_out[tid] = unordered_bits(uint32_t(win >> 32));
+    if (tid == 0) *a.counter = 0;
+  }
+}
+
+size_t lm_head_affine_smem_bytes(int n_rows, int hidden, int group_size) {
+  (void)group_size;
+  return size_t(2) * n_rows * lmq_x_stride_bytes(hidden) + size_t(n_rows) * (hidden / 64) * sizeof(float);
+}
+
+cudaError_t launch_lm_head_argmax_affine(const LmHeadAffineArgs& a, int sm_count, cudaStream_t stream) {
+  const size_t smem = lm_head_affine_smem_bytes(a.n_rows, a.hidden, a.w.group_size);
+  int per_sm = static_cast<int>((200 * 1024) / (smem + 1024));
+  per_sm = per_sm > 2 ? 2 : per_sm < 1 ? 1 : per_sm;
+  int blocks = sm_count * per_sm;
+  const int64_t tiles = (a.vocab + 15) / 16;
+  if (int64_t(blocks) * LM_WARPS > tiles) blocks = static_cast<int>((tiles + LM_WARPS - 1) / LM_WARPS);
+  auto kernel = a.w.bits == 8 ? lm_head_argmax_affine_kernel<8> : lm_head_argmax_affine_kernel<4>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return e;
+  }
+  ChainLaunch l(dim3(blocks), dim3(LM_THREADS), smem, stream, a.pdl_wait != 0);
+  return cudaLaunchKernelEx(&l.cfg, kernel, a);
+}
+
+// Row `*index` of an affine-quantised table, dequantised (code * scale + bias), times `scale`
+// (the quantised form of encode_embedding_from_index_buffers_scaled,
+// src/metal_backend/matmul_encode.rs:424-557).
+__global__ void embed_gather_affine_kernel(AffineWeight w, const int32_t* index, int64_t vocab, int hidden, float scale,
+                                           int recast_bf16, float* out, int pdl_trigger, int pdl_wait) {
+  if (pdl_trigger) lm_pdl_trigger();
+  if (pdl_wait) lm_pdl_wait();
+  const int64_t token = *index;
+  if (token < 0 || token >= vocab) return;
+  const int64_t row_words = int64_t(hidden) * w.bits / 32;
+  const int groups = hidden / w.group_size;
+  const uint32_t mask = (1u << w.bits) - 1u;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < hidden; i += gridDim.x * blockDim.x) {
+    const int bit = i * w.bits;
+    const uint32_t code = (w.packed[token * row_words + bit / 32] >> (bit % 32)) & mask;   // 4 and 8 divide 32
+    const int grp = i / w.group_size;
+    const float sc = __uint_as_float(uint32_t(w.scales[token * groups + grp]) << 16);
+    const float bi = __uint_as_float(uint32_t(w.biases[token * groups + grp]) << 16);
+    const float v = __fmul_rn(__fadd_rn(__fmul_rn(static_cast<float>(code), sc), bi), scale);
+    out[i] = recast_bf16 ? __bfloat162float(__float2bfloat16_rn(v)) : v;
+  }
+}
+
+cudaError_t launch_embed_gather_affine(const AffineWeight& table, const int32_t* index, int64_t vocab, int hidden,
+                                       float scale, int recast_bf16, float* out, int pdl_trigger, int pdl_wait,
+                                       cudaStream_t stream) {
+  const int blocks = (hidden + 255) / 256 < 64 ? (hidden + 255) / 256 : 64;
+  ChainLaunch l(dim3(blocks), dim3(256), 0, stream, pdl_wait != 0);
+  return cudaLaunchKernelEx(&l.cfg, embed_gather_affine_kernel, table, index, vocab, hidden, scale, recast_bf16, out,
+                            pdl_trigger, pdl_wait);
+}
+
 size_t lm_head_smem_bytes(int w_bf16, int n_rows, int hidden) {
   if (w_bf16) return size_t(2) * n_rows * lm_x_stride_bytes(hidden);
   const int R = n_rows <= 1 ? 1 : n_rows <= 2 ? 2 : n_rows <= 4 ? 4 : 8;

@@ -145,6 +145,52 @@ class BlockAwarePrefixCache:
         return self._dump(1)
 
 
+class DecoderPrefixCache:
+    """The decoder-internal prefix cache (src/decoder/generation.rs:2998-3139): whole prompts, most
+    recent first, capacity RETI_RUST_PREFIX_CACHE_CAP (4 by default)."""
+
+    def __init__(self, pool=None, capacity=4):
+        self.L = _ffi.lib()
+        self.pool = pool
+        h = C.c_void_p()
+        check(self.L.sgk_dprefix_create(pool.h if pool is not None else None, capacity, C.byref(h)))
+        self.h = h
+        if pool is not None and pool.state is not None:
+            pool.state._adopt(self)
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.L.sgk_dprefix_destroy(self.h)
+            self.h = None
+
+    def get(self, prompt, seq=None, linear_state=None, stream=None) -> int:
+        """prefix_cache_get up to the suffix: rows of the longest cached prefix become seq's; returns
+        their number (0: miss)."""
+        t = _tokens(prompt)
+        n = C.c_int64()
+        check(self.L.sgk_dprefix_get(self.h, t.ctypes.data, t.size, seq.h if seq is not None else None,
+                                     linear_state.h if linear_state is not None else None, stream, C.byref(n)))
+        return n.value
+
+    def put(self, prompt, seq=None, linear_state=None, stream=None):
+        t = _tokens(prompt)
+        check(self.L.sgk_dprefix_put(self.h, t.ctypes.data, t.size, seq.h if seq is not None else None,
+                                     linear_state.h if linear_state is not None else None, stream))
+
+    def __len__(self):
+        return self.L.sgk_dprefix_len(self.h)
+
+    def entries(self):
+        """Token lists, most recent first."""
+        out = []
+        for i in range(len(self)):
+            n = self.L.sgk_dprefix_entry_tokens(self.h, i, None, 0)
+            buf = np.zeros(max(n, 1), np.uint64)
+            self.L.sgk_dprefix_entry_tokens(self.h, i, buf.ctypes.data, n)
+            out.append([int(x) for x in buf[:n]])
+        return out
+
+
 def longest_prefix_entry_index(entries, prompt):
     """src/decoder/generation.rs:190-204."""
     flat = _tokens([t for e in entries for t in e])

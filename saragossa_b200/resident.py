@@ -56,11 +56,18 @@ def encode_gated_delta_step_batch(states, layer, shape, d_q, d_k, d_v, d_g, d_be
                                                                  d_k.ptr, d_v.ptr, d_g.ptr, d_beta.ptr, d_out.ptr))
 
 
+class AffineWeight(C.Structure):
+    """sgk_affine_weight: device pointers of an affine-quantised [rows][cols] weight."""
+    _fields_ = [("d_packed", C.c_void_p), ("d_scales", C.c_void_p), ("d_biases", C.c_void_p), ("bits", C.c_int32),
+                ("group_size", C.c_int32)]
+
+
 class TokenIO(C.Structure):
     """sgk_token_io: what the whole-token graph reads and writes around the layers."""
     _fields_ = [("d_table", C.c_void_p), ("table_dtype", C.c_int32), ("vocab", C.c_int64), ("hidden", C.c_int32),
                 ("embedding_scale", C.c_float), ("recast_bf16", C.c_int32), ("d_x", C.c_void_p),
-                ("d_lm_weight", C.c_void_p), ("lm_weight_dtype", C.c_int32), ("d_final", C.c_void_p)]
+                ("d_lm_weight", C.c_void_p), ("lm_weight_dtype", C.c_int32), ("d_final", C.c_void_p),
+                ("table_affine", C.c_void_p), ("lm_affine", C.c_void_p)]
 
 
 class LinearShape(C.Structure):
@@ -290,6 +297,28 @@ class DecodeResidentState:
         check(self.L.sgk_lm_head_enqueue_argmax(self.h, stream, d_weight.ptr, weight_dtype, vocab, hidden, d_x.ptr,
                                                 n_rows, index_offset, d_index_out.ptr,
                                                 d_value_out.ptr if d_value_out is not None else None))
+
+    def upload_affine(self, packed, scales_bf16, biases_bf16, bits, group_size):
+        """Uploads an affine-quantised weight (u32 codes, bf16 scale / bias bits) and returns its descriptor;
+        the descriptor keeps the device buffers alive."""
+        bufs = (self.upload(np.ascontiguousarray(packed, np.uint32)), self.upload(np.ascontiguousarray(scales_bf16, np.uint16)),
+                self.upload(np.ascontiguousarray(biases_bf16, np.uint16)))
+        w = AffineWeight(bufs[0].ptr, bufs[1].ptr, bufs[2].ptr, bits, group_size)
+        w._keep = bufs
+        return w
+
+    def encode_lm_head_argmax_affine(self, weight, vocab, hidden, d_x, d_index_out, n_rows=1, index_offset=0,
+                                     d_value_out=None, stream=None):
+        """encode_affine_argmax_qmv_fast (src/metal_backend/lm_head.rs:934-990): argmax over an affine-quantised weight."""
+        check(self.L.sgk_lm_head_enqueue_argmax_affine(self.h, stream, C.byref(weight), vocab, hidden, d_x.ptr, n_rows,
+                                                       index_offset, d_index_out.ptr,
+                                                       d_value_out.ptr if d_value_out is not None else None))
+
+    def encode_embedding_from_index_affine(self, table, vocab, hidden, d_index, d_out, embedding_scale=1.0,
+                                           recast_bf16=False, stream=None):
+        index = d_index.ptr if hasattr(d_index, "ptr") else d_index
+        check(self.L.sgk_embed_enqueue_from_index_affine(self.h, stream, C.byref(table), vocab, hidden, index,
+                                                         embedding_scale, int(recast_bf16), d_out.ptr))
 
     def encode_embedding_from_index(self, d_table, table_dtype, vocab, hidden, d_index, d_out, embedding_scale=1.0,
                                     recast_bf16=False, stream=None):
@@ -683,12 +712,15 @@ class Step:
 
     def token_capture(self, window, d_table, table_dtype, vocab, hidden, d_x, d_lm_weight, lm_weight_dtype, d_final,
                       d_k, d_v, d_q, d_out, sliding_windows=None, attn_scalar=0.0, embedding_scale=1.0,
-                      recast_bf16=False):
+                      recast_bf16=False, table_affine=None, lm_affine=None):
         """The whole token as ONE graph per ring slot: embedding lookup by the previous token's index,
         every layer, greedy epilogue into the window (sgk_token_capture)."""
         keep, p = self._windows(sliding_windows)
-        io = TokenIO(d_table.ptr, table_dtype, vocab, hidden, embedding_scale, 1 if recast_bf16 else 0, d_x.ptr,
-                     d_lm_weight.ptr, lm_weight_dtype, d_final.ptr)
+        io = TokenIO(d_table.ptr if d_table is not None else None, table_dtype, vocab, hidden, embedding_scale,
+                     1 if recast_bf16 else 0, d_x.ptr, d_lm_weight.ptr if d_lm_weight is not None else None,
+                     lm_weight_dtype, d_final.ptr,
+                     C.addressof(table_affine) if table_affine is not None else None,
+                     C.addressof(lm_affine) if lm_affine is not None else None)
         check(self.L.sgk_token_capture(self.h, window.h, C.byref(io), d_k.ptr, d_v.ptr, d_q.ptr, d_out.ptr, p,
                                        attn_scalar))
 

@@ -283,3 +283,55 @@ def test_failed_restore_leaves_the_sequence_as_it_was():
     cache.close()
     assert pool.free_pages == 12
     pool.close()
+
+
+def test_decoder_prefix_cache_matches_the_oracle_and_shares_pages():
+    """The decoder-internal prefix cache (src/decoder/generation.rs:2998-3139) on a bookkeeping pool:
+    hits, order and capacity follow the restated reference logic on a random trace; an entry holds its
+    prompt's pages by reference and a restored sequence shares them."""
+    rng = random.Random(5)
+    ours = sg.DecoderPrefixCache(None, capacity=4)
+    ref = sgo.DecoderPrefixCache(4)
+    base = [[rng.randrange(0, 4) for _ in range(rng.randrange(1, 9))] for _ in range(6)]
+    for _ in range(400):
+        prompt = list(rng.choice(base)) + [rng.randrange(0, 4) for _ in range(rng.randrange(0, 4))]
+        got = ours.get(prompt)
+        if 0 < got < len(prompt):
+            ours.put(prompt)                     # the caller's half of prefix_cache_get (:3019-3022)
+        if got == 0 and rng.random() < 0.7:
+            ours.put(prompt)                     # a cold prefill ends with a put
+            want = ref.get(prompt)
+            ref.put(prompt)
+        else:
+            want = ref.get(prompt)
+        assert got == want
+        assert ours.entries() == ref.entries
+    assert len(ours) == 4
+    zero = sg.DecoderPrefixCache(None, capacity=0)
+    zero.put([1, 2, 3])
+    assert len(zero) == 0 and zero.get([1, 2, 3]) == 0
+    ours.close()
+    zero.close()
+    # pages: an entry pins ceil(n / 16) pages of its sequence; a hit shares them with the new sequence
+    pool = sg.PagePool(None, layers=1, kv_heads=1, head_dim=64, dtype=sg.KV_BF16, num_pages=16, max_seqs=4,
+                       max_seq_tokens=128)
+    cache = sg.DecoderPrefixCache(pool, capacity=2)
+    a = pool.sequence(128)
+    a.reserve(40)
+    a.layer(0, 1).truncate(40)
+    prompt = list(range(40))
+    cache.put(prompt, a)
+    table = list(a.block_table())
+    assert [pool.refcount(p) for p in table[:3]] == [2, 2, 2]
+    b = pool.sequence(128)
+    assert cache.get(prompt + [7, 8], b) == 40
+    assert list(b.block_table()) == table[:3] and b.layer(0, 1).len() == 40
+    assert [pool.refcount(p) for p in table[:3]] == [3, 3, 3]
+    with pytest.raises(sg.InferError):
+        cache.put(list(range(50)), a)            # the sequence holds 40 rows only
+    a.close()
+    b.close()
+    assert pool.free_pages == 13                  # the entry alone still pins its three pages
+    cache.close()
+    assert pool.free_pages == 16
+    pool.close()

@@ -366,3 +366,84 @@ def test_whole_token_is_one_graph_submission(gpu_state, depth):
     for a, b in zip(outs[0][1], outs[1][1]):
         assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
     assert gpu_state.device_status() == 0
+
+
+def _affine_weight(vocab, hidden, bits, group, seed):
+    rng = np.random.default_rng(seed)
+    codes = rng.integers(0, 1 << bits, size=(vocab, hidden), dtype=np.uint32)
+    groups = hidden // group
+    scales = _bf16_bits((rng.uniform(0.5, 1.5, size=(vocab, groups)) * (0.02 / (1 << bits))).astype(np.float32))
+    biases = _bf16_bits((rng.normal(0, 0.01, size=(vocab, groups))).astype(np.float32))
+    return sgo.affine_pack(codes, bits), scales, biases
+
+
+def test_oracle_affine_dequantize_known_answers():
+    """The unpacking order of src/quantization.rs:208-228 (LSB first) and value = code * scale + bias."""
+    packed = np.array([[0x76543210, 0xFEDCBA98]], np.uint32)                   # 16 four-bit codes 0..15
+    one, two = _bf16_bits(np.array([1.0], np.float32)), _bf16_bits(np.array([2.0], np.float32))
+    w = sgo.affine_dequantize(packed, np.repeat(two, 1), np.repeat(one, 1), 4, 16, 1, 16)
+    assert np.array_equal(w[0], 2.0 * np.arange(16, dtype=np.float32) + 1.0)
+    packed8 = np.array([[0x04030201, 0xFF070605]], np.uint32)
+    w8 = sgo.affine_dequantize(packed8, np.repeat(one, 1), np.repeat(two, 1), 8, 8, 1, 8)
+    assert np.array_equal(w8[0], np.array([1, 2, 3, 4, 5, 6, 7, 255], np.float32) + 2.0)
+    codes = np.arange(64, dtype=np.uint32).reshape(2, 32) % 16
+    assert np.array_equal(sgo.affine_dequantize(sgo.affine_pack(codes, 4), np.repeat(one, 2), np.repeat(_bf16_bits(np.zeros(1, np.float32)), 2),
+                                                4, 32, 2, 32), codes.astype(np.float32))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("bits,group", [(4, 64), (8, 64), (4, 128), (8, 128)])
+@pytest.mark.parametrize("rows", [1, 3, 8])
+def test_affine_lm_head_matches_oracle(gpu_state, bits, group, rows):
+    """Greedy epilogue over an affine-quantised weight: the index is the oracle's (argmax over the
+    dequantised weight, first maximum), the winning logit is within 2e-4 of the f64 value, planted
+    maxima are found, and a row's answer does not depend on the rows that share the pass."""
+    vocab, hidden = 5003, 1280
+    packed, scales, biases = _affine_weight(vocab, hidden, bits, group, 70 + bits + group)
+    w = sgo.affine_dequantize(packed, scales, biases, bits, group, vocab, hidden)
+    x = sgo.fill_normal8(rows * hidden, 71, bits).reshape(rows, hidden)
+    # push one vocabulary row per activation row towards the top: x gets that row's deviation from the mean row
+    mean = w.mean(axis=0)
+    for r in range(rows):
+        x[r] += (w[(977 * (r + 1)) % vocab] - mean) * np.float32(400.0)
+    d_w = gpu_state.upload_affine(packed, scales, biases, bits, group)
+    d_x = gpu_state.upload(x)
+    d_idx, d_val = gpu_state.alloc(4 * 8), gpu_state.alloc(4 * 8)
+    gpu_state.encode_lm_head_argmax_affine(d_w, vocab, hidden, d_x, d_idx, n_rows=rows, d_value_out=d_val)
+    gpu_state.sync()
+    idx, val = d_idx.download(np.int32, rows), d_val.download(np.float32, rows)
+    logits = w.astype(np.float64) @ x.astype(np.float64).T
+    for r in range(rows):
+        st, want, _ = sgo.lm_head_argmax(w, x[r])
+        assert st == 0 and int(idx[r]) == want
+        if group == 64:
+            assert want == (977 * (r + 1)) % vocab          # the planted row wins where the groups are fine enough
+        assert abs(float(val[r]) - logits[want, r]) <= 2e-4 * max(1.0, abs(logits[want, r]))
+    # one row alone gives the same bits as the same row among others
+    if rows > 1:
+        gpu_state.encode_lm_head_argmax_affine(d_w, vocab, hidden, d_x, d_idx, n_rows=1, d_value_out=d_val)
+        gpu_state.sync()
+        assert d_idx.download(np.int32, 1)[0] == idx[0]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("bits", [4, 8])
+def test_affine_embedding_lookup_is_the_dequantised_row(gpu_state, bits):
+    vocab, hidden, group = 301, 256, 64
+    packed, scales, biases = _affine_weight(vocab, hidden, bits, group, 90 + bits)
+    w = sgo.affine_dequantize(packed, scales, biases, bits, group, vocab, hidden)
+    d_t = gpu_state.upload_affine(packed, scales, biases, bits, group)
+    d_out = gpu_state.alloc(4 * hidden)
+    for token, scale in ((0, 1.0), (300, 1.5), (123, 0.25)):
+        d_i = gpu_state.upload(np.array([token], np.int32))
+        gpu_state.encode_embedding_from_index_affine(d_t, vocab, hidden, d_i, d_out, embedding_scale=scale)
+        gpu_state.sync()
+        assert np.array_equal(d_out.download(), w[token] * np.float32(scale))
+    d_out.upload(np.full(hidden, 7.0, np.float32))
+    d_i = gpu_state.upload(np.array([vocab], np.int32))                    # outside the table: nothing is written
+    gpu_state.encode_embedding_from_index_affine(d_t, vocab, hidden, d_i, d_out)
+    gpu_state.sync()
+    assert np.array_equal(d_out.download(), np.full(hidden, 7.0, np.float32))
+    with pytest.raises(Exception):
+        bad = gpu_state.upload_affine(packed, scales, biases, 6, group)
+        gpu_state.encode_embedding_from_index_affine(bad, vocab, hidden, d_i, d_out)

@@ -250,3 +250,54 @@ def test_linear_state_config3_shape_and_prefix_entry(state):
     pool.close()
     ls.close()
     bf.close()
+
+
+def test_decoder_prefix_cache_restores_rows_and_never_aliases_them(state):
+    """prefix_cache_get / _put (src/decoder/generation.rs:2998-3139) over pages: a hit gives the new
+    sequence exactly the cached rows; its appends (the suffix of the prompt) copy the shared last
+    page first, so the entry and the sequence that made it keep their rows bit for bit."""
+    layers, q_heads, kv_heads, hd = 2, 4, 2, 64
+    kv_dim = kv_heads * hd
+    pool = state.pool(layers, kv_heads, hd, sg.KV_BF16, num_pages=32, max_seqs=4, max_seq_tokens=128)
+    cache = sg.DecoderPrefixCache(pool, capacity=2)
+    prompt = list(range(35))                      # 2 full pages + 3 rows of a third
+
+    def rows(layer, which, p0, p1):
+        return sgo.fill_normal8((p1 - p0) * kv_dim, 61, 2 * layer + which, p0 * kv_dim).reshape(p1 - p0, kv_dim)
+
+    a = pool.sequence(128)
+    kva = [a.layer(layer, q_heads) for layer in range(layers)]
+    for layer, kv in enumerate(kva):
+        kv.append_batch(rows(layer, 0, 0, 35), rows(layer, 1, 0, 35))
+    cache.put(prompt, a)
+    b = pool.sequence(128)
+    longer = prompt + [100, 101, 102, 103, 104]
+    assert cache.get(longer, b) == 35
+    kvb = [b.layer(layer, q_heads) for layer in range(layers)]
+    for layer, kv in enumerate(kvb):
+        assert kv.len() == 35
+        gk, gv = kv.gather_rows_f32()
+        assert np.array_equal(gk, sgo.bf16_round(rows(layer, 0, 0, 35))) and np.array_equal(gv, sgo.bf16_round(rows(layer, 1, 0, 35)))
+        kv.append_batch(rows(layer, 0, 35, 40), rows(layer, 1, 35, 40))       # the suffix: copies the shared page first
+    cache.put(longer, b)
+    for layer, kv in enumerate(kva):                                           # the first sequence goes on too
+        kv.append_batch(rows(layer, 0, 50, 53), rows(layer, 1, 50, 53))
+    assert list(a.block_table())[:2] == list(b.block_table())[:2]               # full pages stay shared
+    assert a.block_table()[2] != b.block_table()[2]                             # the written one does not
+    c = pool.sequence(128)
+    assert cache.get(prompt, c) == 35                                           # the shorter entry is intact
+    for layer in range(layers):
+        gk, gv = c.layer(layer, q_heads).gather_rows_f32()
+        assert np.array_equal(gk, sgo.bf16_round(rows(layer, 0, 0, 35))) and np.array_equal(gv, sgo.bf16_round(rows(layer, 1, 0, 35)))
+        gk, gv = kvb[layer].gather_rows_f32()
+        assert np.array_equal(gk, sgo.bf16_round(rows(layer, 0, 0, 40)))
+        gk, gv = kva[layer].gather_rows_f32()
+        assert np.array_equal(gk[35:], sgo.bf16_round(rows(layer, 0, 50, 53)))
+    d = pool.sequence(128)
+    assert cache.get(longer + [9], d) == 40 and cache.entries()[0] == longer
+    assert cache.get([77, 1], d) == 0 and d.layer(0, q_heads).len() == 40       # a miss leaves the sequence alone
+    for s_ in (a, b, c, d):
+        s_.close()
+    cache.close()
+    assert pool.free_pages == 32
+    pool.close()
