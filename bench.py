@@ -1254,29 +1254,34 @@ def bulk_append_leg(sg, st, torch, stream):
     out = {}
     for name, dtype, roped, store in (("bf16", sg.KV_BF16, False, 2.0), ("bf16_rope", sg.KV_BF16, True, 2.0),
                                       ("u8", sg.KV_U8G32, False, 1.125)):
-        kv = st.full_attention(rows * (reps + 2), 32, kvh, hd, dtype)
+        # the layers of one prompt chunk: every layer appends the same positions (with rope, the
+        # cos/sin table made for the first layer's launch serves the others)
+        kvs = [st.full_attention(rows * 3, 32, kvh, hd, dtype) for _ in range(reps)]
 
-        def one():
+        def one(kv):
             if roped:
                 kv.encode_rope_append_rows(d_k, d_v, rows, d_w, rope, stream=stream.cuda_stream)
             else:
                 kv.encode_append_rows(d_k, d_v, rows, stream=stream.cuda_stream)
 
-        one()
-        one()
+        for kv in kvs:
+            one(kv)
+        for kv in kvs:
+            one(kv)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         stream.synchronize()
         st.sync()
         e0.record(stream)
-        for _ in range(reps):
-            one()
+        for kv in kvs:
+            one(kv)
         e1.record(stream)
         stream.synchronize()
         t = e0.elapsed_time(e1) * 1e-3 / reps
         nbytes = rows * kv_dim * (4 * 2 + store * 2)
         out[name] = {"us_per_launch": t * 1e6, "hbm_gbs": nbytes / t / 1e9}
-        kv.close()
-    out["shape"] = f"{rows} rows x {kvh} KV heads x hd{hd} per launch, one layer"
+        for kv in kvs:
+            kv.close()
+    out["shape"] = f"{rows} rows x {kvh} KV heads x hd{hd} per launch, {reps} layers of one prompt chunk"
     return out
 
 

@@ -81,6 +81,8 @@ int32_t sgk_state_device_status(sgk_state* state, int32_t* status_out);
  * cooperative launches, which the driver places all at once or not at all, at about 2 us more per
  * launch. Set before the first enqueue; a captured step keeps the mode it was captured in. */
 int32_t sgk_state_set_concurrent_streams(sgk_state* state, int32_t enabled);
+/* Kernels launched so far through this state (a graph replay counts the launches it holds). */
+int64_t sgk_state_launches(const sgk_state* state);
 
 /* Token chain: the launches of ONE decode token, enqueued one after the other on one stream
  * (the reference encodes them into one command buffer, src/decoder/resident/decode.rs:243-253).

@@ -101,6 +101,8 @@ int32_t sgk_state_set_concurrent_streams(sgk_state* st, int32_t enabled) {
   return SGK_OK;
 }
 
+int64_t sgk_state_launches(const sgk_state* st) { return st ? st->launches : 0; }
+
 int32_t sgk_state_chain_begin(sgk_state* st, void* stream) {
   if (!st) return fail(SGK_ERR_BACKEND, "null state");
   if (st->chain_active) return fail(SGK_ERR_CONFIG, "a token chain is open already");
@@ -1116,6 +1118,7 @@ int32_t sgk_lm_head_enqueue_argmax_affine(sgk_state* st, void* stream, const sgk
   a.index_offset = index_offset;
   a.index_out = d_index_out;
   a.value_out = d_value_out;
+  a.status = st->d_status;
   cudaStream_t cs = st->pick(stream);
   const bool member = st->chain_member(cs);
   a.pdl_trigger = member ? 1 : 0;

@@ -56,6 +56,12 @@ struct State {
   // {cos, sin} table of a bulk append with rope (grown on demand; reuse is ordered by the stream)
   float2* d_rope_table = nullptr;
   size_t rope_table_cap = 0;
+  // what the table holds now: the layers of a prompt append the same rows one after the other on
+  // one stream, so the table is made for the first layer and read by the others
+  int64_t rope_table_lo = 0, rope_table_rows = 0;
+  cudaStream_t rope_table_stream = nullptr;
+  RopeArgs rope_table_args{};
+  bool rope_table_in_graph = false;   // a captured graph rewrites the table whenever it runs: never held again
   unsigned long long* d_lm_ws = nullptr;  // lm_head argmax: [0..8) best key per row, [8] blocks-done counter; zero between launches
   int64_t launches = 0;  // kernels launched through this state
   // false (default): the caller never has two launches of this state in flight on different

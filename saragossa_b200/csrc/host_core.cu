@@ -338,6 +338,12 @@ int Batch::choose_kernel() const {
 
 int Batch::choose_splits(int kernel, int64_t max_rows) const {
   int s = splits_override;
+  // tuning flag: a split count for every launch of the process
+  static const int env_splits = [] {
+    const char* e = std::getenv("SGK_SPLITS");
+    return e ? std::atoi(e) : 0;
+  }();
+  if (s <= 0 && env_splits > 0) s = env_splits;
   if (s <= 0) {
     // Blocks per launch = heads * n * s over `slots` resident blocks (two per SM
     // for the tensor-core kernel, eight for the generic one). Take the split count
@@ -418,15 +424,31 @@ int Batch::enqueue_append(cudaStream_t stream, const float* d_k, const float* d_
       if (pairs > 0 && hi - lo <= 65536) {
         if (need > st->rope_table_cap) {
           if (st->d_rope_table) cudaFree(st->d_rope_table);
-          st->d_rope_table = nullptr, st->rope_table_cap = 0;
+          st->d_rope_table = nullptr, st->rope_table_cap = 0, st->rope_table_rows = 0;
           const size_t cap = std::max(need, size_t(4096) * 64);
           SGK_CUDA(cudaMalloc(&st->d_rope_table, cap * sizeof(float2)));
           st->rope_table_cap = cap;
         }
-        SGK_CUDA(launch_rope_table(st->d_rope_table, lo, static_cast<int>(hi - lo), *rope, stream));
-        st->launches += 1;
+        cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+        SGK_CUDA(cudaStreamIsCapturing(stream, &capturing));
+        const RopeArgs& have = st->rope_table_args;
+        const bool held = capturing == cudaStreamCaptureStatusNone && !st->rope_table_in_graph && st->rope_table_rows > 0 &&
+                          st->rope_table_stream == stream && lo >= st->rope_table_lo &&
+                          hi <= st->rope_table_lo + st->rope_table_rows && have.rope_dims == rope->rope_dims &&
+                          have.frequency_dim == rope->frequency_dim && have.theta == rope->theta &&
+                          have.position_scale == rope->position_scale;
+        if (!held) {
+          SGK_CUDA(launch_rope_table(st->d_rope_table, lo, static_cast<int>(hi - lo), *rope, stream));
+          st->launches += 1;
+          // a captured launch fills the table when the graph runs, not now: nothing is held then
+          st->rope_table_rows = capturing == cudaStreamCaptureStatusNone ? hi - lo : 0;
+          st->rope_table_lo = lo;
+          st->rope_table_stream = stream;
+          st->rope_table_args = *rope;
+          if (capturing != cudaStreamCaptureStatusNone) st->rope_table_in_graph = true;
+        }
         a.rope_table = st->d_rope_table;
-        a.rope_row0 = lo;
+        a.rope_row0 = st->rope_table_lo;
       }
     }
     SGK_CUDA(launch_append_rows(a, n(), stream));

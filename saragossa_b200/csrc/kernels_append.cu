@@ -218,9 +218,14 @@ __device__ __forceinline__ uint32_t store_u8_row(uint8_t* tile, int hd, int is_v
 __global__ void __launch_bounds__(128) append_tiles_kernel(AppendArgs a) {
   extern __shared__ float smem[];
   const int hd = a.pool.head_dim;
-  float* ks = smem;                           // [16][hd]
-  float* vs = smem + PAGE_TOKENS * hd;        // [16][hd]
-  float* inv_s = vs + PAGE_TOKENS * hd;       // [16] 1/rms per row
+  // staged path only: K rows [16][hd + 4], 1/rms per row [16], rope denominators [128], and for
+  // u8 pools the V rows [16][hd] and a tile pair being put together
+  const int kstride = hd + 4;
+  float* ks = smem;
+  float* inv_s = ks + PAGE_TOKENS * kstride;
+  float* denom_s = inv_s + PAGE_TOKENS;
+  float* vs = denom_s + 128;
+  uint8_t* stage = reinterpret_cast<uint8_t*>(vs + PAGE_TOKENS * hd);
   __shared__ uint32_t big_s;
   const int head = blockIdx.x, tile_i = blockIdx.y, seq = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -286,42 +291,96 @@ __global__ void __launch_bounds__(128) append_tiles_kernel(AppendArgs a) {
       atomicExch(a.status, DEV_ERR_BAD_PAGE);
     }
   } else if (rows > 0) {
+    // K is worked on in shared memory; V only when it is quantised. K rows sit kstride floats
+    // apart: with the rows a whole number of 128-byte lines apart, the sixteen threads that
+    // walk one row each for the sequential sums hit one bank sixteen times per step, which made
+    // a launch of 2056 tiles shared-memory bound (47.9 us against 15.3 us without rope).
     const int rin0 = static_cast<int>(row_lo % PAGE_TOKENS);
-    const int vec_per_row = hd / 4;
+    const bool stage_v = a.pool.dtype == KV_U8G32;
+    const int chunks = hd / 8, total = rows * chunks;
     const float* kbase = a.k + (int64_t(seq) * a.n_rows + (row_lo - len0)) * kv_dim + head * hd;
     const float* vbase = a.v + (int64_t(seq) * a.n_rows + (row_lo - len0)) * kv_dim + head * hd;
-    for (int i = tid; i < rows * vec_per_row; i += blockDim.x) {
-      const int r = i / vec_per_row, c = i % vec_per_row;
-      reinterpret_cast<float4*>(ks + r * hd)[c] = __ldg(reinterpret_cast<const float4*>(kbase + int64_t(r) * kv_dim) + c);
-      reinterpret_cast<float4*>(vs + r * hd)[c] = __ldg(reinterpret_cast<const float4*>(vbase + int64_t(r) * kv_dim) + c);
+    int32_t page = -1;
+    if (page_index < a.pool.table_stride) page = a.pool.tables[int64_t(slot) * a.pool.table_stride + page_index];
+    const bool page_ok = page >= 0 && page < a.num_pages;
+    uint8_t* ktile = page_ok ? a.pool.base + tile_offset(a.pool, page, a.layer, head, 0) : nullptr;
+    uint8_t* vtile = page_ok ? a.pool.base + tile_offset(a.pool, page, a.layer, head, 1) : nullptr;
+    // two chunks of eight values of K and of V per thread and pass: all loads of a pass are
+    // issued before anything waits for one
+    constexpr int U = 2;
+    for (int base = 0; base < total; base += U * blockDim.x) {
+      float4 k0[U], k1[U], v0[U], v1[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int i = base + u * blockDim.x + tid;
+        if (i < total) {
+          const int r = i / chunks, chunk = i % chunks;
+          const float4* ksrc = reinterpret_cast<const float4*>(kbase + int64_t(r) * kv_dim + chunk * 8);
+          const float4* vsrc = reinterpret_cast<const float4*>(vbase + int64_t(r) * kv_dim + chunk * 8);
+          k0[u] = __ldg(ksrc);
+          k1[u] = __ldg(ksrc + 1);
+          v0[u] = __ldg(vsrc);
+          v1[u] = __ldg(vsrc + 1);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int i = base + u * blockDim.x + tid;
+        if (i >= total) continue;
+        const int r = i / chunks, chunk = i % chunks;
+        float4* kd = reinterpret_cast<float4*>(ks + r * kstride + chunk * 8);
+        kd[0] = k0[u];
+        kd[1] = k1[u];
+        if (stage_v) {
+          float4* vd = reinterpret_cast<float4*>(vs + r * hd + chunk * 8);
+          vd[0] = v0[u];
+          vd[1] = v1[u];
+        } else if (page_ok) {
+          if (a.pool.dtype == KV_F32) {
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(vtile) + (rin0 + r) * hd + chunk * 8);
+            dst[0] = v0[u];
+            dst[1] = v1[u];
+          } else {
+            const uint4 w = make_uint4(uint32_t(f32_to_bf16_bits(v0[u].x)) | (uint32_t(f32_to_bf16_bits(v0[u].y)) << 16),
+                                       uint32_t(f32_to_bf16_bits(v0[u].z)) | (uint32_t(f32_to_bf16_bits(v0[u].w)) << 16),
+                                       uint32_t(f32_to_bf16_bits(v1[u].x)) | (uint32_t(f32_to_bf16_bits(v1[u].y)) << 16),
+                                       uint32_t(f32_to_bf16_bits(v1[u].z)) | (uint32_t(f32_to_bf16_bits(v1[u].w)) << 16));
+            *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(vtile) + bf16_elem_index(rin0 + r, chunk * 8, hd)) = w;
+          }
+        }
+      }
     }
     __syncthreads();
     if (a.has_rope) {
       // same float order as norm_rope_head, one thread per row for the sequential sums
       if (tid < rows) {
-        const float* xs = ks + tid * hd;
+        const float4* xs = reinterpret_cast<const float4*>(ks + tid * kstride);
         float sum = 0.0f;
-        for (int c = 0; c < hd; ++c) sum = __fadd_rn(sum, __fmul_rn(xs[c], xs[c]));
+#pragma unroll 4
+        for (int c = 0; c < hd / 4; ++c) {
+          const float4 x = xs[c];
+          sum = __fadd_rn(sum, __fmul_rn(x.x, x.x));
+          sum = __fadd_rn(sum, __fmul_rn(x.y, x.y));
+          sum = __fadd_rn(sum, __fmul_rn(x.z, x.z));
+          sum = __fadd_rn(sum, __fmul_rn(x.w, x.w));
+        }
         const float mean_square = __fdiv_rn(sum, static_cast<float>(hd));
         inv_s[tid] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean_square, a.rope.eps)));
       }
-      __syncthreads();
-      for (int i = tid; i < rows * hd; i += blockDim.x) {
-        const int r = i / hd, c = i % hd;
-        ks[i] = __fmul_rn(__fmul_rn(ks[i], inv_s[r]), a.knorm_w[c]);
-      }
-      __syncthreads();
       const int pairs = a.rope.rope_dims / 2;
-      // theta^(2i/d) depends on the pair only: once per pair, not once per (row, pair)
-      float* denom_s = vs + PAGE_TOKENS * hd + PAGE_TOKENS;   // [pairs], behind inv_s
-      for (int pair = tid; pair < pairs; pair += blockDim.x) {
-        const float exponent = __fdiv_rn(static_cast<float>(2 * pair), static_cast<float>(a.rope.frequency_dim));
-        denom_s[pair] = static_cast<float>(pow(static_cast<double>(a.rope.theta), static_cast<double>(exponent)));
+      if (a.rope_table == nullptr) {
+        // theta^(2i/d) depends on the pair only: once per pair, not once per (row, pair)
+        for (int pair = tid; pair < pairs; pair += blockDim.x) {
+          const float exponent = __fdiv_rn(static_cast<float>(2 * pair), static_cast<float>(a.rope.frequency_dim));
+          denom_s[pair] = static_cast<float>(pow(static_cast<double>(a.rope.theta), static_cast<double>(exponent)));
+        }
       }
       __syncthreads();
+      // x * inv_rms * w and the rotation of a pair in one pass: a pair's two values are
+      // read, scaled and rotated by the same thread
       for (int i = tid; i < rows * pairs; i += blockDim.x) {
         const int r = i / pairs, pair = i % pairs;
-        float* xs = ks + r * hd;
+        float* xs = ks + r * kstride;
         float c, s;
         if (a.rope_table != nullptr) {
           // made once per launch: cos and sin of (row, pair) depend neither on the head nor on the sequence
@@ -337,47 +396,47 @@ __global__ void __launch_bounds__(128) append_tiles_kernel(AppendArgs a) {
         }
         const int i0 = a.rope.interleaved ? 2 * pair : pair;
         const int i1 = a.rope.interleaved ? 2 * pair + 1 : pair + pairs;
-        const float first = xs[i0], second = xs[i1];
+        const float inv = inv_s[r];
+        const float first = __fmul_rn(__fmul_rn(xs[i0], inv), a.knorm_w[i0]);
+        const float second = __fmul_rn(__fmul_rn(xs[i1], inv), a.knorm_w[i1]);
         xs[i0] = __fsub_rn(__fmul_rn(first, c), __fmul_rn(second, s));
         xs[i1] = __fadd_rn(__fmul_rn(first, s), __fmul_rn(second, c));
+      }
+      // dims the rotation leaves alone are still normalised
+      const int tail = hd - 2 * pairs;
+      for (int i = tid; i < rows * tail; i += blockDim.x) {
+        const int r = i / tail, c = 2 * pairs + i % tail;
+        ks[r * kstride + c] = __fmul_rn(__fmul_rn(ks[r * kstride + c], inv_s[r]), a.knorm_w[c]);
       }
       __syncthreads();
     }
 
-    int32_t page = -1;
-    if (page_index < a.pool.table_stride) page = a.pool.tables[int64_t(slot) * a.pool.table_stride + page_index];
-    if (page >= 0 && page < a.num_pages) {
-      uint8_t* ktile = a.pool.base + tile_offset(a.pool, page, a.layer, head, 0);
-      uint8_t* vtile = a.pool.base + tile_offset(a.pool, page, a.layer, head, 1);
+    if (page_ok) {
       if (a.pool.dtype == KV_F32) {
-        for (int i = tid; i < rows * vec_per_row; i += blockDim.x) {
-          const int r = i / vec_per_row, c = i % vec_per_row;
-          reinterpret_cast<float4*>(reinterpret_cast<float*>(ktile) + (rin0 + r) * hd)[c] = reinterpret_cast<const float4*>(ks + r * hd)[c];
-          reinterpret_cast<float4*>(reinterpret_cast<float*>(vtile) + (rin0 + r) * hd)[c] = reinterpret_cast<const float4*>(vs + r * hd)[c];
+        for (int i = tid; i < rows * (hd / 4); i += blockDim.x) {
+          const int r = i / (hd / 4), c = i % (hd / 4);
+          reinterpret_cast<float4*>(reinterpret_cast<float*>(ktile) + (rin0 + r) * hd)[c] = reinterpret_cast<const float4*>(ks + r * kstride)[c];
         }
       } else if (a.pool.dtype == KV_BF16) {
-        const int chunks = hd / 8;
-        for (int i = tid; i < 2 * rows * chunks; i += blockDim.x) {
-          const int is_v = i / (rows * chunks), rest = i % (rows * chunks);
-          const int r = rest / chunks, chunk = rest % chunks;
-          const float* xs = (is_v ? vs : ks) + r * hd + chunk * 8;
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e)
-            w[e] = static_cast<uint32_t>(f32_to_bf16_bits(xs[2 * e])) | (static_cast<uint32_t>(f32_to_bf16_bits(xs[2 * e + 1])) << 16);
-          uint16_t* dst = reinterpret_cast<uint16_t*>(is_v ? vtile : ktile);
-          *reinterpret_cast<uint4*>(dst + bf16_elem_index(rin0 + r, chunk * 8, hd)) = make_uint4(w[0], w[1], w[2], w[3]);
+        for (int i = tid; i < total; i += blockDim.x) {
+          const int r = i / chunks, chunk = i % chunks;
+          const float4 x0 = reinterpret_cast<const float4*>(ks + r * kstride + chunk * 8)[0];
+          const float4 x1 = reinterpret_cast<const float4*>(ks + r * kstride + chunk * 8)[1];
+          const uint4 w = make_uint4(uint32_t(f32_to_bf16_bits(x0.x)) | (uint32_t(f32_to_bf16_bits(x0.y)) << 16),
+                                     uint32_t(f32_to_bf16_bits(x0.z)) | (uint32_t(f32_to_bf16_bits(x0.w)) << 16),
+                                     uint32_t(f32_to_bf16_bits(x1.x)) | (uint32_t(f32_to_bf16_bits(x1.y)) << 16),
+                                     uint32_t(f32_to_bf16_bits(x1.z)) | (uint32_t(f32_to_bf16_bits(x1.w)) << 16));
+          *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(ktile) + bf16_elem_index(rin0 + r, chunk * 8, hd)) = w;
         }
       } else {
         uint32_t biggest = 0;
         // a full tile is put together in shared memory and leaves with 16-byte stores; a
         // partial one (first or last page of the append) is written in place, byte by byte
         const int tile_b = static_cast<int>(a.pool.tile_bytes);
-        uint8_t* stage = reinterpret_cast<uint8_t*>(vs + PAGE_TOKENS * hd + PAGE_TOKENS + 128);
         const bool full = rows == PAGE_TOKENS;
         for (int task = warp; task < 2 * rows; task += blockDim.x / 32) {
           const int is_v = task / rows, r = task % rows;
-          const float* xs = (is_v ? vs : ks) + r * hd;
+          const float* xs = is_v ? vs + r * hd : ks + r * kstride;
           uint8_t* tile = full ? stage + is_v * tile_b : (is_v ? vtile : ktile);
           if (hd == 256) biggest = max(biggest, store_u8_row<8>(tile, hd, is_v, rin0 + r, xs, lane));
           else if (hd == 128) biggest = max(biggest, store_u8_row<4>(tile, hd, is_v, rin0 + r, xs, lane));
@@ -451,9 +510,10 @@ cudaError_t launch_append_rows(const AppendArgs& a, int n_seq, cudaStream_t stre
   if (a.n_rows >= 4 && a.out_k == nullptr && (hd == 64 || hd == 128 || hd == 256)) {
     // bulk: one block per page tile; the first row may sit anywhere in its page, so one tile more
     dim3 grid(a.pool.kv_heads, (a.n_rows + PAGE_TOKENS - 1) / PAGE_TOKENS + 1, n_seq);
-    // K rows, V rows, 1/rms per row, rope denominators (<= 128 pairs), a u8 tile pair being put together
-    size_t smem = (2 * size_t(PAGE_TOKENS) * hd + PAGE_TOKENS + 128) * sizeof(float);
-    if (a.pool.dtype == KV_U8G32) smem += 2 * size_t(a.pool.tile_bytes);
+    // the kernel's carve-up: K rows, 1/rms per row, rope denominators (<= 128 pairs); V rows and a
+    // tile pair being put together only where V is quantised
+    size_t smem = (size_t(PAGE_TOKENS) * (hd + 4) + PAGE_TOKENS + 128) * sizeof(float);
+    if (a.pool.dtype == KV_U8G32) smem += size_t(PAGE_TOKENS) * hd * sizeof(float) + 2 * size_t(a.pool.tile_bytes);
     append_tiles_kernel<<<grid, 128, smem, stream>>>(a);
     return cudaGetLastError();
   }

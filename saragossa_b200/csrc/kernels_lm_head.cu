@@ -507,19 +507,374 @@ __global__ void __launch_bounds__(LM_THREADS, 2) lm_head_argmax_affine_kernel(Lm
   }
 }
 
+// ---- the same epilogue, software-pipelined (hidden a multiple of 64 * P columns) --------------
+// The kernel above asks for six blocks of codes, works through them and only then asks again; a
+// profile showed about 130 warp instructions per 16 x 64 block (u16 loads of every scale and bias,
+// an integer division per block, 64-bit address arithmetic per load) and the issue slots half
+// busy at 46 % of the DRAM rate: it could not have doubled its speed. Here a pass is P blocks;
+// the codes, scales and biases of pass i+1 are asked for before pass i is multiplied (two register
+// buffers, also across the end of a 16-row tile), a pass's scales and biases arrive as one 4 to
+// 16-byte load per row, addresses advance by increments, and the group of a block is known at
+// compile time. Same products, same order of the f32 additions: bit-identical logits.
+template <int BITS, int P, int PG>
+struct LmqPass {
+  static constexpr int LW = 16 * BITS / 32;       // words of a row a lane holds per block
+  static constexpr int NS = P / PG;               // scales (and biases) of a row per pass
+  static constexpr int MW = NS >= 2 ? NS / 2 : 1; // 32-bit words they come in
+  uint32_t a0[P][LW], a1[P][LW];
+  uint32_t s0[MW], s1[MW], z0[MW], z1[MW];
+};
+
+template <int N>
+__device__ __forceinline__ void lmq_load_words(const void* p, uint32_t (&out)[N]) {
+  if (N == 4) {
+    const uint4 v = __ldcs(reinterpret_cast<const uint4*>(p));
+    out[0] = v.x, out[1 % N] = v.y, out[2 % N] = v.z, out[3 % N] = v.w;
+  } else if (N == 2) {
+    const uint2 v = __ldcs(reinterpret_cast<const uint2*>(p));
+    out[0] = v.x, out[1 % N] = v.y;
+  } else {
+    out[0] = __ldcs(reinterpret_cast<const uint32_t*>(p));
+  }
+}
+
+// bf16 number `i` of a packed array of 32-bit words, as f32
+template <int N>
+__device__ __forceinline__ float lmq_meta(const uint32_t (&w)[N], int i) {
+  const uint32_t word = w[(i >> 1) % N];
+  return __uint_as_float((i & 1) ? (word & 0xffff0000u) : (word << 16));
+}
+
+template <int BITS, int P, int PG, bool PAIRED>
+__global__ void __launch_bounds__(LM_THREADS, 2) lm_head_argmax_affine_pipe_kernel(LmHeadAffineArgs a) {
+  extern __shared__ __align__(16) unsigned char lm_smem[];
+  __shared__ unsigned long long best_s[LM_WARPS][8];
+  __shared__ unsigned int last_s;
+  __shared__ float red_s[LM_WARPS];
+  using Pass = LmqPass<BITS, P, PG>;
+  constexpr int LW = Pass::LW, NS = Pass::NS;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  if (a.pdl_trigger) lm_pdl_trigger();
+  const int stride = lmq_x_stride_bytes(a.hidden);
+  const int blocks64 = a.hidden / 64;
+  const int groups = a.hidden / (64 * PG);
+  constexpr int RW = 64 * BITS / 32;                    // u32 words of a row per 64-column block
+  const int64_t row_words = int64_t(a.hidden) * BITS / 32;
+  const int passes = blocks64 / P;
+  const int64_t tiles = (a.vocab + 15) / 16;
+  const int64_t n_warps = int64_t(gridDim.x) * LM_WARPS;
+  const int64_t bias_delta = a.w.biases - a.w.scales;   // in elements; the two arrays have one shape
+
+  // Tiles of 16 rows. 151 936 rows are 4.01 tiles per warp: whichever way whole tiles are handed
+  // out, a few warps work through a fifth one (ten passes, each a DRAM round trip) while the
+  // rest of the GPU is done. So a warp takes the same number of whole tiles as every other warp
+  // (tile = its number + round * warps), and the tiles left over are shared out among the blocks
+  // afterwards, the eight warps of a block splitting the columns of one tile. The load cursor
+  // is one pass ahead of the compute cursor, also from one tile to the next.
+  const int64_t rounds = tiles / n_warps;
+  const int64_t first_tile = int64_t(blockIdx.x) * LM_WARPS + warp;
+  const int64_t end_tile = first_tile + rounds * n_warps;   // first tile this warp does not take
+  int64_t l_tile = rounds > 0 ? first_tile : end_tile;
+  int l_pass = 0;
+  const uint32_t* wp = nullptr;   // codes of row r0 at the cursor's pass (this lane's 16 columns)
+  const uint16_t* sp = nullptr;   // scales of row r0 at the cursor's pass
+  int32_t w_delta = 0, s_delta = 0;   // from row r0 to row r1 (0 where r1 is past the last row)
+  int64_t c_tile = l_tile;
+  auto load = [&](Pass& b) {
+    if (l_pass == 0) {
+      const int64_t r0 = l_tile * 16 + g;
+      const int64_t rr0 = r0 < a.vocab ? r0 : a.vocab - 1, rr1 = r0 + 8 < a.vocab ? r0 + 8 : a.vocab - 1;
+      wp = a.w.packed + rr0 * row_words + t * LW;
+      sp = a.w.scales + rr0 * groups;
+      w_delta = static_cast<int32_t>((rr1 - rr0) * row_words);
+      s_delta = static_cast<int32_t>((rr1 - rr0) * groups);
+    }
+#pragma unroll
+    for (int u = 0; u < P; ++u) {
+      lmq_load_words<LW>(wp + u * RW, b.a0[u]);
+      lmq_load_words<LW>(wp + w_delta + u * RW, b.a1[u]);
+    }
+    lmq_load_words<Pass::MW>(sp, b.s0);
+    lmq_load_words<Pass::MW>(sp + s_delta, b.s1);
+    lmq_load_words<Pass::MW>(sp + bias_delta, b.z0);
+    lmq_load_words<Pass::MW>(sp + bias_delta + s_delta, b.z1);
+    wp += P * RW;
+    sp += NS;
+    if (++l_pass == passes) l_pass = 0, l_tile += n_warps;
+  };
+  // the weight does not depend on the launch before this one: the first pass is on its way
+  // while that launch finishes and while the activation is staged
+  Pass A, B;
+  if (l_tile < end_tile) load(A);
+  if (a.pdl_wait) lm_pdl_wait();
+  unsigned char* xhi = lm_smem;
+  unsigned char* xlo = lm_smem + size_t(a.n_rows) * stride;
+  float* xsum = reinterpret_cast<float*>(lm_smem + size_t(2) * a.n_rows * stride);   // [n_rows][blocks64]
+  // the activation, staged exactly as in the kernel above
+  float big = 0.0f;
+  for (int i = tid; i < a.n_rows * a.hidden; i += LM_THREADS) big = fmaxf(big, fabsf(a.x[i]));
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, off));
+  if (lane == 0) red_s[warp] = big;
+  __syncthreads();
+  big = red_s[0];
+  for (int w = 1; w < LM_WARPS; ++w) big = fmaxf(big, red_s[w]);
+  int e = static_cast<int>((__float_as_uint(big) >> 23) & 0xffu) - 127;
+  e = max(-100, min(100, e));
+  const float xscale = exp2f(static_cast<float>(8 - e)), inv_xscale = exp2f(static_cast<float>(e - 8)) * LMQ_UNIT_INV;
+  for (int i = tid; i < a.n_rows * a.hidden; i += LM_THREADS) {
+    const int r = i / a.hidden, p = i - r * a.hidden;
+    const int col = (p & ~15) + lmq_slot_column<BITS>(p & 15);
+    const float v = a.x[size_t(r) * a.hidden + col] * xscale;
+    const __half h = __float2half_rn(v);
+    const __half l = __float2half_rn(v - __half2float(h));
+    reinterpret_cast<__half*>(xhi + size_t(r) * stride)[p] = h;
+    reinterpret_cast<__half*>(xlo + size_t(r) * stride)[p] = l;
+  }
+  __syncthreads();
+  for (int i = tid; i < a.n_rows * blocks64; i += LM_THREADS) {
+    const int r = i / blocks64, b = i - r * blocks64;
+    const __half* ph = reinterpret_cast<const __half*>(xhi + size_t(r) * stride) + b * 64;
+    const __half* pl = reinterpret_cast<const __half*>(xlo + size_t(r) * stride) + b * 64;
+    float sum = 0.0f;
+    for (int c = 0; c < 64; ++c) sum += __half2float(ph[c]) + __half2float(pl[c]);
+    xsum[i] = sum * (1.0f / LMQ_UNIT_INV);
+  }
+  __syncthreads();
+  constexpr bool paired = PAIRED;   // up to four activation rows: hi and lo halves share a product
+  const int act = paired ? g >> 1 : g;
+  const bool has_col = act < a.n_rows;
+  const unsigned char* bh = (paired && (g & 1) ? xlo : xhi) + (has_col ? act : 0) * stride + t * 32;
+  const unsigned char* bl = xlo + (has_col ? act : 0) * stride + t * 32;
+  const int c_row0 = paired ? t : 2 * t, c_row1 = paired ? t : 2 * t + 1;
+  const float* xs0 = xsum + (c_row0 < a.n_rows ? c_row0 : 0) * blocks64;
+  const float* xs1 = xsum + (c_row1 < a.n_rows ? c_row1 : 0) * blocks64;
+  // compute cursor
+  int c_pass = 0;
+  float v[4] = {0.f, 0.f, 0.f, 0.f};   // (r0, act 2t), (r0, act 2t+1), (r1, act 2t), (r1, act 2t+1)
+  unsigned long long best0 = 0, best1 = 0;
+  auto compute = [&](const Pass& b) {
+    const int blk0 = c_pass * P;
+#pragma unroll
+    for (int u = 0; u < P; ++u) {
+      const int blk = blk0 + u;
+      uint4 xh[2], xl[2];
+      xh[0] = xh[1] = xl[0] = xl[1] = make_uint4(0, 0, 0, 0);
+      if (has_col) {
+        xh[0] = *reinterpret_cast<const uint4*>(bh + blk * 128);
+        xh[1] = *reinterpret_cast<const uint4*>(bh + blk * 128 + 16);
+        if (!paired) {
+          xl[0] = *reinterpret_cast<const uint4*>(bl + blk * 128);
+          xl[1] = *reinterpret_cast<const uint4*>(bl + blk * 128 + 16);
+        }
+      }
+      const uint32_t bhr[8] = {xh[0].x, xh[0].y, xh[0].z, xh[0].w, xh[1].x, xh[1].y, xh[1].z, xh[1].w};
+      const uint32_t blr[8] = {xl[0].x, xl[0].y, xl[0].z, xl[0].w, xl[1].x, xl[1].y, xl[1].z, xl[1].w};
+      float ch[4] = {0.f, 0.f, 0.f, 0.f}, cl[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t a0, a1, a2, a3;
+        if (BITS == 8) {
+          a0 = __byte_perm(b.a0[u][j % LW], 0, 0x4140), a2 = __byte_perm(b.a0[u][j % LW], 0, 0x4342);
+          a1 = __byte_perm(b.a1[u][j % LW], 0, 0x4140), a3 = __byte_perm(b.a1[u][j % LW], 0, 0x4342);
+        } else {
+          const uint32_t p0 = b.a0[u][(j >> 1) % LW] >> ((j & 1) * 8), p1 = b.a1[u][(j >> 1) % LW] >> ((j & 1) * 8);
+          a0 = p0 & 0x000f000fu, a2 = (p0 >> 4) & 0x000f000fu;
+          a1 = p1 & 0x000f000fu, a3 = (p1 >> 4) & 0x000f000fu;
+        }
+        mma_f16_lm(ch, a0, a1, a2, a3, bhr[2 * j], bhr[2 * j + 1]);
+        if (!paired) mma_f16_lm(cl, a0, a1, a2, a3, blr[2 * j], blr[2 * j + 1]);
+      }
+      const float sc0 = lmq_meta(b.s0, u / PG), sc1 = lmq_meta(b.s1, u / PG);
+      const float bi0 = lmq_meta(b.z0, u / PG), bi1 = lmq_meta(b.z1, u / PG);
+      const float x0 = xs0[blk];
+      if (paired) {
+        v[0] += sc0 * (ch[0] + ch[1]) + bi0 * x0;
+        v[2] += sc1 * (ch[2] + ch[3]) + bi1 * x0;
+      } else {
+        const float x1 = xs1[blk];
+        v[0] += sc0 * (ch[0] + cl[0]) + bi0 * x0;
+        v[1] += sc0 * (ch[1] + cl[1]) + bi0 * x1;
+        v[2] += sc1 * (ch[2] + cl[2]) + bi1 * x0;
+        v[3] += sc1 * (ch[3] + cl[3]) + bi1 * x1;
+      }
+    }
+    if (++c_pass == passes) {
+      const int64_t r0 = c_tile * 16 + g, r1 = r0 + 8;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[i] *= inv_xscale;
+      if (r0 < a.vocab) {
+        const unsigned long long k0 = pack_key(v[0], r0), k1 = pack_key(v[1], r0);
+        best0 = k0 > best0 ? k0 : best0;
+        best1 = k1 > best1 ? k1 : best1;
+      }
+      if (r1 < a.vocab) {
+        const unsigned long long k0 = pack_key(v[2], r1), k1 = pack_key(v[3], r1);
+        best0 = k0 > best0 ? k0 : best0;
+        best1 = k1 > best1 ? k1 : best1;
+      }
+      v[0] = v[1] = v[2] = v[3] = 0.f;
+      c_pass = 0, c_tile += n_warps;
+    }
+  };
+
+  while (c_tile < end_tile) {
+    if (l_tile < end_tile) load(B);
+    compute(A);
+    if (c_tile >= end_tile) break;
+    if (l_tile < end_tile) load(A);
+    compute(B);
+  }
+
+  // the tiles left over: one per block and turn, warp w takes the 64-column blocks w, w + 8, ...;
+  // the partial sums meet in shared memory and are added in warp order
+  __shared__ float left_s[LM_WARPS][16][8];
+  unsigned long long left_best = 0;   // threads 0..127: (row tid / 8 of the tile, activation row tid % 8)
+  for (int64_t tile = rounds * n_warps + blockIdx.x; tile < tiles; tile += gridDim.x) {
+    const int64_t r0 = tile * 16 + g;
+    const int64_t rr0 = r0 < a.vocab ? r0 : a.vocab - 1, rr1 = r0 + 8 < a.vocab ? r0 + 8 : a.vocab - 1;
+    const uint32_t* w0 = a.w.packed + rr0 * row_words + t * LW;
+    const uint32_t* w1 = a.w.packed + rr1 * row_words + t * LW;
+    float lv[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+    for (int blk = warp; blk < blocks64; blk += LM_WARPS) {
+      uint32_t A0[LW], A1[LW];
+      lmq_load_words<LW>(w0 + blk * RW, A0);
+      lmq_load_words<LW>(w1 + blk * RW, A1);
+      const int grp = blk / PG;
+      const uint16_t s0 = a.w.scales[rr0 * groups + grp], s1 = a.w.scales[rr1 * groups + grp];
+      const uint16_t z0 = a.w.biases[rr0 * groups + grp], z1 = a.w.biases[rr1 * groups + grp];
+      uint4 xh[2], xl[2];
+      xh[0] = xh[1] = xl[0] = xl[1] = make_uint4(0, 0, 0, 0);
+      if (has_col) {
+        xh[0] = *reinterpret_cast<const uint4*>(bh + blk * 128);
+        xh[1] = *reinterpret_cast<const uint4*>(bh + blk * 128 + 16);
+        if (!paired) {
+          xl[0] = *reinterpret_cast<const uint4*>(bl + blk * 128);
+          xl[1] = *reinterpret_cast<const uint4*>(bl + blk * 128 + 16);
+        }
+      }
+      const uint32_t bhr[8] = {xh[0].x, xh[0].y, xh[0].z, xh[0].w, xh[1].x, xh[1].y, xh[1].z, xh[1].w};
+      const uint32_t blr[8] = {xl[0].x, xl[0].y, xl[0].z, xl[0].w, xl[1].x, xl[1].y, xl[1].z, xl[1].w};
+      float ch[4] = {0.f, 0.f, 0.f, 0.f}, cl[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t a0, a1, a2, a3;
+        if (BITS == 8) {
+          a0 = __byte_perm(A0[j % LW], 0, 0x4140), a2 = __byte_perm(A0[j % LW], 0, 0x4342);
+          a1 = __byte_perm(A1[j % LW], 0, 0x4140), a3 = __byte_perm(A1[j % LW], 0, 0x4342);
+        } else {
+          const uint32_t p0 = A0[(j >> 1) % LW] >> ((j & 1) * 8), p1 = A1[(j >> 1) % LW] >> ((j & 1) * 8);
+          a0 = p0 & 0x000f000fu, a2 = (p0 >> 4) & 0x000f000fu;
+          a1 = p1 & 0x000f000fu, a3 = (p1 >> 4) & 0x000f000fu;
+        }
+        mma_f16_lm(ch, a0, a1, a2, a3, bhr[2 * j], bhr[2 * j + 1]);
+        if (!paired) mma_f16_lm(cl, a0, a1, a2, a3, blr[2 * j], blr[2 * j + 1]);
+      }
+      const float sc0 = __uint_as_float(uint32_t(s0) << 16), sc1 = __uint_as_float(uint32_t(s1) << 16);
+      const float bi0 = __uint_as_float(uint32_t(z0) << 16), bi1 = __uint_as_float(uint32_t(z1) << 16);
+      const float x0 = xs0[blk];
+      if (paired) {
+        lv[0] += sc0 * (ch[0] + ch[1]) + bi0 * x0;
+        lv[2] += sc1 * (ch[2] + ch[3]) + bi1 * x0;
+      } else {
+        const float x1 = xs1[blk];
+        lv[0] += sc0 * (ch[0] + cl[0]) + bi0 * x0;
+        lv[1] += sc0 * (ch[1] + cl[1]) + bi0 * x1;
+        lv[2] += sc1 * (ch[2] + cl[2]) + bi1 * x0;
+        lv[3] += sc1 * (ch[3] + cl[3]) + bi1 * x1;
+      }
+    }
+    __syncthreads();   // the turn before this one has been added up
+    left_s[warp][g][c_row0] = lv[0];
+    left_s[warp][g + 8][c_row0] = lv[2];
+    if (!paired) {
+      left_s[warp][g][c_row1] = lv[1];
+      left_s[warp][g + 8][c_row1] = lv[3];
+    }
+    __syncthreads();
+    if (tid < 128) {
+      const int row = tid >> 3, arow = tid & 7;
+      float sum = left_s[0][row][arow];
+#pragma unroll
+      for (int w = 1; w < LM_WARPS; ++w) sum += left_s[w][row][arow];
+      const int64_t r = tile * 16 + row;
+      if (r < a.vocab && arow < a.n_rows) {
+        const unsigned long long key = pack_key(sum * inv_xscale, r);
+        left_best = key > left_best ? key : left_best;
+      }
+    }
+  }
+  // threads 0..127 hold the left-over tiles' best per (row, activation row): best per activation row
+  __shared__ unsigned long long left_best_s[4][8];
+#pragma unroll
+  for (int off = 8; off < 32; off <<= 1) {
+    const unsigned long long o = __shfl_xor_sync(0xffffffffu, left_best, off);
+    left_best = o > left_best ? o : left_best;
+  }
+  if (tid < 128 && lane < 8) left_best_s[warp][lane] = left_best;
+
+#pragma unroll
+  for (int off = 4; off < 32; off <<= 1) {
+    const unsigned long long o0 = __shfl_xor_sync(0xffffffffu, best0, off), o1 = __shfl_xor_sync(0xffffffffu, best1, off);
+    best0 = o0 > best0 ? o0 : best0;
+    best1 = o1 > best1 ? o1 : best1;
+  }
+  if (lane < 4) {
+    if (paired) {
+      best_s[warp][lane] = best0;
+    } else {
+      best_s[warp][2 * lane] = best0;
+      best_s[warp][2 * lane + 1] = best1;
+    }
+  }
+  __syncthreads();
+  if (tid < a.n_rows) {
+    unsigned long long b = best_s[0][tid];
+    for (int w = 1; w < LM_WARPS; ++w) b = best_s[w][tid] > b ? best_s[w][tid] : b;
+    for (int w = 0; w < 4; ++w) b = left_best_s[w][tid] > b ? left_best_s[w][tid] : b;
+    atomicMax(a.keys + tid, b);
+    __threadfence();
+  }
+  __syncthreads();
+  if (tid == 0) last_s = atomicAdd(a.counter, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (last_s && tid < a.n_rows) {
+    __threadfence();
+    const unsigned long long win = atomicExch(a.keys + tid, 0ull);
+    a.index_out[tid] = static_cast<int32_t>(0xffffffffu - uint32_t(win & 0xffffffffu)) + a.index_offset;
+    if (a.value_out) a.value_out[tid] = unordered_bits(uint32_t(win >> 32));
+    if (tid == 0) *a.counter = 0;
+  }
+}
+
 size_t lm_head_affine_smem_bytes(int n_rows, int hidden, int group_size) {
   (void)group_size;
   return size_t(2) * n_rows * lmq_x_stride_bytes(hidden) + size_t(n_rows) * (hidden / 64) * sizeof(float);
 }
 
 cudaError_t launch_lm_head_argmax_affine(const LmHeadAffineArgs& a, int sm_count, cudaStream_t stream) {
+  const int64_t tiles = (a.vocab + 15) / 16;
+  const int per_group = a.w.group_size / 64;
   const size_t smem = lm_head_affine_smem_bytes(a.n_rows, a.hidden, a.w.group_size);
   int per_sm = static_cast<int>((200 * 1024) / (smem + 1024));
   per_sm = per_sm > 2 ? 2 : per_sm < 1 ? 1 : per_sm;
   int blocks = sm_count * per_sm;
-  const int64_t tiles = (a.vocab + 15) / 16;
   if (int64_t(blocks) * LM_WARPS > tiles) blocks = static_cast<int>((tiles + LM_WARPS - 1) / LM_WARPS);
-  auto kernel = a.w.bits == 8 ? lm_head_argmax_affine_kernel<8> : lm_head_argmax_affine_kernel<4>;
+  void (*kernel)(LmHeadAffineArgs) = a.w.bits == 8 ? lm_head_argmax_affine_kernel<8> : lm_head_argmax_affine_kernel<4>;
+  // the pipelined kernel wherever a row is a whole number of passes and the rows' scales can be
+  // fetched with aligned vector loads
+  static const bool pipe_off = std::getenv("SGK_LM_NO_PIPE") != nullptr;
+  const int pass_blocks = a.w.bits == 8 ? 4 : 8;
+  const bool aligned = (reinterpret_cast<uintptr_t>(a.w.scales) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.w.biases) & 15) == 0 &&
+                       ((a.hidden / a.w.group_size) * 2) % (pass_blocks / per_group * 2) == 0;
+  if (!pipe_off && aligned && a.hidden % (64 * pass_blocks) == 0 && a.hidden >= 2 * 64 * pass_blocks) {
+    const bool paired = a.n_rows <= 4;
+    if (a.w.bits == 8 && paired) kernel = per_group == 1 ? lm_head_argmax_affine_pipe_kernel<8, 4, 1, true> : lm_head_argmax_affine_pipe_kernel<8, 4, 2, true>;
+    else if (a.w.bits == 8) kernel = per_group == 1 ? lm_head_argmax_affine_pipe_kernel<8, 4, 1, false> : lm_head_argmax_affine_pipe_kernel<8, 4, 2, false>;
+    else if (paired) kernel = per_group == 1 ? lm_head_argmax_affine_pipe_kernel<4, 8, 1, true> : lm_head_argmax_affine_pipe_kernel<4, 8, 2, true>;
+    else kernel = per_group == 1 ? lm_head_argmax_affine_pipe_kernel<4, 8, 1, false> : lm_head_argmax_affine_pipe_kernel<4, 8, 2, false>;
+  }
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return e;

@@ -259,6 +259,10 @@ class DecodeResidentState:
         """Says that launches of this state may run on two streams at once (default: they do not)."""
         check(self.L.sgk_state_set_concurrent_streams(self.h, 1 if enabled else 0))
 
+    def launches(self) -> int:
+        """Kernels launched so far through this state."""
+        return int(self.L.sgk_state_launches(self.h))
+
     def chain_begin(self, stream=None):
         """Opens a token chain on `stream`: the enqueues up to chain_end are one decode token."""
         check(self.L.sgk_state_chain_begin(self.h, stream))

@@ -448,6 +448,43 @@ def test_prefill_producer_equals_row_by_row_fused_append(state, dtype):
     serial.close()
 
 
+@pytest.mark.parametrize("rope_dims,interleaved", [(128, False), (64, False), (64, True)])
+def test_prompt_layers_share_one_rope_table(state, rope_dims, interleaved):
+    """The layers of a prompt append the same positions one after the other: the cos/sin table of
+    the first layer's launch serves the next ones, and a launch with other positions or another
+    theta gets its own. Every multi-row launch equals the row-by-row fused appends bit for bit
+    (also where only part of a head is rotated, or in the interleaved pairing)."""
+    kv_heads, hd = 2, 128
+    kv_dim = kv_heads * hd
+    w = np.float32(0.8) + np.abs(sgo.pseudo(5, hd))
+    d_w = state.upload(w)
+    n = 3 * 16 + 5
+    cases = [(10_000.0, 0), (10_000.0, 0), (1_000_000.0, 0), (10_000.0, 7), (10_000.0, 7)]
+    launches0 = state.launches()
+    for seed, (theta, already) in enumerate(cases):
+        rope = sg.make_rope(rope_dims, theta, eps=1e-6, interleaved=interleaved)
+        k_raw = sgo.fill_normal8((already + n) * kv_dim, 20 + seed, 0).reshape(already + n, kv_dim)
+        v = sgo.fill_normal8((already + n) * kv_dim, 20 + seed, 1).reshape(already + n, kv_dim)
+        bulk = state.full_attention(already + n, 4, kv_heads, hd, sg.KV_BF16)
+        serial = state.full_attention(already + n, 4, kv_heads, hd, sg.KV_BF16)
+        for r in range(already):
+            bulk.encode_rope_append(state.upload(k_raw[r]), state.upload(v[r]), d_w, rope)
+        before = state.launches()
+        bulk.encode_rope_append_rows(state.upload(k_raw[already:]), state.upload(v[already:]), n, d_w, rope)
+        made_table = state.launches() - before == 2
+        # a table is made when theta or the positions change, and held otherwise
+        assert made_table == (seed in (0, 2, 3))
+        for r in range(already + n):
+            serial.encode_rope_append(state.upload(k_raw[r]), state.upload(v[r]), d_w, rope)
+        state.sync()
+        bk, bv = bulk.gather_rows_f32()
+        sk, sv = serial.gather_rows_f32()
+        assert np.array_equal(bk, sk) and np.array_equal(bv, sv)
+        bulk.close()
+        serial.close()
+    assert state.launches() > launches0
+
+
 # ---- long context, paged, batched: against the oracle on seeded normal inputs ------------------
 def _normal_kv(n, kv_dim, seed, stream):
     return sgo.fill_normal8(n * kv_dim, seed, stream).reshape(n, kv_dim)
