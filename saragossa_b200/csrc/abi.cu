@@ -1118,7 +1118,6 @@ int32_t sgk_lm_head_enqueue_argmax_affine(sgk_state* st, void* stream, const sgk
   a.index_offset = index_offset;
   a.index_out = d_index_out;
   a.value_out = d_value_out;
-  a.status = st->d_status;
   cudaStream_t cs = st->pick(stream);
   const bool member = st->chain_member(cs);
   a.pdl_trigger = member ? 1 : 0;

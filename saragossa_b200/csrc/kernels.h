@@ -235,7 +235,6 @@ struct LmHeadAffineArgs {
   int32_t* index_out;
   float* value_out;
   int32_t pdl_trigger, pdl_wait;
-  int32_t* status;   // device status word: a bounded wait that ran out reports here
 };
 cudaError_t launch_lm_head_argmax_affine(const LmHeadAffineArgs& a, int sm_count, cudaStream_t stream);
 size_t lm_head_affine_smem_bytes(int n_rows, int hidden, int group_size);

@@ -427,6 +427,42 @@ def test_affine_lm_head_matches_oracle(gpu_state, bits, group, rows):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("bits,group", [(4, 64), (8, 64), (4, 128), (8, 128)])
+def test_affine_lm_head_large_vocabulary_same_answer_from_every_kernel(gpu_state, bits, group):
+    """A vocabulary of several whole rounds of tiles per warp plus left-over tiles and a last tile
+    of fewer than 16 rows: index and logit are the oracle's, and row 0 gets the same logit bits
+    alone, among three rows (hi and lo halves of the activation in one product) and among eight
+    rows (a product each)."""
+    import torch
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    vocab, hidden = 16 * (sms * 8 * 2 + 29) + 5, 1024
+    packed, scales, biases = _affine_weight(vocab, hidden, bits, group, 40 + bits + group)
+    w = sgo.affine_dequantize(packed, scales, biases, bits, group, vocab, hidden)
+    x = sgo.fill_normal8(8 * hidden, 72, bits).reshape(8, hidden)
+    mean = w.mean(axis=0)
+    planted = [vocab - 3, 16 * sms * 8 * 2 + 7, 5, 16 * sms * 8 + 1, 977, 4242, vocab - 40, 16 * sms * 8 * 2 - 1]
+    for r in range(8):
+        x[r] += (w[planted[r]] - mean) * np.float32(400.0)
+    d_w = gpu_state.upload_affine(packed, scales, biases, bits, group)
+    d_x = gpu_state.upload(x)
+    d_idx, d_val = gpu_state.alloc(4 * 8), gpu_state.alloc(4 * 8)
+    logits = w.astype(np.float64) @ x.astype(np.float64).T
+    want = logits.argmax(axis=0)
+    got = {}
+    for rows in (1, 3, 8):
+        gpu_state.encode_lm_head_argmax_affine(d_w, vocab, hidden, d_x, d_idx, n_rows=rows, d_value_out=d_val)
+        gpu_state.sync()
+        idx, val = d_idx.download(np.int32, rows), d_val.download(np.float32, rows)
+        for r in range(rows):
+            assert int(idx[r]) == int(want[r])
+            assert abs(float(val[r]) - logits[want[r], r]) <= 2e-4 * max(1.0, abs(logits[want[r], r]))
+        got[rows] = val.copy()
+    assert got[1][0].tobytes() == got[3][0].tobytes() == got[8][0].tobytes()
+    assert got[3][:3].tobytes() == got[8][:3].tobytes()
+    assert gpu_state.device_status() == 0
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("bits", [4, 8])
 def test_affine_embedding_lookup_is_the_dequantised_row(gpu_state, bits):
     vocab, hidden, group = 301, 256, 64
