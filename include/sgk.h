@@ -585,7 +585,12 @@ int32_t sgk_budget_limit(const sgk_budget* b, uint64_t* limit_out); /* 1 when a 
 int32_t sgk_budget_check_allocation(const sgk_budget* b, uint64_t requested, uint64_t* projected_out,
                                     uint64_t* available_out);
 
-/* ---- utilities used by the tests and the benchmark ---- */
+/* ---- TEST AND BENCHMARK SUPPORT: not part of the drop-in boundary --------------------------
+ * No interface of the reference stands behind the functions below: they feed the parity tests
+ * and the benchmark (seeded inputs made on the device, raw device buffers for callers without a
+ * CUDA runtime of their own, the block copier on raw ranges). A binding of the crate leaves them
+ * out by defining SGK_NO_TEST_SUPPORT before including this header. ---- */
+#ifndef SGK_NO_TEST_SUPPORT
 /* Device fill with the counter-based approximate-normal generator (integer only,
  * bit-identical to the host restatement used for parity inputs). */
 int32_t sgk_util_fill_normal(sgk_state* state, void* stream, float* d_out, int64_t n, uint64_t seed,
@@ -598,6 +603,7 @@ int32_t sgk_util_d2h(sgk_state* state, void* dst, const void* d_src, size_t byte
 int32_t sgk_util_copy_blocks(sgk_state* state, void* stream, void* d_dst, const void* d_src,
                              const int32_t* dst_pages, const int32_t* src_pages, int32_t n_pages,
                              int64_t page_bytes);
+#endif /* SGK_NO_TEST_SUPPORT */
 
 #ifdef __cplusplus
 }
