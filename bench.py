@@ -387,6 +387,19 @@ def run_ours(args):
     c3 = guarded(c3_token_leg, sg, st, torch, stream)
     c5 = guarded(c5_serving_leg, sg, st, torch, stream, dist, rank, world)
     c4 = guarded(c4_prefix_leg, sg, st, torch, stream, args.c4_turns, 128, rank, world)
+    if world > 1:
+        # whole job: all turns over the slowest rank's wall time (a rank that failed contributes zero turns)
+        ok = isinstance(c4, dict) and "error" not in c4
+        mine = [float(c4["turns_on_this_gpu"]), c4["turns_on_this_gpu"] / max(c4["turns_per_s"], 1e-9)] if ok else [0.0, 0.0]
+        t_sum = torch.tensor(mine, device="cuda", dtype=torch.float64)
+        t_max = t_sum.clone()
+        dist.all_reduce(t_sum, op=dist.ReduceOp.SUM)
+        dist.all_reduce(t_max, op=dist.ReduceOp.MAX)
+        if ok:
+            wall = max(float(t_max[1].item()), 1e-9)
+            c4["turns_done_all_gpus"] = int(t_sum[0].item())
+            c4["turns_per_s_all_gpus"] = float(t_sum[0].item()) / wall
+            c4["decode_tokens_per_s_all_gpus"] = float(t_sum[0].item()) * 128 / wall
     c1 = guarded(c1_decode_leg, sg, st, torch, stream) if rank == 0 else None
     lm_head = guarded(lm_head_leg, sg, st, torch, stream)
 
