@@ -278,7 +278,7 @@ def run_ours(args):
     K, W = args.steps, max(args.warmup, 3)
     e2e_steps = max(2, min(8, K))
     b1_steps = max(4, min(32, K))
-    extra = W + K + e2e_steps + 2 + 2 * (3 + b1_steps) + 16
+    extra = W + K + 2 * e2e_steps + 2 + 2 * (3 + b1_steps) + 16
     capacity = ((CTX + extra + 15) // 16) * 16
     pages_per_seq = capacity // 16
     dtype = sg.KV_BF16 if KV_DTYPE == "bf16" else sg.KV_U8G32
@@ -353,6 +353,26 @@ def run_ours(args):
         te = float(t.item())
     e2e_bytes = sum(algorithmic_bytes(rows_e2e + i + 1) for i in range(e2e_steps)) * LAYERS * BATCH
     e2e_value = e2e_bytes * world / te / 1e9
+    # The same without any overlap, for a caller whose layer l+1 inputs exist only after layer l:
+    # all inputs copied in, the token's graph, all outputs copied out, one after the other.
+    rows_serial = kvs[0][0].len()
+    ts = time.perf_counter()
+    for _ in range(e2e_steps):
+        d_k.upload(h_k)
+        d_v.upload(h_v)
+        d_q.upload(h_q)
+        step.replay(stream.cuda_stream)
+        stream.synchronize()
+        check_out = st.L.sgk_util_d2h(st.h, h_out.ctypes.data, d_out.ptr, h_out.nbytes)
+        if check_out != 0:
+            raise RuntimeError("device to host copy failed")
+    ts = time.perf_counter() - ts
+    if world > 1:
+        t = torch.tensor([ts], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ts = float(t.item())
+    serial_bytes = sum(algorithmic_bytes(rows_serial + i + 1) for i in range(e2e_steps)) * LAYERS * BATCH
+    e2e_serial_value = serial_bytes * world / ts / 1e9
     h2d = (2 * LAYERS * BATCH * KV_DIM + LAYERS * BATCH * Q_DIM) * 4
     d2h = LAYERS * BATCH * Q_DIM * 4
     finite = bool(np.isfinite(h_out).all())
@@ -435,6 +455,7 @@ def run_ours(args):
                                        "restatement of the reference path (oracle/), f32 storage of bf16-rounded K/V"},
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "ms_per_step": te / e2e_steps * 1e3,
+                    "no_overlap_value": e2e_serial_value, "no_overlap_ms_per_step": ts / e2e_steps * 1e3,
                     "call": "sgk_step_run_host (pinned host k,v,q in; out back; synchronous)"},
             "gpu_launches": int(launches), "clocks": clocks, "device_status": status, "outputs_finite": finite,
             "seed_seconds": t_seed,
@@ -908,7 +929,9 @@ def c3_token_leg(sg, st, torch, stream):
     """Config 3 as it is stated: one sequence, 40 layers, every 4th a full-attention layer
     (16 Q / 2 KV heads, hd256, u8 group-32 pages, context 32768), the other 30 recurrent
     (32 heads x 128 x 128 f32 state + conv history of 8192 channels, kernel 4). One token of the
-    whole KV path (fused append+attention, conv step, gated-delta step) as ONE CUDA graph."""
+    whole KV path as ONE CUDA graph: fused append+attention on the attention layers, the
+    one-launch decode step (conv + SiLU + norms + gates + gated delta) on the recurrent ones; the
+    same token with the conv step and the gated-delta step as two launches is timed beside it."""
     layers, qh, kvh, hd, ctx = 40, 16, 2, 256, CTX
     attn_layers = [i for i in range(layers) if (i + 1) % 4 == 0]
     rec_layers = [i for i in range(layers) if (i + 1) % 4 != 0]
@@ -943,15 +966,25 @@ def c3_token_leg(sg, st, torch, stream):
         bufs[name] = st.upload(b.download(count=n) * np.float32(scale))
     bufs["g"] = st.upload(np.full(hv, 0.97, np.float32))
     bufs["beta"] = st.upload(np.full(hv, 0.5, np.float32))
+    # gates of the one-launch step: sigmoid(0) = 0.5 and exp(-softplus(-3.49)) = 0.97
+    bufs["beta_in"] = st.upload(np.zeros(hv, np.float32))
+    bufs["gate_in"] = st.upload(np.full(hv, -3.49, np.float32))
+    bufs["a_log"] = st.upload(np.zeros(hv, np.float32))
+    bufs["dt_bias"] = st.upload(np.zeros(hv, np.float32))
     d_out, d_y, d_c = st.alloc(4 * q_dim), st.alloc(4 * hv * dv), st.alloc(4 * conv_dim)
 
-    def token():
+    def token(one_launch):
         a = r = 0
         st.chain_begin(stream.cuda_stream)   # one decode token: every launch lets the next one start early
         for layer in range(layers):
             if layer in attn_layers:
                 batches[a].enqueue_step(bufs["k"], bufs["v"], bufs["q"], d_out, stream=stream.cuda_stream)
                 a += 1
+            elif one_launch:
+                # conv + SiLU + unit norms + gates + gated delta of the layer in one launch
+                ls.encode_decode_step(r, shape, bufs["x"], bufs["w"], kernel, bufs["beta_in"], bufs["gate_in"],
+                                      bufs["a_log"], bufs["dt_bias"], d_y, stream=stream.cuda_stream)
+                r += 1
             else:
                 ls.encode_conv_step(r, bufs["x"], bufs["w"], conv_dim, kernel, d_c, stream=stream.cuda_stream)
                 ls.encode_gated_delta_step(r, shape, bufs["gq"], bufs["gk"], bufs["gv"], bufs["g"], bufs["beta"], d_y,
@@ -959,23 +992,27 @@ def c3_token_leg(sg, st, torch, stream):
                 r += 1
         st.chain_end()
 
-    token()
-    stream.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph, stream=stream):
-        token()
-    reps = 20
-    with torch.cuda.stream(stream):
-        for _ in range(3):
-            graph.replay()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    def timed(one_launch):
+        token(one_launch)
         stream.synchronize()
-        e0.record(stream)
-        for _ in range(reps):
-            graph.replay()
-        e1.record(stream)
-        stream.synchronize()
-    us = e0.elapsed_time(e1) * 1e3 / reps
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            token(one_launch)
+        reps = 20
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                graph.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            stream.synchronize()
+            e0.record(stream)
+            for _ in range(reps):
+                graph.replay()
+            e1.record(stream)
+            stream.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / reps
+
+    us_two = timed(False)
+    us = timed(True)
     kv_bytes = len(attn_layers) * ctx * kv_dim * 2 * 1.125
     state_bytes = len(rec_layers) * 2 * 4 * hv * dv * dk
     finite = bool(np.isfinite(d_out.download(count=q_dim)).all() and np.isfinite(d_y.download(count=hv * dv)).all())
@@ -984,7 +1021,8 @@ def c3_token_leg(sg, st, torch, stream):
     ls.close()
     seq.close()
     pool.close()
-    return {"us_per_token": us, "launches_per_token": len(attn_layers) + 2 * len(rec_layers),
+    return {"us_per_token": us, "launches_per_token": len(attn_layers) + len(rec_layers),
+            "conv_and_gated_delta_as_two_launches_us_per_token": us_two,
             "hbm_gbs": (kv_bytes + state_bytes) / (us * 1e-6) / 1e9, "kv_bytes": kv_bytes, "state_bytes": state_bytes,
             "outputs_finite": finite, "device_status": st.device_status(),
             "shape": "batch 1, ctx 32768: 10 x (16Q/2KV hd256 u8-g32) + 30 x (32 x 128 x 128 f32 state)"}

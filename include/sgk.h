@@ -489,6 +489,23 @@ int32_t sgk_linstate_enqueue_gated_delta_step_batch(sgk_linstate* const* states,
                                                     int32_t layer, const sgk_linear_shape* shape,
                                                     const float* d_q, const float* d_k, const float* d_v,
                                                     const float* d_g, const float* d_beta, float* d_out);
+/* The whole decode step of a recurrent layer between its projections, ONE launch: the reference's
+ * resident decode issues conv + SiLU + unit RMS norm of q and k + gates as one dispatch and the
+ * gated-delta update as the next (linear_attn_conv_norm_gates_k4_dk128_f32 and
+ * linear_attn_gated_delta_dk128_tg4_f32, src/kernels.metal:2295-2416,2569-2643); CPU order of
+ * operations src/linear_attention.rs:313-342:
+ *   c = silu(depthwise_causal_conv(qkv))                     (the history slides by one token)
+ *   q = rms_norm_heads_unit(c[0 : key_dim], eps 1e-6) * d_k^-1;  k = ...(c[key_dim : 2 key_dim]) * d_k^-1/2
+ *   v = c[2 key_dim :];  beta = sigmoid(beta_input);  g = exp(-exp(a_log) * softplus(gate_input + dt_bias))
+ *   out = gated_delta(q, k, v, g, beta) on the layer's state
+ * d_qkv [2 H_k d_k + H_v d_v]; d_conv_weight [conv_dim][conv_kernel_dim]; d_beta_input, d_gate_input,
+ * d_a_log, d_dt_bias [H_v]; d_out [H_v d_v]. Head dims of 128 and 1 to 8 taps (Config error otherwise:
+ * the two steps below take every shape). Within 1e-5 of the CPU order (f32 state), the reference's own
+ * bound for its fused dispatches; the conv part is bit-exact. */
+int32_t sgk_linstate_enqueue_decode_step(sgk_linstate* ls, void* stream, int32_t layer, const sgk_linear_shape* shape,
+                                         const float* d_qkv, const float* d_conv_weight, int32_t conv_kernel_dim,
+                                         const float* d_beta_input, const float* d_gate_input, const float* d_a_log,
+                                         const float* d_dt_bias, float* d_out);
 void* sgk_linstate_ssm_ptr(sgk_linstate* ls, int32_t layer);
 
 /* ---- block hashes: BlockHash::{root,for_session,chain} (src/serve/cache.rs:11-47) ---- */

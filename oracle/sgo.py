@@ -475,6 +475,66 @@ def depthwise_conv_step(qkv, weight, kernel, history):
     return st, out, hist
 
 
+def silu(x):
+    """src/activation.rs:14-16: v / (1 + exp(-v)) in f32."""
+    x = _f32(x)
+    return (x / (np.float32(1.0) + np.exp(-x, dtype=np.float32))).astype(np.float32)
+
+
+def rms_norm_heads_unit(x, heads, head_dim, eps=1.0e-6):
+    """src/linear_attention.rs:1029-1050: per head x / sqrt(mean(x^2) + eps), the squares summed in
+    order in f32."""
+    x = _f32(x).reshape(heads, head_dim)
+    out = np.empty_like(x)
+    for h in range(heads):
+        acc = np.float32(0.0)
+        for v in x[h]:
+            acc = np.float32(acc + np.float32(v * v))
+        inv = np.float32(1.0) / np.sqrt(np.float32(acc / np.float32(head_dim)) + np.float32(eps), dtype=np.float32)
+        out[h] = x[h] * inv
+    return out.ravel()
+
+
+def key_scale(head_dim, squared):
+    """src/linear_attention.rs:1203-1210."""
+    inv = np.float32(np.power(np.float32(head_dim), np.float32(-0.5)))
+    return np.float32(inv * inv) if squared else inv
+
+
+def compute_decay(gate_input, a_log, dt_bias):
+    """src/linear_attention.rs:1122-1146 with softplus :1218-1224 (identity above 20)."""
+    arg = (_f32(gate_input) + _f32(dt_bias)).astype(np.float32)
+    with np.errstate(over="ignore"):
+        soft = np.where(arg > 20.0, arg, np.log(np.float32(1.0) + np.exp(arg, dtype=np.float32), dtype=np.float32))
+    return np.exp(-np.exp(_f32(a_log), dtype=np.float32) * soft.astype(np.float32), dtype=np.float32)
+
+
+def sigmoid(x):
+    """src/linear_attention.rs:1213-1215."""
+    return (np.float32(1.0) / (np.float32(1.0) + np.exp(-_f32(x), dtype=np.float32))).astype(np.float32)
+
+
+def linear_decode_step(qkv, conv_weight, kernel, history, beta_input, gate_input, a_log, dt_bias, num_key_heads,
+                       num_value_heads, key_head_dim, value_head_dim, ssm):
+    """One token of a recurrent layer between its projections, in the CPU order of
+    src/linear_attention.rs:313-342: conv -> silu -> unit RMS norm of q and k times key_scale ->
+    sigmoid / decay gates -> gated_delta. Returns (status, out, new_history, new_ssm, parts) where
+    parts holds the intermediate q, k, v, beta, g."""
+    st, conv, hist = depthwise_conv_step(qkv, conv_weight, kernel, history)
+    if st != 0:
+        return st, None, None, None, None
+    act = silu(conv)
+    key_dim = num_key_heads * key_head_dim
+    q = rms_norm_heads_unit(act[:key_dim], num_key_heads, key_head_dim) * key_scale(key_head_dim, True)
+    k = rms_norm_heads_unit(act[key_dim:2 * key_dim], num_key_heads, key_head_dim) * key_scale(key_head_dim, False)
+    v = act[2 * key_dim:]
+    beta = sigmoid(beta_input)
+    g = compute_decay(gate_input, a_log, dt_bias)
+    st, out, new_ssm = gated_delta_step(q.astype(np.float32), k.astype(np.float32), v, g, beta, num_key_heads,
+                                        num_value_heads, key_head_dim, value_head_dim, ssm)
+    return st, out, hist, new_ssm, {"q": q, "k": k, "v": v, "beta": beta, "g": g}
+
+
 def lm_head_argmax(weight, x):
     """First maximum of W . x (src/sampling.rs:49-62); weight [vocab][hidden]; returns (status, index, value)."""
     weight, x = _f32(weight), _f32(x).ravel()

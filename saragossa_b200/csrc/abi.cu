@@ -1,6 +1,7 @@
 // extern "C" surface of libsgk: argument validation in the reference's error
 // vocabulary, then the host objects of host.h. Declared in include/sgk.h.
 #include <algorithm>
+#include <cmath>
 #include <cstring>
 #include <random>
 
@@ -943,6 +944,8 @@ int32_t sgk_linstate_create(sgk_state* st, int32_t layers, int64_t conv_len, int
     return fail(SGK_ERR_MEMORY_GUARD, "linear state of %lld bytes does not fit: %s", (long long)ls->total_bytes,
                 cudaGetErrorString(e));
   SGK_CUDA(cudaMemset(ls->d_base, 0, static_cast<size_t>(ls->total_bytes)));
+  SGK_CUDA(cudaMalloc(&ls->d_head_counters, 64 * sizeof(int32_t)));
+  SGK_CUDA(cudaMemset(ls->d_head_counters, 0, 64 * sizeof(int32_t)));
   *out = ls.release();
   return SGK_OK;
 }
@@ -1482,6 +1485,63 @@ static int32_t conv_impl(sgk_linstate* ls, void* stream, int32_t layer, const fl
   const bool member = st->chain_member(s);
   SGK_CUDA(launch_conv_step(d_qkv, d_weight, static_cast<float*>(sgk_linstate_conv_ptr(ls, layer)), d_out, conv_dim,
                             conv_kernel_dim, n_tokens, member ? 1 : 0, st->chain_follows(s) ? 1 : 0, s));
+  st->launches += 1;
+  if (member) st->chain_note();
+  return SGK_OK;
+}
+
+int32_t sgk_linstate_enqueue_decode_step(sgk_linstate* ls, void* stream, int32_t layer, const sgk_linear_shape* shape,
+                                         const float* d_qkv, const float* d_conv_weight, int32_t conv_kernel_dim,
+                                         const float* d_beta_input, const float* d_gate_input, const float* d_a_log,
+                                         const float* d_dt_bias, float* d_out) {
+  if (!ls || !shape || !d_qkv || !d_conv_weight || !d_beta_input || !d_gate_input || !d_a_log || !d_dt_bias || !d_out)
+    return fail(SGK_ERR_BACKEND, "null argument");
+  if (layer < 0 || layer >= ls->layers) return fail(SGK_ERR_DIMENSION, "layer %d out of range", layer);
+  const int hk = shape->num_key_heads, hv = shape->num_value_heads;
+  // the validation of LinearAttentionConfig (src/linear_attention.rs:113-150)
+  if (hk <= 0 || hv <= 0 || shape->key_head_dim <= 0 || shape->value_head_dim <= 0)
+    return fail(SGK_ERR_CONFIG, "linear attention: zero dimension");
+  if (hv % hk != 0) return fail(SGK_ERR_CONFIG, "value heads %d are not a multiple of key heads %d", hv, hk);
+  if (shape->key_head_dim != 128 || shape->value_head_dim != 128)
+    return fail(SGK_ERR_CONFIG, "the one-launch decode step takes head dims of 128 (got %d / %d): use the conv and "
+                "gated-delta steps", shape->key_head_dim, shape->value_head_dim);
+  if (hk > 64) return fail(SGK_ERR_CONFIG, "more than 64 key heads");
+  if (conv_kernel_dim < 1 || conv_kernel_dim > 8)
+    return fail(SGK_ERR_CONFIG, "conv kernel %d: 1 to 8 taps in the one-launch decode step", conv_kernel_dim);
+  const int64_t conv_dim = int64_t(2) * hk * 128 + int64_t(hv) * 128;
+  if (ls->conv_len != int64_t(conv_kernel_dim - 1) * conv_dim)
+    return fail(SGK_ERR_DIMENSION, "conv history holds %lld values, expected %lld", (long long)ls->conv_len,
+                (long long)(int64_t(conv_kernel_dim - 1) * conv_dim));
+  if (ls->ssm_len != int64_t(hv) * 128 * 128)
+    return fail(SGK_ERR_DIMENSION, "recurrent state holds %lld values, expected %lld", (long long)ls->ssm_len,
+                (long long)(int64_t(hv) * 128 * 128));
+  State* st = ls->st;
+  cudaStream_t s = st->pick(stream);
+  const bool member = st->chain_member(s);
+  LinearDecodeArgs a{};
+  a.ssm = sgk_linstate_ssm_ptr(ls, layer);
+  a.history = static_cast<float*>(sgk_linstate_conv_ptr(ls, layer));
+  a.qkv = d_qkv;
+  a.conv_weight = d_conv_weight;
+  a.beta_input = d_beta_input;
+  a.gate_input = d_gate_input;
+  a.a_log = d_a_log;
+  a.dt_bias = d_dt_bias;
+  a.out = d_out;
+  a.head_counters = ls->d_head_counters;
+  a.conv_dim = static_cast<int32_t>(conv_dim);
+  a.kernel = conv_kernel_dim;
+  a.num_key_heads = hk;
+  a.num_value_heads = hv;
+  // key_scale (src/linear_attention.rs:1203-1210): d^-1/2 for k, its square for q
+  const float inv = std::pow(128.0f, -0.5f);
+  a.q_scale = inv * inv;
+  a.k_scale = inv;
+  a.eps = 1.0e-6f;
+  a.ssm_bf16 = ls->ssm_bf16 ? 1 : 0;
+  a.pdl_trigger = member ? 1 : 0;
+  a.pdl_wait = st->chain_follows(s) ? 1 : 0;
+  SGK_CUDA(launch_linear_decode_step(a, s));
   st->launches += 1;
   if (member) st->chain_note();
   return SGK_OK;

@@ -253,6 +253,7 @@ struct LinState {
   bool ssm_bf16 = false;
   int64_t conv_stride = 0, layer_stride = 0, total_bytes = 0;
   uint8_t* d_base = nullptr;
+  int32_t* d_head_counters = nullptr;   // [64] arrivals per key head of the one-launch decode step; zero between launches
   int64_t ssm_elem() const { return ssm_bf16 ? 2 : 4; }
   int64_t estimated_bytes() const { return layers * (conv_len * 4 + ssm_len * ssm_elem()); }
   ~LinState();

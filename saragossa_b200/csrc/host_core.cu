@@ -688,6 +688,7 @@ int Step::enqueue_range(cudaStream_t stream, size_t l0, size_t l1, const float* 
 // ---------------------------------------------------------------- LinState
 LinState::~LinState() {
   if (d_base) cudaFree(d_base);
+  if (d_head_counters) cudaFree(d_head_counters);
 }
 
 Exchange::~Exchange() {

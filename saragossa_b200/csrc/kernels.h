@@ -181,6 +181,25 @@ struct GatedDeltaArgs {
   int32_t pdl_trigger, pdl_wait;
 };
 cudaError_t launch_gated_delta_step(const GatedDeltaArgs& a, int sm_count, cudaStream_t stream);
+// One decode token of a whole recurrent layer between its projections, one launch:
+// conv + SiLU + unit RMS norm of q and k + gates + gated-delta update (key and value head dim 128).
+struct LinearDecodeArgs {
+  void* ssm;                  // [H_v][128][128] state of this layer
+  float* history;             // [(K-1)][conv_dim] conv history of this layer
+  const float* qkv;           // [conv_dim] the token's projected q | k | v
+  const float* conv_weight;   // [conv_dim][K]
+  const float* beta_input;    // [H_v]
+  const float* gate_input;    // [H_v]
+  const float* a_log;         // [H_v]
+  const float* dt_bias;       // [H_v]
+  float* out;                 // [H_v * 128]
+  int32_t* head_counters;     // [H_k] arrivals of a key head's blocks; zero between launches
+  int32_t conv_dim, kernel;
+  int32_t num_key_heads, num_value_heads;
+  float q_scale, k_scale, eps;
+  int32_t ssm_bf16, pdl_trigger, pdl_wait;
+};
+cudaError_t launch_linear_decode_step(const LinearDecodeArgs& a, cudaStream_t stream);
 cudaError_t launch_conv_step(const float* qkv, const float* weight, float* history, float* out, int conv_dim,
                              int kernel, int n_tokens, int pdl_trigger, int pdl_wait, cudaStream_t stream);
 // Launch configuration shared by the small kernels of a token chain.

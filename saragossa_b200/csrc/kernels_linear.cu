@@ -228,6 +228,159 @@ cudaError_t launch_gated_delta_step(const GatedDeltaArgs& a, int sm_count, cudaS
                     : cudaLaunchKernelEx(&l.cfg, gated_delta_step_kernel<false>, a);
 }
 
+// ---- the whole decode step of a recurrent layer in one launch ----------------------------------
+// The reference's resident decode runs conv + SiLU + unit RMS norm + gates as one dispatch and the
+// gated-delta update as the next (linear_attn_conv_norm_gates_k4_dk128_f32 and
+// linear_attn_gated_delta_dk128_tg4_f32, src/kernels.metal:2295-2416,2569-2643; CPU order of
+// operations src/linear_attention.rs:313-342). Two small launches that depend on each other cost
+// about 2 us each however they overlap their neighbours, and config 3 has 30 such layers per
+// token. Here a block of 8 warps owns 8 state rows of one value head and does everything they
+// need: the 256 threads redo the conv of the key head's 128 q and 128 k channels (8 KiB from L2),
+// eight of them the conv of the block's own v channels, two block reductions give the norms, and
+// each warp updates its row. The conv history of q and k is read by all 32 blocks of a key head
+// and must be shifted by one of them only after all have read it: a block arrives on the head's
+// counter once its history values are in registers, and the block that arrives last writes the
+// shifted rows (from its registers). Nobody waits. v channels belong to one block each.
+// All 512 blocks of config 3's shape (32 value heads) must be resident at once or the launch takes two
+// waves: at most 64 registers per thread (four blocks of 256 threads per SM), which the usual conv
+// kernel of four taps fits; up to eight taps take the instance with longer tap arrays.
+template <bool BF16, int LD_MAX_KERNEL>
+__global__ void __launch_bounds__(GD_THREADS, LD_MAX_KERNEL <= 4 ? 4 : 3) linear_decode_step_dk128_kernel(LinearDecodeArgs a) {
+  __shared__ float qk_s[256];        // normalised q [128] | k [128] of the key head
+  __shared__ float red_s[GD_WARPS];
+  __shared__ float v_s[GD_WARPS];    // silu(conv) of the block's eight v channels
+  __shared__ float gate_s[2];        // beta, decay of the value head
+  __shared__ int last_s;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int blocks_per_vh = 128 / GD_WARPS;                 // 16 blocks of 8 rows per value head
+  const int vh = blockIdx.x / blocks_per_vh, rb = blockIdx.x % blocks_per_vh;
+  const int repeat = a.num_value_heads / a.num_key_heads;
+  const int kh = vh / repeat;
+  const int key_dim = a.num_key_heads * 128;
+  const int K = a.kernel, keep = K - 1;
+  if (a.pdl_trigger) lin_pdl_trigger();
+
+  // this warp's state row, and the taps and history of this thread's channels: none of them is
+  // written by the launch before this one
+  const int row = vh * 128 + rb * GD_WARPS + warp;
+  const int64_t base = int64_t(row) * 128 + lane * 4;
+  float4 s;
+  if (BF16) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(a.ssm) + base);
+    s = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                    __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+  } else {
+    s = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.ssm) + base);
+  }
+  // channel of this thread: q (threads 0..127) or k (128..255) of the key head
+  const int c = (tid < 128 ? 0 : key_dim) + kh * 128 + (tid & 127);
+  // and, for the first eight threads, one v channel of the block
+  const bool has_v = tid < GD_WARPS;
+  const int cv = 2 * key_dim + vh * 128 + rb * GD_WARPS + (has_v ? tid : 0);
+  float w[LD_MAX_KERNEL], h[LD_MAX_KERNEL], wv[LD_MAX_KERNEL], hv[LD_MAX_KERNEL];
+#pragma unroll
+  for (int kk = 0; kk < LD_MAX_KERNEL; ++kk) {
+    w[kk] = kk < K ? a.conv_weight[int64_t(c) * K + kk] : 0.0f;
+    h[kk] = kk < keep ? a.history[int64_t(kk) * a.conv_dim + c] : 0.0f;
+    wv[kk] = has_v && kk < K ? a.conv_weight[int64_t(cv) * K + kk] : 0.0f;
+    hv[kk] = has_v && kk < keep ? a.history[int64_t(kk) * a.conv_dim + cv] : 0.0f;
+  }
+  const float a_log = a.a_log[vh], dt_bias = a.dt_bias[vh];
+  if (a.pdl_wait) lin_pdl_wait();   // the token's inputs come from the launch before
+
+  // depthwise conv in tap order with separate roundings (the CPU loop), then SiLU
+  const float x = a.qkv[c];
+  float acc = 0.0f;
+#pragma unroll
+  for (int kk = 0; kk < LD_MAX_KERNEL; ++kk)
+    if (kk < K) acc = __fadd_rn(acc, __fmul_rn(kk < keep ? h[kk] : x, w[kk]));
+  const float act = __fdiv_rn(acc, __fadd_rn(1.0f, expf(-acc)));
+  float xv = 0.0f;
+  if (has_v) {
+    xv = a.qkv[cv];
+    float av = 0.0f;
+#pragma unroll
+    for (int kk = 0; kk < LD_MAX_KERNEL; ++kk)
+      if (kk < K) av = __fadd_rn(av, __fmul_rn(kk < keep ? hv[kk] : xv, wv[kk]));
+    v_s[tid] = __fdiv_rn(av, __fadd_rn(1.0f, expf(-av)));
+    // this block is the only reader of its v channels: their history slides at once
+#pragma unroll
+    for (int kk = 0; kk < LD_MAX_KERNEL; ++kk)
+      if (kk < keep) a.history[int64_t(kk) * a.conv_dim + cv] = kk + 1 < keep ? hv[kk + 1] : xv;
+  }
+  if (tid == 0) {
+    const float b = a.beta_input[vh];
+    gate_s[0] = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-b)));
+    const float dt_arg = __fadd_rn(a.gate_input[vh], dt_bias);
+    const float dt = dt_arg > 20.0f ? dt_arg : logf(__fadd_rn(1.0f, expf(dt_arg)));
+    gate_s[1] = expf(__fmul_rn(-expf(a_log), dt));
+  }
+  // unit RMS norm per head: sum of squares over the head's 128 channels (warps 0-3: q, 4-7: k)
+  float ss = __fmul_rn(act, act);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if (lane == 0) red_s[warp] = ss;
+  __syncthreads();   // every history value of this block has been read (it went into acc)
+  // The arrival is asked for now and looked at after the row's arithmetic, by a thread that has
+  // no store of its own in flight (its fence has nothing to wait for): the round trip to the
+  // counter stays off the path from the token's inputs to the state update.
+  int arrived = 0;
+  if (tid == 32) {
+    __threadfence();
+    arrived = atomicAdd(a.head_counters + kh, 1);
+  }
+  const int half = tid < 128 ? 0 : 4;
+  const float sum = (red_s[half] + red_s[half + 1]) + (red_s[half + 2] + red_s[half + 3]);
+  const float inv_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, 128.0f), a.eps)));
+  qk_s[tid] = __fmul_rn(__fmul_rn(act, inv_rms), tid < 128 ? a.q_scale : a.k_scale);
+  __syncthreads();
+
+  // gated delta on this warp's row (the arithmetic of gated_delta_step_dk128_kernel)
+  const float4 qq = *reinterpret_cast<const float4*>(qk_s + lane * 4);
+  const float4 kk4 = *reinterpret_cast<const float4*>(qk_s + 128 + lane * 4);
+  const float beta = gate_s[0], decay = gate_s[1];
+  s.x = __fmul_rn(s.x, decay), s.y = __fmul_rn(s.y, decay), s.z = __fmul_rn(s.z, decay), s.w = __fmul_rn(s.w, decay);
+  float kv = dot4(s, kk4);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) kv += __shfl_xor_sync(0xffffffffu, kv, off);
+  const float delta = __fmul_rn(__fsub_rn(v_s[warp], kv), beta);
+  s.x = __fmaf_rn(delta, kk4.x, s.x), s.y = __fmaf_rn(delta, kk4.y, s.y);
+  s.z = __fmaf_rn(delta, kk4.z, s.z), s.w = __fmaf_rn(delta, kk4.w, s.w);
+  float y = dot4(s, qq);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) y += __shfl_xor_sync(0xffffffffu, y, off);
+  if (lane == 0) a.out[row] = y;
+  if (BF16) {
+    uint2 raw;
+    raw.x = uint32_t(f32_to_bf16_bits(s.x)) | (uint32_t(f32_to_bf16_bits(s.y)) << 16);
+    raw.y = uint32_t(f32_to_bf16_bits(s.z)) | (uint32_t(f32_to_bf16_bits(s.w)) << 16);
+    *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(a.ssm) + base) = raw;
+  } else {
+    *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.ssm) + base) = s;
+  }
+  if (tid == 32) {
+    last_s = arrived == repeat * blocks_per_vh - 1;
+    if (last_s) a.head_counters[kh] = 0;
+  }
+  __syncthreads();
+  if (last_s) {
+    // every block of the key head has its history in registers: slide the q and k rows
+    __threadfence();
+#pragma unroll
+    for (int kk = 0; kk < LD_MAX_KERNEL; ++kk)
+      if (kk < keep) a.history[int64_t(kk) * a.conv_dim + c] = kk + 1 < keep ? h[kk + 1] : x;
+  }
+}
+
+cudaError_t launch_linear_decode_step(const LinearDecodeArgs& a, cudaStream_t stream) {
+  ChainLaunch l(dim3(a.num_value_heads * (128 / GD_WARPS)), dim3(GD_THREADS), 0, stream, a.pdl_wait != 0);
+  if (a.kernel <= 4)
+    return a.ssm_bf16 ? cudaLaunchKernelEx(&l.cfg, linear_decode_step_dk128_kernel<true, 4>, a)
+                      : cudaLaunchKernelEx(&l.cfg, linear_decode_step_dk128_kernel<false, 4>, a);
+  return a.ssm_bf16 ? cudaLaunchKernelEx(&l.cfg, linear_decode_step_dk128_kernel<true, 8>, a)
+                    : cudaLaunchKernelEx(&l.cfg, linear_decode_step_dk128_kernel<false, 8>, a);
+}
+
 // One thread per channel: the products are summed in kernel-tap order with separate
 // roundings, exactly like the CPU loop, then the channel's history slides by one token.
 constexpr int CONV_MAX_KERNEL = 16;

@@ -801,6 +801,15 @@ class LinearAttentionState:
         check(self.L.sgk_linstate_enqueue_conv_step(self.h, stream, layer, d_qkv.ptr, d_weight.ptr, conv_dim,
                                                     conv_kernel_dim, d_out.ptr))
 
+    def encode_decode_step(self, layer, shape, d_qkv, d_conv_weight, conv_kernel_dim, d_beta_input, d_gate_input,
+                           d_a_log, d_dt_bias, d_out, stream=None):
+        """conv + SiLU + unit norms + gates + gated delta of one token in one launch
+        (src/linear_attention.rs:313-342); shape = (H_k, H_v, 128, 128)."""
+        sh = LinearShape(*shape)
+        check(self.L.sgk_linstate_enqueue_decode_step(self.h, stream, layer, C.byref(sh), d_qkv.ptr, d_conv_weight.ptr,
+                                                      conv_kernel_dim, d_beta_input.ptr, d_gate_input.ptr,
+                                                      d_a_log.ptr, d_dt_bias.ptr, d_out.ptr))
+
     def encode_gated_delta_step(self, layer, shape, d_q, d_k, d_v, d_g, d_beta, d_out, stream=None):
         """gated_delta for one token (src/linear_attention.rs:896-991); shape = (H_k, H_v, d_k, d_v)."""
         sh = LinearShape(*shape)

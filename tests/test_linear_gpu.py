@@ -338,3 +338,54 @@ class _Off:
 
     def __init__(self, buf, offset):
         self.ptr = buf.ptr + offset
+
+
+@pytest.mark.parametrize("shape,kernel", [((2, 4, 128, 128), 4), ((16, 32, 128, 128), 4), ((1, 2, 128, 128), 2),
+                                          ((2, 2, 128, 128), 7)])
+@pytest.mark.parametrize("ssm_bf16", [False, True])
+def test_one_launch_decode_step_matches_the_cpu_order(state, shape, kernel, ssm_bf16):
+    """conv + SiLU + unit RMS norm + gates + gated delta of a token in ONE launch against the
+    composition of the oracle's pieces (src/linear_attention.rs:313-342), over several tokens so
+    that the history (shifted by whichever block of a key head arrives last) and the state carry
+    over: the history is bit-exact, output and state are inside the reference's bounds for its own
+    fused dispatches (1e-5 with an f32 state; 5e-4 / one bf16 step with a bf16 state)."""
+    hk, hv, dk, dv = shape
+    conv_dim, ssm_len = 2 * hk * dk + hv * dv, hv * dv * dk
+    w = sgo.fill_normal8(conv_dim * kernel, 61, 0) * np.float32(0.5)
+    a_log = sgo.fill_normal8(hv, 61, 1) * np.float32(0.3)
+    dt_bias = sgo.fill_normal8(hv, 61, 2) * np.float32(0.3)
+    hist = sgo.fill_normal8((kernel - 1) * conv_dim, 61, 3)
+    ssm = sgo.fill_normal8(ssm_len, 61, 4) * np.float32(0.1)
+    ls = sg.LinearAttentionState(state, 2, (kernel - 1) * conv_dim, ssm_len, ssm_bf16=ssm_bf16)
+    ls.write(1, hist, ssm)
+    if ssm_bf16:
+        ssm = sgo.bf16_round(ssm)
+    d_w, d_al, d_dt = state.upload(w), state.upload(a_log), state.upload(dt_bias)
+    d_out = state.alloc(4 * hv * dv)
+    for t in range(4):
+        qkv = sgo.fill_normal8(conv_dim, 62, 3 * t)
+        bi = sgo.fill_normal8(hv, 62, 3 * t + 1)
+        gi = sgo.fill_normal8(hv, 62, 3 * t + 2) + (np.float32(24.0) if t == 2 else np.float32(0.0))   # softplus's linear branch
+        st, want, hist, new_ssm, _ = sgo.linear_decode_step(qkv, w, kernel, hist, bi, gi, a_log, dt_bias, hk, hv, dk, dv, ssm)
+        assert st == 0
+        ls.encode_decode_step(1, shape, state.upload(qkv), d_w, kernel, state.upload(bi), state.upload(gi), d_al, d_dt, d_out)
+        state.sync()
+        got = d_out.download(count=hv * dv)
+        got_hist, got_ssm = ls.read(1)
+        assert np.array_equal(got_hist, hist)
+        if ssm_bf16:
+            assert np.all(np.abs(got - want) <= 5e-4)
+            step = np.maximum(2e-4, np.abs(new_ssm) * np.float32(2.0 ** -7))
+            assert np.all(np.abs(got_ssm - new_ssm) <= step)
+            ssm = got_ssm          # the stored state is what the next token starts from
+        else:
+            assert np.all(np.abs(got - want) <= 1e-5)
+            assert np.all(np.abs(got_ssm - new_ssm) <= 1e-5)
+            ssm = new_ssm
+    # layer 0 was never touched
+    h0, s0 = ls.read(0)
+    assert not h0.any() and not s0.any()
+    with pytest.raises(sg.InferError) as e:
+        ls.encode_decode_step(1, (hk, hv, 64, 128), state.upload(qkv), d_w, kernel, state.upload(bi), state.upload(gi), d_al, d_dt, d_out)
+    assert e.value.kind == "Config"
+    ls.close()

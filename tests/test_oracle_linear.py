@@ -141,3 +141,42 @@ def test_conv_step_is_the_causal_convolution_of_the_whole_sequence():
     np.testing.assert_array_equal(hist.reshape(kernel - 1, conv_dim), x[-(kernel - 1):])
     st, _, _ = sgo.depthwise_conv_step(x[0], w, kernel, np.zeros(5, np.float32))
     assert st == sgo.ERR_DIMENSION
+
+
+def test_decode_step_helpers_known_answers():
+    """silu's known values (src/activation.rs:62-69), key_scale, sigmoid, softplus's linear branch and
+    a unit RMS norm worked by hand: the pieces the one-launch decode step is checked against."""
+    out = sgo.silu(np.array([-1.0, 0.0, 1.0], np.float32))
+    assert abs(out[0] - -0.26894143) < 1e-6 and out[1] == 0.0 and abs(out[2] - 0.7310586) < 1e-6
+    assert sgo.key_scale(128, False) == np.float32(128.0) ** np.float32(-0.5)
+    assert abs(float(sgo.key_scale(128, True)) - 1.0 / 128.0) < 1e-9
+    assert abs(float(sgo.sigmoid(np.array([0.0], np.float32))[0]) - 0.5) < 1e-7
+    # softplus(25) = 25 (linear branch), softplus(0) = ln 2; decay = exp(-exp(a_log) * softplus)
+    g = sgo.compute_decay(np.array([25.0, 0.0], np.float32), np.array([0.0, 0.0], np.float32), np.array([0.0, 0.0], np.float32))
+    assert abs(float(g[0]) - np.exp(-25.0)) < 1e-12 and abs(float(g[1]) - 0.5) < 1e-6
+    x = np.array([3.0, 4.0, 0.0, 0.0], np.float32)          # mean square 6.25 -> rms 2.5
+    n = sgo.rms_norm_heads_unit(x, 1, 4, eps=0.0)
+    assert np.allclose(n, [1.2, 1.6, 0.0, 0.0], atol=1e-7)
+    two = sgo.rms_norm_heads_unit(np.concatenate([x, 2 * x]), 2, 4, eps=0.0)
+    assert np.allclose(two[:4], two[4:], atol=1e-7)          # a head's scale does not matter
+
+
+def test_decode_step_is_the_composition_of_its_pieces():
+    hk, hv, d = 2, 4, 128
+    conv_dim, kernel = 2 * hk * d + hv * d, 4
+    qkv = sgo.fill_normal8(conv_dim, 3, 0)
+    w = sgo.fill_normal8(conv_dim * kernel, 3, 1) * np.float32(0.5)
+    hist = sgo.fill_normal8((kernel - 1) * conv_dim, 3, 2)
+    ssm = sgo.fill_normal8(hv * d * d, 3, 3) * np.float32(0.1)
+    bi, gi = sgo.fill_normal8(hv, 3, 4), sgo.fill_normal8(hv, 3, 5)
+    a_log, dt = sgo.fill_normal8(hv, 3, 6) * np.float32(0.3), sgo.fill_normal8(hv, 3, 7) * np.float32(0.3)
+    st, out, new_hist, new_ssm, parts = sgo.linear_decode_step(qkv, w, kernel, hist, bi, gi, a_log, dt, hk, hv, d, d, ssm)
+    assert st == 0 and np.isfinite(out).all()
+    # the history slid by one token and q, k have unit RMS times their scales
+    assert np.array_equal(new_hist.reshape(kernel - 1, conv_dim)[-1], qkv)
+    assert np.array_equal(new_hist.reshape(kernel - 1, conv_dim)[:-1], hist.reshape(kernel - 1, conv_dim)[1:])
+    q = parts["q"].reshape(hk, d)
+    assert np.allclose(np.sqrt((q.astype(np.float64) ** 2).mean(axis=1)), 1.0 / 128.0, rtol=1e-4)
+    k = parts["k"].reshape(hk, d)
+    assert np.allclose(np.sqrt((k.astype(np.float64) ** 2).mean(axis=1)), 128.0 ** -0.5, rtol=1e-4)
+    assert ((parts["g"] > 0) & (parts["g"] < 1)).all() and ((parts["beta"] > 0) & (parts["beta"] < 1)).all()
