@@ -389,3 +389,64 @@ def test_one_launch_decode_step_matches_the_cpu_order(state, shape, kernel, ssm_
         ls.encode_decode_step(1, (hk, hv, 64, 128), state.upload(qkv), d_w, kernel, state.upload(bi), state.upload(gi), d_al, d_dt, d_out)
     assert e.value.kind == "Config"
     ls.close()
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_token_chain_of_one_launch_decode_steps_equals_plain_enqueues(state, graph):
+    """The one-launch decode steps of consecutive layers as a token chain: each launch reads its own
+    layer's state rows, taps and conv history before it waits for the launch before it. Outputs,
+    states and histories (shifted by whichever block arrives last) equal the plain enqueues bit for
+    bit over several tokens, in stream mode and as a CUDA graph."""
+    import torch
+    shape = (2, 4, 128, 128)
+    hk, hv, dk, dv = shape
+    layers, kernel, tokens = 4, 4, 3
+    conv_dim, ssm_len = 2 * hk * dk + hv * dv, hv * dv * dk
+    w = [sgo.fill_normal8(conv_dim * kernel, 51, layer) * np.float32(0.5) for layer in range(layers)]
+    results = []
+    for chained in (False, True):
+        ls = sg.LinearAttentionState(state, layers, (kernel - 1) * conv_dim, ssm_len)
+        for layer in range(layers):
+            ls.write(layer, sgo.fill_normal8((kernel - 1) * conv_dim, 52, layer),
+                     sgo.fill_normal8(ssm_len, 53, layer) * np.float32(0.1))
+        d_w = [state.upload(x) for x in w]
+        d_x = state.alloc(4 * conv_dim * layers)
+        d_gates = [state.alloc(4 * hv * layers) for _ in range(4)]      # beta_input, gate_input, a_log, dt_bias
+        d_y = state.alloc(4 * hv * dv * layers)
+        stream = torch.cuda.Stream()
+
+        def token():
+            if chained:
+                state.chain_begin(stream.cuda_stream)
+            for layer in range(layers):
+                ls.encode_decode_step(layer, shape, _Off(d_x, 4 * conv_dim * layer), d_w[layer], kernel,
+                                      *[_Off(b, 4 * hv * layer) for b in d_gates], _Off(d_y, 4 * hv * dv * layer),
+                                      stream=stream.cuda_stream)
+            if chained:
+                state.chain_end()
+
+        g = None
+        if graph:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                token()
+        got = []
+        for t in range(tokens):
+            d_x.upload(sgo.fill_normal8(conv_dim * layers, 54, t))
+            for i, b in enumerate(d_gates):
+                b.upload(sgo.fill_normal8(hv * layers, 55, 4 * t + i) * np.float32(0.5))
+            state.sync()
+            if g is not None:
+                with torch.cuda.stream(stream):
+                    g.replay()
+            else:
+                token()
+            stream.synchronize()
+            got.append(d_y.download(count=hv * dv * layers).copy())
+        results.append((got, [ls.read(layer) for layer in range(layers)]))
+        ls.close()
+    plain, chain = results
+    for y0, y1 in zip(plain[0], chain[0]):
+        assert np.isfinite(y0).all() and np.array_equal(y0, y1)
+    for (h0, s0), (h1, s1) in zip(plain[1], chain[1]):
+        assert np.array_equal(h0, h1) and np.array_equal(s0, s1)
