@@ -16,10 +16,12 @@
  *     methods (src/decode_resident/attention.rs:950-1038); host-pointer calls
  *     are synchronous;
  *   - one stream per pool: the calls that use a pool's sequences (append, attention, restore,
- *     release, destroy) are ordered by the stream they are enqueued on; a caller that spreads them
- *     over several streams orders them itself (events) before a call that frees, shares or
- *     replaces pages of a sequence (sgk_prefix_restore, sgk_seq_release_before, sgk_seq_destroy,
- *     sgk_kv_truncate followed by appends): the library does not track other streams;
+ *     release, destroy) are ordered by the stream they are enqueued on. The library remembers the
+ *     caller stream used last: sgk_prefix_restore makes its own stream wait for what was enqueued
+ *     there, sgk_seq_release_before and sgk_seq_destroy wait for it on the host before pages go
+ *     back to the pool. A caller that spreads the calls over MORE streams orders them itself
+ *     (events) before a call that frees, shares or replaces pages of a sequence (the three above,
+ *     sgk_kv_truncate followed by appends): the library does not track further streams;
  *   - pointers named d_* are device pointers, everything else is host memory;
  *   - there is no CPU fallback: without a CUDA device sgk_state_create fails.
  */

@@ -67,6 +67,7 @@ void sgk_state_destroy(sgk_state* st) {
   if (st->d_status) cudaFree(st->d_status);
   if (st->d_lm_ws) cudaFree(st->d_lm_ws);
   if (st->d_rope_table) cudaFree(st->d_rope_table);
+  if (st->order_event) cudaEventDestroy(st->order_event);
   if (st->stream) cudaStreamDestroy(st->stream);
   delete st;
 }
@@ -257,7 +258,10 @@ void sgk_seq_destroy(sgk_seq* s) {
   if (!s) return;
   Pool* p = s->pool;
   if (!p->host_only()) {
+    // the pages go back to the pool: wait for whatever was enqueued on the state's stream and on
+    // the caller stream used last
     cudaSetDevice(p->st->device);
+    p->st->order_after_last_caller(p->st->stream);
     cudaStreamSynchronize(p->st->stream);
   }
   s->views.clear();
@@ -293,7 +297,10 @@ int32_t sgk_seq_block_table(const sgk_seq* s, int32_t* pages_out, int64_t cap, i
 int32_t sgk_seq_release_before(sgk_seq* s, int64_t row) {
   if (!s) return fail(SGK_ERR_BACKEND, "null sequence");
   if (row < 0) return fail(SGK_ERR_DIMENSION, "negative row");
-  if (!s->pool->host_only()) SGK_CUDA(cudaStreamSynchronize(s->pool->st->stream));
+  if (!s->pool->host_only()) {
+    SGK_CUDA(s->pool->st->order_after_last_caller(s->pool->st->stream));
+    SGK_CUDA(cudaStreamSynchronize(s->pool->st->stream));
+  }
   return s->release_before(row);
 }
 
@@ -1757,10 +1764,17 @@ int32_t sgk_prefix_restore(sgk_prefix* pc, uint64_t entry, sgk_seq* seq, sgk_lin
       return fail(SGK_ERR_MEMORY_GUARD, "page pool exhausted: need %zu pages, %zu free", src.size(),
                   pool->free_list.size() + own);
   }
-  cudaStream_t cs = pool->host_only() ? nullptr : pool->st->pick(stream);
-  // Everything below is enqueued on `cs` in order: earlier launches on it still read the old
-  // table and pages, later ones the restored ones. (Launches on OTHER streams that use this
-  // sequence must have finished: see the stream rule in sgk.h.)
+  // Everything below is enqueued on the call's stream in order: earlier launches on it still read
+  // the old table and pages, later ones the restored ones. When the caller stream used last is
+  // another one, the call's stream first waits for what was enqueued there (no host wait).
+  // (Launches on further streams that use this sequence must have finished: the stream rule.)
+  cudaStream_t cs = nullptr;
+  if (!pool->host_only()) {
+    State* st = pool->st;
+    cs = stream ? static_cast<cudaStream_t>(stream) : st->stream;
+    SGK_CUDA(st->order_after_last_caller(cs));
+    cs = st->pick(stream);
+  }
   seq->release_all();
   if (mode == 1) {
     for (int32_t p : src) pool->retain(p);

@@ -85,7 +85,18 @@ struct State {
   bool chain_follows(cudaStream_t s) const { return chain_member(s) && chain_mark == launches; }
   void chain_note() { chain_mark = launches; }   // call right after counting a member's launch
   void chain_break() { chain_mark = -1; }
-  cudaStream_t pick(void* s) const { return s ? static_cast<cudaStream_t>(s) : stream; }
+  // The caller's stream used last (the library's own stream when none was given). A call that frees,
+  // shares or replaces pages first orders itself after what was enqueued there.
+  mutable cudaStream_t last_caller = nullptr;
+  cudaEvent_t order_event = nullptr;
+  cudaStream_t pick(void* s) const {
+    if (s) last_caller = static_cast<cudaStream_t>(s);
+    return s ? static_cast<cudaStream_t>(s) : stream;
+  }
+  // Makes `cs` wait for everything enqueued so far on the caller stream used last (no host wait).
+  // Nothing to do when that is `cs` itself; skipped while either stream is being captured (a capture
+  // cannot wait for work outside it, and frees no pages).
+  cudaError_t order_after_last_caller(cudaStream_t cs);
 };
 
 struct Pool {

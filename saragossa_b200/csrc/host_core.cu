@@ -686,6 +686,23 @@ int Step::enqueue_range(cudaStream_t stream, size_t l0, size_t l1, const float* 
 }
 
 // ---------------------------------------------------------------- LinState
+cudaError_t State::order_after_last_caller(cudaStream_t cs) {
+  cudaStream_t prev = last_caller;
+  if (prev == nullptr || prev == cs) return cudaSuccess;
+  cudaStreamCaptureStatus a = cudaStreamCaptureStatusNone, b = cudaStreamCaptureStatusNone;
+  cudaError_t e = cudaStreamIsCapturing(prev, &a);
+  if (e == cudaSuccess) e = cudaStreamIsCapturing(cs, &b);
+  if (e != cudaSuccess) return e;
+  if (a != cudaStreamCaptureStatusNone || b != cudaStreamCaptureStatusNone) return cudaSuccess;
+  if (order_event == nullptr) {
+    e = cudaEventCreateWithFlags(&order_event, cudaEventDisableTiming);
+    if (e != cudaSuccess) return e;
+  }
+  e = cudaEventRecord(order_event, prev);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(cs, order_event, 0);
+  return e;
+}
+
 LinState::~LinState() {
   if (d_base) cudaFree(d_base);
   if (d_head_counters) cudaFree(d_head_counters);

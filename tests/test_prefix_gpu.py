@@ -301,3 +301,80 @@ def test_decoder_prefix_cache_restores_rows_and_never_aliases_them(state):
     cache.close()
     assert pool.free_pages == 32
     pool.close()
+
+
+def _busy(stream, torch):
+    """Keeps `stream` busy for tens of milliseconds, so that what is enqueued behind it has not run
+    when the host goes on."""
+    with torch.cuda.stream(stream):
+        x = torch.ones((4096, 4096), device="cuda", dtype=torch.float32)
+        for _ in range(60):
+            x = (x @ x) * 1e-4
+    return x
+
+
+def test_destroy_and_restore_wait_for_the_caller_stream_used_last(state):
+    """An attention launch sits behind a long computation on a caller's stream. The sequence it
+    reads is then (a) destroyed, with its pages handed to another sequence that overwrites them
+    through the state's own stream, and (b) in a second round, overwritten by a prefix restore on
+    the state's own stream. Both calls order themselves after the caller stream used last, so the
+    waiting launch still sees the rows it was enqueued for."""
+    import torch
+    n, block = 64, 32
+    pool = state.pool(1, KV_HEADS, HD, sg.KV_BF16, num_pages=8, max_seqs=4, max_seq_tokens=64)
+    q = sgo.fill_normal8(Q_HEADS * HD, 31, 0)
+    d_q, d_out = state.upload(q), state.alloc(4 * Q_HEADS * HD)
+    side = torch.cuda.Stream()
+
+    def reference(k, v):
+        ref = sgo.ResidentKv(n, Q_HEADS, KV_HEADS, HD, sg.KV_BF16)
+        ref.seed(k, v, n)
+        return ref.attention(q)[1]
+
+    # (a) destroy
+    a = pool.sequence(64)
+    kv = a.layer(0, Q_HEADS)
+    ka, va = _rows(n, 32, 0), _rows(n, 32, 1)
+    kv.seed(ka, va, n)
+    keep = _busy(side, torch)
+    kv.encode_attention_decode_windowed(d_q, d_out, stream=side.cuda_stream)
+    a.close()                                     # must wait for the side stream
+    b = pool.sequence(64)
+    b2 = pool.sequence(64)                        # the pool has 8 pages: a's four are among these eight
+    for s_, seed in ((b, 33), (b2, 34)):
+        s_.layer(0, Q_HEADS).seed(_rows(n, seed, 0), _rows(n, seed, 1), n)
+    side.synchronize()
+    got = d_out.download(count=Q_HEADS * HD)
+    want = reference(ka, va)
+    assert np.all(np.abs(got - want) <= 2e-2 * np.abs(want) + 1e-3)
+    b2.close()
+
+    # (b) restore on the state's own stream while a launch on the side stream still has to read the sequence
+    cache = sg.BlockAwarePrefixCache(block, 16, pool=pool)
+    root = sg.BlockHash.for_session("s")
+    toks = list(range(n))
+    for i, h in enumerate(_chain(root, toks, block)):
+        assert cache.insert(root, h, (i + 1) * block, seq=b)
+    c = pool.sequence(64)
+    kc, vc = _rows(n, 35, 0), _rows(n, 35, 1)
+    kvc = c.layer(0, Q_HEADS)
+    kvc.seed(kc, vc, n)
+    keep2 = _busy(side, torch)
+    kvc.encode_attention_decode_windowed(d_q, d_out, stream=side.cuda_stream)
+    hit = cache.match_prefix(root, toks)
+    assert hit.tokens == n
+    cache.restore(hit, c)                         # own stream: ordered after the side stream
+    side.synchronize()
+    state.sync()
+    got = d_out.download(count=Q_HEADS * HD)
+    want = reference(kc, vc)
+    assert np.all(np.abs(got - want) <= 2e-2 * np.abs(want) + 1e-3)
+    # and the sequence now holds the restored rows
+    gk, _ = kvc.gather_rows_f32()
+    bk, _ = b.layer(0, Q_HEADS).gather_rows_f32()
+    assert np.array_equal(gk, bk)
+    del keep, keep2
+    c.close()
+    b.close()
+    cache.close()
+    pool.close()
