@@ -691,7 +691,13 @@ cudaError_t State::order_after_last_caller(cudaStream_t cs) {
   if (prev == nullptr || prev == cs) return cudaSuccess;
   cudaStreamCaptureStatus a = cudaStreamCaptureStatusNone, b = cudaStreamCaptureStatusNone;
   cudaError_t e = cudaStreamIsCapturing(prev, &a);
-  if (e == cudaSuccess) e = cudaStreamIsCapturing(cs, &b);
+  if (e != cudaSuccess) {
+    // the caller has destroyed that stream since: its work is done, nothing to order after
+    cudaGetLastError();
+    last_caller = nullptr;
+    return cudaSuccess;
+  }
+  e = cudaStreamIsCapturing(cs, &b);
   if (e != cudaSuccess) return e;
   if (a != cudaStreamCaptureStatusNone || b != cudaStreamCaptureStatusNone) return cudaSuccess;
   if (order_event == nullptr) {
