@@ -21,7 +21,8 @@
  *     there, sgk_seq_release_before and sgk_seq_destroy wait for it on the host before pages go
  *     back to the pool. A caller that spreads the calls over MORE streams orders them itself
  *     (events) before a call that frees, shares or replaces pages of a sequence (the three above,
- *     sgk_kv_truncate followed by appends): the library does not track further streams;
+ *     sgk_kv_truncate followed by appends): the library does not track further streams. A stream
+ *     given to the library stays alive until another one has been given or the state is destroyed;
  *   - pointers named d_* are device pointers, everything else is host memory;
  *   - there is no CPU fallback: without a CUDA device sgk_state_create fails.
  */
