@@ -580,7 +580,9 @@ def affine_dequantize(packed, scales_bf16, biases_bf16, bits, group_size, rows, 
     per_word = 32 // bits
     shifts = (np.arange(per_word, dtype=np.uint32) * bits)[None, None, :]
     codes = ((packed[:, :, None] >> shifts) & np.uint32((1 << bits) - 1)).reshape(rows, cols).astype(np.float32)
-    to_f32 = lambda b: (np.ascontiguousarray(b, np.uint16).astype(np.uint32) << 16).view(np.float32)
+    # scales and biases as bf16 bit patterns (the Metal buffers), or as f32 (the reference's CPU tensors)
+    to_f32 = lambda b: (_f32(b) if np.asarray(b).dtype == np.float32
+                        else (np.ascontiguousarray(b, np.uint16).astype(np.uint32) << 16).view(np.float32))
     scale = np.repeat(to_f32(scales_bf16).reshape(rows, cols // group_size), group_size, axis=1)
     bias = np.repeat(to_f32(biases_bf16).reshape(rows, cols // group_size), group_size, axis=1)
     return (codes * scale).astype(np.float32) + bias

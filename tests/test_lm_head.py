@@ -391,6 +391,22 @@ def test_oracle_affine_dequantize_known_answers():
                                                 4, 32, 2, 32), codes.astype(np.float32))
 
 
+def test_oracle_affine_dequantize_replays_the_reference_known_answers():
+    """The reference's own dequantisation cases (src/quantization.rs:386-418): an 8-bit weight of two
+    rows in groups of 2 with scale 1/255, and a 4-bit row in groups of 4 with scales (1/15, 2) and
+    biases (0, -1); words packed LSB first (pack_lanes, :538-543); tolerance 1e-6 (:560-565)."""
+    pack = lambda values, bits: np.uint32(sum(int(v) << (i * bits) for i, v in enumerate(values)))
+    packed = np.array([[pack([255, 0, 0, 0], 8)], [pack([0, 255, 0, 0], 8)]], np.uint32)
+    scales = np.full((2, 2), 1.0 / 255.0, np.float32)
+    dense = sgo.affine_dequantize(packed, scales, np.zeros((2, 2), np.float32), 8, 2, 2, 4)
+    assert np.all(np.abs(dense.ravel() - np.array([1, 0, 0, 0, 0, 1, 0, 0], np.float32)) <= 1e-6)
+    packed4 = np.array([[pack([15, 0, 7, 8, 1, 2, 3, 4], 4)]], np.uint32)
+    dense4 = sgo.affine_dequantize(packed4, np.array([[1.0 / 15.0, 2.0]], np.float32), np.array([[0.0, -1.0]], np.float32),
+                                   4, 4, 1, 8)
+    want = np.array([1.0, 0.0, 7.0 / 15.0, 8.0 / 15.0, 1.0, 3.0, 5.0, 7.0], np.float32)
+    assert np.all(np.abs(dense4.ravel() - want) <= 1e-6)
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("bits,group", [(4, 64), (8, 64), (4, 128), (8, 128)])
 @pytest.mark.parametrize("rows", [1, 3, 8])
