@@ -219,6 +219,17 @@ class DecodeResidentState {
                                            static_cast<int64_t>(vocab), static_cast<int32_t>(hidden), d_x,
                                            static_cast<int32_t>(n_rows), index_offset, d_index_out, d_value_out));
   }
+  // encode_affine_argmax_qmv_fast (src/metal_backend/lm_head.rs:934-990): the same epilogue over an
+  // affine-quantised weight (u32 code words, bf16 scales and biases per group of 64 or 128 inputs).
+  Result<Unit> encode_lm_head_argmax_affine(void* stream, const uint32_t* d_packed, const uint16_t* d_scales,
+                                            const uint16_t* d_biases, size_t bits, size_t group_size, size_t vocab,
+                                            size_t hidden, const float* d_x, size_t n_rows, int32_t* d_index_out,
+                                            int32_t index_offset = 0, float* d_value_out = nullptr) {
+    sgk_affine_weight w{d_packed, d_scales, d_biases, static_cast<int32_t>(bits), static_cast<int32_t>(group_size)};
+    return unit(sgk_lm_head_enqueue_argmax_affine(h_, stream, &w, static_cast<int64_t>(vocab),
+                                                  static_cast<int32_t>(hidden), d_x, static_cast<int32_t>(n_rows),
+                                                  index_offset, d_index_out, d_value_out));
+  }
   sgk_state* handle() const { return h_; }
 
  private:
@@ -332,6 +343,17 @@ class LinearAttentionState {
     return unit(sgk_linstate_enqueue_gated_delta_step(h_, stream, static_cast<int32_t>(layer), &shape, d_q, d_k, d_v, d_g,
                                                       d_beta, d_out));
   }
+  // The resident decode of a recurrent layer between its projections in one launch
+  // (src/linear_attention.rs:313-342; linear_attn_conv_norm_gates_k4_dk128_f32 + linear_attn_gated_delta_dk128_tg4_f32).
+  Result<Unit> encode_decode_step(void* stream, size_t layer, size_t num_key_heads, size_t num_value_heads,
+                                  const float* d_qkv, const float* d_conv_weight, size_t conv_kernel_dim,
+                                  const float* d_beta_input, const float* d_gate_input, const float* d_a_log,
+                                  const float* d_dt_bias, float* d_out) {
+    sgk_linear_shape shape{static_cast<int32_t>(num_key_heads), static_cast<int32_t>(num_value_heads), 128, 128};
+    return unit(sgk_linstate_enqueue_decode_step(h_, stream, static_cast<int32_t>(layer), &shape, d_qkv, d_conv_weight,
+                                                 static_cast<int32_t>(conv_kernel_dim), d_beta_input, d_gate_input,
+                                                 d_a_log, d_dt_bias, d_out));
+  }
   sgk_linstate* handle() const { return h_; }
 
  private:
@@ -392,6 +414,14 @@ class BlockAwarePrefixCache {
     sgk_prefix_insert(h_, session.bytes, hash.bytes, static_cast<int64_t>(tokens), nullptr, nullptr, nullptr, &inserted);
     return inserted != 0;
   }
+  // prefill_prompt_state's loop over the full blocks of a prompt (src/serve/state.rs:596-604) in one call;
+  // returns the number of blocks inserted.
+  size_t insert_chain(const BlockHash& root, const std::vector<uint64_t>& tokens, size_t from_tokens = 0) {
+    int32_t inserted = 0;
+    sgk_prefix_insert_chain(h_, root.bytes, tokens.data(), tokens.size(), static_cast<int64_t>(from_tokens), nullptr,
+                            nullptr, &inserted, nullptr);
+    return static_cast<size_t>(inserted);
+  }
   bool evict_lru_block() {
     int32_t ev = 0;
     sgk_prefix_evict_lru(h_, &ev, nullptr);
@@ -410,6 +440,33 @@ class BlockAwarePrefixCache {
 
  private:
   sgk_prefix* h_ = nullptr;
+};
+
+// The decoder's own prefix cache (prefix_cache_get / prefix_cache_put, src/decoder/generation.rs:2998-3139),
+// bookkeeping form (no pool): at most `capacity` prompts, the most recent at the front; get moves the entry
+// with the longest token prefix of the prompt to the front and returns its length (0: miss).
+class PrefixCache {
+ public:
+  explicit PrefixCache(size_t capacity) { sgk_dprefix_create(nullptr, static_cast<int64_t>(capacity), &h_); }
+  PrefixCache(const PrefixCache&) = delete;
+  PrefixCache& operator=(const PrefixCache&) = delete;
+  ~PrefixCache() { sgk_dprefix_destroy(h_); }
+  size_t get(const std::vector<uint64_t>& prompt) {
+    int64_t cached = 0;
+    sgk_dprefix_get(h_, prompt.data(), prompt.size(), nullptr, nullptr, nullptr, &cached);
+    return static_cast<size_t>(cached);
+  }
+  void put(const std::vector<uint64_t>& tokens) { sgk_dprefix_put(h_, tokens.data(), tokens.size(), nullptr, nullptr, nullptr); }
+  size_t len() const { return static_cast<size_t>(sgk_dprefix_len(h_)); }
+  std::vector<uint64_t> entry_tokens(size_t index) const {  // front = 0; empty past the end
+    std::vector<uint64_t> out(4096);
+    int64_t n = sgk_dprefix_entry_tokens(h_, static_cast<int64_t>(index), out.data(), static_cast<int64_t>(out.size()));
+    out.resize(n > 0 ? static_cast<size_t>(n) : 0);
+    return out;
+  }
+
+ private:
+  sgk_dprefix* h_ = nullptr;
 };
 
 }  // namespace saragossa

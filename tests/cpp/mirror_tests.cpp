@@ -68,6 +68,54 @@ static void hashes_and_longest_chain() {
   CHECK(!cache.match_prefix(BlockHash::for_session("agent-b"), {1, 2, 3, 4}).first);
 }
 
+// prefill_prompt_state's block loop (src/serve/state.rs:596-604): all full blocks of a prompt in one call
+// leave the cache as the block-by-block inserts do, and blocks before the matched prefix are not inserted again.
+static void chain_insert_equals_block_by_block() {
+  const std::vector<uint64_t> prompt = {5, 6, 7, 8, 9, 10, 11};     // three full blocks of 2 and a tail
+  BlockHash root = BlockHash::for_session("s");
+  BlockAwarePrefixCache one(2, 8), all(2, 8);
+  BlockHash prev = root;
+  for (size_t b = 0; b < 3; ++b) {
+    prev = prev.chain({prompt[2 * b], prompt[2 * b + 1]});
+    CHECK(one.insert(root, prev, 2 * (b + 1)));
+  }
+  CHECK(all.insert_chain(root, prompt) == 3);
+  auto h1 = one.entry_hashes(), h2 = all.entry_hashes();
+  CHECK(h1.size() == 3 && h2.size() == 3);
+  for (size_t i = 0; i < h1.size() && i < h2.size(); ++i) CHECK(h1[i] == h2[i]);
+  auto hit = all.match_prefix(root, prompt);
+  CHECK(hit.first && hit.second.tokens == 6 && hit.second.hash == prev);
+  // a longer prompt of the same conversation: only the new blocks
+  std::vector<uint64_t> longer = prompt;
+  longer.insert(longer.end(), {12, 13, 14});
+  CHECK(all.insert_chain(root, longer, 6) == 2);
+  CHECK(all.match_prefix(root, longer).second.tokens == 10);
+}
+
+// prefix_cache_selects_longest_append_prefix (src/decoder/tests.rs:428-465) through the cache itself, and
+// the bookkeeping of prefix_cache_get / prefix_cache_put (src/decoder/generation.rs:2998-3024,3105-3139).
+static void decoder_prefix_cache_keeps_the_reference_order() {
+  PrefixCache cache(4);
+  cache.put({1, 2});
+  cache.put({1, 2, 3});
+  cache.put({1});
+  CHECK(cache.len() == 3);
+  CHECK(cache.get({1, 2, 3, 4}) == 3);                       // entry [1,2,3] wins and moves to the front
+  CHECK(cache.entry_tokens(0) == std::vector<uint64_t>({1, 2, 3}));
+  CHECK(cache.get({1, 9}) == 1);
+  CHECK(cache.entry_tokens(0) == std::vector<uint64_t>({1}));
+  CHECK(cache.get({9}) == 0);
+  cache.put({1, 2, 3});                                      // same tokens: replaced, not doubled
+  CHECK(cache.len() == 3 && cache.entry_tokens(0) == std::vector<uint64_t>({1, 2, 3}));
+  cache.put({4});
+  cache.put({5});                                            // beyond the capacity the rear entry goes
+  CHECK(cache.len() == 4);
+  CHECK(cache.get({1, 2, 7}) == 1);                          // [1,2] fell off the rear; [1] is the longest left
+  PrefixCache none(0);
+  none.put({1});
+  CHECK(none.len() == 0 && none.get({1}) == 0);
+}
+
 // src/decode_resident/tests.rs:380-430
 static void kv_seed_then_append_matches_cpu(DecodeResidentState& state) {
   const size_t q_heads = 16, kv_heads = 2, head_dim = 256, kv_dim = kv_heads * head_dim, capacity = 6;
@@ -290,6 +338,8 @@ int main(int argc, char** argv) {
   prefix_cache_evicts_lru_block();
   reduced_session_cap_evicts_only_that_session_first();
   hashes_and_longest_chain();
+  chain_insert_equals_block_by_block();
+  decoder_prefix_cache_keeps_the_reference_order();
   if (gpu) {
     auto made = DecodeResidentState::create(0);
     CHECK(made.ok);
