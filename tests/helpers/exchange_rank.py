@@ -97,6 +97,25 @@ def main(rank, n, d):
         for sq in seqs:
             sq.close()
         pool.close()
+    # ---- a peer that stops joining: the last rank skips one exchange (it stays alive, its rows and
+    # flags stay mapped); the others' wait for its flag runs out on the device after a second or
+    # so, the kernel reports through the status word and returns, and the context stays usable.
+    # Nothing faults and nothing hangs: the failure is made on the host.
+    if rank != n - 1:
+        off = 0
+        peer_rows = [0 if p == rank else peers[p].ptr + 4 * off for p in range(n)]
+        t0 = time.time()
+        ex.enqueue(rows.ptr + 4 * off, peer_rows, rank * sl, sl)
+        st.sync()
+        waited = time.time() - t0
+        status = st.device_status()                      # reads and clears
+        assert status == 6, status                      # SGK_ERR_TIMEOUT: a bounded device-side wait expired
+        assert waited < 30.0, waited
+        assert st.device_status() == 0
+        probe = st.alloc(4 * 64)
+        probe.upload(np.arange(64, dtype=np.float32))
+        assert np.array_equal(probe.download(np.float32, 64), np.arange(64, dtype=np.float32))
+        print(f"TIMEOUT-REPORTED after {waited:.2f} s", flush=True)
     # everybody done before anybody unmaps
     put(os.path.join(d, f"done{rank}"), b"1")
     for p in range(n):

@@ -1,6 +1,7 @@
 """The exchange of output slices between GPUs over peer memory (sgk_peer_*, sgk_exchange_*): two
 processes, one per GPU, each stores its slice into the other's rows and waits for the other's flag.
-Needs two GPUs; skipped on one. The waits are bounded on the device and on the host."""
+Needs two GPUs; skipped on one. The waits are bounded on the device and on the host; the last
+phase makes one of them run out (a peer that stays alive but stops joining) and checks the report."""
 import os
 import subprocess
 import sys
@@ -30,6 +31,8 @@ def test_two_ranks_exchange_slices_over_peer_memory(tmp_path):
             outs.append(p.communicate())
     for p, (out, err) in zip(procs, outs):
         assert p.returncode == 0 and "OK" in out, err[-2000:]
+    # the rank whose peer stopped joining saw its bounded wait run out and went on
+    assert "TIMEOUT-REPORTED" in outs[0][0] and "TIMEOUT-REPORTED" not in outs[1][0]
 
 
 def test_exchange_rejects_bad_arguments():
