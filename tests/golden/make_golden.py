@@ -37,6 +37,42 @@ def attention_case(name, q_heads, kv_heads, hd, dtype, rows, ws, seed):
     return {"out": out, "stored_k_row0": ref.keys()[0], "stored_v_last": ref.values()[-1]}
 
 
+def decode_step_inputs(seed):
+    hk, hv, d, kernel = 2, 4, 128, 4
+    conv_dim = 2 * hk * d + hv * d
+    f = lambda n, stream, scale=1.0: sgo.fill_normal8(n, seed, stream) * np.float32(scale)
+    return {"qkv": f(conv_dim, 0), "w": f(conv_dim * kernel, 1, 0.5), "hist": f((kernel - 1) * conv_dim, 2),
+            "ssm": f(hv * d * d, 3, 0.1), "beta_in": f(hv, 4), "gate_in": f(hv, 5), "a_log": f(hv, 6, 0.3),
+            "dt_bias": f(hv, 7, 0.3), "shape": (hk, hv, d, d), "kernel": kernel, "conv_dim": conv_dim}
+
+
+def decode_step_case(seed):
+    i = decode_step_inputs(seed)
+    hk, hv, dk, dv = i["shape"]
+    st, out, hist, ssm, parts = sgo.linear_decode_step(i["qkv"], i["w"], i["kernel"], i["hist"], i["beta_in"], i["gate_in"],
+                                                       i["a_log"], i["dt_bias"], hk, hv, dk, dv, i["ssm"])
+    assert st == sgo.OK
+    return {"y": out, "hist_last": hist[-i["conv_dim"]:], "ssm_head": ssm[:256],
+            "ssm_checksum": np.array([ssm.astype(np.float64).sum()]), "q": parts["q"].astype(np.float32),
+            "g": parts["g"], "beta": parts["beta"]}
+
+
+AFFINE_VOCAB, AFFINE_HIDDEN = 2051, 512
+
+
+def affine_case(seed, bits):
+    """Codes, bf16 scales and biases of a [2051][512] weight in groups of 64 and one activation row, all from
+    the integer-exact generator."""
+    n, groups = AFFINE_VOCAB * AFFINE_HIDDEN, AFFINE_VOCAB * (AFFINE_HIDDEN // 64)
+    top = (1 << bits) - 1
+    raw = sgo.fill_normal8(n, seed + bits, 0)
+    codes = np.clip(np.floor(raw * np.float32(top / 6.0) + np.float32(top / 2.0)), 0, top).astype(np.uint32)
+    scales = sgo.f32_to_bf16_bits((np.float32(1.0) + np.abs(sgo.fill_normal8(groups, seed + bits, 1))) * np.float32(0.02 / (top + 1)))
+    biases = sgo.f32_to_bf16_bits(sgo.fill_normal8(groups, seed + bits, 2) * np.float32(0.01))
+    x = sgo.fill_normal8(AFFINE_HIDDEN, seed, 9)
+    return sgo.affine_pack(codes.reshape(AFFINE_VOCAB, AFFINE_HIDDEN), bits), scales, biases, x
+
+
 def main():
     meta = {"generator": "oracle.sgo.fill_normal8(n, seed, stream)", "cases": {}}
     arrays = {}
@@ -81,6 +117,24 @@ def main():
     arrays["gated_delta.y"], arrays["gated_delta.ssm_checksum"] = y, np.array([new_ssm.astype(np.float64).sum()])
     arrays["gated_delta.ssm_head"] = new_ssm[:256]
     meta["cases"]["gated_delta"] = {"shape": [hk, hv, dk, dv], "seed": 202}
+
+    # the whole decode step of a recurrent layer (conv, SiLU, unit norms, gates, gated delta)
+    res = decode_step_case(203)
+    for key, val in res.items():
+        arrays[f"decode_step.{key}"] = val
+    meta["cases"]["decode_step"] = {"shape": [2, 4, 128, 128], "kernel": 4, "seed": 203}
+
+    # greedy epilogue over an affine-quantised weight: the winning row and its logit
+    for bits in (8, 4):
+        packed, scales, biases, x = affine_case(204, bits)
+        w = sgo.affine_dequantize(packed, scales, biases, bits, 64, AFFINE_VOCAB, AFFINE_HIDDEN)
+        logits = w.astype(np.float64) @ x.astype(np.float64)
+        st, idx, _ = sgo.lm_head_argmax(w, x)
+        assert st == sgo.OK and idx == int(np.argmax(logits))
+        arrays[f"affine_u{bits}.index"] = np.array([idx], np.int64)
+        arrays[f"affine_u{bits}.logit"] = np.array([logits[idx]], np.float64)
+        arrays[f"affine_u{bits}.row_head"] = w[idx, :64]
+    meta["cases"]["affine_lm_head"] = {"vocab": AFFINE_VOCAB, "hidden": AFFINE_HIDDEN, "group": 64, "seed": 204}
 
     # hash chain and the eviction order of a fixed operation trace (src/serve/cache.rs)
     root = sgo.hash_for_session("golden-session")

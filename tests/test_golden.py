@@ -4,6 +4,7 @@ hashing / eviction bookkeeping must give the same digests and the same order; on
 path is compared with the files themselves, without running the oracle."""
 import json
 import os
+import sys
 
 import numpy as np
 import pytest
@@ -12,6 +13,8 @@ import saragossa_b200 as sg
 from oracle import sgo
 
 HERE = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+sys.path.insert(0, HERE)
+import make_golden  # noqa: E402  (the generator of the fixtures: its input builders are reused here)
 META = json.load(open(os.path.join(HERE, "kv_path_golden.json")))["cases"]
 GOLD = np.load(os.path.join(HERE, "kv_path_golden.npz"))
 ATTN = [n for n in META if n.startswith("attn_")]
@@ -142,3 +145,45 @@ def test_cuda_quantiser_rope_and_recurrence_match_fixtures(state):
     assert np.abs(new_ssm[:256] - GOLD["gated_delta.ssm_head"]).max() <= 1e-5
     assert abs(float(new_ssm.astype(np.float64).sum()) - float(GOLD["gated_delta.ssm_checksum"][0])) <= 1e-2
     ls.close()
+
+
+# ---- the decode step of a recurrent layer and the affine-quantised greedy epilogue ------------
+def test_oracle_reproduces_decode_step_and_affine_fixtures():
+    res = make_golden.decode_step_case(META["decode_step"]["seed"])
+    for key, val in res.items():
+        np.testing.assert_array_equal(val, GOLD[f"decode_step.{key}"])
+    c = META["affine_lm_head"]
+    for bits in (8, 4):
+        packed, scales, biases, x = make_golden.affine_case(c["seed"], bits)
+        w = sgo.affine_dequantize(packed, scales, biases, bits, c["group"], c["vocab"], c["hidden"])
+        st, idx, _ = sgo.lm_head_argmax(w, x)
+        assert st == sgo.OK and idx == int(GOLD[f"affine_u{bits}.index"][0])
+        np.testing.assert_array_equal(w[idx, :64], GOLD[f"affine_u{bits}.row_head"])
+
+
+@pytest.mark.gpu
+def test_cuda_decode_step_and_affine_epilogue_match_fixtures(state):
+    i = make_golden.decode_step_inputs(META["decode_step"]["seed"])
+    hk, hv, dk, dv = i["shape"]
+    ls = sg.LinearAttentionState(state, 1, (i["kernel"] - 1) * i["conv_dim"], hv * dv * dk)
+    ls.write(0, i["hist"], i["ssm"])
+    d_y = state.alloc(4 * hv * dv)
+    ls.encode_decode_step(0, i["shape"], state.upload(i["qkv"]), state.upload(i["w"]), i["kernel"], state.upload(i["beta_in"]),
+                          state.upload(i["gate_in"]), state.upload(i["a_log"]), state.upload(i["dt_bias"]), d_y)
+    state.sync()
+    assert np.abs(d_y.download(count=hv * dv) - GOLD["decode_step.y"]).max() <= 1e-5
+    hist, ssm = ls.read(0)
+    np.testing.assert_array_equal(hist[-i["conv_dim"]:], GOLD["decode_step.hist_last"])
+    assert np.abs(ssm[:256] - GOLD["decode_step.ssm_head"]).max() <= 1e-5
+    assert abs(float(ssm.astype(np.float64).sum()) - float(GOLD["decode_step.ssm_checksum"][0])) <= 1e-2
+    ls.close()
+    c = META["affine_lm_head"]
+    d_idx, d_val = state.alloc(4 * 8), state.alloc(4 * 8)
+    for bits in (8, 4):
+        packed, scales, biases, x = make_golden.affine_case(c["seed"], bits)
+        d_w = state.upload_affine(packed, scales, biases, bits, c["group"])
+        state.encode_lm_head_argmax_affine(d_w, c["vocab"], c["hidden"], state.upload(x), d_idx, n_rows=1, d_value_out=d_val)
+        state.sync()
+        assert int(d_idx.download(np.int32, 1)[0]) == int(GOLD[f"affine_u{bits}.index"][0])
+        want = float(GOLD[f"affine_u{bits}.logit"][0])
+        assert abs(float(d_val.download(np.float32, 1)[0]) - want) <= 2e-4 * max(1.0, abs(want))
