@@ -772,8 +772,23 @@ def lm_head_leg(sg, st, torch, stream):
             stream.synchronize()
         launches += 3 + reps
         t = e0.elapsed_time(e1) * 1e-3 / reps
+        with torch.cuda.stream(stream):      # the same launches as members of a token chain (see below)
+            st.chain_begin(stream.cuda_stream)
+            for _ in range(3):
+                step()
+            stream.synchronize()
+            e0.record(stream)
+            for _ in range(reps):
+                step()
+            e1.record(stream)
+            st.chain_end()
+            stream.synchronize()
+        launches += 3 + reps
+        t_chain = e0.elapsed_time(e1) * 1e-3 / reps
         want = torch.argmax(x[:rows] @ w.float().T, dim=1).to(torch.int32)
         out[f"rows{rows}"] = {"us": t * 1e6, "hbm_gbs": vocab * hidden * 2 / t / 1e9,
+                              "in_token_chain_us": t_chain * 1e6,
+                              "in_token_chain_hbm_gbs": vocab * hidden * 2 / t_chain / 1e9,
                               "matches_torch_argmax": bool((idx[:rows] == want).all().item())}
     del w
     # the same over affine-quantised weights (the format the reference's models ship in): u8 and u4
@@ -802,6 +817,21 @@ def lm_head_leg(sg, st, torch, stream):
             stream.synchronize()
         launches += 3 + reps
         t = e0.elapsed_time(e1) * 1e-3 / reps
+        # the same launches as members of a token chain, the way the epilogue runs inside a token's
+        # graph: a launch asks for its first weight tiles before it waits for the launch before it
+        with torch.cuda.stream(stream):
+            st.chain_begin(stream.cuda_stream)
+            for _ in range(3):
+                qstep()
+            stream.synchronize()
+            e0.record(stream)
+            for _ in range(reps):
+                qstep()
+            e1.record(stream)
+            st.chain_end()
+            stream.synchronize()
+        launches += 3 + reps
+        t_chain = e0.elapsed_time(e1) * 1e-3 / reps
         nbytes = vocab * hidden * bits // 8 + vocab * (hidden // 64) * 4
         # reference value: dequantise on the device with torch and take the argmax
         shifts = torch.arange(per_word, device=dev, dtype=torch.int32) * bits
@@ -810,6 +840,8 @@ def lm_head_leg(sg, st, torch, stream):
         want = torch.argmax(x[:1] @ deq.T, dim=1).to(torch.int32)
         out[f"affine_u{bits}_g64_rows1"] = {"us": t * 1e6, "weight_bytes": nbytes, "hbm_gbs": nbytes / t / 1e9,
                                             "frac_of_peak": nbytes / t / 1e9 / peak,
+                                            "in_token_chain_us": t_chain * 1e6,
+                                            "in_token_chain_frac_of_peak": nbytes / t_chain / 1e9 / peak,
                                             "matches_torch_argmax": bool((idx[:1] == want).all().item())}
         del packed, scales, biases, codes, deq
     out["launches"] = launches
