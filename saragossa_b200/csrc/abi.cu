@@ -1070,6 +1070,8 @@ int32_t sgk_lm_head_enqueue_argmax(sgk_state* st, void* stream, const void* d_we
   a.index_offset = index_offset;
   a.index_out = d_index_out;
   a.value_out = d_value_out;
+  a.index_mirror = st->lm_index_mirror;
+  st->lm_index_mirror = nullptr;
   cudaStream_t cs = st->pick(stream);
   const bool member = st->chain_member(cs);
   a.pdl_trigger = member ? 1 : 0;
@@ -1128,6 +1130,8 @@ int32_t sgk_lm_head_enqueue_argmax_affine(sgk_state* st, void* stream, const sgk
   a.index_offset = index_offset;
   a.index_out = d_index_out;
   a.value_out = d_value_out;
+  a.index_mirror = st->lm_index_mirror;
+  st->lm_index_mirror = nullptr;
   cudaStream_t cs = st->pick(stream);
   const bool member = st->chain_member(cs);
   a.pdl_trigger = member ? 1 : 0;
@@ -1287,7 +1291,8 @@ int32_t sgk_token_window_create(sgk_state* st, int32_t depth, sgk_token_window**
   w->depth = depth;
   SGK_CUDA(cudaMalloc(&w->d_ring, sizeof(int32_t) * depth));
   SGK_CUDA(cudaMemset(w->d_ring, 0xff, sizeof(int32_t) * depth));
-  SGK_CUDA(cudaHostAlloc(&w->h_ring, sizeof(int32_t) * depth, cudaHostAllocDefault));
+  SGK_CUDA(cudaHostAlloc(&w->h_ring, sizeof(int32_t) * depth, cudaHostAllocMapped));
+  SGK_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&w->h_ring_dev), w->h_ring, 0));
   for (int i = 0; i < depth; ++i) {
     w->h_ring[i] = -1;
     cudaEvent_t e;
@@ -1390,6 +1395,9 @@ int32_t sgk_token_capture(sgk_step* s, sgk_token_window* w, const sgk_token_io* 
              : sgk_embed_enqueue_from_index(static_cast<sgk_state*>(st), stream, io->d_table, io->table_dtype, io->vocab,
                                             io->hidden, d_prev, io->embedding_scale, io->recast_bf16, io->d_x);
     if (rc == SGK_OK) rc = s->enqueue(stream, d_k, d_v, d_q, d_out, sliding_windows, attn_scalar);
+    // the epilogue writes the token's index into the ring slot and into the slot's pinned mirror
+    // itself: no copy node sits between this token's last kernel and the next token's first one
+    if (rc == SGK_OK) st->lm_index_mirror = w->h_ring_dev + slot;
     if (rc == SGK_OK)
       rc = io->lm_affine
                ? sgk_lm_head_enqueue_argmax_affine(static_cast<sgk_state*>(st), stream, io->lm_affine, io->vocab, io->hidden,
@@ -1397,10 +1405,7 @@ int32_t sgk_token_capture(sgk_step* s, sgk_token_window* w, const sgk_token_io* 
                : sgk_lm_head_enqueue_argmax(static_cast<sgk_state*>(st), stream, io->d_lm_weight, io->lm_weight_dtype,
                                             io->vocab, io->hidden, io->d_final, 1, 0, w->d_ring + slot, nullptr);
     st->chain_active = false;
-    if (rc == SGK_OK) {
-      cudaError_t ce = cudaMemcpyAsync(w->h_ring + slot, w->d_ring + slot, sizeof(int32_t), cudaMemcpyDeviceToHost, stream);
-      if (ce != cudaSuccess) rc = fail(SGK_ERR_BACKEND, "token_capture: %s", cudaGetErrorString(ce));
-    }
+    st->lm_index_mirror = nullptr;
     cudaGraph_t graph = nullptr;
     cudaError_t e = cudaStreamEndCapture(stream, &graph);
     for (size_t l = 0; l < s->layers.size(); ++l)

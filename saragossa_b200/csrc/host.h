@@ -62,6 +62,8 @@ struct State {
   cudaStream_t rope_table_stream = nullptr;
   RopeArgs rope_table_args{};
   bool rope_table_in_graph = false;   // a captured graph rewrites the table whenever it runs: never held again
+  // where the NEXT lm_head launch also writes its indices (mapped host memory); taken and cleared by that launch
+  int32_t* lm_index_mirror = nullptr;
   unsigned long long* d_lm_ws = nullptr;  // lm_head argmax: [0..8) best key per row, [8] blocks-done counter; zero between launches
   int64_t launches = 0;  // kernels launched through this state
   // false (default): the caller never has two launches of this state in flight on different
@@ -280,7 +282,8 @@ struct TokenWindow {
   int64_t enqueued = 0;  // tokens submitted so far
   int inflight = 0;      // submitted and not yet popped
   int32_t* d_ring = nullptr;
-  int32_t* h_ring = nullptr;  // pinned mirror, one word per slot
+  int32_t* h_ring = nullptr;  // pinned mirror, one word per slot (mapped: kernels may write it)
+  int32_t* h_ring_dev = nullptr;   // the device's address of h_ring
   std::vector<cudaEvent_t> done;
   ~TokenWindow();
 };

@@ -231,6 +231,11 @@ struct LmHeadArgs {
   int32_t* index_out;  // [n_rows]
   float* value_out;    // [n_rows], may be NULL
   int32_t pdl_trigger, pdl_wait;   // member of a token chain (see GatedDeltaArgs)
+  int32_t* index_mirror;   // mapped host memory that gets the indices too (may be NULL)
+  // 16-row tiles handed out in whole rounds (a multiple of every grid's warp count, set by the launcher
+  // from the SM count alone so that it does not depend on the number of activation rows); the rest
+  // are split across the warps of a block
+  int64_t whole_tiles;
 };
 cudaError_t launch_lm_head_argmax(const LmHeadArgs& a, int sm_count, cudaStream_t stream);
 // The same over an affine-quantised weight (MLX layout, src/quantization.rs:173-238): codes of
@@ -254,6 +259,11 @@ struct LmHeadAffineArgs {
   int32_t* index_out;
   float* value_out;
   int32_t pdl_trigger, pdl_wait;
+  int32_t* index_mirror;   // mapped host memory that gets the indices too (may be NULL)
+  // 16-row tiles handed out in whole rounds (a multiple of every grid's warp count, set by the launcher
+  // from the SM count alone so that it does not depend on the number of activation rows); the rest
+  // are split across the warps of a block
+  int64_t whole_tiles;
 };
 cudaError_t launch_lm_head_argmax_affine(const LmHeadAffineArgs& a, int sm_count, cudaStream_t stream);
 size_t lm_head_affine_smem_bytes(int n_rows, int hidden, int group_size);

@@ -118,7 +118,12 @@ __global__ void __launch_bounds__(LM_THREADS) lm_head_argmax_f32_kernel(LmHeadAr
   if (last_s && tid < a.n_rows) {
     __threadfence();
     const unsigned long long win = atomicExch(a.keys + tid, 0ull);
-    a.index_out[tid] = static_cast<int32_t>(0xffffffffu - uint32_t(win & 0xffffffffu)) + a.index_offset;
+    const int32_t winner = static_cast<int32_t>(0xffffffffu - uint32_t(win & 0xffffffffu)) + a.index_offset;
+    a.index_out[tid] = winner;
+    if (a.index_mirror) {   // the host's copy, written from here: no copy node behind the launch
+      a.index_mirror[tid] = winner;
+      __threadfence_system();
+    }
     if (a.value_out) a.value_out[tid] = unordered_bits(uint32_t(win >> 32));
     if (tid == 0) *a.counter = 0;
   }
@@ -146,7 +151,7 @@ __global__ void __launch_bounds__(LM_THREADS, LM_BLOCKS_PER_SM) lm_head_argmax_b
   __shared__ unsigned int last_s;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   if (a.pdl_trigger) lm_pdl_trigger();
-  if (a.pdl_wait) lm_pdl_wait();
+  if (a.pdl_wait) lm_pdl_wait();   // x comes from the launch before
   const int stride = lm_x_stride_bytes(a.hidden);
   unsigned char* xhi = lm_smem;
   unsigned char* xlo = lm_smem + size_t(a.n_rows) * stride;
@@ -167,7 +172,13 @@ __global__ void __launch_bounds__(LM_THREADS, LM_BLOCKS_PER_SM) lm_head_argmax_b
   const int chunks = (a.hidden + 31) / 32;
   unsigned long long best0 = 0, best1 = 0;  // activation rows 2t and 2t+1; 0 is below every real key
   const int64_t tiles = (a.vocab + 15) / 16;
-  for (int64_t tile = int64_t(blockIdx.x) * LM_WARPS + warp; tile < tiles; tile += int64_t(gridDim.x) * LM_WARPS) {
+  // Every warp takes the same number of whole 16-row tiles; the tiles left over (151 936 rows are
+  // 4.01 tiles per warp: a fifth tile for a few warps would run, pass after pass of DRAM round
+  // trips, while the rest of the GPU is done) are shared out among the blocks afterwards, the
+  // eight warps of a block splitting the columns of one tile.
+  const int64_t n_warps = int64_t(gridDim.x) * LM_WARPS;
+  const int64_t whole = a.whole_tiles;
+  for (int64_t tile = int64_t(blockIdx.x) * LM_WARPS + warp; tile < whole; tile += n_warps) {
     const int64_t r0 = tile * 16 + g, r1 = r0 + 8;
     const uint16_t* w0 = reinterpret_cast<const uint16_t*>(a.w) + (r0 < a.vocab ? r0 : a.vocab - 1) * a.hidden + t * 8;
     const uint16_t* w1 = reinterpret_cast<const uint16_t*>(a.w) + (r1 < a.vocab ? r1 : a.vocab - 1) * a.hidden + t * 8;
@@ -210,6 +221,56 @@ __global__ void __launch_bounds__(LM_THREADS, LM_BLOCKS_PER_SM) lm_head_argmax_b
       best1 = k1 > best1 ? k1 : best1;
     }
   }
+  // the tiles left over: one per block and turn, warp w takes the 32-column chunks w, w + 8, ...
+  __shared__ float left_s[LM_WARPS][16][8];
+  unsigned long long left_best = 0;   // threads 0..127: (row tid / 8 of the tile, activation row tid % 8)
+  for (int64_t tile = whole + blockIdx.x; tile < tiles; tile += gridDim.x) {
+    const int64_t r0 = tile * 16 + g, r1 = r0 + 8;
+    const uint16_t* w0 = reinterpret_cast<const uint16_t*>(a.w) + (r0 < a.vocab ? r0 : a.vocab - 1) * a.hidden + t * 8;
+    const uint16_t* w1 = reinterpret_cast<const uint16_t*>(a.w) + (r1 < a.vocab ? r1 : a.vocab - 1) * a.hidden + t * 8;
+    float h1[4] = {0, 0, 0, 0}, h2[4] = {0, 0, 0, 0}, l1[4] = {0, 0, 0, 0}, l2[4] = {0, 0, 0, 0};
+#pragma unroll 4
+    for (int c = warp; c < chunks; c += LM_WARPS) {
+      const int k = c * 32;
+      const bool valid = k + t * 8 < a.hidden;
+      const uint4 A0 = valid ? __ldcs(reinterpret_cast<const uint4*>(w0 + k)) : make_uint4(0, 0, 0, 0);
+      const uint4 A1 = valid ? __ldcs(reinterpret_cast<const uint4*>(w1 + k)) : make_uint4(0, 0, 0, 0);
+      uint4 xh = make_uint4(0, 0, 0, 0), xl = make_uint4(0, 0, 0, 0);
+      if (has_col) {
+        xh = *reinterpret_cast<const uint4*>(bh + c * 64);
+        xl = *reinterpret_cast<const uint4*>(bl + c * 64);
+      }
+      mma_bf16(h1, A0.x, A1.x, A0.y, A1.y, xh.x, xh.y);
+      mma_bf16(l1, A0.x, A1.x, A0.y, A1.y, xl.x, xl.y);
+      mma_bf16(h2, A0.z, A1.z, A0.w, A1.w, xh.z, xh.w);
+      mma_bf16(l2, A0.z, A1.z, A0.w, A1.w, xl.z, xl.w);
+    }
+    __syncthreads();   // the turn before this one has been added up
+    left_s[warp][g][2 * t] = (h1[0] + h2[0]) + (l1[0] + l2[0]);
+    left_s[warp][g][2 * t + 1] = (h1[1] + h2[1]) + (l1[1] + l2[1]);
+    left_s[warp][g + 8][2 * t] = (h1[2] + h2[2]) + (l1[2] + l2[2]);
+    left_s[warp][g + 8][2 * t + 1] = (h1[3] + h2[3]) + (l1[3] + l2[3]);
+    __syncthreads();
+    if (tid < 128) {
+      const int row = tid >> 3, arow = tid & 7;
+      float sum = left_s[0][row][arow];
+#pragma unroll
+      for (int w = 1; w < LM_WARPS; ++w) sum += left_s[w][row][arow];
+      const int64_t r = tile * 16 + row;
+      if (r < a.vocab && arow < a.n_rows) {
+        const unsigned long long key = pack_key(sum, r);
+        left_best = key > left_best ? key : left_best;
+      }
+    }
+  }
+  // threads 0..127 hold the left-over tiles' best per (row, activation row): best per activation row
+  __shared__ unsigned long long left_best_s[4][8];
+#pragma unroll
+  for (int off = 8; off < 32; off <<= 1) {
+    const unsigned long long o = __shfl_xor_sync(0xffffffffu, left_best, off);
+    left_best = o > left_best ? o : left_best;
+  }
+  if (tid < 128 && lane < 8) left_best_s[warp][lane] = left_best;
 #pragma unroll
   for (int off = 4; off < 32; off <<= 1) {
     const unsigned long long o0 = __shfl_xor_sync(0xffffffffu, best0, off), o1 = __shfl_xor_sync(0xffffffffu, best1, off);
@@ -224,6 +285,7 @@ __global__ void __launch_bounds__(LM_THREADS, LM_BLOCKS_PER_SM) lm_head_argmax_b
   if (tid < a.n_rows) {
     unsigned long long b = best_s[0][tid];
     for (int w = 1; w < LM_WARPS; ++w) b = best_s[w][tid] > b ? best_s[w][tid] : b;
+    for (int w = 0; w < 4; ++w) b = left_best_s[w][tid] > b ? left_best_s[w][tid] : b;
     atomicMax(a.keys + tid, b);
     __threadfence();
   }
@@ -233,7 +295,12 @@ __global__ void __launch_bounds__(LM_THREADS, LM_BLOCKS_PER_SM) lm_head_argmax_b
   if (last_s && tid < a.n_rows) {
     __threadfence();
     const unsigned long long win = atomicExch(a.keys + tid, 0ull);
-    a.index_out[tid] = static_cast<int32_t>(0xffffffffu - uint32_t(win & 0xffffffffu)) + a.index_offset;
+    const int32_t winner = static_cast<int32_t>(0xffffffffu - uint32_t(win & 0xffffffffu)) + a.index_offset;
+    a.index_out[tid] = winner;
+    if (a.index_mirror) {   // the host's copy, written from here: no copy node behind the launch
+      a.index_mirror[tid] = winner;
+      __threadfence_system();
+    }
     if (a.value_out) a.value_out[tid] = unordered_bits(uint32_t(win >> 32));
     if (tid == 0) *a.counter = 0;
   }
@@ -501,7 +568,12 @@ __global__ void __launch_bounds__(LM_THREADS, 2) lm_head_argmax_affine_kernel(Lm
   if (last_s && tid < a.n_rows) {
     __threadfence();
     const unsigned long long win = atomicExch(a.keys + tid, 0ull);
-    a.index_out[tid] = static_cast<int32_t>(0xffffffffu - uint32_t(win & 0xffffffffu)) + a.index_offset;
+    const int32_t winner = static_cast<int32_t>(0xffffffffu - uint32_t(win & 0xffffffffu)) + a.index_offset;
+    a.index_out[tid] = winner;
+    if (a.index_mirror) {   // the host's copy, written from here: no copy node behind the launch
+      a.index_mirror[tid] = winner;
+      __threadfence_system();
+    }
     if (a.value_out) a.value_out[tid] = unordered_bits(uint32_t(win >> 32));
     if (tid == 0) *a.counter = 0;
   }
@@ -580,7 +652,7 @@ __global__ void __launch_bounds__(LM_THREADS, 2) lm_head_argmax_affine_pipe_kern
   // (tile = its number + round * warps), and the tiles left over are shared out among the blocks
   // afterwards, the eight warps of a block splitting the columns of one tile. The load cursor
   // is one pass ahead of the compute cursor, also from one tile to the next.
-  const int64_t rounds = tiles / n_warps;
+  const int64_t rounds = a.whole_tiles / n_warps;
   const int64_t first_tile = int64_t(blockIdx.x) * LM_WARPS + warp;
   const int64_t end_tile = first_tile + rounds * n_warps;   // first tile this warp does not take
   int64_t l_tile = rounds > 0 ? first_tile : end_tile;
@@ -851,10 +923,25 @@ __global__ void __launch_bounds__(LM_THREADS, 2) lm_head_argmax_affine_pipe_kern
   if (last_s && tid < a.n_rows) {
     __threadfence();
     const unsigned long long win = atomicExch(a.keys + tid, 0ull);
-    a.index_out[tid] = static_cast<int32_t>(0xffffffffu - uint32_t(win & 0xffffffffu)) + a.index_offset;
+    const int32_t winner = static_cast<int32_t>(0xffffffffu - uint32_t(win & 0xffffffffu)) + a.index_offset;
+    a.index_out[tid] = winner;
+    if (a.index_mirror) {   // the host's copy, written from here: no copy node behind the launch
+      a.index_mirror[tid] = winner;
+      __threadfence_system();
+    }
     if (a.value_out) a.value_out[tid] = unordered_bits(uint32_t(win >> 32));
     if (tid == 0) *a.counter = 0;
   }
+}
+
+// Tiles handed out in whole rounds: a multiple of the warp count of the largest grid (two blocks per
+// SM), hence of every grid a launch of this vocabulary can get whatever its number of activation
+// rows, so a tile is worked on the same way (and gives the same bits) in all of them. A grid that was
+// cut down to the vocabulary has no whole round.
+static int64_t lm_whole_tiles(int64_t tiles, int sm_count, int blocks) {
+  const int64_t widest = int64_t(sm_count) * LM_BLOCKS_PER_SM * LM_WARPS;
+  if (blocks != sm_count && blocks != sm_count * LM_BLOCKS_PER_SM) return 0;
+  return tiles / widest * widest;
 }
 
 size_t lm_head_affine_smem_bytes(int n_rows, int hidden, int group_size) {
@@ -888,8 +975,10 @@ cudaError_t launch_lm_head_argmax_affine(const LmHeadAffineArgs& a, int sm_count
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return e;
   }
+  LmHeadAffineArgs b = a;
+  b.whole_tiles = lm_whole_tiles(tiles, sm_count, blocks);
   ChainLaunch l(dim3(blocks), dim3(LM_THREADS), smem, stream, a.pdl_wait != 0);
-  return cudaLaunchKernelEx(&l.cfg, kernel, a);
+  return cudaLaunchKernelEx(&l.cfg, kernel, b);
 }
 
 // Row `*index` of an affine-quantised table, dequantised (code * scale + bias), times `scale`
@@ -942,8 +1031,10 @@ cudaError_t launch_lm_head_argmax(const LmHeadArgs& a, int sm_count, cudaStream_
       cudaError_t e = cudaFuncSetAttribute(lm_head_argmax_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
       if (e != cudaSuccess) return e;
     }
+    LmHeadArgs b = a;
+    b.whole_tiles = lm_whole_tiles(tiles, sm_count, blocks);
     ChainLaunch l(dim3(blocks), dim3(LM_THREADS), smem, stream, a.pdl_wait != 0);
-    return cudaLaunchKernelEx(&l.cfg, lm_head_argmax_bf16_kernel, a);
+    return cudaLaunchKernelEx(&l.cfg, lm_head_argmax_bf16_kernel, b);
   }
   const int R = a.n_rows <= 1 ? 1 : a.n_rows <= 2 ? 2 : a.n_rows <= 4 ? 4 : 8;
   per_sm = per_sm > 4 ? 4 : per_sm < 1 ? 1 : per_sm;

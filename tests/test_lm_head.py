@@ -129,6 +129,48 @@ def test_kernel_bf16_logit_is_close_and_independent_of_the_other_rows(gpu_state)
 
 
 @pytest.mark.gpu
+def test_kernel_bf16_large_vocabulary_whole_rounds_and_left_over_tiles(gpu_state):
+    """A vocabulary of two whole rounds of tiles per warp plus left-over tiles and a ragged last
+    tile, at a hidden size where eight activation rows get half the blocks of one row (one block
+    per SM instead of two): planted maxima in the whole rounds, among the left-over tiles and in
+    the last tile are found, and a row's logit has the same bits alone and among eight rows."""
+    import torch
+    import saragossa_b200 as sg
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    widest = sms * 2 * 8
+    vocab, hidden, rows = 16 * (2 * widest + 37) + 3, 4096, 8
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(5)
+    w = (torch.randn(vocab, hidden, device=dev, generator=gen) * 0.02).to(torch.bfloat16)
+    x = torch.randn(rows, hidden, device=dev, generator=gen)
+    planted = [vocab - 1, 16 * 2 * widest + 5, 7, 16 * widest + 3, vocab - 30, 12345, 16 * 2 * widest - 1, 16 * (2 * widest + 36)]
+    for r, row in enumerate(planted):
+        x[r] += w[row].float() * 40.0
+    logits = x.double() @ w.double().T                                  # [rows][vocab]
+    want = torch.argmax(logits, dim=1).cpu().numpy()
+    assert list(want) == planted
+
+    class P:
+        def __init__(self, t):
+            self.ptr = t.data_ptr()
+
+    idx, val = torch.zeros(8, dtype=torch.int32, device=dev), torch.zeros(8, dtype=torch.float32, device=dev)
+    got = {}
+    for n in (1, 8):
+        gpu_state.encode_lm_head_argmax(P(w), sg.KV_BF16, vocab, hidden, P(x), P(idx), n_rows=n, d_value_out=P(val))
+        gpu_state.sync()
+        torch.cuda.synchronize()
+        i, v = idx.cpu().numpy()[:n], val.cpu().numpy()[:n]
+        for r in range(n):
+            assert int(i[r]) == planted[r]
+            exact = float(logits[r, planted[r]].item())
+            assert abs(float(v[r]) - exact) <= 2e-4 * max(1.0, abs(exact))
+        got[n] = v.copy()
+    assert got[1][0].tobytes() == got[8][0].tobytes()
+
+
+@pytest.mark.gpu
 def test_kernel_tie_goes_to_the_lowest_index_and_value_is_returned(gpu_state):
     import saragossa_b200 as sg
     vocab, hidden = 20000, 64
