@@ -215,7 +215,11 @@ __device__ __forceinline__ uint32_t store_u8_row(uint8_t* tile, int hd, int is_v
   return biggest;
 }
 
-__global__ void __launch_bounds__(128) append_tiles_kernel(AppendArgs a) {
+// DIRECT: rows that need no arithmetic across a row (no rope, f32 or bf16 storage) go from registers
+// to the page; that instance is held to 32 registers so that sixteen blocks fit an SM and a launch
+// of a few thousand tiles is ONE wave (with 64 registers it was 1.74 waves: 15.3 us for 50 MB).
+template <bool DIRECT>
+__global__ void __launch_bounds__(128, DIRECT ? 16 : 8) append_tiles_kernel(AppendArgs a) {
   extern __shared__ float smem[];
   const int hd = a.pool.head_dim;
   // staged path only: K rows [16][hd + 4], 1/rms per row [16], rope denominators [128], and for
@@ -239,65 +243,68 @@ __global__ void __launch_bounds__(128) append_tiles_kernel(AppendArgs a) {
   const int rows = static_cast<int>(row_hi - row_lo);
   if (tid == 0) big_s = 0;
 
-  const bool direct = !a.has_rope && a.pool.dtype != KV_U8G32;
-  if (rows > 0 && direct) {
-    // nothing to compute across a row: registers only, no staging
+  if (rows > 0 && DIRECT) {
+    // nothing to compute across a row: registers only, no staging. The block-table entry is asked
+    // for first and looked at only before the stores: the rows' loads do not wait for it.
     const int rin0 = static_cast<int>(row_lo % PAGE_TOKENS);
     const float* kbase = a.k + (int64_t(seq) * a.n_rows + (row_lo - len0)) * kv_dim + head * hd;
     const float* vbase = a.v + (int64_t(seq) * a.n_rows + (row_lo - len0)) * kv_dim + head * hd;
     int32_t page = -1;
     if (page_index < a.pool.table_stride) page = a.pool.tables[int64_t(slot) * a.pool.table_stride + page_index];
-    if (page >= 0 && page < a.num_pages) {
-      uint8_t* ktile = a.pool.base + tile_offset(a.pool, page, a.layer, head, 0);
-      uint8_t* vtile = a.pool.base + tile_offset(a.pool, page, a.layer, head, 1);
-      const int chunks = hd / 8;
-      const int total = 2 * rows * chunks;
-      // four chunks of eight values per thread and pass, every load issued before the first store
-      constexpr int U = 4;
-      for (int base = 0; base < total; base += U * blockDim.x) {
-        float4 x0[U], x1[U];
+    // head_dim is 64, 128 or 256 here: the chunk arithmetic is shifts and masks, not divisions
+    const int chunk_shift = hd == 64 ? 3 : hd == 128 ? 4 : 5;
+    const int chunks = 1 << chunk_shift, half = rows << chunk_shift;
+    const int total = 2 * half;
+    // two chunks of eight values per thread and pass, every load issued before the first store
+    // (sixteen blocks per SM keep 128 KB of loads in flight; four chunks would spill at 32 registers)
+    constexpr int U = 2;
+    for (int base = 0; base < total; base += U * blockDim.x) {
+      float4 x0[U], x1[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int i = base + u * blockDim.x + tid;
-          if (i < total) {
-            const int is_v = i / (rows * chunks), rest = i % (rows * chunks);
-            const int r = rest / chunks, chunk = rest % chunks;
-            const float4* src = reinterpret_cast<const float4*>((is_v ? vbase : kbase) + int64_t(r) * kv_dim + chunk * 8);
-            x0[u] = __ldg(src);
-            x1[u] = __ldg(src + 1);
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int i = base + u * blockDim.x + tid;
-          if (i >= total) continue;
-          const int is_v = i / (rows * chunks), rest = i % (rows * chunks);
-          const int r = rest / chunks, chunk = rest % chunks;
-          uint8_t* tile = is_v ? vtile : ktile;
-          if (a.pool.dtype == KV_F32) {
-            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(tile) + (rin0 + r) * hd + chunk * 8);
-            dst[0] = x0[u];
-            dst[1] = x1[u];
-          } else {
-            const uint4 w = make_uint4(uint32_t(f32_to_bf16_bits(x0[u].x)) | (uint32_t(f32_to_bf16_bits(x0[u].y)) << 16),
-                                       uint32_t(f32_to_bf16_bits(x0[u].z)) | (uint32_t(f32_to_bf16_bits(x0[u].w)) << 16),
-                                       uint32_t(f32_to_bf16_bits(x1[u].x)) | (uint32_t(f32_to_bf16_bits(x1[u].y)) << 16),
-                                       uint32_t(f32_to_bf16_bits(x1[u].z)) | (uint32_t(f32_to_bf16_bits(x1[u].w)) << 16));
-            *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(tile) + bf16_elem_index(rin0 + r, chunk * 8, hd)) = w;
-          }
+      for (int u = 0; u < U; ++u) {
+        const int i = base + u * blockDim.x + tid;
+        if (i < total) {
+          const int is_v = i >= half, rest = is_v ? i - half : i;
+          const int r = rest >> chunk_shift, chunk = rest & (chunks - 1);
+          const float4* src = reinterpret_cast<const float4*>((is_v ? vbase : kbase) + int64_t(r) * kv_dim + chunk * 8);
+          x0[u] = __ldg(src);
+          x1[u] = __ldg(src + 1);
         }
       }
-    } else if (tid == 0) {
-      atomicExch(a.status, DEV_ERR_BAD_PAGE);
+      if (page < 0 || page >= a.num_pages) break;   // uniform over the block; reported below
+      uint8_t* ktile = a.pool.base + tile_offset(a.pool, page, a.layer, head, 0);
+      uint8_t* vtile = a.pool.base + tile_offset(a.pool, page, a.layer, head, 1);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int i = base + u * blockDim.x + tid;
+        if (i >= total) continue;
+        const int is_v = i >= half, rest = is_v ? i - half : i;
+        const int r = rest >> chunk_shift, chunk = rest & (chunks - 1);
+        uint8_t* tile = is_v ? vtile : ktile;
+        if (a.pool.dtype == KV_F32) {
+          float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(tile) + (rin0 + r) * hd + chunk * 8);
+          dst[0] = x0[u];
+          dst[1] = x1[u];
+        } else {
+          const uint4 w = make_uint4(uint32_t(f32_to_bf16_bits(x0[u].x)) | (uint32_t(f32_to_bf16_bits(x0[u].y)) << 16),
+                                     uint32_t(f32_to_bf16_bits(x0[u].z)) | (uint32_t(f32_to_bf16_bits(x0[u].w)) << 16),
+                                     uint32_t(f32_to_bf16_bits(x1[u].x)) | (uint32_t(f32_to_bf16_bits(x1[u].y)) << 16),
+                                     uint32_t(f32_to_bf16_bits(x1[u].z)) | (uint32_t(f32_to_bf16_bits(x1[u].w)) << 16));
+          *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(tile) + bf16_elem_index(rin0 + r, chunk * 8, hd)) = w;
+        }
+      }
     }
-  } else if (rows > 0) {
+    if ((page < 0 || page >= a.num_pages) && tid == 0) atomicExch(a.status, DEV_ERR_BAD_PAGE);
+  } else if (rows > 0 && !DIRECT) {
     // K is worked on in shared memory; V only when it is quantised. K rows sit kstride floats
     // apart: with the rows a whole number of 128-byte lines apart, the sixteen threads that
     // walk one row each for the sequential sums hit one bank sixteen times per step, which made
     // a launch of 2056 tiles shared-memory bound (47.9 us against 15.3 us without rope).
     const int rin0 = static_cast<int>(row_lo % PAGE_TOKENS);
     const bool stage_v = a.pool.dtype == KV_U8G32;
-    const int chunks = hd / 8, total = rows * chunks;
+    // head_dim is 64, 128 or 256 here: the chunk arithmetic is shifts and masks, not divisions
+    const int chunk_shift = hd == 64 ? 3 : hd == 128 ? 4 : 5;
+    const int chunks = 1 << chunk_shift, total = rows << chunk_shift;
     const float* kbase = a.k + (int64_t(seq) * a.n_rows + (row_lo - len0)) * kv_dim + head * hd;
     const float* vbase = a.v + (int64_t(seq) * a.n_rows + (row_lo - len0)) * kv_dim + head * hd;
     int32_t page = -1;
@@ -314,7 +321,7 @@ __global__ void __launch_bounds__(128) append_tiles_kernel(AppendArgs a) {
       for (int u = 0; u < U; ++u) {
         const int i = base + u * blockDim.x + tid;
         if (i < total) {
-          const int r = i / chunks, chunk = i % chunks;
+          const int r = i >> chunk_shift, chunk = i & (chunks - 1);
           const float4* ksrc = reinterpret_cast<const float4*>(kbase + int64_t(r) * kv_dim + chunk * 8);
           const float4* vsrc = reinterpret_cast<const float4*>(vbase + int64_t(r) * kv_dim + chunk * 8);
           k0[u] = __ldg(ksrc);
@@ -327,7 +334,7 @@ __global__ void __launch_bounds__(128) append_tiles_kernel(AppendArgs a) {
       for (int u = 0; u < U; ++u) {
         const int i = base + u * blockDim.x + tid;
         if (i >= total) continue;
-        const int r = i / chunks, chunk = i % chunks;
+        const int r = i >> chunk_shift, chunk = i & (chunks - 1);
         float4* kd = reinterpret_cast<float4*>(ks + r * kstride + chunk * 8);
         kd[0] = k0[u];
         kd[1] = k1[u];
@@ -378,8 +385,11 @@ __global__ void __launch_bounds__(128) append_tiles_kernel(AppendArgs a) {
       __syncthreads();
       // x * inv_rms * w and the rotation of a pair in one pass: a pair's two values are
       // read, scaled and rotated by the same thread
+      // (row, pair) items over the block; the usual power-of-two pair count splits with a shift
+      const int pair_shift = (pairs & (pairs - 1)) == 0 ? 31 - __clz(pairs) : -1;
       for (int i = tid; i < rows * pairs; i += blockDim.x) {
-        const int r = i / pairs, pair = i % pairs;
+        const int r = pair_shift >= 0 ? i >> pair_shift : i / pairs;
+        const int pair = i - r * pairs;
         float* xs = ks + r * kstride;
         float c, s;
         if (a.rope_table != nullptr) {
@@ -403,23 +413,21 @@ __global__ void __launch_bounds__(128) append_tiles_kernel(AppendArgs a) {
         xs[i1] = __fadd_rn(__fmul_rn(first, s), __fmul_rn(second, c));
       }
       // dims the rotation leaves alone are still normalised
-      const int tail = hd - 2 * pairs;
-      for (int i = tid; i < rows * tail; i += blockDim.x) {
-        const int r = i / tail, c = 2 * pairs + i % tail;
-        ks[r * kstride + c] = __fmul_rn(__fmul_rn(ks[r * kstride + c], inv_s[r]), a.knorm_w[c]);
-      }
+      for (int r = 0; r < rows; ++r)
+        for (int c = 2 * pairs + tid; c < hd; c += blockDim.x)
+          ks[r * kstride + c] = __fmul_rn(__fmul_rn(ks[r * kstride + c], inv_s[r]), a.knorm_w[c]);
       __syncthreads();
     }
 
     if (page_ok) {
       if (a.pool.dtype == KV_F32) {
         for (int i = tid; i < rows * (hd / 4); i += blockDim.x) {
-          const int r = i / (hd / 4), c = i % (hd / 4);
+          const int r = i >> (chunk_shift + 1), c = i & (hd / 4 - 1);
           reinterpret_cast<float4*>(reinterpret_cast<float*>(ktile) + (rin0 + r) * hd)[c] = reinterpret_cast<const float4*>(ks + r * kstride)[c];
         }
       } else if (a.pool.dtype == KV_BF16) {
         for (int i = tid; i < total; i += blockDim.x) {
-          const int r = i / chunks, chunk = i % chunks;
+          const int r = i >> chunk_shift, chunk = i & (chunks - 1);
           const float4 x0 = reinterpret_cast<const float4*>(ks + r * kstride + chunk * 8)[0];
           const float4 x1 = reinterpret_cast<const float4*>(ks + r * kstride + chunk * 8)[1];
           const uint4 w = make_uint4(uint32_t(f32_to_bf16_bits(x0.x)) | (uint32_t(f32_to_bf16_bits(x0.y)) << 16),
@@ -514,7 +522,8 @@ cudaError_t launch_append_rows(const AppendArgs& a, int n_seq, cudaStream_t stre
     // tile pair being put together only where V is quantised
     size_t smem = (size_t(PAGE_TOKENS) * (hd + 4) + PAGE_TOKENS + 128) * sizeof(float);
     if (a.pool.dtype == KV_U8G32) smem += size_t(PAGE_TOKENS) * hd * sizeof(float) + 2 * size_t(a.pool.tile_bytes);
-    append_tiles_kernel<<<grid, 128, smem, stream>>>(a);
+    if (!a.has_rope && a.pool.dtype != KV_U8G32) append_tiles_kernel<true><<<grid, 128, 0, stream>>>(a);
+    else append_tiles_kernel<false><<<grid, 128, smem, stream>>>(a);
     return cudaGetLastError();
   }
   dim3 grid(a.pool.kv_heads, a.n_rows, n_seq);
