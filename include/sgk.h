@@ -423,7 +423,8 @@ int32_t sgk_token_window_drain(sgk_token_window* w);
  * sgk_token_capture records, for every slot of the window's ring, ONE CUDA graph:
  *   sgk_embed_enqueue_from_index (index of the previous slot -> io.d_x)
  *   the step's layers (as sgk_step_capture: d_k, d_v, d_q in, d_out out, cursors on the device)
- *   sgk_lm_head_enqueue_argmax (io.d_final -> this slot) and the slot's copy to pinned memory
+ *   sgk_lm_head_enqueue_argmax (io.d_final -> this slot; the kernel writes the index into the slot's
+ *   pinned host mirror as well, so no copy node follows the token's last launch)
  * as one token chain (every launch lets the next one start early). What lies between these
  * pieces in a model (projections, MLP) is the caller's and belongs in the same capture when it
  * exists; here the pointers are fixed device buffers. sgk_token_seed puts the first input token
