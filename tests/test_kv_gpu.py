@@ -485,6 +485,39 @@ def test_prompt_layers_share_one_rope_table(state, rope_dims, interleaved):
     assert state.launches() > launches0
 
 
+def test_bulk_u8_quantiser_on_ties_and_near_ties(state):
+    """Codes, scales and biases of the bulk append are the oracle's bit for bit (IEEE division, half
+    to even): on normal data, and on rows built to sit on and around the rounding boundaries of
+    every code, with scales that are and are not powers of two."""
+    kv_heads, hd = 2, 256
+    kv_dim = kv_heads * hd
+    n = 1024
+    k = sgo.fill_normal8(n * kv_dim, 77, 0).reshape(n, kv_dim).copy()
+    v = sgo.fill_normal8(n * kv_dim, 77, 1).reshape(n, kv_dim).copy()
+    # crafted groups: min 0 and max 255 * s pin bias = 0 and scale = s (bf16-exact values of s); the
+    # other 30 values sit at (c + 0.5) * s * (1 + e) for small e of both signs
+    rng = np.random.default_rng(3)
+    scales = np.array([2.0 ** -7, 1.5 * 2.0 ** -7, 1.375 * 2.0 ** -3, 3.0, 0.0087890625], np.float32)
+    eps = np.array([0.0, 2.0 ** -23, -(2.0 ** -23), 2.0 ** -21, -(2.0 ** -21), 2.0 ** -18, -(2.0 ** -18), 1e-4, -1e-4], np.float32)
+    for r in range(0, n, 2):
+        for g in range(kv_dim // 32):
+            s_ = scales[(r // 2 + g) % len(scales)]
+            c = rng.integers(0, 255, size=32).astype(np.float32)
+            e = eps[rng.integers(0, len(eps), size=32)]
+            row = ((c + np.float32(0.5)) * s_ * (np.float32(1.0) + e)).astype(np.float32)
+            row[0], row[1] = np.float32(0.0), np.float32(255.0) * s_
+            k[r, g * 32:(g + 1) * 32] = row
+    kv = state.full_attention(n, 4, kv_heads, hd, sg.KV_U8G32)
+    kv.seed(k, v, n)                       # one multi-row launch: the bulk kernel
+    kc, ks, kb, vc, vs, vb = kv.gather_rows_u8()
+    for r in range(n):
+        codes, scale, bias = sgo.quantize_row_u8(k[r])
+        assert np.array_equal(kc[r], codes) and np.array_equal(ks[r], scale) and np.array_equal(kb[r], bias), r
+        codes, scale, bias = sgo.quantize_row_u8(v[r])
+        assert np.array_equal(vc[r], codes) and np.array_equal(vs[r], scale) and np.array_equal(vb[r], bias), r
+    kv.close()
+
+
 # ---- long context, paged, batched: against the oracle on seeded normal inputs ------------------
 def _normal_kv(n, kv_dim, seed, stream):
     return sgo.fill_normal8(n * kv_dim, seed, stream).reshape(n, kv_dim)
